@@ -1,0 +1,262 @@
+"""ctypes/numpy front end of the CPU oracle (oracle/liboracle.so).
+
+Test infrastructure: imported by tests/, by the smoke check and by the benchmark's
+CPU-baseline leg only.  The product package never imports this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build(force=False):
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "vla_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(build())
+        _LIB.orc_num_threads.restype = C.c_int
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def num_threads():
+    return int(lib().orc_num_threads())
+
+
+def f32_to_bf16_bits(x):
+    x = _c(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().orc_f32_to_bf16(_p(x), C.c_int64(x.size), _p(out))
+    return out
+
+
+def bf16_bits_to_f32(x):
+    x = _c(x, np.uint16)
+    out = np.empty(x.shape, np.float32)
+    lib().orc_bf16_to_f32(_p(x), C.c_int64(x.size), _p(out))
+    return out
+
+
+def bf16_round(x):
+    return bf16_bits_to_f32(f32_to_bf16_bits(x))
+
+
+def ternarize(w):
+    w = _c(w, np.float32)
+    t = np.empty(w.shape, np.int8)
+    am = C.c_float()
+    lib().orc_ternarize(_p(w), C.c_int64(w.size), _p(t), C.byref(am))
+    return t, np.float32(am.value)
+
+
+def pack_ladder_int2(t):
+    t = _c(t, np.int8)
+    n, k = t.shape
+    out = np.empty(n * k // 4, np.uint8)
+    rc = lib().orc_pack_ladder_int2(_p(t), C.c_int64(n), C.c_int64(k), _p(out))
+    if rc:
+        raise ValueError("N must be a multiple of 16 and K of 128")
+    return out
+
+
+def unpack_ladder_int2(packed, n, k):
+    packed = _c(packed, np.uint8)
+    out = np.empty((n, k), np.int8)
+    rc = lib().orc_unpack_ladder_int2(_p(packed), C.c_int64(n), C.c_int64(k), _p(out))
+    if rc:
+        raise ValueError("N must be a multiple of 16 and K of 128")
+    return out
+
+
+def act_quant(x):
+    x = _c(x, np.float32)
+    m, k = x.shape
+    q = np.empty((m, k), np.int8)
+    s = np.empty(m, np.float32)
+    lib().orc_act_quant(_p(x), m, k, _p(q), _p(s))
+    return q, s
+
+
+def gemm_i8_i32(a, w):
+    a, w = _c(a, np.int8), _c(w, np.int8)
+    m, k = a.shape
+    n = w.shape[0]
+    acc = np.empty((m, n), np.int32)
+    lib().orc_gemm_i8_i32(_p(a), _p(w), m, n, k, _p(acc))
+    return acc
+
+
+def gemm_i8_i32_rows(a, w, rows):
+    a, w = _c(a, np.int8), _c(w, np.int8)
+    rows = _c(rows, np.int32)
+    k = a.shape[1]
+    n = w.shape[0]
+    acc = np.empty((rows.size, n), np.int32)
+    lib().orc_gemm_i8_i32_rows(_p(a), _p(w), _p(rows), int(rows.size), n, k, _p(acc))
+    return acc
+
+
+def ternary_gemm_i32(a, packed, n):
+    a = _c(a, np.int8)
+    packed = _c(packed, np.uint8)
+    m, k = a.shape
+    acc = np.empty((m, n), np.int32)
+    rc = lib().orc_ternary_gemm_i32(_p(a), _p(packed), m, n, k, _p(acc))
+    if rc:
+        raise ValueError("bad ternary gemm shape")
+    return acc
+
+
+def ternary_epilogue(acc, s, ws):
+    acc = _c(acc, np.int32)
+    s, ws = _c(s, np.float32), _c(ws, np.float32)
+    m, n = acc.shape
+    out = np.empty((m, n), np.uint16)
+    lib().orc_ternary_epilogue(_p(acc), _p(s), _p(ws), int(ws.size), m, n, _p(out))
+    return out
+
+
+def linear(x, w, b=None):
+    x, w = _c(x, np.float32), _c(w, np.float32)
+    t, i = x.shape
+    o = w.shape[0]
+    y = np.empty((t, o), np.float32)
+    bb = _c(b, np.float32) if b is not None else None
+    lib().orc_linear(_p(x), _p(w), _p(bb) if bb is not None else None, t, i, o, _p(y))
+    return y
+
+
+def rmsnorm(x, w, eps):
+    x = _c(x, np.float32)
+    t, h = x.shape
+    y = np.empty_like(x)
+    ww = _c(w, np.float32) if w is not None else None
+    lib().orc_rmsnorm(_p(x), _p(ww) if ww is not None else None, t, h, C.c_float(eps), _p(y))
+    return y
+
+
+def rope_neox(x, pos, base=10000.0):
+    """x: [T][heads][hd]; returns a rotated copy."""
+    x = _c(x, np.float32).copy()
+    pos = _c(pos, np.int32)
+    t, heads, hd = x.shape
+    lib().orc_rope_neox(_p(x), _p(pos), t, heads, hd, C.c_float(base))
+    return x
+
+
+def rope_table(pos, hd, base=10000.0):
+    pos = _c(pos, np.int32)
+    cos_t = np.empty((pos.size, hd // 2), np.float32)
+    sin_t = np.empty((pos.size, hd // 2), np.float32)
+    lib().orc_rope_table(_p(pos), int(pos.size), hd, C.c_float(base), _p(cos_t), _p(sin_t))
+    return cos_t, sin_t
+
+
+def time_emb(t, dim, min_p, max_p):
+    out = np.empty(dim, np.float32)
+    lib().orc_time_emb(C.c_double(t), dim, C.c_double(min_p), C.c_double(max_p), _p(out))
+    return out
+
+
+MASK_NONE, MASK_PI0, MASK_SMOLVLA = 0, 1, 2
+
+
+def attention(q, k, v, p, mode, pad_start=0, pad_end=0):
+    """q: [S][n_q][hd]; k, v: [Tkv][n_kv][hd] -> [S][n_q*hd]."""
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    s, n_q, hd = q.shape
+    tkv, n_kv, _ = k.shape
+    out = np.empty((s, n_q * hd), np.float32)
+    lib().orc_attention(_p(q), _p(k), _p(v), s, tkv, n_q, n_kv, hd, p, mode, pad_start, pad_end, _p(out))
+    return out
+
+
+def qkv_rope(x, ln_w, wqkv, pos, n_q, n_kv, hd, eps, rope_base=10000.0, act_bf16=False):
+    x, ln_w, wqkv = _c(x, np.float32), _c(ln_w, np.float32), _c(wqkv, np.float32)
+    pos = _c(pos, np.int32)
+    s, h = x.shape
+    q = np.empty((s, n_q, hd), np.float32)
+    k = np.empty((s, n_kv, hd), np.float32)
+    v = np.empty((s, n_kv, hd), np.float32)
+    lib().orc_qkv_rope(_p(x), _p(ln_w), _p(wqkv), _p(pos), s, h, n_q, n_kv, hd, C.c_float(eps),
+                       C.c_float(rope_base), int(act_bf16), _p(q), _p(k), _p(v))
+    return q, k, v
+
+
+class DenoiseCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "model", "n_layers", "H", "n_q", "n_kv", "hd", "inter", "P", "chunk", "A", "state_dim", "T",
+        "pos_base", "pad_start", "pad_end", "self_every", "act_bf16")] + [
+        ("rms_eps", C.c_float), ("rope_base", C.c_float), ("min_period", C.c_double), ("max_period", C.c_double)]
+
+
+class DenoiseWeights(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_void_p)) for n in (
+        "ln_in", "Wqkv", "Wo", "ln_post", "Wgate", "Wup", "Wdown")] + [
+        (n, C.c_void_p) for n in ("W_sp", "b_sp", "W_ain", "b_ain", "W_at1", "b_at1", "W_at2", "b_at2",
+                                   "out_norm", "W_aout", "b_aout")]
+
+
+def _ptr_array(arrs):
+    keep = [_c(a, np.float32) for a in arrs]
+    arr = (C.c_void_p * len(keep))(*[a.ctypes.data for a in keep])
+    return arr, keep
+
+
+class DenoiseModel:
+    """Holds float32 weights (dict of numpy arrays / lists per layer) for orc_denoise_loop."""
+
+    def __init__(self, cfg: dict, weights: dict):
+        self.cfg = DenoiseCfg(**cfg)
+        self._keep = []
+        w = DenoiseWeights()
+        for name in ("ln_in", "Wqkv", "Wo", "ln_post", "Wgate", "Wup", "Wdown"):
+            arr, keep = _ptr_array(weights[name])
+            self._keep += [arr, keep]
+            setattr(w, name, C.cast(arr, C.POINTER(C.c_void_p)))
+        for name in ("W_sp", "b_sp", "W_ain", "b_ain", "W_at1", "b_at1", "W_at2", "b_at2", "out_norm",
+                     "W_aout", "b_aout"):
+            a = weights.get(name)
+            if a is None:
+                setattr(w, name, None)
+            else:
+                a = _c(a, np.float32)
+                self._keep.append(a)
+                setattr(w, name, a.ctypes.data)
+        self.w = w
+
+    def denoise(self, kp, vp, state, x0):
+        """kp, vp: lists (n_layers) of [P][n_kv][hd]; state [state_dim]; x0 [chunk][A]."""
+        ka, kk = _ptr_array(kp)
+        va, vk = _ptr_array(vp)
+        x0 = _c(x0, np.float32)
+        st = _c(state if state is not None else np.zeros(self.cfg.state_dim), np.float32)
+        out = np.empty_like(x0)
+        rc = lib().orc_denoise_loop(C.byref(self.cfg), C.byref(self.w), ka, va, _p(st), _p(x0), _p(out))
+        assert rc == 0
+        return out
+
+    def expert_layer(self, l, h, kp, vp, is_self=True):
+        h = _c(h, np.float32).copy()
+        kp, vp = _c(kp, np.float32), _c(vp, np.float32)
+        lib().orc_expert_layer(C.byref(self.cfg), C.byref(self.w), l, _p(h), h.shape[0], _p(kp), _p(vp),
+                               int(is_self))
+        return h

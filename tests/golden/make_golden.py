@@ -1,0 +1,75 @@
+"""Regenerates the golden fixtures in this directory from the reference itself.
+
+Runs only where the reference tree is mounted (it is never needed at test time):
+  python tests/golden/make_golden.py [/path/to/reference]
+
+* ladder_pack.npz  -- scripts/convert_bitvla_to_gguf.py (imported as a module):
+                      weight_quant_to_ternary() and pack_ladder_int2() applied to
+                      seeded random matrices.
+* time_emb.npz     -- src/layers/embed.h sinusoidal_time_emb(), through the driver
+                      oracle/_ref/time_emb_ref (built by oracle/Makefile).
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+
+def ladder(ref):
+    import torch
+
+    sys.path.insert(0, os.path.join(ref, "scripts"))
+    import convert_bitvla_to_gguf as conv
+
+    out = {}
+    rng = np.random.default_rng(20240521)
+    for i, (n, k) in enumerate([(16, 128), (32, 256), (48, 384), (64, 128)]):
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        if i == 3:
+            w[:] = 1e-7  # exercises the absmean floor of 1e-5
+        tern, absmean = conv.weight_quant_to_ternary(torch.from_numpy(w))
+        packed = conv.pack_ladder_int2(tern)
+        out[f"w{i}"] = w
+        out[f"tern{i}"] = tern.astype(np.int8)
+        out[f"absmean{i}"] = np.float32(absmean)
+        out[f"packed{i}"] = packed.astype(np.uint8)
+    # fused projection: per-part scales, rows concatenated
+    parts = [torch.from_numpy((rng.standard_normal((16, 128)) * s).astype(np.float32)) for s in (0.02, 0.05)]
+    packed, scales = conv.pack_fused_projection(parts)
+    out["fused_w0"], out["fused_w1"] = parts[0].numpy(), parts[1].numpy()
+    out["fused_packed"], out["fused_scales"] = packed.astype(np.uint8), scales.astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "ladder_pack.npz"), **out)
+
+
+def time_emb():
+    exe = os.path.join(ROOT, "oracle", "_ref", "time_emb_ref")
+    out = {}
+    cases = []
+    for dim in (720, 1024, 2, 8):
+        for step in range(10):
+            # pi0 evaluates the timestep in float32, SmolVLA in double
+            dt = np.float32(-1.0) / np.float32(10)
+            cases.append((float(np.float32(1.0) + np.float32(step) * dt), dim, 4e-3, 4.0))
+            cases.append((1.0 + float(step) * float(dt), dim, 4e-3, 4.0))
+    args, vals = [], []
+    for t, dim, mn, mx in cases:
+        txt = subprocess.run([exe, repr(t), str(dim), repr(mn), repr(mx)], check=True, capture_output=True, text=True).stdout
+        bits = np.array([int(x, 16) for x in txt.split()], dtype=np.uint32)
+        assert bits.size == dim
+        args.append((t, dim, mn, mx))
+        vals.append(bits.view(np.float32))
+    out["args"] = np.array(args, dtype=np.float64)
+    out["offsets"] = np.cumsum([0] + [v.size for v in vals]).astype(np.int64)
+    out["values"] = np.concatenate(vals)
+    np.savez_compressed(os.path.join(HERE, "time_emb.npz"), **out)
+
+
+if __name__ == "__main__":
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ladder(ref)
+    time_emb()
+    print("golden fixtures written to", HERE)
