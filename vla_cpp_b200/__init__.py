@@ -1,0 +1,15 @@
+"""vla_cpp_b200 -- host-side mirror of the vla.cpp denoise-step interfaces over libvla_b200.so.
+
+The library is hand-written sm_100a CUDA behind a C ABI (include/vla_b200.h).  This
+package only loads it and marshals device pointers; there is no CPU or PyTorch fallback:
+importing works anywhere (so the exported symbols can be checked), but every compute
+call needs the built library and a B200.
+"""
+from .api import (  # noqa: F401
+    LIB_PATH,
+    VlaB200Error,
+    act_quant,
+    device_status,
+    lib,
+    ternary_linear,
+)

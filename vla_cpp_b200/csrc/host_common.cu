@@ -1,0 +1,96 @@
+#include "host_common.h"
+
+#include <cstring>
+#include <mutex>
+
+namespace vb {
+
+__device__ int g_dev_status;
+
+static thread_local char g_last_error[256] = "";
+
+int cuda_fail(cudaError_t e, const char *what) {
+    std::snprintf(g_last_error, sizeof(g_last_error), "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e),
+                  what);
+    return VLAB200_ERR_CUDA;
+}
+
+int *device_status_ptr() {
+    static int *ptrs[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_dev_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<int *>(p);
+    }
+    return ptrs[dev];
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode() {
+    static encode_tiled_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+    });
+    return fn;
+}
+
+int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swz) {
+    encode_tiled_fn fn = get_encode();
+    if (!fn) {
+        std::snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled entry point unavailable");
+        return VLAB200_ERR_CUDA;
+    }
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[5];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i + 1 < rank) gstr[i] = strides_bytes[i];
+    }
+    CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void *>(base), gdim, gstr, bx, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        std::snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return VLAB200_ERR_CUDA;
+    }
+    return VLAB200_OK;
+}
+
+}  // namespace vb
+
+extern "C" {
+
+const char *vlab200_last_error(void) { return vb::g_last_error; }
+
+int32_t vlab200_abi_version(void) { return VLAB200_ABI_VERSION; }
+
+int32_t vlab200_device_status(int32_t *out, int32_t reset) {
+    if (!out) return VLAB200_ERR_ARG;
+    int *p = vb::device_status_ptr();
+    if (!p) return vb::cuda_fail(cudaGetLastError(), "device_status_ptr");
+    VB_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    VB_CUDA(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
+    *out = v;
+    if (reset && v != 0) VB_CUDA(cudaMemset(p, 0, sizeof(int)));
+    return VLAB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,30 @@
+// Host-side helpers shared by the translation units of libvla_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/vla_b200.h"
+
+namespace vb {
+
+// Pointer to the per-device status word (device memory) for the current device,
+// or nullptr when no CUDA device can be used.
+int *device_status_ptr();
+
+// Records and returns a CUDA failure as VLAB200_ERR_CUDA.
+int cuda_fail(cudaError_t e, const char *what);
+
+#define VB_CUDA(expr)                                        \
+    do {                                                     \
+        cudaError_t _e = (expr);                             \
+        if (_e != cudaSuccess) return vb::cuda_fail(_e, #expr); \
+    } while (0)
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
+// dims/strides innermost first; strides_bytes has rank-1 entries (dim 1 .. rank-1).
+int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swz);
+
+}  // namespace vb
