@@ -43,6 +43,72 @@ VLAB200_API const char *vlab200_last_error(void);
  * failure; 101..104 = a bounded wait inside a kernel ran out).  reset != 0 clears it. */
 VLAB200_API int32_t vlab200_device_status(int32_t *out, int32_t reset);
 
+/* ------------------------------------------------- prefix-KV store, QKV+RoPE, attention */
+
+/* bf16 K/V pages, written once per observation for the prefix and appended per denoise
+ * step for the suffix.  Layout of k_pages / v_pages (caller-allocated device memory,
+ * zero-initialised, 16-byte aligned, vlab200_kv_store_bytes() each):
+ *     [n_layers][n_obs][n_kv][cap][head_dim]      (one contiguous page per layer, observation
+ *                                                  and kv head; rows are tokens)
+ * Rows [0, prefix_len) hold the prefix (K already rotated with prefix positions), rows
+ * [prefix_len, prefix_len + S) the current step's suffix.  The reference keeps the same data
+ * as F32 graph tensors [hd, n_kv, P] per layer and concatenates the suffix onto a copy of it
+ * every layer-step (src/models/pi0.cpp:191-201, src/models/smolvla.cpp:793-794,832-833). */
+typedef struct {
+    void *k_pages;
+    void *v_pages;
+    int32_t n_layers;
+    int32_t n_obs;
+    int32_t n_kv;       /* kv heads */
+    int32_t head_dim;   /* 64, 128 or 256 */
+    int32_t cap;        /* token rows per page, >= prefix_len + suffix length */
+    int32_t prefix_len; /* P */
+} vlab200_kv_store;
+
+/* Bytes of ONE of the two page arrays; -1 on a non-positive dimension. */
+VLAB200_API int64_t vlab200_kv_store_bytes(int32_t n_layers, int32_t n_obs, int32_t n_kv, int32_t head_dim,
+                                           int32_t cap);
+
+/* Writes the prefix rows of `layer` for observations [obs0, obs0 + n_obs) from the prefill's
+ * K, V: float32 [n_obs][prefix_len][n_kv][head_dim] (ggml [hd, n_kv, P] per observation), K
+ * already rotated.  Replaces the k_out / v_out hand-off of build_gemma_layer / build_vlm_layer
+ * (src/models/pi0.cpp:191-194, src/models/smolvla.cpp:793-794). */
+VLAB200_API int32_t vlab200_kv_store_write(const vlab200_kv_store *st, int32_t layer, int32_t obs0, int32_t n_obs,
+                                           const float *K, const float *V, void *stream);
+
+/* cos/sin tables [S][head_dim/2] (float32) for positions pos0 .. pos0+S-1 of a plain NeoX
+ * RoPE with frequency base `base` (ggml_rope_ext call of src/models/smolvla.cpp:759-766). */
+VLAB200_API int32_t vlab200_rope_table(float *cos_out, float *sin_out, int32_t pos0, int32_t S, int32_t head_dim,
+                                       float base, void *stream);
+
+/* Fused RMSNorm -> Q/K/V projection -> NeoX RoPE -> KV append for the suffix tokens of ALL
+ * observations of the store (M = n_obs * S rows):
+ *   xn = x * rsqrt(mean(x^2) + eps) * ln_w;  [q | k | v] = Wqkv xn;  q, k rotated;
+ *   q_out bf16 [n_obs][n_q][S][head_dim];  k, v -> page rows prefix_len + tok.
+ * x: [n_obs*S][H], bf16 or (x_is_f32) float32.  Wqkv: bf16 [(n_q + 2 n_kv) head_dim][H], rows
+ * ordered q heads, k heads, v heads.  project_kv == 0 projects q only (SmolVLA cross-attention
+ * layers, src/models/smolvla.cpp:870-873; Wqkv then holds the q rows only).  H % 8 == 0.
+ * Replaces the rms_norm/mul, three mul_mat, two rope and two concat nodes of
+ * src/models/pi0.cpp:170-201 and src/models/smolvla.cpp:820-833. */
+VLAB200_API int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const void *x,
+                                            int32_t x_is_f32, const float *ln_w, const void *wqkv_bf16,
+                                            const float *rope_cos, const float *rope_sin, float eps, int32_t S,
+                                            int32_t H, int32_t n_q, int32_t project_kv, void *q_out,
+                                            void *stream);
+
+/* out[obs][tok][h*hd ..] = softmax(q K^T / sqrt(hd) + mask) V over page rows [0, kv_len) of
+ * `layer`, query head h reading kv head h / (n_q / n_kv).  q: bf16 [n_obs][n_q][S][hd];
+ * out: bf16 [n_obs][S][n_q*hd].  mask_mode: 0 = all rows < kv_len visible; 1 = pi0 rule
+ * (suffix row 0 sees only suffix column 0, other rows every column; src/models/pi0.cpp:640-651);
+ * 2 = causal over the suffix (src/models/smolvla.cpp:1655-1664).  pad_ranges (optional, int32
+ * [n_obs][2]) masks prefix columns [lo, hi) per observation (padded language slots).
+ * Implemented for head_dim 64, kv_len <= 256, (n_q / n_kv) * S <= 256.
+ * Replaces ggml_flash_attn_ext / mul_mat+soft_max_ext+mul_mat at src/models/pi0.cpp:204-223,
+ * src/models/smolvla.cpp:835-842,874-881 (src/layers/attn.h:38-57). */
+VLAB200_API int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, const void *q, void *out,
+                                      int32_t S, int32_t n_q, int32_t kv_len, int32_t mask_mode,
+                                      const int32_t *pad_ranges, void *stream);
+
 /* ---------------------------------------------------------------- BitVLA ternary path */
 
 /* Per-token absmax int8 quantisation: scales[m] = 127 / max(max_k |x[m][k]|, 1e-5),

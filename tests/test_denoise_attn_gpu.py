@@ -1,0 +1,213 @@
+"""GPU parity of the prefix-KV store, fused QKV+RoPE+append and attention kernels, through
+the C ABI.  Tolerance (from the build's contract): rel-L2 <= 2e-2 per attention / QKV output
+in bf16 against the float32 oracle; the KV page writer is bit-exact (a bf16 rounding)."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import bf16_bits, bits_to_bf16_tensor, rel_l2, require_cuda, to_dev
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+SMOL = dict(H=720, n_q=15, n_kv=5, hd=64, S=51, P=177, eps=1e-5)   # isolated-op config (bf16)
+PI0 = dict(H=1024, n_q=8, n_kv=1, hd=256, S=51, P=816, eps=1e-6)
+
+
+def bf16_tensor(oracle, a):
+    return bits_to_bf16_tensor(oracle.f32_to_bf16_bits(a))
+
+
+def from_bf16(oracle, t):
+    return oracle.bf16_bits_to_f32(bf16_bits(t))
+
+
+def test_kv_store_write_is_a_bf16_rounding(oracle):
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(0)
+    L, B, n_kv, hd, P, S = 3, 4, 5, 64, 37, 6
+    st = vb.KvStore(L, B, n_kv, hd, P, S)
+    k = rng.standard_normal((B, P, n_kv, hd)).astype(np.float32)
+    v = rng.standard_normal((B, P, n_kv, hd)).astype(np.float32)
+    st.write_prefix(1, to_dev(k), to_dev(v))
+    st.write_prefix(2, to_dev(k[1:3]), to_dev(v[1:3]), obs0=2)
+    assert vb.device_status() == 0
+    kp = bf16_bits(st.k)  # [L][B][n_kv][cap][hd]
+    vp = bf16_bits(st.v)
+    assert np.array_equal(kp[1, :, :, :P], oracle.f32_to_bf16_bits(k).transpose(0, 2, 1, 3))
+    assert np.array_equal(vp[1, :, :, :P], oracle.f32_to_bf16_bits(v).transpose(0, 2, 1, 3))
+    assert np.array_equal(kp[2, 2:4, :, :P], oracle.f32_to_bf16_bits(k[1:3]).transpose(0, 2, 1, 3))
+    assert not kp[0].any() and not kp[1, :, :, P:].any() and not kp[2, :2].any()
+
+
+def test_rope_table(oracle):
+    require_cuda()
+    import vla_cpp_b200 as vb
+
+    for hd, pos0, S in [(64, 177, 51), (256, 816, 51), (64, 0, 50)]:
+        c, s = vb.rope_table(pos0, S, hd)
+        rc, rs = oracle.rope_table(np.arange(pos0, pos0 + S), hd)
+        np.testing.assert_allclose(c.cpu().numpy(), rc, atol=3e-4)  # float32 angle ulp at pos ~870 is 6e-5
+        np.testing.assert_allclose(s.cpu().numpy(), rs, atol=3e-4)
+
+
+def qkv_case(oracle, cfg, n_obs, seed, x_f32=False, project_kv=True, ln_rand=True):
+    import torch
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(seed)
+    H, n_q, n_kv, hd, S, P = (cfg[k] for k in ("H", "n_q", "n_kv", "hd", "S", "P"))
+    n_rows = (n_q + (2 * n_kv if project_kv else 0)) * hd
+    x = rng.standard_normal((n_obs * S, H)).astype(np.float32)
+    if not x_f32:
+        x = oracle.bf16_round(x)
+    w = oracle.bf16_round((rng.standard_normal((n_rows, H)) * 0.02).astype(np.float32))
+    ln = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32) if ln_rand else np.ones(H, np.float32)
+    st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
+    rope = vb.rope_table(P, S, hd)
+    xd = to_dev(x) if x_f32 else bf16_tensor(oracle, x)
+    q = vb.qkv_rope_append(st, 1, xd, to_dev(ln), bf16_tensor(oracle, w), rope, cfg["eps"], S, n_q,
+                           project_kv=project_kv)
+    assert vb.device_status() == 0
+    pos = np.arange(P, P + S).astype(np.int32)
+    q_gpu = from_bf16(oracle, q)            # [n_obs][n_q][S][hd]
+    k_gpu = from_bf16(oracle, st.k[1])      # [n_obs][n_kv][cap][hd]
+    v_gpu = from_bf16(oracle, st.v[1])
+    errs = []
+    for b in range(n_obs):
+        xb = x[b * S:(b + 1) * S]
+        if project_kv:
+            rq, rk, rv = oracle.qkv_rope(xb, ln, w, pos, n_q, n_kv, hd, cfg["eps"])
+            errs.append(rel_l2(k_gpu[b, :, P:P + S].transpose(1, 0, 2), rk))
+            errs.append(rel_l2(v_gpu[b, :, P:P + S].transpose(1, 0, 2), rv))
+        else:
+            rq = oracle.rope_neox(oracle.linear(oracle.rmsnorm(xb, ln, cfg["eps"]), w).reshape(S, n_q, hd), pos)
+        errs.append(rel_l2(q_gpu[b].transpose(1, 0, 2), rq))
+    assert not k_gpu[:, :, :P].any() and not from_bf16(oracle, st.k[0]).any()  # only suffix rows of layer 1 touched
+    if not project_kv:
+        assert not k_gpu.any() and not v_gpu.any()
+    return max(errs)
+
+
+@pytest.mark.parametrize("n_obs", [1, 3, 16])
+def test_qkv_rope_append_smolvla_shape(oracle, n_obs):
+    require_cuda()
+    assert qkv_case(oracle, SMOL, n_obs, seed=10 + n_obs) < TOL
+
+
+def test_qkv_rope_append_f32_input_and_unit_norm(oracle):
+    require_cuda()
+    assert qkv_case(oracle, SMOL, 2, seed=21, x_f32=True) < TOL
+    assert qkv_case(oracle, SMOL, 2, seed=22, ln_rand=False) < TOL
+
+
+def test_qkv_rope_append_pi0_shape(oracle):
+    require_cuda()
+    assert qkv_case(oracle, PI0, 3, seed=30) < TOL
+    assert qkv_case(oracle, PI0, 1, seed=31, x_f32=True) < TOL
+
+
+def test_q_only_projection_for_cross_attention_layers(oracle):
+    require_cuda()
+    assert qkv_case(oracle, SMOL, 2, seed=40, project_kv=False) < TOL
+
+
+def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads=None, poison=False):
+    import torch
+    import vla_cpp_b200 as vb
+
+    hd = 64
+    rng = np.random.default_rng(seed)
+    st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
+    kv_len = P if cross else P + S
+    k = oracle.bf16_round(rng.standard_normal((n_obs, n_kv, st.cap, hd)).astype(np.float32))
+    v = oracle.bf16_round(rng.standard_normal((n_obs, n_kv, st.cap, hd)).astype(np.float32))
+    q = oracle.bf16_round(rng.standard_normal((n_obs, n_q, S, hd)).astype(np.float32))
+    kd, vd = k.copy(), v.copy()
+    if poison:  # rows past kv_len hold NaN patterns: they must not reach the output
+        kd[:, :, kv_len:] = np.nan
+        vd[:, :, kv_len:] = np.nan
+    st.k[1].copy_(bf16_tensor(oracle, kd))
+    st.v[1].copy_(bf16_tensor(oracle, vd))
+    pad_t = to_dev(np.asarray(pads, np.int32)) if pads is not None else None
+    out = vb.attention(st, 1, bf16_tensor(oracle, q), S, n_q, kv_len, mask_mode, pad_ranges=pad_t)
+    assert vb.device_status() == 0
+    got = from_bf16(oracle, out)  # [n_obs][S][n_q*hd]
+    assert np.isfinite(got).all()
+    worst = 0.0
+    for b in range(n_obs):
+        ps, pe = (pads[b] if pads is not None else (0, 0))
+        ref = oracle.attention(q[b].transpose(1, 0, 2), k[b, :, :kv_len].transpose(1, 0, 2),
+                               v[b, :, :kv_len].transpose(1, 0, 2), P, mask_mode, int(ps), int(pe))
+        worst = max(worst, rel_l2(got[b], ref))
+    return worst
+
+
+@pytest.mark.parametrize("mask_mode", [0, 1, 2])
+def test_attention_smolvla_shape_all_masks(oracle, mask_mode):
+    require_cuda()
+    assert attn_case(oracle, 3, 15, 5, 51, 177, mask_mode, seed=50 + mask_mode) < TOL
+
+
+def test_attention_batch_and_pad_ranges(oracle):
+    require_cuda()
+    pads = [(130 + b, 176) if b % 2 else (0, 0) for b in range(16)]
+    assert attn_case(oracle, 16, 15, 5, 50, 177, 2, seed=60, pads=pads) < TOL
+
+
+def test_attention_edge_shapes(oracle):
+    require_cuda()
+    assert attn_case(oracle, 2, 4, 4, 5, 3, 2, seed=70) < TOL            # tiny, MHA
+    assert attn_case(oracle, 2, 8, 1, 32, 224, 1, seed=71) < TOL          # MQA, kv_len = 256 (max), R = 256
+    assert attn_case(oracle, 2, 6, 2, 40, 1, 2, seed=72) < TOL            # one prefix token
+    assert attn_case(oracle, 1, 15, 5, 51, 177, 2, seed=73) < TOL         # single observation
+
+
+def test_cross_attention_ignores_rows_past_kv_len(oracle):
+    require_cuda()
+    assert attn_case(oracle, 2, 15, 5, 50, 177, 0, seed=80, cross=True, poison=True) < TOL
+    assert attn_case(oracle, 2, 15, 5, 50, 170, 0, seed=81, cross=True, poison=True,
+                     pads=[(150, 169), (0, 0)]) < TOL
+
+
+def test_attention_rejects_unsupported(oracle):
+    require_cuda()
+    import vla_cpp_b200 as vb
+
+    st = vb.KvStore(1, 1, 1, 256, 816, 51)
+    q = np.zeros((1, 8, 51, 256), np.float32)
+    with pytest.raises(vb.VlaB200Error) as e:
+        vb.attention(st, 0, bf16_tensor(oracle, q), 51, 8, 867, 1)
+    assert e.value.code == -4
+
+
+def test_isolated_denoise_attention_two_layers_chain(oracle):
+    """QKV+RoPE+append feeding attention, two layers, as the isolated-op config runs them."""
+    require_cuda()
+    import vla_cpp_b200 as vb
+
+    cfg, n_obs = SMOL, 4
+    H, n_q, n_kv, hd, S, P = (cfg[k] for k in ("H", "n_q", "n_kv", "hd", "S", "P"))
+    rng = np.random.default_rng(90)
+    st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
+    rope = vb.rope_table(P, S, hd)
+    pos = np.arange(P, P + S).astype(np.int32)
+    for layer in range(2):
+        kp = rng.standard_normal((n_obs, P, n_kv, hd)).astype(np.float32)
+        vp = rng.standard_normal((n_obs, P, n_kv, hd)).astype(np.float32)
+        st.write_prefix(layer, to_dev(kp), to_dev(vp))
+        x = oracle.bf16_round(rng.standard_normal((n_obs * S, H)).astype(np.float32))
+        w = oracle.bf16_round((rng.standard_normal(((n_q + 2 * n_kv) * hd, H)) * 0.02).astype(np.float32))
+        ln = np.ones(H, np.float32)
+        q = vb.qkv_rope_append(st, layer, bf16_tensor(oracle, x), to_dev(ln), bf16_tensor(oracle, w), rope,
+                               cfg["eps"], S, n_q)
+        out = vb.attention(st, layer, q, S, n_q, P + S, vb.MASK_CAUSAL)
+        assert vb.device_status() == 0
+        got = from_bf16(oracle, out)
+        for b in range(n_obs):
+            rq, rk, rv = oracle.qkv_rope(x[b * S:(b + 1) * S], ln, w, pos, n_q, n_kv, hd, cfg["eps"])
+            K = np.concatenate([oracle.bf16_round(kp[b]), rk])
+            V = np.concatenate([oracle.bf16_round(vp[b]), rv])
+            ref = oracle.attention(rq, K, V, P, 2)
+            assert rel_l2(got[b], ref) < TOL

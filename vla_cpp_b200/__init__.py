@@ -7,9 +7,16 @@ call needs the built library and a B200.
 """
 from .api import (  # noqa: F401
     LIB_PATH,
+    MASK_CAUSAL,
+    MASK_NONE,
+    MASK_PI0,
+    KvStore,
     VlaB200Error,
     act_quant,
+    attention,
     device_status,
     lib,
+    qkv_rope_append,
+    rope_table,
     ternary_linear,
 )

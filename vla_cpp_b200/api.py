@@ -34,6 +34,7 @@ def lib():
             fn = getattr(L, name)
             if name.startswith("vlab200_") and name not in ("vlab200_last_error",):
                 fn.restype = C.c_int32
+        L.vlab200_kv_store_bytes.restype = C.c_int64
         _LIB = L
     return _LIB
 
@@ -41,6 +42,8 @@ def lib():
 # every symbol include/vla_b200.h declares
 EXPORTS = [
     "vlab200_abi_version", "vlab200_last_error", "vlab200_device_status",
+    "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_qkv_rope_append",
+    "vlab200_attention",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
@@ -88,4 +91,76 @@ def ternary_linear(a, w_ladder, s, ws, n, out=None, acc_out=None, path=0):
     out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device) if out is None else out
     _check(lib().vlab200_ternary_linear(_ptr(a), _ptr(w_ladder), _ptr(out), _ptr(acc_out), _ptr(s), _ptr(ws),
                                         int(ws.numel()), m, n, k, int(path), _stream()), "vlab200_ternary_linear")
+    return out
+
+
+MASK_NONE, MASK_PI0, MASK_CAUSAL = 0, 1, 2
+
+
+class _KvStoreC(C.Structure):
+    _fields_ = [("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("n_layers", C.c_int32), ("n_obs", C.c_int32),
+                ("n_kv", C.c_int32), ("head_dim", C.c_int32), ("cap", C.c_int32), ("prefix_len", C.c_int32)]
+
+
+class KvStore:
+    """bf16 prefix+suffix K/V pages [n_layers][n_obs][n_kv][cap][head_dim] in device memory."""
+
+    def __init__(self, n_layers, n_obs, n_kv, head_dim, prefix_len, suffix_len, device="cuda"):
+        import torch
+
+        self.cap = prefix_len + suffix_len
+        nbytes = lib().vlab200_kv_store_bytes(n_layers, n_obs, n_kv, head_dim, self.cap)
+        if nbytes < 0:
+            raise VlaB200Error(ERR_ARG, "vlab200_kv_store_bytes")
+        shape = (n_layers, n_obs, n_kv, self.cap, head_dim)
+        self.k = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        assert self.k.numel() * 2 == nbytes
+        self.n_layers, self.n_obs, self.n_kv, self.head_dim = n_layers, n_obs, n_kv, head_dim
+        self.prefix_len, self.suffix_len = prefix_len, suffix_len
+        self.c = _KvStoreC(self.k.data_ptr(), self.v.data_ptr(), n_layers, n_obs, n_kv, head_dim, self.cap,
+                           prefix_len)
+
+    def write_prefix(self, layer, k_f32, v_f32, obs0=0):
+        """k_f32, v_f32: cuda float32 [n, prefix_len, n_kv, head_dim] (K already rotated)."""
+        assert k_f32.is_contiguous() and v_f32.is_contiguous()
+        n = k_f32.shape[0]
+        assert tuple(k_f32.shape) == (n, self.prefix_len, self.n_kv, self.head_dim) == tuple(v_f32.shape)
+        _check(lib().vlab200_kv_store_write(C.byref(self.c), layer, obs0, n, _ptr(k_f32), _ptr(v_f32), _stream()),
+               "vlab200_kv_store_write")
+
+
+def rope_table(pos0, S, head_dim, base=10000.0, device="cuda"):
+    import torch
+
+    cos_t = torch.empty((S, head_dim // 2), dtype=torch.float32, device=device)
+    sin_t = torch.empty_like(cos_t)
+    _check(lib().vlab200_rope_table(_ptr(cos_t), _ptr(sin_t), pos0, S, head_dim, C.c_float(base), _stream()),
+           "vlab200_rope_table")
+    return cos_t, sin_t
+
+
+def qkv_rope_append(store, layer, x, ln_w, wqkv, rope, eps, S, n_q, q_out=None, project_kv=True):
+    """x: [n_obs*S, H] bf16 or f32; wqkv: bf16 [(n_q + 2 n_kv) hd, H]; rope = (cos, sin) tables.
+    Returns q: bf16 [n_obs, n_q, S, hd]; suffix K/V land in the store."""
+    import torch
+
+    assert x.is_contiguous() and wqkv.is_contiguous() and wqkv.dtype == torch.bfloat16
+    H = x.shape[-1]
+    if q_out is None:
+        q_out = torch.empty((store.n_obs, n_q, S, store.head_dim), dtype=torch.bfloat16, device=x.device)
+    _check(lib().vlab200_qkv_rope_append(C.byref(store.c), layer, _ptr(x), int(x.dtype == torch.float32), _ptr(ln_w),
+                                         _ptr(wqkv), _ptr(rope[0]), _ptr(rope[1]), C.c_float(eps), S, H, n_q,
+                                         int(project_kv), _ptr(q_out), _stream()), "vlab200_qkv_rope_append")
+    return q_out
+
+
+def attention(store, layer, q, S, n_q, kv_len, mask_mode, pad_ranges=None, out=None):
+    """q: bf16 [n_obs, n_q, S, hd] -> bf16 [n_obs, S, n_q*hd]."""
+    import torch
+
+    if out is None:
+        out = torch.empty((store.n_obs, S, n_q * store.head_dim), dtype=torch.bfloat16, device=q.device)
+    _check(lib().vlab200_attention(C.byref(store.c), layer, _ptr(q), _ptr(out), S, n_q, kv_len, mask_mode,
+                                   _ptr(pad_ranges), _stream()), "vlab200_attention")
     return out
