@@ -1,0 +1,296 @@
+#!/usr/bin/env python
+"""Benchmark of the denoise hot path on B200.
+
+Metric (BASELINE.json): action chunks/s and p50 chunk latency of the denoise loop.
+
+Default workload ("smolvla_attn", BASELINE.json configs[1]): the isolated denoise-attention
+op, bf16 -- 16 layers, prefix KV length 177 written once per observation, a 51-token suffix
+projected by the fused RMSNorm+QKV+RoPE kernel and appended each step, attention over the
+228 keys, 10 steps; GQA 15q/5kv, head_dim 64; batch 256 observations per GPU.  One bench
+"step" runs the whole 10-step x 16-layer loop over the batch, i.e. produces `batch` chunks.
+
+  python bench.py --gpus N --steps K --warmup W            # this library
+  python bench.py --impl reference ...                     # the CPU restatement on host cores
+
+Multi-GPU: observations are independent, so each rank owns `batch` observations with a full
+replica of the weights and its own KV store; no collective on the data path (weak scaling).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(L=16, T=10, H=720, n_q=15, n_kv=5, hd=64, S=51, P=177, eps=1e-5)
+ATTN_BYTES_PER_OBS_LAYER_STEP = 2 * (177 * 5 * 64 * 2) + 2 * (51 * 5 * 64 * 2) + 2 * (51 * 15 * 64 * 2)  # 487,680
+INT8_PEAK_TOPS = 3249.8  # measured on this pool, profiles/int8_tensor_peak_b200.md
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def oracle_chunk(orc, rng, n_chunks):
+    """CPU restatement of the same workload for `n_chunks` observations; returns seconds."""
+    c = CFG
+    n_rows = (c["n_q"] + 2 * c["n_kv"]) * c["hd"]
+    w = orc.bf16_round((rng.standard_normal((c["L"], n_rows, c["H"])) * 0.02).astype(np.float32))
+    ln = np.ones(c["H"], np.float32)
+    pos = np.arange(c["P"], c["P"] + c["S"]).astype(np.int32)
+    kp = rng.standard_normal((c["L"], c["P"], c["n_kv"], c["hd"])).astype(np.float32)
+    vp = rng.standard_normal((c["L"], c["P"], c["n_kv"], c["hd"])).astype(np.float32)
+    t0 = time.perf_counter()
+    for _ in range(n_chunks):
+        for _step in range(c["T"]):
+            for l in range(c["L"]):
+                x = rng.standard_normal((c["S"], c["H"])).astype(np.float32)
+                q, k, v = orc.qkv_rope(x, ln, w[l], pos, c["n_q"], c["n_kv"], c["hd"], c["eps"])
+                orc.attention(q, np.concatenate([kp[l], k]), np.concatenate([vp[l], v]), c["P"], orc.MASK_SMOLVLA)
+    return time.perf_counter() - t0
+
+
+def config_dict(batch, n_gpus):
+    return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
+                        "P=177, S=51, 15q/5kv, hd 64, bf16",
+            "batch_per_gpu": batch, "global_batch": batch * n_gpus, "parallelism": f"replica x{n_gpus}",
+            "l2": "inputs larger than L2 (KV store + hidden states > 126 MB per GPU)"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import oracle_ffi as orc
+
+    rng = np.random.default_rng(1)
+    threads = orc.num_threads()
+    for _ in range(max(args.warmup, 0)):
+        oracle_chunk(orc, rng, 1)
+    times = [oracle_chunk(orc, rng, 1) for _ in range(args.steps)]
+    total = sum(times)
+    value = args.steps / total
+    line = {
+        "impl": "reference", "metric": "action chunks/s (denoise loop)", "value": value, "unit": "chunks/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "p50_chunk_latency_ms": 1e3 * statistics.median(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(1, 1),
+        "cpu_baseline": {"value": value, "unit": "chunks/s", "cores": threads, "kind": "port",
+                         "sample": "1 observation (chunk) per step: 10 steps x 16 layers of QKV+RoPE+attention; "
+                                   "the reference's own CPU path needs ggml (llama.cpp b10331), absent here"},
+        "e2e": {"value": value, "unit": "chunks/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="observations per GPU")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import vla_cpp_b200 as vb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    vb.lib()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    c, B = CFG, args.batch
+    dev = torch.device("cuda", local_rank)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    # ---- synthetic inputs, resident in HBM --------------------------------------------------
+    store = vb.KvStore(c["L"], B, c["n_kv"], c["hd"], c["P"], c["S"], device=dev)
+    for l in range(c["L"]):  # the prefix KV is written once per observation
+        kp = torch.randn((B, c["P"], c["n_kv"], c["hd"]), device=dev, generator=g)
+        vp = torch.randn((B, c["P"], c["n_kv"], c["hd"]), device=dev, generator=g)
+        store.write_prefix(l, kp, vp)
+    n_rows = (c["n_q"] + 2 * c["n_kv"]) * c["hd"]
+    wqkv = (torch.randn((c["L"], n_rows, c["H"]), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    ln_w = torch.ones((c["L"], c["H"]), device=dev)
+    x = torch.empty((c["T"], c["L"], B * c["S"], c["H"]), dtype=torch.bfloat16, device=dev)
+    for t in range(c["T"]):
+        x[t] = torch.randn((c["L"], B * c["S"], c["H"]), device=dev, generator=g).to(torch.bfloat16)
+    op = vb.DenoiseAttn(store, c["H"], c["n_q"], c["S"], ln_w, wqkv, c["eps"], vb.MASK_CAUSAL)
+    torch.cuda.synchronize()
+
+    # ---- device-resident throughput -----------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        op.run(x)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        op.run(x)
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    total_ms = ev[0].elapsed_time(ev[-1])
+    if vb.device_status() != 0:
+        raise SystemExit("device status word reports a kernel failure")
+
+    # ---- dominant kernel alone: attention launches on the launching stream ---------------------
+    n_att = c["L"] * c["T"]
+    for l in range(c["L"]):
+        vb.attention(store, l, op.q, c["S"], c["n_q"], c["P"] + c["S"], vb.MASK_CAUSAL, out=op.out[l])
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for i in range(n_att):
+        l = i % c["L"]
+        vb.attention(store, l, op.q, c["S"], c["n_q"], c["P"] + c["S"], vb.MASK_CAUSAL, out=op.out[l])
+    a1.record()
+    torch.cuda.synchronize()
+    att_ms = a0.elapsed_time(a1) / n_att
+    q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    q0.record()
+    for i in range(n_att):
+        l = i % c["L"]
+        vb.qkv_rope_append(store, l, x[0, l], ln_w[l], wqkv[l], op.rope, c["eps"], c["S"], c["n_q"], q_out=op.q)
+    q1.record()
+    torch.cuda.synchronize()
+    qkv_ms = q0.elapsed_time(q1) / n_att
+
+    # ---- end to end through the C ABI with host buffers ----------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        x_host = torch.empty(x.shape, dtype=torch.bfloat16, pin_memory=True)
+        x_host.copy_(x)
+        out_host = torch.empty(op.out.shape, dtype=torch.bfloat16, pin_memory=True)
+        for _ in range(2):
+            op.run_host(x_host, out_host)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, min(args.steps, 5))
+        e0.record()
+        for _ in range(n_e2e):
+            op.run_host(x_host, out_host)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+        e2e = {"ms": e2e_ms, "h2d": x_host.numel() * 2, "d2h": out_host.numel() * 2}
+        del x_host, out_host
+
+    # ---- max over ranks ------------------------------------------------------------------------
+    stats = torch.tensor([total_ms, statistics.median(step_ms), att_ms, qkv_ms, e2e["ms"] if e2e else 0.0],
+                         device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total_ms, p50_ms, att_ms, qkv_ms, e2e_ms = [float(v) for v in stats.tolist()]
+
+    if rank == 0:
+        hbm_peak, peak_kind = measured_peaks()
+        att_gbs = ATTN_BYTES_PER_OBS_LAYER_STEP * B / (att_ms * 1e-3) / 1e9
+        line = {
+            "metric": "action chunks/s (denoise loop)", "value": B * world * args.steps / (total_ms * 1e-3),
+            "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config_dict(B, world), "clocks": clocks,
+            "gpu_launches": 2 * n_att * args.steps,
+            "roofline": {"kernel": "attn_hd64_kernel", "bound": "hbm", "achieved": att_gbs, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": att_gbs / hbm_peak, "peak_kind": f"of {peak_kind}",
+                         "traffic": None, "us_per_launch": att_ms * 1e3,
+                         "algorithmic_bytes_per_launch": ATTN_BYTES_PER_OBS_LAYER_STEP * B},
+            "kernels": {"attn_us": att_ms * 1e3, "qkv_rope_append_us": qkv_ms * 1e3,
+                        "qkv_tflops": 2.0 * B * c["S"] * n_rows * c["H"] / (qkv_ms * 1e-3) / 1e12},
+        }
+        if e2e:
+            line["e2e"] = {"value": B * world / (e2e_ms * 1e-3), "unit": "chunks/s",
+                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                           "ms_per_step": e2e_ms}
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle_ffi as orc
+
+            rng = np.random.default_rng(7)
+            t1 = oracle_chunk(orc, rng, 1)
+            n = max(1, min(16, int(args.cpu_seconds / max(t1, 1e-3))))
+            tn = oracle_chunk(orc, rng, n)
+            line["cpu_baseline"] = {"value": n / tn, "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
+                                    "sample": f"{n} observation(s) of the same workload (10 steps x 16 layers each)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -109,6 +109,35 @@ VLAB200_API int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer,
                                       int32_t S, int32_t n_q, int32_t kv_len, int32_t mask_mode,
                                       const int32_t *pad_ranges, void *stream);
 
+/* The isolated denoise-attention op: for step in [0, steps), layer in [0, n_layers):
+ * vlab200_qkv_rope_append(layer) then vlab200_attention(layer) over every observation of
+ * the store, on one stream.  It is the layer x step loop the reference unrolls into its graph
+ * (src/models/smolvla.cpp:1405-1415, src/models/pi0.cpp:572-577) restricted to the QKV and
+ * attention nodes, with the hidden states given as inputs. */
+typedef struct {
+    int32_t n_layers, steps, S, H, n_q, mask_mode, x_is_f32;
+    float eps;
+    const void *x;          /* [steps][n_layers][n_obs*S][H] hidden states, bf16 or float32 */
+    const float *ln_w;      /* [n_layers][H] */
+    const void *wqkv;       /* bf16 [n_layers][(n_q + 2 n_kv) hd][H] */
+    const float *rope_cos;  /* [S][hd/2] */
+    const float *rope_sin;
+    void *q_scratch;        /* bf16 [n_obs][n_q][S][hd] */
+    void *out;              /* bf16 [n_layers][n_obs][S][n_q*hd]: the last step's attention output */
+    const int32_t *pad_ranges; /* optional, see vlab200_attention */
+} vlab200_denoise_attn_args;
+
+VLAB200_API int32_t vlab200_denoise_attn_loop(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
+                                              void *stream);
+
+/* Same loop with the hidden states and the result in (pinned) HOST memory: a->x is a host
+ * pointer; each step's hidden states [n_layers][n_obs*S][H] are copied into the device
+ * staging buffer x_stage (2 x that size, double-buffered on an internal copy stream) while
+ * the previous step computes; after the last step a->out (device) is copied to out_host.
+ * Creates one stream and four events per calling thread on first use. */
+VLAB200_API int32_t vlab200_denoise_attn_loop_host(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
+                                                   void *x_stage, void *out_host, void *stream);
+
 /* ---------------------------------------------------------------- BitVLA ternary path */
 
 /* Per-token absmax int8 quantisation: scales[m] = 127 / max(max_k |x[m][k]|, 1e-5),

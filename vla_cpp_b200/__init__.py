@@ -10,6 +10,7 @@ from .api import (  # noqa: F401
     MASK_CAUSAL,
     MASK_NONE,
     MASK_PI0,
+    DenoiseAttn,
     KvStore,
     VlaB200Error,
     act_quant,

@@ -43,7 +43,7 @@ def lib():
 EXPORTS = [
     "vlab200_abi_version", "vlab200_last_error", "vlab200_device_status",
     "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_qkv_rope_append",
-    "vlab200_attention",
+    "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
@@ -164,3 +164,57 @@ def attention(store, layer, q, S, n_q, kv_len, mask_mode, pad_ranges=None, out=N
     _check(lib().vlab200_attention(C.byref(store.c), layer, _ptr(q), _ptr(out), S, n_q, kv_len, mask_mode,
                                    _ptr(pad_ranges), _stream()), "vlab200_attention")
     return out
+
+
+class _DenoiseAttnArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "steps", "S", "H", "n_q", "mask_mode", "x_is_f32")] + [
+        ("eps", C.c_float)] + [(n, C.c_void_p) for n in (
+            "x", "ln_w", "wqkv", "rope_cos", "rope_sin", "q_scratch", "out", "pad_ranges")]
+
+
+class DenoiseAttn:
+    """The isolated denoise-attention op over a KvStore: steps x layers of fused
+    QKV+RoPE+append and attention, driven by the library's C++ loop."""
+
+    def __init__(self, store, H, n_q, S, ln_w, wqkv, eps, mask_mode, pos0=None, rope_base=10000.0):
+        import torch
+
+        self.store, self.H, self.n_q, self.S, self.eps, self.mask_mode = store, H, n_q, S, eps, mask_mode
+        self.ln_w, self.wqkv = ln_w.contiguous(), wqkv.contiguous()
+        self.n_layers = wqkv.shape[0]
+        self.rope = rope_table(store.prefix_len if pos0 is None else pos0, S, store.head_dim, rope_base)
+        dev = wqkv.device
+        self.q = torch.empty((store.n_obs, n_q, S, store.head_dim), dtype=torch.bfloat16, device=dev)
+        self.out = torch.empty((self.n_layers, store.n_obs, S, n_q * store.head_dim), dtype=torch.bfloat16,
+                               device=dev)
+        self._stage = None
+
+    def _args(self, x_ptr, steps, x_is_f32):
+        return _DenoiseAttnArgs(self.n_layers, steps, self.S, self.H, self.n_q, self.mask_mode, int(x_is_f32),
+                                self.eps, x_ptr, self.ln_w.data_ptr(), self.wqkv.data_ptr(),
+                                self.rope[0].data_ptr(), self.rope[1].data_ptr(), self.q.data_ptr(),
+                                self.out.data_ptr(), None)
+
+    def run(self, x):
+        """x: cuda [steps, n_layers, n_obs*S, H] bf16/f32.  Returns the last step's outputs (device)."""
+        import torch
+
+        assert x.is_cuda and x.is_contiguous() and x.shape[1] == self.n_layers
+        a = self._args(x.data_ptr(), x.shape[0], x.dtype == torch.float32)
+        _check(lib().vlab200_denoise_attn_loop(C.byref(self.store.c), C.byref(a), _stream()),
+               "vlab200_denoise_attn_loop")
+        return self.out
+
+    def run_host(self, x_host, out_host):
+        """x_host: pinned host tensor [steps, n_layers, n_obs*S, H]; out_host: pinned host bf16 like self.out."""
+        import torch
+
+        assert not x_host.is_cuda and x_host.is_contiguous()
+        step_elems = x_host[0].numel()
+        if self._stage is None or self._stage.numel() != 2 * step_elems or self._stage.dtype != x_host.dtype:
+            self._stage = torch.empty(2 * step_elems, dtype=x_host.dtype, device=self.out.device)
+        a = self._args(x_host.data_ptr(), x_host.shape[0], x_host.dtype == torch.float32)
+        _check(lib().vlab200_denoise_attn_loop_host(C.byref(self.store.c), C.byref(a), _ptr(self._stage),
+                                                    C.c_void_p(out_host.data_ptr()), _stream()),
+               "vlab200_denoise_attn_loop_host")
+        return out_host

@@ -378,11 +378,18 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
     const int smem = vb::QKV_STAGES * vb::QKV_STAGE_BYTES + 256 + ksteps * vb::QKV_BK * 4 + 1024;
     dim3 grid((M + vb::QKV_BM - 1) / vb::QKV_BM, (n_total + vb::QKV_BN - 1) / vb::QKV_BN);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    static int smem_set[2] = {0, 0};  // largest dynamic shared memory size opted into so far
     if (x_is_f32) {
-        VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (smem > smem_set[1]) {
+            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            smem_set[1] = smem;
+        }
         vb::qkv_rope_kernel<true><<<grid, vb::QKV_THREADS, smem, cs>>>(wmap, p);
     } else {
-        VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (smem > smem_set[0]) {
+            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            smem_set[0] = smem;
+        }
         vb::qkv_rope_kernel<false><<<grid, vb::QKV_THREADS, smem, cs>>>(wmap, p);
     }
     VB_CUDA(cudaGetLastError());
