@@ -225,7 +225,7 @@ def main():
     q0.record()
     for i in range(n_att):
         l = i % c["L"]
-        vb.qkv_rope_append(store, l, x[0, l], ln_w[l], wqkv[l], op.rope, c["eps"], c["S"], c["n_q"], q_out=op.q)
+        vb.qkv_rope_append(store, l, x[0, l], None, op.wqkv[l], op.rope, c["eps"], c["S"], c["n_q"], q_out=op.q)
     q1.record()
     torch.cuda.synchronize()
     qkv_ms = q0.elapsed_time(q1) / n_att

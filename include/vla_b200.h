@@ -81,6 +81,12 @@ VLAB200_API int32_t vlab200_kv_store_write(const vlab200_kv_store *st, int32_t l
 VLAB200_API int32_t vlab200_rope_table(float *cos_out, float *sin_out, int32_t pos0, int32_t S, int32_t head_dim,
                                        float base, void *stream);
 
+/* out[n][k] = bf16(w[n][k] * ln_w[k]) for a bf16 [rows][H] weight: folds an RMSNorm weight
+ * (Gemma-style norms already carry their +1, src/gguf_reader.h:169) into the projection that
+ * consumes the normalised activations.  Run once at load time; `out` may alias `w`. */
+VLAB200_API int32_t vlab200_fold_norm_weight(const void *w_bf16, const float *ln_w, void *out_bf16, int64_t rows,
+                                             int32_t H, void *stream);
+
 /* Fused RMSNorm -> Q/K/V projection -> NeoX RoPE -> KV append for the suffix tokens of ALL
  * observations of the store (M = n_obs * S rows):
  *   xn = x * rsqrt(mean(x^2) + eps) * ln_w;  [q | k | v] = Wqkv xn;  q, k rotated;
@@ -88,6 +94,8 @@ VLAB200_API int32_t vlab200_rope_table(float *cos_out, float *sin_out, int32_t p
  * x: [n_obs*S][H], bf16 or (x_is_f32) float32.  Wqkv: bf16 [(n_q + 2 n_kv) head_dim][H], rows
  * ordered q heads, k heads, v heads.  project_kv == 0 projects q only (SmolVLA cross-attention
  * layers, src/models/smolvla.cpp:870-873; Wqkv then holds the q rows only).  H % 8 == 0.
+ * ln_w == NULL means Wqkv was already multiplied by ln_w (vlab200_fold_norm_weight); with bf16 x
+ * this selects the fastest kernel (both operands by TMA, persistent CTAs).
  * Replaces the rms_norm/mul, three mul_mat, two rope and two concat nodes of
  * src/models/pi0.cpp:170-201 and src/models/smolvla.cpp:820-833. */
 VLAB200_API int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const void *x,
@@ -118,7 +126,7 @@ typedef struct {
     int32_t n_layers, steps, S, H, n_q, mask_mode, x_is_f32;
     float eps;
     const void *x;          /* [steps][n_layers][n_obs*S][H] hidden states, bf16 or float32 */
-    const float *ln_w;      /* [n_layers][H] */
+    const float *ln_w;      /* [n_layers][H], or NULL when wqkv already has it folded in */
     const void *wqkv;       /* bf16 [n_layers][(n_q + 2 n_kv) hd][H] */
     const float *rope_cos;  /* [S][hd/2] */
     const float *rope_sin;

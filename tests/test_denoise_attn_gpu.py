@@ -52,7 +52,7 @@ def test_rope_table(oracle):
         np.testing.assert_allclose(s.cpu().numpy(), rs, atol=3e-4)
 
 
-def qkv_case(oracle, cfg, n_obs, seed, x_f32=False, project_kv=True, ln_rand=True):
+def qkv_case(oracle, cfg, n_obs, seed, x_f32=False, project_kv=True, ln_rand=True, fold=False):
     import torch
     import vla_cpp_b200 as vb
 
@@ -67,8 +67,10 @@ def qkv_case(oracle, cfg, n_obs, seed, x_f32=False, project_kv=True, ln_rand=Tru
     st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
     rope = vb.rope_table(P, S, hd)
     xd = to_dev(x) if x_f32 else bf16_tensor(oracle, x)
-    q = vb.qkv_rope_append(st, 1, xd, to_dev(ln), bf16_tensor(oracle, w), rope, cfg["eps"], S, n_q,
-                           project_kv=project_kv)
+    wd, lnd = bf16_tensor(oracle, w), to_dev(ln)
+    if fold:  # RMSNorm weight multiplied into the projection once; x then goes to the MMA by TMA
+        wd, lnd = vb.fold_norm_weight(wd, lnd), None
+    q = vb.qkv_rope_append(st, 1, xd, lnd, wd, rope, cfg["eps"], S, n_q, project_kv=project_kv)
     assert vb.device_status() == 0
     pos = np.arange(P, P + S).astype(np.int32)
     q_gpu = from_bf16(oracle, q)            # [n_obs][n_q][S][hd]
@@ -94,6 +96,29 @@ def qkv_case(oracle, cfg, n_obs, seed, x_f32=False, project_kv=True, ln_rand=Tru
 def test_qkv_rope_append_smolvla_shape(oracle, n_obs):
     require_cuda()
     assert qkv_case(oracle, SMOL, n_obs, seed=10 + n_obs) < TOL
+
+
+@pytest.mark.parametrize("n_obs", [1, 3, 16, 40])
+def test_qkv_rope_append_folded_weights_tma_path(oracle, n_obs):
+    require_cuda()
+    assert qkv_case(oracle, SMOL, n_obs, seed=100 + n_obs, fold=True) < TOL
+
+
+def test_qkv_rope_append_folded_pi0_shape_and_q_only(oracle):
+    require_cuda()
+    assert qkv_case(oracle, PI0, 5, seed=110, fold=True) < TOL
+    assert qkv_case(oracle, SMOL, 3, seed=111, fold=True, project_kv=False) < TOL
+
+
+def test_fold_norm_weight_is_exact_product(oracle):
+    require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(5)
+    w = oracle.bf16_round(rng.standard_normal((96, 720)).astype(np.float32))
+    ln = (1 + 0.1 * rng.standard_normal(720)).astype(np.float32)
+    got = bf16_bits(vb.fold_norm_weight(bf16_tensor(oracle, w), to_dev(ln)))
+    assert np.array_equal(got, oracle.f32_to_bf16_bits(w * ln[None, :]))
 
 
 def test_qkv_rope_append_f32_input_and_unit_norm(oracle):
@@ -211,3 +236,36 @@ def test_isolated_denoise_attention_two_layers_chain(oracle):
             V = np.concatenate([oracle.bf16_round(vp[b]), rv])
             ref = oracle.attention(rq, K, V, P, 2)
             assert rel_l2(got[b], ref) < TOL
+
+
+def test_loop_driver_matches_stepwise_calls(oracle):
+    """vlab200_denoise_attn_loop (C++ driver, folded weights) against per-call composition, and the
+    host-buffer variant against the device-resident one."""
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    cfg, n_obs, L, T = SMOL, 3, 2, 2
+    H, n_q, n_kv, hd, S, P = (cfg[k] for k in ("H", "n_q", "n_kv", "hd", "S", "P"))
+    g = torch.Generator(device="cuda").manual_seed(3)
+    st = vb.KvStore(L, n_obs, n_kv, hd, P, S)
+    for l in range(L):
+        st.write_prefix(l, torch.randn((n_obs, P, n_kv, hd), device="cuda", generator=g),
+                        torch.randn((n_obs, P, n_kv, hd), device="cuda", generator=g))
+    w = (torch.randn((L, (n_q + 2 * n_kv) * hd, H), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    ln = 1 + 0.1 * torch.randn((L, H), device="cuda", generator=g)
+    x = torch.randn((T, L, n_obs * S, H), device="cuda", generator=g).to(torch.bfloat16)
+    op = vb.DenoiseAttn(st, H, n_q, S, ln, w, cfg["eps"], vb.MASK_CAUSAL)
+    out = op.run(x).clone()
+    assert vb.device_status() == 0
+    rope = vb.rope_table(P, S, hd)
+    for l in range(L):  # the last step decides the result
+        q = vb.qkv_rope_append(st, l, x[T - 1, l], ln[l].contiguous(), w[l].contiguous(), rope, cfg["eps"], S, n_q)
+        ref = vb.attention(st, l, q, S, n_q, P + S, vb.MASK_CAUSAL)
+        a, b = from_bf16(oracle, out[l]), from_bf16(oracle, ref)
+        assert rel_l2(a, b) < 1e-2  # folded vs unfolded weights differ by bf16 roundings only
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty(op.out.shape, dtype=torch.bfloat16).pin_memory()
+    op.run_host(x_host, out_host)
+    torch.cuda.synchronize()
+    assert vb.device_status() == 0
+    assert torch.equal(out_host, out.cpu())

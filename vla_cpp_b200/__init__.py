@@ -16,6 +16,7 @@ from .api import (  # noqa: F401
     act_quant,
     attention,
     device_status,
+    fold_norm_weight,
     lib,
     qkv_rope_append,
     rope_table,

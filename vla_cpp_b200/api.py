@@ -42,7 +42,8 @@ def lib():
 # every symbol include/vla_b200.h declares
 EXPORTS = [
     "vlab200_abi_version", "vlab200_last_error", "vlab200_device_status",
-    "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_qkv_rope_append",
+    "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_fold_norm_weight",
+    "vlab200_qkv_rope_append",
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
@@ -140,6 +141,18 @@ def rope_table(pos0, S, head_dim, base=10000.0, device="cuda"):
     return cos_t, sin_t
 
 
+def fold_norm_weight(w, ln_w):
+    """bf16 [..., rows, H] weight times an RMSNorm weight [H] (float32) -> new bf16 tensor."""
+    import torch
+
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and ln_w.dtype == torch.float32
+    out = torch.empty_like(w)
+    H = w.shape[-1]
+    _check(lib().vlab200_fold_norm_weight(_ptr(w), _ptr(ln_w), _ptr(out), C.c_int64(w.numel() // H), H, _stream()),
+           "vlab200_fold_norm_weight")
+    return out
+
+
 def qkv_rope_append(store, layer, x, ln_w, wqkv, rope, eps, S, n_q, q_out=None, project_kv=True):
     """x: [n_obs*S, H] bf16 or f32; wqkv: bf16 [(n_q + 2 n_kv) hd, H]; rope = (cos, sin) tables.
     Returns q: bf16 [n_obs, n_q, S, hd]; suffix K/V land in the store."""
@@ -176,12 +189,20 @@ class DenoiseAttn:
     """The isolated denoise-attention op over a KvStore: steps x layers of fused
     QKV+RoPE+append and attention, driven by the library's C++ loop."""
 
-    def __init__(self, store, H, n_q, S, ln_w, wqkv, eps, mask_mode, pos0=None, rope_base=10000.0):
+    def __init__(self, store, H, n_q, S, ln_w, wqkv, eps, mask_mode, pos0=None, rope_base=10000.0, fold=True):
+        """ln_w: f32 [n_layers, H]; wqkv: bf16 [n_layers, (n_q+2n_kv)hd, H].  fold=True multiplies the
+        RMSNorm weights into wqkv once (load-time step), which lets bf16 hidden states go straight
+        to the tensor cores by TMA; fold=False keeps them separate (needed for float32 hidden states)."""
         import torch
 
         self.store, self.H, self.n_q, self.S, self.eps, self.mask_mode = store, H, n_q, S, eps, mask_mode
-        self.ln_w, self.wqkv = ln_w.contiguous(), wqkv.contiguous()
         self.n_layers = wqkv.shape[0]
+        if fold:
+            self.wqkv = torch.stack([fold_norm_weight(wqkv[l].contiguous(), ln_w[l].contiguous())
+                                     for l in range(self.n_layers)])
+            self.ln_w = None
+        else:
+            self.ln_w, self.wqkv = ln_w.contiguous(), wqkv.contiguous()
         self.rope = rope_table(store.prefix_len if pos0 is None else pos0, S, store.head_dim, rope_base)
         dev = wqkv.device
         self.q = torch.empty((store.n_obs, n_q, S, store.head_dim), dtype=torch.bfloat16, device=dev)
@@ -191,7 +212,7 @@ class DenoiseAttn:
 
     def _args(self, x_ptr, steps, x_is_f32):
         return _DenoiseAttnArgs(self.n_layers, steps, self.S, self.H, self.n_q, self.mask_mode, int(x_is_f32),
-                                self.eps, x_ptr, self.ln_w.data_ptr(), self.wqkv.data_ptr(),
+                                self.eps, x_ptr, self.ln_w.data_ptr() if self.ln_w is not None else None, self.wqkv.data_ptr(),
                                 self.rope[0].data_ptr(), self.rope[1].data_ptr(), self.q.data_ptr(),
                                 self.out.data_ptr(), None)
 

@@ -1,20 +1,22 @@
 // Action-query attention over the prefix + suffix KV pages (head_dim 64, up to 256 keys).
 //
-// One CTA per (kv head, observation).  The g = n_q / n_kv query heads that share the kv head
-// are stacked into one row block of g*S rows (GQA/MQA head sharing: K and V are fetched once
-// for all of them), processed as 128-row tcgen05 tiles:
+// Persistent kernel, one CTA per SM, looping over work items (kv head, observation) of one
+// layer.  The g = n_q / n_kv query heads that share a kv head are stacked into one block of
+// R = g*S rows (GQA/MQA head sharing: K and V are fetched once for all of them) and processed
+// as 128-row tcgen05 tiles.
 //
-//   TMA (SWIZZLE_128B): Q rows, the K page, the V page -> shared memory (pages are read once)
-//   S = Q K^T           tcgen05.mma kind::f16, f32 accumulator in TMEM (whole key range at once)
-//   softmax             one thread per row (TMEM lane): two passes over its row, exp2 with
-//                       the scale folded in, masked columns skipped; P written back to TMEM
-//                       as bf16 over the consumed S columns
-//   O = P V             tcgen05.mma with A = P from TMEM, B = V page as an MN-major operand
-//   epilogue            O / rowsum -> bf16 -> out[obs][tok][head*hd ..]
+//   loader warp   TMA (SWIZZLE_128B): Q rows, K page, V page of item n+1 into a 2-stage ring
+//                 while item n computes (pages are read from HBM exactly once)
+//   2 MMA warps   one per TMEM region (items alternate between the regions):
+//                 S = Q K^T (kind::f16, f32 accumulator, all keys at once), then O = P V with
+//                 A = P read from TMEM and V as an MN-major operand
+//   2 x 4 softmax warps (one group per region): one thread per row (TMEM lane); two passes over
+//                 the row straight out of TMEM, exp2 with the scale folded in, masked columns
+//                 skipped; P (bf16) overwrites the consumed S columns; epilogue O / rowsum -> bf16
 //
-// Reference: src/layers/attn.h:38-46, src/models/pi0.cpp:204-223 (explicit mul_mat -> soft_max
-// -> mul_mat with the score matrix in HBM), src/models/smolvla.cpp:835-842,874-881
-// (ggml_flash_attn_ext); masks src/models/pi0.cpp:640-651, smolvla.cpp:1655-1664.
+// Reference: src/layers/attn.h:38-46, src/models/pi0.cpp:204-223 (mul_mat -> soft_max -> mul_mat
+// with the score matrix in HBM), src/models/smolvla.cpp:835-842,874-881 (ggml_flash_attn_ext);
+// masks src/models/pi0.cpp:640-651, smolvla.cpp:1655-1664.
 #include <cuda_bf16.h>
 
 #include "host_common.h"
@@ -22,52 +24,169 @@
 
 namespace vb {
 
-constexpr int ATT_THREADS = 160;      // warps 0-3: softmax / epilogue (TMEM quarters), warp 4: TMA + MMA
+constexpr int ATT_THREADS = 352;  // warps 0-3 / 4-7: softmax groups, 8: loader, 9-10: MMA issuers
 constexpr int ATT_MAX_KEYS = 256;
 constexpr int ATT_Q_TILE_BYTES = 128 * 128;
 constexpr int ATT_KV_BYTES = ATT_MAX_KEYS * 128;
-constexpr int ATT_TMEM_COLS = 256;    // S [0,256) / P [0,128) aliased, O [128,192)
+constexpr int ATT_QK_BYTES = 2 * ATT_Q_TILE_BYTES + ATT_KV_BYTES;  // Q0, Q1, K of one item
+constexpr int ATT_SMEM_DATA = 2 * ATT_QK_BYTES + 2 * ATT_KV_BYTES;  // two Q/K buffers, two V buffers
+constexpr int ATT_REGION_COLS = 256;  // per region: S [0,256) / P [0,128) aliased, O [128,192)
 constexpr int ATT_O_COL = 128;
 
 struct AttnParams {
     __nv_bfloat16 *out;  // [n_obs][S][n_q*hd]
     const int32_t *pad;  // [n_obs][2] masked prefix columns, or null
-    int S, n_q, n_kv, g, kv_len, prefix_len, mask_mode, nk16, R, n_mt, page0;
+    int S, n_q, n_kv, g, kv_len, prefix_len, mask_mode, nk16, R, n_items, page0;
+    int t1_rows;   // rows of the second 128-row tile (0: none)
+    int t1_rot;    // 1: t1_rows <= 32, its rows are placed in TMEM quarter (item ordinal % 4)
     float scale_log2;
     int *status;
+#ifdef VB_TRACE
+    long long *trace;  // [block][unit][8] clock64 stamps of one softmax warp (developer builds only)
+#endif
 };
 
-__global__ void __launch_bounds__(ATT_THREADS, 2)
-attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                 const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
+#ifdef VB_TRACE
+#define VB_STAMP(slot)                                                                      \
+    do {                                                                                    \
+        if (p.trace && qtr == 0 && lane == 0 && k_unit_global < 16)                         \
+            p.trace[((size_t)blockIdx.x * 32 + (size_t)(k_unit_global * 2 + r)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#define VB_STAMP_CHUNK(cc)                                                                   \
+    do {                                                                                    \
+        if (p.trace && qtr == 0 && lane == 0 && k_unit_global == 0)                         \
+            p.trace[((size_t)blockIdx.x * 32 + 24 + r) * 8 + ((cc) & 7)] = clock64();       \
+    } while (0)
+#else
+#define VB_STAMP(slot) do { } while (0)
+#define VB_STAMP_CHUNK(cc) do { } while (0)
+#endif
+
+__device__ __forceinline__ float ex2_approx(float x) {
+#ifdef VB_EXP_NOEX2
+    return x * 0.001f + 0.5f;  // developer experiment: no transcendental
+#else
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+#endif
+}
+
+// Per-row mask description used by the softmax helpers: columns [0, jmax) minus [pad_lo, pad_hi)
+// are visible; columns below clean_end need no test in any lane of the warp.
+struct RowMask {
+    int jmax, pad_lo, pad_hi, clean_end;
+};
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Visibility is applied to the INPUT of max / exp2 (a select to -inf), never as a branch around
+// them, so lanes with different row limits stay converged.
+__device__ __forceinline__ float att_masked(uint32_t bits, int j, int rel_jmax, int rel_pad_lo, int pad_w) {
+    const bool vis = j < rel_jmax && !((unsigned)(j - rel_pad_lo) < (unsigned)pad_w);
+    return vis ? __uint_as_float(bits) : -INFINITY;
+}
+
+__device__ __forceinline__ void att_max_chunk(const uint32_t (&sv)[32], int c, const RowMask &rm, float (&mx)[4]) {
+    if (c * 32 + 32 <= rm.clean_end) {
+        // a reduction tree (independent operations), then one update of the running maxima
+        float t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            t[j] = max3(__uint_as_float(sv[4 * j]), __uint_as_float(sv[4 * j + 1]),
+                        fmaxf(__uint_as_float(sv[4 * j + 2]), __uint_as_float(sv[4 * j + 3])));
+        mx[0] = max3(mx[0], t[0], t[1]);
+        mx[1] = max3(mx[1], t[2], t[3]);
+        mx[2] = max3(mx[2], t[4], t[5]);
+        mx[3] = max3(mx[3], t[6], t[7]);
+    } else {
+        const int rel_jmax = rm.jmax - c * 32, rel_pad_lo = rm.pad_lo - c * 32, pad_w = rm.pad_hi - rm.pad_lo;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            mx[0] = max3(mx[0], att_masked(sv[j], j, rel_jmax, rel_pad_lo, pad_w),
+                         att_masked(sv[j + 1], j + 1, rel_jmax, rel_pad_lo, pad_w));
+            mx[1] = max3(mx[1], att_masked(sv[j + 2], j + 2, rel_jmax, rel_pad_lo, pad_w),
+                         att_masked(sv[j + 3], j + 3, rel_jmax, rel_pad_lo, pad_w));
+            mx[2] = max3(mx[2], att_masked(sv[j + 4], j + 4, rel_jmax, rel_pad_lo, pad_w),
+                         att_masked(sv[j + 5], j + 5, rel_jmax, rel_pad_lo, pad_w));
+            mx[3] = max3(mx[3], att_masked(sv[j + 6], j + 6, rel_jmax, rel_pad_lo, pad_w),
+                         att_masked(sv[j + 7], j + 7, rel_jmax, rel_pad_lo, pad_w));
+        }
+    }
+}
+
+// p = exp2(s*c - m*c) for one 32-column chunk; P (bf16) is stored over consumed S columns.  bf16
+// rounding uses integer adds (round-half-up on the magnitude; p >= 0): the conversion instruction
+// shares the transcendental unit that ex2 saturates.
+__device__ __forceinline__ void att_exp_chunk(const uint32_t (&sv)[32], int c, const RowMask &rm, float scale_log2,
+                                              float m2, float &sum0, float &sum1, uint32_t p_addr) {
+    uint32_t pk[16];
+    if (c * 32 + 32 <= rm.clean_end) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[j]), scale_log2, -m2));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[j + 1]), scale_log2, -m2));
+            sum0 += p0;
+            sum1 += p1;
+            pk[j >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
+        }
+    } else {
+        const int rel_jmax = rm.jmax - c * 32, rel_pad_lo = rm.pad_lo - c * 32, pad_w = rm.pad_hi - rm.pad_lo;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            // exp2(-inf) = 0 for the masked columns
+            const float p0 = ex2_approx(fmaf(att_masked(sv[j], j, rel_jmax, rel_pad_lo, pad_w), scale_log2, -m2));
+            const float p1 =
+                ex2_approx(fmaf(att_masked(sv[j + 1], j + 1, rel_jmax, rel_pad_lo, pad_w), scale_log2, -m2));
+            sum0 += p0;
+            sum1 += p1;
+            pk[j >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
+        }
+    }
+#ifdef VB_EXP_NOST
+    if (sum0 == 12345.678f) tmem_st16(p_addr, pk);  // developer experiment: no TMEM store
+#else
+    tmem_st16(p_addr, pk);
+#endif
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap q_map32,
+                 const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                 const AttnParams p) {
     extern __shared__ uint8_t att_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(att_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
-    uint8_t *sQ = smem;
-    uint8_t *sK = smem + 2 * ATT_Q_TILE_BYTES;
-    uint8_t *sV = sK + ATT_KV_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + ATT_KV_BYTES);
-    uint64_t *bar_qk = bars, *bar_v = bars + 1, *bar_s = bars + 2, *bar_p = bars + 3, *bar_o = bars + 4,
-             *bar_free = bars + 5;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ATT_SMEM_DATA);
+    uint64_t *full_qk = bars, *full_v = bars + 2, *free_qk = bars + 4, *free_v = bars + 6;    // per buffer
+    uint64_t *bar_s = bars + 8, *bar_p = bars + 10, *bar_o = bars + 12, *bar_free = bars + 14;  // per region
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kvh = blockIdx.x, obs = blockIdx.y;
     const WaitCtx wc{abort_flag, p.status};
+    const int n_tiles = p.t1_rows > 0 ? 2 : 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(bar_qk, 1);
-        mbar_init(bar_v, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_p, 128);
-        mbar_init(bar_o, 1);
-        mbar_init(bar_free, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&full_qk[i], 1);
+            mbar_init(&full_v[i], 1);
+            mbar_init(&free_qk[i], 1);
+            mbar_init(&free_v[i], 1);
+            mbar_init(&bar_s[i], 1);
+            mbar_init(&bar_p[i], 128);
+            mbar_init(&bar_o[i], 1);
+            mbar_init(&bar_free[i], 128);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 4) {
-        tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+    if (warp == 8) {
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -75,154 +194,235 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == 8) {
+        // ------------------------------------------------------------- loader
         if (lane == 0) {
-            const int page = p.page0 + obs * p.n_kv + kvh;
-            const int qrow0 = (obs * p.n_q + kvh * p.g) * p.S;
-            mbar_expect_tx(bar_qk, (uint32_t)(p.n_mt * ATT_Q_TILE_BYTES + ATT_KV_BYTES));
-            for (int mt = 0; mt < p.n_mt; ++mt) tma_load_2d(sQ + mt * ATT_Q_TILE_BYTES, &q_map, bar_qk, 0, qrow0 + mt * 128);
-            tma_load_3d(sK, &k_map, bar_qk, 0, 0, page);
-            mbar_expect_tx(bar_v, (uint32_t)ATT_KV_BYTES);
-            tma_load_3d(sV, &v_map, bar_v, 0, 0, page);
-
+            tma_prefetch_desc(&q_map);
+            tma_prefetch_desc(&k_map);
+            tma_prefetch_desc(&v_map);
+            int n = 0;
+            for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+                const int st = n & 1;
+                const uint32_t m = (uint32_t)(n >> 1);
+                // Q and K are released as soon as the item's last S MMA has read them, V after its last P V
+                if (!mbar_wait(&free_qk[st], (m & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY)) break;
+                const int obs = item / p.n_kv, kvh = item % p.n_kv;
+                const int page = p.page0 + item;
+                const int qrow0 = (obs * p.n_q + kvh * p.g) * p.S;
+                uint8_t *sQ = smem + st * ATT_QK_BYTES;
+                uint8_t *sK = sQ + 2 * ATT_Q_TILE_BYTES, *sV = smem + 2 * ATT_QK_BYTES + st * ATT_KV_BYTES;
+                uint32_t bytes = ATT_Q_TILE_BYTES + ATT_KV_BYTES;
+                if (p.t1_rows > 0) bytes += p.t1_rot ? 32 * 128 : ATT_Q_TILE_BYTES;
+                mbar_expect_tx(&full_qk[st], bytes);
+                tma_load_2d(sQ, &q_map, &full_qk[st], 0, qrow0);
+                if (p.t1_rows > 0) {
+                    if (p.t1_rot)
+                        tma_load_2d(sQ + ATT_Q_TILE_BYTES + (n & 3) * 32 * 128, &q_map32, &full_qk[st], 0, qrow0 + 128);
+                    else
+                        tma_load_2d(sQ + ATT_Q_TILE_BYTES, &q_map, &full_qk[st], 0, qrow0 + 128);
+                }
+                tma_load_3d(sK, &k_map, &full_qk[st], 0, 0, page);
+                if (!mbar_wait(&free_v[st], (m & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY)) break;
+                mbar_expect_tx(&full_v[st], (uint32_t)ATT_KV_BYTES);
+                tma_load_3d(sV, &v_map, &full_v[st], 0, 0, page);
+            }
+        }
+    } else if (warp == 9 || warp == 10) {
+        // ------------------------------------------------------------- MMA issuer of region r
+        const int r = warp - 9;
+        if (lane == 0) {
             const uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 128, p.nk16);
             const uint32_t idesc_o = make_idesc(1, 1, 1, 0, 1, 128, 64);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = mbar_wait(bar_qk, 0, wc, DEV_TIMEOUT_FULL);
-            for (int mt = 0; ok && mt < p.n_mt; ++mt) {
-                if (mt > 0) ok = mbar_wait(bar_free, (uint32_t)(mt - 1) & 1u, wc, DEV_TIMEOUT_EMPTY);
-                if (!ok) break;
-                tc_fence_after();
+            const uint32_t treg = tmem_base + (uint32_t)(r * ATT_REGION_COLS);
+            int n = r;
+            bool ok = true;
+            for (int item = blockIdx.x + r * gridDim.x; ok && item < p.n_items; item += 2 * gridDim.x, n += 2) {
+                const int st = n & 1;  // == r
+                const uint32_t m = (uint32_t)(n >> 1);
+                const uint32_t q_addr = smem_u32(smem + st * ATT_QK_BYTES);
+                const uint32_t k_addr = q_addr + 2 * ATT_Q_TILE_BYTES;
+                const uint32_t v_addr = smem_u32(smem + 2 * ATT_QK_BYTES + st * ATT_KV_BYTES);
+                ok = mbar_wait(&full_qk[st], m & 1u, wc, DEV_TIMEOUT_FULL);
+                for (int t = 0; ok && t < n_tiles; ++t) {
+                    const uint32_t k_unit = m * (uint32_t)n_tiles + (uint32_t)t;  // units completed in this region
+                    ok = mbar_wait(&bar_free[r], (k_unit & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    mma_f16(tmem_base, smem_desc_sw128(q_addr + mt * ATT_Q_TILE_BYTES + k * 32, 16, 1024),
-                            smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
-                tc_commit(bar_s);
-                ok = mbar_wait(bar_p, (uint32_t)mt & 1u, wc, DEV_TIMEOUT_FULL);
-                if (ok && mt == 0) ok = mbar_wait(bar_v, 0, wc, DEV_TIMEOUT_FULL);
-                if (!ok) break;
-                tc_fence_after();
-                for (int k16 = 0; k16 < p.nk16 / 16; ++k16)
-                    mma_f16_tmem_a(tmem_base + ATT_O_COL, tmem_base + (uint32_t)(k16 * 8),
-                                   smem_desc_sw128(v_addr + k16 * 2048, 16, 1024), idesc_o, k16 != 0 ? 1u : 0u);
-                tc_commit(bar_o);
+                    for (int k = 0; k < 4; ++k)
+                        mma_f16(treg, smem_desc_sw128(q_addr + t * ATT_Q_TILE_BYTES + k * 32, 16, 1024),
+                                smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+                    tc_commit(&bar_s[r]);
+                    if (t == n_tiles - 1) tc_commit(&free_qk[st]);  // Q, K of this item are dead once these MMAs ran
+                    ok = mbar_wait(&bar_p[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
+                    if (ok && t == 0) ok = mbar_wait(&full_v[st], m & 1u, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    for (int k16 = 0; k16 < p.nk16 / 16; ++k16)
+                        mma_f16_tmem_a(treg + ATT_O_COL, treg + (uint32_t)(k16 * 8),
+                                       smem_desc_sw128(v_addr + k16 * 2048, 16, 1024), idesc_o, k16 != 0 ? 1u : 0u);
+                    tc_commit(&bar_o[r]);
+                }
+                if (ok) tc_commit(&free_v[st]);  // every MMA that reads this V buffer has been issued
             }
         }
     } else {
-        const int qtr = warp;  // warps 0..3 <-> TMEM lane quarters 0..3
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(qtr * 32) << 16);
-        int pad_lo = 0, pad_hi = 0;
-        if (p.pad) {
-            pad_lo = p.pad[2 * obs];
-            pad_hi = p.pad[2 * obs + 1];
-        }
+        // ------------------------------------------------------------- softmax group of region r
+        const int r = warp >> 2, qtr = warp & 3;
+        const uint32_t lane_addr = tmem_base + (uint32_t)(r * ATT_REGION_COLS) + ((uint32_t)(qtr * 32) << 16);
         const int n_suffix_cols = p.kv_len - p.prefix_len;
         const int nchunks = (p.nk16 + 31) / 32;
-        for (int mt = 0; mt < p.n_mt; ++mt) {
-            const int r = mt * 128 + qtr * 32 + lane;
-            const bool row_ok = r < p.R;
-            const int head_l = r / p.S, tok = r % p.S;
-            int limit = n_suffix_cols;
-            if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
-            else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
-            const int jmax = p.prefix_len + limit;
-            if (!mbar_wait(bar_s, (uint32_t)mt & 1u, wc, DEV_TIMEOUT_FULL)) break;
-            tc_fence_after();
-            // pass 1: row maximum over the visible columns
-            float mx = -INFINITY;
-            for (int c = 0; c < nchunks; ++c) {
-                uint32_t sv[32];
-                tmem_ld32(lane_addr + (uint32_t)(c * 32), sv);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = c * 32 + j;
-                    const bool vis = col < jmax && !(col >= pad_lo && col < pad_hi);
-                    if (vis) mx = fmaxf(mx, __uint_as_float(sv[j]));
-                }
+        int n = r;
+        bool ok = true;
+        for (int item = blockIdx.x + r * gridDim.x; ok && item < p.n_items; item += 2 * gridDim.x, n += 2) {
+            const uint32_t m = (uint32_t)(n >> 1);
+            const int obs = item / p.n_kv, kvh = item % p.n_kv;
+            int pad_lo = 0, pad_hi = 0;
+            if (p.pad) {
+                pad_lo = p.pad[2 * obs];
+                pad_hi = p.pad[2 * obs + 1];
             }
-            const float m2 = (mx == -INFINITY) ? 0.0f : mx * p.scale_log2;
-            // pass 2: p = exp2(s*c - m*c), P (bf16) over the consumed S columns
-            float sum = 0.0f;
-            for (int c = 0; c < nchunks; ++c) {
-                uint32_t sv[32];
-                tmem_ld32(lane_addr + (uint32_t)(c * 32), sv);
-                tmem_ld_wait();
-                uint32_t pk[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int col = c * 32 + j;
-                    const bool v0 = col < jmax && !(col >= pad_lo && col < pad_hi);
-                    const bool v1 = col + 1 < jmax && !(col + 1 >= pad_lo && col + 1 < pad_hi);
-                    const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -m2)) : 0.0f;
-                    const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -m2)) : 0.0f;
-                    sum += p0 + p1;
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    pk[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
-                }
-                tmem_st16(lane_addr + (uint32_t)(c * 16), pk);
-            }
-            if (mt == 0) {
-                // keys kv_len .. nk16-1 enter the P V product with p = 0: make their V rows finite
-                if (!mbar_wait(bar_v, 0, wc, DEV_TIMEOUT_FULL)) break;
-                const int tail_rows = p.nk16 - p.kv_len;
-                for (int i = threadIdx.x; i < tail_rows * 8; i += 128) {
-                    const int row = p.kv_len + (i >> 3);
-                    *reinterpret_cast<uint4 *>(sV + (row >> 3) * 1024 + (row & 7) * 128 + ((i & 7) << 4)) =
-                        make_uint4(0, 0, 0, 0);
-                }
-                fence_proxy_async_smem();
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bar_p);
-            if (!mbar_wait(bar_o, (uint32_t)mt & 1u, wc, DEV_TIMEOUT_ACCUM)) break;
-            tc_fence_after();
-            uint32_t o0[32], o1[32];
-            tmem_ld32(lane_addr + ATT_O_COL, o0);
-            tmem_ld32(lane_addr + ATT_O_COL + 32, o1);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar_free);
-            if (row_ok) {
-                const float inv = 1.0f / sum;
-                __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * 64) +
-                                     (size_t)(kvh * p.g + head_l) * 64;
-                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o0[8 * j + 2 * e]) * inv,
-                                                                       __uint_as_float(o0[8 * j + 2 * e + 1]) * inv);
-                        w[e] = *reinterpret_cast<const uint32_t *>(&h);
+            for (int t = 0; ok && t < n_tiles; ++t) {
+                const uint32_t k_unit = m * (uint32_t)n_tiles + (uint32_t)t;
+                const uint32_t k_unit_global = k_unit;
+                (void)k_unit_global;
+                VB_STAMP(0);
+                // row of this thread inside the R-row block, or -1
+                int row;
+                if (t == 0) row = qtr * 32 + lane;
+                else if (p.t1_rot) row = (qtr == (n & 3)) ? 128 + lane : -1;
+                else row = 128 + qtr * 32 + lane;
+                const bool row_ok = row >= 0 && row < p.R;
+                const bool warp_active = __any_sync(0xffffffffu, row_ok);
+                const int head_l = row_ok ? row / p.S : 0, tok = row_ok ? row % p.S : 0;
+                int limit = n_suffix_cols;
+                if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
+                else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+                const int jmax = p.prefix_len + limit;
+                ok = mbar_wait(&bar_s[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                VB_STAMP(1);
+                float sum = 0.0f;
+                if (warp_active) {
+                    // columns below `clean_end` need no mask test in any lane of the warp
+                    int clean_end = p.prefix_len;
+                    if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
+                    RowMask rm{jmax, pad_lo, pad_hi, clean_end};
+                    // ---- pass 1: row maximum over the visible columns (two chunks per TMEM wait) ----
+                    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    for (int c = 0; c < nchunks; c += 2) {
+                        uint32_t sa[32], sb[32];
+                        tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
+                        tmem_ld32(lane_addr + (uint32_t)(min(c + 1, nchunks - 1) * 32), sb);
+                        tmem_ld_wait();
+                        att_max_chunk(sa, c, rm, mx);
+                        if (c + 1 < nchunks) att_max_chunk(sb, c + 1, rm, mx);
                     }
-                    d4[j] = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o1[8 * j + 2 * e]) * inv,
-                                                                       __uint_as_float(o1[8 * j + 2 * e + 1]) * inv);
-                        w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                    VB_STAMP(2);
+                    const float mxx = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                    const float m2 = (mxx == -INFINITY) ? 0.0f : mxx * p.scale_log2;
+#if defined(VB_EXP_NOLD)
+                    float sum0 = 0.0f, sum1 = 0.0f;
+                    {   // developer experiment: compute on one loaded chunk, no further TMEM loads
+                        uint32_t sa[32];
+                        tmem_ld32(lane_addr, sa);
+                        tmem_ld_wait();
+                        for (int c = 0; c < nchunks; ++c)
+                            att_exp_chunk(sa, c, rm, p.scale_log2, m2, sum0, sum1, lane_addr + (uint32_t)(c * 16));
                     }
-                    d4[4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
+#elif defined(VB_EXP_LDONLY)
+                    float sum0 = 0.0f, sum1 = 0.0f;
+                    {   // developer experiment: TMEM loads only
+                        uint32_t acc = 0;
+                        for (int c = 0; c < nchunks; ++c) {
+                            uint32_t sa[32];
+                            tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc ^= sa[j];
+                        }
+                        sum0 = __uint_as_float(acc | 0x3f800000u);
+                    }
+#else
+                    // ---- pass 2: the next chunk's TMEM load is in flight while this one is exponentiated ----
+                    float sum0 = 0.0f, sum1 = 0.0f;
+                    {
+                        uint32_t sa[32], sb[32];
+                        tmem_ld32(lane_addr, sa);
+                        tmem_ld_wait();
+                        for (int c = 0; c < nchunks; c += 2) {
+                            tmem_ld32(lane_addr + (uint32_t)(min(c + 1, nchunks - 1) * 32), sb);
+                            att_exp_chunk(sa, c, rm, p.scale_log2, m2, sum0, sum1, lane_addr + (uint32_t)(c * 16));
+                            VB_STAMP_CHUNK(c);
+                            tmem_ld_wait();
+                            if (c + 1 < nchunks) {
+                                tmem_ld32(lane_addr + (uint32_t)(min(c + 2, nchunks - 1) * 32), sa);
+                                att_exp_chunk(sb, c + 1, rm, p.scale_log2, m2, sum0, sum1,
+                                              lane_addr + (uint32_t)(c * 16 + 16));
+                                VB_STAMP_CHUNK(c + 1);
+                                tmem_ld_wait();
+                            }
+                        }
+                    }
+#endif
+                    sum = sum0 + sum1;
+                    tmem_st_wait();
+                }
+                VB_STAMP(3);
+                tc_fence_before();
+                mbar_arrive(&bar_p[r]);
+                ok = mbar_wait(&bar_o[r], k_unit & 1u, wc, DEV_TIMEOUT_ACCUM);
+                if (!ok) break;
+                tc_fence_after();
+                VB_STAMP(4);
+                uint32_t o0[32], o1[32];
+                if (warp_active) {
+                    tmem_ld32(lane_addr + ATT_O_COL, o0);
+                    tmem_ld32(lane_addr + ATT_O_COL + 32, o1);
+                    tmem_ld_wait();
+                }
+                tc_fence_before();
+                mbar_arrive(&bar_free[r]);
+                VB_STAMP(5);
+                if (row_ok) {
+                    const float inv = 1.0f / sum;
+                    __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * 64) +
+                                         (size_t)(kvh * p.g + head_l) * 64;
+                    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[4], x[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o0[8 * j + 2 * e]) * inv,
+                                                                           __uint_as_float(o0[8 * j + 2 * e + 1]) * inv);
+                            const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o1[8 * j + 2 * e]) * inv,
+                                                                            __uint_as_float(o1[8 * j + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                            x[e] = *reinterpret_cast<const uint32_t *>(&h1);
+                        }
+                        d4[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        d4[4 + j] = make_uint4(x[0], x[1], x[2], x[3]);
+                    }
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, ATT_TMEM_COLS);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
 }  // namespace vb
+
+#ifdef VB_TRACE
+long long *g_vb_attn_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void vlab200_set_attn_trace(long long *p) { g_vb_attn_trace = p; }
+#endif
 
 extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, const void *q, void *out,
                                      int32_t S, int32_t n_q, int32_t kv_len, int32_t mask_mode,
@@ -241,17 +441,21 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     int *status = vb::device_status_ptr();
     if (!status) return vb::cuda_fail(cudaGetLastError(), "device_status_ptr");
 
-    CUtensorMap qmap, kmap, vmap;
+    CUtensorMap qmap, qmap32, kmap, vmap;
     {
         const uint64_t dims[2] = {64, (uint64_t)st->n_obs * n_q * S};
         const uint64_t strides[1] = {128};
-        const uint32_t box[2] = {64, 128};
+        const uint32_t box[2] = {64, 128}, box32[2] = {64, 32};
         int rc = vb::make_tensor_map(&qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
+        rc = vb::make_tensor_map(&qmap32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, dims, strides, box32,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
     }
     {
-        const uint64_t dims[3] = {64, (uint64_t)st->cap, (uint64_t)st->n_layers * st->n_obs * st->n_kv};
+        // rows >= kv_len are outside the map, so TMA zero-fills them (they enter P V with p = 0)
+        const uint64_t dims[3] = {64, (uint64_t)kv_len, (uint64_t)st->n_layers * st->n_obs * st->n_kv};
         const uint64_t strides[2] = {128, (uint64_t)st->cap * 128};
         const uint32_t box[3] = {64, vb::ATT_MAX_KEYS, 1};
         int rc = vb::make_tensor_map(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->k_pages, dims, strides, box,
@@ -268,18 +472,29 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     p.mask_mode = mask_mode;
     p.nk16 = (kv_len + 15) / 16 * 16;
     p.R = R;
-    p.n_mt = (R + 127) / 128;
+    p.n_items = st->n_obs * st->n_kv;
     p.page0 = layer * st->n_obs * st->n_kv;
+    p.t1_rows = R > 128 ? R - 128 : 0;
+    p.t1_rot = (p.t1_rows > 0 && p.t1_rows <= 32) ? 1 : 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf(64.0f);
     p.status = status;
-    const int smem = 2 * vb::ATT_Q_TILE_BYTES + 2 * vb::ATT_KV_BYTES + 128 + 1024;
+#ifdef VB_TRACE
+    extern long long *g_vb_attn_trace;
+    p.trace = g_vb_attn_trace;
+#endif
+    const int smem = vb::ATT_SMEM_DATA + 256 + 1024;
     static bool attr_done = false;
+    static int n_sm = 0;
     if (!attr_done) {
         VB_CUDA(cudaFuncSetAttribute(vb::attn_hd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        int dev = 0;
+        VB_CUDA(cudaGetDevice(&dev));
+        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
         attr_done = true;
     }
-    dim3 grid(st->n_kv, st->n_obs);
-    vb::attn_hd64_kernel<<<grid, vb::ATT_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(qmap, kmap, vmap, p);
+    const int grid = p.n_items < n_sm ? p.n_items : n_sm;
+    vb::attn_hd64_kernel<<<grid, vb::ATT_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(qmap, qmap32, kmap, vmap,
+                                                                                            p);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }

@@ -16,7 +16,7 @@ static int check_loop_args(const vlab200_kv_store *st, const vlab200_denoise_att
     if (!st || !a) return VLAB200_ERR_ARG;
     if (a->n_layers <= 0 || a->n_layers > st->n_layers || a->steps <= 0 || a->S <= 0 || a->H <= 0 || a->n_q <= 0)
         return VLAB200_ERR_ARG;
-    if (!a->x || !a->ln_w || !a->wqkv || !a->rope_cos || !a->rope_sin || !a->q_scratch || !a->out)
+    if (!a->x || !a->wqkv || !a->rope_cos || !a->rope_sin || !a->q_scratch || !a->out)
         return VLAB200_ERR_ARG;
     return VLAB200_OK;
 }
@@ -25,7 +25,7 @@ static int run_layer_step(const vlab200_kv_store *st, const vlab200_denoise_attn
                           const void *x_layer, void *out_layer, cudaStream_t cs) {
     const size_t w_elems = (size_t)(a->n_q + 2 * st->n_kv) * st->head_dim * a->H;
     const void *w = static_cast<const __nv_bfloat16 *>(a->wqkv) + (size_t)layer * w_elems;
-    int rc = vlab200_qkv_rope_append(st, layer, x_layer, a->x_is_f32, a->ln_w + (size_t)layer * a->H, w, a->rope_cos,
+    int rc = vlab200_qkv_rope_append(st, layer, x_layer, a->x_is_f32, a->ln_w ? a->ln_w + (size_t)layer * a->H : nullptr, w, a->rope_cos,
                                      a->rope_sin, a->eps, a->S, a->H, a->n_q, 1, a->q_scratch, cs);
     if (rc) return rc;
     return vlab200_attention(st, layer, a->q_scratch, out_layer, a->S, a->n_q, st->prefix_len + a->S, a->mask_mode,

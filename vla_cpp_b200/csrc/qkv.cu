@@ -243,6 +243,236 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap w_map, const QkvParams p) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Fast path: bf16 x and weights with ln_w already folded in (W'[n][k] = W[n][k] * ln_w[k]).
+// Persistent CTAs (one per SM) walk the 128 x 256 output tiles; both operands arrive by TMA
+// through a 4-stage ring; the f32 accumulator is double-buffered in TMEM (2 x 256 columns) so
+// the epilogue of tile j overlaps the main loop of tile j+1.
+//   warp 0      TMA loader (x tile 128 x 64, weight tile 256 x 64 per stage)
+//   warp 1      tcgen05.mma issuer
+//   warps 2-5   epilogue: TMEM -> RMSNorm factor -> RoPE -> q buffer / KV pages
+//   warps 6-9   row statistics: read the x tile from shared memory, accumulate sum(x^2) per row
+constexpr int QKVF_THREADS = 320;
+
+__global__ void __launch_bounds__(QKVF_THREADS, 1)
+qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                    const QkvParams p, int tiles_m, int tiles_n) {
+    extern __shared__ uint8_t qkvf_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(qkvf_smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QKV_STAGES * QKV_STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + QKV_STAGES;
+    uint64_t *accum_full = bars + 2 * QKV_STAGES, *accum_empty = accum_full + 2;
+    uint64_t *stats_full = accum_empty + 2, *stats_empty = stats_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stats_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *stats = reinterpret_cast<float *>(smem + QKV_STAGES * QKV_STAGE_BYTES + 256);  // [2][128]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ksteps = (p.H + QKV_BK - 1) / QKV_BK;
+    const int n_tiles = tiles_m * tiles_n;
+    const WaitCtx wc{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < QKV_STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 5);  // MMA commit + one arrive per statistics warp
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&accum_full[i], 1);
+            mbar_init(&accum_empty[i], 128);
+            mbar_init(&stats_full[i], 128);
+            mbar_init(&stats_empty[i], 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&x_map);
+            tma_prefetch_desc(&w_map);
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
+                bool ok = true;
+                for (int kt = 0; kt < ksteps; ++kt, ++it) {
+                    const int st = it % QKV_STAGES;
+                    const uint32_t ph = (it / QKV_STAGES) & 1u;
+                    ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[st], QKV_STAGE_BYTES);
+                    uint8_t *sa = smem + st * QKV_STAGE_BYTES;
+                    tma_load_2d(sa, &x_map, &full[st], kt * QKV_BK, m0);
+                    tma_load_2d(sa + QKV_A_BYTES, &w_map, &full[st], kt * QKV_BK, n0);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, QKV_BM, QKV_BN);
+            uint32_t it = 0, j = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+                const uint32_t buf = j & 1u;
+                bool ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * QKV_BN;
+                for (int kt = 0; kt < ksteps; ++kt, ++it) {
+                    const int st = it % QKV_STAGES;
+                    const uint32_t ph = (it / QKV_STAGES) & 1u;
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + st * QKV_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + QKV_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < QKV_BK / 16; ++k)
+                        mma_f16(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                                smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
+                    tc_commit(&empty[st]);
+                }
+                if (!ok) break;
+                tc_commit(&accum_full[buf]);
+            }
+        }
+    } else if (warp >= 6) {
+        // ---- row statistics: thread <-> row of the tile ----
+        const int row = (warp - 6) * 32 + lane;
+        const uint32_t row_base = (row >> 3) * 1024 + (row & 7) * 128;
+        const uint32_t sw = row & 7;
+        uint32_t it = 0, j = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            const uint32_t buf = j & 1u;
+            float s0 = 0.0f, s1 = 0.0f;
+            for (int kt = 0; kt < ksteps; ++kt, ++it) {
+                const int st = it % QKV_STAGES;
+                const uint32_t ph = (it / QKV_STAGES) & 1u;
+                ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                const uint8_t *at = smem + st * QKV_STAGE_BYTES + row_base;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(h[e]);
+                        s0 = fmaf(f.x, f.x, s0);
+                        s1 = fmaf(f.y, f.y, s1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
+            }
+            if (!ok) break;
+            ok = mbar_wait(&stats_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+            if (!ok) break;
+            stats[buf * 128 + row] = s0 + s1;
+            mbar_arrive(&stats_full[buf]);
+        }
+    } else {
+        // ---- epilogue warps 2..5 ----
+        const int qtr = warp & 3;
+        const int row = qtr * 32 + lane;
+        const int hd = p.hd, half = hd >> 1;
+        const int n_total = (p.n_q + 2 * p.n_kv_proj) * hd;
+        uint32_t j = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            const uint32_t buf = j & 1u;
+            const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
+            const int m = m0 + row;
+            const bool row_ok = m < p.M;
+            ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (ok) ok = mbar_wait(&stats_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
+            const float rms = rsqrtf(stats[buf * 128 + row] / (float)p.H + p.eps);
+            const int obs = m / p.S, tok = m % p.S;
+            const float *cs = p.rope_cos + (size_t)tok * half;
+            const float *sn = p.rope_sin + (size_t)tok * half;
+            const uint32_t lane_addr = tmem_base + buf * QKV_BN + ((uint32_t)(qtr * 32) << 16);
+            for (int hc = 0; hc < QKV_BN; hc += hd) {  // one head per iteration
+                const int n = n0 + hc;
+                if (n >= n_total) break;
+                const int head = n / hd;
+                __nv_bfloat16 *dst;
+                bool rotate = true;
+                if (head < p.n_q) {
+                    dst = p.q_out + (((size_t)obs * p.n_q + head) * p.S + tok) * hd;
+                } else if (head < p.n_q + p.n_kv_proj) {
+                    const int kvh = head - p.n_q;
+                    dst = p.k_pages + (((size_t)obs * p.n_kv + kvh) * p.cap + p.prefix_len + tok) * hd;
+                } else {
+                    const int kvh = head - p.n_q - p.n_kv_proj;
+                    dst = p.v_pages + (((size_t)obs * p.n_kv + kvh) * p.cap + p.prefix_len + tok) * hd;
+                    rotate = false;
+                }
+                for (int c = 0; c < half; c += 32) {
+                    uint32_t lo[32], hi[32];
+                    tmem_ld32(lane_addr + (uint32_t)(hc + c), lo);
+                    tmem_ld32(lane_addr + (uint32_t)(hc + half + c), hi);
+                    tmem_ld_wait();
+                    uint32_t olo[16], ohi[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float a0 = __uint_as_float(lo[e]) * rms, a1 = __uint_as_float(lo[e + 1]) * rms;
+                        float b0 = __uint_as_float(hi[e]) * rms, b1 = __uint_as_float(hi[e + 1]) * rms;
+                        if (rotate) {
+                            const float2 cc = *reinterpret_cast<const float2 *>(cs + c + e);
+                            const float2 ss = *reinterpret_cast<const float2 *>(sn + c + e);
+                            const float r0 = a0 * cc.x - b0 * ss.x, r1 = a1 * cc.y - b1 * ss.y;
+                            b0 = b0 * cc.x + a0 * ss.x;
+                            b1 = b1 * cc.y + a1 * ss.y;
+                            a0 = r0;
+                            a1 = r1;
+                        }
+                        const __nv_bfloat162 l2 = __floats2bfloat162_rn(a0, a1), h2 = __floats2bfloat162_rn(b0, b1);
+                        olo[e >> 1] = *reinterpret_cast<const uint32_t *>(&l2);
+                        ohi[e >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
+                    }
+                    if (!row_ok) continue;
+                    uint4 *dl = reinterpret_cast<uint4 *>(dst + c), *dh = reinterpret_cast<uint4 *>(dst + half + c);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        dl[e] = make_uint4(olo[4 * e], olo[4 * e + 1], olo[4 * e + 2], olo[4 * e + 3]);
+                        dh[e] = make_uint4(ohi[4 * e], ohi[4 * e + 1], ohi[4 * e + 2], ohi[4 * e + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&accum_empty[buf]);
+            mbar_arrive(&stats_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// W'[n][k] = bf16(W[n][k] * ln_w[k])
+__global__ void fold_norm_weight_kernel(const __nv_bfloat16 *__restrict__ w, const float *__restrict__ ln_w,
+                                        __nv_bfloat16 *__restrict__ out, size_t rows, int H) {
+    const size_t total = rows * (size_t)H;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16(__bfloat162float(w[i]) * ln_w[i % H]);
+}
+
 // ---- prefix KV page writer: f32 [n_obs][P][n_kv][hd] -> bf16 pages [n_obs][n_kv][cap][hd] ----
 // (the reference keeps the prefill's K/V as F32 graph tensors: src/models/pi0.cpp:172-194,
 //  src/models/smolvla.cpp:793-794)
@@ -337,13 +567,23 @@ int32_t vlab200_rope_table(float *cos_out, float *sin_out, int32_t pos0, int32_t
     return VLAB200_OK;
 }
 
+int32_t vlab200_fold_norm_weight(const void *w_bf16, const float *ln_w, void *out_bf16, int64_t rows, int32_t H,
+                                 void *stream) {
+    if (!w_bf16 || !ln_w || !out_bf16 || rows <= 0 || H <= 0) return VLAB200_ERR_ARG;
+    vb::fold_norm_weight_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16 *>(w_bf16), ln_w, static_cast<__nv_bfloat16 *>(out_bf16), (size_t)rows, H);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
 int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const void *x, int32_t x_is_f32,
                                 const float *ln_w, const void *wqkv_bf16, const float *rope_cos,
                                 const float *rope_sin, float eps, int32_t S, int32_t H, int32_t n_q,
                                 int32_t project_kv, void *q_out, void *stream) {
     int rc = vb::check_store(st, layer);
     if (rc) return rc;
-    if (!x || !ln_w || !wqkv_bf16 || !rope_cos || !rope_sin || !q_out) return VLAB200_ERR_ARG;
+    if (!x || !wqkv_bf16 || !rope_cos || !rope_sin || !q_out) return VLAB200_ERR_ARG;
+    if (!ln_w && x_is_f32) return VLAB200_ERR_UNSUPPORTED;  // folded weights go with the bf16 TMA path
     if (S <= 0 || H <= 0 || n_q <= 0) return VLAB200_ERR_ARG;
     if (project_kv && st->prefix_len + S > st->cap) return VLAB200_ERR_ARG;
     if (H % 8 || H > 4096) return VLAB200_ERR_UNSUPPORTED;  // 16-byte rows; ln_w staged in shared memory
@@ -375,9 +615,34 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
     p.M = M; p.H = H; p.S = S; p.hd = hd; p.n_q = n_q; p.n_kv_proj = n_kv_proj; p.n_kv = st->n_kv;
     p.cap = st->cap; p.prefix_len = st->prefix_len; p.eps = eps; p.status = status;
     const int ksteps = (H + vb::QKV_BK - 1) / vb::QKV_BK;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (!ln_w) {
+        // folded weights + bf16 x: persistent all-TMA kernel
+        CUtensorMap xmap;
+        const uint64_t xdims[2] = {(uint64_t)H, (uint64_t)M};
+        const uint64_t xstrides[1] = {(uint64_t)H * 2};
+        const uint32_t xbox[2] = {vb::QKV_BK, vb::QKV_BM};
+        rc = vb::make_tensor_map(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, xdims, xstrides, xbox,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        const int fsmem = vb::QKV_STAGES * vb::QKV_STAGE_BYTES + 256 + 2 * 128 * 4 + 1024;
+        static bool fdone = false;
+        static int n_sm = 0;
+        if (!fdone) {
+            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
+            int dev = 0;
+            VB_CUDA(cudaGetDevice(&dev));
+            VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+            fdone = true;
+        }
+        const int tiles_m = (M + vb::QKV_BM - 1) / vb::QKV_BM, tiles_n = (n_total + vb::QKV_BN - 1) / vb::QKV_BN;
+        const int nt = tiles_m * tiles_n;
+        vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m, tiles_n);
+        VB_CUDA(cudaGetLastError());
+        return VLAB200_OK;
+    }
     const int smem = vb::QKV_STAGES * vb::QKV_STAGE_BYTES + 256 + ksteps * vb::QKV_BK * 4 + 1024;
     dim3 grid((M + vb::QKV_BM - 1) / vb::QKV_BM, (n_total + vb::QKV_BN - 1) / vb::QKV_BN);
-    cudaStream_t cs = static_cast<cudaStream_t>(stream);
     static int smem_set[2] = {0, 0};  // largest dynamic shared memory size opted into so far
     if (x_is_f32) {
         if (smem > smem_set[1]) {
