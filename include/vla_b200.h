@@ -110,7 +110,9 @@ VLAB200_API int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t 
  * (suffix row 0 sees only suffix column 0, other rows every column; src/models/pi0.cpp:640-651);
  * 2 = causal over the suffix (src/models/smolvla.cpp:1655-1664).  pad_ranges (optional, int32
  * [n_obs][2]) masks prefix columns [lo, hi) per observation (padded language slots).
- * Implemented for head_dim 64, kv_len <= 256, (n_q / n_kv) * S <= 256.
+ * head_dim 64 with kv_len <= 256 and (n_q / n_kv) * S <= 256 runs a kernel that holds the whole
+ * key range on chip; head_dim 64 / 128 / 256 of any length stream K and V in 64-key blocks with
+ * an online softmax.
  * Replaces ggml_flash_attn_ext / mul_mat+soft_max_ext+mul_mat at src/models/pi0.cpp:204-223,
  * src/models/smolvla.cpp:835-842,874-881 (src/layers/attn.h:38-57). */
 VLAB200_API int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, const void *q, void *out,

@@ -138,11 +138,10 @@ def test_q_only_projection_for_cross_attention_layers(oracle):
     assert qkv_case(oracle, SMOL, 2, seed=40, project_kv=False) < TOL
 
 
-def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads=None, poison=False):
+def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads=None, poison=False, hd=64):
     import torch
     import vla_cpp_b200 as vb
 
-    hd = 64
     rng = np.random.default_rng(seed)
     st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
     kv_len = P if cross else P + S
@@ -200,11 +199,57 @@ def test_attention_rejects_unsupported(oracle):
     require_cuda()
     import vla_cpp_b200 as vb
 
-    st = vb.KvStore(1, 1, 1, 256, 816, 51)
-    q = np.zeros((1, 8, 51, 256), np.float32)
+    st = vb.KvStore(1, 1, 1, 64, 20, 5)
+    st.c.head_dim = 96  # no kernel for this head size
+    q = np.zeros((1, 8, 5, 96), np.float32)
     with pytest.raises(vb.VlaB200Error) as e:
-        vb.attention(st, 0, bf16_tensor(oracle, q), 51, 8, 867, 1)
+        vb.attention(st, 0, bf16_tensor(oracle, q), 5, 8, 25, 1)
     assert e.value.code == -4
+    st.c.head_dim = 64
+    with pytest.raises(vb.VlaB200Error) as e:  # kv_len beyond the page capacity
+        vb.attention(st, 0, bf16_tensor(oracle, q), 5, 8, 26, 1)
+    assert e.value.code == -1
+
+
+@pytest.mark.parametrize("mask_mode", [0, 1, 2])
+def test_attention_pi0_shape_streaming_kernel(oracle, mask_mode):
+    """8 q heads on 1 kv head, head_dim 256, 816 + 51 keys: 4 row tiles x 14 key blocks."""
+    require_cuda()
+    assert attn_case(oracle, 2, 8, 1, 51, 816, mask_mode, seed=200 + mask_mode, hd=256) < TOL
+
+
+def test_attention_streaming_kernel_other_shapes(oracle):
+    require_cuda()
+    # BitVLA-LM-like heads (20q / 5kv, head_dim 128), bidirectional
+    assert attn_case(oracle, 2, 20, 5, 40, 300, 0, seed=210, hd=128) < TOL
+    # head_dim 64 beyond the on-chip kernel's limits: 400 keys; and g*S = 408 rows
+    assert attn_case(oracle, 2, 6, 2, 30, 370, 2, seed=211, hd=64) < TOL
+    assert attn_case(oracle, 1, 8, 1, 51, 100, 1, seed=212, hd=64) < TOL
+    # pad ranges, ragged key tail (kv_len % 64 != 0), cross-attention over a poisoned suffix
+    assert attn_case(oracle, 3, 8, 1, 51, 816, 1, seed=213, hd=256, pads=[(700, 816), (0, 0), (64, 128)]) < TOL
+    assert attn_case(oracle, 2, 8, 1, 51, 777, 0, seed=214, hd=256, cross=True, poison=True) < TOL
+    assert attn_case(oracle, 1, 8, 1, 5, 3, 2, seed=215, hd=256) < TOL
+
+
+def test_attention_streaming_kernel_large_score_spread(oracle):
+    """Keys whose scores grow along the sequence force the lazy running-maximum update (and the
+    rescale of O through TMEM) to trigger."""
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    hd, n_q, n_kv, S, P, n_obs = 256, 8, 1, 51, 816, 1
+    rng = np.random.default_rng(300)
+    st = vb.KvStore(1, n_obs, n_kv, hd, P, S)
+    q = oracle.bf16_round(rng.standard_normal((n_obs, n_q, S, hd)).astype(np.float32))
+    ramp = np.linspace(0.2, 3.0, st.cap).astype(np.float32)[None, None, :, None]
+    k = oracle.bf16_round((rng.standard_normal((n_obs, n_kv, st.cap, hd)) * ramp).astype(np.float32))
+    v = oracle.bf16_round(rng.standard_normal((n_obs, n_kv, st.cap, hd)).astype(np.float32))
+    st.k[0].copy_(bf16_tensor(oracle, k))
+    st.v[0].copy_(bf16_tensor(oracle, v))
+    out = vb.attention(st, 0, bf16_tensor(oracle, q), S, n_q, P + S, vb.MASK_PI0)
+    assert vb.device_status() == 0
+    ref = oracle.attention(q[0].transpose(1, 0, 2), k[0].transpose(1, 0, 2), v[0].transpose(1, 0, 2), P, 1)
+    assert rel_l2(from_bf16(oracle, out)[0], ref) < TOL
 
 
 def test_isolated_denoise_attention_two_layers_chain(oracle):

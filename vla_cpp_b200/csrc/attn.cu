@@ -24,6 +24,10 @@
 
 namespace vb {
 
+// streaming kernel for wide heads / long key ranges (attn_flash.cu)
+int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream);
+
 constexpr int ATT_THREADS = 352;  // warps 0-3 / 4-7: softmax groups, 8: loader, 9-10: MMA issuers
 constexpr int ATT_MAX_KEYS = 256;
 constexpr int ATT_Q_TILE_BYTES = 128 * 128;
@@ -437,7 +441,10 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
         return VLAB200_ERR_ARG;
     const int g = n_q / st->n_kv;
     const int R = g * S;
-    if (st->head_dim != 64 || kv_len > vb::ATT_MAX_KEYS || R > 256) return VLAB200_ERR_UNSUPPORTED;
+    if (st->head_dim != 64 && st->head_dim != 128 && st->head_dim != 256) return VLAB200_ERR_UNSUPPORTED;
+    if (st->head_dim != 64 || kv_len > vb::ATT_MAX_KEYS || R > 256)
+        return vb::attention_flash(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges,
+                                   static_cast<cudaStream_t>(stream));
     int *status = vb::device_status_ptr();
     if (!status) return vb::cuda_fail(cudaGetLastError(), "device_status_ptr");
 

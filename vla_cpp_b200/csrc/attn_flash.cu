@@ -1,0 +1,410 @@
+// Action-query attention for wide heads / long prefixes (head_dim 128 or 256, any number of
+// keys): the pi0-shaped case (8 q heads on 1 kv head, head_dim 256, 816 + 51 keys).
+//
+// Work unit = (kv head, observation, 128-row tile of the g*S stacked query rows).  Persistent
+// CTAs walk the units; K and V pages stream through shared memory in 64-key blocks:
+//
+//   loader warp   TMA (SWIZZLE_128B): the Q tile once per unit, K / V blocks through 2-stage rings
+//   MMA warp      S_j = Q K_j^T (kind::f16, f32 in TMEM, double-buffered), O += P_j V_j with
+//                 A = P_j read from TMEM and V_j as an MN-major operand; S_{j+1} is issued
+//                 before P_j V_j so the tensor pipe works while block j is in the softmax
+//   4 softmax warps  one thread per row: block maximum, exp2 with the scale folded in, running
+//                 row sum; P_j (bf16) overwrites S_j in TMEM.  The running maximum is only raised
+//                 (and O rescaled through TMEM) when a block exceeds it by more than 2^8, which
+//                 keeps P within bf16 range without touching O in the common case.
+//
+// Reference: src/models/pi0.cpp:204-223 (explicit K^T Q -> soft_max_ext -> V P with the score
+// matrix and two permuted copies of K/V in HBM every layer-step), mask src/models/pi0.cpp:640-651.
+#include <cuda_bf16.h>
+
+#include "host_common.h"
+#include "tc5.cuh"
+
+namespace vb {
+
+constexpr int FA_THREADS = 192;  // warps 0-3 softmax/epilogue, 4 loader, 5 MMA
+constexpr int FA_BKV = 64;       // keys per block
+
+struct FlashParams {
+    __nv_bfloat16 *out;  // [n_obs][S][n_q*hd]
+    const int32_t *pad;
+    int S, n_q, n_kv, g, kv_len, prefix_len, mask_mode, R, n_mt, n_units, n_blocks, page0;
+    float scale_log2;
+    int *status;
+};
+
+__device__ __forceinline__ float fa_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+        "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+        "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+template <int HD>
+struct FlashSmem {
+    static constexpr int CB = HD / 64;                   // 64-element column blocks
+    static constexpr int Q_BYTES = CB * 128 * 128;       // [CB][128 rows][128 B]
+    static constexpr int KV_BYTES = CB * FA_BKV * 128;   // [CB][64 keys][128 B]
+    static constexpr int K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_BYTES;
+    static constexpr int BAR_OFF = Q_BYTES + 4 * KV_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+    static constexpr int O_COLS = HD;                    // O [0, HD), S buffers at HD, HD + 64
+    static constexpr int TMEM_COLS = (HD + 128 <= 256) ? 256 : 512;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                  const __grid_constant__ CUtensorMap v_map, const FlashParams p) {
+    using L = FlashSmem<HD>;
+    extern __shared__ uint8_t fa_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *q_full = bars, *q_free = bars + 1, *o_done = bars + 2, *o_free = bars + 3;
+    uint64_t *k_full = bars + 4, *k_free = bars + 6, *v_full = bars + 8, *v_free = bars + 10;
+    uint64_t *s_full = bars + 12, *p_full = bars + 14, *pv_done = bars + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const WaitCtx wc{abort_flag, p.status};
+    const int nb = p.n_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(q_free, 1);
+        mbar_init(o_done, 1);
+        mbar_init(o_free, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_free[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_free[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&pv_done[i], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, L::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ----------------------------------------------------------------- loader
+        if (lane == 0) {
+            tma_prefetch_desc(&q_map);
+            tma_prefetch_desc(&k_map);
+            tma_prefetch_desc(&v_map);
+            uint32_t ui = 0, jb = 0;  // units and key blocks processed so far by this CTA
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+                const int item = unit / p.n_mt, mt = unit % p.n_mt;
+                const int obs = item / p.n_kv, kvh = item % p.n_kv;
+                const int page = p.page0 + item;
+                const int qrow0 = (obs * p.n_q + kvh * p.g) * p.S + mt * 128;
+                ok = mbar_wait(q_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                mbar_expect_tx(q_full, L::Q_BYTES);
+                for (int cb = 0; cb < L::CB; ++cb) tma_load_2d(smem + cb * 16384, &q_map, q_full, cb * 64, qrow0);
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    const int st = jb & 1;
+                    const uint32_t ph = (jb >> 1) & 1u;
+                    ok = mbar_wait(&k_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&k_full[st], L::KV_BYTES);
+                    for (int cb = 0; cb < L::CB; ++cb)
+                        tma_load_3d(smem + L::K_OFF + st * L::KV_BYTES + cb * 8192, &k_map, &k_full[st], cb * 64,
+                                    j * FA_BKV, page);
+                    ok = mbar_wait(&v_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&v_full[st], L::KV_BYTES);
+                    for (int cb = 0; cb < L::CB; ++cb)
+                        tma_load_3d(smem + L::V_OFF + st * L::KV_BYTES + cb * 8192, &v_map, &v_full[st], cb * 64,
+                                    j * FA_BKV, page);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ----------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 128, FA_BKV);
+            constexpr uint32_t idesc_o = make_idesc(1, 1, 1, 0, 1, 128, HD);
+            const uint32_t q_addr = smem_u32(smem);
+            const uint32_t k_base = q_addr + L::K_OFF, v_base = q_addr + L::V_OFF;
+            uint32_t ui = 0, jb = 0;
+            bool ok = true;
+            auto issue_s = [&](uint32_t jbx) {  // S block with global block counter jbx
+                const uint32_t st = jbx & 1u;
+                const uint32_t k_addr = k_base + st * L::KV_BYTES;
+                const uint32_t d = tmem_base + L::O_COLS + st * 64;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    mma_f16(d, smem_desc_sw128(q_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                            smem_desc_sw128(k_addr + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_s,
+                            kk != 0 ? 1u : 0u);
+                tc_commit(&s_full[st]);
+                tc_commit(&k_free[st]);
+            };
+            for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+                ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                // first S block of the unit: its TMEM buffer was last read by the P V of block jb-2
+                ok = mbar_wait(&k_full[jb & 1u], (jb >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
+                if (ok && jb >= 2) ok = mbar_wait(&pv_done[jb & 1u], ((jb - 2) >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                issue_s(jb);
+                if (nb == 1) tc_commit(q_free);
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    const uint32_t st = jb & 1u, ph = (jb >> 1) & 1u;
+                    if (j + 1 < nb) {
+                        const uint32_t jn = jb + 1;
+                        ok = mbar_wait(&k_full[jn & 1u], (jn >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
+                        if (ok && jn >= 2) ok = mbar_wait(&pv_done[jn & 1u], ((jn - 2) >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(jn);
+                        if (j + 2 == nb) tc_commit(q_free);  // the unit's last S block has been issued
+                    }
+                    ok = mbar_wait(&p_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok) ok = mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok && j == 0) ok = mbar_wait(o_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t v_addr = v_base + st * L::KV_BYTES;
+                    const uint32_t p_tmem = tmem_base + L::O_COLS + st * 64;
+#pragma unroll
+                    for (int k16 = 0; k16 < FA_BKV / 16; ++k16)
+                        mma_f16_tmem_a(tmem_base, p_tmem + (uint32_t)(k16 * 8),
+                                       smem_desc_sw128(v_addr + k16 * 2048, 8192, 1024), idesc_o,
+                                       (j | k16) != 0 ? 1u : 0u);
+                    tc_commit(&pv_done[st]);
+                    tc_commit(&v_free[st]);
+                }
+                if (!ok) break;
+                tc_commit(o_done);
+            }
+        }
+    } else {
+        // ----------------------------------------------------------------- softmax / epilogue
+        const int qtr = warp;
+        const uint32_t lane_sel = (uint32_t)(qtr * 32) << 16;
+        const int n_suffix_cols = p.kv_len - p.prefix_len;
+        uint32_t ui = 0, jb = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+            const int item = unit / p.n_mt, mt = unit % p.n_mt;
+            const int obs = item / p.n_kv, kvh = item % p.n_kv;
+            const int row = mt * 128 + qtr * 32 + lane;
+            const bool row_ok = row < p.R;
+            const int head_l = row_ok ? row / p.S : 0, tok = row_ok ? row % p.S : 0;
+            int pad_lo = 0, pad_hi = 0;
+            if (p.pad) {
+                pad_lo = p.pad[2 * obs];
+                pad_hi = p.pad[2 * obs + 1];
+            }
+            int limit = n_suffix_cols;
+            if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
+            else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+            const int jmax = p.prefix_len + limit;
+            int clean_end = p.prefix_len;
+            if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
+            const int pad_w = pad_hi - pad_lo;
+            float m_used = -INFINITY;  // running maximum in log2 units (lazy)
+            float l_sum = 0.0f;
+            for (int j = 0; j < nb; ++j, ++jb) {
+                const uint32_t st = jb & 1u, ph = (jb >> 1) & 1u;
+                const uint32_t s_addr = tmem_base + L::O_COLS + st * 64 + lane_sel;
+                ok = mbar_wait(&s_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sa[32], sb[32];
+                tmem_ld32(s_addr, sa);
+                tmem_ld32(s_addr + 32, sb);
+                tmem_ld_wait();
+                const int c0 = j * FA_BKV;
+                const bool clean = c0 + FA_BKV <= clean_end;
+                if (!clean) {
+                    const int rel_jmax = jmax - c0, rel_pad = pad_lo - c0;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
+                        const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
+                        sa[e] = v0 ? sa[e] : 0xff800000u;
+                        sb[e] = v1 ? sb[e] : 0xff800000u;
+                    }
+                }
+                float t[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    t[e] = fmaxf(fmaxf(fmaxf(__uint_as_float(sa[4 * e]), __uint_as_float(sa[4 * e + 1])),
+                                       fmaxf(__uint_as_float(sa[4 * e + 2]), __uint_as_float(sa[4 * e + 3]))),
+                                 fmaxf(fmaxf(__uint_as_float(sb[4 * e]), __uint_as_float(sb[4 * e + 1])),
+                                       fmaxf(__uint_as_float(sb[4 * e + 2]), __uint_as_float(sb[4 * e + 3]))));
+                const float bm = fmaxf(fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])),
+                                       fmaxf(fmaxf(t[4], t[5]), fmaxf(t[6], t[7]))) * p.scale_log2;
+                // raise the running maximum only when a block exceeds it by more than 2^8
+                float factor = 1.0f;
+                const bool raise = bm > m_used + 8.0f;
+                if (raise) {
+                    factor = (m_used == -INFINITY) ? 0.0f : fa_ex2(m_used - bm);
+                    m_used = bm;
+                    l_sum *= factor;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                    // O holds contributions scaled with the old maximum: rescale it in TMEM once the
+                    // previous block's P V has landed
+                    const uint32_t jp = jb - 1;
+                    ok = mbar_wait(&pv_done[jp & 1u], (jp >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+                    if (!ok) break;
+                    tc_fence_after();
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * factor);
+                        tmem_st32(tmem_base + lane_sel + (uint32_t)c, ov);
+                    }
+                    tmem_st_wait();
+                }
+                const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+                uint32_t pk[32];
+                float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const float p0 = fa_ex2(fmaf(__uint_as_float(sa[e]), p.scale_log2, -mref));
+                    const float p1 = fa_ex2(fmaf(__uint_as_float(sa[e + 1]), p.scale_log2, -mref));
+                    const float p2 = fa_ex2(fmaf(__uint_as_float(sb[e]), p.scale_log2, -mref));
+                    const float p3 = fa_ex2(fmaf(__uint_as_float(sb[e + 1]), p.scale_log2, -mref));
+                    s0 += p0 + p2;
+                    s1 += p1 + p3;
+                    pk[e >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
+                    pk[16 + (e >> 1)] = __byte_perm(__float_as_uint(p2) + 0x8000u, __float_as_uint(p3) + 0x8000u, 0x7632);
+                }
+                l_sum += s0 + s1;
+                tmem_st32(s_addr, pk);  // P_j (64 keys, bf16) over the first 32 columns of S_j
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&p_full[st]);
+            }
+            if (!ok) break;
+            // ---- epilogue: O / l -> bf16 -> out ----
+            ok = mbar_wait(o_done, ui & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
+            const float inv = 1.0f / l_sum;
+            __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                tmem_ld_wait();
+                if (row_ok) {
+                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + c);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[8 * q4 + 2 * e]) * inv,
+                                                                           __uint_as_float(ov[8 * q4 + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        d4[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(o_free);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, L::TMEM_COLS);
+    }
+}
+
+template <int HD>
+static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
+                        int mask_mode, const int32_t *pad_ranges, cudaStream_t stream) {
+    using L = FlashSmem<HD>;
+    int *status = device_status_ptr();
+    if (!status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
+    CUtensorMap qmap, kmap, vmap;
+    {
+        const uint64_t dims[2] = {(uint64_t)HD, (uint64_t)st->n_obs * n_q * S};
+        const uint64_t strides[1] = {(uint64_t)HD * 2};
+        const uint32_t box[2] = {64, 128};
+        int rc = make_tensor_map(&qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    {
+        // rows >= kv_len are outside the map: TMA zero-fills them
+        const uint64_t dims[3] = {(uint64_t)HD, (uint64_t)kv_len, (uint64_t)st->n_layers * st->n_obs * st->n_kv};
+        const uint64_t strides[2] = {(uint64_t)HD * 2, (uint64_t)st->cap * HD * 2};
+        const uint32_t box[3] = {64, FA_BKV, 1};
+        int rc = make_tensor_map(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->k_pages, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        rc = make_tensor_map(&vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->v_pages, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    FlashParams p;
+    p.out = static_cast<__nv_bfloat16 *>(out);
+    p.pad = pad_ranges;
+    p.S = S; p.n_q = n_q; p.n_kv = st->n_kv; p.g = n_q / st->n_kv; p.kv_len = kv_len; p.prefix_len = st->prefix_len;
+    p.mask_mode = mask_mode;
+    p.R = p.g * S;
+    p.n_mt = (p.R + 127) / 128;
+    p.n_units = st->n_obs * st->n_kv * p.n_mt;
+    p.n_blocks = (kv_len + FA_BKV - 1) / FA_BKV;
+    p.page0 = layer * st->n_obs * st->n_kv;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    p.status = status;
+    static bool attr_done = false;
+    static int n_sm = 0;
+    if (!attr_done) {
+        VB_CUDA(cudaFuncSetAttribute(attn_flash_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        int dev = 0;
+        VB_CUDA(cudaGetDevice(&dev));
+        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+        attr_done = true;
+    }
+    const int grid = p.n_units < n_sm ? p.n_units : n_sm;
+    attn_flash_kernel<HD><<<grid, FA_THREADS, L::TOTAL, stream>>>(qmap, kmap, vmap, p);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream) {
+    if (st->head_dim == 256) return launch_flash<256>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
+    if (st->head_dim == 128) return launch_flash<128>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
+    if (st->head_dim == 64) return launch_flash<64>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
+    return VLAB200_ERR_UNSUPPORTED;
+}
+
+}  // namespace vb
