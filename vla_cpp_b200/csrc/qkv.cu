@@ -251,42 +251,54 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap w_map, const QkvParams p) {
 // the epilogue of tile j overlaps the main loop of tile j+1.
 //   warp 0      TMA loader (x tile 128 x 64, weight tile 256 x 64 per stage)
 //   warp 1      tcgen05.mma issuer
-//   warps 2-5   epilogue: TMEM -> RMSNorm factor -> RoPE -> q buffer / KV pages
+//   warps 2-5, 10-13  epilogue (two warps per TMEM lane quarter, alternating heads):
+//               TMEM -> RMSNorm factor -> RoPE -> transpose in shared memory -> q buffer / KV pages
 //   warps 6-9   row statistics: read the x tile from shared memory, accumulate sum(x^2) per row
-constexpr int QKVF_THREADS = 320;
+constexpr int QKVF_THREADS = 448;
+constexpr int QKVF_STAGING = 8 * 4096;  // per epilogue warp: 2 pieces x 32 rows x 64 bytes
 
 __global__ void __launch_bounds__(QKVF_THREADS, 1)
 qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
-                    const QkvParams p, int tiles_m, int tiles_n) {
+                    const QkvParams p, int tiles_m, int tiles_n, int nst) {
     extern __shared__ uint8_t qkvf_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(qkvf_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QKV_STAGES * QKV_STAGE_BYTES);
-    uint64_t *full = bars, *empty = bars + QKV_STAGES;
-    uint64_t *accum_full = bars + 2 * QKV_STAGES, *accum_empty = accum_full + 2;
+    uint8_t *aux = smem + nst * QKV_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aux);
+    uint64_t *full = bars, *empty = bars + 4;
+    uint64_t *accum_full = bars + 8, *accum_empty = accum_full + 2;
     uint64_t *stats_full = accum_empty + 2, *stats_empty = stats_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stats_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *stats = reinterpret_cast<float *>(smem + QKV_STAGES * QKV_STAGE_BYTES + 256);  // [2][128]
+    float *stats = reinterpret_cast<float *>(aux + 256);   // [2][128]
+    uint8_t *staging = aux + 256 + 1024;                   // [4 warps][2][32][64 B]
+    float *rope_s = reinterpret_cast<float *>(staging + QKVF_STAGING);  // cos [half][S], sin [half][S]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ksteps = (p.H + QKV_BK - 1) / QKV_BK;
     const int n_tiles = tiles_m * tiles_n;
+    const int half = p.hd >> 1;
     const WaitCtx wc{abort_flag, p.status};
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < QKV_STAGES; ++i) {
+        for (int i = 0; i < nst; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 5);  // MMA commit + one arrive per statistics warp
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&accum_full[i], 1);
-            mbar_init(&accum_empty[i], 128);
+            mbar_init(&accum_empty[i], 256);
             mbar_init(&stats_full[i], 128);
-            mbar_init(&stats_empty[i], 128);
+            mbar_init(&stats_empty[i], 256);
         }
         *abort_flag = 0;
         fence_barrier_init();
+    }
+    // RoPE table, transposed so that lanes (consecutive tokens) read consecutive words
+    for (int i = threadIdx.x; i < p.S * half; i += QKVF_THREADS) {
+        const int t = i / half, d = i % half;
+        rope_s[d * p.S + t] = p.rope_cos[i];
+        rope_s[(half + d) * p.S + t] = p.rope_sin[i];
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 512);
@@ -301,36 +313,33 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
         if (lane == 0) {
             tma_prefetch_desc(&x_map);
             tma_prefetch_desc(&w_map);
-            uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
-                bool ok = true;
-                for (int kt = 0; kt < ksteps; ++kt, ++it) {
-                    const int st = it % QKV_STAGES;
-                    const uint32_t ph = (it / QKV_STAGES) & 1u;
+                for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_expect_tx(&full[st], QKV_STAGE_BYTES);
                     uint8_t *sa = smem + st * QKV_STAGE_BYTES;
                     tma_load_2d(sa, &x_map, &full[st], kt * QKV_BK, m0);
                     tma_load_2d(sa + QKV_A_BYTES, &w_map, &full[st], kt * QKV_BK, n0);
+                    if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
                 }
-                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, QKV_BM, QKV_BN);
-            uint32_t it = 0, j = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+            uint32_t st = 0, ph = 0, j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
                 const uint32_t buf = j & 1u;
-                bool ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * QKV_BN;
-                for (int kt = 0; kt < ksteps; ++kt, ++it) {
-                    const int st = it % QKV_STAGES;
-                    const uint32_t ph = (it / QKV_STAGES) & 1u;
+                for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
@@ -341,24 +350,23 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                         mma_f16(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
                                 smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
                     tc_commit(&empty[st]);
+                    if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 tc_commit(&accum_full[buf]);
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < 10) {
         // ---- row statistics: thread <-> row of the tile ----
         const int row = (warp - 6) * 32 + lane;
         const uint32_t row_base = (row >> 3) * 1024 + (row & 7) * 128;
         const uint32_t sw = row & 7;
-        uint32_t it = 0, j = 0;
+        uint32_t st = 0, ph = 0, j = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
             const uint32_t buf = j & 1u;
             float s0 = 0.0f, s1 = 0.0f;
-            for (int kt = 0; kt < ksteps; ++kt, ++it) {
-                const int st = it % QKV_STAGES;
-                const uint32_t ph = (it / QKV_STAGES) & 1u;
+            for (int kt = 0; kt < ksteps; ++kt) {
                 ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 const uint8_t *at = smem + st * QKV_STAGE_BYTES + row_base;
@@ -375,6 +383,7 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[st]);
+                if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
             }
             if (!ok) break;
             ok = mbar_wait(&stats_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
@@ -383,44 +392,60 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
             mbar_arrive(&stats_full[buf]);
         }
     } else {
-        // ---- epilogue warps 2..5 ----
+        // ---- epilogue warps 2..5 (group 0) and 10..13 (group 1) ----
         const int qtr = warp & 3;
+        const int grp = warp >= 10 ? 1 : 0;
         const int row = qtr * 32 + lane;
-        const int hd = p.hd, half = hd >> 1;
+        const int hd = p.hd;
         const int n_total = (p.n_q + 2 * p.n_kv_proj) * hd;
+        uint8_t *stg = staging + (grp * 4 + qtr) * 4096;
+        const uint32_t my_sw = (uint32_t)((lane >> 1) & 3);
         uint32_t j = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
             const uint32_t buf = j & 1u;
             const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
             const int m = m0 + row;
-            const bool row_ok = m < p.M;
+            const int tok = m % p.S;
+            // the four rows this lane writes out after the transpose through shared memory
+            int w_obs[4], w_tok[4];
+            bool w_ok[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int mr = m0 + qtr * 32 + (lane >> 2) + 8 * i;
+                w_ok[i] = mr < p.M;
+                w_obs[i] = mr / p.S;
+                w_tok[i] = mr % p.S;
+            }
             ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
             if (ok) ok = mbar_wait(&stats_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
             if (!ok) break;
             tc_fence_after();
             const float rms = rsqrtf(stats[buf * 128 + row] / (float)p.H + p.eps);
-            const int obs = m / p.S, tok = m % p.S;
-            const float *cs = p.rope_cos + (size_t)tok * half;
-            const float *sn = p.rope_sin + (size_t)tok * half;
+            const float *cs = rope_s + tok, *sn = rope_s + (size_t)half * p.S + tok;
             const uint32_t lane_addr = tmem_base + buf * QKV_BN + ((uint32_t)(qtr * 32) << 16);
-            for (int hc = 0; hc < QKV_BN; hc += hd) {  // one head per iteration
+            // heads of the tile alternate between the two groups; a single wide head is split by columns
+            const int heads_in_tile = QKV_BN / hd;
+            for (int hc = (heads_in_tile > 1 ? grp * hd : 0); hc < QKV_BN; hc += (heads_in_tile > 1 ? 2 * hd : hd)) {
                 const int n = n0 + hc;
                 if (n >= n_total) break;
                 const int head = n / hd;
-                __nv_bfloat16 *dst;
                 bool rotate = true;
+                __nv_bfloat16 *base;
+                size_t obs_stride, tok0;  // element offsets: base + obs*obs_stride + (tok0 + tok)*hd
                 if (head < p.n_q) {
-                    dst = p.q_out + (((size_t)obs * p.n_q + head) * p.S + tok) * hd;
-                } else if (head < p.n_q + p.n_kv_proj) {
-                    const int kvh = head - p.n_q;
-                    dst = p.k_pages + (((size_t)obs * p.n_kv + kvh) * p.cap + p.prefix_len + tok) * hd;
+                    base = p.q_out + (size_t)head * p.S * hd;
+                    obs_stride = (size_t)p.n_q * p.S * hd;
+                    tok0 = 0;
                 } else {
-                    const int kvh = head - p.n_q - p.n_kv_proj;
-                    dst = p.v_pages + (((size_t)obs * p.n_kv + kvh) * p.cap + p.prefix_len + tok) * hd;
-                    rotate = false;
+                    const bool is_v = head >= p.n_q + p.n_kv_proj;
+                    const int kvh = head - p.n_q - (is_v ? p.n_kv_proj : 0);
+                    base = (is_v ? p.v_pages : p.k_pages) + (size_t)kvh * p.cap * hd;
+                    obs_stride = (size_t)p.n_kv * p.cap * hd;
+                    tok0 = (size_t)p.prefix_len;
+                    rotate = !is_v;
                 }
-                for (int c = 0; c < half; c += 32) {
+                for (int c = (heads_in_tile > 1 ? 0 : grp * 32); c < half; c += (heads_in_tile > 1 ? 32 : 64)) {
                     uint32_t lo[32], hi[32];
                     tmem_ld32(lane_addr + (uint32_t)(hc + c), lo);
                     tmem_ld32(lane_addr + (uint32_t)(hc + half + c), hi);
@@ -431,11 +456,11 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                         float a0 = __uint_as_float(lo[e]) * rms, a1 = __uint_as_float(lo[e + 1]) * rms;
                         float b0 = __uint_as_float(hi[e]) * rms, b1 = __uint_as_float(hi[e + 1]) * rms;
                         if (rotate) {
-                            const float2 cc = *reinterpret_cast<const float2 *>(cs + c + e);
-                            const float2 ss = *reinterpret_cast<const float2 *>(sn + c + e);
-                            const float r0 = a0 * cc.x - b0 * ss.x, r1 = a1 * cc.y - b1 * ss.y;
-                            b0 = b0 * cc.x + a0 * ss.x;
-                            b1 = b1 * cc.y + a1 * ss.y;
+                            const float c0 = cs[(c + e) * p.S], c1 = cs[(c + e + 1) * p.S];
+                            const float s0 = sn[(c + e) * p.S], s1 = sn[(c + e + 1) * p.S];
+                            const float r0 = a0 * c0 - b0 * s0, r1 = a1 * c1 - b1 * s1;
+                            b0 = b0 * c0 + a0 * s0;
+                            b1 = b1 * c1 + a1 * s1;
                             a0 = r0;
                             a1 = r1;
                         }
@@ -443,13 +468,29 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                         olo[e >> 1] = *reinterpret_cast<const uint32_t *>(&l2);
                         ohi[e >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
                     }
-                    if (!row_ok) continue;
-                    uint4 *dl = reinterpret_cast<uint4 *>(dst + c), *dh = reinterpret_cast<uint4 *>(dst + half + c);
+                    // transpose through shared memory: thread-per-row -> 64 contiguous bytes per 4 lanes
+                    uint8_t *mine = stg + lane * 64;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        dl[e] = make_uint4(olo[4 * e], olo[4 * e + 1], olo[4 * e + 2], olo[4 * e + 3]);
-                        dh[e] = make_uint4(ohi[4 * e], ohi[4 * e + 1], ohi[4 * e + 2], ohi[4 * e + 3]);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        *reinterpret_cast<uint4 *>(mine + (((uint32_t)q4 ^ my_sw) << 4)) =
+                            make_uint4(olo[4 * q4], olo[4 * q4 + 1], olo[4 * q4 + 2], olo[4 * q4 + 3]);
+                        *reinterpret_cast<uint4 *>(mine + 2048 + (((uint32_t)q4 ^ my_sw) << 4)) =
+                            make_uint4(ohi[4 * q4], ohi[4 * q4 + 1], ohi[4 * q4 + 2], ohi[4 * q4 + 3]);
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = (lane >> 2) + 8 * i;
+                        const uint32_t off = (uint32_t)rr * 64 + ((((uint32_t)lane & 3u) ^ (uint32_t)((rr >> 1) & 3)) << 4);
+                        const uint4 vlo = *reinterpret_cast<const uint4 *>(stg + off);
+                        const uint4 vhi = *reinterpret_cast<const uint4 *>(stg + 2048 + off);
+                        if (w_ok[i]) {
+                            __nv_bfloat16 *d = base + (size_t)w_obs[i] * obs_stride + (tok0 + w_tok[i]) * hd + (lane & 3) * 8;
+                            *reinterpret_cast<uint4 *>(d + c) = vlo;
+                            *reinterpret_cast<uint4 *>(d + half + c) = vhi;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
@@ -625,11 +666,17 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
         rc = vb::make_tensor_map(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, xdims, xstrides, xbox,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        const int fsmem = vb::QKV_STAGES * vb::QKV_STAGE_BYTES + 256 + 2 * 128 * 4 + 1024;
+        // shared memory: stages + barriers/stats + store staging + transposed RoPE table
+        const int aux = 256 + 1024 + vb::QKVF_STAGING + 2 * (hd / 2) * S * 4;
+        int nst = 4;
+        while (nst > 2 && nst * vb::QKV_STAGE_BYTES + aux + 1024 > 227 * 1024) --nst;
+        const int fsmem = nst * vb::QKV_STAGE_BYTES + aux + 1024;
+        if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
         static bool fdone = false;
         static int n_sm = 0;
         if (!fdone) {
-            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
+            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024));
             int dev = 0;
             VB_CUDA(cudaGetDevice(&dev));
             VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
@@ -637,7 +684,8 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
         }
         const int tiles_m = (M + vb::QKV_BM - 1) / vb::QKV_BM, tiles_n = (n_total + vb::QKV_BN - 1) / vb::QKV_BN;
         const int nt = tiles_m * tiles_n;
-        vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m, tiles_n);
+        vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m, tiles_n,
+                                                                                      nst);
         VB_CUDA(cudaGetLastError());
         return VLAB200_OK;
     }
