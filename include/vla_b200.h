@@ -140,6 +140,21 @@ typedef struct {
 VLAB200_API int32_t vlab200_denoise_attn_loop(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
                                               void *stream);
 
+/* vlab200_denoise_attn_loop for callers that have no way to obtain device scratch memory: a
+ * plugin running inside a host that owns the allocator and hands out only input and output
+ * buffers, or code running while cudaMalloc is off limits (inside a latency-critical control
+ * loop, or when the device is fully committed to other tenants).  It has no counterpart in the
+ * reference.  The query buffer (a->q_scratch, which is ignored here) comes from a 16 MiB array
+ * built into the library image, so n_obs * n_q * S * head_dim * 2 bytes must not exceed 16 MiB
+ * (VLAB200_ERR_UNSUPPORTED with an explanatory vlab200_last_error() otherwise).  The call
+ * allocates nothing on host or device.  The first call on each device looks up the array's
+ * device address; make that first call outside any stream capture.  All calls on a device share
+ * the one array and it keeps whatever the previous call left in it (every row that is read is
+ * written first, so nothing needs clearing); two calls whose kernels overlap on the GPU (different
+ * streams, or threads) race on it. */
+VLAB200_API int32_t vlab200_denoise_attn_loop_static(const vlab200_kv_store *st,
+                                                     const vlab200_denoise_attn_args *a, void *stream);
+
 /* Same loop with the hidden states and the result in (pinned) HOST memory: a->x is a host
  * pointer; each step's hidden states [n_layers][n_obs*S][H] are copied into the device
  * staging buffer x_stage (2 x that size, double-buffered on an internal copy stream) while

@@ -17,7 +17,8 @@ OK, ERR_ARG, ERR_CUDA, ERR_DEVICE, ERR_UNSUPPORTED = 0, -1, -2, -3, -4
 class VlaB200Error(RuntimeError):
     def __init__(self, code, what):
         self.code = code
-        super().__init__(f"{what}: status {code}" + (f" ({lib().vlab200_last_error().decode()})" if code == ERR_CUDA else ""))
+        detail = lib().vlab200_last_error().decode() if code in (ERR_CUDA, ERR_UNSUPPORTED) else ""
+        super().__init__(f"{what}: status {code}" + (f" ({detail})" if detail else ""))
 
 
 def lib():
@@ -45,6 +46,7 @@ EXPORTS = [
     "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_fold_norm_weight",
     "vlab200_qkv_rope_append",
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
+    "vlab200_denoise_attn_loop_static",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
@@ -224,6 +226,18 @@ class DenoiseAttn:
         a = self._args(x.data_ptr(), x.shape[0], x.dtype == torch.float32)
         _check(lib().vlab200_denoise_attn_loop(C.byref(self.store.c), C.byref(a), _stream()),
                "vlab200_denoise_attn_loop")
+        return self.out
+
+    def run_static(self, x):
+        """Like run(), but the query buffer comes from the library's built-in scratch array (no
+        device allocation on this path; limited to 16 MiB of queries)."""
+        import torch
+
+        assert x.is_cuda and x.is_contiguous() and x.shape[1] == self.n_layers
+        a = self._args(x.data_ptr(), x.shape[0], x.dtype == torch.float32)
+        a.q_scratch = None
+        _check(lib().vlab200_denoise_attn_loop_static(C.byref(self.store.c), C.byref(a), _stream()),
+               "vlab200_denoise_attn_loop_static")
         return self.out
 
     def run_host(self, x_host, out_host):

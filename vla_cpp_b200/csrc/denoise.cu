@@ -32,6 +32,27 @@ static int run_layer_step(const vlab200_kv_store *st, const vlab200_denoise_attn
                              a->pad_ranges, cs);
 }
 
+// Scratch for vlab200_denoise_attn_loop_static: lives in the library image, so every device
+// that loads the library carries these bytes until the process exits.
+constexpr size_t kStaticQBytes = (size_t)16 << 20;
+static __device__ __align__(256) unsigned char g_static_q_scratch[kStaticQBytes];
+
+// The array name is only a host-side handle; kernels need its device address.  Looked up once
+// per device, with that device current.
+static int static_q_scratch_ptr(void **out) {
+    static void *ptrs[64] = {nullptr};
+    int dev = 0;
+    VB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return VLAB200_ERR_UNSUPPORTED;
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        VB_CUDA(cudaGetSymbolAddress(&p, g_static_q_scratch));
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return VLAB200_OK;
+}
+
 }  // namespace vb
 
 extern "C" {
@@ -51,6 +72,25 @@ int32_t vlab200_denoise_attn_loop(const vlab200_kv_store *st, const vlab200_deno
             if (rc) return rc;
         }
     return VLAB200_OK;
+}
+
+int32_t vlab200_denoise_attn_loop_static(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
+                                         void *stream) {
+    if (!st || !a) return VLAB200_ERR_ARG;
+    const size_t need = (size_t)st->n_obs * a->n_q * a->S * st->head_dim * 2;
+    if (st->n_obs <= 0 || a->n_q <= 0 || a->S <= 0 || st->head_dim <= 0) return VLAB200_ERR_ARG;
+    if (need > vb::kStaticQBytes) {
+        vb::set_last_error("vlab200_denoise_attn_loop_static: the query buffer needs %zu bytes, the built-in scratch "
+                           "holds %zu; use vlab200_denoise_attn_loop with a caller-provided q_scratch",
+                           need, vb::kStaticQBytes);
+        return VLAB200_ERR_UNSUPPORTED;
+    }
+    void *q = nullptr;
+    int rc = vb::static_q_scratch_ptr(&q);
+    if (rc) return rc;
+    vlab200_denoise_attn_args b = *a;
+    b.q_scratch = q;
+    return vlab200_denoise_attn_loop(st, &b, stream);
 }
 
 int32_t vlab200_denoise_attn_loop_host(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,

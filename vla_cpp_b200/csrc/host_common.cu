@@ -1,5 +1,6 @@
 #include "host_common.h"
 
+#include <cstdarg>
 #include <cstring>
 #include <mutex>
 
@@ -8,6 +9,13 @@ namespace vb {
 __device__ int g_dev_status;
 
 static thread_local char g_last_error[256] = "";
+
+void set_last_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+}
 
 int cuda_fail(cudaError_t e, const char *what) {
     std::snprintf(g_last_error, sizeof(g_last_error), "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e),

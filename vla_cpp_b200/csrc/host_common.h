@@ -13,6 +13,9 @@ namespace vb {
 // or nullptr when no CUDA device can be used.
 int *device_status_ptr();
 
+// printf-style text for vlab200_last_error() on the calling thread.
+void set_last_error(const char *fmt, ...);
+
 // Records and returns a CUDA failure as VLAB200_ERR_CUDA.
 int cuda_fail(cudaError_t e, const char *what);
 
