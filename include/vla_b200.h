@@ -163,6 +163,66 @@ VLAB200_API int32_t vlab200_denoise_attn_loop_static(const vlab200_kv_store *st,
 VLAB200_API int32_t vlab200_denoise_attn_loop_host(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
                                                    void *x_stage, void *out_host, void *stream);
 
+/* ------------------------------------------------------------- whole denoise loop (engine) */
+
+/* Shape of a flow-matching policy's action expert (fields follow vla_config of include/vla.h:59-96
+ * in the reference: expert_h, n_q_heads, n_kv_heads, head_dim, expert_inter, n_suffix / chunk,
+ * max_action_dim, max_state_dim, num_steps, self_attn_every_n, rms_eps, rope_freq_base, periods). */
+typedef struct {
+    int32_t model;       /* 0 = pi0 (state token in the suffix, tanh-GELU MLP; src/models/pi0.cpp),
+                            1 = SmolVLA (SiLU MLP, alternating self / cross layers; src/models/smolvla.cpp) */
+    int32_t n_layers, H, n_q, n_kv, head_dim, inter, chunk, action_dim, state_dim, steps;
+    int32_t self_every;  /* SmolVLA: layer l self-attends iff l % self_every == 0; <= 1: every layer */
+    float rms_eps, rope_base;
+    double min_period, max_period;
+} vlab200_policy_config;
+
+/* Device pointers to the expert's weights, in the reference's tensor shapes (GGUF names of
+ * src/modules/gemma_expert.h:46-62 / src/models/smolvla.cpp:648-756): matrices bf16 [out][in],
+ * vectors float32.  Per-layer entries are HOST arrays of n_layers device pointers.
+ * SmolVLA cross layers: wk, wv are [n_kv*hd][n_kv*hd].  The engine keeps its own prepared copies
+ * (norm weights folded in, q/k/v concatenated, gate/up interleaved); the caller's buffers may be
+ * released after vlab200_engine_create returns. */
+typedef struct {
+    const void *const *wq, *const *wk, *const *wv, *const *wo, *const *wgate, *const *wup, *const *wdown;
+    const float *const *ln_in, *const *ln_post;
+    const void *w_sp;   const float *b_sp;    /* pi0: [H][state_dim] */
+    const void *w_ain;  const float *b_ain;   /* [H][action_dim] */
+    const void *w_at1;  const float *b_at1;   /* [H][2H] */
+    const void *w_at2;  const float *b_at2;   /* [H][H] */
+    const float *out_norm;                    /* [H] (Gemma norms with their +1 applied) */
+    const void *w_aout; const float *b_aout;  /* [action_dim][H] */
+} vlab200_policy_weights;
+
+typedef struct vlab200_engine vlab200_engine;
+
+/* Allocates (cudaMalloc) the prepared weights, the KV pages for max_obs observations with
+ * prefix_len prefix rows, and the activation workspace.  NULL on failure (vlab200_last_error). */
+VLAB200_API vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg,
+                                                  const vlab200_policy_weights *w, int32_t max_obs,
+                                                  int32_t prefix_len);
+VLAB200_API void vlab200_engine_free(vlab200_engine *e);
+
+/* Prefix K/V of `layer` for observations [obs0, obs0+n_obs): float32 [n_obs][prefix_len][n_kv][hd],
+ * K rotated (what build_gemma_layer / build_vlm_layer hand over, src/models/pi0.cpp:191-194,
+ * src/models/smolvla.cpp:793-794).  Self-attention layers store it as bf16 pages; SmolVLA
+ * cross-attention layers store Wk K / Wv V instead (expert_cross_kv, smolvla.cpp:853-860). */
+VLAB200_API int32_t vlab200_engine_set_prefix(vlab200_engine *e, int32_t layer, int32_t obs0, int32_t n_obs,
+                                              const float *K, const float *V, void *stream);
+
+/* The Euler loop for n_obs observations: x0, x_out float32 [n_obs][chunk][action_dim] (device),
+ * state float32 [n_obs][state_dim] (pi0; normalised), pos_base = RoPE position of suffix token 0
+ * on self-attention layers (< 0: prefix_len), pad_ranges optional [n_obs][2] masked prefix columns.
+ * Replaces the unrolled suffix sub-graph of src/models/pi0.cpp:568-588 / smolvla.cpp:1393-1418. */
+VLAB200_API int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *state, const float *x0,
+                                           float *x_out, int32_t pos_base, const int32_t *pad_ranges,
+                                           void *stream);
+
+/* Same with state, x0 and x_out in (pinned) host memory: the copies are enqueued on `stream`. */
+VLAB200_API int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const float *state_host,
+                                                const float *x0_host, float *x_out_host, int32_t pos_base,
+                                                void *stream);
+
 /* ---------------------------------------------------------------- BitVLA ternary path */
 
 /* Per-token absmax int8 quantisation: scales[m] = 127 / max(max_k |x[m][k]|, 1e-5),

@@ -12,6 +12,7 @@ from .api import (  # noqa: F401
     MASK_PI0,
     DenoiseAttn,
     KvStore,
+    PolicyEngine,
     VlaB200Error,
     act_quant,
     attention,

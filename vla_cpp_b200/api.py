@@ -36,6 +36,8 @@ def lib():
             if name.startswith("vlab200_") and name not in ("vlab200_last_error",):
                 fn.restype = C.c_int32
         L.vlab200_kv_store_bytes.restype = C.c_int64
+        L.vlab200_engine_create.restype = C.c_void_p
+        L.vlab200_engine_free.restype = None
         _LIB = L
     return _LIB
 
@@ -47,6 +49,8 @@ EXPORTS = [
     "vlab200_qkv_rope_append",
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_denoise_attn_loop_static",
+    "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
+    "vlab200_engine_denoise_host",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
@@ -252,4 +256,88 @@ class DenoiseAttn:
         _check(lib().vlab200_denoise_attn_loop_host(C.byref(self.store.c), C.byref(a), _ptr(self._stage),
                                                     C.c_void_p(out_host.data_ptr()), _stream()),
                "vlab200_denoise_attn_loop_host")
+        return out_host
+
+
+class _PolicyConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("model", "n_layers", "H", "n_q", "n_kv", "head_dim", "inter", "chunk",
+                                          "action_dim", "state_dim", "steps", "self_every")] + [
+        ("rms_eps", C.c_float), ("rope_base", C.c_float), ("min_period", C.c_double), ("max_period", C.c_double)]
+
+
+_PER_LAYER = ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "ln_in", "ln_post")
+_GLOBAL = ("w_sp", "b_sp", "w_ain", "b_ain", "w_at1", "b_at1", "w_at2", "b_at2", "out_norm", "w_aout", "b_aout")
+
+
+class _PolicyWeights(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_void_p)) for n in _PER_LAYER] + [(n, C.c_void_p) for n in _GLOBAL]
+
+
+class PolicyEngine:
+    """Batched flow-matching denoise loop of a pi0- or SmolVLA-shaped action expert.
+
+    cfg: dict with the vlab200_policy_config fields.  weights: dict of cuda tensors -- per-layer
+    lists for wq, wk, wv, wo, wgate, wup, wdown (bf16 [out, in]) and ln_in, ln_post (f32), plus
+    w_sp/b_sp (pi0), w_ain/b_ain, w_at1/b_at1, w_at2/b_at2, out_norm, w_aout/b_aout."""
+
+    def __init__(self, cfg, weights, max_obs, prefix_len):
+        import torch
+
+        self.cfg = dict(cfg)
+        c = _PolicyConfig(**{k: cfg[k] for k, _ in _PolicyConfig._fields_})
+        w = _PolicyWeights()
+        keep = []
+        for name in _PER_LAYER:
+            ts = [t.contiguous() for t in weights[name]]
+            want = torch.float32 if name.startswith("ln") else torch.bfloat16
+            assert all(t.is_cuda and t.dtype == want for t in ts), name
+            arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+            keep += [ts, arr]
+            setattr(w, name, C.cast(arr, C.POINTER(C.c_void_p)))
+        for name in _GLOBAL:
+            t = weights.get(name)
+            if t is None:
+                setattr(w, name, None)
+                continue
+            t = t.contiguous()
+            want = torch.bfloat16 if name.startswith("w_") else torch.float32
+            assert t.is_cuda and t.dtype == want, name
+            keep.append(t)
+            setattr(w, name, t.data_ptr())
+        self.max_obs, self.prefix_len = max_obs, prefix_len
+        self.chunk, self.A, self.sd = cfg["chunk"], cfg["action_dim"], cfg["state_dim"]
+        self.h = lib().vlab200_engine_create(C.byref(c), C.byref(w), max_obs, prefix_len)
+        torch.cuda.synchronize()
+        del keep
+        if not self.h:
+            raise VlaB200Error(ERR_CUDA, "vlab200_engine_create")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().vlab200_engine_free(C.c_void_p(self.h))
+            self.h = None
+
+    def set_prefix(self, layer, k_f32, v_f32, obs0=0):
+        """k_f32, v_f32: cuda float32 [n, prefix_len, n_kv, hd] (K rotated)."""
+        assert k_f32.is_contiguous() and v_f32.is_contiguous()
+        _check(lib().vlab200_engine_set_prefix(C.c_void_p(self.h), layer, obs0, k_f32.shape[0], _ptr(k_f32),
+                                               _ptr(v_f32), _stream()), "vlab200_engine_set_prefix")
+
+    def denoise(self, x0, state=None, pos_base=-1, pad_ranges=None):
+        """x0: cuda f32 [n_obs, chunk, A]; state: cuda f32 [n_obs, state_dim] -> x_T like x0."""
+        import torch
+
+        assert x0.is_cuda and x0.dtype == torch.float32 and x0.is_contiguous()
+        out = torch.empty_like(x0)
+        _check(lib().vlab200_engine_denoise(C.c_void_p(self.h), x0.shape[0], _ptr(state), _ptr(x0), _ptr(out),
+                                            pos_base, _ptr(pad_ranges), _stream()), "vlab200_engine_denoise")
+        return out
+
+    def denoise_host(self, x0_host, state_host, out_host, pos_base=-1):
+        """Pinned host float32 buffers in and out; copies are enqueued on the current stream."""
+        _check(lib().vlab200_engine_denoise_host(
+            C.c_void_p(self.h), x0_host.shape[0],
+            C.c_void_p(state_host.data_ptr()) if state_host is not None else None,
+            C.c_void_p(x0_host.data_ptr()), C.c_void_p(out_host.data_ptr()), pos_base, _stream()),
+            "vlab200_engine_denoise_host")
         return out_host

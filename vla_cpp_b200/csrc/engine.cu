@@ -1,0 +1,427 @@
+// The flow-matching denoise loop of a pi0- or SmolVLA-shaped policy, batched over observations:
+// host-side C++ driver + the small kernels around the GEMM / attention kernels.
+//
+// Per Euler step (src/models/pi0.cpp:570-588, src/models/smolvla.cpp:1393-1418):
+//   suffix embedding   a = W_ain x + b;  u = W_at2 silu(W_at1 [a ; tau_k] + b) + b   (pi0: + state token)
+//   L expert layers    fused RMSNorm+QKV+RoPE(+KV append) -> attention -> Wo + residual ->
+//                      fused RMSNorm + gate/up + activation -> Wdown + residual
+//   head               v = W_aout (rms(h) * w_out) + b on the action rows;  x += dt * v   (x stays f32)
+// W_at1 [a ; tau_k] is split: the tau_k half is a per-step constant vector computed once at
+// engine creation, so the GEMM runs over K = H only.  RMSNorm weights are folded into the
+// projections that consume the normalised activations (load-time step).
+#include <cuda_bf16.h>
+
+#include <cmath>
+#include <new>
+#include <vector>
+
+#include "gemm.h"
+#include "host_common.h"
+
+namespace vb {
+
+// ------------------------------------------------------------------ small kernels --
+
+// W'[r][k] = bf16(W[r][k] * ln[k]) written at out row (r * row_mul + row_add): concatenation and
+// gate/up interleaving are both expressed through the row map.
+__global__ void fold_rows_kernel(const __nv_bfloat16 *__restrict__ w, const float *__restrict__ ln,
+                                 __nv_bfloat16 *__restrict__ out, int rows, int K, int row_mul, int row_add) {
+    const size_t total = (size_t)rows * K;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / K, k = i % K;
+        const float v = __bfloat162float(w[i]) * (ln ? ln[k] : 1.0f);
+        out[(r * row_mul + row_add) * K + k] = __float2bfloat16(v);
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16(in[i]);
+}
+
+// tvec[s][o] = b_at1[o] + sum_k W_at1[o][H + k] * tau[s][k]   (one warp per output)
+__global__ void time_vector_kernel(const __nv_bfloat16 *__restrict__ w_at1, const float *__restrict__ b_at1,
+                                   const float *__restrict__ tau, float *__restrict__ tvec, int H, int T) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T * H) return;
+    const int s = warp / H, o = warp % H;
+    const __nv_bfloat16 *wr = w_at1 + (size_t)o * 2 * H + H;
+    float acc = 0.0f;
+    for (int k = lane; k < H; k += 32) acc = fmaf(__bfloat162float(wr[k]), tau[s * H + k], acc);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) tvec[warp] = acc + (b_at1 ? b_at1[o] : 0.0f);
+}
+
+// a[obs*chunk + t][o] = bf16(b_ain[o] + sum_k W_ain[o][k] x[obs][t][k]);  pi0 also writes the state
+// token (row 0 of each observation) of h / hb.  One CTA per observation row group.
+__global__ void __launch_bounds__(256) suffix_in_kernel(const float *__restrict__ x, const float *__restrict__ state,
+                                                        const __nv_bfloat16 *__restrict__ w_ain,
+                                                        const float *__restrict__ b_ain,
+                                                        const __nv_bfloat16 *__restrict__ w_sp,
+                                                        const float *__restrict__ b_sp, __nv_bfloat16 *__restrict__ a,
+                                                        float *__restrict__ h, __nv_bfloat16 *__restrict__ hb, int H,
+                                                        int A, int sd, int chunk, int S) {
+    extern __shared__ float sx[];  // [chunk][A] then [sd]
+    const int obs = blockIdx.x;
+    for (int i = threadIdx.x; i < chunk * A; i += blockDim.x) sx[i] = x[(size_t)obs * chunk * A + i];
+    if (w_sp)
+        for (int i = threadIdx.x; i < sd; i += blockDim.x) sx[chunk * A + i] = state[(size_t)obs * sd + i];
+    __syncthreads();
+    for (int o = threadIdx.x; o < H; o += blockDim.x) {
+        const __nv_bfloat16 *wr = w_ain + (size_t)o * A;
+        const float b = b_ain ? b_ain[o] : 0.0f;
+        for (int t = 0; t < chunk; ++t) {
+            float acc = 0.0f;
+            for (int k = 0; k < A; ++k) acc = fmaf(__bfloat162float(wr[k]), sx[t * A + k], acc);
+            a[((size_t)obs * chunk + t) * H + o] = __float2bfloat16(acc + b);
+        }
+        if (w_sp) {
+            const __nv_bfloat16 *ws = w_sp + (size_t)o * sd;
+            float acc = 0.0f;
+            for (int k = 0; k < sd; ++k) acc = fmaf(__bfloat162float(ws[k]), sx[chunk * A + k], acc);
+            acc += b_sp ? b_sp[o] : 0.0f;
+            h[(size_t)obs * S * H + o] = acc;
+            hb[(size_t)obs * S * H + o] = __float2bfloat16(acc);
+        }
+    }
+}
+
+// v = W_aout (rms(h_row) * w_out) + b_aout;  x += dt * v.  One warp per action row.
+__global__ void __launch_bounds__(256) head_euler_kernel(const float *__restrict__ h, const float *__restrict__ w_out,
+                                                         const __nv_bfloat16 *__restrict__ w_aout,
+                                                         const float *__restrict__ b_aout, float *__restrict__ x,
+                                                         int n_rows, int H, int A, int chunk, int S, float eps,
+                                                         float dt) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows) return;
+    const int obs = warp / chunk, t = warp % chunk;
+    const float *hr = h + ((size_t)obs * S + (S - chunk) + t) * H;
+    float ss = 0.0f;
+    for (int k = lane; k < H; k += 32) ss = fmaf(hr[k], hr[k], ss);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int o = 0; o < A; ++o) {
+        const __nv_bfloat16 *wr = w_aout + (size_t)o * H;
+        float acc = 0.0f;
+        for (int k = lane; k < H; k += 32) acc = fmaf(__bfloat162float(wr[k]), hr[k] * r * w_out[k], acc);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+            const size_t xi = ((size_t)obs * chunk + t) * A + o;
+            x[xi] += dt * (acc + (b_aout ? b_aout[o] : 0.0f));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------ engine --
+
+struct DevBuf {
+    void *p = nullptr;
+    DevBuf() = default;
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    DevBuf(DevBuf &&o) noexcept : p(o.p) { o.p = nullptr; }
+    int alloc(size_t bytes) {
+        cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+        return e == cudaSuccess ? VLAB200_OK : cuda_fail(e, "cudaMalloc");
+    }
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    template <typename T>
+    T *as() const {
+        return static_cast<T *>(p);
+    }
+};
+
+}  // namespace vb
+
+struct vlab200_engine {
+    vlab200_policy_config c;
+    int max_obs, P, S, cap, qf, kvf;
+    std::vector<int> is_self;
+    // prepared weights
+    std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
+    vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
+    // workspace
+    vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage;
+    int rope_pos0 = -1;
+};
+
+namespace vb {
+
+static int copy_dev(DevBuf &dst, const void *src, size_t bytes) {
+    int rc = dst.alloc(bytes);
+    if (rc) return rc;
+    if (src) VB_CUDA(cudaMemcpy(dst.p, src, bytes, cudaMemcpyDeviceToDevice));
+    return VLAB200_OK;
+}
+
+static int fold_rows(const void *w, const float *ln, void *out, int rows, int K, int row_mul, int row_add) {
+    fold_rows_kernel<<<148 * 4, 256>>>(static_cast<const __nv_bfloat16 *>(w), ln, static_cast<__nv_bfloat16 *>(out),
+                                       rows, K, row_mul, row_add);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
+    const vlab200_policy_config &c = e->c;
+    const int L = c.n_layers, H = c.H, hd = c.head_dim, I = c.inter;
+    const int qf = e->qf, kvf = e->kvf;
+    e->wqkv.resize(L); e->wo.resize(L); e->wgu.resize(L); e->wdown.resize(L); e->wkx.resize(L); e->wvx.resize(L);
+    int rc;
+    for (int l = 0; l < L; ++l) {
+        const bool self = e->is_self[l];
+        const int rows = self ? qf + 2 * kvf : qf;
+        if ((rc = e->wqkv[l].alloc((size_t)rows * H * 2))) return rc;
+        auto *dst = e->wqkv[l].as<__nv_bfloat16>();
+        if ((rc = fold_rows(w->wq[l], w->ln_in[l], dst, qf, H, 1, 0))) return rc;
+        if (self) {
+            if ((rc = fold_rows(w->wk[l], w->ln_in[l], dst + (size_t)qf * H, kvf, H, 1, 0))) return rc;
+            if ((rc = fold_rows(w->wv[l], w->ln_in[l], dst + (size_t)(qf + kvf) * H, kvf, H, 1, 0))) return rc;
+        } else {
+            if ((rc = copy_dev(e->wkx[l], w->wk[l], (size_t)kvf * kvf * 2))) return rc;
+            if ((rc = copy_dev(e->wvx[l], w->wv[l], (size_t)kvf * kvf * 2))) return rc;
+        }
+        if ((rc = copy_dev(e->wo[l], w->wo[l], (size_t)H * qf * 2))) return rc;
+        if ((rc = e->wgu[l].alloc((size_t)2 * I * H * 2))) return rc;
+        if ((rc = fold_rows(w->wgate[l], w->ln_post[l], e->wgu[l].p, I, H, 2, 0))) return rc;
+        if ((rc = fold_rows(w->wup[l], w->ln_post[l], e->wgu[l].p, I, H, 2, 1))) return rc;
+        if ((rc = copy_dev(e->wdown[l], w->wdown[l], (size_t)H * I * 2))) return rc;
+    }
+    const int A = c.action_dim, sd = c.state_dim, T = c.steps;
+    if ((rc = copy_dev(e->w_ain, w->w_ain, (size_t)H * A * 2))) return rc;
+    if ((rc = copy_dev(e->b_ain, w->b_ain, (size_t)H * 4))) return rc;
+    if (c.model == 0) {
+        if ((rc = copy_dev(e->w_sp, w->w_sp, (size_t)H * sd * 2))) return rc;
+        if ((rc = copy_dev(e->b_sp, w->b_sp, (size_t)H * 4))) return rc;
+    }
+    if ((rc = e->w_at1l.alloc((size_t)H * H * 2))) return rc;
+    VB_CUDA(cudaMemcpy2D(e->w_at1l.p, (size_t)H * 2, w->w_at1, (size_t)2 * H * 2, (size_t)H * 2, H,
+                         cudaMemcpyDeviceToDevice));
+    // time embeddings tau_k on the host in double, as the reference computes them
+    // (src/layers/embed.h:61-73; pi0 forms the timestep in float, SmolVLA in double)
+    std::vector<float> tau((size_t)T * H);
+    const float dtf = -1.0f / (float)T;
+    for (int s = 0; s < T; ++s) {
+        const double t = c.model == 0 ? (double)(1.0f + (float)s * dtf) : 1.0 + (double)s * (double)dtf;
+        const int half = H / 2;
+        for (int i = 0; i < half; ++i) {
+            const double frac = half == 1 ? 0.0 : (double)i / (double)(half - 1);
+            const double period = c.min_period * std::pow(c.max_period / c.min_period, frac);
+            const double ang = (2.0 * M_PI / period) * t;
+            tau[(size_t)s * H + i] = (float)std::sin(ang);
+            tau[(size_t)s * H + half + i] = (float)std::cos(ang);
+        }
+    }
+    DevBuf tau_d;
+    if ((rc = tau_d.alloc(tau.size() * 4))) return rc;
+    VB_CUDA(cudaMemcpy(tau_d.p, tau.data(), tau.size() * 4, cudaMemcpyHostToDevice));
+    if ((rc = e->tvec.alloc((size_t)T * H * 4))) return rc;
+    time_vector_kernel<<<(T * H * 32 + 255) / 256, 256>>>(static_cast<const __nv_bfloat16 *>(w->w_at1), w->b_at1,
+                                                         tau_d.as<float>(), e->tvec.as<float>(), H, T);
+    VB_CUDA(cudaGetLastError());
+    if ((rc = copy_dev(e->w_at2, w->w_at2, (size_t)H * H * 2))) return rc;
+    if ((rc = copy_dev(e->b_at2, w->b_at2, (size_t)H * 4))) return rc;
+    if ((rc = copy_dev(e->out_norm, w->out_norm, (size_t)H * 4))) return rc;
+    if ((rc = copy_dev(e->w_aout, w->w_aout, (size_t)A * H * 2))) return rc;
+    if ((rc = copy_dev(e->b_aout, w->b_aout, (size_t)A * 4))) return rc;
+    // workspace
+    const size_t B = e->max_obs, M = B * e->S, Mc = B * c.chunk;
+    const size_t page_bytes = (size_t)L * B * c.n_kv * e->cap * hd * 2;
+    if ((rc = e->k_pages.alloc(page_bytes)) || (rc = e->v_pages.alloc(page_bytes))) return rc;
+    VB_CUDA(cudaMemset(e->k_pages.p, 0, page_bytes));
+    VB_CUDA(cudaMemset(e->v_pages.p, 0, page_bytes));
+    if ((rc = e->h.alloc(M * H * 4)) || (rc = e->hb.alloc(M * H * 2)) || (rc = e->q.alloc(M * qf * 2)) ||
+        (rc = e->att.alloc(M * qf * 2)) || (rc = e->g.alloc(M * I * 2)) || (rc = e->a.alloc(Mc * H * 2)) ||
+        (rc = e->m1.alloc(Mc * H * 2)) || (rc = e->x.alloc(Mc * A * 4)) ||
+        (rc = e->rope_self.alloc((size_t)2 * e->S * (hd / 2) * 4)) ||
+        (rc = e->rope_cross.alloc((size_t)2 * e->S * (hd / 2) * 4)) ||
+        (rc = e->tmp_bf.alloc((size_t)2 * B * e->P * kvf * 2)) || (rc = e->x_stage.alloc(Mc * A * 4)) ||
+        (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)))
+        return rc;
+    VB_CUDA(cudaMemset(e->h.p, 0, M * H * 4));
+    VB_CUDA(cudaMemset(e->hb.p, 0, M * H * 2));
+    VB_CUDA(cudaDeviceSynchronize());
+    return VLAB200_OK;
+}
+
+static vlab200_kv_store engine_store(const vlab200_engine *e, int n_obs_view) {
+    vlab200_kv_store st;
+    st.k_pages = e->k_pages.p;
+    st.v_pages = e->v_pages.p;
+    st.n_layers = e->c.n_layers;
+    st.n_obs = n_obs_view;
+    st.n_kv = e->c.n_kv;
+    st.head_dim = e->c.head_dim;
+    st.cap = e->cap;
+    st.prefix_len = e->P;
+    return st;
+}
+
+}  // namespace vb
+
+extern "C" {
+
+vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vlab200_policy_weights *w,
+                                      int32_t max_obs, int32_t prefix_len) {
+    if (!cfg || !w || max_obs <= 0 || prefix_len <= 0) return nullptr;
+    const vlab200_policy_config &c = *cfg;
+    if (c.n_layers <= 0 || c.H <= 0 || c.n_q <= 0 || c.n_kv <= 0 || c.n_q % c.n_kv || c.inter <= 0 || c.chunk <= 0 ||
+        c.action_dim <= 0 || c.action_dim > 64 || c.steps <= 0 || (c.model != 0 && c.model != 1)) {
+        vb::set_last_error("vlab200_engine_create: bad configuration");
+        return nullptr;
+    }
+    if (c.H % 64 && c.H % 8) return nullptr;
+    vlab200_engine *e = new (std::nothrow) vlab200_engine();
+    if (!e) return nullptr;
+    e->c = c;
+    e->max_obs = max_obs;
+    e->P = prefix_len;
+    e->S = c.chunk + (c.model == 0 ? 1 : 0);
+    e->cap = e->P + e->S;
+    e->qf = c.n_q * c.head_dim;
+    e->kvf = c.n_kv * c.head_dim;
+    e->is_self.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; ++l)
+        e->is_self[l] = (c.model == 0) || (c.self_every <= 1) || (l % c.self_every == 0);
+    if (vb::engine_build(e, w) != VLAB200_OK) {
+        delete e;
+        return nullptr;
+    }
+    return e;
+}
+
+void vlab200_engine_free(vlab200_engine *e) { delete e; }
+
+int32_t vlab200_engine_set_prefix(vlab200_engine *e, int32_t layer, int32_t obs0, int32_t n_obs, const float *K,
+                                  const float *V, void *stream) {
+    if (!e || !K || !V || layer < 0 || layer >= e->c.n_layers || obs0 < 0 || n_obs <= 0 || obs0 + n_obs > e->max_obs)
+        return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    vlab200_kv_store st = vb::engine_store(e, e->max_obs);
+    if (e->is_self[layer]) return vlab200_kv_store_write(&st, layer, obs0, n_obs, K, V, cs);
+    // SmolVLA cross-attention layer: K' = Wk K_flat, V' = Wv V_flat once per observation
+    // (src/models/smolvla.cpp:853-860), written head-major into the pages of this layer
+    const size_t n = (size_t)n_obs * e->P * e->kvf;
+    __nv_bfloat16 *kb = e->tmp_bf.as<__nv_bfloat16>(), *vbuf = kb + (size_t)e->max_obs * e->P * e->kvf;
+    vb::f32_to_bf16_kernel<<<148 * 4, 256, 0, cs>>>(K, kb, n);
+    vb::f32_to_bf16_kernel<<<148 * 4, 256, 0, cs>>>(V, vbuf, n);
+    VB_CUDA(cudaGetLastError());
+    const size_t page_off = ((size_t)layer * e->max_obs + obs0) * e->c.n_kv * e->cap * e->c.head_dim;
+    for (int which = 0; which < 2; ++which) {
+        vb::GemmParams p{};
+        p.M = n_obs * e->P; p.N = e->kvf; p.K = e->kvf;
+        p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 0; p.eps = 0.f;
+        p.out_bf = (which ? e->v_pages.as<__nv_bfloat16>() : e->k_pages.as<__nv_bfloat16>()) + page_off;
+        p.ld_out = e->c.head_dim;
+        p.rows_in = e->P; p.rows_out = 0; p.row_off = 0;
+        p.scatter_hd = e->c.head_dim; p.scatter_cap = e->cap;
+        int rc = vb::dense_gemm(which ? vbuf : kb, e->kvf, which ? e->wvx[layer].p : e->wkx[layer].p, p, cs);
+        if (rc) return rc;
+    }
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *state, const float *x0, float *x_out,
+                               int32_t pos_base, const int32_t *pad_ranges, void *stream) {
+    if (!e || !x0 || !x_out || n_obs <= 0 || n_obs > e->max_obs) return VLAB200_ERR_ARG;
+    if (e->c.model == 0 && !state) return VLAB200_ERR_ARG;
+    const vlab200_policy_config &c = e->c;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const int H = c.H, S = e->S, chunk = c.chunk, A = c.action_dim, hd = c.head_dim, I = c.inter;
+    const int M = n_obs * S, Mc = n_obs * chunk;
+    int rc;
+    if (pos_base < 0) pos_base = e->P;
+    float *rs = e->rope_self.as<float>(), *rx = e->rope_cross.as<float>();
+    const int half = hd / 2;
+    if ((rc = vlab200_rope_table(rs, rs + (size_t)S * half, pos_base, S, hd, c.rope_base, cs))) return rc;
+    if ((rc = vlab200_rope_table(rx, rx + (size_t)S * half, 0, S, hd, c.rope_base, cs))) return rc;
+    VB_CUDA(cudaMemcpyAsync(e->x.p, x0, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
+    // the KV pages are laid out for max_obs observations; the kernels index pages by observation
+    // within a layer, so the view must keep the layer stride of the full store
+    vlab200_kv_store st = vb::engine_store(e, e->max_obs);
+    const float dt = -1.0f / (float)c.steps;
+    for (int step = 0; step < c.steps; ++step) {
+        vb::suffix_in_kernel<<<n_obs, 256, (size_t)(chunk * A + c.state_dim) * 4, cs>>>(
+            e->x.as<float>(), state, e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(),
+            c.model == 0 ? e->w_sp.as<__nv_bfloat16>() : nullptr, e->b_sp.as<float>(), e->a.as<__nv_bfloat16>(),
+            e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, A, c.state_dim, chunk, S);
+        VB_CUDA(cudaGetLastError());
+        {
+            vb::GemmParams p{};
+            p.M = Mc; p.N = H; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_SILU;
+            p.out_bf = e->m1.as<__nv_bfloat16>(); p.bias = e->tvec.as<float>() + (size_t)step * H; p.ld_out = H;
+            if ((rc = vb::dense_gemm(e->a.p, H, e->w_at1l.p, p, cs))) return rc;
+        }
+        {
+            vb::GemmParams p{};
+            p.M = Mc; p.N = H; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE;
+            p.out_bf = e->hb.as<__nv_bfloat16>(); p.out_f32 = e->h.as<float>(); p.bias = e->b_at2.as<float>();
+            p.ld_out = H; p.rows_in = chunk; p.rows_out = S; p.row_off = S - chunk;
+            if ((rc = vb::dense_gemm(e->m1.p, H, e->w_at2.p, p, cs))) return rc;
+        }
+        for (int l = 0; l < c.n_layers; ++l) {
+            const bool self = e->is_self[l];
+            // pages are laid out for max_obs observations per layer; the kernels walk st.n_obs
+            // observations from the store base, so hand them a one-layer view of the live ones
+            vlab200_kv_store live = st;
+            live.n_obs = n_obs;
+            const size_t layer_off = (size_t)l * e->max_obs * c.n_kv * e->cap * hd;
+            live.k_pages = e->k_pages.as<__nv_bfloat16>() + layer_off;
+            live.v_pages = e->v_pages.as<__nv_bfloat16>() + layer_off;
+            live.n_layers = 1;
+            const float *rope = self ? rs : rx;
+            if ((rc = vlab200_qkv_rope_append(&live, 0, e->hb.p, 0, nullptr, e->wqkv[l].p, rope, rope + (size_t)S * half,
+                                              c.rms_eps, S, H, c.n_q, self ? 1 : 0, e->q.p, cs)))
+                return rc;
+            const int kv_len = self ? e->P + S : e->P;
+            const int mode = self ? (c.model == 0 ? 1 : 2) : 0;
+            if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs))) return rc;
+            {
+                vb::GemmParams p{};
+                p.M = M; p.N = H; p.K = e->qf; p.epi = vb::EPI_RESIDUAL;
+                p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
+                if ((rc = vb::dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs))) return rc;
+            }
+            {
+                vb::GemmParams p{};
+                p.M = M; p.N = 2 * I; p.K = H; p.epi = vb::EPI_GATED; p.use_rms = 1; p.eps = c.rms_eps;
+                p.act = c.model == 0 ? vb::ACT_GELU_TANH : vb::ACT_SILU;
+                p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = I;
+                if ((rc = vb::dense_gemm(e->hb.p, H, e->wgu[l].p, p, cs))) return rc;
+            }
+            {
+                vb::GemmParams p{};
+                p.M = M; p.N = H; p.K = I; p.epi = vb::EPI_RESIDUAL;
+                p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
+                if ((rc = vb::dense_gemm(e->g.p, I, e->wdown[l].p, p, cs))) return rc;
+            }
+        }
+        vb::head_euler_kernel<<<(Mc * 32 + 255) / 256, 256, 0, cs>>>(e->h.as<float>(), e->out_norm.as<float>(),
+                                                                    e->w_aout.as<__nv_bfloat16>(), e->b_aout.as<float>(),
+                                                                    e->x.as<float>(), Mc, H, A, chunk, S, c.rms_eps, dt);
+        VB_CUDA(cudaGetLastError());
+    }
+    VB_CUDA(cudaMemcpyAsync(x_out, e->x.p, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const float *state_host, const float *x0_host,
+                                    float *x_out_host, int32_t pos_base, void *stream) {
+    if (!e || !x0_host || !x_out_host || n_obs <= 0 || n_obs > e->max_obs) return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const size_t xb = (size_t)n_obs * e->c.chunk * e->c.action_dim * 4, sb = (size_t)n_obs * e->c.state_dim * 4;
+    float *x_dev = e->x_stage.as<float>();
+    float *s_dev = e->state_stage.as<float>();
+    VB_CUDA(cudaMemcpyAsync(x_dev, x0_host, xb, cudaMemcpyHostToDevice, cs));
+    if (state_host) VB_CUDA(cudaMemcpyAsync(s_dev, state_host, sb, cudaMemcpyHostToDevice, cs));
+    int rc = vlab200_engine_denoise(e, n_obs, state_host ? s_dev : nullptr, x_dev, x_dev, pos_base, nullptr, cs);
+    if (rc) return rc;
+    VB_CUDA(cudaMemcpyAsync(x_out_host, x_dev, xb, cudaMemcpyDeviceToHost, cs));
+    return VLAB200_OK;
+}
+
+}  // extern "C"

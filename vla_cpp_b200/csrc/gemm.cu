@@ -1,0 +1,313 @@
+// Persistent tcgen05 GEMM with fused prologue statistics and epilogues for the rest of the
+// expert layer (O-projection + residual, gated MLP, suffix-embedding MLPs):
+//
+//   C[m][n] = sum_k A[m][k] * W[n][k]      A: bf16 [M][K], W: bf16 [N][K] (PyTorch [out][in])
+//
+// Structure (same as the QKV kernel): one CTA per SM walks 128 x 256 output tiles; warp 0 loads
+// both operands by TMA (SWIZZLE_128B) into a 4-stage ring, warp 1 issues tcgen05.mma kind::f16
+// into a double-buffered f32 accumulator in TMEM, warps 6-9 optionally accumulate sum(a^2) per
+// row from the A tiles in shared memory (RMSNorm whose weight was folded into W), and eight
+// epilogue warps (two per TMEM lane quarter) drain the accumulator.
+//
+// Epilogues
+//   RESIDUAL  h[m][n] += C                     (f32 master copy) and hb = bf16(h)   -- Wo, Wdown
+//   GATED     g[m][i] = act(r C[m][2i]) * (r C[m][2i+1]),  r = rsqrt(mean a^2 + eps) -- Wgate/Wup
+//             (gate and up rows interleaved in W; act = SiLU or tanh-GELU)
+//   BIAS_ACT  y[m'][n] = act(C + bias[n]); bf16 and/or f32 output; rows may be re-mapped
+//             (m -> (m / rows_in) * rows_out + row_off + m % rows_in) so that the action-token
+//             rows land behind the state token of each observation                   -- W_at1, W_at2
+//
+// Reference: src/models/pi0.cpp:224-248, src/models/smolvla.cpp:843-848,1397-1403 (one mul_mat /
+// add / mul / unary ggml node each; src/cuda/vla_cuda_bf16.cu:624-678 for the cuBLAS GEMM node).
+#include <cuda_bf16.h>
+
+#include "gemm.h"
+#include "host_common.h"
+#include "tc5.cuh"
+
+namespace vb {
+
+constexpr int G_BM = 128, G_BN = 256, G_BK = 64, G_STAGES = 4, G_THREADS = 448;
+constexpr int G_A_BYTES = G_BM * 128, G_B_BYTES = G_BN * 128, G_STAGE_BYTES = G_A_BYTES + G_B_BYTES;
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+    if (act == ACT_SILU) return x / (1.0f + __expf(-x));
+    if (act == ACT_GELU_TANH) {
+        // constants of src/cuda/vla_cuda_bf16.cu:470-474
+        const float k0 = 0.79788456080286535587989211986876f, k1 = 0.044715f;
+        return 0.5f * x * (1.0f + tanhf(k0 * x * (1.0f + k1 * x * x)));
+    }
+    return x;
+}
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                  const GemmParams p, int tiles_m, int tiles_n) {
+    extern __shared__ uint8_t g_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(g_smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *aux = smem + G_STAGES * G_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aux);
+    uint64_t *full = bars, *empty = bars + 4;
+    uint64_t *accum_full = bars + 8, *accum_empty = bars + 10, *stats_full = bars + 12, *stats_empty = bars + 14;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *stats = reinterpret_cast<float *>(aux + 256);  // [2][128]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ksteps = (p.K + G_BK - 1) / G_BK;
+    const int n_tiles = tiles_m * tiles_n;
+    const WaitCtx wc{abort_flag, p.status};
+    const uint32_t empty_count = p.use_rms ? 5u : 1u;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < G_STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], empty_count);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&accum_full[i], 1);
+            mbar_init(&accum_empty[i], 256);
+            mbar_init(&stats_full[i], 128);
+            mbar_init(&stats_empty[i], 256);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a_map);
+            tma_prefetch_desc(&w_map);
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * G_BM, n0 = (tile % tiles_n) * G_BN;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[st], G_STAGE_BYTES);
+                    uint8_t *sa = smem + st * G_STAGE_BYTES;
+                    tma_load_2d(sa, &a_map, &full[st], kt * G_BK, m0);
+                    tma_load_2d(sa + G_A_BYTES, &w_map, &full[st], kt * G_BK, n0);
+                    if (++st == G_STAGES) { st = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, G_BM, G_BN);
+            uint32_t st = 0, ph = 0, j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+                const uint32_t buf = j & 1u;
+                ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * G_BN;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + st * G_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + G_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < G_BK / 16; ++k)
+                        mma_f16(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                                smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
+                    tc_commit(&empty[st]);
+                    if (++st == G_STAGES) { st = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(&accum_full[buf]);
+            }
+        }
+    } else if (warp >= 6 && warp < 10) {
+        if (p.use_rms) {
+            const int row = (warp - 6) * 32 + lane;
+            const uint32_t row_base = (row >> 3) * 1024 + (row & 7) * 128;
+            const uint32_t sw = row & 7;
+            uint32_t st = 0, ph = 0, j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+                const uint32_t buf = j & 1u;
+                float s0 = 0.0f, s1 = 0.0f;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    const uint8_t *at = smem + st * G_STAGE_BYTES + row_base;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
+                        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h2[e]);
+                            s0 = fmaf(f.x, f.x, s0);
+                            s1 = fmaf(f.y, f.y, s1);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[st]);
+                    if (++st == G_STAGES) { st = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                ok = mbar_wait(&stats_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                stats[buf * 128 + row] = s0 + s1;
+                mbar_arrive(&stats_full[buf]);
+            }
+        }
+    } else {
+        // ---- epilogue warps 2..5 (group 0: columns [0,128)) and 10..13 (group 1: [128,256)) ----
+        const int qtr = warp & 3;
+        const int grp = warp >= 10 ? 1 : 0;
+        const int row = qtr * 32 + lane;
+        uint32_t j = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            const uint32_t buf = j & 1u;
+            const int m0 = (tile / tiles_n) * G_BM, n0 = (tile % tiles_n) * G_BN;
+            const int m = m0 + row;
+            const bool row_ok = m < p.M;
+            ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (ok && p.use_rms) ok = mbar_wait(&stats_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
+            const float rms = p.use_rms ? rsqrtf(stats[buf * 128 + row] / (float)p.K + p.eps) : 1.0f;
+            const uint32_t lane_addr = tmem_base + buf * G_BN + ((uint32_t)(qtr * 32) << 16);
+            size_t mo = (size_t)m;
+            if (p.rows_in > 0 && p.scatter_hd == 0) mo = (size_t)(m / p.rows_in) * p.rows_out + p.row_off + (m % p.rows_in);
+            for (int c = grp * 128; c < grp * 128 + 128; c += 32) {
+                const int n = n0 + c;
+                if (n >= p.N) break;  // N % 8 == 0: a chunk may be cut after a multiple of 8 columns
+                uint32_t v[32];
+                tmem_ld32(lane_addr + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                if (p.epi == EPI_RESIDUAL) {
+                    float4 *hp = reinterpret_cast<float4 *>(p.h + mo * p.ld_out + n);
+                    uint4 *bp = reinterpret_cast<uint4 *>(p.out_bf + mo * p.ld_out + n);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        if (n + 8 * q4 >= p.N) break;
+                        float4 a = hp[2 * q4], b = hp[2 * q4 + 1];
+                        a.x += __uint_as_float(v[8 * q4]); a.y += __uint_as_float(v[8 * q4 + 1]);
+                        a.z += __uint_as_float(v[8 * q4 + 2]); a.w += __uint_as_float(v[8 * q4 + 3]);
+                        b.x += __uint_as_float(v[8 * q4 + 4]); b.y += __uint_as_float(v[8 * q4 + 5]);
+                        b.z += __uint_as_float(v[8 * q4 + 6]); b.w += __uint_as_float(v[8 * q4 + 7]);
+                        hp[2 * q4] = a;
+                        hp[2 * q4 + 1] = b;
+                        const __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x, b.y), h3 = __floats2bfloat162_rn(b.z, b.w);
+                        bp[q4] = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                                            *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+                    }
+                } else if (p.epi == EPI_GATED) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float g0 = act_apply(__uint_as_float(v[4 * e]) * rms, p.act) * (__uint_as_float(v[4 * e + 1]) * rms);
+                        const float g1 = act_apply(__uint_as_float(v[4 * e + 2]) * rms, p.act) * (__uint_as_float(v[4 * e + 3]) * rms);
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
+                        w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                    }
+                    uint4 *bp = reinterpret_cast<uint4 *>(p.out_bf + mo * p.ld_out + (n >> 1));
+                    bp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (n + 16 < p.N) bp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                } else {
+                    float f[32];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        f[e] = act_apply(__uint_as_float(v[e]) * rms + ((p.bias && n + e < p.N) ? __ldg(p.bias + n + e) : 0.0f),
+                                         p.act);
+                    if (p.out_f32) {
+                        float4 *fp = reinterpret_cast<float4 *>(p.out_f32 + mo * p.ld_out + n);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (n + 4 * e < p.N) fp[e] = make_float4(f[4 * e], f[4 * e + 1], f[4 * e + 2], f[4 * e + 3]);
+                    }
+                    if (p.out_bf) {
+                        size_t off = mo * p.ld_out + n;
+                        if (p.scatter_hd > 0)  // head-major pages: [obs][head][cap][hd]
+                            off = ((size_t)(m / p.rows_in) * (p.N / p.scatter_hd) + (size_t)(n / p.scatter_hd)) *
+                                      ((size_t)p.scatter_cap * p.scatter_hd) +
+                                  (size_t)(m % p.rows_in) * p.scatter_hd + (n % p.scatter_hd);
+                        uint4 *bp = reinterpret_cast<uint4 *>(p.out_bf + off);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            if (n + 8 * q4 >= p.N) break;
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(f[8 * q4 + 2 * e], f[8 * q4 + 2 * e + 1]);
+                                w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                            }
+                            bp[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&accum_empty[buf]);
+            if (p.use_rms) mbar_arrive(&stats_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
+int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
+    if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
+    if (p.N % 8 || (p.epi == EPI_GATED && p.N % 16) || p.K % 8 || lda % 8 || p.ld_out % 8) return VLAB200_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VLAB200_ERR_ARG;
+    p.status = device_status_ptr();
+    if (!p.status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
+    CUtensorMap amap, wmap;
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.M};
+        const uint64_t strides[1] = {(uint64_t)lda * 2};
+        const uint32_t box[2] = {G_BK, G_BM};
+        int rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
+        const uint64_t strides[1] = {(uint64_t)p.K * 2};
+        const uint32_t box[2] = {G_BK, G_BN};
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    const int smem = G_STAGES * G_STAGE_BYTES + 256 + 1024 + 1024;
+    static bool done = false;
+    static int n_sm = 0;
+    if (!done) {
+        VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        int dev = 0;
+        VB_CUDA(cudaGetDevice(&dev));
+        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+        done = true;
+    }
+    const int tiles_m = (p.M + G_BM - 1) / G_BM, tiles_n = (p.N + G_BN - 1) / G_BN;
+    const int nt = tiles_m * tiles_n;
+    dense_gemm_kernel<<<nt < n_sm ? nt : n_sm, G_THREADS, smem, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+}  // namespace vb

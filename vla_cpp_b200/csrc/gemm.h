@@ -1,0 +1,28 @@
+// Interface of the persistent tcgen05 GEMM (gemm.cu) used by the denoise engine.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace vb {
+
+enum { EPI_RESIDUAL = 0, EPI_GATED = 1, EPI_BIAS_ACT = 2 };
+enum { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
+
+struct GemmParams {
+    int M, N, K;
+    int epi, act, use_rms;
+    float eps;
+    float *h;               // RESIDUAL: f32 [M][N] read-modify-write
+    __nv_bfloat16 *out_bf;  // RESIDUAL: bf16 mirror [M][N]; GATED: [M][N/2]; BIAS_ACT: bf16 output (optional)
+    float *out_f32;         // BIAS_ACT: f32 output (optional)
+    const float *bias;      // BIAS_ACT: [N] (optional)
+    int ld_out;             // row stride (elements) of out_bf / out_f32 / h
+    int rows_in, rows_out, row_off;  // BIAS_ACT row re-mapping (rows_in == 0: identity)
+    int scatter_hd, scatter_cap;     // BIAS_ACT into head-major pages: [m / rows_in][n / hd][cap][hd] (0: off)
+    int *status;
+};
+
+// A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
+int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream);
+
+}  // namespace vb
