@@ -103,6 +103,79 @@ def oracle_chunk(orc, rng, n_chunks):
     return time.perf_counter() - t0
 
 
+PI0 = dict(model=0, n_layers=18, H=1024, n_q=8, n_kv=1, head_dim=256, inter=4096, chunk=50, action_dim=32,
+           state_dim=32, steps=10, self_every=1, rms_eps=1e-6, rope_base=10000.0, min_period=4e-3, max_period=4.0)
+PI0_P = 816
+
+
+def pi0_flops_per_chunk():
+    """Dense FLOPs of the pi0-shaped loop per observation: expert GEMMs + attention (algorithmic)."""
+    c, S = PI0, 51
+    qf, kvf, H, I = c["n_q"] * c["head_dim"], c["n_kv"] * c["head_dim"], c["H"], c["inter"]
+    per_layer = 2 * S * H * (qf + 2 * kvf) + 2 * S * qf * H + 3 * 2 * S * H * I + 4 * S * c["n_q"] * (PI0_P + S) * c["head_dim"]
+    per_step = c["n_layers"] * per_layer + 2 * 2 * c["chunk"] * H * H
+    return per_step * c["steps"]
+
+
+def build_pi0_engine(torch, vb, dev, n_obs, seed):
+    c = PI0
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    H, I, qf, kvf, A, sd = c["H"], c["inter"], c["n_q"] * c["head_dim"], c["n_kv"] * c["head_dim"], 32, 32
+    bw = lambda *s: (torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    fv = lambda n: torch.zeros(n, device=dev)
+    L = c["n_layers"]
+    w = dict(wq=[bw(qf, H) for _ in range(L)], wk=[bw(kvf, H) for _ in range(L)], wv=[bw(kvf, H) for _ in range(L)],
+             wo=[bw(H, qf) for _ in range(L)], wgate=[bw(I, H) for _ in range(L)], wup=[bw(I, H) for _ in range(L)],
+             wdown=[bw(H, I) for _ in range(L)], ln_in=[torch.ones(H, device=dev) for _ in range(L)],
+             ln_post=[torch.ones(H, device=dev) for _ in range(L)], w_sp=bw(H, sd), b_sp=fv(H), w_ain=bw(H, A),
+             b_ain=fv(H), w_at1=bw(H, 2 * H), b_at1=fv(H), w_at2=bw(H, H), b_at2=fv(H),
+             out_norm=torch.ones(H, device=dev), w_aout=bw(A, H), b_aout=fv(A))
+    eng = vb.PolicyEngine(c, w, max_obs=n_obs, prefix_len=PI0_P)
+    del w
+    blk = 64
+    for l in range(L):  # the prefix KV is written once per observation
+        for o in range(0, n_obs, blk):
+            n = min(blk, n_obs - o)
+            eng.set_prefix(l, torch.randn((n, PI0_P, 1, 256), device=dev, generator=g),
+                           torch.randn((n, PI0_P, 1, 256), device=dev, generator=g), obs0=o)
+    x0 = torch.randn((n_obs, 50, 32), device=dev, generator=g)
+    state = torch.randn((n_obs, 32), device=dev, generator=g)
+    torch.cuda.synchronize()
+    return eng, x0, state
+
+
+def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None):
+    """Times `steps` whole denoise loops over n_obs observations: device-resident and through host buffers."""
+    eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, seed)
+    sync = barrier or torch.cuda.synchronize
+    for _ in range(warmup):
+        eng.denoise(x0, state)
+    sync()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        eng.denoise(x0, state)
+        ev[i + 1].record()
+    sync()
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+    x0h, sth = x0.cpu().pin_memory(), state.cpu().pin_memory()
+    outh = torch.empty_like(x0h).pin_memory()
+    eng.denoise_host(x0h, sth, outh)
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(2, min(steps, 3))
+    e0.record()
+    for _ in range(n_e2e):
+        eng.denoise_host(x0h, sth, outh)
+    e1.record()
+    sync()
+    if vb.device_status() != 0:
+        raise SystemExit("device status word reports a kernel failure")
+    return {"total_ms": ev[0].elapsed_time(ev[-1]), "p50_ms": statistics.median(step_ms),
+            "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4}
+
+
 def config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
@@ -141,7 +214,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--batch", type=int, default=256, help="observations per GPU")
+    ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
+    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0"],
+                    help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
+                         "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
+    ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
+    ap.add_argument("--no-pi0-extra", action="store_true", help="skip the short pi0-loop measurement in the default run")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -171,8 +249,48 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    c, B = CFG, args.batch
     dev = torch.device("cuda", local_rank)
+    if args.workload == "pi0":
+        from vla_cpp_b200.shard import shard_range
+
+        n_obs = args.pi0_obs or shard_range(1024, world, rank)[1]
+        n_global = args.pi0_obs * world if args.pi0_obs else 1024
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier)
+        clocks = sampler.stop()
+        stats = torch.tensor([r["total_ms"], r["p50_ms"], r["e2e_ms"]], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        total_ms, p50_ms, e2e_ms = [float(v) for v in stats.tolist()]
+        if rank == 0:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+                os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+            tf_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+            tf = pi0_flops_per_chunk() * n_obs * args.steps / (total_ms * 1e-3) / 1e12  # per GPU (rank 0's share)
+            line = {
+                "metric": "action chunks/s (denoise loop)", "value": n_global * args.steps / (total_ms * 1e-3),
+                "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
+                "scaling": "weak" if args.pi0_obs else "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": "pi0: whole pi0-shaped denoise loop (BASELINE configs[2]/[4]): 18 layers, "
+                                       "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32, 10 steps",
+                           "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
+                           "l2": "inputs larger than L2 (KV pages + expert weights > 126 MB per GPU)"},
+                "clocks": clocks, "gpu_launches": (10 * (3 + 18 * 5 + 1) + 3) * args.steps,
+                "roofline": {"kernel": "whole loop (dense_gemm_kernel, qkv_rope_tma_kernel, attn_flash_kernel)",
+                             "bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
+                             "frac": tf / tf_peak, "peak_kind": "of measured (sustained)", "traffic": None},
+                "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": r["h2d"],
+                        "d2h_bytes_per_step": r["d2h"], "ms_per_step": e2e_ms},
+            }
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    c, B = CFG, args.batch
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
     # ---- synthetic inputs, resident in HBM --------------------------------------------------
@@ -278,6 +396,16 @@ def main():
             line["e2e"] = {"value": B * world / (e2e_ms * 1e-3), "unit": "chunks/s",
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                            "ms_per_step": e2e_ms}
+        if world == 1 and not args.no_pi0_extra:
+            # the whole pi0-shaped loop at batch 64 (BASELINE configs[2]), as an extra figure
+            del store, x, op, wqkv
+            torch.cuda.empty_cache()
+            r = measure_pi0(torch, vb, dev, 64, 3, 2, 5)
+            line["pi0_loop_batch64"] = {
+                "chunks_per_s": 64 * 3 / (r["total_ms"] * 1e-3), "p50_chunk_latency_ms": r["p50_ms"],
+                "tflops": pi0_flops_per_chunk() * 64 * 3 / (r["total_ms"] * 1e-3) / 1e12,
+                "e2e_chunks_per_s": 64 / (r["e2e_ms"] * 1e-3), "h2d_bytes_per_step": r["h2d"],
+                "d2h_bytes_per_step": r["d2h"]}
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle_ffi as orc
 
