@@ -98,9 +98,18 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16 *__r
 
 // ------------------------------------------------------------ shared decode ----
 // One 4-byte ladder slot -> four words of int8x4 (16 consecutive k), value = code - 2.
+// Per byte: code c in {0..3} -> c - 2 as int8.  The low two bits of c - 2 are c ^ 2 and the upper
+// six bits are ones exactly when c < 2, so with u = (x & 3) ^ 2 and neg = u & 2 (set when c < 2)
+// the result is u + neg * 126 (0x02 * 126 = 0xFC, no carry between bytes).
+__device__ __forceinline__ uint32_t decode_word(uint32_t x) {
+    uint32_t u, neg;
+    asm("lop3.b32 %0, %1, 0x03030303, 0x02020202, 0x6a;" : "=r"(u) : "r"(x));    // (x & a) ^ b
+    asm("lop3.b32 %0, %1, 0x02020202, 0x02020202, 0x0c;" : "=r"(neg) : "r"(x));  // ~x & b  (c < 2)
+    return neg * 126u + u;
+}
 __device__ __forceinline__ void decode_slot(uint32_t w, uint32_t (&d)[4]) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d[j] = __vsub4((w >> (2 * j)) & 0x03030303u, 0x02020202u);
+    for (int j = 0; j < 4; ++j) d[j] = decode_word(w >> (2 * j));
 }
 
 __device__ __forceinline__ float ternary_scale_out(int acc, float s, float ws) {
@@ -204,18 +213,29 @@ __global__ void __launch_bounds__(128) ternary_gemv_kernel(const int8_t *__restr
 // ----------------------------------------------------------------- tcgen05 GEMM --
 // C[m, n] = sum_k A[m, k] * W[n, k].  MMA M = 128 activation rows (TMA, SWIZZLE_128B),
 // MMA N = BN weight rows decoded from the ladder pack into the same swizzled K-major
-// layout, K step 128 bytes = 4 MMAs of K = 32.
+// layout, K step 128 bytes = 4 MMAs of K = 32.  Persistent CTAs (one per SM) walk the output
+// tiles; the s32 accumulator is double-buffered in TMEM so a tile's epilogue overlaps the next
+// tile's main loop.
+//   warp 0      TMA loader (activations)
+//   warp 1      tcgen05.mma issuer
+//   warps 2-9   decoders: 2-bit ladder slots -> int8, written into the swizzled B tile
+//   warps 10-13 epilogue (one per TMEM lane quarter): acc / s[m] * ws -> bf16
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 128;
-constexpr int GEMM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: decode + epilogue
+constexpr int GEMM_THREADS = 448;
+
+// Separate rings: the activation ring is deep (TMA latency from L2 is several main-loop steps),
+// the decoded-weight ring shallow (its producers are warps of this CTA).
+constexpr int GEMM_SA = 7, GEMM_SW = 3;
 
 template <int BN, int STAGES>
 struct GemmSmem {
     static constexpr int A_BYTES = GEMM_BM * GEMM_BK;
     static constexpr int W_BYTES = BN * GEMM_BK;
-    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+    static constexpr int W_OFFSET = GEMM_SA * A_BYTES;
+    static constexpr int BAR_OFFSET = W_OFFSET + GEMM_SW * W_BYTES;
+    static constexpr int STAGING_OFFSET = BAR_OFFSET + 256;  // 4 epilogue warps x 32 rows x 128 bytes
+    static constexpr int TOTAL = STAGING_OFFSET + 4 * 4096 + 1024;  // + alignment slack
 };
 
 template <int BN, int STAGES>
@@ -223,36 +243,43 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ Wp,
                        __nv_bfloat16 *__restrict__ out, int32_t *__restrict__ acc_out,
                        const float *__restrict__ s, const float *__restrict__ ws, int ws_num, int M, int N, int K,
-                       int *status) {
+                       int tiles_m, int tiles_n, int *status) {
     using L = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
     uint64_t *full_a = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
-    uint64_t *full_w = full_a + STAGES;
-    uint64_t *empty = full_w + STAGES;
-    uint64_t *accum_bar = empty + STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_bar + 1);
+    uint64_t *empty_a = full_a + GEMM_SA;
+    uint64_t *full_w = empty_a + GEMM_SA;
+    uint64_t *empty_w = full_w + GEMM_SW;
+    uint64_t *accum_full = empty_w + GEMM_SW;
+    uint64_t *accum_empty = accum_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * GEMM_BM;
-    const int n0 = blockIdx.y * BN;
     const int ksteps = K / GEMM_BK;
+    const int n_tiles = tiles_m * tiles_n;
     const WaitCtx wc{abort_flag, status};
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; ++i) {
+        for (int i = 0; i < GEMM_SA; ++i) {
             mbar_init(&full_a[i], 1);
-            mbar_init(&full_w[i], 128);
-            mbar_init(&empty[i], 1);
+            mbar_init(&empty_a[i], 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int i = 0; i < GEMM_SW; ++i) {
+            mbar_init(&full_w[i], 256);
+            mbar_init(&empty_w[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&accum_full[i], 1);
+            mbar_init(&accum_empty[i], 128);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, BN);
+        tmem_alloc(tmem_slot, 2 * BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -260,71 +287,87 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // tiles are ordered m-fastest so that CTAs running at the same time share a weight slab
     if (warp == 0) {
         if (lane == 0) {
             tma_prefetch_desc(&a_map);
-            for (int kt = 0; kt < ksteps; ++kt) {
-                const int st = kt % STAGES;
-                const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-                if (!mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY)) break;
-                mbar_expect_tx(&full_a[st], L::A_BYTES);
-                tma_load_2d(smem + st * L::STAGE_BYTES, &a_map, &full_a[st], kt * GEMM_BK, m0);
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * GEMM_BM;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&empty_a[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&full_a[st], L::A_BYTES);
+                    tma_load_2d(smem + st * L::A_BYTES, &a_map, &full_a[st], kt * GEMM_BK, m0);
+                    if (++st == GEMM_SA) { st = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(2, 1, 1, 0, 0, GEMM_BM, BN);
-            for (int kt = 0; kt < ksteps; ++kt) {
-                const int st = kt % STAGES;
-                const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-                if (!mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL)) break;
-                if (!mbar_wait(&full_w[st], ph, wc, DEV_TIMEOUT_FULL)) break;
+            uint32_t st = 0, ph = 0, sw = 0, pw = 0, j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+                const uint32_t buf = j & 1u;
+                ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + st * L::STAGE_BYTES);
-                const uint32_t w_addr = a_addr + L::A_BYTES;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok) ok = mbar_wait(&full_w[sw], pw, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + st * L::A_BYTES);
+                    const uint32_t w_addr = smem_u32(smem + L::W_OFFSET + sw * L::W_BYTES);
+#ifdef VB_TERN_NOMMA
+                    if (kt == 0)  // developer experiment: one MMA group per tile only
+#endif
 #pragma unroll
-                for (int k = 0; k < GEMM_BK / 32; ++k) {
-                    const uint64_t ad = smem_desc_sw128(a_addr + k * 32, 16, 1024);
-                    const uint64_t bd = smem_desc_sw128(w_addr + k * 32, 16, 1024);
-                    mma_i8(tmem_base, ad, bd, idesc, (kt | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < GEMM_BK / 32; ++k)
+                        mma_i8(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                               smem_desc_sw128(w_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
+                    tc_commit(&empty_a[st]);
+                    tc_commit(&empty_w[sw]);
+                    if (++st == GEMM_SA) { st = 0; ph ^= 1u; }
+                    if (++sw == GEMM_SW) { sw = 0; pw ^= 1u; }
                 }
-                tc_commit(&empty[st]);
+                if (!ok) break;
+                tc_commit(&accum_full[buf]);
             }
-            tc_commit(accum_bar);
         }
-    } else {
+    } else if (warp < 10) {
         // ---- decode warps: ladder slots -> swizzled K-major int8 tile ----
-        const int dw = warp - 2;                  // 0..3
+        const int dw = warp - 2;                  // 0..7
         constexpr int NBLK = BN / 16;             // 16-row weight blocks in the tile
-        constexpr int PER_WARP = NBLK / 4;
+        constexpr int PER_WARP = NBLK / 8;
         const int nblk_total = N / 16;
-        const int nb0 = n0 / 16;
         // lane geometry inside one 512-byte chunk
         const int row_in_blk = 8 * ((lane & 7) >> 2) + 4 * (lane & 1);  // + slot 0..3
         const int chunk16 = 2 * (lane >> 3) + ((lane & 3) >> 1);        // 16-byte column 0..7
-        uint4 nxt[PER_WARP];
-        auto fetch = [&](int kt) {
+        // Packed weights are prefetched three main-loop steps ahead into registers: one step is
+        // shorter than the latency of a load that misses L2.
+        constexpr int PF = 3;
+        uint4 pf[PF][PER_WARP];
+        const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const int total = my_tiles * ksteps;
+        auto fetch = [&](int g, uint4 (&dst)[PER_WARP]) {  // g: flat step index over this CTA's tiles
+            const int tile = blockIdx.x + (g / ksteps) * gridDim.x, kt = g % ksteps;
+            const int nb0 = (tile / tiles_m) * NBLK;
 #pragma unroll
             for (int i = 0; i < PER_WARP; ++i) {
-                const int nb = nb0 + dw + 4 * i;
-                nxt[i] = (nb < nblk_total && kt < ksteps)
+                const int nb = nb0 + dw + 8 * i;
+                dst[i] = (g < total && nb < nblk_total)
                              ? __ldg(reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K + (size_t)kt * 512) + lane)
                              : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
             }
         };
-        fetch(0);
-        for (int kt = 0; kt < ksteps; ++kt) {
-            const int st = kt % STAGES;
-            const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-            uint4 cur[PER_WARP];
-#pragma unroll
-            for (int i = 0; i < PER_WARP; ++i) cur[i] = nxt[i];
-            fetch(kt + 1);
-            if (!mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY)) break;
-            uint8_t *wt = smem + st * L::STAGE_BYTES + L::A_BYTES;
+        auto decode_store = [&](const uint4 (&cur)[PER_WARP], uint8_t *wt) {
 #pragma unroll
             for (int i = 0; i < PER_WARP; ++i) {
-                const int blk = dw + 4 * i;
+                const int blk = dw + 8 * i;
                 const uint32_t words[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
 #pragma unroll
                 for (int sl = 0; sl < 4; ++sl) {
@@ -335,55 +378,115 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
                     *reinterpret_cast<uint4 *>(dst) = make_uint4(d[0], d[1], d[2], d[3]);
                 }
             }
-            fence_proxy_async_smem();
-            mbar_arrive(&full_w[st]);
+        };
+        uint32_t st = 0, ph = 0;
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < PF; ++i) fetch(i, pf[i]);
+        for (int g0 = 0; ok && g0 < total; g0 += PF) {
+#pragma unroll
+            for (int u = 0; u < PF; ++u) {
+                const int g = g0 + u;
+                if (g >= total) break;
+                uint4 cur[PER_WARP];
+#pragma unroll
+                for (int i = 0; i < PER_WARP; ++i) cur[i] = pf[u][i];
+                fetch(g + PF, pf[u]);
+                ok = mbar_wait(&empty_w[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+#ifdef VB_TERN_NODECODE
+                if (cur[0].x == 0x12345u)  // developer experiment: skip the decode work
+#endif
+                decode_store(cur, smem + L::W_OFFSET + st * L::W_BYTES);
+                fence_proxy_async_smem();
+                mbar_arrive(&full_w[st]);
+                if (++st == GEMM_SW) { st = 0; ph ^= 1u; }
+            }
         }
-        // ---- epilogue: TMEM -> registers -> global ----
-        if (mbar_wait(accum_bar, 0, wc, DEV_TIMEOUT_ACCUM)) {
-            tc_fence_after();
-            const int q = warp & 3;  // TMEM lane quarter this warp may read
+    } else {
+        // ---- epilogue warps 10..13: TMEM -> registers -> shared-memory transpose -> global ----
+        // A thread owns one accumulator row; writing its 128 bytes straight to global memory would
+        // scatter 16-byte pieces over 32 rows per instruction.  Each warp instead stages 32 rows x 64
+        // columns (bf16) in shared memory and writes them back as whole 128-byte lines.
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int group = N / ws_num;
+        uint8_t *stg = smem + L::STAGING_OFFSET + (warp - 10) * 4096;
+        const uint32_t my_sw = (uint32_t)(lane & 7);
+        uint32_t j = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            const uint32_t buf = j & 1u;
+            const int m0 = (tile % tiles_m) * GEMM_BM, n0 = (tile / tiles_m) * BN;
             const int m = m0 + q * 32 + lane;
+            ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
             const float sm = (m < M) ? s[m] : 1.0f;
-            const int group = N / ws_num;
+            const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+            for (int c = 0; c < BN; c += 64) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(lane_addr + (uint32_t)c, r0);
+                tmem_ld32(lane_addr + (uint32_t)(c + 32), r1);
                 tmem_ld_wait();
-                const int n = n0 + c * 32;
-                if (m < M && n < N) {
-                    if (acc_out) {
-                        int4 *dst = reinterpret_cast<int4 *>(acc_out + (size_t)m * N + n);
+                const int n = n0 + c;
+                if (n >= N) break;  // uniform: N % 32 == 0, the second half may still be past N
+                if (acc_out && m < M) {
+                    int4 *dst = reinterpret_cast<int4 *>(acc_out + (size_t)m * N + n);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (n + 4 * j < N)
-                                dst[j] = make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]);
-                    }
-                    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)m * N + n);
+                    for (int e = 0; e < 8; ++e)
+                        dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
+                    if (n + 32 < N) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (n + 8 * j >= N) break;
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int col = n + 8 * j + 2 * e;
-                            const float w0 = ws[col / group], w1 = ws[(col + 1) / group];
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(
-                                ternary_scale_out((int)r[8 * j + 2 * e], sm, w0),
-                                ternary_scale_out((int)r[8 * j + 2 * e + 1], sm, w1));
-                            pk[e] = *reinterpret_cast<const uint32_t *>(&h);
-                        }
-                        dst[j] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        for (int e = 0; e < 8; ++e)
+                            dst[8 + e] = make_int4((int)r1[4 * e], (int)r1[4 * e + 1], (int)r1[4 * e + 2], (int)r1[4 * e + 3]);
                     }
                 }
+                // acc / s * ws evaluated as acc * (ws / s): at most one float ulp from the two-step form.
+                // A 32-column chunk never straddles a scale group (the group size is a multiple of 32).
+                const float cs0 = __fdiv_rn(ws[n / group], sm);
+                const float cs1 = __fdiv_rn(ws[min(n + 32, N - 1) / group], sm);
+                uint8_t *mine = stg + lane * 128;
+#pragma unroll
+                for (int e4 = 0; e4 < 4; ++e4) {
+                    uint32_t pa[4], pb[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 ha = __floats2bfloat162_rn((float)(int)r0[8 * e4 + 2 * e] * cs0,
+                                                                        (float)(int)r0[8 * e4 + 2 * e + 1] * cs0);
+                        const __nv_bfloat162 hb = __floats2bfloat162_rn((float)(int)r1[8 * e4 + 2 * e] * cs1,
+                                                                        (float)(int)r1[8 * e4 + 2 * e + 1] * cs1);
+                        pa[e] = *reinterpret_cast<const uint32_t *>(&ha);
+                        pb[e] = *reinterpret_cast<const uint32_t *>(&hb);
+                    }
+                    *reinterpret_cast<uint4 *>(mine + (((uint32_t)e4 ^ my_sw) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                    *reinterpret_cast<uint4 *>(mine + (((uint32_t)(4 + e4) ^ my_sw) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+                }
+                __syncwarp();
+                const int cols_valid = min(64, N - n);  // 32 or 64
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = (lane >> 3) + 4 * i;
+                    const int ch = lane & 7;
+                    const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * 128 + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4));
+                    const int mr = m0 + q * 32 + rr;
+#ifdef VB_TERN_NOSTORE
+                    if (v.x == 0x12345u)  // developer experiment: no output stores
+#endif
+                    if (mr < M && ch * 8 < cols_valid)
+                        *reinterpret_cast<uint4 *>(out + (size_t)mr * N + n + ch * 8) = v;
+                }
+                __syncwarp();
             }
+            tc_fence_before();
+            mbar_arrive(&accum_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
@@ -421,14 +524,19 @@ static int launch_gemm_tc(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
     if (rc) return rc;
     using L = GemmSmem<BN, STAGES>;
     static bool attr_done = false;
+    static int n_sm = 0;
     if (!attr_done) {
         VB_CUDA(cudaFuncSetAttribute(ternary_gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      L::TOTAL));
+        int dev = 0;
+        VB_CUDA(cudaGetDevice(&dev));
+        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
         attr_done = true;
     }
-    dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN);
-    ternary_gemm_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, st>>>(amap, W, out, acc, s, ws, ws_num, M, N, K,
-                                                                           status);
+    const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + BN - 1) / BN;
+    const int nt = tiles_m * tiles_n;
+    ternary_gemm_tc_kernel<BN, STAGES><<<nt < n_sm ? nt : n_sm, GEMM_THREADS, L::TOTAL, st>>>(
+        amap, W, out, acc, s, ws, ws_num, M, N, K, tiles_m, tiles_n, status);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
@@ -454,7 +562,7 @@ static int ternary_linear(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (acc && (reinterpret_cast<uintptr_t>(acc) & 15)))
         return VLAB200_ERR_ARG;
-    if (N % 32) return VLAB200_ERR_UNSUPPORTED;
+    if (N % 32 || (N / ws_num) % 32) return VLAB200_ERR_UNSUPPORTED;
     if (N >= 256) return launch_gemm_tc<256, 4>(A, W, out, acc, s, ws, ws_num, M, N, K, st);
     return launch_gemm_tc<128, 4>(A, W, out, acc, s, ws, ws_num, M, N, K, st);
 }
