@@ -5,14 +5,21 @@
 // R = g*S rows (GQA/MQA head sharing: K and V are fetched once for all of them) and processed
 // as 128-row tcgen05 tiles.
 //
-//   loader warp   TMA (SWIZZLE_128B): Q rows, K page, V page of item n+1 into a 2-stage ring
-//                 while item n computes (pages are read from HBM exactly once)
-//   2 MMA warps   one per TMEM region (items alternate between the regions):
+//   loader warp   TMA (SWIZZLE_128B): Q rows, K page, V page of the next items into 2-deep rings
+//                 while the current ones compute (pages are read from HBM exactly once)
+//   2 MMA warps   one per TMEM region (items alternate between the two regions):
 //                 S = Q K^T (kind::f16, f32 accumulator, all keys at once), then O = P V with
 //                 A = P read from TMEM and V as an MN-major operand
-//   2 x 4 softmax warps (one group per region): one thread per row (TMEM lane); two passes over
-//                 the row straight out of TMEM, exp2 with the scale folded in, masked columns
-//                 skipped; P (bf16) overwrites the consumed S columns; epilogue O / rowsum -> bf16
+//   2 x 8 softmax warps (per region two warps per TMEM lane quarter, one per half of the key
+//                 columns): one thread per (row, column half); two passes over its columns
+//                 straight out of TMEM, exp2 with the scale folded in, masks applied as selects;
+//                 the halves exchange row maximum and row sum through shared memory; P (bf16)
+//                 overwrites consumed S columns; epilogue O / rowsum -> bf16
+//
+// TMEM region (256 columns): S [0, nk16) in nchunks chunks of 32 columns, the first n_a of them
+// owned by column half A.  P (bf16, 16 columns per chunk) overwrites columns its own half has
+// already consumed: half A at [0, 16 n_a), half B at [32 n_a, 32 n_a + 16 (nchunks - n_a)); O (64
+// columns) follows the P of half B.
 //
 // Reference: src/layers/attn.h:38-46, src/models/pi0.cpp:204-223 (mul_mat -> soft_max -> mul_mat
 // with the score matrix in HBM), src/models/smolvla.cpp:835-842,874-881 (ggml_flash_attn_ext);
@@ -28,14 +35,14 @@ namespace vb {
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
                     int mask_mode, const int32_t *pad_ranges, cudaStream_t stream);
 
-constexpr int ATT_THREADS = 352;  // warps 0-3 / 4-7: softmax groups, 8: loader, 9-10: MMA issuers
+constexpr int ATT_SOFTMAX_WARPS = 16;
+constexpr int ATT_THREADS = (ATT_SOFTMAX_WARPS + 3) * 32;  // + loader + 2 MMA issuers
 constexpr int ATT_MAX_KEYS = 256;
 constexpr int ATT_Q_TILE_BYTES = 128 * 128;
 constexpr int ATT_KV_BYTES = ATT_MAX_KEYS * 128;
 constexpr int ATT_QK_BYTES = 2 * ATT_Q_TILE_BYTES + ATT_KV_BYTES;  // Q0, Q1, K of one item
 constexpr int ATT_SMEM_DATA = 2 * ATT_QK_BYTES + 2 * ATT_KV_BYTES;  // two Q/K buffers, two V buffers
-constexpr int ATT_REGION_COLS = 256;  // per region: S [0,256) / P [0,128) aliased, O [128,192)
-constexpr int ATT_O_COL = 128;
+constexpr int ATT_REGION_COLS = 256;
 
 struct AttnParams {
     __nv_bfloat16 *out;  // [n_obs][S][n_q*hd]
@@ -46,38 +53,32 @@ struct AttnParams {
     float scale_log2;
     int *status;
 #ifdef VB_TRACE
-    long long *trace;  // [block][unit][8] clock64 stamps of one softmax warp (developer builds only)
+    long long *trace;  // developer builds: clock64 stamps of one softmax warp per region
 #endif
 };
 
 #ifdef VB_TRACE
-#define VB_STAMP(slot)                                                                      \
-    do {                                                                                    \
-        if (p.trace && qtr == 0 && lane == 0 && k_unit_global < 16)                         \
-            p.trace[((size_t)blockIdx.x * 32 + (size_t)(k_unit_global * 2 + r)) * 8 + (slot)] = clock64(); \
-    } while (0)
-#define VB_STAMP_CHUNK(cc)                                                                   \
-    do {                                                                                    \
-        if (p.trace && qtr == 0 && lane == 0 && k_unit_global == 0)                         \
-            p.trace[((size_t)blockIdx.x * 32 + 24 + r) * 8 + ((cc) & 7)] = clock64();       \
+#define VB_STAMP(slot)                                                                                     \
+    do {                                                                                                   \
+        if (p.trace && qtr == 0 && half == 0 && lane == 0 && k_unit < 16)                                  \
+            p.trace[((size_t)blockIdx.x * 32 + (size_t)(k_unit * 2 + r)) * 8 + (slot)] = clock64();        \
     } while (0)
 #else
 #define VB_STAMP(slot) do { } while (0)
-#define VB_STAMP_CHUNK(cc) do { } while (0)
 #endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
-#ifdef VB_EXP_NOEX2
-    return x * 0.001f + 0.5f;  // developer experiment: no transcendental
-#else
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-#endif
 }
 
-// Per-row mask description used by the softmax helpers: columns [0, jmax) minus [pad_lo, pad_hi)
-// are visible; columns below clean_end need no test in any lane of the warp.
+__device__ __forceinline__ void region_sync(int r) {  // the 256 softmax threads of region r
+    asm volatile("bar.sync %0, 256;" ::"r"(r + 1) : "memory");
+}
+
+// Per-row mask description: columns [0, jmax) minus [pad_lo, pad_hi) are visible; columns below
+// clean_end need no test in any lane of the warp.
 struct RowMask {
     int jmax, pad_lo, pad_hi, clean_end;
 };
@@ -97,7 +98,6 @@ __device__ __forceinline__ float att_masked(uint32_t bits, int j, int rel_jmax, 
 
 __device__ __forceinline__ void att_max_chunk(const uint32_t (&sv)[32], int c, const RowMask &rm, float (&mx)[4]) {
     if (c * 32 + 32 <= rm.clean_end) {
-        // a reduction tree (independent operations), then one update of the running maxima
         float t[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -124,8 +124,7 @@ __device__ __forceinline__ void att_max_chunk(const uint32_t (&sv)[32], int c, c
 }
 
 // p = exp2(s*c - m*c) for one 32-column chunk; P (bf16) is stored over consumed S columns.  bf16
-// rounding uses integer adds (round-half-up on the magnitude; p >= 0): the conversion instruction
-// shares the transcendental unit that ex2 saturates.
+// rounding uses integer adds (round-half-up on the magnitude; p >= 0).
 __device__ __forceinline__ void att_exp_chunk(const uint32_t (&sv)[32], int c, const RowMask &rm, float scale_log2,
                                               float m2, float &sum0, float &sum1, uint32_t p_addr) {
     uint32_t pk[16];
@@ -151,11 +150,7 @@ __device__ __forceinline__ void att_exp_chunk(const uint32_t (&sv)[32], int c, c
             pk[j >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
         }
     }
-#ifdef VB_EXP_NOST
-    if (sum0 == 12345.678f) tmem_st16(p_addr, pk);  // developer experiment: no TMEM store
-#else
     tmem_st16(p_addr, pk);
-#endif
 }
 
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -170,6 +165,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     uint64_t *bar_s = bars + 8, *bar_p = bars + 10, *bar_o = bars + 12, *bar_free = bars + 14;  // per region
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *xch = reinterpret_cast<float *>(smem + ATT_SMEM_DATA + 256);  // [2 regions][max|sum][2 halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const WaitCtx wc{abort_flag, p.status};
@@ -182,14 +178,14 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             mbar_init(&free_qk[i], 1);
             mbar_init(&free_v[i], 1);
             mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_p[i], 128);
+            mbar_init(&bar_p[i], 256);
             mbar_init(&bar_o[i], 1);
-            mbar_init(&bar_free[i], 128);
+            mbar_init(&bar_free[i], 256);
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 8) {
+    if (warp == ATT_SOFTMAX_WARPS) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -197,8 +193,12 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int nchunks = (p.nk16 + 31) / 32;
+    const int n_a = (nchunks + 1) / 2;  // chunks of the first column half
+    const int pb_col = n_a * 32;        // P of the second half starts where its S columns start
+    const int o_col = pb_col + (nchunks - n_a) * 16;
 
-    if (warp == 8) {
+    if (warp == ATT_SOFTMAX_WARPS) {
         // ------------------------------------------------------------- loader
         if (lane == 0) {
             tma_prefetch_desc(&q_map);
@@ -231,13 +231,14 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 tma_load_3d(sV, &v_map, &full_v[st], 0, 0, page);
             }
         }
-    } else if (warp == 9 || warp == 10) {
+    } else if (warp > ATT_SOFTMAX_WARPS) {
         // ------------------------------------------------------------- MMA issuer of region r
-        const int r = warp - 9;
+        const int r = warp - ATT_SOFTMAX_WARPS - 1;
         if (lane == 0) {
             const uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 128, p.nk16);
             const uint32_t idesc_o = make_idesc(1, 1, 1, 0, 1, 128, 64);
             const uint32_t treg = tmem_base + (uint32_t)(r * ATT_REGION_COLS);
+            const int k16_a = n_a * 2;  // 16-key steps whose P lives in the first column half
             int n = r;
             bool ok = true;
             for (int item = blockIdx.x + r * gridDim.x; ok && item < p.n_items; item += 2 * gridDim.x, n += 2) {
@@ -262,20 +263,25 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                     if (ok && t == 0) ok = mbar_wait(&full_v[st], m & 1u, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    for (int k16 = 0; k16 < p.nk16 / 16; ++k16)
-                        mma_f16_tmem_a(treg + ATT_O_COL, treg + (uint32_t)(k16 * 8),
-                                       smem_desc_sw128(v_addr + k16 * 2048, 16, 1024), idesc_o, k16 != 0 ? 1u : 0u);
+                    for (int k16 = 0; k16 < p.nk16 / 16; ++k16) {
+                        const uint32_t p_col = k16 < k16_a ? (uint32_t)(k16 * 8) : (uint32_t)(pb_col + (k16 - k16_a) * 8);
+                        mma_f16_tmem_a(treg + (uint32_t)o_col, treg + p_col, smem_desc_sw128(v_addr + k16 * 2048, 16, 1024),
+                                       idesc_o, k16 != 0 ? 1u : 0u);
+                    }
                     tc_commit(&bar_o[r]);
                 }
                 if (ok) tc_commit(&free_v[st]);  // every MMA that reads this V buffer has been issued
             }
         }
     } else {
-        // ------------------------------------------------------------- softmax group of region r
-        const int r = warp >> 2, qtr = warp & 3;
+        // ------------------------------------------------------------- softmax warps of region r
+        const int r = warp >> 3, half = (warp >> 2) & 1, qtr = warp & 3;
         const uint32_t lane_addr = tmem_base + (uint32_t)(r * ATT_REGION_COLS) + ((uint32_t)(qtr * 32) << 16);
         const int n_suffix_cols = p.kv_len - p.prefix_len;
-        const int nchunks = (p.nk16 + 31) / 32;
+        const int c_begin = half ? n_a : 0, c_end = half ? nchunks : n_a;
+        const uint32_t p_base = lane_addr + (half ? (uint32_t)pb_col : 0u);
+        float *x_max = xch + r * 512, *x_sum = x_max + 256;  // [2 halves][128 rows] each
+        const int my_row_slot = qtr * 32 + lane;
         int n = r;
         bool ok = true;
         for (int item = blockIdx.x + r * gridDim.x; ok && item < p.n_items; item += 2 * gridDim.x, n += 2) {
@@ -288,8 +294,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             }
             for (int t = 0; ok && t < n_tiles; ++t) {
                 const uint32_t k_unit = m * (uint32_t)n_tiles + (uint32_t)t;
-                const uint32_t k_unit_global = k_unit;
-                (void)k_unit_global;
                 VB_STAMP(0);
                 // row of this thread inside the R-row block, or -1
                 int row;
@@ -302,77 +306,42 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 int limit = n_suffix_cols;
                 if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
                 else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
-                const int jmax = p.prefix_len + limit;
+                int clean_end = p.prefix_len;
+                if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
+                const RowMask rm{p.prefix_len + limit, pad_lo, pad_hi, clean_end};
                 ok = mbar_wait(&bar_s[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
                 VB_STAMP(1);
-                float sum = 0.0f;
+                // ---- pass 1: maximum over this thread's columns ----
+                float mxx = -INFINITY;
                 if (warp_active) {
-                    // columns below `clean_end` need no mask test in any lane of the warp
-                    int clean_end = p.prefix_len;
-                    if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
-                    RowMask rm{jmax, pad_lo, pad_hi, clean_end};
-                    // ---- pass 1: row maximum over the visible columns (two chunks per TMEM wait) ----
                     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    for (int c = 0; c < nchunks; c += 2) {
-                        uint32_t sa[32], sb[32];
+                    for (int c = c_begin; c < c_end; ++c) {
+                        uint32_t sa[32];
                         tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
-                        tmem_ld32(lane_addr + (uint32_t)(min(c + 1, nchunks - 1) * 32), sb);
                         tmem_ld_wait();
                         att_max_chunk(sa, c, rm, mx);
-                        if (c + 1 < nchunks) att_max_chunk(sb, c + 1, rm, mx);
                     }
-                    VB_STAMP(2);
-                    const float mxx = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                    const float m2 = (mxx == -INFINITY) ? 0.0f : mxx * p.scale_log2;
-#if defined(VB_EXP_NOLD)
-                    float sum0 = 0.0f, sum1 = 0.0f;
-                    {   // developer experiment: compute on one loaded chunk, no further TMEM loads
+                    mxx = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                }
+                x_max[half * 128 + my_row_slot] = mxx;
+                region_sync(r);
+                mxx = fmaxf(mxx, x_max[(half ^ 1) * 128 + my_row_slot]);
+                const float m2 = (mxx == -INFINITY) ? 0.0f : mxx * p.scale_log2;
+                VB_STAMP(2);
+                // ---- pass 2: p = exp2(s*c - m*c), P (bf16) over this half's consumed S columns ----
+                float sum0 = 0.0f, sum1 = 0.0f;
+                if (warp_active) {
+                    for (int c = c_begin; c < c_end; ++c) {
                         uint32_t sa[32];
-                        tmem_ld32(lane_addr, sa);
+                        tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
                         tmem_ld_wait();
-                        for (int c = 0; c < nchunks; ++c)
-                            att_exp_chunk(sa, c, rm, p.scale_log2, m2, sum0, sum1, lane_addr + (uint32_t)(c * 16));
+                        att_exp_chunk(sa, c, rm, p.scale_log2, m2, sum0, sum1, p_base + (uint32_t)((c - c_begin) * 16));
                     }
-#elif defined(VB_EXP_LDONLY)
-                    float sum0 = 0.0f, sum1 = 0.0f;
-                    {   // developer experiment: TMEM loads only
-                        uint32_t acc = 0;
-                        for (int c = 0; c < nchunks; ++c) {
-                            uint32_t sa[32];
-                            tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) acc ^= sa[j];
-                        }
-                        sum0 = __uint_as_float(acc | 0x3f800000u);
-                    }
-#else
-                    // ---- pass 2: the next chunk's TMEM load is in flight while this one is exponentiated ----
-                    float sum0 = 0.0f, sum1 = 0.0f;
-                    {
-                        uint32_t sa[32], sb[32];
-                        tmem_ld32(lane_addr, sa);
-                        tmem_ld_wait();
-                        for (int c = 0; c < nchunks; c += 2) {
-                            tmem_ld32(lane_addr + (uint32_t)(min(c + 1, nchunks - 1) * 32), sb);
-                            att_exp_chunk(sa, c, rm, p.scale_log2, m2, sum0, sum1, lane_addr + (uint32_t)(c * 16));
-                            VB_STAMP_CHUNK(c);
-                            tmem_ld_wait();
-                            if (c + 1 < nchunks) {
-                                tmem_ld32(lane_addr + (uint32_t)(min(c + 2, nchunks - 1) * 32), sa);
-                                att_exp_chunk(sb, c + 1, rm, p.scale_log2, m2, sum0, sum1,
-                                              lane_addr + (uint32_t)(c * 16 + 16));
-                                VB_STAMP_CHUNK(c + 1);
-                                tmem_ld_wait();
-                            }
-                        }
-                    }
-#endif
-                    sum = sum0 + sum1;
                     tmem_st_wait();
                 }
+                x_sum[half * 128 + my_row_slot] = sum0 + sum1;
                 VB_STAMP(3);
                 tc_fence_before();
                 mbar_arrive(&bar_p[r]);
@@ -380,10 +349,11 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 if (!ok) break;
                 tc_fence_after();
                 VB_STAMP(4);
-                uint32_t o0[32], o1[32];
+                region_sync(r);  // both halves' partial sums are in shared memory
+                const float sum = x_sum[my_row_slot] + x_sum[128 + my_row_slot];
+                uint32_t o[32];
                 if (warp_active) {
-                    tmem_ld32(lane_addr + ATT_O_COL, o0);
-                    tmem_ld32(lane_addr + ATT_O_COL + 32, o1);
+                    tmem_ld32(lane_addr + (uint32_t)(o_col + half * 32), o);
                     tmem_ld_wait();
                 }
                 tc_fence_before();
@@ -392,22 +362,18 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 if (row_ok) {
                     const float inv = 1.0f / sum;
                     __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * 64) +
-                                         (size_t)(kvh * p.g + head_l) * 64;
+                                         (size_t)(kvh * p.g + head_l) * 64 + half * 32;
                     uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        uint32_t w[4], x[4];
+                        uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o0[8 * j + 2 * e]) * inv,
-                                                                           __uint_as_float(o0[8 * j + 2 * e + 1]) * inv);
-                            const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o1[8 * j + 2 * e]) * inv,
-                                                                            __uint_as_float(o1[8 * j + 2 * e + 1]) * inv);
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[8 * j + 2 * e]) * inv,
+                                                                           __uint_as_float(o[8 * j + 2 * e + 1]) * inv);
                             w[e] = *reinterpret_cast<const uint32_t *>(&h);
-                            x[e] = *reinterpret_cast<const uint32_t *>(&h1);
                         }
                         d4[j] = make_uint4(w[0], w[1], w[2], w[3]);
-                        d4[4 + j] = make_uint4(x[0], x[1], x[2], x[3]);
                     }
                 }
             }
@@ -415,7 +381,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == ATT_SOFTMAX_WARPS) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -424,7 +390,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 }  // namespace vb
 
 #ifdef VB_TRACE
-long long *g_vb_attn_trace = nullptr;
+static long long *g_vb_attn_trace = nullptr;
 extern "C" __attribute__((visibility("default"))) void vlab200_set_attn_trace(long long *p) { g_vb_attn_trace = p; }
 #endif
 
@@ -486,10 +452,9 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     p.scale_log2 = 1.4426950408889634f / sqrtf(64.0f);
     p.status = status;
 #ifdef VB_TRACE
-    extern long long *g_vb_attn_trace;
     p.trace = g_vb_attn_trace;
 #endif
-    const int smem = vb::ATT_SMEM_DATA + 256 + 1024;
+    const int smem = vb::ATT_SMEM_DATA + 256 + 2 * 512 * 4 + 1024;
     static bool attr_done = false;
     static int n_sm = 0;
     if (!attr_done) {
