@@ -176,6 +176,56 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None):
             "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4}
 
 
+def measure_ternary(torch, vb, dev, steps, warmup):
+    """BitVLA-shaped ternary linear layers (BASELINE configs[3]): per-token int8 act-quant + 2-bit
+    ladder-packed weights; M in {1, 300, 4800} x the four LM shapes.  Rotating operand sets larger
+    than L2 between timed launches."""
+    shapes = [("q/o", 2560, 2560, 1), ("k/v", 640, 2560, 1), ("gate_up", 13824, 2560, 2), ("down", 2560, 6912, 1)]
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    rows = []
+    for name, N, K, ws_num in shapes:
+        for M in (1, 300, 4800):
+            n_sets = max(2, int(160e6 // (N * K // 4 + M * K + M * N * 2)) + 1)
+            n_sets = min(n_sets, 24)
+            a = torch.randint(-127, 128, (n_sets, M, K), dtype=torch.int8, device=dev, generator=g)
+            wp = torch.randint(0, 256, (n_sets, N * K // 4), dtype=torch.uint8, device=dev, generator=g)
+            sc = torch.rand((n_sets, M), device=dev, generator=g) * 100 + 40
+            ws = torch.rand((ws_num,), device=dev, generator=g) * 0.05 + 0.01
+            out = torch.empty((n_sets, M, N), dtype=torch.bfloat16, device=dev)
+            for i in range(warmup):
+                vb.ternary_linear(a[i % n_sets], wp[i % n_sets], sc[i % n_sets], ws, N, out=out[i % n_sets])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(steps, 10) * 2
+            e0.record()
+            for i in range(reps):
+                vb.ternary_linear(a[i % n_sets], wp[i % n_sets], sc[i % n_sets], ws, N, out=out[i % n_sets])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            rows.append({"layer": name, "M": M, "N": N, "K": K, "us": ms * 1e3, "tops": 2.0 * M * N * K / ms / 1e9,
+                         "packed_weight_gbs": N * K / 4 / ms / 1e6})
+            del a, wp, sc, out
+    if vb.device_status() != 0:
+        raise SystemExit("device status word reports a kernel failure")
+    big = max((r for r in rows if r["M"] == 4800), key=lambda r: r["tops"])
+    gemv = max((r for r in rows if r["M"] == 1), key=lambda r: r["packed_weight_gbs"])
+    hbm_peak, kind = measured_peaks()
+    return {"metric": "ternary x int8 GEMM throughput (BitVLA LM shapes)", "value": big["tops"], "unit": "TOPS",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": big["us"] / 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary (int32 accumulate)", "data": "synthetic",
+            "config": {"workload": "ternary: BASELINE configs[3], 4 LM shapes x M in {1, 300, 4800}",
+                       "l2": "operand sets rotated (> 126 MB) between launches"},
+            "roofline": {"kernel": "ternary_gemm_tc_kernel", "bound": "tensor", "achieved": big["tops"],
+                         "peak": INT8_PEAK_TOPS, "unit": "TOPS", "frac": big["tops"] / INT8_PEAK_TOPS,
+                         "peak_kind": "of measured (cuBLASLt int8, burst)", "traffic": None, "shape": big},
+            "roofline_gemv": {"kernel": "ternary_gemv_kernel", "bound": "hbm", "achieved": gemv["packed_weight_gbs"],
+                              "peak": hbm_peak, "unit": "GB/s", "frac": gemv["packed_weight_gbs"] / hbm_peak,
+                              "peak_kind": f"of {kind}", "shape": gemv},
+            "shapes": rows}
+
+
 def config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
@@ -215,7 +265,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0"],
+    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary"],
                     help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
                          "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
     ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
@@ -250,6 +300,12 @@ def main():
         torch.cuda.synchronize()
 
     dev = torch.device("cuda", local_rank)
+    if args.workload == "ternary":
+        if rank == 0:
+            print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3))), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "pi0":
         from vla_cpp_b200.shard import shard_range
 

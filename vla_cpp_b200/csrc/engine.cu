@@ -53,66 +53,60 @@ __global__ void time_vector_kernel(const __nv_bfloat16 *__restrict__ w_at1, cons
     if (lane == 0) tvec[warp] = acc + (b_at1 ? b_at1[o] : 0.0f);
 }
 
-// a[obs*chunk + t][o] = bf16(b_ain[o] + sum_k W_ain[o][k] x[obs][t][k]);  pi0 also writes the state
-// token (row 0 of each observation) of h / hb.  One CTA per observation row group.
-__global__ void __launch_bounds__(256) suffix_in_kernel(const float *__restrict__ x, const float *__restrict__ state,
+// a[row][o] = bf16(b_ain[o] + sum_k W_ain[o][k] x[row][k]) for the n_rows = n_obs*chunk action
+// tokens.  One thread per output: the token's x row (A <= 64 floats) sits in shared memory, the
+// weight row is read with 16-byte loads.
+__global__ void __launch_bounds__(256) action_in_kernel(const float *__restrict__ x,
                                                         const __nv_bfloat16 *__restrict__ w_ain,
-                                                        const float *__restrict__ b_ain,
-                                                        const __nv_bfloat16 *__restrict__ w_sp,
-                                                        const float *__restrict__ b_sp, __nv_bfloat16 *__restrict__ a,
-                                                        float *__restrict__ h, __nv_bfloat16 *__restrict__ hb, int H,
-                                                        int A, int sd, int chunk, int S) {
-    extern __shared__ float sx[];  // [chunk][A] then [sd]
-    const int obs = blockIdx.x;
-    for (int i = threadIdx.x; i < chunk * A; i += blockDim.x) sx[i] = x[(size_t)obs * chunk * A + i];
-    if (w_sp)
-        for (int i = threadIdx.x; i < sd; i += blockDim.x) sx[chunk * A + i] = state[(size_t)obs * sd + i];
+                                                        const float *__restrict__ b_ain, __nv_bfloat16 *__restrict__ a,
+                                                        int H, int A) {
+    __shared__ float sx[64];
+    const int row = blockIdx.x;
+    if (threadIdx.x < A) sx[threadIdx.x] = x[(size_t)row * A + threadIdx.x];
     __syncthreads();
-    for (int o = threadIdx.x; o < H; o += blockDim.x) {
+    for (int o = blockIdx.y * blockDim.x + threadIdx.x; o < H; o += gridDim.y * blockDim.x) {
         const __nv_bfloat16 *wr = w_ain + (size_t)o * A;
-        const float b = b_ain ? b_ain[o] : 0.0f;
-        for (int t = 0; t < chunk; ++t) {
-            float acc = 0.0f;
-            for (int k = 0; k < A; ++k) acc = fmaf(__bfloat162float(wr[k]), sx[t * A + k], acc);
-            a[((size_t)obs * chunk + t) * H + o] = __float2bfloat16(acc + b);
+        float acc = b_ain ? b_ain[o] : 0.0f;
+        for (int k = 0; k < A; k += 8) {  // A % 8 == 0
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(wr + k));
+            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h2[e]);
+                acc = fmaf(f.x, sx[k + 2 * e], acc);
+                acc = fmaf(f.y, sx[k + 2 * e + 1], acc);
+            }
         }
-        if (w_sp) {
-            const __nv_bfloat16 *ws = w_sp + (size_t)o * sd;
-            float acc = 0.0f;
-            for (int k = 0; k < sd; ++k) acc = fmaf(__bfloat162float(ws[k]), sx[chunk * A + k], acc);
-            acc += b_sp ? b_sp[o] : 0.0f;
-            h[(size_t)obs * S * H + o] = acc;
-            hb[(size_t)obs * S * H + o] = __float2bfloat16(acc);
-        }
+        a[(size_t)row * H + o] = __float2bfloat16(acc);
     }
 }
 
-// v = W_aout (rms(h_row) * w_out) + b_aout;  x += dt * v.  One warp per action row.
-__global__ void __launch_bounds__(256) head_euler_kernel(const float *__restrict__ h, const float *__restrict__ w_out,
-                                                         const __nv_bfloat16 *__restrict__ w_aout,
-                                                         const float *__restrict__ b_aout, float *__restrict__ x,
-                                                         int n_rows, int H, int A, int chunk, int S, float eps,
-                                                         float dt) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= n_rows) return;
-    const int obs = warp / chunk, t = warp % chunk;
-    const float *hr = h + ((size_t)obs * S + (S - chunk) + t) * H;
-    float ss = 0.0f;
-    for (int k = lane; k < H; k += 32) ss = fmaf(hr[k], hr[k], ss);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-    const float r = rsqrtf(ss / (float)H + eps);
-    for (int o = 0; o < A; ++o) {
-        const __nv_bfloat16 *wr = w_aout + (size_t)o * H;
-        float acc = 0.0f;
-        for (int k = lane; k < H; k += 32) acc = fmaf(__bfloat162float(wr[k]), hr[k] * r * w_out[k], acc);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) {
-            const size_t xi = ((size_t)obs * chunk + t) * A + o;
-            x[xi] += dt * (acc + (b_aout ? b_aout[o] : 0.0f));
-        }
+// pi0: the state token (row 0 of each observation) of h / hb = W_sp state + b_sp.
+__global__ void __launch_bounds__(256) state_token_kernel(const float *__restrict__ state,
+                                                          const __nv_bfloat16 *__restrict__ w_sp,
+                                                          const float *__restrict__ b_sp, float *__restrict__ h,
+                                                          __nv_bfloat16 *__restrict__ hb, int H, int sd, int S) {
+    __shared__ float ss[64];
+    const int obs = blockIdx.x;
+    if (threadIdx.x < sd) ss[threadIdx.x] = state[(size_t)obs * sd + threadIdx.x];
+    __syncthreads();
+    for (int o = threadIdx.x; o < H; o += blockDim.x) {
+        const __nv_bfloat16 *wr = w_sp + (size_t)o * sd;
+        float acc = b_sp ? b_sp[o] : 0.0f;
+        for (int k = 0; k < sd; ++k) acc = fmaf(__bfloat162float(wr[k]), ss[k], acc);
+        h[(size_t)obs * S * H + o] = acc;
+        hb[(size_t)obs * S * H + o] = __float2bfloat16(acc);
     }
+}
+
+// x[obs][t][a] += dt * v[obs*S + (S - chunk) + t][a]   (v from the head GEMM, row stride A)
+__global__ void euler_kernel(float *__restrict__ x, const float *__restrict__ v, int n, int A, int chunk, int S,
+                             float dt) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int a = i % A, row = i / A;
+    const int obs = row / chunk, t = row % chunk;
+    x[i] += dt * v[((size_t)obs * S + (S - chunk) + t) * A + a];
 }
 
 // ------------------------------------------------------------------------ engine --
@@ -146,7 +140,7 @@ struct vlab200_engine {
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
     vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
     // workspace
-    vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage;
+    vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage, vbuf;
     int rope_pos0 = -1;
 };
 
@@ -225,8 +219,9 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
     VB_CUDA(cudaGetLastError());
     if ((rc = copy_dev(e->w_at2, w->w_at2, (size_t)H * H * 2))) return rc;
     if ((rc = copy_dev(e->b_at2, w->b_at2, (size_t)H * 4))) return rc;
-    if ((rc = copy_dev(e->out_norm, w->out_norm, (size_t)H * 4))) return rc;
-    if ((rc = copy_dev(e->w_aout, w->w_aout, (size_t)A * H * 2))) return rc;
+    // the output norm weight is folded into the action head like the layer norms into their projections
+    if ((rc = e->w_aout.alloc((size_t)A * H * 2))) return rc;
+    if ((rc = fold_rows(w->w_aout, w->out_norm, e->w_aout.p, A, H, 1, 0))) return rc;
     if ((rc = copy_dev(e->b_aout, w->b_aout, (size_t)A * 4))) return rc;
     // workspace
     const size_t B = e->max_obs, M = B * e->S, Mc = B * c.chunk;
@@ -240,7 +235,8 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
         (rc = e->rope_self.alloc((size_t)2 * e->S * (hd / 2) * 4)) ||
         (rc = e->rope_cross.alloc((size_t)2 * e->S * (hd / 2) * 4)) ||
         (rc = e->tmp_bf.alloc((size_t)2 * B * e->P * kvf * 2)) || (rc = e->x_stage.alloc(Mc * A * 4)) ||
-        (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)))
+        (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)) ||
+        (rc = e->vbuf.alloc(M * A * 4)))
         return rc;
     VB_CUDA(cudaMemset(e->h.p, 0, M * H * 4));
     VB_CUDA(cudaMemset(e->hb.p, 0, M * H * 2));
@@ -270,7 +266,7 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
     if (!cfg || !w || max_obs <= 0 || prefix_len <= 0) return nullptr;
     const vlab200_policy_config &c = *cfg;
     if (c.n_layers <= 0 || c.H <= 0 || c.n_q <= 0 || c.n_kv <= 0 || c.n_q % c.n_kv || c.inter <= 0 || c.chunk <= 0 ||
-        c.action_dim <= 0 || c.action_dim > 64 || c.steps <= 0 || (c.model != 0 && c.model != 1)) {
+        c.action_dim <= 0 || c.action_dim > 64 || c.action_dim % 8 || c.state_dim > 64 || c.steps <= 0 || (c.model != 0 && c.model != 1)) {
         vb::set_last_error("vlab200_engine_create: bad configuration");
         return nullptr;
     }
@@ -345,10 +341,11 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     vlab200_kv_store st = vb::engine_store(e, e->max_obs);
     const float dt = -1.0f / (float)c.steps;
     for (int step = 0; step < c.steps; ++step) {
-        vb::suffix_in_kernel<<<n_obs, 256, (size_t)(chunk * A + c.state_dim) * 4, cs>>>(
-            e->x.as<float>(), state, e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(),
-            c.model == 0 ? e->w_sp.as<__nv_bfloat16>() : nullptr, e->b_sp.as<float>(), e->a.as<__nv_bfloat16>(),
-            e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, A, c.state_dim, chunk, S);
+        vb::action_in_kernel<<<dim3(Mc, (H + 1023) / 1024), 256, 0, cs>>>(e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(),
+                                                                          e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), H, A);
+        if (c.model == 0)
+            vb::state_token_kernel<<<n_obs, 256, 0, cs>>>(state, e->w_sp.as<__nv_bfloat16>(), e->b_sp.as<float>(),
+                                                          e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, c.state_dim, S);
         VB_CUDA(cudaGetLastError());
         {
             vb::GemmParams p{};
@@ -400,10 +397,14 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
                 if ((rc = vb::dense_gemm(e->g.p, I, e->wdown[l].p, p, cs))) return rc;
             }
         }
-        vb::head_euler_kernel<<<(Mc * 32 + 255) / 256, 256, 0, cs>>>(e->h.as<float>(), e->out_norm.as<float>(),
-                                                                    e->w_aout.as<__nv_bfloat16>(), e->b_aout.as<float>(),
-                                                                    e->x.as<float>(), Mc, H, A, chunk, S, c.rms_eps, dt);
-        VB_CUDA(cudaGetLastError());
+        {   // v = W_aout (rms(h) * w_out) + b_aout over every suffix row, then the Euler update on the action rows
+            vb::GemmParams p{};
+            p.M = M; p.N = A; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 1; p.eps = c.rms_eps;
+            p.out_f32 = e->vbuf.as<float>(); p.bias = e->b_aout.as<float>(); p.ld_out = A;
+            if ((rc = vb::dense_gemm(e->hb.p, H, e->w_aout.p, p, cs))) return rc;
+            vb::euler_kernel<<<(Mc * A + 255) / 256, 256, 0, cs>>>(e->x.as<float>(), e->vbuf.as<float>(), Mc * A, A, chunk, S, dt);
+            VB_CUDA(cudaGetLastError());
+        }
     }
     VB_CUDA(cudaMemcpyAsync(x_out, e->x.p, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
     return VLAB200_OK;
