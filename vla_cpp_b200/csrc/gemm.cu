@@ -27,8 +27,17 @@
 
 namespace vb {
 
-constexpr int G_BM = 128, G_BN = 256, G_BK = 64, G_STAGES = 4, G_THREADS = 448;
-constexpr int G_A_BYTES = G_BM * 128, G_B_BYTES = G_BN * 128, G_STAGE_BYTES = G_A_BYTES + G_B_BYTES;
+constexpr int G_BM = 128, G_BK = 64, G_THREADS = 448;
+constexpr int G_A_BYTES = G_BM * 128;
+// BN = 256 minimises operand traffic per flop; BN = 128 doubles the number of tiles when the
+// problem has too few of them to occupy the SMs.
+template <int BN>
+struct GemmCfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024 + 1024;  // + barriers, statistics, alignment
+};
 
 __device__ __forceinline__ float act_apply(float x, int act) {
     if (act == ACT_SILU) return x / (1.0f + __expf(-x));
@@ -40,17 +49,20 @@ __device__ __forceinline__ float act_apply(float x, int act) {
     return x;
 }
 
+template <int G_BN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
                   const GemmParams p, int tiles_m, int tiles_n) {
+    constexpr int G_STAGES = GemmCfg<G_BN>::STAGES, G_B_BYTES = GemmCfg<G_BN>::B_BYTES, G_STAGE_BYTES = GemmCfg<G_BN>::STAGE_BYTES;
+    (void)G_B_BYTES;
     extern __shared__ uint8_t g_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(g_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
     uint8_t *aux = smem + G_STAGES * G_STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(aux);
-    uint64_t *full = bars, *empty = bars + 4;
-    uint64_t *accum_full = bars + 8, *accum_empty = bars + 10, *stats_full = bars + 12, *stats_empty = bars + 14;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *full = bars, *empty = bars + 8;
+    uint64_t *accum_full = bars + 16, *accum_empty = bars + 18, *stats_full = bars + 20, *stats_empty = bars + 22;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *stats = reinterpret_cast<float *>(aux + 256);  // [2][128]
 
@@ -75,7 +87,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
+        tmem_alloc(tmem_slot, 2 * G_BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -167,7 +179,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
             }
         }
     } else {
-        // ---- epilogue warps 2..5 (group 0: columns [0,128)) and 10..13 (group 1: [128,256)) ----
+        // ---- epilogue warps 2..5 (group 0: first half of the tile's columns) and 10..13 (group 1: second half) ----
         const int qtr = warp & 3;
         const int grp = warp >= 10 ? 1 : 0;
         const int row = qtr * 32 + lane;
@@ -186,7 +198,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
             const uint32_t lane_addr = tmem_base + buf * G_BN + ((uint32_t)(qtr * 32) << 16);
             size_t mo = (size_t)m;
             if (p.rows_in > 0 && p.scatter_hd == 0) mo = (size_t)(m / p.rows_in) * p.rows_out + p.row_off + (m % p.rows_in);
-            for (int c = grp * 128; c < grp * 128 + 128; c += 32) {
+            for (int c = grp * (G_BN / 2); c < (grp + 1) * (G_BN / 2); c += 32) {
                 const int n = n0 + c;
                 if (n >= p.N) break;  // N % 8 == 0: a chunk may be cut after a multiple of 8 columns
                 uint32_t v[32];
@@ -265,7 +277,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, 2 * G_BN);
     }
 }
 
@@ -288,24 +300,42 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
     {
         const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
         const uint64_t strides[1] = {(uint64_t)p.K * 2};
-        const uint32_t box[2] = {G_BK, G_BN};
+        const uint32_t box[2] = {G_BK, 256};
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
-    const int smem = G_STAGES * G_STAGE_BYTES + 256 + 1024 + 1024;
-    static bool done = false;
     static int n_sm = 0;
-    if (!done) {
-        VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (!n_sm) {
         int dev = 0;
         VB_CUDA(cudaGetDevice(&dev));
         VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-        done = true;
     }
-    const int tiles_m = (p.M + G_BM - 1) / G_BM, tiles_n = (p.N + G_BN - 1) / G_BN;
-    const int nt = tiles_m * tiles_n;
-    dense_gemm_kernel<<<nt < n_sm ? nt : n_sm, G_THREADS, smem, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+    const int tiles_m = (p.M + G_BM - 1) / G_BM;
+    const bool narrow = tiles_m * ((p.N + 255) / 256) < 2 * n_sm && p.N > 128;
+    if (narrow) {
+        const uint32_t box[2] = {G_BK, 128};
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
+        const uint64_t strides[1] = {(uint64_t)p.K * 2};
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        static bool done = false;
+        if (!done) {
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<128>::SMEM));
+            done = true;
+        }
+        const int tiles_n = (p.N + 127) / 128, nt = tiles_m * tiles_n;
+        dense_gemm_kernel<128><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<128>::SMEM, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+    } else {
+        static bool done = false;
+        if (!done) {
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256>::SMEM));
+            done = true;
+        }
+        const int tiles_n = (p.N + 255) / 256, nt = tiles_m * tiles_n;
+        dense_gemm_kernel<256><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<256>::SMEM, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+    }
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
