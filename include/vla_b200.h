@@ -244,6 +244,69 @@ VLAB200_API int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_lad
                                            int32_t *acc_out, const float *s, const float *ws, int32_t ws_num,
                                            int32_t M, int32_t N, int32_t K, int32_t path, void *stream);
 
+/* ---- BitVLA language-model block: the callers either side of the ternary linear ----------
+ * One BitNet transformer layer = RMSNorm -> act-quant -> ternary q/k/v -> NeoX RoPE ->
+ * bidirectional GQA attention -> sub-norm -> act-quant -> ternary o -> residual -> RMSNorm ->
+ * act-quant -> ternary gate_up -> relu(gate)^2 * up -> sub-norm -> act-quant -> ternary down ->
+ * residual, every intermediate rounded to bf16 where the reference stores bf16.
+ * Same life cycle and argument meaning as bitvla_lm_cuda_init / _set_layer / _set_output_norm /
+ * _forward / _free (src/kernels/bitvla/bitvla_lm_cuda.cu:314-393,668-725, layer body
+ * bitvla_lm_cuda.cu:395-525); the layer struct has the field order of bitvla_lm_layer_cuda
+ * (src/kernels/bitvla/bitvla_lm_cuda.h:204-225) so a pointer to one can be passed as is.
+ * Differences: `max_batch` / `n_seq` run several sequences of equal length in one call (rows
+ * [i*seq, (i+1)*seq) of d_in / d_out belong to sequence i, attention never crosses sequences);
+ * set_layer copies the q, k, v packs into one fused matrix (device memory is allocated in init
+ * and set_layer only, never in forward); attention keeps scores in float on chip instead of
+ * rounding them to bf16 in HBM.  gate_up_ws holds two scales (gate rows, up rows), the other
+ * *_ws one.  Needs hidden, n_q*head_dim, ffn multiples of 128 and head_dim in {64,128,256}. */
+typedef struct {
+    const void *attn_norm_w;     /* bf16 [hidden] */
+    const void *attn_sub_norm_w; /* bf16 [n_q*head_dim] */
+    const void *ffn_norm_w;      /* bf16 [hidden] */
+    const void *ffn_sub_norm_w;  /* bf16 [ffn] */
+    const void *q_packed;        /* ladder pack [n_q*head_dim][hidden] */
+    const float *q_ws;
+    const void *k_packed;        /* [n_kv*head_dim][hidden] */
+    const float *k_ws;
+    const void *v_packed;
+    const float *v_ws;
+    const void *o_packed;        /* [hidden][n_q*head_dim] */
+    const float *o_ws;
+    const void *gate_up_packed;  /* [2*ffn][hidden], gate rows then up rows */
+    const float *gate_up_ws;     /* 2 floats */
+    const void *down_packed;     /* [hidden][ffn] */
+    const float *down_ws;
+} vlab200_bitvla_lm_layer;
+
+typedef struct vlab200_bitvla_lm vlab200_bitvla_lm;
+
+/* The fused element-wise stage between two ternary linears, one pass over each token row:
+ *   mode 0: x = x_bf16[m][k]
+ *   mode 1: x = bf16(x_bf16[m][k] + add_bf16[m][k]), also written back to x_bf16 (residual add)
+ *   mode 2: x = bf16(relu(g)^2 * u), g = x_bf16[m][k], u = x_bf16[m][K + k] (rows of 2K: gate | up)
+ *   y = bf16(x * rsqrt(mean_k x^2 + eps) * w_bf16[k])
+ *   y_bf16 != NULL: y is stored (bf16 [M][K]) and nothing is quantised; otherwise
+ *   scales[m] = 127 / max(max_k |y|, 1e-5), q[m][k] = clamp(rne(y * scales[m]), -128, 127).
+ * Replaces bitvla_add_bf16 / gate_up_fused_sqrelu_mul_bf16 + bitvla_rmsnorm_bf16 + bitvla_act_quant_cuda
+ * (src/kernels/bitvla/bitvla_lm_cuda.cu:37-75,527-549; src/kernels/bitvla/bitnet_kernels.h:465-521).
+ * K even, K <= 51200. */
+VLAB200_API int32_t vlab200_bitvla_norm_quant(void *x_bf16, const void *add_bf16, const void *w_bf16, float eps,
+                                              int32_t M, int32_t K, int32_t mode, int8_t *q, float *scales,
+                                              void *y_bf16, void *stream);
+
+/* NULL on failure (vlab200_last_error() says why). */
+VLAB200_API vlab200_bitvla_lm *vlab200_bitvla_lm_init(int32_t hidden, int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                      int32_t ffn, int32_t n_layers, float rope_base,
+                                                      float rms_eps, int32_t max_seq, int32_t max_batch);
+VLAB200_API void vlab200_bitvla_lm_free(vlab200_bitvla_lm *ctx);
+/* Weight pointers stay owned by the caller and must outlive the context (q/k/v packs are copied). */
+VLAB200_API int32_t vlab200_bitvla_lm_set_layer(vlab200_bitvla_lm *ctx, int32_t L,
+                                                const vlab200_bitvla_lm_layer *layer);
+VLAB200_API int32_t vlab200_bitvla_lm_set_output_norm(vlab200_bitvla_lm *ctx, const void *w_bf16);
+/* d_in, d_out: bf16 [n_seq*seq][hidden] device pointers; d_out = output_norm(layers(d_in)). */
+VLAB200_API int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void *d_in, void *d_out, int32_t seq,
+                                              int32_t n_seq, void *stream);
+
 /* The reference's own symbol names and signatures for the three calls above
  * (src/kernels/bitvla/bitnet_kernels.cu:31,76,118), so src/models/bitvla.cpp and
  * src/kernels/bitvla/bitvla_lm_cuda.cu link against this library unchanged.  The bf16

@@ -260,3 +260,78 @@ class DenoiseModel:
         lib().orc_expert_layer(C.byref(self.cfg), C.byref(self.w), l, _p(h), h.shape[0], _p(kp), _p(vp),
                                int(is_self))
         return h
+
+
+# --------------------------------------------------------------- BitVLA LM layer --
+# Composite restatement of run_layer (src/kernels/bitvla/bitvla_lm_cuda.cu:395-525) and
+# bitvla_lm_cuda_forward (:668-725) from the pinned pieces above (act-quant, ladder GEMM,
+# epilogue) plus numpy for the bf16 element-wise kernels.  PARITY UNPINNED as a whole: the
+# reference holds no golden vector for a layer and its CUDA build cannot run here.
+
+def bitvla_rmsnorm_bf16(x, w, eps):
+    """rmsnorm_bf16_kernel (bitvla_lm_cuda.cu:37-75): bf16(x * rsqrt(mean x^2 + eps) * w)."""
+    x = _c(x, np.float32)
+    ss = (x.astype(np.float64) ** 2).sum(-1)
+    scale = (1.0 / np.sqrt(ss / x.shape[-1] + eps)).astype(np.float32)
+    return bf16_round((x * scale[:, None]) * _c(w, np.float32)[None, :])
+
+
+def bitvla_linear(xn, packed, ws, n):
+    """act-quant -> ternary GEMM -> bf16 epilogue (bitvla_lm_cuda.cu:427-436)."""
+    q, s = act_quant(xn)
+    acc = ternary_gemm_i32(q, packed, n)
+    return bf16_bits_to_f32(ternary_epilogue(acc, s, np.atleast_1d(ws)))
+
+
+def bitvla_rope_table(seq, hd, base):
+    """Host loop of bitvla_lm_cuda_init (bitvla_lm_cuda.cu:333-342), float arithmetic."""
+    half = hd // 2
+    k = np.arange(half, dtype=np.float32)
+    freq = (np.float32(1.0) / np.power(np.float32(base), (2 * k) / np.float32(hd))).astype(np.float32)
+    ang = (np.arange(seq, dtype=np.float32)[:, None] * freq[None, :]).astype(np.float32)
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+def bitvla_lm_layer(h, lw, cfg, cos, sin):
+    """h: [seq, hidden] bf16-valued float32 -> same.  lw: dict with the reference's
+    bitvla_lm_layer_cuda fields (norms bf16-valued float32, packs uint8, scales float32)."""
+    n_q, n_kv, hd, ffn, eps = cfg["n_q"], cfg["n_kv"], cfg["head_dim"], cfg["ffn"], cfg["rms_eps"]
+    seq, hidden = h.shape
+    hq, hkv, half = n_q * hd, n_kv * hd, hd // 2
+    hn = bitvla_rmsnorm_bf16(h, lw["attn_norm_w"], eps)
+    q = bitvla_linear(hn, lw["q_packed"], lw["q_ws"], hq).reshape(seq, n_q, hd).transpose(1, 0, 2)
+    k = bitvla_linear(hn, lw["k_packed"], lw["k_ws"], hkv).reshape(seq, n_kv, hd).transpose(1, 0, 2)
+    v = bitvla_linear(hn, lw["v_packed"], lw["v_ws"], hkv).reshape(seq, n_kv, hd).transpose(1, 0, 2)
+
+    def rope(t):  # rope_neox_bf16_kernel (bitvla_lm_cuda.cu:77-99)
+        a, b = t[..., :half], t[..., half:]
+        c, s = cos[None, :seq], sin[None, :seq]
+        return bf16_round(np.concatenate([a * c - b * s, b * c + a * s], -1).astype(np.float32))
+
+    q, k = rope(q), rope(k)
+    att = np.empty((seq, n_q, hd), np.float32)
+    scl = np.float32(1.0 / np.sqrt(np.float32(hd)))
+    for qh in range(n_q):
+        kvh = qh * n_kv // n_q  # repeat_kv_bf16_kernel (bitvla_lm_cuda.cu:181-190)
+        sc = bf16_round((q[qh] @ k[kvh].T).astype(np.float32))  # scores stored bf16 (:452-463)
+        x = sc * scl  # softmax_scaled_bf16_kernel (:101-157)
+        p = np.exp(x - x.max(-1, keepdims=True)).astype(np.float32)
+        p = bf16_round(p * (np.float32(1.0) / p.sum(-1, keepdims=True, dtype=np.float32)))
+        att[:, qh] = bf16_round((p @ v[kvh]).astype(np.float32))
+    an = bitvla_rmsnorm_bf16(att.reshape(seq, hq), lw["attn_sub_norm_w"], eps)
+    h = bf16_round(h + bitvla_linear(an, lw["o_packed"], lw["o_ws"], hidden))
+    hn = bitvla_rmsnorm_bf16(h, lw["ffn_norm_w"], eps)
+    gu = bitvla_linear(hn, lw["gate_up_packed"], lw["gate_up_ws"], 2 * ffn)
+    g, u = np.maximum(gu[:, :ffn], 0), gu[:, ffn:]
+    t = bf16_round((g * g * u).astype(np.float32))  # gate_up_fused_sqrelu_mul_bf16_kernel (:527-542)
+    tn = bitvla_rmsnorm_bf16(t, lw["ffn_sub_norm_w"], eps)
+    return bf16_round(h + bitvla_linear(tn, lw["down_packed"], lw["down_ws"], hidden))
+
+
+def bitvla_lm_forward(x, layers, output_norm, cfg):
+    """bitvla_lm_cuda_forward (bitvla_lm_cuda.cu:668-725) for one sequence x [seq, hidden]."""
+    cos, sin = bitvla_rope_table(x.shape[0], cfg["head_dim"], cfg["rope_base"])
+    h = bf16_round(x)
+    for lw in layers:
+        h = bitvla_lm_layer(h, lw, cfg, cos, sin)
+    return bitvla_rmsnorm_bf16(h, output_norm, cfg["rms_eps"])

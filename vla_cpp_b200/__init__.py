@@ -10,12 +10,14 @@ from .api import (  # noqa: F401
     MASK_CAUSAL,
     MASK_NONE,
     MASK_PI0,
+    BitvlaLM,
     DenoiseAttn,
     KvStore,
     PolicyEngine,
     VlaB200Error,
     act_quant,
     attention,
+    bitvla_norm_quant,
     device_status,
     fold_norm_weight,
     lib,

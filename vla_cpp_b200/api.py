@@ -38,6 +38,9 @@ def lib():
         L.vlab200_kv_store_bytes.restype = C.c_int64
         L.vlab200_engine_create.restype = C.c_void_p
         L.vlab200_engine_free.restype = None
+        L.vlab200_bitvla_lm_init.restype = C.c_void_p
+        L.vlab200_bitvla_lm_init.argtypes = [C.c_int32] * 6 + [C.c_float, C.c_float, C.c_int32, C.c_int32]
+        L.vlab200_bitvla_lm_free.restype = None
         _LIB = L
     return _LIB
 
@@ -52,6 +55,8 @@ EXPORTS = [
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
     "vlab200_engine_denoise_host",
     "vlab200_act_quant", "vlab200_ternary_linear",
+    "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
+    "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
 
@@ -341,3 +346,81 @@ class PolicyEngine:
             C.c_void_p(x0_host.data_ptr()), C.c_void_p(out_host.data_ptr()), pos_base, _stream()),
             "vlab200_engine_denoise_host")
         return out_host
+
+
+NQ_PLAIN, NQ_ADD, NQ_GATE_UP = 0, 1, 2
+
+
+def bitvla_norm_quant(x, w, eps, mode=NQ_PLAIN, add=None, quantise=True):
+    """x: cuda bf16 [M, K] (mode 2: [M, 2K]) -> (int8 [M, K], float32 [M]) or, with quantise=False, bf16 [M, K].
+    mode 1 also replaces x by x + add."""
+    import torch
+
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and w.dtype == torch.bfloat16
+    m, k = x.shape[0], w.shape[0]
+    assert x.shape[1] == (2 * k if mode == NQ_GATE_UP else k)
+    if quantise:
+        q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+        s = torch.empty((m,), dtype=torch.float32, device=x.device)
+        y = None
+    else:
+        q = s = None
+        y = torch.empty((m, k), dtype=torch.bfloat16, device=x.device)
+    _check(lib().vlab200_bitvla_norm_quant(_ptr(x), _ptr(add), _ptr(w), C.c_float(eps), m, k, mode, _ptr(q), _ptr(s),
+                                           _ptr(y), _stream()), "vlab200_bitvla_norm_quant")
+    return (q, s) if quantise else y
+
+
+_LM_FIELDS = ["attn_norm_w", "attn_sub_norm_w", "ffn_norm_w", "ffn_sub_norm_w", "q_packed", "q_ws", "k_packed",
+              "k_ws", "v_packed", "v_ws", "o_packed", "o_ws", "gate_up_packed", "gate_up_ws", "down_packed",
+              "down_ws"]
+
+
+class _BitvlaLmLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in _LM_FIELDS]
+
+
+class BitvlaLM:
+    """BitVLA language-model stack (BitNet layers on the ternary kernels).
+
+    Mirrors bitvla_lm_cuda_init / set_layer / set_output_norm / forward of the reference
+    (src/kernels/bitvla/bitvla_lm_cuda.cu:314-393,668-725).  layers: list of dicts of cuda tensors with
+    the vlab200_bitvla_lm_layer field names (norm weights bf16, packs uint8, scales float32)."""
+
+    def __init__(self, hidden, n_q, n_kv, head_dim, ffn, layers, output_norm, rope_base=10000.0, rms_eps=1e-5,
+                 max_seq=512, max_batch=1):
+        import torch
+
+        self.hidden = hidden
+        self.h = lib().vlab200_bitvla_lm_init(hidden, n_q, n_kv, head_dim, ffn, len(layers), rope_base, rms_eps,
+                                              max_seq, max_batch)
+        if not self.h:
+            raise VlaB200Error(ERR_CUDA, "vlab200_bitvla_lm_init")
+        self._keep = [layers, output_norm]
+        for i, lw in enumerate(layers):
+            st = _BitvlaLmLayer()
+            for n in _LM_FIELDS:
+                t = lw[n]
+                want = torch.float32 if n.endswith("_ws") else (torch.uint8 if n.endswith("_packed") else torch.bfloat16)
+                assert t.is_cuda and t.is_contiguous() and t.dtype == want, n
+                setattr(st, n, t.data_ptr())
+            _check(lib().vlab200_bitvla_lm_set_layer(C.c_void_p(self.h), i, C.byref(st)), "vlab200_bitvla_lm_set_layer")
+        assert output_norm.is_cuda and output_norm.dtype == torch.bfloat16
+        _check(lib().vlab200_bitvla_lm_set_output_norm(C.c_void_p(self.h), _ptr(output_norm)),
+               "vlab200_bitvla_lm_set_output_norm")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().vlab200_bitvla_lm_free(C.c_void_p(self.h))
+            self.h = None
+
+    def forward(self, x, out=None):
+        """x: cuda bf16 [n_seq, seq, hidden] (or [seq, hidden]) -> same shape."""
+        import torch
+
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] == self.hidden
+        n_seq, seq = (1, x.shape[0]) if x.dim() == 2 else (x.shape[0], x.shape[1])
+        out = torch.empty_like(x) if out is None else out
+        _check(lib().vlab200_bitvla_lm_forward(C.c_void_p(self.h), _ptr(x), _ptr(out), seq, n_seq, _stream()),
+               "vlab200_bitvla_lm_forward")
+        return out

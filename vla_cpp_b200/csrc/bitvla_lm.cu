@@ -1,0 +1,384 @@
+// BitVLA language-model block on the ternary kernels: the callers either side of
+// vlab200_ternary_linear, so that a whole BitNet transformer layer runs on this library.
+//
+// One layer of the reference (run_layer, src/kernels/bitvla/bitvla_lm_cuda.cu:395-525) is 25
+// launches: rmsnorm, act-quant, three ternary GEMMs, three head-split transposes, two RoPE
+// passes, two GQA repeats, cuBLAS QK^T with the score matrix in HBM, softmax, cuBLAS PV,
+// merge transpose, rmsnorm, act-quant, GEMM, add, rmsnorm, act-quant, GEMM, gate*up,
+// rmsnorm, act-quant, GEMM, add.  Here it is 9:
+//
+//   norm_quant_kernel   [residual add ->] RMSNorm (bf16 rounding as the reference) -> per-token
+//                       absmax int8; one pass over the row, nothing but int8 + scale written
+//   ternary GEMM        q, k, v as ONE matrix (rows concatenated at set_layer, one weight scale
+//                       per 'group' rows through ws_num)
+//   rope_split_kernel   NeoX RoPE on q and k, head split, K / V rows into the attention pages
+//   attention           streaming tcgen05 kernel, no score matrix, no repeated K/V
+//   norm_quant_kernel   attn sub-norm -> int8
+//   ternary GEMM        o
+//   norm_quant_kernel   h += o; ffn norm -> int8
+//   ternary GEMM        gate_up
+//   norm_quant_kernel   relu(gate)^2 * up -> ffn sub-norm -> int8
+//   ternary GEMM        down   (its residual add is fused into the next norm_quant_kernel)
+//
+// Sequences of equal length can be batched (n_seq); the reference runs one per call.
+#include <cuda_bf16.h>
+
+#include <cmath>
+#include <new>
+#include <vector>
+
+#include "host_common.h"
+
+namespace vb {
+
+enum { NQ_PLAIN = 0, NQ_ADD = 1, NQ_GATE_UP = 2 };
+
+__device__ __forceinline__ float block_sum_256(float v, float *red) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();  // red may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) t += red[i];
+    return t;
+}
+
+__device__ __forceinline__ float block_max_256(float v, float *red) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) t = fmaxf(t, red[i]);
+    return t;
+}
+
+// One CTA per token row.  MODE selects where the row comes from:
+//   NQ_PLAIN    x = in[m][k]
+//   NQ_ADD      x = bf16(in[m][k] + add[m][k]), written back to in (bitvla_add_bf16, reference
+//               bitvla_lm_cuda.cu:497,522)
+//   NQ_GATE_UP  x = bf16(relu(g)^2 * u), g = in[m][k], u = in[m][K + k] (row stride 2K;
+//               gate_up_fused_sqrelu_mul_bf16_kernel, bitvla_lm_cuda.cu:527-542)
+// then y = bf16(x * rsqrt(mean x^2 + eps) * w[k]) (rmsnorm_bf16_kernel, bitvla_lm_cuda.cu:37-75) and
+// either y is stored (out_bf != nullptr) or quantised: s = 127 / max(max|y|, 1e-5),
+// q = clamp(rne(y * s), -128, 127) (act_quant_kernel, src/kernels/bitvla/bitnet_kernels.h:465-521).
+// The row lives in shared memory as float between the passes (K * 4 bytes).
+template <int MODE>
+__global__ void __launch_bounds__(256) norm_quant_kernel(__nv_bfloat16 *__restrict__ in,
+                                                         const __nv_bfloat16 *__restrict__ add,
+                                                         const __nv_bfloat16 *__restrict__ w, float eps, int K,
+                                                         int8_t *__restrict__ q_out, float *__restrict__ s_out,
+                                                         __nv_bfloat16 *__restrict__ out_bf) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const int K2 = K >> 1;
+    const size_t ld = MODE == NQ_GATE_UP ? 2 * (size_t)K : (size_t)K;
+    __nv_bfloat162 *src = reinterpret_cast<__nv_bfloat162 *>(in + m * ld);
+    float ss = 0.f;
+    for (int i = tid; i < K2; i += 256) {
+        float2 x = __bfloat1622float2(src[i]);
+        if (MODE == NQ_ADD) {
+            const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162 *>(add + m * ld)[i]);
+            const __nv_bfloat162 r = __floats2bfloat162_rn(x.x + a.x, x.y + a.y);
+            src[i] = r;
+            x = __bfloat1622float2(r);
+        } else if (MODE == NQ_GATE_UP) {
+            const float2 u = __bfloat1622float2(src[K2 + i]);
+            const float g0 = fmaxf(x.x, 0.f), g1 = fmaxf(x.y, 0.f);
+            x = __bfloat1622float2(__floats2bfloat162_rn(g0 * g0 * u.x, g1 * g1 * u.y));
+        }
+        row[2 * i] = x.x;
+        row[2 * i + 1] = x.y;
+        ss += x.x * x.x + x.y * x.y;
+    }
+    ss = block_sum_256(ss, red);
+    const float scale = rsqrtf(ss / (float)K + eps);
+    const __nv_bfloat162 *w2 = reinterpret_cast<const __nv_bfloat162 *>(w);
+    float amax = 0.f;
+    for (int i = tid; i < K2; i += 256) {
+        const float2 wv = __bfloat1622float2(w2[i]);
+        const __nv_bfloat162 y = __floats2bfloat162_rn(row[2 * i] * scale * wv.x, row[2 * i + 1] * scale * wv.y);
+        if (out_bf) reinterpret_cast<__nv_bfloat162 *>(out_bf + (size_t)m * K)[i] = y;
+        const float2 yf = __bfloat1622float2(y);
+        row[2 * i] = yf.x;
+        row[2 * i + 1] = yf.y;
+        amax = fmaxf(amax, fmaxf(fabsf(yf.x), fabsf(yf.y)));
+    }
+    if (out_bf) return;
+    amax = block_max_256(amax, red);
+    amax = amax < 1e-5f ? 1e-5f : amax;
+    const float qs = __fdiv_rn(127.0f, amax);
+    if (tid == 0) s_out[m] = qs;
+    char2 *dst = reinterpret_cast<char2 *>(q_out + (size_t)m * K);
+    for (int i = tid; i < K2; i += 256) {  // each thread re-reads the elements it wrote itself
+        const float a = fminf(fmaxf(rintf(row[2 * i] * qs), -128.f), 127.f);
+        const float b = fminf(fmaxf(rintf(row[2 * i + 1] * qs), -128.f), 127.f);
+        dst[i] = make_char2((signed char)(int)a, (signed char)(int)b);
+    }
+}
+
+// qkv: bf16 [M][(n_q + 2 n_kv) hd] (q heads, k heads, v heads) -> q_out [n_seq][n_q][seq][hd]
+// rotated, K page rows rotated, V page rows copied.  Pages: [n_seq][n_kv][cap][hd].
+// The rotation is computed in float on bf16 inputs and rounded once, as rope_neox_bf16_kernel
+// (bitvla_lm_cuda.cu:77-99) does after the head split (bitvla_lm_cuda.cu:441-446).
+__global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__restrict__ qkv,
+                                                         const float *__restrict__ cos_t,
+                                                         const float *__restrict__ sin_t,
+                                                         __nv_bfloat16 *__restrict__ q_out,
+                                                         __nv_bfloat16 *__restrict__ k_pages,
+                                                         __nv_bfloat16 *__restrict__ v_pages, int seq, int n_q,
+                                                         int n_kv, int hd, int cap) {
+    const int m = blockIdx.x;
+    const int sq = m / seq, s = m % seq;
+    const int half = hd >> 1;
+    const int n_heads = n_q + 2 * n_kv;
+    const __nv_bfloat16 *src = qkv + (size_t)m * n_heads * hd;
+    for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+        const int head = i / half, k = i % half;
+        const __nv_bfloat16 *hp = src + (size_t)head * hd;
+        const float a = __bfloat162float(hp[k]), b = __bfloat162float(hp[k + half]);
+        __nv_bfloat16 *dst;
+        float lo = a, hi = b;
+        if (head < n_q + n_kv) {
+            const float c = cos_t[(size_t)s * half + k], sn = sin_t[(size_t)s * half + k];
+            lo = a * c - b * sn;
+            hi = b * c + a * sn;
+            dst = head < n_q ? q_out + (((size_t)sq * n_q + head) * seq + s) * hd
+                             : k_pages + (((size_t)sq * n_kv + (head - n_q)) * cap + s) * hd;
+        } else {
+            dst = v_pages + (((size_t)sq * n_kv + (head - n_q - n_kv)) * cap + s) * hd;
+        }
+        dst[k] = __float2bfloat16(lo);
+        dst[k + half] = __float2bfloat16(hi);
+    }
+}
+
+static int gcd_int(int a, int b) {
+    while (b) {
+        const int t = a % b;
+        a = b;
+        b = t;
+    }
+    return a;
+}
+
+struct LmLayer {
+    vlab200_bitvla_lm_layer w{};
+    DevBuf qkv_packed, qkv_ws;
+    bool set = false;
+};
+
+}  // namespace vb
+
+struct vlab200_bitvla_lm {
+    int hidden, n_q, n_kv, hd, ffn, n_layers, max_seq, max_batch, hq, hkv, qkv_group, qkv_ws_num;
+    float rope_base, eps;
+    const void *output_norm = nullptr;
+    std::vector<vb::LmLayer> layers;
+    vb::DevBuf cos_t, sin_t, h, a8, s, qkv, q, k_pages, v_pages, att, proj, gate_up;
+};
+
+using vb::DevBuf;
+
+extern "C" {
+
+vlab200_bitvla_lm *vlab200_bitvla_lm_init(int32_t hidden, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t ffn,
+                                          int32_t n_layers, float rope_base, float rms_eps, int32_t max_seq,
+                                          int32_t max_batch) {
+    if (hidden <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || ffn <= 0 || n_layers <= 0 || max_seq <= 0 ||
+        max_batch <= 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) {
+        vb::set_last_error("vlab200_bitvla_lm_init: bad dimensions");
+        return nullptr;
+    }
+    const int hq = n_q * head_dim, hkv = n_kv * head_dim;
+    if (hidden % 128 || hq % 128 || ffn % 128 || hkv % 32) {
+        vb::set_last_error("vlab200_bitvla_lm_init: hidden, n_q*head_dim and ffn must be multiples of 128 (K of the "
+                           "ladder pack), n_kv*head_dim of 32");
+        return nullptr;
+    }
+    auto *c = new (std::nothrow) vlab200_bitvla_lm();
+    if (!c) return nullptr;
+    c->hidden = hidden; c->n_q = n_q; c->n_kv = n_kv; c->hd = head_dim; c->ffn = ffn; c->n_layers = n_layers;
+    c->max_seq = max_seq; c->max_batch = max_batch; c->hq = hq; c->hkv = hkv;
+    c->rope_base = rope_base; c->eps = rms_eps;
+    c->qkv_group = vb::gcd_int(hq, hkv);
+    c->qkv_ws_num = (hq + 2 * hkv) / c->qkv_group;
+    c->layers.resize(n_layers);
+    const size_t rows = (size_t)max_seq * max_batch;
+    size_t kmax = (size_t)hidden;
+    if ((size_t)ffn > kmax) kmax = ffn;
+    if ((size_t)hq > kmax) kmax = hq;
+    const int64_t page_bytes = vlab200_kv_store_bytes(1, max_batch, n_kv, head_dim, max_seq);
+    int rc = c->cos_t.alloc((size_t)max_seq * head_dim / 2 * 4);
+    if (!rc) rc = c->sin_t.alloc((size_t)max_seq * head_dim / 2 * 4);
+    if (!rc) rc = c->h.alloc(rows * hidden * 2);
+    if (!rc) rc = c->a8.alloc(rows * kmax);
+    if (!rc) rc = c->s.alloc(rows * 4);
+    if (!rc) rc = c->qkv.alloc(rows * (hq + 2 * hkv) * 2);
+    if (!rc) rc = c->q.alloc(rows * hq * 2);
+    if (!rc) rc = c->k_pages.alloc((size_t)page_bytes);
+    if (!rc) rc = c->v_pages.alloc((size_t)page_bytes);
+    if (!rc) rc = c->att.alloc(rows * hq * 2);
+    if (!rc) rc = c->proj.alloc(rows * hidden * 2);
+    if (!rc) rc = c->gate_up.alloc(rows * 2 * ffn * 2);
+    // same table as the reference's host loop (bitvla_lm_cuda.cu:333-342), positions 0 .. max_seq-1
+    if (!rc) rc = vlab200_rope_table(c->cos_t.as<float>(), c->sin_t.as<float>(), 0, max_seq, head_dim, rope_base, nullptr);
+    if (!rc && cudaStreamSynchronize(nullptr) != cudaSuccess) rc = VLAB200_ERR_CUDA;
+    if (rc) {
+        delete c;
+        return nullptr;
+    }
+    return c;
+}
+
+void vlab200_bitvla_lm_free(vlab200_bitvla_lm *ctx) { delete ctx; }
+
+int32_t vlab200_bitvla_lm_set_layer(vlab200_bitvla_lm *ctx, int32_t L, const vlab200_bitvla_lm_layer *layer) {
+    if (!ctx || !layer || L < 0 || L >= ctx->n_layers) return VLAB200_ERR_ARG;
+    const vlab200_bitvla_lm_layer &w = *layer;
+    if (!w.attn_norm_w || !w.attn_sub_norm_w || !w.ffn_norm_w || !w.ffn_sub_norm_w || !w.q_packed || !w.q_ws ||
+        !w.k_packed || !w.k_ws || !w.v_packed || !w.v_ws || !w.o_packed || !w.o_ws || !w.gate_up_packed ||
+        !w.gate_up_ws || !w.down_packed || !w.down_ws) {
+        vb::set_last_error("vlab200_bitvla_lm_set_layer: null weight pointer");
+        return VLAB200_ERR_ARG;
+    }
+    vb::LmLayer &l = ctx->layers[L];
+    l.w = w;
+    // q, k, v rows back to back: a ladder pack is a sequence of independent 16-row runs, so the
+    // packed matrices concatenate byte-wise; their scales are repeated once per 'group' rows.
+    const size_t qb = (size_t)ctx->hq * ctx->hidden / 4, kb = (size_t)ctx->hkv * ctx->hidden / 4;
+    if (!l.qkv_packed.p) {
+        int rc = l.qkv_packed.alloc(qb + 2 * kb);
+        if (!rc) rc = l.qkv_ws.alloc((size_t)ctx->qkv_ws_num * 4);
+        if (rc) return rc;
+    }
+    uint8_t *dst = l.qkv_packed.as<uint8_t>();
+    VB_CUDA(cudaMemcpy(dst, w.q_packed, qb, cudaMemcpyDeviceToDevice));
+    VB_CUDA(cudaMemcpy(dst + qb, w.k_packed, kb, cudaMemcpyDeviceToDevice));
+    VB_CUDA(cudaMemcpy(dst + qb + kb, w.v_packed, kb, cudaMemcpyDeviceToDevice));
+    float sc[3];
+    VB_CUDA(cudaMemcpy(&sc[0], w.q_ws, 4, cudaMemcpyDeviceToHost));
+    VB_CUDA(cudaMemcpy(&sc[1], w.k_ws, 4, cudaMemcpyDeviceToHost));
+    VB_CUDA(cudaMemcpy(&sc[2], w.v_ws, 4, cudaMemcpyDeviceToHost));
+    std::vector<float> ws(ctx->qkv_ws_num);
+    const int nq_groups = ctx->hq / ctx->qkv_group, nk_groups = ctx->hkv / ctx->qkv_group;
+    for (int i = 0; i < ctx->qkv_ws_num; ++i) ws[i] = i < nq_groups ? sc[0] : (i < nq_groups + nk_groups ? sc[1] : sc[2]);
+    VB_CUDA(cudaMemcpy(l.qkv_ws.p, ws.data(), ws.size() * 4, cudaMemcpyHostToDevice));
+    l.set = true;
+    return VLAB200_OK;
+}
+
+int32_t vlab200_bitvla_lm_set_output_norm(vlab200_bitvla_lm *ctx, const void *w_bf16) {
+    if (!ctx || !w_bf16) return VLAB200_ERR_ARG;
+    ctx->output_norm = w_bf16;
+    return VLAB200_OK;
+}
+
+}  // extern "C"
+
+namespace vb {
+
+template <int MODE>
+static int launch_norm_quant(void *in, const void *add, const void *w, float eps, int M, int K, int8_t *q, float *s,
+                             void *out_bf, cudaStream_t st) {
+    static bool attr_done = false;
+    const size_t smem = (size_t)K * 4;
+    if (smem > 48 * 1024 && !attr_done) {
+        VB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    norm_quant_kernel<MODE><<<M, 256, smem, st>>>(static_cast<__nv_bfloat16 *>(in),
+                                                  static_cast<const __nv_bfloat16 *>(add),
+                                                  static_cast<const __nv_bfloat16 *>(w), eps, K, q, s,
+                                                  static_cast<__nv_bfloat16 *>(out_bf));
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+}  // namespace vb
+
+extern "C" int32_t vlab200_bitvla_norm_quant(void *x_bf16, const void *add_bf16, const void *w_bf16, float eps,
+                                             int32_t M, int32_t K, int32_t mode, int8_t *q, float *scales,
+                                             void *y_bf16, void *stream) {
+    if (!x_bf16 || !w_bf16 || M < 0 || K <= 0 || K % 2 || (mode == vb::NQ_ADD && !add_bf16) ||
+        (!y_bf16 && (!q || !scales)))
+        return VLAB200_ERR_ARG;
+    if ((size_t)K * 4 > 200 * 1024) {
+        vb::set_last_error("vlab200_bitvla_norm_quant: K=%d exceeds the %d floats a row may hold in shared memory", K,
+                           200 * 1024 / 4);
+        return VLAB200_ERR_UNSUPPORTED;
+    }
+    if (M == 0) return VLAB200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (mode) {
+        case vb::NQ_PLAIN: return vb::launch_norm_quant<vb::NQ_PLAIN>(x_bf16, nullptr, w_bf16, eps, M, K, q, scales, y_bf16, st);
+        case vb::NQ_ADD: return vb::launch_norm_quant<vb::NQ_ADD>(x_bf16, add_bf16, w_bf16, eps, M, K, q, scales, y_bf16, st);
+        case vb::NQ_GATE_UP: return vb::launch_norm_quant<vb::NQ_GATE_UP>(x_bf16, nullptr, w_bf16, eps, M, K, q, scales, y_bf16, st);
+        default: return VLAB200_ERR_ARG;
+    }
+}
+
+extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void *d_in, void *d_out, int32_t seq,
+                                             int32_t n_seq, void *stream) {
+    if (!ctx || !d_in || !d_out) return VLAB200_ERR_ARG;
+    if (seq <= 0 || n_seq <= 0 || seq > ctx->max_seq || n_seq > ctx->max_batch) {
+        vb::set_last_error("vlab200_bitvla_lm_forward: seq=%d n_seq=%d outside max_seq=%d max_batch=%d", seq, n_seq,
+                           ctx->max_seq, ctx->max_batch);
+        return VLAB200_ERR_ARG;
+    }
+    if (!ctx->output_norm) {
+        vb::set_last_error("vlab200_bitvla_lm_forward: output norm not set");
+        return VLAB200_ERR_ARG;
+    }
+    for (const vb::LmLayer &l : ctx->layers)
+        if (!l.set) {
+            vb::set_last_error("vlab200_bitvla_lm_forward: a layer was not set");
+            return VLAB200_ERR_ARG;
+        }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int M = seq * n_seq, H = ctx->hidden, hq = ctx->hq, hkv = ctx->hkv, F = ctx->ffn;
+    int8_t *a8 = ctx->a8.as<int8_t>();
+    float *s = ctx->s.as<float>();
+    VB_CUDA(cudaMemcpyAsync(ctx->h.p, d_in, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, st));
+    const vlab200_kv_store store = {ctx->k_pages.p, ctx->v_pages.p, 1, n_seq, ctx->n_kv, ctx->hd, ctx->max_seq, 0};
+    int rc = VLAB200_OK;
+    for (int L = 0; L < ctx->n_layers && !rc; ++L) {
+        const vb::LmLayer &l = ctx->layers[L];
+        if (L == 0) rc = vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->h.p, nullptr, l.w.attn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
+        else rc = vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, l.w.attn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
+        if (rc) break;
+        rc = vlab200_ternary_linear(a8, l.qkv_packed.as<uint8_t>(), ctx->qkv.p, nullptr, s, l.qkv_ws.as<float>(),
+                                    ctx->qkv_ws_num, M, hq + 2 * hkv, H, 0, st);
+        if (rc) break;
+        vb::rope_split_kernel<<<M, 128, 0, st>>>(ctx->qkv.as<__nv_bfloat16>(), ctx->cos_t.as<float>(),
+                                                 ctx->sin_t.as<float>(), ctx->q.as<__nv_bfloat16>(),
+                                                 ctx->k_pages.as<__nv_bfloat16>(), ctx->v_pages.as<__nv_bfloat16>(),
+                                                 seq, ctx->n_q, ctx->n_kv, ctx->hd, ctx->max_seq);
+        VB_CUDA(cudaGetLastError());
+        rc = vlab200_attention(&store, 0, ctx->q.p, ctx->att.p, seq, ctx->n_q, seq, /*mask_mode=*/0, nullptr, st);
+        if (rc) break;
+        rc = vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->att.p, nullptr, l.w.attn_sub_norm_w, ctx->eps, M, hq, a8, s, nullptr, st);
+        if (rc) break;
+        rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.o_packed), ctx->proj.p, nullptr, s,
+                                    static_cast<const float *>(l.w.o_ws), 1, M, H, hq, 0, st);
+        if (rc) break;
+        rc = vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, l.w.ffn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
+        if (rc) break;
+        rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.gate_up_packed), ctx->gate_up.p, nullptr, s,
+                                    static_cast<const float *>(l.w.gate_up_ws), 2, M, 2 * F, H, 0, st);
+        if (rc) break;
+        rc = vb::launch_norm_quant<vb::NQ_GATE_UP>(ctx->gate_up.p, nullptr, l.w.ffn_sub_norm_w, ctx->eps, M, F, a8, s, nullptr, st);
+        if (rc) break;
+        rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.down_packed), ctx->proj.p, nullptr, s,
+                                    static_cast<const float *>(l.w.down_ws), 1, M, H, F, 0, st);
+    }
+    if (rc) return rc;
+    // h += down of the last layer, then the output norm (bitvla_lm_cuda.cu:718)
+    return vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, ctx->output_norm, ctx->eps, M, H, nullptr, nullptr,
+                                             d_out, st);
+}

@@ -109,29 +109,9 @@ __global__ void euler_kernel(float *__restrict__ x, const float *__restrict__ v,
     x[i] += dt * v[((size_t)obs * S + (S - chunk) + t) * A + a];
 }
 
-// ------------------------------------------------------------------------ engine --
-
-struct DevBuf {
-    void *p = nullptr;
-    DevBuf() = default;
-    DevBuf(const DevBuf &) = delete;
-    DevBuf &operator=(const DevBuf &) = delete;
-    DevBuf(DevBuf &&o) noexcept : p(o.p) { o.p = nullptr; }
-    int alloc(size_t bytes) {
-        cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
-        return e == cudaSuccess ? VLAB200_OK : cuda_fail(e, "cudaMalloc");
-    }
-    ~DevBuf() {
-        if (p) cudaFree(p);
-    }
-    template <typename T>
-    T *as() const {
-        return static_cast<T *>(p);
-    }
-};
-
 }  // namespace vb
 
+// ------------------------------------------------------------------------ engine --
 struct vlab200_engine {
     vlab200_policy_config c;
     int max_obs, P, S, cap, qf, kvf;

@@ -30,4 +30,24 @@ int cuda_fail(cudaError_t e, const char *what);
 int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const uint64_t *dims,
                     const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swz);
 
+// Owning device allocation (move-only).
+struct DevBuf {
+    void *p = nullptr;
+    DevBuf() = default;
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    DevBuf(DevBuf &&o) noexcept : p(o.p) { o.p = nullptr; }
+    int alloc(size_t bytes) {
+        cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+        return e == cudaSuccess ? VLAB200_OK : cuda_fail(e, "cudaMalloc");
+    }
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    template <typename T>
+    T *as() const {
+        return static_cast<T *>(p);
+    }
+};
+
 }  // namespace vb
