@@ -226,6 +226,74 @@ def measure_ternary(torch, vb, dev, steps, warmup):
             "shapes": rows}
 
 
+def measure_bitvla_lm(torch, vb, dev, steps, warmup, n_layers=30):
+    """BitVLA-shaped language-model stack (hidden 2560, 20 q / 5 kv heads of 128, ffn 6912): every layer
+    is norm+quant -> ternary q/k/v -> RoPE -> attention -> norm+quant -> ternary o -> norm+quant ->
+    ternary gate_up -> gate*up+norm+quant -> ternary down.  Random packed weights (520 MB for 30 layers,
+    larger than L2), 300-token sequences, 1 and 16 sequences per call."""
+    hidden, n_q, n_kv, hd, ffn = 2560, 20, 5, 128, 6912
+    hq, hkv = n_q * hd, n_kv * hd
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+
+    def pack(n, k):
+        return torch.randint(0, 256, (n * k // 4,), dtype=torch.uint8, device=dev, generator=g)
+
+    def scale(k, n=1):
+        return (torch.rand((n,), device=dev, generator=g) * 0.4 + 0.8) / (2.0 * k / 3.0) ** 0.5
+
+    def norm(k):
+        return (torch.rand((k,), device=dev, generator=g) * 0.4 + 0.8).bfloat16()
+
+    layers = []
+    for _ in range(n_layers):
+        layers.append({"attn_norm_w": norm(hidden), "attn_sub_norm_w": norm(hq), "ffn_norm_w": norm(hidden),
+                       "ffn_sub_norm_w": norm(ffn), "q_packed": pack(hq, hidden), "q_ws": scale(hidden),
+                       "k_packed": pack(hkv, hidden), "k_ws": scale(hidden), "v_packed": pack(hkv, hidden),
+                       "v_ws": scale(hidden), "o_packed": pack(hidden, hq), "o_ws": scale(hq),
+                       "gate_up_packed": pack(2 * ffn, hidden), "gate_up_ws": scale(hidden, 2),
+                       "down_packed": pack(hidden, ffn), "down_ws": scale(ffn)})
+    seq, max_batch = 300, 16
+    lm = vb.BitvlaLM(hidden, n_q, n_kv, hd, ffn, layers, norm(hidden), rope_base=500000.0, rms_eps=1e-5, max_seq=seq,
+                     max_batch=max_batch)
+    macs_per_token = n_layers * (hidden * (hq + 2 * hkv) + hq * hidden + hidden * 2 * ffn + ffn * hidden)
+    rows = []
+    for n_seq in (1, max_batch):
+        x = torch.randn((n_seq, seq, hidden), device=dev, generator=g).bfloat16()
+        out = torch.empty_like(x)
+        for _ in range(warmup):
+            lm.forward(x, out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            lm.forward(x, out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if not torch.isfinite(out.float()).all():
+            raise SystemExit("non-finite output")
+        rows.append({"n_seq": n_seq, "seq": seq, "ms": ms, "tokens_per_s": n_seq * seq / ms * 1e3,
+                     "ternary_tops": 2.0 * macs_per_token * n_seq * seq / ms / 1e9,
+                     "launches": 1 + 9 * n_layers + 1})
+    if vb.device_status() != 0:
+        raise SystemExit("device status word reports a kernel failure")
+    big = rows[-1]
+    return {"metric": "BitVLA LM stack throughput", "value": big["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": steps, "warmup": warmup, "ms_per_step": big["ms"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x ternary (int32 accumulate), bf16 between the linears",
+            "data": "synthetic",
+            "config": {"workload": f"bitvla_lm: {n_layers} BitNet layers, hidden 2560, 20q/5kv x 128, ffn 6912, "
+                                   f"{max_batch} sequences x {seq} tokens per call",
+                       "l2": "520 MB of packed weights streamed per call (> 126 MB L2)"},
+            "gpu_launches": big["launches"] * steps,
+            "roofline": {"kernel": "ternary_gemm_tc_kernel (whole stack, all kernels' time in the denominator)",
+                         "bound": "tensor", "achieved": big["ternary_tops"], "peak": INT8_PEAK_TOPS, "unit": "TOPS",
+                         "frac": big["ternary_tops"] / INT8_PEAK_TOPS,
+                         "peak_kind": "of measured (cuBLASLt int8, burst)", "traffic": None},
+            "cases": rows}
+
+
 def config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
@@ -265,7 +333,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary"],
+    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary", "bitvla_lm"],
                     help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
                          "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
     ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
@@ -305,6 +373,12 @@ def main():
     if args.workload == "ternary":
         if rank == 0:
             print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3))), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "bitvla_lm":
+        if rank == 0:
+            print(json.dumps(measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3))), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
