@@ -237,7 +237,8 @@ VLAB200_API int32_t vlab200_act_quant(const void *x_bf16, int8_t *q, float *scal
  * reference's 2-bit "ladder" pack (N*K/4 bytes; N % 16 == 0, K % 128 == 0).
  * acc_out (optional, int32 [M][N]) receives the raw accumulators.
  * path: 0 = automatic (M <= 8: HBM-bound GEMV on the packed weights; larger M: tcgen05
- * int8 MMA), 1 = force GEMV, 2 = force tensor-core kernel (needs N % 32 == 0).
+ * int8 MMA, on CTA pairs when N >= 256), 1 = force GEMV, 2 = force the one-CTA-per-tile
+ * tensor-core kernel, 3 = force the CTA-pair kernel (2 and 3 need N % 32 == 0).
  * Replaces bitlinear_int8xint2 / bitlinear_int8xint2_m
  * (src/kernels/bitvla/bitnet_kernels.cu:31-116, kernels bitnet_kernels.h:108-409). */
 VLAB200_API int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_ladder, void *out_bf16,

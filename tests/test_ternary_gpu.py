@@ -62,16 +62,17 @@ def test_gemv_bit_exact(oracle, m, shape):
     assert np.array_equal(out, oracle.ternary_epilogue(ref_acc, s, ws))
 
 
+@pytest.mark.parametrize("path", [2, 3])  # 2: one CTA per tile, 3: CTA pairs (cta_group::2)
 @pytest.mark.parametrize("m", [9, 17, 128, 300, 517])
 @pytest.mark.parametrize("shape", [LM_SHAPES[0], LM_SHAPES[1]])
-def test_gemm_tensor_core_bit_exact_full(oracle, m, shape):
+def test_gemm_tensor_core_bit_exact_full(oracle, m, shape, path):
     require_cuda()
     from vla_cpp_b200 import api
 
     n, k, ws_num = shape
     rng = np.random.default_rng(2000 + m + n)
     a, packed, s, ws = make_case(rng, m, n, k, ws_num, raw_bytes=True)
-    acc, out = run_gpu(api, a, packed, s, ws, n, path=2)
+    acc, out = run_gpu(api, a, packed, s, ws, n, path=path)
     ref_acc = oracle.ternary_gemm_i32(a, packed, n)
     assert np.array_equal(acc, ref_acc)
     assert_bf16_close(out, oracle.ternary_epilogue(ref_acc, s, ws))
@@ -108,9 +109,25 @@ def test_gemv_and_tensor_core_paths_agree(oracle):
     rng = np.random.default_rng(5)
     a, packed, s, ws = make_case(rng, 8, n, k, ws_num, raw_bytes=True)
     acc1, out1 = run_gpu(api, a, packed, s, ws, n, path=1)
+    for path in (2, 3):
+        acc2, out2 = run_gpu(api, a, packed, s, ws, n, path=path)
+        assert np.array_equal(acc1, acc2)
+        assert_bf16_close(out2, out1)
+
+
+@pytest.mark.parametrize("m,n,k,ws_num", [(257, 1536, 384, 2), (1000, 3840, 2560, 6), (4800, 13824, 2560, 2)])
+def test_pair_and_single_cta_kernels_bit_identical(m, n, k, ws_num):
+    """The CTA-pair kernel and the one-CTA kernel run the same arithmetic: equal accumulators and equal
+    bf16 bits on every element, at sizes where the oracle would take minutes."""
+    require_cuda()
+    from vla_cpp_b200 import api
+
+    rng = np.random.default_rng(m + n)
+    a, packed, s, ws = make_case(rng, m, n, k, ws_num, raw_bytes=True)
     acc2, out2 = run_gpu(api, a, packed, s, ws, n, path=2)
-    assert np.array_equal(acc1, acc2)
-    assert_bf16_close(out2, out1)
+    acc3, out3 = run_gpu(api, a, packed, s, ws, n, path=3)
+    assert np.array_equal(acc2, acc3)
+    assert np.array_equal(out2, out3)
 
 
 @pytest.mark.parametrize("m,k", [(1, 2560), (17, 2560), (300, 6912), (5, 1024), (3, 72)])

@@ -117,6 +117,87 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
                  : "memory");
 }
 
+// ---- CTA pairs (cluster of 2, tcgen05 cta_group::2) ----------------------------
+// One MMA spans both CTAs of the pair: M = 256 (each CTA's TMEM holds its own 128 rows of D
+// and its shared memory its own 128 rows of A) and each CTA supplies half of the N rows of B,
+// so an SM stages, and here decodes, only half of the weight tile.  The instruction is issued
+// by one thread of the even-ranked CTA; tcgen05.alloc / dealloc with cta_group::2 are executed
+// by one warp of EACH CTA and return the same TMEM address in both.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of every CTA of the cluster
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_dst, uint32_t ncols) {  // whole warp, both CTAs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {  // whole warp, both CTAs
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives (once the pair's earlier MMAs have finished) on the barrier at this shared-memory
+// offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(cta_mask)
+        : "memory");
+}
+// Arrive on the barrier at the same offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(ra) : "memory");
+}
+// Wait on a local barrier that CTAs of the cluster also arrive on.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *w.abort_flag = 1;
+                atomicCAS(w.status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle.  K-major operand: rows of 128 bytes,
 // 8-row groups of 1024 bytes (sbo = 1024), lbo unused (1).  MN-major operand: 64-element
 // (128-byte) runs along MN, 8 consecutive k per 1024-byte group (sbo), lbo = stride between

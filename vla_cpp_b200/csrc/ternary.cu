@@ -268,7 +268,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
             mbar_init(&empty_a[i], 1);
         }
         for (int i = 0; i < GEMM_SW; ++i) {
-            mbar_init(&full_w[i], 256);
+            mbar_init(&full_w[i], 8);  // one arrival per decode warp
             mbar_init(&empty_w[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -399,7 +399,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
 #endif
                 decode_store(cur, smem + L::W_OFFSET + st * L::W_BYTES);
                 fence_proxy_async_smem();
-                mbar_arrive(&full_w[st]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_w[st]);
                 if (++st == GEMM_SW) { st = 0; ph ^= 1u; }
             }
         }
@@ -490,6 +491,284 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
     }
 }
 
+// ------------------------------------------------------- tcgen05 GEMM, CTA pairs --
+// Same computation on clusters of two CTAs (tcgen05 cta_group::2): one MMA covers 256
+// activation rows x 256 weight rows, each CTA holding its own 128 activation rows (TMA) and
+// decoding only ITS half of the weight tile, so per SM the decode work, the shared-memory
+// writes of decoded weights and the operand bytes the tensor core reads per flop all halve.
+// The even CTA issues the MMAs; tcgen05.commit multicasts the "slot free" / "accumulator
+// ready" arrivals to both CTAs; the odd CTA's MMA warp forwards "my A tile and my W half are
+// in shared memory" to the even CTA's weight barrier, its epilogue warps "accumulator
+// drained" to the even CTA's accum_empty barrier.
+#ifndef VB_PAIR_SW
+#define VB_PAIR_SW 4
+#endif
+#ifndef VB_PAIR_SA
+#define VB_PAIR_SA 7
+#endif
+constexpr int PAIR_SA = VB_PAIR_SA, PAIR_SW = VB_PAIR_SW;
+struct PairSmem {
+    static constexpr int A_BYTES = GEMM_BM * GEMM_BK;  // 128 activation rows
+    static constexpr int W_BYTES = 128 * GEMM_BK;      // 128 of the tile's 256 weight rows
+    static constexpr int W_OFFSET = PAIR_SA * A_BYTES;
+    static constexpr int BAR_OFFSET = W_OFFSET + PAIR_SW * W_BYTES;
+    static constexpr int STAGING_OFFSET = BAR_OFFSET + 256;
+    static constexpr int TOTAL = STAGING_OFFSET + 4 * 4096 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ Wp,
+                         __nv_bfloat16 *__restrict__ out, int32_t *__restrict__ acc_out,
+                         const float *__restrict__ s, const float *__restrict__ ws, int ws_num, int M, int N, int K,
+                         int tiles_mp, int tiles_n, int *status) {
+    using L = PairSmem;
+    constexpr int BN = 256;
+    extern __shared__ uint8_t gemm_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
+    uint64_t *empty_a = full_a + PAIR_SA;
+    uint64_t *full_w = empty_a + PAIR_SA;
+    uint64_t *empty_w = full_w + PAIR_SW;
+    uint64_t *accum_full = empty_w + PAIR_SW;
+    uint64_t *accum_empty = accum_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+    const int ksteps = K / GEMM_BK;
+    const int n_tiles = tiles_mp * tiles_n;
+    const WaitCtx wc{abort_flag, status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < PAIR_SA; ++i) {
+            mbar_init(&full_a[i], 1);
+            mbar_init(&empty_a[i], 1);
+        }
+        for (int i = 0; i < PAIR_SW; ++i) {
+            mbar_init(&full_w[i], rank == 0 ? 9 : 8);  // decode warps (+ the odd CTA's forwarder in the even CTA)
+            mbar_init(&empty_w[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&accum_full[i], 1);
+            mbar_init(&accum_empty[i], 8);  // 4 epilogue warps of each CTA (used in the even CTA)
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them remotely
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * BN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a_map);
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = cid; ok && tile < n_tiles; tile += ncl) {
+                const int m0 = (tile % tiles_mp) * 256 + (int)rank * 128;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&empty_a[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&full_a[st], L::A_BYTES);
+                    tma_load_2d(smem + st * L::A_BYTES, &a_map, &full_a[st], kt * GEMM_BK, m0);
+                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(2, 1, 1, 0, 0, 256, BN);
+            uint32_t st = 0, ph = 0, sw = 0, pw = 0, j = 0;
+            bool ok = true;
+            for (int tile = cid; ok && tile < n_tiles; tile += ncl, ++j) {
+                const uint32_t buf = j & 1u;
+                ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok) ok = mbar_wait(&full_w[sw], pw, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + st * L::A_BYTES);
+                    const uint32_t w_addr = smem_u32(smem + L::W_OFFSET + sw * L::W_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 32; ++k)
+                        mma_i8_pair(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                                    smem_desc_sw128(w_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
+                    tc_commit_pair(&empty_a[st], 3);
+                    tc_commit_pair(&empty_w[sw], 3);
+                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
+                    if (++sw == PAIR_SW) { sw = 0; pw ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit_pair(&accum_full[buf], 3);
+            }
+        } else if (lane == 0) {
+            // odd CTA: tell the even CTA when this CTA's operands of a step are in shared memory
+            uint32_t st = 0, ph = 0, sw = 0, pw = 0;
+            bool ok = true;
+            for (int tile = cid; ok && tile < n_tiles; tile += ncl) {
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok) ok = mbar_wait(&full_w[sw], pw, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    mbar_arrive_cluster(&full_w[sw], 0);
+                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
+                    if (++sw == PAIR_SW) { sw = 0; pw ^= 1u; }
+                }
+            }
+        }
+    } else if (warp < 10) {
+        // ---- decode warps: one 16-row weight block each per step (8 blocks = this CTA's 128 rows) ----
+        const int dw = warp - 2;
+        const int nblk_total = N / 16;
+        const int row_in_blk = 8 * ((lane & 7) >> 2) + 4 * (lane & 1);
+        const int chunk16 = 2 * (lane >> 3) + ((lane & 3) >> 1);
+        constexpr int PF = 4;
+        uint4 pf[PF];
+        const int my_tiles = cid < n_tiles ? (n_tiles - 1 - cid) / ncl + 1 : 0;
+        const int total = my_tiles * ksteps;
+        auto fetch = [&](int g) -> uint4 {
+            const int tile = cid + (g / ksteps) * ncl, kt = g % ksteps;
+            const int nb = (tile / tiles_mp) * (BN / 16) + (int)rank * 8 + dw;
+            return (g < total && nb < nblk_total)
+                       ? __ldg(reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K + (size_t)kt * 512) + lane)
+                       : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
+        };
+        uint32_t st = 0, ph = 0;
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < PF; ++i) pf[i] = fetch(i);
+        for (int g0 = 0; ok && g0 < total; g0 += PF) {
+#pragma unroll
+            for (int u = 0; u < PF; ++u) {
+                const int g = g0 + u;
+                if (g >= total) break;
+                const uint4 cur = pf[u];
+                pf[u] = fetch(g + PF);
+                ok = mbar_wait(&empty_w[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                uint8_t *wt = smem + L::W_OFFSET + st * L::W_BYTES;
+                const uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+#ifdef VB_TERN_NODECODE
+                if (cur.x == 0x12345u)  // developer experiment: skip the decode work
+#endif
+#pragma unroll
+                for (int sl = 0; sl < 4; ++sl) {
+                    uint32_t d[4];
+                    decode_slot(words[sl], d);
+                    const int r = dw * 16 + row_in_blk + sl;  // row inside this CTA's half tile
+                    uint8_t *dst = wt + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk16 ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(d[0], d[1], d[2], d[3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_w[st]);
+                if (++st == PAIR_SW) { st = 0; ph ^= 1u; }
+            }
+        }
+    } else {
+        // ---- epilogue warps 10..13: this CTA's 128 rows of the pair tile ----
+        const int q = warp & 3;
+        const int group = N / ws_num;
+        uint8_t *stg = smem + L::STAGING_OFFSET + (warp - 10) * 4096;
+        const uint32_t my_sw = (uint32_t)(lane & 7);
+        uint32_t j = 0;
+        bool ok = true;
+        for (int tile = cid; ok && tile < n_tiles; tile += ncl, ++j) {
+            const uint32_t buf = j & 1u;
+            const int m0 = (tile % tiles_mp) * 256 + (int)rank * 128, n0 = (tile / tiles_mp) * BN;
+            const int m = m0 + q * 32 + lane;
+            ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
+            const float sm = (m < M) ? s[m] : 1.0f;
+            const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+            if (m0 < M) {  // warp-uniform: the odd CTA's rows may all lie past M
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(lane_addr + (uint32_t)c, r0);
+                    tmem_ld32(lane_addr + (uint32_t)(c + 32), r1);
+                    tmem_ld_wait();
+                    const int n = n0 + c;
+                    if (n >= N) break;
+                    if (acc_out && m < M) {
+                        int4 *dst = reinterpret_cast<int4 *>(acc_out + (size_t)m * N + n);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
+                        if (n + 32 < N) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                dst[8 + e] = make_int4((int)r1[4 * e], (int)r1[4 * e + 1], (int)r1[4 * e + 2], (int)r1[4 * e + 3]);
+                        }
+                    }
+                    const float cs0 = __fdiv_rn(ws[n / group], sm);
+                    const float cs1 = __fdiv_rn(ws[min(n + 32, N - 1) / group], sm);
+                    uint8_t *mine = stg + lane * 128;
+#pragma unroll
+                    for (int e4 = 0; e4 < 4; ++e4) {
+                        uint32_t pa[4], pb[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 ha = __floats2bfloat162_rn((float)(int)r0[8 * e4 + 2 * e] * cs0,
+                                                                            (float)(int)r0[8 * e4 + 2 * e + 1] * cs0);
+                            const __nv_bfloat162 hb = __floats2bfloat162_rn((float)(int)r1[8 * e4 + 2 * e] * cs1,
+                                                                            (float)(int)r1[8 * e4 + 2 * e + 1] * cs1);
+                            pa[e] = *reinterpret_cast<const uint32_t *>(&ha);
+                            pb[e] = *reinterpret_cast<const uint32_t *>(&hb);
+                        }
+                        *reinterpret_cast<uint4 *>(mine + (((uint32_t)e4 ^ my_sw) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                        *reinterpret_cast<uint4 *>(mine + (((uint32_t)(4 + e4) ^ my_sw) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+                    }
+                    __syncwarp();
+                    const int cols_valid = min(64, N - n);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = (lane >> 3) + 4 * i;
+                        const int ch = lane & 7;
+                        const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * 128 + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4));
+                        const int mr = m0 + q * 32 + rr;
+#ifdef VB_TERN_NOSTORE
+                        if (v.x == 0x12345u)  // developer experiment: no output stores
+#endif
+                        if (mr < M && ch * 8 < cols_valid)
+                            *reinterpret_cast<uint4 *>(out + (size_t)mr * N + n + ch * 8) = v;
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&accum_empty[buf]);
+                else mbar_arrive_cluster(&accum_empty[buf], 0);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA may exit while the other can still signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 2 * BN);
+    }
+}
+
 // ------------------------------------------------------------------ host side --
 static int check_gemm_args(const void *A, const void *W, const void *out, const void *s, const void *ws, int ws_num,
                            int M, int N, int K) {
@@ -541,6 +820,35 @@ static int launch_gemm_tc(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
     return VLAB200_OK;
 }
 
+static int launch_gemm_pair(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, int32_t *acc, const float *s,
+                            const float *ws, int ws_num, int M, int N, int K, cudaStream_t st) {
+    int *status = device_status_ptr();
+    if (!status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
+    CUtensorMap amap;
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)K};
+    const uint32_t box[2] = {GEMM_BK, GEMM_BM};
+    int rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    static bool attr_done = false;
+    static int n_sm = 0;
+    if (!attr_done) {
+        VB_CUDA(cudaFuncSetAttribute(ternary_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     PairSmem::TOTAL));
+        int dev = 0;
+        VB_CUDA(cudaGetDevice(&dev));
+        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+        attr_done = true;
+    }
+    const int tiles_mp = (M + 255) / 256, tiles_n = (N + 255) / 256;
+    const int nt = tiles_mp * tiles_n, pairs = n_sm / 2;
+    ternary_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), GEMM_THREADS, PairSmem::TOTAL, st>>>(
+        amap, W, out, acc, s, ws, ws_num, M, N, K, tiles_mp, tiles_n, status);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
 static int ternary_linear(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, int32_t *acc, const float *s,
                           const float *ws, int ws_num, int M, int N, int K, cudaStream_t st, int force_path) {
     int rc = check_gemm_args(A, W, out, s, ws, ws_num, M, N, K);
@@ -563,6 +871,9 @@ static int ternary_linear(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
         (acc && (reinterpret_cast<uintptr_t>(acc) & 15)))
         return VLAB200_ERR_ARG;
     if (N % 32 || (N / ws_num) % 32) return VLAB200_ERR_UNSUPPORTED;
+    // CTA pairs measured faster than one CTA per tile on every BitVLA shape from M = 300 up
+    if (force_path == 3 || (force_path == 0 && N >= 256))
+        return launch_gemm_pair(A, W, out, acc, s, ws, ws_num, M, N, K, st);
     if (N >= 256) return launch_gemm_tc<256, 4>(A, W, out, acc, s, ws, ws_num, M, N, K, st);
     return launch_gemm_tc<128, 4>(A, W, out, acc, s, ws, ws_num, M, N, K, st);
 }
