@@ -176,7 +176,7 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None):
             "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4}
 
 
-def measure_ternary(torch, vb, dev, steps, warmup):
+def measure_ternary(torch, vb, dev, steps, warmup, only=None):
     """BitVLA-shaped ternary linear layers (BASELINE configs[3]): per-token int8 act-quant + 2-bit
     ladder-packed weights; M in {1, 300, 4800} x the four LM shapes.  Rotating operand sets larger
     than L2 between timed launches."""
@@ -186,6 +186,8 @@ def measure_ternary(torch, vb, dev, steps, warmup):
     rows = []
     for name, N, K, ws_num in shapes:
         for M in (1, 300, 4800):
+            if only and only != f"{name}:{M}":
+                continue
             n_sets = max(2, int(160e6 // (N * K // 4 + M * K + M * N * 2)) + 1)
             n_sets = min(n_sets, 24)
             a = torch.randint(-127, 128, (n_sets, M, K), dtype=torch.int8, device=dev, generator=g)
@@ -209,8 +211,8 @@ def measure_ternary(torch, vb, dev, steps, warmup):
             del a, wp, sc, out
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
-    big = max((r for r in rows if r["M"] == 4800), key=lambda r: r["tops"])
-    gemv = max((r for r in rows if r["M"] == 1), key=lambda r: r["packed_weight_gbs"])
+    big = max((r for r in rows if r["M"] == 4800), key=lambda r: r["tops"], default=rows[0])
+    gemv = max((r for r in rows if r["M"] == 1), key=lambda r: r["packed_weight_gbs"], default=rows[0])
     hbm_peak, kind = measured_peaks()
     return {"metric": "ternary x int8 GEMM throughput (BitVLA LM shapes)", "value": big["tops"], "unit": "TOPS",
             "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": big["us"] / 1e3, "higher_is_better": True,
@@ -336,6 +338,8 @@ def main():
     ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary", "bitvla_lm"],
                     help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
                          "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
+    ap.add_argument("--ternary-only", default=None,
+                    help="ternary workload: run one case only, e.g. gate_up:4800 (for profiler captures)")
     ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
     ap.add_argument("--no-pi0-extra", action="store_true", help="skip the short pi0-loop measurement in the default run")
     ap.add_argument("--no-e2e", action="store_true")
@@ -372,7 +376,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if args.workload == "ternary":
         if rank == 0:
-            print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3))), flush=True)
+            print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3), args.ternary_only)),
+                  flush=True)
         if world > 1:
             dist.destroy_process_group()
         return

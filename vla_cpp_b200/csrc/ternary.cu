@@ -344,9 +344,13 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
         constexpr int NBLK = BN / 16;             // 16-row weight blocks in the tile
         constexpr int PER_WARP = NBLK / 8;
         const int nblk_total = N / 16;
-        // lane geometry inside one 512-byte chunk
+        // lane geometry inside one 512-byte chunk (lane t holds the 4 slots at byte offset 16 t)
         const int row_in_blk = 8 * ((lane & 7) >> 2) + 4 * (lane & 1);  // + slot 0..3
         const int chunk16 = 2 * (lane >> 3) + ((lane & 3) >> 1);        // 16-byte column 0..7
+        // 128-bit shared stores are served a quarter-warp at a time.  Lanes t and t ^ 4 of a quarter
+        // write rows 8 apart (same banks); the upper one walks its slots in the order 2, 3, 0, 1 so that
+        // the two never hit the same 16-byte column in the same instruction.
+        const bool swap_slots = (lane & 4) != 0;
         // Packed weights are prefetched three main-loop steps ahead into registers: one step is
         // shorter than the latency of a load that misses L2.
         constexpr int PF = 3;
@@ -372,8 +376,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
 #pragma unroll
                 for (int sl = 0; sl < 4; ++sl) {
                     uint32_t d[4];
-                    decode_slot(words[sl], d);
-                    const int r = blk * 16 + row_in_blk + sl;  // row inside the BN tile
+                    decode_slot(swap_slots ? words[sl ^ 2] : words[sl], d);
+                    const int r = blk * 16 + row_in_blk + (swap_slots ? (sl ^ 2) : sl);  // row inside the BN tile
                     uint8_t *dst = wt + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk16 ^ (r & 7)) << 4);
                     *reinterpret_cast<uint4 *>(dst) = make_uint4(d[0], d[1], d[2], d[3]);
                 }
@@ -500,21 +504,35 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
 // ready" arrivals to both CTAs; the odd CTA's MMA warp forwards "my A tile and my W half are
 // in shared memory" to the even CTA's weight barrier, its epilogue warps "accumulator
 // drained" to the even CTA's accum_empty barrier.
-#ifndef VB_PAIR_SW
-#define VB_PAIR_SW 4
-#endif
-#ifndef VB_PAIR_SA
-#define VB_PAIR_SA 7
-#endif
-constexpr int PAIR_SA = VB_PAIR_SA, PAIR_SW = VB_PAIR_SW;
+constexpr int PAIR_STAGES = 6;
 struct PairSmem {
     static constexpr int A_BYTES = GEMM_BM * GEMM_BK;  // 128 activation rows
     static constexpr int W_BYTES = 128 * GEMM_BK;      // 128 of the tile's 256 weight rows
-    static constexpr int W_OFFSET = PAIR_SA * A_BYTES;
-    static constexpr int BAR_OFFSET = W_OFFSET + PAIR_SW * W_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+    static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
     static constexpr int STAGING_OFFSET = BAR_OFFSET + 256;
     static constexpr int TOTAL = STAGING_OFFSET + 4 * 4096 + 1024;
 };
+
+// Waits that are not on the critical path back off between polls so that the waiting warps do
+// not take issue slots from the MMA and decode warps of the same scheduler.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code,
+                                                  unsigned ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        __nanosleep(ns);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *w.abort_flag = 1;
+                atomicCAS(w.status, 0, code);
+                return false;
+            }
+        }
+    }
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ Wp,
@@ -526,11 +544,13 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
-    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
-    uint64_t *empty_a = full_a + PAIR_SA;
-    uint64_t *full_w = empty_a + PAIR_SA;
-    uint64_t *empty_w = full_w + PAIR_SW;
-    uint64_t *accum_full = empty_w + PAIR_SW;
+    // One ring: stage = this CTA's activation tile + its decoded half of the weight tile.
+    //   full[s]   loader's expect_tx arrival + TMA bytes + the two decode warps of the step
+    //             (+ in the even CTA the odd CTA's "my stage is full" forward)
+    //   empty[s]  tcgen05.commit of the MMAs that read stage s, multicast to both CTAs
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
+    uint64_t *empty = full + PAIR_STAGES;
+    uint64_t *accum_full = empty + PAIR_STAGES;
     uint64_t *accum_empty = accum_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -543,13 +563,9 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
     const WaitCtx wc{abort_flag, status};
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PAIR_SA; ++i) {
-            mbar_init(&full_a[i], 1);
-            mbar_init(&empty_a[i], 1);
-        }
-        for (int i = 0; i < PAIR_SW; ++i) {
-            mbar_init(&full_w[i], rank == 0 ? 9 : 8);  // decode warps (+ the odd CTA's forwarder in the even CTA)
-            mbar_init(&empty_w[i], 1);
+        for (int i = 0; i < PAIR_STAGES; ++i) {
+            mbar_init(&full[i], rank == 0 ? 4 : 3);
+            mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&accum_full[i], 1);
@@ -578,18 +594,25 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
             for (int tile = cid; ok && tile < n_tiles; tile += ncl) {
                 const int m0 = (tile % tiles_mp) * 256 + (int)rank * 128;
                 for (int kt = 0; kt < ksteps; ++kt) {
-                    ok = mbar_wait(&empty_a[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    ok = mbar_wait_backoff(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY, 64);
                     if (!ok) break;
-                    mbar_expect_tx(&full_a[st], L::A_BYTES);
-                    tma_load_2d(smem + st * L::A_BYTES, &a_map, &full_a[st], kt * GEMM_BK, m0);
-                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
+#ifdef VB_TERN_NOLOAD
+                    mbar_arrive(&full[st]);  // developer experiment: no activation traffic
+#else
+                    mbar_expect_tx(&full[st], L::A_BYTES);
+                    tma_load_2d(smem + st * L::STAGE_BYTES, &a_map, &full[st], kt * GEMM_BK, m0);
+#endif
+                    if (++st == PAIR_STAGES) { st = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = make_idesc(2, 1, 1, 0, 0, 256, BN);
-            uint32_t st = 0, ph = 0, sw = 0, pw = 0, j = 0;
+            // descriptors differ between stages and k sub-steps only in the 14-bit start address
+            const uint64_t a_desc0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
+            const uint64_t w_desc0 = smem_desc_sw128(smem_u32(smem + L::A_BYTES), 16, 1024);
+            uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
             for (int tile = cid; ok && tile < n_tiles; tile += ncl, ++j) {
                 const uint32_t buf = j & 1u;
@@ -598,87 +621,93 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kt = 0; kt < ksteps; ++kt) {
-                    ok = mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL);
-                    if (ok) ok = mbar_wait(&full_w[sw], pw, wc, DEV_TIMEOUT_FULL);
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + st * L::A_BYTES);
-                    const uint32_t w_addr = smem_u32(smem + L::W_OFFSET + sw * L::W_BYTES);
+                    const uint64_t off = (uint64_t)(st * (L::STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / 32; ++k)
-                        mma_i8_pair(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                                    smem_desc_sw128(w_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
-                    tc_commit_pair(&empty_a[st], 3);
-                    tc_commit_pair(&empty_w[sw], 3);
-                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
-                    if (++sw == PAIR_SW) { sw = 0; pw ^= 1u; }
+                        mma_i8_pair(d_tmem, a_desc0 + off + 2 * k, w_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                    tc_commit_pair(&empty[st], 3);
+                    if (++st == PAIR_STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 tc_commit_pair(&accum_full[buf], 3);
             }
         } else if (lane == 0) {
-            // odd CTA: tell the even CTA when this CTA's operands of a step are in shared memory
-            uint32_t st = 0, ph = 0, sw = 0, pw = 0;
+            // odd CTA: tell the even CTA when this CTA's stage is in shared memory
+            uint32_t st = 0, ph = 0;
             bool ok = true;
             for (int tile = cid; ok && tile < n_tiles; tile += ncl) {
                 for (int kt = 0; kt < ksteps; ++kt) {
-                    ok = mbar_wait(&full_a[st], ph, wc, DEV_TIMEOUT_FULL);
-                    if (ok) ok = mbar_wait(&full_w[sw], pw, wc, DEV_TIMEOUT_FULL);
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
-                    mbar_arrive_cluster(&full_w[sw], 0);
-                    if (++st == PAIR_SA) { st = 0; ph ^= 1u; }
-                    if (++sw == PAIR_SW) { sw = 0; pw ^= 1u; }
+                    mbar_arrive_cluster(&full[st], 0);
+                    if (++st == PAIR_STAGES) { st = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp < 10) {
-        // ---- decode warps: one 16-row weight block each per step (8 blocks = this CTA's 128 rows) ----
+        // ---- decode warps ----
+        // Two warps share a step (4 of this CTA's 8 weight blocks each) and the four warp pairs take
+        // steps round-robin, so a warp has four steps of time for one unit of work and the barrier
+        // wait, proxy fence and arrival are paid once per 64 decoded rows.
         const int dw = warp - 2;
+        const int pi = dw >> 1, hb = dw & 1;
         const int nblk_total = N / 16;
-        const int row_in_blk = 8 * ((lane & 7) >> 2) + 4 * (lane & 1);
-        const int chunk16 = 2 * (lane >> 3) + ((lane & 3) >> 1);
-        constexpr int PF = 4;
-        uint4 pf[PF];
+        const int row_in_blk = 8 * ((lane & 7) >> 2) + 4 * (lane & 1);  // + slot 0..3
+        const int chunk16 = 2 * (lane >> 3) + ((lane & 3) >> 1);        // 16-byte column 0..7
+        const bool swap_slots = (lane & 4) != 0;  // see ternary_gemm_tc_kernel: avoids 2-way bank conflicts
         const int my_tiles = cid < n_tiles ? (n_tiles - 1 - cid) / ncl + 1 : 0;
         const int total = my_tiles * ksteps;
-        auto fetch = [&](int g) -> uint4 {
+        auto fetch = [&](int g, uint4 (&dst)[4]) {
             const int tile = cid + (g / ksteps) * ncl, kt = g % ksteps;
-            const int nb = (tile / tiles_mp) * (BN / 16) + (int)rank * 8 + dw;
-            return (g < total && nb < nblk_total)
-                       ? __ldg(reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K + (size_t)kt * 512) + lane)
-                       : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
+            const int nb0 = (tile / tiles_mp) * (BN / 16) + (int)rank * 8 + hb * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                dst[i] = (g < total && nb0 + i < nblk_total)
+                             ? __ldg(reinterpret_cast<const uint4 *>(Wp + (size_t)(nb0 + i) * 4 * K + (size_t)kt * 512) + lane)
+                             : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
         };
-        uint32_t st = 0, ph = 0;
+        uint4 nxt[4];
+        fetch(pi, nxt);
+        uint32_t st = (uint32_t)pi, ph = 0;
         bool ok = true;
+        for (int g = pi; ok && g < total; g += 4) {
+            uint4 cur[4];
 #pragma unroll
-        for (int i = 0; i < PF; ++i) pf[i] = fetch(i);
-        for (int g0 = 0; ok && g0 < total; g0 += PF) {
+            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+            fetch(g + 4, nxt);
+            uint8_t *wt = smem + st * L::STAGE_BYTES + L::A_BYTES;
 #pragma unroll
-            for (int u = 0; u < PF; ++u) {
-                const int g = g0 + u;
-                if (g >= total) break;
-                const uint4 cur = pf[u];
-                pf[u] = fetch(g + PF);
-                ok = mbar_wait(&empty_w[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
-                if (!ok) break;
-                uint8_t *wt = smem + L::W_OFFSET + st * L::W_BYTES;
-                const uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t words[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+                uint32_t d[4][4];
 #ifdef VB_TERN_NODECODE
-                if (cur.x == 0x12345u)  // developer experiment: skip the decode work
+                if (cur[0].x == 0x12345u)  // developer experiment: skip the decode work
+#endif
+#pragma unroll
+                for (int sl = 0; sl < 4; ++sl) decode_slot(swap_slots ? words[sl ^ 2] : words[sl], d[sl]);
+                if (i == 0) {  // the first block is decoded before the stage is known to be free
+                    ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                }
+#ifdef VB_TERN_NODECODE
+                if (cur[0].x == 0x12345u)
 #endif
 #pragma unroll
                 for (int sl = 0; sl < 4; ++sl) {
-                    uint32_t d[4];
-                    decode_slot(words[sl], d);
-                    const int r = dw * 16 + row_in_blk + sl;  // row inside this CTA's half tile
+                    const int r = (hb * 4 + i) * 16 + row_in_blk + (swap_slots ? (sl ^ 2) : sl);  // row in the half tile
                     uint8_t *dst = wt + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk16 ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(dst) = make_uint4(d[0], d[1], d[2], d[3]);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(d[sl][0], d[sl][1], d[sl][2], d[sl][3]);
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full_w[st]);
-                if (++st == PAIR_SW) { st = 0; ph ^= 1u; }
             }
+            if (!ok) break;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[st]);
+            st += 4;
+            if (st >= PAIR_STAGES) { st -= PAIR_STAGES; ph ^= 1u; }
         }
     } else {
         // ---- epilogue warps 10..13: this CTA's 128 rows of the pair tile ----
@@ -692,7 +721,7 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
             const uint32_t buf = j & 1u;
             const int m0 = (tile % tiles_mp) * 256 + (int)rank * 128, n0 = (tile / tiles_mp) * BN;
             const int m = m0 + q * 32 + lane;
-            ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
+            ok = mbar_wait_backoff(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM, 256);
             if (!ok) break;
             tc_fence_after();
             const float sm = (m < M) ? s[m] : 1.0f;
