@@ -338,6 +338,8 @@ def main():
     ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary", "bitvla_lm"],
                     help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
                          "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
+    ap.add_argument("--gemm-tiling", type=int, default=0,
+                    help="bf16 GEMM tiling inside the engine: 0 automatic, 1 128x256, 2 128x128, 3 CTA pairs")
     ap.add_argument("--ternary-only", default=None,
                     help="ternary workload: run one case only, e.g. gate_up:4800 (for profiler captures)")
     ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
@@ -374,6 +376,7 @@ def main():
         torch.cuda.synchronize()
 
     dev = torch.device("cuda", local_rank)
+    vb.set_gemm_tiling(args.gemm_tiling)
     if args.workload == "ternary":
         if rank == 0:
             print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3), args.ternary_only)),

@@ -58,9 +58,11 @@ def oracle_model(oracle, cfg, per, glob, wqkv, P, pos_base, pad):
     return oracle.DenoiseModel(ocfg, ow)
 
 
-def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, **kw):
+def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, tiling=0, **kw):
     torch = require_cuda()
     import vla_cpp_b200 as vb
+
+    vb.set_gemm_tiling(tiling)
 
     rng = np.random.default_rng(seed)
     cfg, per, glob, wqkv = make_policy(oracle, rng, P=P, **kw)
@@ -95,6 +97,7 @@ def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, **kw):
     torch.cuda.synchronize()
     if pad is None:
         assert np.array_equal(outh.numpy(), out)
+    vb.set_gemm_tiling(0)
     return worst, worst_d
 
 
@@ -120,3 +123,39 @@ def test_smolvla_full_width_two_layers(oracle):
     w, d = run_case(oracle, 4, n_obs=2, P=177, pos_base=170, model=1, L=2, H=720, n_q=15, n_kv=5, hd=64, inter=2048,
                     chunk=50, A=32, sd=32, T=2, self_every=2)
     assert w < 1e-2 and d < 3e-2, (w, d)
+
+
+@pytest.mark.parametrize("tiling", [1, 2, 3])
+def test_pi0_every_gemm_tiling_matches_oracle(oracle, tiling):
+    """The three tilings of the bf16 GEMMs (one CTA per 128x256 / 128x128 tile, CTA pairs on 256x256)
+    forced in turn on a case with several row tiles (7 observations x 51 rows = 357 rows)."""
+    w, d = run_case(oracle, 5, n_obs=7, P=64, tiling=tiling, model=0, L=2, H=512, n_q=8, n_kv=1, hd=64, inter=1024,
+                    chunk=50, A=32, sd=32, T=2)
+    assert w < 1e-2 and d < 3e-2, (w, d)
+
+
+def test_gemm_tilings_are_bit_identical(oracle):
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(11)
+    kw = dict(model=0, L=2, H=512, n_q=8, n_kv=1, hd=64, inter=1024, chunk=50, A=32, sd=32, T=2)
+    n_obs, P = 12, 64
+    cfg, per, glob, _ = make_policy(oracle, rng, P=P, **kw)
+    bf = lambda a: bits_to_bf16_tensor(oracle.f32_to_bf16_bits(a))
+    weights = {k: [bf(a) if k.startswith("w") else to_dev(a) for a in v] for k, v in per.items()}
+    weights.update({k: (bf(a) if k.startswith("w_") else to_dev(a)) for k, v in glob.items() for a in [v]})
+    eng = vb.PolicyEngine(cfg, weights, max_obs=n_obs, prefix_len=P)
+    for l in range(cfg["n_layers"]):
+        kp = torch.randn((n_obs, P, cfg["n_kv"], cfg["head_dim"]), device="cuda")
+        eng.set_prefix(l, kp, torch.randn_like(kp))
+    x0 = torch.randn((n_obs, cfg["chunk"], cfg["action_dim"]), device="cuda")
+    state = torch.randn((n_obs, cfg["state_dim"]), device="cuda")
+    outs = []
+    for tiling in (1, 2, 3, 0):
+        vb.set_gemm_tiling(tiling)
+        outs.append(eng.denoise(x0, state).cpu().numpy())
+        assert vb.device_status() == 0
+    vb.set_gemm_tiling(0)
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])

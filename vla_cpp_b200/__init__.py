@@ -23,5 +23,6 @@ from .api import (  # noqa: F401
     lib,
     qkv_rope_append,
     rope_table,
+    set_gemm_tiling,
     ternary_linear,
 )

@@ -53,7 +53,7 @@ EXPORTS = [
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_denoise_attn_loop_static",
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
-    "vlab200_engine_denoise_host",
+    "vlab200_engine_denoise_host", "vlab200_set_gemm_tiling",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
@@ -74,6 +74,11 @@ def _stream():
     import torch
 
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def set_gemm_tiling(tiling):
+    """0 = automatic, 1 = 128x256 tiles, 2 = 128x128 tiles, 3 = CTA pairs (testing / measurement knob)."""
+    _check(lib().vlab200_set_gemm_tiling(int(tiling)), "vlab200_set_gemm_tiling")
 
 
 def device_status(reset=True):

@@ -31,30 +31,42 @@ constexpr int G_BM = 128, G_BK = 64, G_THREADS = 448;
 constexpr int G_A_BYTES = G_BM * 128;
 // BN = 256 minimises operand traffic per flop; BN = 128 doubles the number of tiles when the
 // problem has too few of them to occupy the SMs.
-template <int BN>
+// PAIR: two CTAs (a cluster) share one 256 x 256 tile through tcgen05 cta_group::2 -- each loads its
+// own 128 activation rows and only HALF of the weight tile, which halves the shared-memory bytes
+// written and read per flop (a lone CTA moves 96 KB through shared memory per 512 tensor cycles,
+// more than the 128 B/clk the SM has).
+template <int BN, bool PAIR>
 struct GemmCfg {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
-    static constexpr int B_BYTES = BN * 128;
+    static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // weight rows this CTA stages
+    static constexpr int B_BYTES = B_ROWS * 128;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024 + 1024;  // + barriers, statistics, alignment
 };
 
+// Both activations are x * sigmoid(.): SiLU(x) = x / (1 + e^-x) and, since 1 + tanh(u) = 2 / (1 + e^-2u),
+// tanh-GELU(x) = 0.5 x (1 + tanh(u)) = x / (1 + e^-2u) with u = k0 x (1 + k1 x^2) (constants of
+// src/cuda/vla_cuda_bf16.cu:470-474).  One ex2 and one reciprocal each (relative error ~1e-6) keep the
+// epilogue off the critical path; tanhf and an IEEE division cost several times the issue slots.
 __device__ __forceinline__ float act_apply(float x, int act) {
-    if (act == ACT_SILU) return x / (1.0f + __expf(-x));
+    if (act == ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
     if (act == ACT_GELU_TANH) {
-        // constants of src/cuda/vla_cuda_bf16.cu:470-474
         const float k0 = 0.79788456080286535587989211986876f, k1 = 0.044715f;
-        return 0.5f * x * (1.0f + tanhf(k0 * x * (1.0f + k1 * x * x)));
+        const float u = k0 * x * (1.0f + k1 * x * x);
+        return __fdividef(x, 1.0f + __expf(-2.0f * u));
     }
     return x;
 }
 
-template <int G_BN>
-__global__ void __launch_bounds__(G_THREADS, 1)
-dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
-                  const GemmParams p, int tiles_m, int tiles_n) {
-    constexpr int G_STAGES = GemmCfg<G_BN>::STAGES, G_B_BYTES = GemmCfg<G_BN>::B_BYTES, G_STAGE_BYTES = GemmCfg<G_BN>::STAGE_BYTES;
-    (void)G_B_BYTES;
+template <int G_BN, bool PAIR>
+__device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const CUtensorMap &w_map, const GemmParams &p,
+                                                int tiles_m, int tiles_n) {
+    using Cfg = GemmCfg<G_BN, PAIR>;
+    constexpr int G_STAGES = Cfg::STAGES, G_STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int TILE_M = PAIR ? 2 * G_BM : G_BM;  // rows of one work unit
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     extern __shared__ uint8_t g_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(g_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
@@ -74,24 +86,34 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < G_STAGES; ++i) {
-            mbar_init(&full[i], 1);
+            mbar_init(&full[i], (PAIR && rank == 0) ? 2 : 1);  // even CTA of a pair: + the odd CTA's "stage landed"
             mbar_init(&empty[i], empty_count);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&accum_full[i], 1);
-            mbar_init(&accum_empty[i], 256);
+            mbar_init(&accum_empty[i], PAIR ? 16 : 256);  // pairs: one arrival per epilogue warp of both CTAs
             mbar_init(&stats_full[i], 128);
             mbar_init(&stats_empty[i], 256);
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
+    if (PAIR) {
+        __syncthreads();
+        cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them remotely
+    }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 2 * G_BN);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, 2 * G_BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 2 * G_BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -101,8 +123,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
             tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * G_BM, n0 = (tile % tiles_n) * G_BN;
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+                const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM;
+                const int n0 = (tile % tiles_n) * G_BN + (int)rank * Cfg::B_ROWS * (PAIR ? 1 : 0);
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
@@ -115,11 +138,14 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, G_BM, G_BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, TILE_M, G_BN);
+            // descriptors differ between stages and k sub-steps only in the 14-bit start address
+            const uint64_t a_desc0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
+            const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem + G_A_BYTES), 16, 1024);
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
                 const uint32_t buf = j & 1u;
                 ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
@@ -129,17 +155,31 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + st * G_STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + G_A_BYTES;
+                    const uint64_t off = (uint64_t)(st * (G_STAGE_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < G_BK / 16; ++k)
-                        mma_f16(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                                smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
-                    tc_commit(&empty[st]);
+                    for (int k = 0; k < G_BK / 16; ++k) {
+                        if (PAIR) mma_f16_pair(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                        else mma_f16(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                    }
+                    if (PAIR) tc_commit_pair(&empty[st], 3);
+                    else tc_commit(&empty[st]);
                     if (++st == G_STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                tc_commit(&accum_full[buf]);
+                if (PAIR) tc_commit_pair(&accum_full[buf], 3);
+                else tc_commit(&accum_full[buf]);
+            }
+        } else if (PAIR && lane == 0) {
+            // odd CTA of a pair: tell the even CTA when this CTA's stage has landed
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    mbar_arrive_cluster(&full[st], 0);
+                    if (++st == G_STAGES) { st = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp >= 6 && warp < 10) {
@@ -149,7 +189,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
             const uint32_t sw = row & 7;
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
                 const uint32_t buf = j & 1u;
                 float s0 = 0.0f, s1 = 0.0f;
                 for (int kt = 0; kt < ksteps; ++kt) {
@@ -185,9 +225,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
         const int row = qtr * 32 + lane;
         uint32_t j = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
             const uint32_t buf = j & 1u;
-            const int m0 = (tile / tiles_n) * G_BM, n0 = (tile % tiles_n) * G_BN;
+            const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM, n0 = (tile % tiles_n) * G_BN;
             const int m = m0 + row;
             const bool row_ok = m < p.M;
             ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
@@ -269,17 +309,46 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_consta
                 }
             }
             tc_fence_before();
-            mbar_arrive(&accum_empty[buf]);
+            if (PAIR) {
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive(&accum_empty[buf]);
+                    else mbar_arrive_cluster(&accum_empty[buf], 0);
+                }
+            } else {
+                mbar_arrive(&accum_empty[buf]);
+            }
             if (p.use_rms) mbar_arrive(&stats_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // neither CTA may exit while the other can still signal its barriers
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * G_BN);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 2 * G_BN);
+        else tmem_dealloc(tmem_base, 2 * G_BN);
     }
 }
+
+template <int G_BN>
+__global__ void __launch_bounds__(G_THREADS, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                  const GemmParams p, int tiles_m, int tiles_n) {
+    dense_gemm_body<G_BN, false>(a_map, w_map, p, tiles_m, tiles_n);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
+dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                       const GemmParams p, int tiles_m, int tiles_n) {
+    dense_gemm_body<256, true>(a_map, w_map, p, tiles_m, tiles_n);
+}
+
+// 0 = choose by cost; 1 / 2 / 3 force the 128 x 256, 128 x 128 and CTA-pair tilings (testing knob).
+static int g_gemm_variant = 0;
+constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile relative to a lone CTA's 128 x 256 tile
+
+void dense_gemm_set_variant(int v) { g_gemm_variant = (v >= 0 && v <= 3) ? v : 0; }
 
 // Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
@@ -311,33 +380,63 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         VB_CUDA(cudaGetDevice(&dev));
         VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     }
-    const int tiles_m = (p.M + G_BM - 1) / G_BM;
-    const bool narrow = tiles_m * ((p.N + 255) / 256) < 2 * n_sm && p.N > 128;
-    if (narrow) {
-        const uint32_t box[2] = {G_BK, 128};
-        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
-        const uint64_t strides[1] = {(uint64_t)p.K * 2};
-        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, dims, strides, box,
+    // Three tilings: one CTA per 128 x 256 tile, one CTA per 128 x 128 tile (twice the tiles when the
+    // problem has few), a CTA pair per 256 x 256 tile (half the shared-memory traffic per flop).  Costs
+    // in units of one 128 x 256 tile on one SM; the per-tile factors are measured ratios.
+    const int tiles_m = (p.M + G_BM - 1) / G_BM, tiles_mp = (p.M + 2 * G_BM - 1) / (2 * G_BM);
+    const int tn256 = (p.N + 255) / 256, tn128 = (p.N + 127) / 128, pairs = n_sm / 2;
+    auto waves = [](int tiles, int units) { return (tiles + units - 1) / units; };
+    const float cost256 = (float)waves(tiles_m * tn256, n_sm);
+    const float cost128 = p.N > 128 ? 0.55f * waves(tiles_m * tn128, n_sm) : 1e30f;
+    const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
+    int variant = g_gemm_variant;
+    if (variant == 0) variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
+    if (variant == 2 && p.N <= 128) variant = 1;
+    const uint64_t wdims[2] = {(uint64_t)p.K, (uint64_t)p.N};
+    const uint64_t wstrides[1] = {(uint64_t)p.K * 2};
+    if (variant == 3) {
+        const uint32_t box[2] = {G_BK, 128};  // each CTA of a pair stages half of the 256 weight rows
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
         static bool done = false;
         if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<128>::SMEM));
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<256, true>::SMEM));
             done = true;
         }
-        const int tiles_n = (p.N + 127) / 128, nt = tiles_m * tiles_n;
-        dense_gemm_kernel<128><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<128>::SMEM, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+        const int nt = tiles_mp * tn256;
+        dense_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), G_THREADS, GemmCfg<256, true>::SMEM, stream>>>(
+            amap, wmap, p, tiles_mp, tn256);
+    } else if (variant == 2) {
+        const uint32_t box[2] = {G_BK, 128};
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        static bool done = false;
+        if (!done) {
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<128, false>::SMEM));
+            done = true;
+        }
+        const int nt = tiles_m * tn128;
+        dense_gemm_kernel<128><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<128, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn128);
     } else {
         static bool done = false;
         if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256>::SMEM));
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256, false>::SMEM));
             done = true;
         }
-        const int tiles_n = (p.N + 255) / 256, nt = tiles_m * tiles_n;
-        dense_gemm_kernel<256><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<256>::SMEM, stream>>>(amap, wmap, p, tiles_m, tiles_n);
+        const int nt = tiles_m * tn256;
+        dense_gemm_kernel<256><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<256, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn256);
     }
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
 
 }  // namespace vb
+
+extern "C" int32_t vlab200_set_gemm_tiling(int32_t tiling) {
+    if (tiling < 0 || tiling > 3) return VLAB200_ERR_ARG;
+    vb::dense_gemm_set_variant(tiling);
+    return VLAB200_OK;
+}

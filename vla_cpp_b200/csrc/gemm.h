@@ -25,4 +25,7 @@ struct GemmParams {
 // A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream);
 
+// 0 = choose the tiling by cost (default); 1 / 2 / 3 force 128 x 256, 128 x 128, CTA pairs.
+void dense_gemm_set_variant(int v);
+
 }  // namespace vb

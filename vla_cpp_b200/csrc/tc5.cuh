@@ -75,6 +75,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
     }
 }
 
+// Waits that are not on the critical path back off between polls so that the waiting warps do
+// not take issue slots from the MMA and decode warps of the same scheduler.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code,
+                                                  unsigned ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        __nanosleep(ns);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *w.abort_flag = 1;
+                atomicCAS(w.status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05 reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -149,6 +169,17 @@ __device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t adesc, uin
         ".reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");

@@ -514,26 +514,6 @@ struct PairSmem {
     static constexpr int TOTAL = STAGING_OFFSET + 4 * 4096 + 1024;
 };
 
-// Waits that are not on the critical path back off between polls so that the waiting warps do
-// not take issue slots from the MMA and decode warps of the same scheduler.
-__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code,
-                                                  unsigned ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 0;; ++it) {
-        __nanosleep(ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u) {
-            if (*w.abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                *w.abort_flag = 1;
-                atomicCAS(w.status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ Wp,
                          __nv_bfloat16 *__restrict__ out, int32_t *__restrict__ acc_out,
