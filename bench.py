@@ -219,7 +219,7 @@ def measure_ternary(torch, vb, dev, steps, warmup, only=None):
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary (int32 accumulate)", "data": "synthetic",
             "config": {"workload": "ternary: BASELINE configs[3], 4 LM shapes x M in {1, 300, 4800}",
                        "l2": "operand sets rotated (> 126 MB) between launches"},
-            "roofline": {"kernel": "ternary_gemm_tc_kernel", "bound": "tensor", "achieved": big["tops"],
+            "roofline": {"kernel": "ternary_gemm_pair_kernel", "bound": "tensor", "achieved": big["tops"],
                          "peak": INT8_PEAK_TOPS, "unit": "TOPS", "frac": big["tops"] / INT8_PEAK_TOPS,
                          "peak_kind": "of measured (cuBLASLt int8, burst)", "traffic": None, "shape": big},
             "roofline_gemv": {"kernel": "ternary_gemv_kernel", "bound": "hbm", "achieved": gemv["packed_weight_gbs"],
@@ -289,7 +289,7 @@ def measure_bitvla_lm(torch, vb, dev, steps, warmup, n_layers=30):
                                    f"{max_batch} sequences x {seq} tokens per call",
                        "l2": "520 MB of packed weights streamed per call (> 126 MB L2)"},
             "gpu_launches": big["launches"] * steps,
-            "roofline": {"kernel": "ternary_gemm_tc_kernel (whole stack, all kernels' time in the denominator)",
+            "roofline": {"kernel": "ternary_gemm_pair_kernel (whole stack, all kernels' time in the denominator)",
                          "bound": "tensor", "achieved": big["ternary_tops"], "peak": INT8_PEAK_TOPS, "unit": "TOPS",
                          "frac": big["ternary_tops"] / INT8_PEAK_TOPS,
                          "peak_kind": "of measured (cuBLASLt int8, burst)", "traffic": None},
