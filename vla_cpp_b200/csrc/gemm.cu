@@ -207,8 +207,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                             s1 = fmaf(f.y, f.y, s1);
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[st]);
+                    stage_release(&empty[st], s0 + s1, lane);
                     if (++st == G_STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -349,6 +348,7 @@ static int g_gemm_variant = 0;
 constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile relative to a lone CTA's 128 x 256 tile
 
 void dense_gemm_set_variant(int v) { g_gemm_variant = (v >= 0 && v <= 3) ? v : 0; }
+int dense_gemm_variant() { return g_gemm_variant; }
 
 // Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {

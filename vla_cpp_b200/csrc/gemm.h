@@ -27,5 +27,6 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
 
 // 0 = choose the tiling by cost (default); 1 / 2 / 3 force 128 x 256, 128 x 128, CTA pairs.
 void dense_gemm_set_variant(int v);
+int dense_gemm_variant();
 
 }  // namespace vb

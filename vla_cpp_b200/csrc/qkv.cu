@@ -11,6 +11,7 @@
 // two rope, two concat that copy the whole prefix KV each layer-step).
 #include <cuda_bf16.h>
 
+#include "gemm.h"
 #include "host_common.h"
 #include "tc5.cuh"
 
@@ -257,16 +258,23 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap w_map, const QkvParams p) {
 constexpr int QKVF_THREADS = 448;
 constexpr int QKVF_STAGING = 8 * 4096;  // per epilogue warp: 2 pieces x 32 rows x 64 bytes
 
-__global__ void __launch_bounds__(QKVF_THREADS, 1)
-qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
-                    const QkvParams p, int tiles_m, int tiles_n, int nst) {
+// PAIR: a cluster of two CTAs shares one 256 x 256 tile through tcgen05 cta_group::2; each CTA loads
+// its own 128 rows of x and only half of the weight tile (half the shared-memory bytes per flop).
+template <bool PAIR>
+__device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, const CUtensorMap &w_map, const QkvParams &p,
+                                                  int tiles_m, int tiles_n, int nst) {
+    constexpr int STAGE_BYTES = QKV_A_BYTES + (PAIR ? QKV_B_BYTES / 2 : QKV_B_BYTES);
+    constexpr int TILE_M = PAIR ? 2 * QKV_BM : QKV_BM;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     extern __shared__ uint8_t qkvf_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(qkvf_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
-    uint8_t *aux = smem + nst * QKV_STAGE_BYTES;
+    uint8_t *aux = smem + nst * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(aux);
-    uint64_t *full = bars, *empty = bars + 4;
-    uint64_t *accum_full = bars + 8, *accum_empty = accum_full + 2;
+    uint64_t *full = bars, *empty = bars + 6;
+    uint64_t *accum_full = bars + 12, *accum_empty = accum_full + 2;
     uint64_t *stats_full = accum_empty + 2, *stats_empty = stats_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stats_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -282,12 +290,12 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < nst; ++i) {
-            mbar_init(&full[i], 1);
+            mbar_init(&full[i], (PAIR && rank == 0) ? 2 : 1);  // even CTA of a pair: + the odd CTA's "stage landed"
             mbar_init(&empty[i], 5);  // MMA commit + one arrive per statistics warp
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&accum_full[i], 1);
-            mbar_init(&accum_empty[i], 256);
+            mbar_init(&accum_empty[i], PAIR ? 16 : 256);  // pairs: one arrival per epilogue warp of both CTAs
             mbar_init(&stats_full[i], 128);
             mbar_init(&stats_empty[i], 256);
         }
@@ -300,12 +308,22 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
         rope_s[d * p.S + t] = p.rope_cos[i];
         rope_s[(half + d) * p.S + t] = p.rope_sin[i];
     }
+    if (PAIR) {
+        __syncthreads();
+        cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them remotely
+    }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -315,13 +333,14 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
             tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+                const int m0 = (tile / tiles_n) * TILE_M + (int)rank * QKV_BM;
+                const int n0 = (tile % tiles_n) * QKV_BN + (int)rank * (QKV_BN / 2);
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    mbar_expect_tx(&full[st], QKV_STAGE_BYTES);
-                    uint8_t *sa = smem + st * QKV_STAGE_BYTES;
+                    mbar_expect_tx(&full[st], STAGE_BYTES);
+                    uint8_t *sa = smem + st * STAGE_BYTES;
                     tma_load_2d(sa, &x_map, &full[st], kt * QKV_BK, m0);
                     tma_load_2d(sa + QKV_A_BYTES, &w_map, &full[st], kt * QKV_BK, n0);
                     if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
@@ -329,11 +348,14 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, QKV_BM, QKV_BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, 0, TILE_M, QKV_BN);
+            // descriptors differ between stages and k sub-steps only in the 14-bit start address
+            const uint64_t a_desc0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
+            const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem + QKV_A_BYTES), 16, 1024);
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
                 const uint32_t buf = j & 1u;
                 ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
@@ -343,17 +365,31 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + st * QKV_STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + QKV_A_BYTES;
+                    const uint64_t off = (uint64_t)(st * (STAGE_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < QKV_BK / 16; ++k)
-                        mma_f16(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                                smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kt | k) != 0 ? 1u : 0u);
-                    tc_commit(&empty[st]);
+                    for (int k = 0; k < QKV_BK / 16; ++k) {
+                        if (PAIR) mma_f16_pair(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                        else mma_f16(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                    }
+                    if (PAIR) tc_commit_pair(&empty[st], 3);
+                    else tc_commit(&empty[st]);
                     if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                tc_commit(&accum_full[buf]);
+                if (PAIR) tc_commit_pair(&accum_full[buf], 3);
+                else tc_commit(&accum_full[buf]);
+            }
+        } else if (PAIR && lane == 0) {
+            // odd CTA of a pair: tell the even CTA when this CTA's stage has landed
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+                for (int kt = 0; kt < ksteps; ++kt) {
+                    ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    mbar_arrive_cluster(&full[st], 0);
+                    if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp >= 6 && warp < 10) {
@@ -363,13 +399,13 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
         const uint32_t sw = row & 7;
         uint32_t st = 0, ph = 0, j = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
             const uint32_t buf = j & 1u;
             float s0 = 0.0f, s1 = 0.0f;
             for (int kt = 0; kt < ksteps; ++kt) {
                 ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
-                const uint8_t *at = smem + st * QKV_STAGE_BYTES + row_base;
+                const uint8_t *at = smem + st * STAGE_BYTES + row_base;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
@@ -381,8 +417,7 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                         s1 = fmaf(f.y, f.y, s1);
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[st]);
+                stage_release(&empty[st], s0 + s1, lane);
                 if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
             }
             if (!ok) break;
@@ -402,9 +437,9 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
         const uint32_t my_sw = (uint32_t)((lane >> 1) & 3);
         uint32_t j = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++j) {
+        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
             const uint32_t buf = j & 1u;
-            const int m0 = (tile / tiles_n) * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
+            const int m0 = (tile / tiles_n) * TILE_M + (int)rank * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
             const int m = m0 + row;
             const int tok = m % p.S;
             // the four rows this lane writes out after the transpose through shared memory
@@ -494,17 +529,40 @@ qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                 }
             }
             tc_fence_before();
-            mbar_arrive(&accum_empty[buf]);
+            if (PAIR) {
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive(&accum_empty[buf]);
+                    else mbar_arrive_cluster(&accum_empty[buf], 0);
+                }
+            } else {
+                mbar_arrive(&accum_empty[buf]);
+            }
             mbar_arrive(&stats_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // neither CTA may exit while the other can still signal its barriers
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
 }
+
+__global__ void __launch_bounds__(QKVF_THREADS, 1)
+qkv_rope_tma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                    const QkvParams p, int tiles_m, int tiles_n, int nst) {
+    qkv_rope_tma_body<false>(x_map, w_map, p, tiles_m, tiles_n, nst);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(QKVF_THREADS, 1)
+qkv_rope_tma_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                         const QkvParams p, int tiles_m, int tiles_n, int nst) {
+    qkv_rope_tma_body<true>(x_map, w_map, p, tiles_m, tiles_n, nst);
+}
+
 
 // W'[n][k] = bf16(W[n][k] * ln_w[k])
 __global__ void fold_norm_weight_kernel(const __nv_bfloat16 *__restrict__ w, const float *__restrict__ ln_w,
@@ -668,14 +726,12 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
         if (rc) return rc;
         // shared memory: stages + barriers/stats + store staging + transposed RoPE table
         const int aux = 256 + 1024 + vb::QKVF_STAGING + 2 * (hd / 2) * S * 4;
-        int nst = 4;
-        while (nst > 2 && nst * vb::QKV_STAGE_BYTES + aux + 1024 > 227 * 1024) --nst;
-        const int fsmem = nst * vb::QKV_STAGE_BYTES + aux + 1024;
-        if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
         static bool fdone = false;
         static int n_sm = 0;
         if (!fdone) {
             VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024));
+            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024));
             int dev = 0;
             VB_CUDA(cudaGetDevice(&dev));
@@ -683,9 +739,36 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
             fdone = true;
         }
         const int tiles_m = (M + vb::QKV_BM - 1) / vb::QKV_BM, tiles_n = (n_total + vb::QKV_BN - 1) / vb::QKV_BN;
-        const int nt = tiles_m * tiles_n;
-        vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m, tiles_n,
-                                                                                      nst);
+        const int tiles_mp = (M + 2 * vb::QKV_BM - 1) / (2 * vb::QKV_BM), pairs = n_sm / 2;
+        // CTA pairs (256-row tiles) once they fill the machine at least as well as single CTAs do
+        const int waves1 = (tiles_m * tiles_n + n_sm - 1) / n_sm;
+        const int waves2 = pairs > 0 ? (tiles_mp * tiles_n + pairs - 1) / pairs : 1 << 30;
+        const int variant = vb::dense_gemm_variant();
+        const bool pair = variant == 3 || (variant == 0 && waves2 <= waves1 && tiles_mp * tiles_n >= pairs);
+        if (pair) {
+            const uint32_t wbox[2] = {vb::QKV_BK, vb::QKV_BN / 2};  // each CTA stages half of the weight tile
+            const uint64_t wdims[2] = {(uint64_t)H, (uint64_t)n_total};
+            const uint64_t wstrides[1] = {(uint64_t)H * 2};
+            rc = vb::make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, wqkv_bf16, wdims, wstrides, wbox,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return rc;
+            const int stage = vb::QKV_A_BYTES + vb::QKV_B_BYTES / 2;
+            int nst = 6;
+            while (nst > 2 && nst * stage + aux + 1024 > 227 * 1024) --nst;
+            const int fsmem = nst * stage + aux + 1024;
+            if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
+            const int nt = tiles_mp * tiles_n;
+            vb::qkv_rope_tma_pair_kernel<<<2 * (nt < pairs ? nt : pairs), vb::QKVF_THREADS, fsmem, cs>>>(
+                xmap, wmap, p, tiles_mp, tiles_n, nst);
+        } else {
+            int nst = 4;
+            while (nst > 2 && nst * vb::QKV_STAGE_BYTES + aux + 1024 > 227 * 1024) --nst;
+            const int fsmem = nst * vb::QKV_STAGE_BYTES + aux + 1024;
+            if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
+            const int nt = tiles_m * tiles_n;
+            vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m,
+                                                                                          tiles_n, nst);
+        }
         VB_CUDA(cudaGetLastError());
         return VLAB200_OK;
     }
@@ -710,3 +793,4 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
 }
 
 }  // extern "C"
+

@@ -95,6 +95,20 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity
     }
 }
 
+// Releases a TMA-filled stage that the warp has READ with ordinary loads: one arrival per warp.
+// TMA refills the stage through the async proxy as soon as the barrier completes.  An mbarrier
+// arrive orders the generic-proxy loads only against other generic-proxy accesses; without
+// fence.proxy.async between the loads and the arrival, lanes were observed reading bytes of the
+// NEXT fill (row sums off by one k-slice, different from run to run).  `consumed` is a value computed
+// from everything the lane loaded: the ballot cannot execute before every lane has it, and the
+// arrival takes the ballot's result as an operand, so no load is still in flight either.
+__device__ __forceinline__ void stage_release(uint64_t *bar, float consumed, int lane) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const unsigned done = __ballot_sync(0xffffffffu, consumed == consumed);
+    if (lane == 0)
+        asm volatile("{\n.reg .b64 t;\nmbarrier.arrive.shared::cta.b64 t, [%0];\n}" ::"r"(smem_u32(bar) + (done & 0u)) : "memory");
+}
+
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05 reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
