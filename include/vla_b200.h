@@ -261,7 +261,7 @@ VLAB200_API int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_lad
  * Same life cycle and argument meaning as bitvla_lm_cuda_init / _set_layer / _set_output_norm /
  * _forward / _free (src/kernels/bitvla/bitvla_lm_cuda.cu:314-393,668-725, layer body
  * bitvla_lm_cuda.cu:395-525); the layer struct has the field order of bitvla_lm_layer_cuda
- * (src/kernels/bitvla/bitvla_lm_cuda.h:204-225) so a pointer to one can be passed as is.
+ * (src/kernels/bitvla/bitvla_lm_cuda.h:211-229) so a pointer to one can be passed as is.
  * Differences: `max_batch` / `n_seq` run several sequences of equal length in one call (rows
  * [i*seq, (i+1)*seq) of d_in / d_out belong to sequence i, attention never crosses sequences);
  * set_layer copies the q, k, v packs into one fused matrix (device memory is allocated in init
