@@ -145,7 +145,7 @@ def build_pi0_engine(torch, vb, dev, n_obs, seed):
     return eng, x0, state
 
 
-def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None):
+def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_graph=False):
     """Times `steps` whole denoise loops over n_obs observations: device-resident and through host buffers."""
     eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, seed)
     sync = barrier or torch.cuda.synchronize
@@ -170,10 +170,35 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None):
         eng.denoise_host(x0h, sth, outh)
     e1.record()
     sync()
+    graph_ms = None
+    if n_obs <= 8 and allow_graph:
+        # small batches are launch- and latency-bound (943 launches per chunk): the same loop replayed as one CUDA graph
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                eng.denoise(x0, state)
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out_g = eng.denoise(x0, state)
+            g.replay()
+            torch.cuda.synchronize()
+            if torch.equal(out_g, eng.denoise(x0, state)):
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record()
+                for _ in range(max(steps, 5)):
+                    g.replay()
+                g1.record()
+                torch.cuda.synchronize()
+                graph_ms = g0.elapsed_time(g1) / max(steps, 5)
+        except RuntimeError:
+            graph_ms = None
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
     return {"total_ms": ev[0].elapsed_time(ev[-1]), "p50_ms": statistics.median(step_ms),
-            "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4}
+            "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4,
+            "graph_ms": graph_ms}
 
 
 def measure_ternary(torch, vb, dev, steps, warmup, only=None):
@@ -397,7 +422,7 @@ def main():
         n_global = args.pi0_obs * world if args.pi0_obs else 1024
         sampler = ClockSampler(local_rank)
         sampler.start()
-        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier)
+        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier, allow_graph=world == 1)
         clocks = sampler.stop()
         stats = torch.tensor([r["total_ms"], r["p50_ms"], r["e2e_ms"]], device=dev, dtype=torch.float64)
         if world > 1:
@@ -418,10 +443,12 @@ def main():
                                        "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32, 10 steps",
                            "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
                            "l2": "inputs larger than L2 (KV pages + expert weights > 126 MB per GPU)"},
-                "clocks": clocks, "gpu_launches": (10 * (3 + 18 * 5 + 1) + 3) * args.steps,
+                # per Euler step: 2 embedding kernels + 2 GEMMs, 18 layers x 5 kernels (6 on the few-row path), head + Euler
+                "clocks": clocks, "gpu_launches": (10 * (4 + 18 * (6 if n_obs * 51 <= 256 else 5) + 2) + 3) * args.steps,
                 "roofline": {"kernel": "whole loop (dense_gemm_kernel, qkv_rope_tma_kernel, attn_flash_kernel)",
                              "bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
                              "frac": tf / tf_peak, "peak_kind": "of measured (sustained)", "traffic": None},
+                "p50_chunk_latency_ms_cuda_graph": r.get("graph_ms"),
                 "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": r["h2d"],
                         "d2h_bytes_per_step": r["d2h"], "ms_per_step": e2e_ms},
             }

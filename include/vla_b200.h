@@ -226,7 +226,8 @@ VLAB200_API int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs
 /* Tiling of the bf16 GEMMs (the fused QKV projection, and inside the engine the O-projection, MLP,
  * embedding MLPs and action head):
  * 0 = chosen per call from the problem size (default), 1 = one CTA per 128 x 256 tile,
- * 2 = one CTA per 128 x 128 tile (QKV: same as 1), 3 = CTA pairs (tcgen05 cta_group::2) on 256 x 256 tiles.
+ * 2 = one CTA per 128 x 128 tile (QKV: same as 1), 3 = CTA pairs (tcgen05 cta_group::2) on 256 x 256 tiles,
+ * 4 = one CTA per 128 x 64 tile (QKV: same as 1).
  * All tilings give the same results bit for bit; the knob exists for tests and measurements.
  * Process-wide, not thread-safe against concurrent engine calls.  No counterpart in the reference. */
 VLAB200_API int32_t vlab200_set_gemm_tiling(int32_t tiling);

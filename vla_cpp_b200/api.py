@@ -77,7 +77,7 @@ def _stream():
 
 
 def set_gemm_tiling(tiling):
-    """0 = automatic, 1 = 128x256 tiles, 2 = 128x128 tiles, 3 = CTA pairs (testing / measurement knob)."""
+    """0 = automatic, 1 = 128x256 tiles, 2 = 128x128, 3 = CTA pairs, 4 = 128x64 (testing / measurement knob)."""
     _check(lib().vlab200_set_gemm_tiling(int(tiling)), "vlab200_set_gemm_tiling")
 
 

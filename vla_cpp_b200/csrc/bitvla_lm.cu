@@ -27,6 +27,7 @@
 #include <new>
 #include <vector>
 
+#include "gemm.h"
 #include "host_common.h"
 
 namespace vb {
@@ -122,8 +123,9 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(__nv_bfloat16 *__restri
     }
 }
 
-// qkv: bf16 [M][(n_q + 2 n_kv) hd] (q heads, k heads, v heads) -> q_out [n_seq][n_q][seq][hd]
-// rotated, K page rows rotated, V page rows copied.  Pages: [n_seq][n_kv][cap][hd].
+// qkv: bf16 [M][(n_q + 2 n_kv_proj) hd] (q heads, k heads, v heads) -> q_out [n_seq][n_q][seq][hd]
+// rotated, K page rows rotated, V page rows copied.  Pages: [n_seq][n_kv_store][cap][hd], token s of a
+// sequence goes to page row row0 + s.  n_kv_proj == 0: only q heads are present (cross-attention).
 // The rotation is computed in float on bf16 inputs and rounded once, as rope_neox_bf16_kernel
 // (bitvla_lm_cuda.cu:77-99) does after the head split (bitvla_lm_cuda.cu:441-446).
 __global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__restrict__ qkv,
@@ -132,11 +134,11 @@ __global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__
                                                          __nv_bfloat16 *__restrict__ q_out,
                                                          __nv_bfloat16 *__restrict__ k_pages,
                                                          __nv_bfloat16 *__restrict__ v_pages, int seq, int n_q,
-                                                         int n_kv, int hd, int cap) {
+                                                         int n_kv_proj, int n_kv_store, int hd, int cap, int row0) {
     const int m = blockIdx.x;
     const int sq = m / seq, s = m % seq;
     const int half = hd >> 1;
-    const int n_heads = n_q + 2 * n_kv;
+    const int n_heads = n_q + 2 * n_kv_proj;
     const __nv_bfloat16 *src = qkv + (size_t)m * n_heads * hd;
     for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
         const int head = i / half, k = i % half;
@@ -144,18 +146,29 @@ __global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__
         const float a = __bfloat162float(hp[k]), b = __bfloat162float(hp[k + half]);
         __nv_bfloat16 *dst;
         float lo = a, hi = b;
-        if (head < n_q + n_kv) {
+        if (head < n_q + n_kv_proj) {
             const float c = cos_t[(size_t)s * half + k], sn = sin_t[(size_t)s * half + k];
             lo = a * c - b * sn;
             hi = b * c + a * sn;
             dst = head < n_q ? q_out + (((size_t)sq * n_q + head) * seq + s) * hd
-                             : k_pages + (((size_t)sq * n_kv + (head - n_q)) * cap + s) * hd;
+                             : k_pages + (((size_t)sq * n_kv_store + (head - n_q)) * cap + row0 + s) * hd;
         } else {
-            dst = v_pages + (((size_t)sq * n_kv + (head - n_q - n_kv)) * cap + s) * hd;
+            dst = v_pages + (((size_t)sq * n_kv_store + (head - n_q - n_kv_proj)) * cap + row0 + s) * hd;
         }
         dst[k] = __float2bfloat16(lo);
         dst[k + half] = __float2bfloat16(hi);
     }
+}
+
+// Host entry for other translation units (the engine's few-row path).
+int rope_split(const void *qkv, const float *cos_t, const float *sin_t, void *q_out, void *k_pages, void *v_pages,
+               int M, int seq, int n_q, int n_kv_proj, int n_kv_store, int hd, int cap, int row0, cudaStream_t st) {
+    rope_split_kernel<<<M, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
+                                         static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
+                                         static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd, cap,
+                                         row0);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
 }
 
 static int gcd_int(int a, int b) {
@@ -355,11 +368,9 @@ extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void 
         rc = vlab200_ternary_linear(a8, l.qkv_packed.as<uint8_t>(), ctx->qkv.p, nullptr, s, l.qkv_ws.as<float>(),
                                     ctx->qkv_ws_num, M, hq + 2 * hkv, H, 0, st);
         if (rc) break;
-        vb::rope_split_kernel<<<M, 128, 0, st>>>(ctx->qkv.as<__nv_bfloat16>(), ctx->cos_t.as<float>(),
-                                                 ctx->sin_t.as<float>(), ctx->q.as<__nv_bfloat16>(),
-                                                 ctx->k_pages.as<__nv_bfloat16>(), ctx->v_pages.as<__nv_bfloat16>(),
-                                                 seq, ctx->n_q, ctx->n_kv, ctx->hd, ctx->max_seq);
-        VB_CUDA(cudaGetLastError());
+        rc = vb::rope_split(ctx->qkv.p, ctx->cos_t.as<float>(), ctx->sin_t.as<float>(), ctx->q.p, ctx->k_pages.p,
+                            ctx->v_pages.p, M, seq, ctx->n_q, ctx->n_kv, ctx->n_kv, ctx->hd, ctx->max_seq, 0, st);
+        if (rc) break;
         rc = vlab200_attention(&store, 0, ctx->q.p, ctx->att.p, seq, ctx->n_q, seq, /*mask_mode=*/0, nullptr, st);
         if (rc) break;
         rc = vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->att.p, nullptr, l.w.attn_sub_norm_w, ctx->eps, M, hq, a8, s, nullptr, st);

@@ -111,6 +111,10 @@ __global__ void euler_kernel(float *__restrict__ x, const float *__restrict__ v,
 
 }  // namespace vb
 
+namespace vb {
+constexpr int kFewRows = 256;  // suffix rows (n_obs * S) up to which the QKV projection takes the narrow-tile path
+}
+
 // ------------------------------------------------------------------------ engine --
 struct vlab200_engine {
     vlab200_policy_config c;
@@ -351,9 +355,23 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
             live.v_pages = e->v_pages.as<__nv_bfloat16>() + layer_off;
             live.n_layers = 1;
             const float *rope = self ? rs : rx;
-            if ((rc = vlab200_qkv_rope_append(&live, 0, e->hb.p, 0, nullptr, e->wqkv[l].p, rope, rope + (size_t)S * half,
-                                              c.rms_eps, S, H, c.n_q, self ? 1 : 0, e->q.p, cs)))
+            const int qkv_n = (c.n_q + (self ? 2 * c.n_kv : 0)) * hd;
+            if (M <= vb::kFewRows && qkv_n <= I) {
+                // Few rows: the fused kernel's 128 x 256 tiles leave most SMs idle (10 CTAs for one
+                // observation).  Project with the narrow-tile GEMM (RMS factor in its epilogue) into the
+                // MLP scratch buffer, which is free here, then rotate / split / append in one small kernel.
+                vb::GemmParams p{};
+                p.M = M; p.N = qkv_n; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 1;
+                p.eps = c.rms_eps; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
+                if ((rc = vb::dense_gemm(e->hb.p, H, e->wqkv[l].p, p, cs))) return rc;
+                if ((rc = vb::rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S,
+                                         c.n_q, self ? c.n_kv : 0, c.n_kv, hd, e->cap, e->P, cs)))
+                    return rc;
+            } else if ((rc = vlab200_qkv_rope_append(&live, 0, e->hb.p, 0, nullptr, e->wqkv[l].p, rope,
+                                                     rope + (size_t)S * half, c.rms_eps, S, H, c.n_q, self ? 1 : 0,
+                                                     e->q.p, cs))) {
                 return rc;
+            }
             const int kv_len = self ? e->P + S : e->P;
             const int mode = self ? (c.model == 0 ? 1 : 2) : 0;
             if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs))) return rc;

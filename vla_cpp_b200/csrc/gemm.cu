@@ -37,7 +37,7 @@ constexpr int G_A_BYTES = G_BM * 128;
 // more than the 128 B/clk the SM has).
 template <int BN, bool PAIR>
 struct GemmCfg {
-    static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
+    static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
     static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // weight rows this CTA stages
     static constexpr int B_BYTES = B_ROWS * 128;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
@@ -343,11 +343,11 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_c
     dense_gemm_body<256, true>(a_map, w_map, p, tiles_m, tiles_n);
 }
 
-// 0 = choose by cost; 1 / 2 / 3 force the 128 x 256, 128 x 128 and CTA-pair tilings (testing knob).
+// 0 = choose by cost; 1 / 2 / 3 / 4 force the 128 x 256, 128 x 128, CTA-pair and 128 x 64 tilings (testing knob).
 static int g_gemm_variant = 0;
 constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile relative to a lone CTA's 128 x 256 tile
 
-void dense_gemm_set_variant(int v) { g_gemm_variant = (v >= 0 && v <= 3) ? v : 0; }
+void dense_gemm_set_variant(int v) { g_gemm_variant = (v >= 0 && v <= 4) ? v : 0; }
 int dense_gemm_variant() { return g_gemm_variant; }
 
 // Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
@@ -380,18 +380,26 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         VB_CUDA(cudaGetDevice(&dev));
         VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     }
-    // Three tilings: one CTA per 128 x 256 tile, one CTA per 128 x 128 tile (twice the tiles when the
-    // problem has few), a CTA pair per 256 x 256 tile (half the shared-memory traffic per flop).  Costs
+    // Four tilings: one CTA per 128 x 256 tile, per 128 x 128 or 128 x 64 tile (more CTAs streaming the
+    // weights when the problem has few rows), a CTA pair per 256 x 256 tile (half the shared-memory traffic
+    // per flop).  Costs
     // in units of one 128 x 256 tile on one SM; the per-tile factors are measured ratios.
     const int tiles_m = (p.M + G_BM - 1) / G_BM, tiles_mp = (p.M + 2 * G_BM - 1) / (2 * G_BM);
     const int tn256 = (p.N + 255) / 256, tn128 = (p.N + 127) / 128, pairs = n_sm / 2;
     auto waves = [](int tiles, int units) { return (tiles + units - 1) / units; };
     const float cost256 = (float)waves(tiles_m * tn256, n_sm);
     const float cost128 = p.N > 128 ? 0.55f * waves(tiles_m * tn128, n_sm) : 1e30f;
+    const int tn64 = (p.N + 63) / 64;
+    const float cost64 = p.N > 64 ? 0.33f * waves(tiles_m * tn64, n_sm) : 1e30f;  // few rows: as many CTAs as possible stream W
     const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
     int variant = g_gemm_variant;
-    if (variant == 0) variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
+    if (variant == 0) {
+        variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
+        const float best = variant == 3 ? cost_pair : (variant == 2 ? cost128 : cost256);
+        if (cost64 < best) variant = 4;
+    }
     if (variant == 2 && p.N <= 128) variant = 1;
+    if (variant == 4 && p.N <= 64) variant = 1;
     const uint64_t wdims[2] = {(uint64_t)p.K, (uint64_t)p.N};
     const uint64_t wstrides[1] = {(uint64_t)p.K * 2};
     if (variant == 3) {
@@ -408,6 +416,18 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         const int nt = tiles_mp * tn256;
         dense_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), G_THREADS, GemmCfg<256, true>::SMEM, stream>>>(
             amap, wmap, p, tiles_mp, tn256);
+    } else if (variant == 4) {
+        const uint32_t box[2] = {G_BK, 64};
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        static bool done = false;
+        if (!done) {
+            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<64, false>::SMEM));
+            done = true;
+        }
+        const int nt = tiles_m * tn64;
+        dense_gemm_kernel<64><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<64, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn64);
     } else if (variant == 2) {
         const uint32_t box[2] = {G_BK, 128};
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
@@ -436,7 +456,7 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
 }  // namespace vb
 
 extern "C" int32_t vlab200_set_gemm_tiling(int32_t tiling) {
-    if (tiling < 0 || tiling > 3) return VLAB200_ERR_ARG;
+    if (tiling < 0 || tiling > 4) return VLAB200_ERR_ARG;
     vb::dense_gemm_set_variant(tiling);
     return VLAB200_OK;
 }

@@ -25,7 +25,12 @@ struct GemmParams {
 // A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream);
 
-// 0 = choose the tiling by cost (default); 1 / 2 / 3 force 128 x 256, 128 x 128, CTA pairs.
+// NeoX rotation + head split of a fused [M][(n_q + 2 n_kv_proj) hd] bf16 projection into the q buffer
+// [M / seq][n_q][seq][hd] and K / V page rows row0 + s (pages [.][n_kv_store][cap][hd]); bitvla_lm.cu.
+int rope_split(const void *qkv, const float *cos_t, const float *sin_t, void *q_out, void *k_pages, void *v_pages,
+               int M, int seq, int n_q, int n_kv_proj, int n_kv_store, int hd, int cap, int row0, cudaStream_t st);
+
+// 0 = choose the tiling by cost (default); 1 / 2 / 3 / 4 force 128 x 256, 128 x 128, CTA pairs, 128 x 64.
 void dense_gemm_set_variant(int v);
 int dense_gemm_variant();
 
