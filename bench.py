@@ -334,6 +334,8 @@ def run_reference(args, rank, world):
     from oracle import oracle_ffi as orc
 
     rng = np.random.default_rng(1)
+    # as the reference's default_cpu_threads() (src/arch.h:43-54): min(cores, 16), whatever the launcher exported
+    orc.set_num_threads(min(os.cpu_count() or 1, 16))
     threads = orc.num_threads()
     for _ in range(max(args.warmup, 0)):
         oracle_chunk(orc, rng, 1)
@@ -577,6 +579,7 @@ def main():
             from oracle import oracle_ffi as orc
 
             rng = np.random.default_rng(7)
+            orc.set_num_threads(min(os.cpu_count() or 1, 16))
             t1 = oracle_chunk(orc, rng, 1)
             n = max(1, min(16, int(args.cpu_seconds / max(t1, 1e-3))))
             tn = oracle_chunk(orc, rng, n)

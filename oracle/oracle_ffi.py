@@ -41,6 +41,10 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n):
+    lib().orc_set_num_threads(int(n))
+
+
 def f32_to_bf16_bits(x):
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint16)

@@ -73,6 +73,14 @@ ORC_API int orc_num_threads(void) {
     return 1;
 #endif
 }
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline asks for its threads itself. */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 
 /* ------------------------------------------------------- ternary / BitVLA -- */
 
