@@ -138,9 +138,11 @@ def test_q_only_projection_for_cross_attention_layers(oracle):
     assert qkv_case(oracle, SMOL, 2, seed=40, project_kv=False) < TOL
 
 
-def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads=None, poison=False, hd=64):
+def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads=None, poison=False, hd=64, tiling=0):
     import torch
     import vla_cpp_b200 as vb
+
+    vb.set_gemm_tiling(tiling)  # 1 / 3 also force the one-CTA / CTA-pair form of the streaming attention kernel
 
     rng = np.random.default_rng(seed)
     st = vb.KvStore(2, n_obs, n_kv, hd, P, S)
@@ -156,6 +158,7 @@ def attn_case(oracle, n_obs, n_q, n_kv, S, P, mask_mode, seed, cross=False, pads
     st.v[1].copy_(bf16_tensor(oracle, vd))
     pad_t = to_dev(np.asarray(pads, np.int32)) if pads is not None else None
     out = vb.attention(st, 1, bf16_tensor(oracle, q), S, n_q, kv_len, mask_mode, pad_ranges=pad_t)
+    vb.set_gemm_tiling(0)
     assert vb.device_status() == 0
     got = from_bf16(oracle, out)  # [n_obs][S][n_q*hd]
     assert np.isfinite(got).all()
@@ -211,31 +214,40 @@ def test_attention_rejects_unsupported(oracle):
     assert e.value.code == -1
 
 
+@pytest.mark.parametrize("tiling", [1, 3])  # one CTA per row tile / CTA pairs (two row tiles of an item per MMA)
 @pytest.mark.parametrize("mask_mode", [0, 1, 2])
-def test_attention_pi0_shape_streaming_kernel(oracle, mask_mode):
+def test_attention_pi0_shape_streaming_kernel(oracle, mask_mode, tiling):
     """8 q heads on 1 kv head, head_dim 256, 816 + 51 keys: 4 row tiles x 14 key blocks."""
     require_cuda()
-    assert attn_case(oracle, 2, 8, 1, 51, 816, mask_mode, seed=200 + mask_mode, hd=256) < TOL
+    assert attn_case(oracle, 2, 8, 1, 51, 816, mask_mode, seed=200 + mask_mode, hd=256, tiling=tiling) < TOL
 
 
-def test_attention_streaming_kernel_other_shapes(oracle):
+@pytest.mark.parametrize("tiling", [1, 3])
+def test_attention_streaming_kernel_other_shapes(oracle, tiling):
     require_cuda()
-    # BitVLA-LM-like heads (20q / 5kv, head_dim 128), bidirectional
-    assert attn_case(oracle, 2, 20, 5, 40, 300, 0, seed=210, hd=128) < TOL
+    # BitVLA-LM-like heads (20q / 5kv, head_dim 128), bidirectional; 160 rows per item = two row tiles
+    assert attn_case(oracle, 2, 20, 5, 40, 300, 0, seed=210, hd=128, tiling=tiling) < TOL
+    # an odd number of row tiles (3 x 128 >= 8 x 40 rows): the pair's second CTA has no rows in the last unit
+    assert attn_case(oracle, 2, 8, 1, 40, 200, 2, seed=216, hd=128, tiling=tiling) < TOL
+    # five observations x 4 row tiles: units wrap around the CTA pairs
+    assert attn_case(oracle, 5, 8, 1, 51, 130, 1, seed=217, hd=256, tiling=tiling) < TOL
     # head_dim 64 beyond the on-chip kernel's limits: 400 keys; and g*S = 408 rows
     assert attn_case(oracle, 2, 6, 2, 30, 370, 2, seed=211, hd=64) < TOL
     assert attn_case(oracle, 1, 8, 1, 51, 100, 1, seed=212, hd=64) < TOL
     # pad ranges, ragged key tail (kv_len % 64 != 0), cross-attention over a poisoned suffix
-    assert attn_case(oracle, 3, 8, 1, 51, 816, 1, seed=213, hd=256, pads=[(700, 816), (0, 0), (64, 128)]) < TOL
-    assert attn_case(oracle, 2, 8, 1, 51, 777, 0, seed=214, hd=256, cross=True, poison=True) < TOL
-    assert attn_case(oracle, 1, 8, 1, 5, 3, 2, seed=215, hd=256) < TOL
+    assert attn_case(oracle, 3, 8, 1, 51, 816, 1, seed=213, hd=256, pads=[(700, 816), (0, 0), (64, 128)], tiling=tiling) < TOL
+    assert attn_case(oracle, 2, 8, 1, 51, 777, 0, seed=214, hd=256, cross=True, poison=True, tiling=tiling) < TOL
+    assert attn_case(oracle, 1, 8, 1, 5, 3, 2, seed=215, hd=256, tiling=tiling) < TOL
 
 
-def test_attention_streaming_kernel_large_score_spread(oracle):
+@pytest.mark.parametrize("tiling", [1, 3])
+def test_attention_streaming_kernel_large_score_spread(oracle, tiling):
     """Keys whose scores grow along the sequence force the lazy running-maximum update (and the
     rescale of O through TMEM) to trigger."""
     torch = require_cuda()
     import vla_cpp_b200 as vb
+
+    vb.set_gemm_tiling(tiling)
 
     hd, n_q, n_kv, S, P, n_obs = 256, 8, 1, 51, 816, 1
     rng = np.random.default_rng(300)
@@ -247,6 +259,7 @@ def test_attention_streaming_kernel_large_score_spread(oracle):
     st.k[0].copy_(bf16_tensor(oracle, k))
     st.v[0].copy_(bf16_tensor(oracle, v))
     out = vb.attention(st, 0, bf16_tensor(oracle, q), S, n_q, P + S, vb.MASK_PI0)
+    vb.set_gemm_tiling(0)
     assert vb.device_status() == 0
     ref = oracle.attention(q[0].transpose(1, 0, 2), k[0].transpose(1, 0, 2), v[0].transpose(1, 0, 2), P, 1)
     assert rel_l2(from_bf16(oracle, out)[0], ref) < TOL

@@ -17,6 +17,7 @@
 // matrix and two permuted copies of K/V in HBM every layer-step), mask src/models/pi0.cpp:640-651.
 #include <cuda_bf16.h>
 
+#include "gemm.h"
 #include "host_common.h"
 #include "tc5.cuh"
 
@@ -345,6 +346,408 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------ CTA pairs --
+// The same algorithm on clusters of two CTAs (tcgen05 cta_group::2, M = 256): the pair works on two
+// 128-row tiles of ONE item, so a K / V block is fetched once per pair -- each CTA stages half of it
+// (K: 32 of the block's 64 keys, V: half of the head dimension) -- and one MMA instruction serves both
+// row tiles.  That halves the L2 -> SM traffic per row (the single-CTA kernel re-streams K / V for every
+// row tile and was at the L2 bandwidth the GEMMs also meet) and the MMA instructions per row (a thread
+// issues at most one tcgen05.mma every ~64 cycles, twice the duration of an N = 64 MMA).  Rings are 4
+// deep.  The even CTA issues; commits are multicast to both CTAs; the odd CTA's MMA warp forwards "my
+// Q tile / K half / V half has landed", its softmax warps arrive on the even CTA's p_full / o_free.
+#ifdef VB_TRACE
+__device__ long long g_fp_trace[2][64][8];
+#define FP_STAMP(who, slot)                                                                             \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && jb < 64 && ((who) == 0 || (warp == 0 && lane == 0)))                      \
+            g_fp_trace[who][jb][slot] = clock64();                                                      \
+    } while (0)
+#else
+#define FP_STAMP(who, slot) do { } while (0)
+#endif
+constexpr int FP_STAGES = 4;  // K / V ring depth
+constexpr int FP_NS = 4;      // S / P buffers in TMEM: Q K^T runs up to three blocks ahead of P V
+constexpr int FP_LA = 3;
+constexpr int FP_THREADS = 352;  // warps 0-7 softmax (quarter = warp & 3, column half = warp >> 2), 8 loader, 9 Q K^T issuer, 10 P V issuer
+constexpr int FP_LOADER_WARP = 8, FP_MMA_WARP = 9, FP_PV_WARP = 10;
+
+template <int HD>
+struct FlashPairSmem {
+    static constexpr int CB = HD / 64;                 // 64-element column blocks of the head dimension
+    static constexpr int CBH = HD / 128;               // column blocks of V this CTA stages
+    static constexpr int Q_BYTES = CB * 128 * 128;     // [CB][128 rows][128 B]
+    static constexpr int K_BYTES = CB * 32 * 128;      // [CB][32 keys][128 B]
+    static constexpr int V_BYTES = CBH * FA_BKV * 128; // [CBH][64 keys][128 B]
+    static constexpr int K_OFF = Q_BYTES, V_OFF = K_OFF + FP_STAGES * K_BYTES;
+    static constexpr int BAR_OFF = V_OFF + FP_STAGES * V_BYTES;
+    static constexpr int XCH_OFF = BAR_OFF + 512;      // float [2 halves][128 rows] block maxima, then row sums
+    static constexpr int TOTAL = XCH_OFF + 2048 + 1024;
+    static constexpr int O_COLS = HD;
+    static constexpr int TMEM_COLS = 512;              // O [0, HD), then FP_NS S buffers of 64 columns
+    static_assert(HD + FP_NS * 64 <= 512, "TMEM");
+};
+
+__device__ __forceinline__ void mma_f16_tmem_a_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int HD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FP_THREADS, 1)
+attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, const FlashParams p) {
+    using L = FlashPairSmem<HD>;
+    extern __shared__ uint8_t fa_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *q_full = bars, *q_free = bars + 1, *o_done = bars + 2, *o_free = bars + 3;
+    uint64_t *k_full = bars + 4, *k_free = bars + 8, *v_full = bars + 12, *v_free = bars + 16;  // [FP_STAGES]
+    uint64_t *s_full = bars + 20, *p_full = bars + 24, *pv_done = bars + 28;                    // [FP_NS]
+    uint64_t *pair_bar = bars + 32;  // [4] the two softmax warps of a lane quarter meet here (64 arrivals)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 36);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+    const WaitCtx wc{abort_flag, p.status};
+    const int nb = p.n_blocks;
+    const int n_mt2 = (p.n_mt + 1) >> 1;                 // pairs of row tiles per item
+    const int n_units = (p.n_units / p.n_mt) * n_mt2;    // (item, tile pair)
+    const uint32_t both = rank == 0 ? 2u : 1u;           // even CTA: own TMA + the odd CTA's forward
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, both);
+        mbar_init(q_free, 1);
+        mbar_init(o_done, 1);
+        mbar_init(o_free, 16);  // one arrival per softmax warp of both CTAs (used in the even CTA)
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
+        for (int i = 0; i < FP_STAGES; ++i) {
+            mbar_init(&k_full[i], both);
+            mbar_init(&k_free[i], 1);
+            mbar_init(&v_full[i], both);
+            mbar_init(&v_free[i], 1);
+        }
+        for (int i = 0; i < FP_NS; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 16);
+            mbar_init(&pv_done[i], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them remotely
+    if (warp == FP_MMA_WARP) {
+        tmem_alloc_pair(tmem_slot, L::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == FP_LOADER_WARP) {
+        // ----------------------------------------------------------------- loader (each CTA its own halves)
+        if (lane == 0) {
+            tma_prefetch_desc(&q_map);
+            tma_prefetch_desc(&k_map);
+            tma_prefetch_desc(&v_map);
+            uint32_t ui = 0, jb = 0;
+            bool ok = true;
+            for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
+                const int item = unit / n_mt2, mt = (unit % n_mt2) * 2 + (int)rank;
+                const int obs = item / p.n_kv, kvh = item % p.n_kv;
+                const int page = p.page0 + item;
+                const int qrow0 = (obs * p.n_q + kvh * p.g) * p.S + mt * 128;
+                ok = mbar_wait(q_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                if (!ok) break;
+                mbar_expect_tx(q_full, L::Q_BYTES);
+                for (int cb = 0; cb < L::CB; ++cb) tma_load_2d(smem + cb * 16384, &q_map, q_full, cb * 64, qrow0);
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    const int st = jb % FP_STAGES;
+                    const uint32_t ph = (jb / FP_STAGES) & 1u;
+                    ok = mbar_wait(&k_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&k_full[st], L::K_BYTES);
+                    for (int cb = 0; cb < L::CB; ++cb)
+                        tma_load_3d(smem + L::K_OFF + st * L::K_BYTES + cb * 4096, &k_map, &k_full[st], cb * 64,
+                                    j * FA_BKV + (int)rank * 32, page);
+                    ok = mbar_wait(&v_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(&v_full[st], L::V_BYTES);
+                    for (int cb = 0; cb < L::CBH; ++cb)
+                        tma_load_3d(smem + L::V_OFF + st * L::V_BYTES + cb * 8192, &v_map, &v_full[st],
+                                    ((int)rank * L::CBH + cb) * 64, j * FA_BKV, page);
+                }
+            }
+        }
+    } else if (warp == FP_MMA_WARP) {
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------- MMA issuer (even CTA)
+            constexpr uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 256, FA_BKV);
+            const uint32_t q_addr = smem_u32(smem);
+            const uint64_t q_desc0 = smem_desc_sw128(q_addr, 16, 1024);
+            const uint64_t k_desc0 = smem_desc_sw128(q_addr + L::K_OFF, 16, 1024);
+            uint32_t ui = 0, jb = 0;
+            bool ok = true;
+            auto issue_s = [&](uint32_t jbx) {  // S block with global block counter jbx
+                const uint32_t st = jbx % FP_STAGES;
+                const uint64_t k_desc = k_desc0 + (uint64_t)(st * (L::K_BYTES >> 4));
+                const uint32_t d = tmem_base + L::O_COLS + (jbx % FP_NS) * 64;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    mma_f16_pair(d, q_desc0 + (uint64_t)((kk >> 2) * 1024 + (kk & 3) * 2),
+                                 k_desc + (uint64_t)((kk >> 2) * 256 + (kk & 3) * 2), idesc_s, kk != 0 ? 1u : 0u);
+                tc_commit_pair(&s_full[jbx % FP_NS], 3);
+                tc_commit_pair(&k_free[st], 3);
+            };
+            // S block jbx may be issued once its K half-blocks have landed and the P V of the block that
+            // used the same TMEM buffer (jbx - FP_NS) has finished.  This thread issues only the Q K^T MMAs
+            // (16 per block, the longer stream); the P V MMAs come from a thread of their own (warp
+            // FP_PV_WARP): one thread issuing both spent ~2500 cycles per block, twice the tensor time.
+            auto ready_s = [&](uint32_t jbx) -> bool {
+                bool r = mbar_wait(&k_full[jbx % FP_STAGES], (jbx / FP_STAGES) & 1u, wc, DEV_TIMEOUT_FULL);
+                if (r && jbx >= FP_NS) r = mbar_wait(&pv_done[jbx % FP_NS], ((jbx / FP_NS) - 1u) & 1u, wc, DEV_TIMEOUT_FULL);
+                return r;
+            };
+            for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
+                ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    FP_STAMP(0, 0);
+                    ok = ready_s(jb);
+                    if (!ok) break;
+                    tc_fence_after();
+                    FP_STAMP(0, 1);
+                    issue_s(jb);
+                    FP_STAMP(0, 2);
+                }
+                if (!ok) break;
+                tc_commit_pair(q_free, 3);  // the unit's last S block has been issued
+            }
+        } else if (lane == 0) {
+            // ------------------------------------------------------------- odd CTA: forward "landed" to the even CTA
+            uint32_t ui = 0, jb = 0;
+            bool ok = true;
+            for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
+                ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                mbar_arrive_cluster(q_full, 0);
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    const uint32_t st = jb % FP_STAGES, ph = (jb / FP_STAGES) & 1u;
+                    ok = mbar_wait(&k_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    mbar_arrive_cluster(&k_full[st], 0);
+                    ok = mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    mbar_arrive_cluster(&v_full[st], 0);
+                }
+            }
+        }
+    } else if (warp == FP_PV_WARP) {
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------- P V issuer (even CTA)
+            constexpr uint32_t idesc_o = make_idesc(1, 1, 1, 0, 1, 256, HD);
+            const uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem) + L::V_OFF, 8192, 1024);
+            uint32_t ui = 0, jb = 0;
+            bool ok = true;
+            for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
+                for (int j = 0; j < nb; ++j, ++jb) {
+                    const uint32_t sb = jb % FP_NS, sph = (jb / FP_NS) & 1u;         // S / P buffer and its phase
+                    const uint32_t st = jb % FP_STAGES, ph = (jb / FP_STAGES) & 1u;  // K / V stage and its phase
+                    ok = mbar_wait(&p_full[sb], sph, wc, DEV_TIMEOUT_FULL);
+                    if (ok) ok = mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_FULL);
+                    if (ok && j == 0) ok = mbar_wait(o_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
+                    FP_STAMP(0, 3);
+                    const uint64_t v_desc = v_desc0 + (uint64_t)(st * (L::V_BYTES >> 4));
+                    const uint32_t p_tmem = tmem_base + L::O_COLS + sb * 64;
+#pragma unroll
+                    for (int k16 = 0; k16 < FA_BKV / 16; ++k16)
+                        mma_f16_tmem_a_pair(tmem_base, p_tmem + (uint32_t)(k16 * 8), v_desc + (uint64_t)(k16 * 128), idesc_o,
+                                            (j | k16) != 0 ? 1u : 0u);
+                    tc_commit_pair(&pv_done[sb], 3);
+                    tc_commit_pair(&v_free[st], 3);
+                    FP_STAMP(0, 4);
+                }
+                if (!ok) break;
+                tc_commit_pair(o_done, 3);
+            }
+        }
+    } else {
+        // ----------------------------------------------------------------- softmax / epilogue (own row tile)
+        // Two warps per TMEM lane quarter: warp `half` takes 32 of a block's 64 key columns of its rows (one
+        // row per lane), half of the O columns when O is rescaled and half of them in the epilogue.  The two
+        // exchange block maxima and row sums through shared memory; their meeting (an mbarrier, so that the
+        // wait is bounded) also orders half 1's P store over columns that half 0 has just read.
+        const int qtr = warp & 3, half = warp >> 2;
+        const uint32_t lane_sel = (uint32_t)(qtr * 32) << 16;
+        float *xch = reinterpret_cast<float *>(smem + L::XCH_OFF);
+        const int my_slot = qtr * 32 + lane;
+        uint32_t pair_n = 0;
+        auto pair_sync = [&]() -> bool {
+            mbar_arrive(&pair_bar[qtr]);
+            return mbar_wait(&pair_bar[qtr], (pair_n++) & 1u, wc, DEV_TIMEOUT_MISC);
+        };
+        const int n_suffix_cols = p.kv_len - p.prefix_len;
+        auto arrive_even = [&](uint64_t *bar) {  // one arrival per warp on the even CTA's barrier
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(bar);
+                else mbar_arrive_cluster(bar, 0);
+            }
+        };
+        uint32_t ui = 0, jb = 0;
+        bool ok = true;
+        for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
+            const int item = unit / n_mt2, mt = (unit % n_mt2) * 2 + (int)rank;
+            const int obs = item / p.n_kv, kvh = item % p.n_kv;
+            const int row = mt * 128 + qtr * 32 + lane;
+            const bool row_ok = row < p.R;
+            const int head_l = row_ok ? row / p.S : 0, tok = row_ok ? row % p.S : 0;
+            int pad_lo = 0, pad_hi = 0;
+            if (p.pad) {
+                pad_lo = p.pad[2 * obs];
+                pad_hi = p.pad[2 * obs + 1];
+            }
+            int limit = n_suffix_cols;
+            if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
+            else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+            const int jmax = p.prefix_len + limit;
+            int clean_end = p.prefix_len;
+            if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
+            const int pad_w = pad_hi - pad_lo;
+            float m_used = -INFINITY;  // running maximum in log2 units (lazy), identical in both halves
+            float l_sum = 0.0f;        // this half's part of the row sum
+            for (int j = 0; j < nb; ++j, ++jb) {
+                const uint32_t sb = jb % FP_NS, sph = (jb / FP_NS) & 1u;
+                const uint32_t s_addr = tmem_base + L::O_COLS + sb * 64 + lane_sel;
+                FP_STAMP(1, 0);
+                ok = mbar_wait(&s_full[sb], sph, wc, DEV_TIMEOUT_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                FP_STAMP(1, 1);
+                uint32_t sa[32];
+                tmem_ld32(s_addr + (uint32_t)(half * 32), sa);
+                tmem_ld_wait();
+                FP_STAMP(1, 2);
+                const int c0 = j * FA_BKV + half * 32;
+                const bool clean = j * FA_BKV + FA_BKV <= clean_end;
+                if (!clean) {
+                    const int rel_jmax = jmax - c0, rel_pad = pad_lo - c0;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
+                        sa[e] = v0 ? sa[e] : 0xff800000u;
+                    }
+                }
+                float t[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    t[e] = fmaxf(fmaxf(__uint_as_float(sa[4 * e]), __uint_as_float(sa[4 * e + 1])),
+                                 fmaxf(__uint_as_float(sa[4 * e + 2]), __uint_as_float(sa[4 * e + 3])));
+                float bm = fmaxf(fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])), fmaxf(fmaxf(t[4], t[5]), fmaxf(t[6], t[7])));
+                xch[half * 128 + my_slot] = bm;
+                ok = pair_sync();
+                if (!ok) break;
+                bm = fmaxf(bm, xch[(half ^ 1) * 128 + my_slot]) * p.scale_log2;
+                ok = pair_sync();  // the slot is rewritten in the next block
+                if (!ok) break;
+                FP_STAMP(1, 3);
+                float factor = 1.0f;
+                const bool raise = bm > m_used + 8.0f;
+                if (raise) {
+                    factor = (m_used == -INFINITY) ? 0.0f : fa_ex2(m_used - bm);
+                    m_used = bm;
+                    l_sum *= factor;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                    const uint32_t jp = jb - 1;
+                    ok = mbar_wait(&pv_done[jp % FP_NS], (jp / FP_NS) & 1u, wc, DEV_TIMEOUT_ACCUM);
+                    if (!ok) break;
+                    tc_fence_after();
+                    for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * factor);
+                        tmem_st32(tmem_base + lane_sel + (uint32_t)c, ov);
+                    }
+                    tmem_st_wait();
+                }
+                const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+                uint32_t pk[16];
+                float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const float p0 = fa_ex2(fmaf(__uint_as_float(sa[e]), p.scale_log2, -mref));
+                    const float p1 = fa_ex2(fmaf(__uint_as_float(sa[e + 1]), p.scale_log2, -mref));
+                    s0 += p0;
+                    s1 += p1;
+                    pk[e >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
+                }
+                l_sum += s0 + s1;
+                tmem_st16(s_addr + (uint32_t)(half * 16), pk);  // P_j (64 keys, bf16) over the first 32 columns of S_j
+                tmem_st_wait();
+                tc_fence_before();
+                arrive_even(&p_full[sb]);
+                FP_STAMP(1, 4);
+            }
+            if (!ok) break;
+            // ---- epilogue: O / l -> bf16 -> out (each half stores half of the head dimension) ----
+            xch[256 + half * 128 + my_slot] = l_sum;
+            ok = mbar_wait(o_done, ui & 1u, wc, DEV_TIMEOUT_ACCUM);
+            if (!ok) break;
+            tc_fence_after();
+            ok = pair_sync();
+            if (!ok) break;
+            const float inv = 1.0f / (l_sum + xch[256 + (half ^ 1) * 128 + my_slot]);
+            __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
+            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                tmem_ld_wait();
+                if (row_ok) {
+                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + c);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[8 * q4 + 2 * e]) * inv,
+                                                                           __uint_as_float(ov[8 * q4 + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        d4[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            // (the row-sum slots are next written after at least two more meetings of the pair)
+            tc_fence_before();
+            arrive_even(o_free);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA may exit while the other can still signal its barriers
+    if (warp == FP_MMA_WARP) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, L::TMEM_COLS);
+    }
+}
+
 template <int HD>
 static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
                         int mask_mode, const int32_t *pad_ranges, cudaStream_t stream) {
@@ -393,6 +796,31 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
         VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
         attr_done = true;
     }
+    if constexpr (HD >= 128) {
+        // CTA pairs once an item has two row tiles and the pairs fill the machine (or when forced for tests)
+        const int n_pair_units = st->n_obs * st->n_kv * ((p.n_mt + 1) / 2), pairs = n_sm / 2;
+        const int forced = dense_gemm_variant();
+        if (p.n_mt >= 2 && forced != 1 && (forced == 3 || n_pair_units >= pairs)) {
+            using LP = FlashPairSmem<HD>;
+            CUtensorMap kmap32;
+            const uint64_t dims[3] = {(uint64_t)HD, (uint64_t)kv_len, (uint64_t)st->n_layers * st->n_obs * st->n_kv};
+            const uint64_t strides[2] = {(uint64_t)HD * 2, (uint64_t)st->cap * HD * 2};
+            const uint32_t box[3] = {64, 32, 1};  // each CTA stages 32 of a block's 64 keys
+            int rc = make_tensor_map(&kmap32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->k_pages, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return rc;
+            static bool pair_attr_done = false;
+            if (!pair_attr_done) {
+                VB_CUDA(cudaFuncSetAttribute(attn_flash_pair_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             LP::TOTAL));
+                pair_attr_done = true;
+            }
+            const int ncl = n_pair_units < pairs ? n_pair_units : pairs;
+            attn_flash_pair_kernel<HD><<<2 * ncl, FP_THREADS, LP::TOTAL, stream>>>(qmap, kmap32, vmap, p);
+            VB_CUDA(cudaGetLastError());
+            return VLAB200_OK;
+        }
+    }
     const int grid = p.n_units < n_sm ? p.n_units : n_sm;
     attn_flash_kernel<HD><<<grid, FA_THREADS, L::TOTAL, stream>>>(qmap, kmap, vmap, p);
     VB_CUDA(cudaGetLastError());
@@ -408,3 +836,9 @@ int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *
 }
 
 }  // namespace vb
+
+#ifdef VB_TRACE
+extern "C" __attribute__((visibility("default"))) int vlab200_flash_pair_trace(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, vb::g_fp_trace, sizeof(long long) * 2 * 64 * 8);
+}
+#endif
