@@ -365,26 +365,26 @@ __device__ long long g_fp_trace[2][64][8];
 #else
 #define FP_STAMP(who, slot) do { } while (0)
 #endif
-constexpr int FP_STAGES = 4;  // K / V ring depth
-constexpr int FP_NS = 4;      // S / P buffers in TMEM: Q K^T runs up to three blocks ahead of P V
-constexpr int FP_LA = 3;
+constexpr int FP_BKV = 128;   // keys per block: 16 Q K^T MMAs (N = 128) serve twice the keys of the one-CTA kernel's N = 64
 constexpr int FP_THREADS = 352;  // warps 0-7 softmax (quarter = warp & 3, column half = warp >> 2), 8 loader, 9 Q K^T issuer, 10 P V issuer
 constexpr int FP_LOADER_WARP = 8, FP_MMA_WARP = 9, FP_PV_WARP = 10;
 
 template <int HD>
 struct FlashPairSmem {
+    static constexpr int STAGES = HD == 256 ? 2 : 4;   // K / V ring depth (what fits beside the Q tile)
+    static constexpr int NS = (512 - HD) / FP_BKV;     // S / P buffers of 128 TMEM columns behind O: Q K^T runs NS - 1 blocks ahead
     static constexpr int CB = HD / 64;                 // 64-element column blocks of the head dimension
     static constexpr int CBH = HD / 128;               // column blocks of V this CTA stages
     static constexpr int Q_BYTES = CB * 128 * 128;     // [CB][128 rows][128 B]
-    static constexpr int K_BYTES = CB * 32 * 128;      // [CB][32 keys][128 B]
-    static constexpr int V_BYTES = CBH * FA_BKV * 128; // [CBH][64 keys][128 B]
-    static constexpr int K_OFF = Q_BYTES, V_OFF = K_OFF + FP_STAGES * K_BYTES;
-    static constexpr int BAR_OFF = V_OFF + FP_STAGES * V_BYTES;
+    static constexpr int K_BYTES = CB * (FP_BKV / 2) * 128;  // [CB][64 keys][128 B]: this CTA's half of the block's keys
+    static constexpr int V_BYTES = CBH * FP_BKV * 128;       // [CBH][128 keys][128 B]: this CTA's half of the head dimension
+    static constexpr int K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * K_BYTES;
+    static constexpr int BAR_OFF = V_OFF + STAGES * V_BYTES;
     static constexpr int XCH_OFF = BAR_OFF + 512;      // float [2 halves][128 rows] block maxima, then row sums
     static constexpr int TOTAL = XCH_OFF + 2048 + 1024;
     static constexpr int O_COLS = HD;
-    static constexpr int TMEM_COLS = 512;              // O [0, HD), then FP_NS S buffers of 64 columns
-    static_assert(HD + FP_NS * 64 <= 512, "TMEM");
+    static constexpr int TMEM_COLS = 512;              // O [0, HD), then NS S buffers of 128 columns
+    static_assert(HD + NS * FP_BKV <= 512 && NS >= 2, "TMEM");
 };
 
 __device__ __forceinline__ void mma_f16_tmem_a_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -404,6 +404,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FP_THREADS, 1)
 attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const FlashParams p) {
     using L = FlashPairSmem<HD>;
+    constexpr int FP_STAGES = L::STAGES, FP_NS = L::NS;
     extern __shared__ uint8_t fa_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
@@ -419,7 +420,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const uint32_t rank = cluster_ctarank();
     const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
     const WaitCtx wc{abort_flag, p.status};
-    const int nb = p.n_blocks;
+    const int nb = (p.kv_len + FP_BKV - 1) / FP_BKV;
     const int n_mt2 = (p.n_mt + 1) >> 1;                 // pairs of row tiles per item
     const int n_units = (p.n_units / p.n_mt) * n_mt2;    // (item, tile pair)
     const uint32_t both = rank == 0 ? 2u : 1u;           // even CTA: own TMA + the odd CTA's forward
@@ -480,21 +481,21 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     if (!ok) break;
                     mbar_expect_tx(&k_full[st], L::K_BYTES);
                     for (int cb = 0; cb < L::CB; ++cb)
-                        tma_load_3d(smem + L::K_OFF + st * L::K_BYTES + cb * 4096, &k_map, &k_full[st], cb * 64,
-                                    j * FA_BKV + (int)rank * 32, page);
+                        tma_load_3d(smem + L::K_OFF + st * L::K_BYTES + cb * 8192, &k_map, &k_full[st], cb * 64,
+                                    j * FP_BKV + (int)rank * (FP_BKV / 2), page);
                     ok = mbar_wait(&v_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_expect_tx(&v_full[st], L::V_BYTES);
                     for (int cb = 0; cb < L::CBH; ++cb)
-                        tma_load_3d(smem + L::V_OFF + st * L::V_BYTES + cb * 8192, &v_map, &v_full[st],
-                                    ((int)rank * L::CBH + cb) * 64, j * FA_BKV, page);
+                        tma_load_3d(smem + L::V_OFF + st * L::V_BYTES + cb * (FP_BKV * 128), &v_map, &v_full[st],
+                                    ((int)rank * L::CBH + cb) * 64, j * FP_BKV, page);
                 }
             }
         }
     } else if (warp == FP_MMA_WARP) {
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------- MMA issuer (even CTA)
-            constexpr uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 256, FA_BKV);
+            constexpr uint32_t idesc_s = make_idesc(1, 1, 1, 0, 0, 256, FP_BKV);
             const uint32_t q_addr = smem_u32(smem);
             const uint64_t q_desc0 = smem_desc_sw128(q_addr, 16, 1024);
             const uint64_t k_desc0 = smem_desc_sw128(q_addr + L::K_OFF, 16, 1024);
@@ -503,11 +504,11 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             auto issue_s = [&](uint32_t jbx) {  // S block with global block counter jbx
                 const uint32_t st = jbx % FP_STAGES;
                 const uint64_t k_desc = k_desc0 + (uint64_t)(st * (L::K_BYTES >> 4));
-                const uint32_t d = tmem_base + L::O_COLS + (jbx % FP_NS) * 64;
+                const uint32_t d = tmem_base + L::O_COLS + (jbx % FP_NS) * FP_BKV;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk)
                     mma_f16_pair(d, q_desc0 + (uint64_t)((kk >> 2) * 1024 + (kk & 3) * 2),
-                                 k_desc + (uint64_t)((kk >> 2) * 256 + (kk & 3) * 2), idesc_s, kk != 0 ? 1u : 0u);
+                                 k_desc + (uint64_t)((kk >> 2) * 512 + (kk & 3) * 2), idesc_s, kk != 0 ? 1u : 0u);
                 tc_commit_pair(&s_full[jbx % FP_NS], 3);
                 tc_commit_pair(&k_free[st], 3);
             };
@@ -558,7 +559,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------- P V issuer (even CTA)
             constexpr uint32_t idesc_o = make_idesc(1, 1, 1, 0, 1, 256, HD);
-            const uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem) + L::V_OFF, 8192, 1024);
+            const uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem) + L::V_OFF, FP_BKV * 128, 1024);
             uint32_t ui = 0, jb = 0;
             bool ok = true;
             for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
@@ -572,9 +573,9 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tc_fence_after();
                     FP_STAMP(0, 3);
                     const uint64_t v_desc = v_desc0 + (uint64_t)(st * (L::V_BYTES >> 4));
-                    const uint32_t p_tmem = tmem_base + L::O_COLS + sb * 64;
+                    const uint32_t p_tmem = tmem_base + L::O_COLS + sb * FP_BKV;
 #pragma unroll
-                    for (int k16 = 0; k16 < FA_BKV / 16; ++k16)
+                    for (int k16 = 0; k16 < FP_BKV / 16; ++k16)
                         mma_f16_tmem_a_pair(tmem_base, p_tmem + (uint32_t)(k16 * 8), v_desc + (uint64_t)(k16 * 128), idesc_o,
                                             (j | k16) != 0 ? 1u : 0u);
                     tc_commit_pair(&pv_done[sb], 3);
@@ -632,31 +633,36 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             float l_sum = 0.0f;        // this half's part of the row sum
             for (int j = 0; j < nb; ++j, ++jb) {
                 const uint32_t sb = jb % FP_NS, sph = (jb / FP_NS) & 1u;
-                const uint32_t s_addr = tmem_base + L::O_COLS + sb * 64 + lane_sel;
+                const uint32_t s_addr = tmem_base + L::O_COLS + sb * FP_BKV + lane_sel;
                 FP_STAMP(1, 0);
                 ok = mbar_wait(&s_full[sb], sph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
                 FP_STAMP(1, 1);
-                uint32_t sa[32];
-                tmem_ld32(s_addr + (uint32_t)(half * 32), sa);
+                uint32_t sa[32], sc[32];  // this half's 64 of the block's 128 key columns
+                tmem_ld32(s_addr + (uint32_t)(half * 64), sa);
+                tmem_ld32(s_addr + (uint32_t)(half * 64 + 32), sc);
                 tmem_ld_wait();
                 FP_STAMP(1, 2);
-                const int c0 = j * FA_BKV + half * 32;
-                const bool clean = j * FA_BKV + FA_BKV <= clean_end;
+                const int c0 = j * FP_BKV + half * 64;
+                const bool clean = j * FP_BKV + FP_BKV <= clean_end;
                 if (!clean) {
                     const int rel_jmax = jmax - c0, rel_pad = pad_lo - c0;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
                         const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
+                        const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
                         sa[e] = v0 ? sa[e] : 0xff800000u;
+                        sc[e] = v1 ? sc[e] : 0xff800000u;
                     }
                 }
                 float t[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
-                    t[e] = fmaxf(fmaxf(__uint_as_float(sa[4 * e]), __uint_as_float(sa[4 * e + 1])),
-                                 fmaxf(__uint_as_float(sa[4 * e + 2]), __uint_as_float(sa[4 * e + 3])));
+                    t[e] = fmaxf(fmaxf(fmaxf(__uint_as_float(sa[4 * e]), __uint_as_float(sa[4 * e + 1])),
+                                       fmaxf(__uint_as_float(sa[4 * e + 2]), __uint_as_float(sa[4 * e + 3]))),
+                                 fmaxf(fmaxf(__uint_as_float(sc[4 * e]), __uint_as_float(sc[4 * e + 1])),
+                                       fmaxf(__uint_as_float(sc[4 * e + 2]), __uint_as_float(sc[4 * e + 3]))));
                 float bm = fmaxf(fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])), fmaxf(fmaxf(t[4], t[5]), fmaxf(t[6], t[7])));
                 xch[half * 128 + my_slot] = bm;
                 ok = pair_sync();
@@ -688,18 +694,21 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tmem_st_wait();
                 }
                 const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
-                uint32_t pk[16];
+                uint32_t pk[32];
                 float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const float p0 = fa_ex2(fmaf(__uint_as_float(sa[e]), p.scale_log2, -mref));
                     const float p1 = fa_ex2(fmaf(__uint_as_float(sa[e + 1]), p.scale_log2, -mref));
-                    s0 += p0;
-                    s1 += p1;
+                    const float p2 = fa_ex2(fmaf(__uint_as_float(sc[e]), p.scale_log2, -mref));
+                    const float p3 = fa_ex2(fmaf(__uint_as_float(sc[e + 1]), p.scale_log2, -mref));
+                    s0 += p0 + p2;
+                    s1 += p1 + p3;
                     pk[e >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
+                    pk[16 + (e >> 1)] = __byte_perm(__float_as_uint(p2) + 0x8000u, __float_as_uint(p3) + 0x8000u, 0x7632);
                 }
                 l_sum += s0 + s1;
-                tmem_st16(s_addr + (uint32_t)(half * 16), pk);  // P_j (64 keys, bf16) over the first 32 columns of S_j
+                tmem_st32(s_addr + (uint32_t)(half * 32), pk);  // P_j (128 keys, bf16) over the first 64 columns of S_j
                 tmem_st_wait();
                 tc_fence_before();
                 arrive_even(&p_full[sb]);
@@ -802,11 +811,13 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
         const int forced = dense_gemm_variant();
         if (p.n_mt >= 2 && forced != 1 && (forced == 3 || n_pair_units >= pairs)) {
             using LP = FlashPairSmem<HD>;
-            CUtensorMap kmap32;
+            // each CTA stages 64 of a block's 128 keys (the one-CTA kernel's K map has that box) and, for V, all
+            // 128 keys of half of the head dimension
+            CUtensorMap vmap128;
             const uint64_t dims[3] = {(uint64_t)HD, (uint64_t)kv_len, (uint64_t)st->n_layers * st->n_obs * st->n_kv};
             const uint64_t strides[2] = {(uint64_t)HD * 2, (uint64_t)st->cap * HD * 2};
-            const uint32_t box[3] = {64, 32, 1};  // each CTA stages 32 of a block's 64 keys
-            int rc = make_tensor_map(&kmap32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->k_pages, dims, strides, box,
+            const uint32_t box[3] = {64, FP_BKV, 1};
+            int rc = make_tensor_map(&vmap128, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->v_pages, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return rc;
             static bool pair_attr_done = false;
@@ -816,7 +827,7 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
                 pair_attr_done = true;
             }
             const int ncl = n_pair_units < pairs ? n_pair_units : pairs;
-            attn_flash_pair_kernel<HD><<<2 * ncl, FP_THREADS, LP::TOTAL, stream>>>(qmap, kmap32, vmap, p);
+            attn_flash_pair_kernel<HD><<<2 * ncl, FP_THREADS, LP::TOTAL, stream>>>(qmap, kmap, vmap128, p);
             VB_CUDA(cudaGetLastError());
             return VLAB200_OK;
         }
