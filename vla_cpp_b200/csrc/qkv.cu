@@ -406,9 +406,6 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
                 ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 const uint8_t *at = smem + st * STAGE_BYTES + row_base;
-#ifdef VB_QKV_NOSTATS
-                if (p.S == 12345)  // developer experiment
-#endif
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
@@ -493,11 +490,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
                     for (int e = 0; e < 32; e += 2) {
                         float a0 = __uint_as_float(lo[e]) * rms, a1 = __uint_as_float(lo[e + 1]) * rms;
                         float b0 = __uint_as_float(hi[e]) * rms, b1 = __uint_as_float(hi[e + 1]) * rms;
-#ifdef VB_QKV_NOROPE
-                        if (rotate && p.S == 12345) {  // developer experiment
-#else
                         if (rotate) {
-#endif
                             const float c0 = cs[(c + e) * p.S], c1 = cs[(c + e + 1) * p.S];
                             const float s0 = sn[(c + e) * p.S], s1 = sn[(c + e + 1) * p.S];
                             const float r0 = a0 * c0 - b0 * s0, r1 = a1 * c1 - b1 * s1;
@@ -526,11 +519,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
                         const uint32_t off = (uint32_t)rr * 64 + ((((uint32_t)lane & 3u) ^ (uint32_t)((rr >> 1) & 3)) << 4);
                         const uint4 vlo = *reinterpret_cast<const uint4 *>(stg + off);
                         const uint4 vhi = *reinterpret_cast<const uint4 *>(stg + 2048 + off);
-#ifdef VB_QKV_NOSTORE
-                        if (w_ok[i] && vlo.x == 0x12345u) {  // developer experiment
-#else
                         if (w_ok[i]) {
-#endif
                             __nv_bfloat16 *d = base + (size_t)w_obs[i] * obs_stride + (tok0 + w_tok[i]) * hd + (lane & 3) * 8;
                             *reinterpret_cast<uint4 *>(d + c) = vlo;
                             *reinterpret_cast<uint4 *>(d + half + c) = vhi;

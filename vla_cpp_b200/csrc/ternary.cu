@@ -322,9 +322,6 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + st * L::A_BYTES);
                     const uint32_t w_addr = smem_u32(smem + L::W_OFFSET + sw * L::W_BYTES);
-#ifdef VB_TERN_NOMMA
-                    if (kt == 0)  // developer experiment: one MMA group per tile only
-#endif
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / 32; ++k)
                         mma_i8(d_tmem, smem_desc_sw128(a_addr + k * 32, 16, 1024),
@@ -398,9 +395,6 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
                 fetch(g + PF, pf[u]);
                 ok = mbar_wait(&empty_w[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
-#ifdef VB_TERN_NODECODE
-                if (cur[0].x == 0x12345u)  // developer experiment: skip the decode work
-#endif
                 decode_store(cur, smem + L::W_OFFSET + st * L::W_BYTES);
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -475,9 +469,6 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
                     const int ch = lane & 7;
                     const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * 128 + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4));
                     const int mr = m0 + q * 32 + rr;
-#ifdef VB_TERN_NOSTORE
-                    if (v.x == 0x12345u)  // developer experiment: no output stores
-#endif
                     if (mr < M && ch * 8 < cols_valid)
                         *reinterpret_cast<uint4 *>(out + (size_t)mr * N + n + ch * 8) = v;
                 }
@@ -576,12 +567,8 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait_backoff(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY, 64);
                     if (!ok) break;
-#ifdef VB_TERN_NOLOAD
-                    mbar_arrive(&full[st]);  // developer experiment: no activation traffic
-#else
                     mbar_expect_tx(&full[st], L::A_BYTES);
                     tma_load_2d(smem + st * L::STAGE_BYTES, &a_map, &full[st], kt * GEMM_BK, m0);
-#endif
                     if (++st == PAIR_STAGES) { st = 0; ph ^= 1u; }
                 }
             }
@@ -663,18 +650,12 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
             for (int i = 0; i < 4; ++i) {
                 const uint32_t words[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
                 uint32_t d[4][4];
-#ifdef VB_TERN_NODECODE
-                if (cur[0].x == 0x12345u)  // developer experiment: skip the decode work
-#endif
 #pragma unroll
                 for (int sl = 0; sl < 4; ++sl) decode_slot(swap_slots ? words[sl ^ 2] : words[sl], d[sl]);
                 if (i == 0) {  // the first block is decoded before the stage is known to be free
                     ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                 }
-#ifdef VB_TERN_NODECODE
-                if (cur[0].x == 0x12345u)
-#endif
 #pragma unroll
                 for (int sl = 0; sl < 4; ++sl) {
                     const int r = (hb * 4 + i) * 16 + row_in_blk + (swap_slots ? (sl ^ 2) : sl);  // row in the half tile
@@ -752,9 +733,6 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
                         const int ch = lane & 7;
                         const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * 128 + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4));
                         const int mr = m0 + q * 32 + rr;
-#ifdef VB_TERN_NOSTORE
-                        if (v.x == 0x12345u)  // developer experiment: no output stores
-#endif
                         if (mr < M && ch * 8 < cols_valid)
                             *reinterpret_cast<uint4 *>(out + (size_t)mr * N + n + ch * 8) = v;
                     }
