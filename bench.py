@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(L=16, T=10, H=720, n_q=15, n_kv=5, hd=64, S=51, P=177, eps=1e-5)
 ATTN_BYTES_PER_OBS_LAYER_STEP = 2 * (177 * 5 * 64 * 2) + 2 * (51 * 5 * 64 * 2) + 2 * (51 * 15 * 64 * 2)  # 487,680
+ATTN_DRAM_BYTES_PER_OBS_NCU = 25.11e6 / 64  # profiles/attn_hd64_smolvla_attn_b64.md
 INT8_PEAK_TOPS = 3249.8  # measured on this pool, profiles/int8_tensor_peak_b200.md
 
 
@@ -468,6 +469,16 @@ def main():
         kp = torch.randn((B, c["P"], c["n_kv"], c["hd"]), device=dev, generator=g)
         vp = torch.randn((B, c["P"], c["n_kv"], c["hd"]), device=dev, generator=g)
         store.write_prefix(l, kp, vp)
+    # the store write alone (float32 K, V in, bf16 pages out; every layer gets the last layer's values again)
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    w0.record()
+    for l in range(c["L"]):
+        store.write_prefix(l, kp, vp)
+    w1.record()
+    torch.cuda.synchronize()
+    kvw_ms = w0.elapsed_time(w1) / c["L"]
+    kvw_bytes = 2 * B * c["P"] * c["n_kv"] * c["hd"] * (4 + 2)
     n_rows = (c["n_q"] + 2 * c["n_kv"]) * c["hd"]
     wqkv = (torch.randn((c["L"], n_rows, c["H"]), device=dev, generator=g) * 0.02).to(torch.bfloat16)
     ln_w = torch.ones((c["L"], c["H"]), device=dev)
@@ -556,10 +567,13 @@ def main():
             "gpu_launches": 2 * n_att * args.steps,
             "roofline": {"kernel": "attn_hd64_kernel", "bound": "hbm", "achieved": att_gbs, "peak": hbm_peak,
                          "unit": "GB/s", "frac": att_gbs / hbm_peak, "peak_kind": f"of {peak_kind}",
-                         "traffic": None, "us_per_launch": att_ms * 1e3,
+                         # dram__bytes_read + write of one ncu capture at batch 64 (25.11 MB for 64 observations),
+                         # scaled by the observations of a launch: pages are read once, traffic grows in proportion
+                         "traffic": ATTN_DRAM_BYTES_PER_OBS_NCU * B, "us_per_launch": att_ms * 1e3,
                          "algorithmic_bytes_per_launch": ATTN_BYTES_PER_OBS_LAYER_STEP * B},
             "kernels": {"attn_us": att_ms * 1e3, "qkv_rope_append_us": qkv_ms * 1e3,
-                        "qkv_tflops": 2.0 * B * c["S"] * n_rows * c["H"] / (qkv_ms * 1e-3) / 1e12},
+                        "qkv_tflops": 2.0 * B * c["S"] * n_rows * c["H"] / (qkv_ms * 1e-3) / 1e12,
+                        "kv_store_write_us": kvw_ms * 1e3, "kv_store_write_gbs": kvw_bytes / (kvw_ms * 1e-3) / 1e9},
         }
         if e2e:
             line["e2e"] = {"value": B * world / (e2e_ms * 1e-3), "unit": "chunks/s",
