@@ -317,6 +317,34 @@ VLAB200_API int32_t vlab200_bitvla_lm_set_output_norm(vlab200_bitvla_lm *ctx, co
 VLAB200_API int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void *d_in, void *d_out, int32_t seq,
                                               int32_t n_seq, void *stream);
 
+/* ---- node-level bf16 operators ----------------------------------------------------------
+ * What a per-node CUDA hook dispatches when it is handed one graph node at a time: the
+ * reference's vla_cuda_bf16_forward (src/cuda/vla_cuda_bf16.cu:698-720) handles MUL_MAT, ADD,
+ * MUL, SCALE, NORM, RMS_NORM and UNARY on bf16 tensors.  Same arithmetic here: bf16 storage,
+ * float32 math, one rounding per element.  All tensors contiguous; `stream` a cudaStream_t. */
+
+/* out[b][m][n] = sum_k x[b][m][k] * w[b or 0][n][k]  (mul_mat, vla_cuda_bf16.cu:624-678, which
+ * calls cuBLAS; here the tcgen05 GEMM of this library).  w_batched != 0: w is [n_batch][N][K].
+ * K % 8 == 0 and 16-byte aligned pointers (TMA). */
+VLAB200_API int32_t vlab200_node_mul_mat_bf16(const void *w_bf16, const void *x_bf16, void *out_bf16, int32_t N,
+                                              int32_t M, int32_t K, int32_t n_batch, int32_t w_batched,
+                                              void *stream);
+/* out[i] = a[i] + b[i % nb] (op 0) or a[i] * b[i % nb] (op 1); b bf16, or float32 when b_is_f32
+ * (bin_bcast, vla_cuda_bf16.cu:396-452).  n % nb == 0: b is broadcast over the leading dims. */
+VLAB200_API int32_t vlab200_node_bin_bf16(int32_t op, const void *a_bf16, const void *b, int32_t b_is_f32,
+                                          void *out_bf16, int64_t n, int64_t nb, void *stream);
+/* out = scale * x + bias (vla_cuda_bf16.cu:501-527).  16-byte aligned pointers. */
+VLAB200_API int32_t vlab200_node_scale_bf16(const void *x_bf16, void *out_bf16, int64_t n, float scale, float bias,
+                                            void *stream);
+/* op 0 SiLU, 1 ReLU, 2 GELU (tanh form), 3 GELU (erf form) (vla_cuda_bf16.cu:458-495).
+ * 16-byte aligned pointers. */
+VLAB200_API int32_t vlab200_node_unary_bf16(int32_t op, const void *x_bf16, void *out_bf16, int64_t n,
+                                            void *stream);
+/* Row norm without weight over [rows][cols]: rms != 0: x * rsqrt(mean x^2 + eps), else
+ * (x - mean) * rsqrt(var + eps) (k_norm_bf16, vla_cuda_bf16.cu:546-605). */
+VLAB200_API int32_t vlab200_node_norm_bf16(const void *x_bf16, void *out_bf16, int64_t rows, int64_t cols,
+                                           float eps, int32_t rms, void *stream);
+
 /* The reference's own symbol names and signatures for the three calls above
  * (src/kernels/bitvla/bitnet_kernels.cu:31,76,118), so src/models/bitvla.cpp and
  * src/kernels/bitvla/bitvla_lm_cuda.cu link against this library unchanged.  The bf16

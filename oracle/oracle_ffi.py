@@ -339,3 +339,61 @@ def bitvla_lm_forward(x, layers, output_norm, cfg):
     for lw in layers:
         h = bitvla_lm_layer(h, lw, cfg, cos, sin)
     return bitvla_rmsnorm_bf16(h, output_norm, cfg["rms_eps"])
+
+
+# ---- node-level bf16 operators (the reference's per-node CUDA hook, src/cuda/vla_cuda_bf16.cu) ----
+# Inputs are float32 arrays holding bf16 values; float32 math; one bf16 rounding of the result.
+
+def node_unary(op, x):
+    """op: "silu" | "relu" | "gelu" (tanh form) | "gelu_erf" (src/cuda/vla_cuda_bf16.cu:463-474)."""
+    import math
+
+    x = np.asarray(x, dtype=np.float32)
+    if op == "silu":
+        y = x / (np.float32(1) + np.exp(-x, dtype=np.float32))
+    elif op == "relu":
+        y = np.maximum(x, np.float32(0))
+    elif op == "gelu_erf":
+        erf = np.vectorize(math.erf, otypes=[np.float64])
+        y = np.float32(0.5) * x * (np.float32(1) + erf(x * np.float32(0.70710678118654752440)).astype(np.float32))
+    else:
+        c = np.float32(0.79788456080286535588)
+        y = np.float32(0.5) * x * (np.float32(1) + np.tanh(c * (x + np.float32(0.044715) * x * x * x), dtype=np.float32))
+    return bf16_round(y.astype(np.float32))
+
+
+def node_scale(x, scale, bias):
+    """scale * x + bias (src/cuda/vla_cuda_bf16.cu:501-527); the product and the sum round separately in
+    float32 unless the compiler contracts them, so the test allows one bf16 ulp."""
+    x = np.asarray(x, dtype=np.float32)
+    return bf16_round((np.float32(scale) * x + np.float32(bias)).astype(np.float32))
+
+
+def node_bin(op, a, b):
+    """a (+|*) b with b broadcast along the leading dimensions (src/cuda/vla_cuda_bf16.cu:396-452)."""
+    a = np.asarray(a, dtype=np.float32)
+    b = np.asarray(b, dtype=np.float32)
+    return bf16_round((a * b if op == "mul" else a + b).astype(np.float32))
+
+
+def node_norm(x, eps, rms):
+    """Row norm without weight: x * rsqrt(mean x^2 + eps), or (x - mean) * rsqrt(var + eps)
+    (src/cuda/vla_cuda_bf16.cu:548-579)."""
+    x = np.asarray(x, dtype=np.float32)
+    x64 = x.astype(np.float64)
+    if rms:
+        inv = 1.0 / np.sqrt((x64 * x64).mean(-1, keepdims=True) + eps)
+        return bf16_round((x64 * inv).astype(np.float32))
+    mean = x64.mean(-1, keepdims=True)
+    var = (x64 * x64).mean(-1, keepdims=True) - mean * mean
+    return bf16_round(((x64 - mean) / np.sqrt(var + eps)).astype(np.float32))
+
+
+def node_mul_mat(w, x):
+    """out[b][m][n] = sum_k x[b][m][k] * w[(b)][n][k], bf16 operands, float32 accumulation, bf16 result
+    (src/cuda/vla_cuda_bf16.cu:624-678).  w: [N, K] shared by all batches or [B, N, K]."""
+    x = np.asarray(x, dtype=np.float32)
+    w = np.asarray(w, dtype=np.float32)
+    if x.ndim == 2:
+        return bf16_round(linear(x, w))
+    return np.stack([bf16_round(linear(x[b], w[b] if w.ndim == 3 else w)) for b in range(x.shape[0])])

@@ -21,6 +21,11 @@ from .api import (  # noqa: F401
     device_status,
     fold_norm_weight,
     lib,
+    node_bin,
+    node_mul_mat,
+    node_norm,
+    node_scale,
+    node_unary,
     qkv_rope_append,
     rope_table,
     set_gemm_tiling,

@@ -57,6 +57,8 @@ EXPORTS = [
     "vlab200_act_quant", "vlab200_ternary_linear",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
+    "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
+    "vlab200_node_norm_bf16",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
 ]
 
@@ -374,6 +376,75 @@ def bitvla_norm_quant(x, w, eps, mode=NQ_PLAIN, add=None, quantise=True):
     _check(lib().vlab200_bitvla_norm_quant(_ptr(x), _ptr(add), _ptr(w), C.c_float(eps), m, k, mode, _ptr(q), _ptr(s),
                                            _ptr(y), _stream()), "vlab200_bitvla_norm_quant")
     return (q, s) if quantise else y
+
+
+NODE_UNARY = {"silu": 0, "relu": 1, "gelu": 2, "gelu_erf": 3}
+
+
+def _bf16_cuda(*ts):
+    import torch
+
+    for t in ts:
+        assert t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()
+
+
+def node_mul_mat(w, x):
+    """w: cuda bf16 [N, K] or [B, N, K]; x: [M, K] or [B, M, K] -> bf16 [.., M, N] = x @ w^T."""
+    import torch
+
+    _bf16_cuda(w, x)
+    nb = x.shape[0] if x.dim() == 3 else 1
+    m, k = x.shape[-2], x.shape[-1]
+    n = w.shape[-2]
+    assert w.shape[-1] == k and (w.dim() == 2 or w.shape[0] == nb)
+    out = torch.empty((*x.shape[:-1], n), dtype=torch.bfloat16, device=x.device)
+    _check(lib().vlab200_node_mul_mat_bf16(_ptr(w), _ptr(x), _ptr(out), n, m, k, nb, int(w.dim() == 3), _stream()),
+           "vlab200_node_mul_mat_bf16")
+    return out
+
+
+def node_bin(op, a, b):
+    """a: cuda bf16; b: bf16 or float32 whose shape matches the trailing dims of a -> a + b or a * b."""
+    import torch
+
+    _bf16_cuda(a)
+    assert b.is_cuda and b.is_contiguous() and b.dtype in (torch.bfloat16, torch.float32)
+    out = torch.empty_like(a)
+    _check(lib().vlab200_node_bin_bf16({"add": 0, "mul": 1}[op], _ptr(a), _ptr(b), int(b.dtype == torch.float32),
+                                       _ptr(out), C.c_int64(a.numel()), C.c_int64(b.numel()), _stream()),
+           "vlab200_node_bin_bf16")
+    return out
+
+
+def node_scale(x, scale, bias=0.0):
+    import torch
+
+    _bf16_cuda(x)
+    out = torch.empty_like(x)
+    _check(lib().vlab200_node_scale_bf16(_ptr(x), _ptr(out), C.c_int64(x.numel()), C.c_float(scale), C.c_float(bias),
+                                         _stream()), "vlab200_node_scale_bf16")
+    return out
+
+
+def node_unary(op, x):
+    import torch
+
+    _bf16_cuda(x)
+    out = torch.empty_like(x)
+    _check(lib().vlab200_node_unary_bf16(NODE_UNARY[op], _ptr(x), _ptr(out), C.c_int64(x.numel()), _stream()),
+           "vlab200_node_unary_bf16")
+    return out
+
+
+def node_norm(x, eps, rms=True):
+    import torch
+
+    _bf16_cuda(x)
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    _check(lib().vlab200_node_norm_bf16(_ptr(x), _ptr(out), C.c_int64(x.numel() // cols), C.c_int64(cols),
+                                        C.c_float(eps), int(rms), _stream()), "vlab200_node_norm_bf16")
+    return out
 
 
 _LM_FIELDS = ["attn_norm_w", "attn_sub_norm_w", "ffn_norm_w", "ffn_sub_norm_w", "q_packed", "q_ws", "k_packed",

@@ -1,0 +1,194 @@
+// Node-level bf16 operators: what a per-node CUDA hook needs when it is handed ONE graph node at a
+// time (the reference installs such a hook in ggml's CUDA backend: vla_cuda_bf16_forward dispatches
+// MUL_MAT / ADD / MUL / SCALE / NORM / RMS_NORM / UNARY on bf16 tensors,
+// src/cuda/vla_cuda_bf16.cu:698-720).  The fused kernels of this library make most of these nodes
+// disappear from the denoise loop; the operators here cover the nodes that remain outside it, with the
+// same arithmetic: bf16 storage, float math, one rounding per element.
+//
+//   mul_mat   persistent tcgen05 GEMM of gemm.cu (replaces the cuBLAS call, vla_cuda_bf16.cu:624-678)
+//   others    HBM-bound streaming kernels, 16-byte accesses, grid = a few CTAs per SM
+#include <cuda_bf16.h>
+
+#include "gemm.h"
+#include "host_common.h"
+
+namespace vb {
+
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u));
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+enum { UN_SILU = 0, UN_RELU = 1, UN_GELU_TANH = 2, UN_GELU_ERF = 3 };
+
+// src/cuda/vla_cuda_bf16.cu:463-474
+template <int OP>
+__device__ __forceinline__ float unary_f(float x) {
+    if (OP == UN_SILU) return x / (1.0f + expf(-x));
+    if (OP == UN_RELU) return x > 0.0f ? x : 0.0f;
+    if (OP == UN_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    const float c = 0.79788456080286535588f;
+    return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+
+// out[i] = f(x[i]); MODE 0: unary OP, 1: scale * x + bias
+template <int MODE, int OP>
+__global__ void __launch_bounds__(256) map_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out,
+                                                  int64_t n, float scale, float bias) {
+    const int64_t nvec = n >> 3;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint4 *ov = reinterpret_cast<uint4 *>(out);
+    auto f = [&](float v) { return MODE == 0 ? unary_f<OP>(v) : scale * v + bias; };
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 u = __ldg(xv + i);
+        const float2 a = unpack2(u.x), b = unpack2(u.y), c = unpack2(u.z), d = unpack2(u.w);
+        ov[i] = make_uint4(pack2(f(a.x), f(a.y)), pack2(f(b.x), f(b.y)), pack2(f(c.x), f(c.y)), pack2(f(d.x), f(d.y)));
+    }
+    for (int64_t i = (nvec << 3) + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16(f(__bfloat162float(x[i])));
+}
+
+// out[i] = a[i] (+|*) b[i % nb]; b bf16 or float32 (the reference's fused add takes a float32 src1)
+template <bool MUL, typename TB>
+__global__ void __launch_bounds__(256) bin_kernel(const __nv_bfloat16 *__restrict__ a, const TB *__restrict__ b,
+                                                  __nv_bfloat16 *__restrict__ out, int64_t n, int64_t nb) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float x = __bfloat162float(a[i]);
+        const float y = static_cast<float>(b[nb == n ? i : i % nb]);
+        out[i] = __float2bfloat16(MUL ? x * y : x + y);
+    }
+}
+
+// one CTA per row: (x - mean) * rsqrt(var + eps), or x * rsqrt(mean x^2 + eps) (src/cuda/vla_cuda_bf16.cu:548-579)
+template <bool RMS>
+__global__ void __launch_bounds__(256) norm_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out,
+                                                   int64_t cols, float eps) {
+    __shared__ float red[2][8];
+    const __nv_bfloat16 *xr = x + (size_t)blockIdx.x * cols;
+    __nv_bfloat16 *orow = out + (size_t)blockIdx.x * cols;
+    float s = 0.f, ss = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+        const float v = __bfloat162float(xr[c]);
+        s += v;
+        ss += v * v;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, off);
+        ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        red[0][threadIdx.x >> 5] = s;
+        red[1][threadIdx.x >> 5] = ss;
+    }
+    __syncthreads();
+    s = ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        s += red[0][i];
+        ss += red[1][i];
+    }
+    const float mean = RMS ? 0.0f : s / (float)cols;
+    const float inv = rsqrtf(ss / (float)cols - mean * mean + eps);
+    for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = __float2bfloat16((__bfloat162float(xr[c]) - mean) * inv);
+}
+
+static int stream_grid(int64_t work_items) {
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n_sm = 148;
+    }
+    const int64_t blocks = (work_items + 255) / 256;
+    const int64_t cap = (int64_t)n_sm * 8;
+    return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+}  // namespace vb
+
+extern "C" {
+
+int32_t vlab200_node_mul_mat_bf16(const void *w_bf16, const void *x_bf16, void *out_bf16, int32_t N, int32_t M, int32_t K,
+                                  int32_t n_batch, int32_t w_batched, void *stream) {
+    if (!w_bf16 || !x_bf16 || !out_bf16 || N <= 0 || M < 0 || K <= 0 || n_batch <= 0) return VLAB200_ERR_ARG;
+    if (M == 0) return VLAB200_OK;
+    for (int b = 0; b < n_batch; ++b) {
+        vb::GemmParams p{};
+        p.M = M; p.N = N; p.K = K; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE;
+        p.out_bf = static_cast<__nv_bfloat16 *>(out_bf16) + (size_t)b * M * N;
+        p.ld_out = N;
+        const __nv_bfloat16 *w = static_cast<const __nv_bfloat16 *>(w_bf16) + (w_batched ? (size_t)b * N * K : 0);
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(x_bf16) + (size_t)b * M * K;
+        const int rc = vb::dense_gemm(x, K, w, p, static_cast<cudaStream_t>(stream));
+        if (rc) return rc;
+    }
+    return VLAB200_OK;
+}
+
+int32_t vlab200_node_bin_bf16(int32_t op, const void *a_bf16, const void *b, int32_t b_is_f32, void *out_bf16, int64_t n,
+                              int64_t nb, void *stream) {
+    if (!a_bf16 || !b || !out_bf16 || n < 0 || nb <= 0 || (op != 0 && op != 1) || n % nb) return VLAB200_ERR_ARG;
+    if (n == 0) return VLAB200_OK;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const int grid = vb::stream_grid(n);
+    const __nv_bfloat16 *a = static_cast<const __nv_bfloat16 *>(a_bf16);
+    __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(out_bf16);
+    if (b_is_f32) {
+        if (op) vb::bin_kernel<true, float><<<grid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n, nb);
+        else vb::bin_kernel<false, float><<<grid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n, nb);
+    } else {
+        if (op) vb::bin_kernel<true, __nv_bfloat16><<<grid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n, nb);
+        else vb::bin_kernel<false, __nv_bfloat16><<<grid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n, nb);
+    }
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int32_t vlab200_node_scale_bf16(const void *x_bf16, void *out_bf16, int64_t n, float scale, float bias, void *stream) {
+    if (!x_bf16 || !out_bf16 || n < 0) return VLAB200_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(out_bf16) & 15)) return VLAB200_ERR_ARG;
+    if (n == 0) return VLAB200_OK;
+    vb::map_kernel<1, 0><<<vb::stream_grid((n + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16 *>(x_bf16), static_cast<__nv_bfloat16 *>(out_bf16), n, scale, bias);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int32_t vlab200_node_unary_bf16(int32_t op, const void *x_bf16, void *out_bf16, int64_t n, void *stream) {
+    if (!x_bf16 || !out_bf16 || n < 0 || op < 0 || op > 3) return VLAB200_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(out_bf16) & 15)) return VLAB200_ERR_ARG;
+    if (n == 0) return VLAB200_OK;
+    const int grid = vb::stream_grid((n + 7) / 8);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(x_bf16);
+    __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(out_bf16);
+    switch (op) {
+        case vb::UN_SILU: vb::map_kernel<0, vb::UN_SILU><<<grid, 256, 0, cs>>>(x, o, n, 0.f, 0.f); break;
+        case vb::UN_RELU: vb::map_kernel<0, vb::UN_RELU><<<grid, 256, 0, cs>>>(x, o, n, 0.f, 0.f); break;
+        case vb::UN_GELU_TANH: vb::map_kernel<0, vb::UN_GELU_TANH><<<grid, 256, 0, cs>>>(x, o, n, 0.f, 0.f); break;
+        default: vb::map_kernel<0, vb::UN_GELU_ERF><<<grid, 256, 0, cs>>>(x, o, n, 0.f, 0.f); break;
+    }
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int32_t vlab200_node_norm_bf16(const void *x_bf16, void *out_bf16, int64_t rows, int64_t cols, float eps, int32_t rms,
+                               void *stream) {
+    if (!x_bf16 || !out_bf16 || rows < 0 || cols <= 0 || rows > 2147483647) return VLAB200_ERR_ARG;
+    if (rows == 0) return VLAB200_OK;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (rms)
+        vb::norm_kernel<true><<<(int)rows, 256, 0, cs>>>(static_cast<const __nv_bfloat16 *>(x_bf16),
+                                                        static_cast<__nv_bfloat16 *>(out_bf16), cols, eps);
+    else
+        vb::norm_kernel<false><<<(int)rows, 256, 0, cs>>>(static_cast<const __nv_bfloat16 *>(x_bf16),
+                                                         static_cast<__nv_bfloat16 *>(out_bf16), cols, eps);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+}  // extern "C"
