@@ -19,7 +19,7 @@
 // TMEM region (256 columns): S [0, nk16) in nchunks chunks of 32 columns, the first n_a of them
 // owned by column half A.  P (bf16, 16 columns per chunk) overwrites columns its own half has
 // already consumed: half A at [0, 16 n_a), half B at [32 n_a, 32 n_a + 16 (nchunks - n_a)); O (64
-// columns) follows the P of half B.
+// columns) follows the P of half A (n_a >= 4) or of half B.
 //
 // Reference: src/layers/attn.h:38-46, src/models/pi0.cpp:204-223 (mul_mat -> soft_max -> mul_mat
 // with the score matrix in HBM), src/models/smolvla.cpp:835-842,874-881 (ggml_flash_attn_ext);
@@ -89,11 +89,19 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// Visibility of the 32 columns of chunk c as a bit mask (bit j = column c*32 + j is visible).
+__device__ __forceinline__ uint32_t low_bits(int n) {  // bits [0, n), n clamped to [0, 32]
+    return n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
+}
+__device__ __forceinline__ uint32_t att_vis_bits(int c, const RowMask &rm) {
+    const uint32_t below_jmax = low_bits(rm.jmax - c * 32);
+    const uint32_t pad = low_bits(rm.pad_hi - c * 32) & ~low_bits(rm.pad_lo - c * 32);
+    return below_jmax & ~pad;
+}
 // Visibility is applied to the INPUT of max / exp2 (a select to -inf), never as a branch around
 // them, so lanes with different row limits stay converged.
-__device__ __forceinline__ float att_masked(uint32_t bits, int j, int rel_jmax, int rel_pad_lo, int pad_w) {
-    const bool vis = j < rel_jmax && !((unsigned)(j - rel_pad_lo) < (unsigned)pad_w);
-    return vis ? __uint_as_float(bits) : -INFINITY;
+__device__ __forceinline__ float att_masked(uint32_t bits, int j, uint32_t vis) {
+    return (vis & (1u << j)) ? __uint_as_float(bits) : -INFINITY;
 }
 
 __device__ __forceinline__ void att_max_chunk(const uint32_t (&sv)[32], int c, const RowMask &rm, float (&mx)[4]) {
@@ -108,17 +116,17 @@ __device__ __forceinline__ void att_max_chunk(const uint32_t (&sv)[32], int c, c
         mx[2] = max3(mx[2], t[4], t[5]);
         mx[3] = max3(mx[3], t[6], t[7]);
     } else {
-        const int rel_jmax = rm.jmax - c * 32, rel_pad_lo = rm.pad_lo - c * 32, pad_w = rm.pad_hi - rm.pad_lo;
+        const uint32_t vis = att_vis_bits(c, rm);
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-            mx[0] = max3(mx[0], att_masked(sv[j], j, rel_jmax, rel_pad_lo, pad_w),
-                         att_masked(sv[j + 1], j + 1, rel_jmax, rel_pad_lo, pad_w));
-            mx[1] = max3(mx[1], att_masked(sv[j + 2], j + 2, rel_jmax, rel_pad_lo, pad_w),
-                         att_masked(sv[j + 3], j + 3, rel_jmax, rel_pad_lo, pad_w));
-            mx[2] = max3(mx[2], att_masked(sv[j + 4], j + 4, rel_jmax, rel_pad_lo, pad_w),
-                         att_masked(sv[j + 5], j + 5, rel_jmax, rel_pad_lo, pad_w));
-            mx[3] = max3(mx[3], att_masked(sv[j + 6], j + 6, rel_jmax, rel_pad_lo, pad_w),
-                         att_masked(sv[j + 7], j + 7, rel_jmax, rel_pad_lo, pad_w));
+            mx[0] = max3(mx[0], att_masked(sv[j], j, vis),
+                         att_masked(sv[j + 1], j + 1, vis));
+            mx[1] = max3(mx[1], att_masked(sv[j + 2], j + 2, vis),
+                         att_masked(sv[j + 3], j + 3, vis));
+            mx[2] = max3(mx[2], att_masked(sv[j + 4], j + 4, vis),
+                         att_masked(sv[j + 5], j + 5, vis));
+            mx[3] = max3(mx[3], att_masked(sv[j + 6], j + 6, vis),
+                         att_masked(sv[j + 7], j + 7, vis));
         }
     }
 }
@@ -138,13 +146,13 @@ __device__ __forceinline__ void att_exp_chunk(const uint32_t (&sv)[32], int c, c
             pk[j >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
         }
     } else {
-        const int rel_jmax = rm.jmax - c * 32, rel_pad_lo = rm.pad_lo - c * 32, pad_w = rm.pad_hi - rm.pad_lo;
+        const uint32_t vis = att_vis_bits(c, rm);
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
             // exp2(-inf) = 0 for the masked columns
-            const float p0 = ex2_approx(fmaf(att_masked(sv[j], j, rel_jmax, rel_pad_lo, pad_w), scale_log2, -m2));
+            const float p0 = ex2_approx(fmaf(att_masked(sv[j], j, vis), scale_log2, -m2));
             const float p1 =
-                ex2_approx(fmaf(att_masked(sv[j + 1], j + 1, rel_jmax, rel_pad_lo, pad_w), scale_log2, -m2));
+                ex2_approx(fmaf(att_masked(sv[j + 1], j + 1, vis), scale_log2, -m2));
             sum0 += p0;
             sum1 += p1;
             pk[j >> 1] = __byte_perm(__float_as_uint(p0) + 0x8000u, __float_as_uint(p1) + 0x8000u, 0x7632);
@@ -162,8 +170,9 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                                                 ~static_cast<uintptr_t>(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ATT_SMEM_DATA);
     uint64_t *full_qk = bars, *full_v = bars + 2, *free_qk = bars + 4, *free_v = bars + 6;    // per buffer
-    uint64_t *bar_s = bars + 8, *bar_p = bars + 10, *bar_o = bars + 12, *bar_free = bars + 14;  // per region
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *bar_s = bars + 8, *bar_o = bars + 10, *bar_free = bars + 12;  // per region
+    uint64_t *bar_p = bars + 14;                                            // per region and column half
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *xch = reinterpret_cast<float *>(smem + ATT_SMEM_DATA + 256);  // [2 regions][max|sum][2 halves][128 rows]
 
@@ -178,7 +187,8 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             mbar_init(&free_qk[i], 1);
             mbar_init(&free_v[i], 1);
             mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_p[i], 256);
+            mbar_init(&bar_p[2 * i], 128);
+            mbar_init(&bar_p[2 * i + 1], 128);
             mbar_init(&bar_o[i], 1);
             mbar_init(&bar_free[i], 256);
         }
@@ -194,9 +204,28 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int nchunks = (p.nk16 + 31) / 32;
-    const int n_a = (nchunks + 1) / 2;  // chunks of the first column half
-    const int pb_col = n_a * 32;        // P of the second half starts where its S columns start
-    const int o_col = pb_col + (nchunks - n_a) * 16;
+    // Chunks of the first column half.  Chunks below the prefix end take the unmasked path in every row
+    // (pad ranges aside); a masked chunk costs about 1.4 of those, so the first half gets more chunks when
+    // the second one holds the masked ones.
+    int n_a = (nchunks + 1) / 2;
+    {
+        const int n_clean = min(p.prefix_len / 32, nchunks);
+        int best = 1 << 30;
+        for (int a = (nchunks + 1) / 2; a <= max((nchunks + 1) / 2, nchunks - 1); ++a) {
+            const int clean_a = min(a, n_clean), clean_b = n_clean - clean_a;
+            const int cost_a = 10 * clean_a + 14 * (a - clean_a);
+            const int cost_b = 10 * clean_b + 14 * (nchunks - a - clean_b);
+            const int cost = max(cost_a, cost_b);
+            if (cost < best) {
+                best = cost;
+                n_a = a;
+            }
+        }
+    }
+    const int pb_col = n_a * 32;  // P of the second half starts where its S columns start
+    // O (64 columns) goes behind the P of the first half when that half's consumed S columns have room for it,
+    // else behind the P of the second half.
+    const int o_col = (n_a >= 4) ? n_a * 16 : pb_col + (nchunks - n_a) * 16;
 
     if (warp == ATT_SOFTMAX_WARPS) {
         // ------------------------------------------------------------- loader
@@ -259,15 +288,28 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                                 smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
                     tc_commit(&bar_s[r]);
                     if (t == n_tiles - 1) tc_commit(&free_qk[st]);  // Q, K of this item are dead once these MMAs ran
-                    ok = mbar_wait(&bar_p[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
-                    if (ok && t == 0) ok = mbar_wait(&full_v[st], m & 1u, wc, DEV_TIMEOUT_FULL);
+                    if (t == 0) ok = mbar_wait(&full_v[st], m & 1u, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
-                    tc_fence_after();
-                    for (int k16 = 0; k16 < p.nk16 / 16; ++k16) {
-                        const uint32_t p_col = k16 < k16_a ? (uint32_t)(k16 * 8) : (uint32_t)(pb_col + (k16 - k16_a) * 8);
-                        mma_f16_tmem_a(treg + (uint32_t)o_col, treg + p_col, smem_desc_sw128(v_addr + k16 * 2048, 16, 1024),
-                                       idesc_o, k16 != 0 ? 1u : 0u);
+                    // P V over the keys of the column half whose consumed S columns hold O (O may only be
+                    // written once that half has finished reading S), then over the other half's keys
+                    const int n_k16 = p.nk16 / 16;
+                    const int first = (n_a >= 4) ? 0 : 1;
+                    uint32_t acc = 0u;
+                    for (int part = 0; ok && part < 2; ++part) {
+                        const int h = part ^ first;
+                        const int k_lo = h ? k16_a : 0, k_hi = h ? n_k16 : min(k16_a, n_k16);
+                        if (k_lo >= k_hi) continue;
+                        ok = mbar_wait(&bar_p[2 * r + h], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+                        for (int k16 = k_lo; k16 < k_hi; ++k16) {
+                            const uint32_t p_col = h ? (uint32_t)(pb_col + (k16 - k16_a) * 8) : (uint32_t)(k16 * 8);
+                            mma_f16_tmem_a(treg + (uint32_t)o_col, treg + p_col, smem_desc_sw128(v_addr + k16 * 2048, 16, 1024),
+                                           idesc_o, acc);
+                            acc = 1u;
+                        }
                     }
+                    if (!ok) break;
                     tc_commit(&bar_o[r]);
                 }
                 if (ok) tc_commit(&free_v[st]);  // every MMA that reads this V buffer has been issued
@@ -344,7 +386,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 x_sum[half * 128 + my_row_slot] = sum0 + sum1;
                 VB_STAMP(3);
                 tc_fence_before();
-                mbar_arrive(&bar_p[r]);
+                mbar_arrive(&bar_p[2 * r + half]);
                 ok = mbar_wait(&bar_o[r], k_unit & 1u, wc, DEV_TIMEOUT_ACCUM);
                 if (!ok) break;
                 tc_fence_after();
