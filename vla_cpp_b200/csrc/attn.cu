@@ -49,6 +49,7 @@ struct AttnParams {
     const int32_t *pad;  // [n_obs][2] masked prefix columns, or null
     int S, n_q, n_kv, g, kv_len, prefix_len, mask_mode, nk16, R, n_items, page0;
     int t1_rows;   // rows of the second 128-row tile (0: none)
+    int out_al32;  // 1: out is 32-byte aligned (256-bit stores)
     int t1_rot;    // 1: t1_rows <= 32, its rows are placed in TMEM quarter (item ordinal % 4)
     float scale_log2;
     int *status;
@@ -405,17 +406,25 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                     const float inv = 1.0f / sum;
                     __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * 64) +
                                          (size_t)(kvh * p.g + head_l) * 64 + half * 32;
-                    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+                    // one full 32-byte sector per store instruction and thread
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t w[4];
+                    for (int j = 0; j < 2; ++j) {
+                        uint32_t w[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[8 * j + 2 * e]) * inv,
-                                                                           __uint_as_float(o[8 * j + 2 * e + 1]) * inv);
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[16 * j + 2 * e]) * inv,
+                                                                           __uint_as_float(o[16 * j + 2 * e + 1]) * inv);
                             w[e] = *reinterpret_cast<const uint32_t *>(&h);
                         }
-                        d4[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (p.out_al32) {
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * j),
+                                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                                         : "memory");
+                        } else {
+                            uint4 *d4 = reinterpret_cast<uint4 *>(dst + 16 * j);
+                            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
                     }
                 }
             }
@@ -492,6 +501,7 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     p.t1_rows = R > 128 ? R - 128 : 0;
     p.t1_rot = (p.t1_rows > 0 && p.t1_rows <= 32) ? 1 : 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf(64.0f);
+    p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
 #ifdef VB_TRACE
     p.trace = g_vb_attn_trace;
