@@ -481,36 +481,43 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
                     rotate = !is_v;
                 }
                 for (int c = (heads_in_tile > 1 ? 0 : grp * 32); c < half; c += (heads_in_tile > 1 ? 32 : 64)) {
-                    uint32_t lo[32], hi[32];
-                    tmem_ld32(lane_addr + (uint32_t)(hc + c), lo);
-                    tmem_ld32(lane_addr + (uint32_t)(hc + half + c), hi);
-                    tmem_ld_wait();
-                    uint32_t olo[16], ohi[16];
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        float a0 = __uint_as_float(lo[e]) * rms, a1 = __uint_as_float(lo[e + 1]) * rms;
-                        float b0 = __uint_as_float(hi[e]) * rms, b1 = __uint_as_float(hi[e + 1]) * rms;
-                        if (rotate) {
-                            const float c0 = cs[(c + e) * p.S], c1 = cs[(c + e + 1) * p.S];
-                            const float s0 = sn[(c + e) * p.S], s1 = sn[(c + e + 1) * p.S];
-                            const float r0 = a0 * c0 - b0 * s0, r1 = a1 * c1 - b1 * s1;
-                            b0 = b0 * c0 + a0 * s0;
-                            b1 = b1 * c1 + a1 * s1;
-                            a0 = r0;
-                            a1 = r1;
-                        }
-                        const __nv_bfloat162 l2 = __floats2bfloat162_rn(a0, a1), h2 = __floats2bfloat162_rn(b0, b1);
-                        olo[e >> 1] = *reinterpret_cast<const uint32_t *>(&l2);
-                        ohi[e >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
-                    }
-                    // transpose through shared memory: thread-per-row -> 64 contiguous bytes per 4 lanes
+                    // 16 columns of each half per round: lo / hi / packed output stay within 48 registers
+                    // (the kernel is capped at 128 and spilled with 32-column rounds)
                     uint8_t *mine = stg + lane * 64;
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        *reinterpret_cast<uint4 *>(mine + (((uint32_t)q4 ^ my_sw) << 4)) =
-                            make_uint4(olo[4 * q4], olo[4 * q4 + 1], olo[4 * q4 + 2], olo[4 * q4 + 3]);
-                        *reinterpret_cast<uint4 *>(mine + 2048 + (((uint32_t)q4 ^ my_sw) << 4)) =
-                            make_uint4(ohi[4 * q4], ohi[4 * q4 + 1], ohi[4 * q4 + 2], ohi[4 * q4 + 3]);
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t lo[16], hi[16];
+                        tmem_ld16(lane_addr + (uint32_t)(hc + c + hh * 16), lo);
+                        tmem_ld16(lane_addr + (uint32_t)(hc + half + c + hh * 16), hi);
+                        tmem_ld_wait();
+                        uint32_t olo[8], ohi[8];
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            float a0 = __uint_as_float(lo[e]) * rms, a1 = __uint_as_float(lo[e + 1]) * rms;
+                            float b0 = __uint_as_float(hi[e]) * rms, b1 = __uint_as_float(hi[e + 1]) * rms;
+                            if (rotate) {
+                                const int ce = c + hh * 16 + e;
+                                const float c0 = cs[ce * p.S], c1 = cs[(ce + 1) * p.S];
+                                const float s0 = sn[ce * p.S], s1 = sn[(ce + 1) * p.S];
+                                const float r0 = a0 * c0 - b0 * s0, r1 = a1 * c1 - b1 * s1;
+                                b0 = b0 * c0 + a0 * s0;
+                                b1 = b1 * c1 + a1 * s1;
+                                a0 = r0;
+                                a1 = r1;
+                            }
+                            const __nv_bfloat162 l2 = __floats2bfloat162_rn(a0, a1), h2 = __floats2bfloat162_rn(b0, b1);
+                            olo[e >> 1] = *reinterpret_cast<const uint32_t *>(&l2);
+                            ohi[e >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        // transpose through shared memory: thread-per-row -> 64 contiguous bytes per 4 lanes
+#pragma unroll
+                        for (int q2 = 0; q2 < 2; ++q2) {
+                            const uint32_t q4 = (uint32_t)(hh * 2 + q2);
+                            *reinterpret_cast<uint4 *>(mine + ((q4 ^ my_sw) << 4)) =
+                                make_uint4(olo[4 * q2], olo[4 * q2 + 1], olo[4 * q2 + 2], olo[4 * q2 + 3]);
+                            *reinterpret_cast<uint4 *>(mine + 2048 + ((q4 ^ my_sw) << 4)) =
+                                make_uint4(ohi[4 * q2], ohi[4 * q2 + 1], ohi[4 * q2 + 2], ohi[4 * q2 + 3]);
+                        }
                     }
                     __syncwarp();
 #pragma unroll
