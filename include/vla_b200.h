@@ -317,6 +317,42 @@ VLAB200_API int32_t vlab200_bitvla_lm_set_output_norm(vlab200_bitvla_lm *ctx, co
 VLAB200_API int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void *d_in, void *d_out, int32_t seq,
                                               int32_t n_seq, void *stream);
 
+/* ---- GGUF checkpoints ------------------------------------------------------------------
+ * Reader for the reference's on-disk format (GGUF v2 / v3, written by scripts/convert_*_to_gguf.py
+ * through gguf.GGUFWriter).  The reference goes through ggml's gguf_* API and its wrapper
+ * src/gguf_reader.h:60-200 (typed metadata getters, read_raw, read_f32, read_convert with the
+ * Gemma-norm "+1"); this library parses the container itself (the file is mmap'ed read-only). */
+typedef struct vlab200_gguf vlab200_gguf;
+
+/* NULL on failure (vlab200_last_error() says why: missing file, bad magic, truncated directory...). */
+VLAB200_API vlab200_gguf *vlab200_gguf_open(const char *path);
+VLAB200_API void vlab200_gguf_close(vlab200_gguf *g);
+VLAB200_API int64_t vlab200_gguf_n_tensors(const vlab200_gguf *g);
+VLAB200_API const char *vlab200_gguf_tensor_name(const vlab200_gguf *g, int64_t index); /* file order */
+/* type: ggml type id (0 F32, 1 F16, 30 BF16, 24 I8, 8 Q8_0 ...); dims: ggml order, dims[0] fastest;
+ * n_bytes 0 for a type whose size this reader does not know.  VLAB200_ERR_ARG: no such tensor. */
+VLAB200_API int32_t vlab200_gguf_tensor_info(const vlab200_gguf *g, const char *name, int32_t *type,
+                                             int32_t *n_dims, int64_t dims[4], uint64_t *n_bytes);
+/* Pointer into the mapping (valid until close); the read_raw of src/gguf_reader.h:119-136 without a copy. */
+VLAB200_API const void *vlab200_gguf_tensor_data(const vlab200_gguf *g, const char *name);
+/* F32 / F16 / BF16 tensor as float32; gemma_norm != 0 adds 1.0 to every element
+ * (read_f32 + read_convert, src/gguf_reader.h:138-176).  n_elems must match the tensor. */
+VLAB200_API int32_t vlab200_gguf_read_f32(const vlab200_gguf *g, const char *name, float *dst, int64_t n_elems,
+                                          int32_t gemma_norm);
+/* Typed metadata getters (u32 / f32-or-f64 / string); VLAB200_ERR_ARG when the key is absent or has
+ * another type (src/gguf_reader.h:80-104). */
+VLAB200_API int32_t vlab200_gguf_meta_u32(const vlab200_gguf *g, const char *key, uint32_t *out);
+VLAB200_API int32_t vlab200_gguf_meta_f64(const vlab200_gguf *g, const char *key, double *out);
+VLAB200_API int32_t vlab200_gguf_meta_str(const vlab200_gguf *g, const char *key, char *buf, int32_t cap);
+
+/* The denoise engine of a pi0 checkpoint: metadata keys "pi0.*" (src/models/pi0.cpp:267-293), expert
+ * tensors "aex.blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_o,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight",
+ * "aex.output_norm.weight" (Gemma norms get their +1) and the projection heads
+ * (src/modules/gemma_expert.h:46-62, src/models/pi0.cpp:431-437).  Matrices are uploaded as bf16,
+ * vectors as float32; shapes are checked against the metadata.  NULL on failure. */
+VLAB200_API vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g, int32_t max_obs,
+                                                            int32_t prefix_len);
+
 /* ---- node-level bf16 operators ----------------------------------------------------------
  * What a per-node CUDA hook dispatches when it is handed one graph node at a time: the
  * reference's vla_cuda_bf16_forward (src/cuda/vla_cuda_bf16.cu:698-720) handles MUL_MAT, ADD,

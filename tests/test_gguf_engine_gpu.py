@@ -1,0 +1,116 @@
+"""Engine built from a pi0-shaped GGUF (the reference converter's tensor names, metadata keys and dtypes,
+scripts/convert_pi0_to_gguf.py:234-244, scripts/gguf_blocks.py:104-142,196-211) against the engine built from
+the same weights handed over directly: bit-identical action chunks."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+gguf = pytest.importorskip("gguf")
+
+from tests.gpu_util import bits_to_bf16_tensor, require_cuda, to_dev
+from tests.test_engine_gpu import make_policy
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    from oracle import oracle_ffi
+
+    oracle_ffi.build()
+    return oracle_ffi
+
+
+def _write_pi0(path, oracle, cfg, per, glob, bf16_matrices):
+    F32, BF16 = gguf.GGMLQuantizationType.F32, gguf.GGMLQuantizationType.BF16
+    w = gguf.GGUFWriter(str(path), "pi0")
+    kv = lambda k: "pi0." + k
+    for key, val in (("n_layers", cfg["n_layers"]), ("expert_h", cfg["H"]), ("n_q_heads", cfg["n_q"]),
+                     ("n_kv_heads", cfg["n_kv"]), ("head_dim", cfg["head_dim"]), ("expert_inter", cfg["inter"]),
+                     ("chunk_size", cfg["chunk"]), ("num_steps", cfg["steps"]), ("max_state_dim", cfg["state_dim"]),
+                     ("max_action_dim", cfg["action_dim"]), ("hidden", 2048)):
+        w.add_uint32(kv(key), val)
+    w.add_float64(kv("min_period"), cfg["min_period"])
+    w.add_float64(kv("max_period"), cfg["max_period"])
+    w.add_float64(kv("rope_theta"), cfg["rope_base"])
+    w.add_float32(kv("rms_norm_eps"), cfg["rms_eps"])
+
+    def mat(name, a):
+        if bf16_matrices:
+            w.add_tensor(name, oracle.f32_to_bf16_bits(a).astype(np.uint16), raw_shape=list(a.shape), raw_dtype=BF16)
+        else:
+            w.add_tensor(name, np.ascontiguousarray(a, dtype=np.float32), raw_dtype=F32)
+
+    vec = lambda name, a: w.add_tensor(name, np.ascontiguousarray(a, dtype=np.float32), raw_dtype=F32)
+    names = dict(wq="attn_q", wk="attn_k", wv="attn_v", wo="attn_o", wgate="ffn_gate", wup="ffn_up", wdown="ffn_down")
+    for l in range(cfg["n_layers"]):
+        vec(f"aex.blk.{l}.attn_norm.weight", per["ln_raw_in"][l])
+        vec(f"aex.blk.{l}.ffn_norm.weight", per["ln_raw_post"][l])
+        for k, n in names.items():
+            mat(f"aex.blk.{l}.{n}.weight", per[k][l])
+    vec("aex.output_norm.weight", glob["out_norm_raw"])
+    for k, n in (("w_sp", "state_proj"), ("w_ain", "action_in_proj"), ("w_at1", "action_time_mlp_in"),
+                 ("w_at2", "action_time_mlp_out"), ("w_aout", "action_out_proj")):
+        mat(n + ".weight", glob[k])
+        vec(n + ".bias", glob["b_" + k[2:]])
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+@pytest.mark.parametrize("bf16_matrices", [True, False])
+def test_engine_from_gguf_matches_direct_engine(oracle, tmp_path, bf16_matrices):
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(11)
+    P, n_obs = 40, 3
+    cfg, per, glob, _ = make_policy(oracle, rng, model=0, L=2, H=128, n_q=2, n_kv=1, hd=64, inter=256, P=P, chunk=10,
+                                    A=32, sd=32, T=3)
+    # Gemma norms are stored without their +1
+    per["ln_raw_in"] = [(a - 1).astype(np.float32) for a in per["ln_in"]]
+    per["ln_raw_post"] = [(a - 1).astype(np.float32) for a in per["ln_post"]]
+    per["ln_in"] = [a + np.float32(1) for a in per["ln_raw_in"]]
+    per["ln_post"] = [a + np.float32(1) for a in per["ln_raw_post"]]
+    glob["out_norm_raw"] = (glob["out_norm"] - 1).astype(np.float32)
+    glob["out_norm"] = glob["out_norm_raw"] + np.float32(1)
+    path = tmp_path / "pi0.gguf"
+    _write_pi0(path, oracle, cfg, per, glob, bf16_matrices)
+
+    g = vb.Gguf(path)
+    eng_g = vb.PolicyEngine.from_gguf(g, max_obs=n_obs, prefix_len=P)
+    g.close()  # the engine holds its own copies
+    bf = lambda a: bits_to_bf16_tensor(oracle.f32_to_bf16_bits(a))
+    keys = ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "ln_in", "ln_post")
+    weights = {k: [bf(a) if k.startswith("w") else to_dev(a) for a in per[k]] for k in keys}
+    weights.update({k: (bf(v) if k.startswith("w_") else to_dev(v)) for k, v in glob.items() if not k.endswith("_raw")})
+    eng_d = vb.PolicyEngine(cfg, weights, max_obs=n_obs, prefix_len=P)
+
+    L, n_kv, hd = cfg["n_layers"], cfg["n_kv"], cfg["head_dim"]
+    kp = rng.standard_normal((L, n_obs, P, n_kv, hd)).astype(np.float32)
+    vp = rng.standard_normal((L, n_obs, P, n_kv, hd)).astype(np.float32)
+    for e in (eng_g, eng_d):
+        for l in range(L):
+            e.set_prefix(l, to_dev(kp[l]), to_dev(vp[l]))
+    state = to_dev(rng.standard_normal((n_obs, cfg["state_dim"])).astype(np.float32))
+    x0 = to_dev(rng.standard_normal((n_obs, cfg["chunk"], cfg["action_dim"])).astype(np.float32))
+    out_g = eng_g.denoise(x0, state).cpu().numpy()
+    out_d = eng_d.denoise(x0, state).cpu().numpy()
+    assert vb.device_status() == 0
+    assert np.isfinite(out_g).all() and np.array_equal(out_g, out_d)
+
+
+def test_engine_from_gguf_reports_what_is_wrong(oracle, tmp_path):
+    require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(12)
+    cfg, per, glob, _ = make_policy(oracle, rng, model=0, L=1, H=128, n_q=2, n_kv=1, hd=64, inter=256, P=8, chunk=10,
+                                    A=32, sd=32, T=2)
+    per["ln_raw_in"], per["ln_raw_post"], glob["out_norm_raw"] = per["ln_in"], per["ln_post"], glob["out_norm"]
+    per["wo"][0] = per["wo"][0][:, :64]  # wrong shape
+    path = tmp_path / "bad.gguf"
+    _write_pi0(path, oracle, cfg, per, glob, True)
+    g = vb.Gguf(path)
+    with pytest.raises(vb.VlaB200Error, match="attn_o"):
+        vb.PolicyEngine.from_gguf(g, max_obs=1, prefix_len=8)

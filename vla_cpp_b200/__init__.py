@@ -12,6 +12,7 @@ from .api import (  # noqa: F401
     MASK_PI0,
     BitvlaLM,
     DenoiseAttn,
+    Gguf,
     KvStore,
     PolicyEngine,
     VlaB200Error,

@@ -41,6 +41,24 @@ def lib():
         L.vlab200_bitvla_lm_init.restype = C.c_void_p
         L.vlab200_bitvla_lm_init.argtypes = [C.c_int32] * 6 + [C.c_float, C.c_float, C.c_int32, C.c_int32]
         L.vlab200_bitvla_lm_free.restype = None
+        L.vlab200_gguf_open.restype = C.c_void_p
+        L.vlab200_gguf_open.argtypes = [C.c_char_p]
+        L.vlab200_gguf_close.restype = None
+        L.vlab200_gguf_close.argtypes = [C.c_void_p]
+        L.vlab200_gguf_n_tensors.restype = C.c_int64
+        L.vlab200_gguf_n_tensors.argtypes = [C.c_void_p]
+        L.vlab200_gguf_tensor_name.restype = C.c_char_p
+        L.vlab200_gguf_tensor_name.argtypes = [C.c_void_p, C.c_int64]
+        L.vlab200_gguf_tensor_data.restype = C.c_void_p
+        L.vlab200_gguf_tensor_data.argtypes = [C.c_void_p, C.c_char_p]
+        L.vlab200_gguf_tensor_info.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                               C.POINTER(C.c_int64), C.POINTER(C.c_uint64)]
+        L.vlab200_gguf_read_f32.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int64, C.c_int32]
+        L.vlab200_gguf_meta_u32.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint32)]
+        L.vlab200_gguf_meta_f64.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_double)]
+        L.vlab200_gguf_meta_str.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_int32]
+        L.vlab200_engine_create_from_gguf.restype = C.c_void_p
+        L.vlab200_engine_create_from_gguf.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
         _LIB = L
     return _LIB
 
@@ -57,6 +75,9 @@ EXPORTS = [
     "vlab200_act_quant", "vlab200_ternary_linear",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
+    "vlab200_gguf_open", "vlab200_gguf_close", "vlab200_gguf_n_tensors", "vlab200_gguf_tensor_name",
+    "vlab200_gguf_tensor_info", "vlab200_gguf_tensor_data", "vlab200_gguf_read_f32", "vlab200_gguf_meta_u32",
+    "vlab200_gguf_meta_f64", "vlab200_gguf_meta_str", "vlab200_engine_create_from_gguf",
     "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
     "vlab200_node_norm_bf16",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
@@ -271,6 +292,66 @@ class DenoiseAttn:
         return out_host
 
 
+class Gguf:
+    """A GGUF checkpoint opened through the library's reader (host only; no GPU needed)."""
+
+    def __init__(self, path):
+        self.h = lib().vlab200_gguf_open(str(path).encode())
+        if not self.h:
+            raise VlaB200Error(ERR_ARG, "vlab200_gguf_open: " + lib().vlab200_last_error().decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().vlab200_gguf_close(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def names(self):
+        n = lib().vlab200_gguf_n_tensors(self.h)
+        return [lib().vlab200_gguf_tensor_name(self.h, i).decode() for i in range(n)]
+
+    def info(self, name):
+        """-> (ggml type id, dims fastest-first, bytes) or None."""
+        t, nd, nb = C.c_int32(), C.c_int32(), C.c_uint64()
+        dims = (C.c_int64 * 4)()
+        if lib().vlab200_gguf_tensor_info(self.h, name.encode(), C.byref(t), C.byref(nd), dims, C.byref(nb)) != OK:
+            return None
+        return t.value, [dims[i] for i in range(nd.value)], nb.value
+
+    def raw(self, name):
+        """The tensor's bytes as a numpy uint8 array (a copy)."""
+        import numpy as np
+
+        inf = self.info(name)
+        ptr = lib().vlab200_gguf_tensor_data(self.h, name.encode())
+        if inf is None or not ptr:
+            raise KeyError(name)
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(inf[2],)).copy()
+
+    def f32(self, name, gemma_norm=False):
+        import numpy as np
+
+        inf = self.info(name)
+        if inf is None:
+            raise KeyError(name)
+        out = np.empty(inf[1][::-1], dtype=np.float32)
+        _check(lib().vlab200_gguf_read_f32(self.h, name.encode(), out.ctypes.data_as(C.c_void_p), out.size,
+                                           int(gemma_norm)), "vlab200_gguf_read_f32")
+        return out
+
+    def meta(self, key):
+        u, d = C.c_uint32(), C.c_double()
+        buf = C.create_string_buffer(256)
+        if lib().vlab200_gguf_meta_u32(self.h, key.encode(), C.byref(u)) == OK:
+            return u.value
+        if lib().vlab200_gguf_meta_f64(self.h, key.encode(), C.byref(d)) == OK:
+            return d.value
+        if lib().vlab200_gguf_meta_str(self.h, key.encode(), buf, 256) == OK:
+            return buf.value.decode()
+        return None
+
+
 class _PolicyConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("model", "n_layers", "H", "n_q", "n_kv", "head_dim", "inter", "chunk",
                                           "action_dim", "state_dim", "steps", "self_every")] + [
@@ -323,6 +404,22 @@ class PolicyEngine:
         del keep
         if not self.h:
             raise VlaB200Error(ERR_CUDA, "vlab200_engine_create")
+
+    @classmethod
+    def from_gguf(cls, gguf, max_obs, prefix_len):
+        """The engine of a pi0 checkpoint (reference tensor names and metadata keys)."""
+        import torch
+
+        self = cls.__new__(cls)
+        self.h = lib().vlab200_engine_create_from_gguf(gguf.h, max_obs, prefix_len)
+        torch.cuda.synchronize()
+        if not self.h:
+            raise VlaB200Error(ERR_ARG, "vlab200_engine_create_from_gguf: " + lib().vlab200_last_error().decode())
+        self.max_obs, self.prefix_len = max_obs, prefix_len
+        self.chunk, self.A, self.sd = (gguf.meta("pi0.chunk_size"), gguf.meta("pi0.max_action_dim"),
+                                       gguf.meta("pi0.max_state_dim"))
+        self.cfg = None
+        return self
 
     def __del__(self):
         if getattr(self, "h", None):
