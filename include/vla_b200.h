@@ -353,6 +353,13 @@ VLAB200_API int32_t vlab200_gguf_meta_str(const vlab200_gguf *g, const char *key
 VLAB200_API vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g, int32_t max_obs,
                                                             int32_t prefix_len);
 
+/* The BitVLA LM stack of a checkpoint: "bitvla.lm.*" metadata (src/models/bitvla.cpp:360-364), per
+ * layer the four norm vectors and the six ladder-int2 tensors "lm.blk.N.<proj>.weight" (I8) with their
+ * "<proj>.scale" float32 sidecars (scripts/convert_bitvla_to_gguf.py:165-178; a missing sidecar fails the
+ * load as in bitvla.cpp:739-753), and "lm.output_norm.weight".  The context owns the uploaded weights. */
+VLAB200_API vlab200_bitvla_lm *vlab200_bitvla_lm_create_from_gguf(const vlab200_gguf *g, int32_t max_seq,
+                                                                  int32_t max_batch);
+
 /* ---- node-level bf16 operators ----------------------------------------------------------
  * What a per-node CUDA hook dispatches when it is handed one graph node at a time: the
  * reference's vla_cuda_bf16_forward (src/cuda/vla_cuda_bf16.cu:698-720) handles MUL_MAT, ADD,

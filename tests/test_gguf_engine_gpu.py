@@ -114,3 +114,60 @@ def test_engine_from_gguf_reports_what_is_wrong(oracle, tmp_path):
     g = vb.Gguf(path)
     with pytest.raises(vb.VlaB200Error, match="attn_o"):
         vb.PolicyEngine.from_gguf(g, max_obs=1, prefix_len=8)
+
+
+def _write_bitvla_lm(path, cfg, layers, out_norm, drop=None):
+    """The LM part of scripts/convert_bitvla_to_gguf.py:165-178,215-236,366-386: ladder packs as 1-D I8 tensors with
+    float32 .scale sidecars, norm vectors float32, "bitvla.lm.*" metadata."""
+    I8, F32 = gguf.GGMLQuantizationType.I8, gguf.GGMLQuantizationType.F32
+    w = gguf.GGUFWriter(str(path), "bitvla")
+    for k, v in (("hidden", cfg["hidden"]), ("layers", len(layers)), ("q_heads", cfg["n_q"]), ("kv_heads", cfg["n_kv"]),
+                 ("head_dim", cfg["head_dim"]), ("inter", cfg["ffn"])):
+        w.add_uint32("bitvla.lm." + k, v)
+    w.add_float32("bitvla.lm.rope_theta", cfg["rope_base"])
+    w.add_float32("bitvla.lm.rms_eps", cfg["rms_eps"])
+    names = dict(q="attn_q", k="attn_k", v="attn_v", o="attn_o", gate_up="ffn_gate_up", down="ffn_down")
+    for l, lw in enumerate(layers):
+        for k in ("attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm"):
+            w.add_tensor(f"lm.blk.{l}.{k}.weight", np.ascontiguousarray(lw[k + "_w"], dtype=np.float32), raw_dtype=F32)
+        for k, n in names.items():
+            packed = np.ascontiguousarray(lw[k + "_packed"], dtype=np.uint8)
+            w.add_tensor(f"lm.blk.{l}.{n}.weight", packed, raw_shape=[int(packed.size)], raw_dtype=I8)
+            if drop != f"lm.blk.{l}.{n}.scale":
+                w.add_tensor(f"lm.blk.{l}.{n}.scale", np.ascontiguousarray(lw[k + "_ws"], dtype=np.float32), raw_dtype=F32)
+    w.add_tensor("lm.output_norm.weight", np.ascontiguousarray(out_norm, dtype=np.float32), raw_dtype=F32)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+def test_bitvla_lm_from_gguf_matches_direct_context(oracle, tmp_path):
+    require_cuda()
+    import vla_cpp_b200 as vb
+    from tests.gpu_util import bf16_bits
+    from tests.test_bitvla_lm_gpu import SMALL, make_layer, to_dev_layer
+
+    rng = np.random.default_rng(21)
+    layers = [make_layer(oracle, rng, SMALL) for _ in range(2)]
+    out_norm = oracle.bf16_round(rng.uniform(0.8, 1.2, SMALL["hidden"]).astype(np.float32))
+    path = tmp_path / "bitvla.gguf"
+    _write_bitvla_lm(path, SMALL, layers, out_norm)
+    g = vb.Gguf(path)
+    assert g.info("lm.blk.0.ffn_gate_up.weight") == (24, [2 * SMALL["ffn"] * SMALL["hidden"] // 4],
+                                                     2 * SMALL["ffn"] * SMALL["hidden"] // 4)
+    lm_g = vb.BitvlaLM.from_gguf(g, max_seq=64, max_batch=2)
+    g.close()
+    lm_d = vb.BitvlaLM(SMALL["hidden"], SMALL["n_q"], SMALL["n_kv"], SMALL["head_dim"], SMALL["ffn"],
+                       [to_dev_layer(oracle, lw) for lw in layers], bits_to_bf16_tensor(oracle.f32_to_bf16_bits(out_norm)),
+                       rope_base=SMALL["rope_base"], rms_eps=SMALL["rms_eps"], max_seq=64, max_batch=2)
+    x = bits_to_bf16_tensor(oracle.f32_to_bf16_bits(
+        oracle.bf16_round(rng.standard_normal((2, 37, SMALL["hidden"])).astype(np.float32))))
+    a, b = bf16_bits(lm_g.forward(x)), bf16_bits(lm_d.forward(x))
+    assert vb.device_status() == 0
+    assert np.array_equal(a, b)
+
+    _write_bitvla_lm(tmp_path / "nosidecar.gguf", SMALL, layers, out_norm, drop="lm.blk.1.attn_o.scale")
+    g = vb.Gguf(tmp_path / "nosidecar.gguf")
+    with pytest.raises(vb.VlaB200Error, match="sidecar"):
+        vb.BitvlaLM.from_gguf(g)

@@ -57,6 +57,8 @@ def lib():
         L.vlab200_gguf_meta_u32.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint32)]
         L.vlab200_gguf_meta_f64.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_double)]
         L.vlab200_gguf_meta_str.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_int32]
+        L.vlab200_bitvla_lm_create_from_gguf.restype = C.c_void_p
+        L.vlab200_bitvla_lm_create_from_gguf.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
         L.vlab200_engine_create_from_gguf.restype = C.c_void_p
         L.vlab200_engine_create_from_gguf.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
         _LIB = L
@@ -78,6 +80,7 @@ EXPORTS = [
     "vlab200_gguf_open", "vlab200_gguf_close", "vlab200_gguf_n_tensors", "vlab200_gguf_tensor_name",
     "vlab200_gguf_tensor_info", "vlab200_gguf_tensor_data", "vlab200_gguf_read_f32", "vlab200_gguf_meta_u32",
     "vlab200_gguf_meta_f64", "vlab200_gguf_meta_str", "vlab200_engine_create_from_gguf",
+    "vlab200_bitvla_lm_create_from_gguf",
     "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
     "vlab200_node_norm_bf16",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
@@ -586,6 +589,17 @@ class BitvlaLM:
         if getattr(self, "h", None):
             lib().vlab200_bitvla_lm_free(C.c_void_p(self.h))
             self.h = None
+
+    @classmethod
+    def from_gguf(cls, gguf, max_seq=512, max_batch=1):
+        """The LM stack of a BitVLA checkpoint (ladder-int2 tensors with .scale sidecars); the context owns the weights."""
+        self = cls.__new__(cls)
+        self.h = lib().vlab200_bitvla_lm_create_from_gguf(gguf.h, max_seq, max_batch)
+        if not self.h:
+            raise VlaB200Error(ERR_ARG, "vlab200_bitvla_lm_create_from_gguf: " + lib().vlab200_last_error().decode())
+        self.hidden = gguf.meta("bitvla.lm.hidden")
+        self._keep = []
+        return self
 
     def forward(self, x, out=None):
         """x: cuda bf16 [n_seq, seq, hidden] (or [seq, hidden]) -> same shape."""

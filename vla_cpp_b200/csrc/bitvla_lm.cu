@@ -24,7 +24,9 @@
 #include <cuda_bf16.h>
 
 #include <cmath>
+#include <cstring>
 #include <new>
+#include <string>
 #include <vector>
 
 #include "gemm.h"
@@ -194,6 +196,7 @@ struct vlab200_bitvla_lm {
     const void *output_norm = nullptr;
     std::vector<vb::LmLayer> layers;
     vb::DevBuf cos_t, sin_t, h, a8, s, qkv, q, k_pages, v_pages, att, proj, gate_up;
+    std::vector<vb::DevBuf> owned;  // weights uploaded by vlab200_bitvla_lm_create_from_gguf
 };
 
 using vb::DevBuf;
@@ -392,4 +395,101 @@ extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void 
     // h += down of the last layer, then the output norm (bitvla_lm_cuda.cu:718)
     return vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, ctx->output_norm, ctx->eps, M, H, nullptr, nullptr,
                                              d_out, st);
+}
+
+// The LM stack of a BitVLA checkpoint: metadata "bitvla.lm.*" (src/models/bitvla.cpp:360-364), per layer four
+// float32 norm vectors (uploaded as bf16, bitvla.cpp:768-771) and six ladder-int2 tensors "<base>.weight" (I8,
+// N*K/4 bytes) with their "<base>.scale" float32 sidecars (scripts/convert_bitvla_to_gguf.py:165-178;
+// bitvla.cpp:739-753 fails the load when a sidecar is missing, and so does this).
+extern "C" vlab200_bitvla_lm *vlab200_bitvla_lm_create_from_gguf(const vlab200_gguf *g, int32_t max_seq,
+                                                                 int32_t max_batch) {
+    if (!g) return vb::set_last_error("gguf: null handle"), nullptr;
+    uint32_t hidden, n_layers, n_q, n_kv, hd, ffn;
+    const struct { const char *key; uint32_t *dst; } u32s[] = {
+        {"bitvla.lm.hidden", &hidden}, {"bitvla.lm.layers", &n_layers}, {"bitvla.lm.q_heads", &n_q},
+        {"bitvla.lm.kv_heads", &n_kv}, {"bitvla.lm.head_dim", &hd}, {"bitvla.lm.inter", &ffn}};
+    for (const auto &e : u32s)
+        if (vlab200_gguf_meta_u32(g, e.key, e.dst) != VLAB200_OK)
+            return vb::set_last_error("gguf: missing u32 metadata %s", e.key), nullptr;
+    double rope = 500000.0, eps = 1e-5;
+    if (vlab200_gguf_meta_f64(g, "bitvla.lm.rope_theta", &rope) != VLAB200_OK ||
+        vlab200_gguf_meta_f64(g, "bitvla.lm.rms_eps", &eps) != VLAB200_OK)
+        return vb::set_last_error("gguf: missing bitvla.lm.rope_theta / bitvla.lm.rms_eps"), nullptr;
+    vlab200_bitvla_lm *c = vlab200_bitvla_lm_init((int)hidden, (int)n_q, (int)n_kv, (int)hd, (int)ffn, (int)n_layers,
+                                                  (float)rope, (float)eps, max_seq, max_batch);
+    if (!c) return nullptr;
+    bool ok = true;
+    std::vector<float> tmp;
+    std::vector<uint16_t> tmp16;
+    auto upload = [&](const void *src, size_t bytes) -> const void * {
+        c->owned.emplace_back();
+        vb::DevBuf &b = c->owned.back();
+        if (b.alloc(bytes) != VLAB200_OK) return ok = false, nullptr;
+        if (cudaMemcpy(b.p, src, bytes, cudaMemcpyHostToDevice) != cudaSuccess)
+            return vb::cuda_fail(cudaGetLastError(), "cudaMemcpy (gguf upload)"), ok = false, nullptr;
+        return b.p;
+    };
+    auto norm = [&](const std::string &name, int64_t n) -> const void * {  // float32 vector -> bf16 on the device
+        if (!ok) return nullptr;
+        tmp.resize((size_t)n);
+        if (vlab200_gguf_read_f32(g, name.c_str(), tmp.data(), n, 0) != VLAB200_OK) return ok = false, nullptr;
+        tmp16.resize((size_t)n);
+        for (int64_t i = 0; i < n; ++i) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(tmp[(size_t)i]);
+            std::memcpy(&tmp16[(size_t)i], &h, 2);
+        }
+        return upload(tmp16.data(), (size_t)n * 2);
+    };
+    // ladder pack of an [N][K] matrix and its n_scales sidecar entries
+    auto bit = [&](const std::string &base, int64_t N, int64_t K, int n_scales, const void **packed, const float **ws) {
+        if (!ok) return;
+        const std::string wn = base + ".weight", sn = base + ".scale";
+        int32_t type = 0, nd = 0;
+        int64_t dims[4];
+        uint64_t nb = 0;
+        if (vlab200_gguf_tensor_info(g, wn.c_str(), &type, &nd, dims, &nb) != VLAB200_OK) {
+            vb::set_last_error("gguf: missing tensor %s", wn.c_str());
+            ok = false;
+            return;
+        }
+        if (type != 24 || nb != (uint64_t)(N * K / 4)) {
+            vb::set_last_error("gguf: %s is type %d with %llu bytes, expected I8 with %lld (ladder int2 of %lld x %lld)",
+                               wn.c_str(), type, (unsigned long long)nb, (long long)(N * K / 4), (long long)N, (long long)K);
+            ok = false;
+            return;
+        }
+        tmp.resize((size_t)n_scales);
+        if (vlab200_gguf_read_f32(g, sn.c_str(), tmp.data(), n_scales, 0) != VLAB200_OK) {
+            vb::set_last_error("gguf: int2 tensor %s has no %s sidecar with %d entries", wn.c_str(), sn.c_str(), n_scales);
+            ok = false;
+            return;
+        }
+        *ws = static_cast<const float *>(upload(tmp.data(), (size_t)n_scales * 4));
+        if (ok) *packed = upload(vlab200_gguf_tensor_data(g, wn.c_str()), (size_t)nb);
+    };
+    const int64_t hq = (int64_t)n_q * hd, hkv = (int64_t)n_kv * hd;
+    for (uint32_t l = 0; ok && l < n_layers; ++l) {
+        const std::string b = "lm.blk." + std::to_string(l) + ".";
+        vlab200_bitvla_lm_layer ly{};
+        ly.attn_norm_w = norm(b + "attn_norm.weight", hidden);
+        ly.attn_sub_norm_w = norm(b + "attn_sub_norm.weight", hidden);
+        ly.ffn_norm_w = norm(b + "ffn_norm.weight", hidden);
+        ly.ffn_sub_norm_w = norm(b + "ffn_sub_norm.weight", ffn);
+        bit(b + "attn_q", hq, hidden, 1, &ly.q_packed, &ly.q_ws);
+        bit(b + "attn_k", hkv, hidden, 1, &ly.k_packed, &ly.k_ws);
+        bit(b + "attn_v", hkv, hidden, 1, &ly.v_packed, &ly.v_ws);
+        bit(b + "attn_o", hidden, hq, 1, &ly.o_packed, &ly.o_ws);
+        bit(b + "ffn_gate_up", 2 * (int64_t)ffn, hidden, 2, &ly.gate_up_packed, &ly.gate_up_ws);
+        bit(b + "ffn_down", hidden, ffn, 1, &ly.down_packed, &ly.down_ws);
+        if (ok && vlab200_bitvla_lm_set_layer(c, (int)l, &ly) != VLAB200_OK) ok = false;
+    }
+    if (ok) {
+        const void *on = norm("lm.output_norm.weight", hidden);
+        if (ok) vlab200_bitvla_lm_set_output_norm(c, on);
+    }
+    if (!ok || cudaDeviceSynchronize() != cudaSuccess) {
+        vlab200_bitvla_lm_free(c);
+        return nullptr;
+    }
+    return c;
 }
