@@ -345,7 +345,9 @@ VLAB200_API int32_t vlab200_gguf_meta_u32(const vlab200_gguf *g, const char *key
 VLAB200_API int32_t vlab200_gguf_meta_f64(const vlab200_gguf *g, const char *key, double *out);
 VLAB200_API int32_t vlab200_gguf_meta_str(const vlab200_gguf *g, const char *key, char *buf, int32_t cap);
 
-/* The denoise engine of a pi0 checkpoint: metadata keys "pi0.*" (src/models/pi0.cpp:267-293), expert
+/* The denoise engine of a pi0 or SmolVLA checkpoint (general.architecture "pi0" / "smolvla"; SmolVLA:
+ * "smolvla.*" keys of src/models/smolvla.cpp:604-632, same tensor names through hf_to_gguf :648-703, no norm +1,
+ * no state_proj in the loop).  pi0: metadata keys "pi0.*" (src/models/pi0.cpp:267-293), expert
  * tensors "aex.blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_o,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight",
  * "aex.output_norm.weight" (Gemma norms get their +1) and the projection heads
  * (src/modules/gemma_expert.h:46-62, src/models/pi0.cpp:431-437).  Matrices are uploaded as bf16,

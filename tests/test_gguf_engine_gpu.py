@@ -1,4 +1,4 @@
-"""Engine built from a pi0-shaped GGUF (the reference converter's tensor names, metadata keys and dtypes,
+"""Engine built from a pi0- or SmolVLA-shaped GGUF (the reference converters' tensor names, metadata keys and dtypes,
 scripts/convert_pi0_to_gguf.py:234-244, scripts/gguf_blocks.py:104-142,196-211) against the engine built from
 the same weights handed over directly: bit-identical action chunks."""
 import numpy as np
@@ -20,10 +20,10 @@ def oracle():
     return oracle_ffi
 
 
-def _write_pi0(path, oracle, cfg, per, glob, bf16_matrices):
+def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
     F32, BF16 = gguf.GGMLQuantizationType.F32, gguf.GGMLQuantizationType.BF16
-    w = gguf.GGUFWriter(str(path), "pi0")
-    kv = lambda k: "pi0." + k
+    w = gguf.GGUFWriter(str(path), arch)
+    kv = lambda k: arch + "." + k
     for key, val in (("n_layers", cfg["n_layers"]), ("expert_h", cfg["H"]), ("n_q_heads", cfg["n_q"]),
                      ("n_kv_heads", cfg["n_kv"]), ("head_dim", cfg["head_dim"]), ("expert_inter", cfg["inter"]),
                      ("chunk_size", cfg["chunk"]), ("num_steps", cfg["steps"]), ("max_state_dim", cfg["state_dim"]),
@@ -31,8 +31,11 @@ def _write_pi0(path, oracle, cfg, per, glob, bf16_matrices):
         w.add_uint32(kv(key), val)
     w.add_float64(kv("min_period"), cfg["min_period"])
     w.add_float64(kv("max_period"), cfg["max_period"])
-    w.add_float64(kv("rope_theta"), cfg["rope_base"])
-    w.add_float32(kv("rms_norm_eps"), cfg["rms_eps"])
+    if arch == "pi0":
+        w.add_float64(kv("rope_theta"), cfg["rope_base"])
+        w.add_float32(kv("rms_norm_eps"), cfg["rms_eps"])
+    else:
+        w.add_uint32(kv("self_attn_every_n_layers"), cfg["self_every"])
 
     def mat(name, a):
         if bf16_matrices:
@@ -48,8 +51,9 @@ def _write_pi0(path, oracle, cfg, per, glob, bf16_matrices):
         for k, n in names.items():
             mat(f"aex.blk.{l}.{n}.weight", per[k][l])
     vec("aex.output_norm.weight", glob["out_norm_raw"])
-    for k, n in (("w_sp", "state_proj"), ("w_ain", "action_in_proj"), ("w_at1", "action_time_mlp_in"),
-                 ("w_at2", "action_time_mlp_out"), ("w_aout", "action_out_proj")):
+    heads = (("w_sp", "state_proj"),) if arch == "pi0" else ()
+    for k, n in heads + (("w_ain", "action_in_proj"), ("w_at1", "action_time_mlp_in"),
+                         ("w_at2", "action_time_mlp_out"), ("w_aout", "action_out_proj")):
         mat(n + ".weight", glob[k])
         vec(n + ".bias", glob["b_" + k[2:]])
     w.write_header_to_file()
@@ -58,24 +62,30 @@ def _write_pi0(path, oracle, cfg, per, glob, bf16_matrices):
     w.close()
 
 
-@pytest.mark.parametrize("bf16_matrices", [True, False])
-def test_engine_from_gguf_matches_direct_engine(oracle, tmp_path, bf16_matrices):
+@pytest.mark.parametrize("arch,bf16_matrices", [("pi0", True), ("pi0", False), ("smolvla", True)])
+def test_engine_from_gguf_matches_direct_engine(oracle, tmp_path, arch, bf16_matrices):
     torch = require_cuda()
     import vla_cpp_b200 as vb
 
     rng = np.random.default_rng(11)
     P, n_obs = 40, 3
-    cfg, per, glob, _ = make_policy(oracle, rng, model=0, L=2, H=128, n_q=2, n_kv=1, hd=64, inter=256, P=P, chunk=10,
-                                    A=32, sd=32, T=3)
-    # Gemma norms are stored without their +1
-    per["ln_raw_in"] = [(a - 1).astype(np.float32) for a in per["ln_in"]]
-    per["ln_raw_post"] = [(a - 1).astype(np.float32) for a in per["ln_post"]]
-    per["ln_in"] = [a + np.float32(1) for a in per["ln_raw_in"]]
-    per["ln_post"] = [a + np.float32(1) for a in per["ln_raw_post"]]
-    glob["out_norm_raw"] = (glob["out_norm"] - 1).astype(np.float32)
-    glob["out_norm"] = glob["out_norm_raw"] + np.float32(1)
-    path = tmp_path / "pi0.gguf"
-    _write_pi0(path, oracle, cfg, per, glob, bf16_matrices)
+    if arch == "pi0":
+        cfg, per, glob, _ = make_policy(oracle, rng, model=0, L=2, H=128, n_q=2, n_kv=1, hd=64, inter=256, P=P,
+                                        chunk=10, A=32, sd=32, T=3)
+        # Gemma norms are stored without their +1
+        off = np.float32(1)
+    else:
+        cfg, per, glob, _ = make_policy(oracle, rng, model=1, L=4, H=128, n_q=4, n_kv=2, hd=64, inter=256, P=P,
+                                        chunk=10, A=32, sd=32, T=3, self_every=2)
+        off = np.float32(0)
+    per["ln_raw_in"] = [(a - off).astype(np.float32) for a in per["ln_in"]]
+    per["ln_raw_post"] = [(a - off).astype(np.float32) for a in per["ln_post"]]
+    per["ln_in"] = [a + off for a in per["ln_raw_in"]]
+    per["ln_post"] = [a + off for a in per["ln_raw_post"]]
+    glob["out_norm_raw"] = (glob["out_norm"] - off).astype(np.float32)
+    glob["out_norm"] = glob["out_norm_raw"] + off
+    path = tmp_path / "policy.gguf"
+    _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch)
 
     g = vb.Gguf(path)
     eng_g = vb.PolicyEngine.from_gguf(g, max_obs=n_obs, prefix_len=P)
@@ -110,7 +120,7 @@ def test_engine_from_gguf_reports_what_is_wrong(oracle, tmp_path):
     per["ln_raw_in"], per["ln_raw_post"], glob["out_norm_raw"] = per["ln_in"], per["ln_post"], glob["out_norm"]
     per["wo"][0] = per["wo"][0][:, :64]  # wrong shape
     path = tmp_path / "bad.gguf"
-    _write_pi0(path, oracle, cfg, per, glob, True)
+    _write_policy(path, oracle, cfg, per, glob, True)
     g = vb.Gguf(path)
     with pytest.raises(vb.VlaB200Error, match="attn_o"):
         vb.PolicyEngine.from_gguf(g, max_obs=1, prefix_len=8)

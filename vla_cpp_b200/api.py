@@ -410,7 +410,7 @@ class PolicyEngine:
 
     @classmethod
     def from_gguf(cls, gguf, max_obs, prefix_len):
-        """The engine of a pi0 checkpoint (reference tensor names and metadata keys)."""
+        """The engine of a pi0 or SmolVLA checkpoint (reference tensor names and metadata keys)."""
         import torch
 
         self = cls.__new__(cls)
@@ -419,8 +419,9 @@ class PolicyEngine:
         if not self.h:
             raise VlaB200Error(ERR_ARG, "vlab200_engine_create_from_gguf: " + lib().vlab200_last_error().decode())
         self.max_obs, self.prefix_len = max_obs, prefix_len
-        self.chunk, self.A, self.sd = (gguf.meta("pi0.chunk_size"), gguf.meta("pi0.max_action_dim"),
-                                       gguf.meta("pi0.max_state_dim"))
+        arch = gguf.meta("general.architecture")
+        self.chunk, self.A, self.sd = (gguf.meta(arch + ".chunk_size"), gguf.meta(arch + ".max_action_dim"),
+                                       gguf.meta(arch + ".max_state_dim"))
         self.cfg = None
         return self
 

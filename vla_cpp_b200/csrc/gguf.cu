@@ -391,44 +391,55 @@ struct Upload {
 extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g, int32_t max_obs, int32_t prefix_len) {
     if (!g) return vb::set_last_error("gguf: null handle"), nullptr;
     char arch[32] = "";
-    if (vlab200_gguf_meta_str(g, "general.architecture", arch, sizeof arch) != VLAB200_OK || std::strcmp(arch, "pi0") != 0)
-        return vb::set_last_error("gguf: general.architecture is '%s'; only pi0 checkpoints are mapped to the engine", arch), nullptr;
-    // metadata keys of src/models/pi0.cpp:267-293
-    uint32_t n_layers, H, n_q, n_kv, hd, inter, chunk, steps, sdim, adim;
+    vlab200_gguf_meta_str(g, "general.architecture", arch, sizeof arch);
+    const bool pi0 = std::strcmp(arch, "pi0") == 0, smol = std::strcmp(arch, "smolvla") == 0;
+    if (!pi0 && !smol)
+        return vb::set_last_error("gguf: general.architecture is '%s'; pi0 and smolvla checkpoints are mapped to the engine", arch), nullptr;
+    const std::string pfx = std::string(arch) + ".";
+    // metadata keys of src/models/pi0.cpp:267-293 and src/models/smolvla.cpp:604-632
+    uint32_t n_layers, H, n_q, n_kv, hd, inter, chunk, steps, sdim, adim, self_every = 1;
     const struct { const char *key; uint32_t *dst; } u32s[] = {
-        {"pi0.n_layers", &n_layers}, {"pi0.expert_h", &H}, {"pi0.n_q_heads", &n_q}, {"pi0.n_kv_heads", &n_kv},
-        {"pi0.head_dim", &hd}, {"pi0.expert_inter", &inter}, {"pi0.chunk_size", &chunk}, {"pi0.num_steps", &steps},
-        {"pi0.max_state_dim", &sdim}, {"pi0.max_action_dim", &adim}};
+        {"n_layers", &n_layers}, {"expert_h", &H}, {"n_q_heads", &n_q}, {"n_kv_heads", &n_kv},
+        {"head_dim", &hd}, {"expert_inter", &inter}, {"chunk_size", &chunk}, {"num_steps", &steps},
+        {"max_state_dim", &sdim}, {"max_action_dim", &adim}};
     for (const auto &e : u32s)
-        if (vlab200_gguf_meta_u32(g, e.key, e.dst) != VLAB200_OK)
-            return vb::set_last_error("gguf: missing u32 metadata %s", e.key), nullptr;
+        if (vlab200_gguf_meta_u32(g, (pfx + e.key).c_str(), e.dst) != VLAB200_OK)
+            return vb::set_last_error("gguf: missing u32 metadata %s%s", pfx.c_str(), e.key), nullptr;
+    if (smol && vlab200_gguf_meta_u32(g, "smolvla.self_attn_every_n_layers", &self_every) != VLAB200_OK)
+        return vb::set_last_error("gguf: missing u32 metadata smolvla.self_attn_every_n_layers"), nullptr;
     vlab200_policy_config cfg{};
-    cfg.model = 0;
+    cfg.model = pi0 ? 0 : 1;
     cfg.n_layers = (int32_t)n_layers; cfg.H = (int32_t)H; cfg.n_q = (int32_t)n_q; cfg.n_kv = (int32_t)n_kv;
     cfg.head_dim = (int32_t)hd; cfg.inter = (int32_t)inter; cfg.chunk = (int32_t)chunk;
     cfg.action_dim = (int32_t)adim; cfg.state_dim = (int32_t)sdim; cfg.steps = (int32_t)steps;
-    cfg.self_every = 1;
+    cfg.self_every = (int32_t)self_every;
     double v;
-    cfg.rms_eps = vlab200_gguf_meta_f64(g, "pi0.rms_norm_eps", &v) == VLAB200_OK ? (float)v : 1e-6f;
-    cfg.rope_base = vlab200_gguf_meta_f64(g, "pi0.rope_theta", &v) == VLAB200_OK ? (float)v : 10000.0f;
-    if (vlab200_gguf_meta_f64(g, "pi0.min_period", &cfg.min_period) != VLAB200_OK ||
-        vlab200_gguf_meta_f64(g, "pi0.max_period", &cfg.max_period) != VLAB200_OK)
-        return vb::set_last_error("gguf: missing pi0.min_period / pi0.max_period"), nullptr;
-    if (n_layers == 0 || n_layers > 1024) return vb::set_last_error("gguf: pi0.n_layers = %u", n_layers), nullptr;
+    // SmolVLA fixes both constants in code (smolvla.cpp:622-624); pi0 reads them when present (pi0.cpp:289-293)
+    cfg.rms_eps = smol ? 1e-5f : (vlab200_gguf_meta_f64(g, "pi0.rms_norm_eps", &v) == VLAB200_OK ? (float)v : 1e-6f);
+    cfg.rope_base = (pi0 && vlab200_gguf_meta_f64(g, "pi0.rope_theta", &v) == VLAB200_OK) ? (float)v : 10000.0f;
+    if (vlab200_gguf_meta_f64(g, (pfx + "min_period").c_str(), &cfg.min_period) != VLAB200_OK ||
+        vlab200_gguf_meta_f64(g, (pfx + "max_period").c_str(), &cfg.max_period) != VLAB200_OK)
+        return vb::set_last_error("gguf: missing %smin_period / %smax_period", pfx.c_str(), pfx.c_str()), nullptr;
+    if (n_layers == 0 || n_layers > 1024) return vb::set_last_error("gguf: %sn_layers = %u", pfx.c_str(), n_layers), nullptr;
 
-    // tensor names of src/modules/gemma_expert.h:46-62 and src/models/pi0.cpp:431-437
+    // tensor names of src/modules/gemma_expert.h:46-62 / src/models/pi0.cpp:431-437 and, for SmolVLA, of
+    // hf_to_gguf (src/models/smolvla.cpp:648-703) and the projection heads (smolvla.cpp:1226-1236); only Gemma
+    // norms carry the "+1"
     vb::Upload up;
     const int64_t qd = (int64_t)n_q * hd, kvd = (int64_t)n_kv * hd;
     std::vector<const void *> wq(n_layers), wk(n_layers), wv(n_layers), wo(n_layers), wg(n_layers), wu(n_layers), wd(n_layers);
     std::vector<const float *> ln_in(n_layers), ln_post(n_layers);
     for (uint32_t l = 0; l < n_layers; ++l) {
         const std::string b = "aex.blk." + std::to_string(l) + ".";
-        ln_in[l] = static_cast<const float *>(up.get(g, b + "attn_norm.weight", H, 1, false, true));
+        // SmolVLA cross-attention layers project the VLM's K / V rows ([n_kv*hd] wide) instead of the expert's
+        const bool cross = smol && self_every > 1 && l % self_every != 0;
+        const int64_t kv_in = cross ? kvd : (int64_t)H;
+        ln_in[l] = static_cast<const float *>(up.get(g, b + "attn_norm.weight", H, 1, false, pi0));
         wq[l] = up.get(g, b + "attn_q.weight", H, qd, true, false);
-        wk[l] = up.get(g, b + "attn_k.weight", H, kvd, true, false);
-        wv[l] = up.get(g, b + "attn_v.weight", H, kvd, true, false);
+        wk[l] = up.get(g, b + "attn_k.weight", kv_in, kvd, true, false);
+        wv[l] = up.get(g, b + "attn_v.weight", kv_in, kvd, true, false);
         wo[l] = up.get(g, b + "attn_o.weight", qd, H, true, false);
-        ln_post[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.weight", H, 1, false, true));
+        ln_post[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.weight", H, 1, false, pi0));
         wg[l] = up.get(g, b + "ffn_gate.weight", H, inter, true, false);
         wu[l] = up.get(g, b + "ffn_up.weight", H, inter, true, false);
         wd[l] = up.get(g, b + "ffn_down.weight", inter, H, true, false);
@@ -437,9 +448,12 @@ extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g
     w.wq = wq.data(); w.wk = wk.data(); w.wv = wv.data(); w.wo = wo.data();
     w.wgate = wg.data(); w.wup = wu.data(); w.wdown = wd.data();
     w.ln_in = ln_in.data(); w.ln_post = ln_post.data();
-    w.out_norm = static_cast<const float *>(up.get(g, "aex.output_norm.weight", H, 1, false, true));
+    w.out_norm = static_cast<const float *>(up.get(g, "aex.output_norm.weight", H, 1, false, pi0));
     auto vec = [&](const char *name, int64_t n) { return static_cast<const float *>(up.get(g, name, n, 1, false, false)); };
-    w.w_sp = up.get(g, "state_proj.weight", sdim, H, true, false);            w.b_sp = vec("state_proj.bias", H);
+    if (pi0) {  // SmolVLA's state token belongs to the prefix (smolvla.cpp:1103-1104), not to the denoise loop
+        w.w_sp = up.get(g, "state_proj.weight", sdim, H, true, false);
+        w.b_sp = vec("state_proj.bias", H);
+    }
     w.w_ain = up.get(g, "action_in_proj.weight", adim, H, true, false);       w.b_ain = vec("action_in_proj.bias", H);
     w.w_at1 = up.get(g, "action_time_mlp_in.weight", 2 * (int64_t)H, H, true, false);
     w.b_at1 = vec("action_time_mlp_in.bias", H);
