@@ -327,3 +327,26 @@ def test_loop_driver_matches_stepwise_calls(oracle):
     torch.cuda.synchronize()
     assert vb.device_status() == 0
     assert torch.equal(out_host, out.cpu())
+
+
+def test_attention_output_aligned_to_16_bytes_only(oracle):
+    """The head_dim-64 kernel writes 32-byte sectors when `out` allows it and falls back to 16-byte stores when the
+    buffer is only 16-byte aligned: same bits either way."""
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(77)
+    n_obs, n_q, n_kv, S, P, hd = 3, 15, 5, 51, 177, 64
+    st = vb.KvStore(1, n_obs, n_kv, hd, P, S)
+    st.k.copy_(bf16_tensor(oracle, oracle.bf16_round(rng.standard_normal(tuple(st.k.shape)).astype(np.float32))))
+    st.v.copy_(bf16_tensor(oracle, oracle.bf16_round(rng.standard_normal(tuple(st.v.shape)).astype(np.float32))))
+    q = bf16_tensor(oracle, oracle.bf16_round(rng.standard_normal((n_obs, n_q, S, hd)).astype(np.float32)))
+    want = vb.attention(st, 0, q, S, n_q, P + S, 2)
+    assert want.data_ptr() % 32 == 0
+    n = want.numel()
+    buf = torch.zeros(n + 16, dtype=torch.bfloat16, device="cuda")
+    out = buf[8:8 + n].view(want.shape)  # 16 bytes past a 32-byte boundary
+    assert out.data_ptr() % 32 == 16
+    vb.attention(st, 0, q, S, n_q, P + S, 2, out=out)
+    assert vb.device_status() == 0
+    assert torch.equal(out, want) and float(buf[:8].abs().sum()) == 0 and float(buf[8 + n:].abs().sum()) == 0
