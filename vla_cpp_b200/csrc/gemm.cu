@@ -245,8 +245,36 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                 tmem_ld_wait();
                 if (!row_ok) continue;
                 if (p.epi == EPI_RESIDUAL) {
-                    float4 *hp = reinterpret_cast<float4 *>(p.h + mo * p.ld_out + n);
-                    uint4 *bp = reinterpret_cast<uint4 *>(p.out_bf + mo * p.ld_out + n);
+                    float *hrow = p.h + mo * p.ld_out + n;
+                    __nv_bfloat16 *brow = p.out_bf + mo * p.ld_out + n;
+                    if (p.al32) {
+                        // 8 float32 columns = one 32-byte sector per load / store and thread
+#pragma unroll
+                        for (int q8 = 0; q8 < 2; ++q8) {
+                            if (n + 16 * q8 >= p.N) break;
+                            const bool two = n + 16 * q8 + 8 < p.N;
+                            uint32_t w[8];
+#pragma unroll
+                            for (int hlf = 0; hlf < 2; ++hlf) {
+                                if (hlf && !two) break;
+                                const int c0 = 16 * q8 + 8 * hlf;
+                                uint32_t a[8];
+                                ld_global_v8(hrow + c0, a);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) + __uint_as_float(v[c0 + e]));
+                                st_global_v8(hrow + c0, a);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(a[2 * e]), __uint_as_float(a[2 * e + 1]));
+                                    w[4 * hlf + e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                }
+                            }
+                            if (two) st_global_v8(brow + 16 * q8, w);
+                            else *reinterpret_cast<uint4 *>(brow + 16 * q8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                    float4 *hp = reinterpret_cast<float4 *>(hrow);
+                    uint4 *bp = reinterpret_cast<uint4 *>(brow);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         if (n + 8 * q4 >= p.N) break;
@@ -262,6 +290,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                         bp[q4] = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
                                             *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
                     }
+                    }
                 } else if (p.epi == EPI_GATED) {
                     uint32_t w[8];
 #pragma unroll
@@ -271,9 +300,14 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                         const __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
                         w[e] = *reinterpret_cast<const uint32_t *>(&h2);
                     }
-                    uint4 *bp = reinterpret_cast<uint4 *>(p.out_bf + mo * p.ld_out + (n >> 1));
-                    bp[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                    if (n + 16 < p.N) bp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    __nv_bfloat16 *brow = p.out_bf + mo * p.ld_out + (n >> 1);
+                    if (p.al32 && n + 16 < p.N) {
+                        st_global_v8(brow, w);
+                    } else {
+                        uint4 *bp = reinterpret_cast<uint4 *>(brow);
+                        bp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (n + 16 < p.N) bp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
                 } else {
                     float f[32];
 #pragma unroll
@@ -355,6 +389,12 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
     if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
     if (p.N % 8 || (p.epi == EPI_GATED && p.N % 16) || p.K % 8 || lda % 8 || p.ld_out % 8) return VLAB200_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VLAB200_ERR_ARG;
+    {
+        // 256-bit epilogue accesses need every touched row segment on a 32-byte boundary
+        const bool f32_ok = !p.h || ((reinterpret_cast<uintptr_t>(p.h) & 31) == 0 && p.ld_out % 8 == 0);
+        const bool bf_ok = !p.out_bf || ((reinterpret_cast<uintptr_t>(p.out_bf) & 31) == 0 && p.ld_out % 16 == 0);
+        p.al32 = (p.rows_in == 0 && f32_ok && bf_ok) ? 1 : 0;
+    }
     p.status = device_status_ptr();
     if (!p.status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
     CUtensorMap amap, wmap;

@@ -19,6 +19,7 @@ struct GemmParams {
     int ld_out;             // row stride (elements) of out_bf / out_f32 / h
     int rows_in, rows_out, row_off;  // BIAS_ACT row re-mapping (rows_in == 0: identity)
     int scatter_hd, scatter_cap;     // BIAS_ACT into head-major pages: [m / rows_in][n / hd][cap][hd] (0: off)
+    int al32;  // set by dense_gemm: h / out_bf rows start on 32-byte boundaries (256-bit epilogue accesses)
     int *status;
 };
 
