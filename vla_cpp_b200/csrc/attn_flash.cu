@@ -31,6 +31,7 @@ struct FlashParams {
     const int32_t *pad;
     int S, n_q, n_kv, g, kv_len, prefix_len, mask_mode, R, n_mt, n_units, n_blocks, page0;
     float scale_log2;
+    int out_al32;  // out is 32-byte aligned: 256-bit stores
     int *status;
 };
 
@@ -320,17 +321,22 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
                 tmem_ld_wait();
                 if (row_ok) {
-                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + c);
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t w[4];
+                    for (int q8 = 0; q8 < 2; ++q8) {
+                        uint32_t w[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[8 * q4 + 2 * e]) * inv,
-                                                                           __uint_as_float(ov[8 * q4 + 2 * e + 1]) * inv);
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[16 * q8 + 2 * e]) * inv,
+                                                                           __uint_as_float(ov[16 * q8 + 2 * e + 1]) * inv);
                             w[e] = *reinterpret_cast<const uint32_t *>(&h);
                         }
-                        d4[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (p.out_al32) {  // one full 32-byte sector per store instruction and thread
+                            st_global_v8(dst + c + 16 * q8, w);
+                        } else {
+                            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c + 16 * q8);
+                            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
                     }
                 }
             }
@@ -729,17 +735,22 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
                 tmem_ld_wait();
                 if (row_ok) {
-                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + c);
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t w[4];
+                    for (int q8 = 0; q8 < 2; ++q8) {
+                        uint32_t w[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[8 * q4 + 2 * e]) * inv,
-                                                                           __uint_as_float(ov[8 * q4 + 2 * e + 1]) * inv);
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[16 * q8 + 2 * e]) * inv,
+                                                                           __uint_as_float(ov[16 * q8 + 2 * e + 1]) * inv);
                             w[e] = *reinterpret_cast<const uint32_t *>(&h);
                         }
-                        d4[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (p.out_al32) {  // one full 32-byte sector per store instruction and thread
+                            st_global_v8(dst + c + 16 * q8, w);
+                        } else {
+                            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c + 16 * q8);
+                            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
                     }
                 }
             }
@@ -795,6 +806,7 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
     p.n_blocks = (kv_len + FA_BKV - 1) / FA_BKV;
     p.page0 = layer * st->n_obs * st->n_kv;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
     static bool attr_done = false;
     static int n_sm = 0;
