@@ -125,6 +125,102 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(__nv_bfloat16 *__restri
     }
 }
 
+// The same stage with 16-byte accesses and the row held in registers (packed bf16) between the passes: thread t
+// owns the 8-element groups t, t + 256, ... (at most NV of them), so K <= 2048 * NV and K % 8 == 0.  Per element the
+// arithmetic is the one of norm_quant_kernel; only the order of the float sum of squares differs.
+template <int MODE, int NV>
+__global__ void __launch_bounds__(256) norm_quant_vec_kernel(__nv_bfloat16 *__restrict__ in,
+                                                             const __nv_bfloat16 *__restrict__ add,
+                                                             const __nv_bfloat16 *__restrict__ w, float eps, int K,
+                                                             int8_t *__restrict__ q_out, float *__restrict__ s_out,
+                                                             __nv_bfloat16 *__restrict__ out_bf) {
+    __shared__ float red[8];
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const int K8 = K >> 3;
+    const size_t ld = MODE == NQ_GATE_UP ? 2 * (size_t)K : (size_t)K;
+    uint4 *src = reinterpret_cast<uint4 *>(in + m * ld);
+    uint4 x[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = tid + v * 256;
+        if (i >= K8) break;
+        uint4 xv = src[i];
+        uint32_t *xw = reinterpret_cast<uint32_t *>(&xv);
+        if (MODE == NQ_ADD) {
+            const uint4 av = reinterpret_cast<const uint4 *>(add + m * ld)[i];
+            const uint32_t *aw = reinterpret_cast<const uint32_t *>(&av);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[e]));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&aw[e]));
+                const __nv_bfloat162 r = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+                xw[e] = *reinterpret_cast<const uint32_t *>(&r);
+            }
+            src[i] = xv;
+        } else if (MODE == NQ_GATE_UP) {
+            const uint4 uv = src[K8 + i];
+            const uint32_t *uw = reinterpret_cast<const uint32_t *>(&uv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[e]));
+                const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&uw[e]));
+                const float g0 = fmaxf(g.x, 0.f), g1 = fmaxf(g.y, 0.f);
+                const __nv_bfloat162 r = __floats2bfloat162_rn(g0 * g0 * u.x, g1 * g1 * u.y);
+                xw[e] = *reinterpret_cast<const uint32_t *>(&r);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[e]));
+            ss += f.x * f.x + f.y * f.y;
+        }
+        x[v] = xv;
+    }
+    ss = block_sum_256(ss, red);
+    const float scale = rsqrtf(ss / (float)K + eps);
+    float amax = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = tid + v * 256;
+        if (i >= K8) break;
+        const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w) + i);
+        const uint32_t *ww = reinterpret_cast<const uint32_t *>(&wv);
+        uint32_t *xw = reinterpret_cast<uint32_t *>(&x[v]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[e]));
+            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&ww[e]));
+            const __nv_bfloat162 y = __floats2bfloat162_rn(f.x * scale * g.x, f.y * scale * g.y);
+            xw[e] = *reinterpret_cast<const uint32_t *>(&y);
+            const float2 yf = __bfloat1622float2(y);
+            amax = fmaxf(amax, fmaxf(fabsf(yf.x), fabsf(yf.y)));
+        }
+        if (out_bf) reinterpret_cast<uint4 *>(out_bf + (size_t)m * K)[i] = x[v];
+    }
+    if (out_bf) return;
+    amax = block_max_256(amax, red);
+    amax = amax < 1e-5f ? 1e-5f : amax;
+    const float qs = __fdiv_rn(127.0f, amax);
+    if (tid == 0) s_out[m] = qs;
+    uint2 *dst = reinterpret_cast<uint2 *>(q_out + (size_t)m * K);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = tid + v * 256;
+        if (i >= K8) break;
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(&x[v]);
+        uint32_t o[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 yf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[e]));
+            const int a = (int)fminf(fmaxf(rintf(yf.x * qs), -128.f), 127.f);
+            const int b = (int)fminf(fmaxf(rintf(yf.y * qs), -128.f), 127.f);
+            o[e >> 1] |= ((uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8)) << (16 * (e & 1));
+        }
+        dst[i] = make_uint2(o[0], o[1]);
+    }
+}
+
 // qkv: bf16 [M][(n_q + 2 n_kv_proj) hd] (q heads, k heads, v heads) -> q_out [n_seq][n_q][seq][hd]
 // rotated, K page rows rotated, V page rows copied.  Pages: [n_seq][n_kv_store][cap][hd], token s of a
 // sequence goes to page row row0 + s.  n_kv_proj == 0: only q heads are present (cross-attention).
@@ -162,9 +258,65 @@ __global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__
     }
 }
 
+// The same with 16-byte accesses: one work item = 8 consecutive elements of a head's first half and the matching
+// 8 of its second half (hd % 16 == 0, 16-byte aligned buffers).
+__global__ void __launch_bounds__(128) rope_split_vec_kernel(const __nv_bfloat16 *__restrict__ qkv,
+                                                             const float *__restrict__ cos_t,
+                                                             const float *__restrict__ sin_t,
+                                                             __nv_bfloat16 *__restrict__ q_out,
+                                                             __nv_bfloat16 *__restrict__ k_pages,
+                                                             __nv_bfloat16 *__restrict__ v_pages, int seq, int n_q,
+                                                             int n_kv_proj, int n_kv_store, int hd, int cap, int row0) {
+    const int m = blockIdx.x;
+    const int sq = m / seq, s = m % seq;
+    const int half = hd >> 1, h8 = half >> 3;
+    const int n_heads = n_q + 2 * n_kv_proj;
+    const __nv_bfloat16 *src = qkv + (size_t)m * n_heads * hd;
+    for (int i = threadIdx.x; i < n_heads * h8; i += blockDim.x) {
+        const int head = i / h8, k = (i % h8) * 8;
+        const __nv_bfloat16 *hp = src + (size_t)head * hd;
+        uint4 lo = *reinterpret_cast<const uint4 *>(hp + k), hi = *reinterpret_cast<const uint4 *>(hp + k + half);
+        __nv_bfloat16 *dst;
+        if (head < n_q + n_kv_proj) {
+            const float4 *cp = reinterpret_cast<const float4 *>(cos_t + (size_t)s * half + k);
+            const float4 *sp = reinterpret_cast<const float4 *>(sin_t + (size_t)s * half + k);
+            const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            uint32_t *lw = reinterpret_cast<uint32_t *>(&lo), *hw = reinterpret_cast<uint32_t *>(&hi);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lw[e]));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&hw[e]));
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(a.x * c[2 * e] - b.x * sn[2 * e],
+                                                                a.y * c[2 * e + 1] - b.y * sn[2 * e + 1]);
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x * c[2 * e] + a.x * sn[2 * e],
+                                                                b.y * c[2 * e + 1] + a.y * sn[2 * e + 1]);
+                lw[e] = *reinterpret_cast<const uint32_t *>(&l2);
+                hw[e] = *reinterpret_cast<const uint32_t *>(&h2);
+            }
+            dst = head < n_q ? q_out + (((size_t)sq * n_q + head) * seq + s) * hd
+                             : k_pages + (((size_t)sq * n_kv_store + (head - n_q)) * cap + row0 + s) * hd;
+        } else {
+            dst = v_pages + (((size_t)sq * n_kv_store + (head - n_q - n_kv_proj)) * cap + row0 + s) * hd;
+        }
+        *reinterpret_cast<uint4 *>(dst + k) = lo;
+        *reinterpret_cast<uint4 *>(dst + k + half) = hi;
+    }
+}
+
 // Host entry for other translation units (the engine's few-row path).
 int rope_split(const void *qkv, const float *cos_t, const float *sin_t, void *q_out, void *k_pages, void *v_pages,
                int M, int seq, int n_q, int n_kv_proj, int n_kv_store, int hd, int cap, int row0, cudaStream_t st) {
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (hd % 16 == 0 && al16(qkv) && al16(cos_t) && al16(sin_t) && al16(q_out) && al16(k_pages) && al16(v_pages)) {
+        rope_split_vec_kernel<<<M, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
+                                                 static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
+                                                 static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd,
+                                                 cap, row0);
+        VB_CUDA(cudaGetLastError());
+        return VLAB200_OK;
+    }
     rope_split_kernel<<<M, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
                                          static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
                                          static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd, cap,
@@ -302,16 +454,23 @@ namespace vb {
 template <int MODE>
 static int launch_norm_quant(void *in, const void *add, const void *w, float eps, int M, int K, int8_t *q, float *s,
                              void *out_bf, cudaStream_t st) {
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    __nv_bfloat16 *in_b = static_cast<__nv_bfloat16 *>(in);
+    const __nv_bfloat16 *add_b = static_cast<const __nv_bfloat16 *>(add), *w_b = static_cast<const __nv_bfloat16 *>(w);
+    __nv_bfloat16 *out_b = static_cast<__nv_bfloat16 *>(out_bf);
+    if (K % 8 == 0 && K <= 8192 && al16(in) && al16(add) && al16(w) && al16(out_bf) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
+        if (K <= 4096) norm_quant_vec_kernel<MODE, 2><<<M, 256, 0, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
+        else norm_quant_vec_kernel<MODE, 4><<<M, 256, 0, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
+        VB_CUDA(cudaGetLastError());
+        return VLAB200_OK;
+    }
     static bool attr_done = false;
     const size_t smem = (size_t)K * 4;
     if (smem > 48 * 1024 && !attr_done) {
         VB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done = true;
     }
-    norm_quant_kernel<MODE><<<M, 256, smem, st>>>(static_cast<__nv_bfloat16 *>(in),
-                                                  static_cast<const __nv_bfloat16 *>(add),
-                                                  static_cast<const __nv_bfloat16 *>(w), eps, K, q, s,
-                                                  static_cast<__nv_bfloat16 *>(out_bf));
+    norm_quant_kernel<MODE><<<M, 256, smem, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
