@@ -104,7 +104,8 @@ def test_lm_rejects_bad_arguments(oracle):
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
-@pytest.mark.parametrize("m,k", [(1, 256), (37, 2560), (5, 6912), (3, 250), (2, 8200), (4, 4096), (3, 8192)])  # 250, 8200: scalar kernel
+@pytest.mark.parametrize("m,k", [(1, 256), (37, 2560), (5, 6912), (3, 250), (2, 8200), (4, 4096), (3, 8192),
+                                 (70, 2560), (100, 1024), (65, 4096), (64, 2048)])  # 250, 8200: scalar kernel
 def test_norm_quant_stage(oracle, mode, m, k):
     require_cuda()
     from vla_cpp_b200 import api
