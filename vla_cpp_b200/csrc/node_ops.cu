@@ -62,18 +62,53 @@ __global__ void __launch_bounds__(256) bin_kernel(const __nv_bfloat16 *__restric
     }
 }
 
+// 8 elements per thread and iteration (16-byte accesses); n % 8 == 0, nb % 8 == 0, 16-byte aligned pointers
+template <bool MUL, typename TB>
+__global__ void __launch_bounds__(256) bin_vec_kernel(const __nv_bfloat16 *__restrict__ a, const TB *__restrict__ b,
+                                                      __nv_bfloat16 *__restrict__ out, int64_t n8, int64_t nb8) {
+    const uint4 *av = reinterpret_cast<const uint4 *>(a);
+    uint4 *ov = reinterpret_cast<uint4 *>(out);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 x = __ldg(av + i);
+        const int64_t j = nb8 == n8 ? i : i % nb8;
+        float y[8];
+        if (sizeof(TB) == 2) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4 *>(b) + j);
+            const float2 p0 = unpack2(u.x), p1 = unpack2(u.y), p2 = unpack2(u.z), p3 = unpack2(u.w);
+            y[0] = p0.x; y[1] = p0.y; y[2] = p1.x; y[3] = p1.y; y[4] = p2.x; y[5] = p2.y; y[6] = p3.x; y[7] = p3.y;
+        } else {
+            const float4 u0 = __ldg(reinterpret_cast<const float4 *>(b) + 2 * j), u1 = __ldg(reinterpret_cast<const float4 *>(b) + 2 * j + 1);
+            y[0] = u0.x; y[1] = u0.y; y[2] = u0.z; y[3] = u0.w; y[4] = u1.x; y[5] = u1.y; y[6] = u1.z; y[7] = u1.w;
+        }
+        const float2 x0 = unpack2(x.x), x1 = unpack2(x.y), x2 = unpack2(x.z), x3 = unpack2(x.w);
+        auto f = [](float p, float q) { return MUL ? p * q : p + q; };
+        ov[i] = make_uint4(pack2(f(x0.x, y[0]), f(x0.y, y[1])), pack2(f(x1.x, y[2]), f(x1.y, y[3])),
+                           pack2(f(x2.x, y[4]), f(x2.y, y[5])), pack2(f(x3.x, y[6]), f(x3.y, y[7])));
+    }
+}
+
 // one CTA per row: (x - mean) * rsqrt(var + eps), or x * rsqrt(mean x^2 + eps) (src/cuda/vla_cuda_bf16.cu:548-579)
 template <bool RMS>
 __global__ void __launch_bounds__(256) norm_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out,
-                                                   int64_t cols, float eps) {
+                                                   int64_t cols, float eps, bool vec) {
     __shared__ float red[2][8];
     const __nv_bfloat16 *xr = x + (size_t)blockIdx.x * cols;
     __nv_bfloat16 *orow = out + (size_t)blockIdx.x * cols;
     float s = 0.f, ss = 0.f;
-    for (int64_t c = threadIdx.x; c < cols; c += 256) {
-        const float v = __bfloat162float(xr[c]);
-        s += v;
-        ss += v * v;
+    if (vec) {  // cols % 8 == 0 and 16-byte aligned rows
+        const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+        for (int64_t c = threadIdx.x; c < (cols >> 3); c += 256) {
+            const uint4 u = __ldg(xv + c);
+            const float2 a = unpack2(u.x), b = unpack2(u.y), d = unpack2(u.z), e = unpack2(u.w);
+            s += ((a.x + a.y) + (b.x + b.y)) + ((d.x + d.y) + (e.x + e.y));
+            ss += ((a.x * a.x + a.y * a.y) + (b.x * b.x + b.y * b.y)) + ((d.x * d.x + d.y * d.y) + (e.x * e.x + e.y * e.y));
+        }
+    } else {
+        for (int64_t c = threadIdx.x; c < cols; c += 256) {
+            const float v = __bfloat162float(xr[c]);
+            s += v;
+            ss += v * v;
+        }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -93,7 +128,18 @@ __global__ void __launch_bounds__(256) norm_kernel(const __nv_bfloat16 *__restri
     }
     const float mean = RMS ? 0.0f : s / (float)cols;
     const float inv = rsqrtf(ss / (float)cols - mean * mean + eps);
-    for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = __float2bfloat16((__bfloat162float(xr[c]) - mean) * inv);
+    if (vec) {
+        const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+        uint4 *ov = reinterpret_cast<uint4 *>(orow);
+        for (int64_t c = threadIdx.x; c < (cols >> 3); c += 256) {
+            const uint4 u = __ldg(xv + c);
+            const float2 a = unpack2(u.x), b = unpack2(u.y), d = unpack2(u.z), e = unpack2(u.w);
+            ov[c] = make_uint4(pack2((a.x - mean) * inv, (a.y - mean) * inv), pack2((b.x - mean) * inv, (b.y - mean) * inv),
+                               pack2((d.x - mean) * inv, (d.y - mean) * inv), pack2((e.x - mean) * inv, (e.y - mean) * inv));
+        }
+    } else {
+        for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = __float2bfloat16((__bfloat162float(xr[c]) - mean) * inv);
+    }
 }
 
 static int stream_grid(int64_t work_items) {
@@ -137,6 +183,20 @@ int32_t vlab200_node_bin_bf16(int32_t op, const void *a_bf16, const void *b, int
     const int grid = vb::stream_grid(n);
     const __nv_bfloat16 *a = static_cast<const __nv_bfloat16 *>(a_bf16);
     __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(out_bf16);
+    if (n % 8 == 0 && nb % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(a_bf16) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0) {
+        const int vgrid = vb::stream_grid(n / 8);
+        const int64_t n8 = n / 8, nb8 = nb / 8;
+        if (b_is_f32) {
+            if (op) vb::bin_vec_kernel<true, float><<<vgrid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n8, nb8);
+            else vb::bin_vec_kernel<false, float><<<vgrid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n8, nb8);
+        } else {
+            if (op) vb::bin_vec_kernel<true, __nv_bfloat16><<<vgrid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n8, nb8);
+            else vb::bin_vec_kernel<false, __nv_bfloat16><<<vgrid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n8, nb8);
+        }
+        VB_CUDA(cudaGetLastError());
+        return VLAB200_OK;
+    }
     if (b_is_f32) {
         if (op) vb::bin_kernel<true, float><<<grid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n, nb);
         else vb::bin_kernel<false, float><<<grid, 256, 0, cs>>>(a, static_cast<const float *>(b), o, n, nb);
@@ -181,12 +241,13 @@ int32_t vlab200_node_norm_bf16(const void *x_bf16, void *out_bf16, int64_t rows,
     if (!x_bf16 || !out_bf16 || rows < 0 || cols <= 0 || rows > 2147483647) return VLAB200_ERR_ARG;
     if (rows == 0) return VLAB200_OK;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const bool vec = cols % 8 == 0 && ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0;
     if (rms)
         vb::norm_kernel<true><<<(int)rows, 256, 0, cs>>>(static_cast<const __nv_bfloat16 *>(x_bf16),
-                                                        static_cast<__nv_bfloat16 *>(out_bf16), cols, eps);
+                                                        static_cast<__nv_bfloat16 *>(out_bf16), cols, eps, vec);
     else
         vb::norm_kernel<false><<<(int)rows, 256, 0, cs>>>(static_cast<const __nv_bfloat16 *>(x_bf16),
-                                                         static_cast<__nv_bfloat16 *>(out_bf16), cols, eps);
+                                                         static_cast<__nv_bfloat16 *>(out_bf16), cols, eps, vec);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
