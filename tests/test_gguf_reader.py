@@ -81,3 +81,36 @@ def test_rejects_damaged_files(tmp_path):
     for name in ("magic.gguf", "short.gguf", "dir.gguf", "missing.gguf"):
         with pytest.raises(vb.VlaB200Error):
             vb.Gguf(tmp_path / name)
+
+
+def test_truncations_and_corrupt_directories_never_crash(tmp_path):
+    """Every read of the parser is bounds-checked: a file cut anywhere, or with bytes of its header / directory
+    overwritten, either opens (and then every listed tensor lies inside the file) or is refused."""
+    import vla_cpp_b200 as vb
+
+    path = tmp_path / "m.gguf"
+    _write(path)
+    data = path.read_bytes()
+    rng = np.random.default_rng(3)
+    cases = [data[:n] for n in list(range(0, 64, 7)) + [int(x) for x in rng.integers(64, len(data), 40)]]
+    for _ in range(60):  # corrupt a few bytes in the first 1.5 KB (header, metadata, tensor directory)
+        b = bytearray(data)
+        for pos in rng.integers(4, min(1536, len(data)), 3):
+            b[int(pos)] = int(rng.integers(0, 256))
+        cases.append(bytes(b))
+    opened = 0
+    for i, blob in enumerate(cases):
+        p = tmp_path / f"case{i}.gguf"
+        p.write_bytes(blob)
+        try:
+            g = vb.Gguf(p)
+        except vb.VlaB200Error:
+            continue
+        opened += 1
+        for name in g.names():
+            inf = g.info(name)
+            assert inf is not None
+            if inf[2]:
+                assert len(g.raw(name)) == inf[2]  # readable end to end: lies inside the mapping
+        g.close()
+    assert opened < len(cases)
