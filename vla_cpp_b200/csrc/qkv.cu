@@ -266,8 +266,10 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
     constexpr int STAGE_BYTES = QKV_A_BYTES + (PAIR ? QKV_B_BYTES / 2 : QKV_B_BYTES);
     constexpr int TILE_M = PAIR ? 2 * QKV_BM : QKV_BM;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
-    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    // Every CTA (pair) walks a contiguous range of tiles; column tiles vary fastest, so consecutive tiles mostly
+    // share their rows of x and the row statistics are computed once per row tile instead of once per tile.
+    const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     extern __shared__ uint8_t qkvf_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(qkvf_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
@@ -285,6 +287,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ksteps = (p.H + QKV_BK - 1) / QKV_BK;
     const int n_tiles = tiles_m * tiles_n;
+    const int t_begin = (int)((long long)n_tiles * unit / n_units), t_end = (int)((long long)n_tiles * (unit + 1) / n_units);
     const int half = p.hd >> 1;
     const WaitCtx wc{abort_flag, p.status};
 
@@ -333,7 +336,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
             tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile) {
                 const int m0 = (tile / tiles_n) * TILE_M + (int)rank * QKV_BM;
                 const int n0 = (tile % tiles_n) * QKV_BN + (int)rank * (QKV_BN / 2);
                 for (int kt = 0; kt < ksteps; ++kt) {
@@ -355,7 +358,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
             const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem + QKV_A_BYTES), 16, 1024);
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
                 const uint32_t buf = j & 1u;
                 ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
@@ -383,7 +386,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
             // odd CTA of a pair: tell the even CTA when this CTA's stage has landed
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile) {
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
@@ -399,31 +402,39 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
         const uint32_t sw = row & 7;
         uint32_t st = 0, ph = 0, j = 0;
         bool ok = true;
-        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+        int prev_mt = -1;
+        float row_sum = 0.0f;
+        for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
             const uint32_t buf = j & 1u;
+            const int mt = tile / tiles_n;
+            const bool fresh = mt != prev_mt;  // same rows of x as the previous tile: keep their sums
+            prev_mt = mt;
             float s0 = 0.0f, s1 = 0.0f;
             for (int kt = 0; kt < ksteps; ++kt) {
                 ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
-                const uint8_t *at = smem + st * STAGE_BYTES + row_base;
+                if (fresh) {
+                    const uint8_t *at = smem + st * STAGE_BYTES + row_base;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __bfloat1622float2(h[e]);
-                        s0 = fmaf(f.x, f.x, s0);
-                        s1 = fmaf(f.y, f.y, s1);
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h[e]);
+                            s0 = fmaf(f.x, f.x, s0);
+                            s1 = fmaf(f.y, f.y, s1);
+                        }
                     }
                 }
                 stage_release(&empty[st], s0 + s1, lane);
                 if (++st == (uint32_t)nst) { st = 0; ph ^= 1u; }
             }
             if (!ok) break;
+            if (fresh) row_sum = s0 + s1;
             ok = mbar_wait(&stats_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
             if (!ok) break;
-            stats[buf * 128 + row] = s0 + s1;
+            stats[buf * 128 + row] = row_sum;
             mbar_arrive(&stats_full[buf]);
         }
     } else {
@@ -437,7 +448,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
         const uint32_t my_sw = (uint32_t)((lane >> 1) & 3);
         uint32_t j = 0;
         bool ok = true;
-        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+        for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
             const uint32_t buf = j & 1u;
             const int m0 = (tile / tiles_n) * TILE_M + (int)rank * QKV_BM, n0 = (tile % tiles_n) * QKV_BN;
             const int m = m0 + row;
