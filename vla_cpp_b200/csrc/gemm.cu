@@ -65,8 +65,10 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
     constexpr int G_STAGES = Cfg::STAGES, G_STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int TILE_M = PAIR ? 2 * G_BM : G_BM;  // rows of one work unit
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
-    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    // Every CTA (pair) walks a contiguous range of tiles; column tiles vary fastest, so consecutive tiles mostly
+    // share their rows of A and the row statistics are computed once per row tile instead of once per tile.
+    const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     extern __shared__ uint8_t g_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(g_smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
@@ -81,6 +83,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ksteps = (p.K + G_BK - 1) / G_BK;
     const int n_tiles = tiles_m * tiles_n;
+    const int t_begin = (int)((long long)n_tiles * unit / n_units), t_end = (int)((long long)n_tiles * (unit + 1) / n_units);
     const WaitCtx wc{abort_flag, p.status};
     const uint32_t empty_count = p.use_rms ? 5u : 1u;
 
@@ -123,7 +126,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
             tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile) {
                 const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM;
                 const int n0 = (tile % tiles_n) * G_BN + (int)rank * Cfg::B_ROWS * (PAIR ? 1 : 0);
                 for (int kt = 0; kt < ksteps; ++kt) {
@@ -145,7 +148,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
             const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem + G_A_BYTES), 16, 1024);
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
                 const uint32_t buf = j & 1u;
                 ok = mbar_wait(&accum_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
@@ -173,7 +176,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
             // odd CTA of a pair: tell the even CTA when this CTA's stage has landed
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+            for (int tile = t_begin; ok && tile < t_end; ++tile) {
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
@@ -189,31 +192,39 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
             const uint32_t sw = row & 7;
             uint32_t st = 0, ph = 0, j = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+            int prev_mt = -1;
+            float row_sum = 0.0f;
+            for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
                 const uint32_t buf = j & 1u;
+                const int mt = tile / tiles_n;
+                const bool fresh = mt != prev_mt;  // same rows of A as the previous tile: keep their sums
+                prev_mt = mt;
                 float s0 = 0.0f, s1 = 0.0f;
                 for (int kt = 0; kt < ksteps; ++kt) {
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
-                    const uint8_t *at = smem + st * G_STAGE_BYTES + row_base;
+                    if (fresh) {
+                        const uint8_t *at = smem + st * G_STAGE_BYTES + row_base;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
-                        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
+                        for (int c = 0; c < 8; ++c) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(at + ((c ^ sw) << 4));
+                            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 f = __bfloat1622float2(h2[e]);
-                            s0 = fmaf(f.x, f.x, s0);
-                            s1 = fmaf(f.y, f.y, s1);
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __bfloat1622float2(h2[e]);
+                                s0 = fmaf(f.x, f.x, s0);
+                                s1 = fmaf(f.y, f.y, s1);
+                            }
                         }
                     }
                     stage_release(&empty[st], s0 + s1, lane);
                     if (++st == G_STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
+                if (fresh) row_sum = s0 + s1;
                 ok = mbar_wait(&stats_empty[buf], ((j >> 1) & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                 if (!ok) break;
-                stats[buf * 128 + row] = s0 + s1;
+                stats[buf * 128 + row] = row_sum;
                 mbar_arrive(&stats_full[buf]);
             }
         }
@@ -224,7 +235,7 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
         const int row = qtr * 32 + lane;
         uint32_t j = 0;
         bool ok = true;
-        for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step, ++j) {
+        for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
             const uint32_t buf = j & 1u;
             const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM, n0 = (tile % tiles_n) * G_BN;
             const int m = m0 + row;
