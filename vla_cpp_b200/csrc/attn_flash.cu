@@ -689,7 +689,9 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     ok = mbar_wait(&pv_done[jp % FP_NS], (jp / FP_NS) & 1u, wc, DEV_TIMEOUT_ACCUM);
                     if (!ok) break;
                     tc_fence_after();
-                    for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                    // not unrolled: unrolling this loop pushed the kernel over its 168-register cap (spills)
+#pragma unroll 1
+            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
                         uint32_t ov[32];
                         tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
                         tmem_ld_wait();
