@@ -107,6 +107,26 @@ def oracle_chunk(orc, rng, n_chunks):
 PI0 = dict(model=0, n_layers=18, H=1024, n_q=8, n_kv=1, head_dim=256, inter=4096, chunk=50, action_dim=32,
            state_dim=32, steps=10, self_every=1, rms_eps=1e-6, rope_base=10000.0, min_period=4e-3, max_period=4.0)
 PI0_P = 816
+# SmolVLA-shaped action expert (BASELINE configs[0]): hidden 720, 16 layers alternating self- / cross-attention,
+# 15 q / 5 kv heads of 64, MLP 2048, prefix 177, the state token lives in the prefix (suffix = 50 action tokens)
+SMOLVLA = dict(model=1, n_layers=16, H=720, n_q=15, n_kv=5, head_dim=64, inter=2048, chunk=50, action_dim=32,
+               state_dim=32, steps=10, self_every=2, rms_eps=1e-5, rope_base=10000.0, min_period=4e-3, max_period=4.0)
+SMOLVLA_P = 177
+POLICIES = {"pi0": (PI0, PI0_P), "smolvla": (SMOLVLA, SMOLVLA_P)}
+
+
+def policy_flops_per_chunk(c, P):
+    """Dense FLOPs of a policy's denoise loop per observation: expert GEMMs + attention (algorithmic)."""
+    S = c["chunk"] + (1 if c["model"] == 0 else 0)
+    qf, kvf, H, I = c["n_q"] * c["head_dim"], c["n_kv"] * c["head_dim"], c["H"], c["inter"]
+    total = 0
+    for l in range(c["n_layers"]):
+        cross = c["model"] == 1 and c["self_every"] > 1 and l % c["self_every"] != 0
+        proj = 2 * S * H * qf if cross else 2 * S * H * (qf + 2 * kvf)  # cross layers: K / V projected once per observation
+        keys = P if cross else P + S
+        total += proj + 2 * S * qf * H + 3 * 2 * S * H * I + 4 * S * c["n_q"] * keys * c["head_dim"]
+    per_step = total + 2 * 2 * c["chunk"] * H * H
+    return per_step * c["steps"]
 
 
 def pi0_flops_per_chunk():
@@ -118,15 +138,17 @@ def pi0_flops_per_chunk():
     return per_step * c["steps"]
 
 
-def build_pi0_engine(torch, vb, dev, n_obs, seed):
-    c = PI0
+def build_pi0_engine(torch, vb, dev, n_obs, seed, policy="pi0"):
+    c, PI0_P = POLICIES[policy]
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
     H, I, qf, kvf, A, sd = c["H"], c["inter"], c["n_q"] * c["head_dim"], c["n_kv"] * c["head_dim"], 32, 32
     bw = lambda *s: (torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16)
     fv = lambda n: torch.zeros(n, device=dev)
     L = c["n_layers"]
-    w = dict(wq=[bw(qf, H) for _ in range(L)], wk=[bw(kvf, H) for _ in range(L)], wv=[bw(kvf, H) for _ in range(L)],
+    cross = [c["model"] == 1 and c["self_every"] > 1 and l % c["self_every"] != 0 for l in range(L)]
+    w = dict(wq=[bw(qf, H) for _ in range(L)], wk=[bw(kvf, kvf if cross[l] else H) for l in range(L)],
+             wv=[bw(kvf, kvf if cross[l] else H) for l in range(L)],
              wo=[bw(H, qf) for _ in range(L)], wgate=[bw(I, H) for _ in range(L)], wup=[bw(I, H) for _ in range(L)],
              wdown=[bw(H, I) for _ in range(L)], ln_in=[torch.ones(H, device=dev) for _ in range(L)],
              ln_post=[torch.ones(H, device=dev) for _ in range(L)], w_sp=bw(H, sd), b_sp=fv(H), w_ain=bw(H, A),
@@ -138,17 +160,17 @@ def build_pi0_engine(torch, vb, dev, n_obs, seed):
     for l in range(L):  # the prefix KV is written once per observation
         for o in range(0, n_obs, blk):
             n = min(blk, n_obs - o)
-            eng.set_prefix(l, torch.randn((n, PI0_P, 1, 256), device=dev, generator=g),
-                           torch.randn((n, PI0_P, 1, 256), device=dev, generator=g), obs0=o)
+            eng.set_prefix(l, torch.randn((n, PI0_P, c["n_kv"], c["head_dim"]), device=dev, generator=g),
+                           torch.randn((n, PI0_P, c["n_kv"], c["head_dim"]), device=dev, generator=g), obs0=o)
     x0 = torch.randn((n_obs, 50, 32), device=dev, generator=g)
     state = torch.randn((n_obs, 32), device=dev, generator=g)
     torch.cuda.synchronize()
     return eng, x0, state
 
 
-def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_graph=False):
+def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_graph=False, policy="pi0"):
     """Times `steps` whole denoise loops over n_obs observations: device-resident and through host buffers."""
-    eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, seed)
+    eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, seed, policy)
     sync = barrier or torch.cuda.synchronize
     for _ in range(warmup):
         eng.denoise(x0, state)
@@ -363,7 +385,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "ternary", "bitvla_lm"],
+    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "smolvla", "ternary", "bitvla_lm"],
                     help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
                          "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
     ap.add_argument("--gemm-tiling", type=int, default=0,
@@ -418,14 +440,16 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload == "pi0":
+    if args.workload in ("pi0", "smolvla"):
         from vla_cpp_b200.shard import shard_range
 
+        pol_cfg, pol_P = POLICIES[args.workload]
         n_obs = args.pi0_obs or shard_range(1024, world, rank)[1]
         n_global = args.pi0_obs * world if args.pi0_obs else 1024
         sampler = ClockSampler(local_rank)
         sampler.start()
-        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier, allow_graph=world == 1)
+        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier, allow_graph=world == 1,
+                        policy=args.workload)
         clocks = sampler.stop()
         stats = torch.tensor([r["total_ms"], r["p50_ms"], r["e2e_ms"]], device=dev, dtype=torch.float64)
         if world > 1:
@@ -435,19 +459,24 @@ def main():
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
                 os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
             tf_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
-            tf = pi0_flops_per_chunk() * n_obs * args.steps / (total_ms * 1e-3) / 1e12  # per GPU (rank 0's share)
+            tf = policy_flops_per_chunk(pol_cfg, pol_P) * n_obs * args.steps / (total_ms * 1e-3) / 1e12  # per GPU (rank 0's share)
             line = {
                 "metric": "action chunks/s (denoise loop)", "value": n_global * args.steps / (total_ms * 1e-3),
                 "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
                 "scaling": "weak" if args.pi0_obs else "strong", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic",
-                "config": {"workload": "pi0: whole pi0-shaped denoise loop (BASELINE configs[2]/[4]): 18 layers, "
-                                       "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32, 10 steps",
+                "config": {"workload": ("pi0: whole pi0-shaped denoise loop (BASELINE configs[2]/[4]): 18 layers, "
+                                        "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32, 10 steps")
+                           if args.workload == "pi0" else
+                           ("smolvla: whole SmolVLA-shaped denoise loop (the action expert of BASELINE configs[0]): 16 "
+                            "layers alternating self / cross attention, hidden 720, 15q/5kv, hd 64, MLP 2048, prefix 177, "
+                            "chunk 50x32, 10 steps"),
                            "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
                            "l2": "inputs larger than L2 (KV pages + expert weights > 126 MB per GPU)"},
                 # per Euler step: 2 embedding kernels + 2 GEMMs, 18 layers x 5 kernels (6 on the few-row path), head + Euler
-                "clocks": clocks, "gpu_launches": (10 * (4 + 18 * (6 if n_obs * 51 <= 256 else 5) + 2) + 3) * args.steps,
+                "clocks": clocks,
+                "gpu_launches": (10 * (4 + pol_cfg["n_layers"] * (6 if n_obs * 51 <= 256 else 5) + 2) + 3) * args.steps,
                 "roofline": {"kernel": "whole loop (dense_gemm_kernel, qkv_rope_tma_kernel, attn_flash_kernel)",
                              "bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
                              "frac": tf / tf_peak, "peak_kind": "of measured (sustained)", "traffic": None},
