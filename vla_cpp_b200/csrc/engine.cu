@@ -54,30 +54,41 @@ __global__ void time_vector_kernel(const __nv_bfloat16 *__restrict__ w_at1, cons
 }
 
 // a[row][o] = bf16(b_ain[o] + sum_k W_ain[o][k] x[row][k]) for the n_rows = n_obs*chunk action
-// tokens.  One thread per output: the token's x row (A <= 64 floats) sits in shared memory, the
-// weight row is read with 16-byte loads.
+// tokens.  One CTA takes AIN_ROWS tokens (their x rows, A <= 64 floats each, sit in shared memory) and one
+// thread one output column: its weight row is read once (16-byte loads) and kept in registers for all the
+// tokens of the CTA, so W_ain crosses L2 -> SM once per AIN_ROWS tokens instead of once per token.
+constexpr int AIN_ROWS = 16;
 __global__ void __launch_bounds__(256) action_in_kernel(const float *__restrict__ x,
                                                         const __nv_bfloat16 *__restrict__ w_ain,
                                                         const float *__restrict__ b_ain, __nv_bfloat16 *__restrict__ a,
-                                                        int H, int A) {
-    __shared__ float sx[64];
-    const int row = blockIdx.x;
-    if (threadIdx.x < A) sx[threadIdx.x] = x[(size_t)row * A + threadIdx.x];
+                                                        int n_rows, int H, int A) {
+    __shared__ float sx[AIN_ROWS][64];
+    const int row0 = blockIdx.x * AIN_ROWS;
+    const int rows = min(AIN_ROWS, n_rows - row0);
+    for (int i = threadIdx.x; i < rows * A; i += blockDim.x) sx[i / A][i % A] = x[(size_t)row0 * A + i];
     __syncthreads();
-    for (int o = blockIdx.y * blockDim.x + threadIdx.x; o < H; o += gridDim.y * blockDim.x) {
-        const __nv_bfloat16 *wr = w_ain + (size_t)o * A;
-        float acc = b_ain ? b_ain[o] : 0.0f;
-        for (int k = 0; k < A; k += 8) {  // A % 8 == 0
-            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(wr + k));
-            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
+    const int o = blockIdx.y * blockDim.x + threadIdx.x;
+    if (o >= H) return;
+    uint4 wv[8];  // A % 8 == 0, A <= 64
+    const uint4 *wr = reinterpret_cast<const uint4 *>(w_ain + (size_t)o * A);
+#pragma unroll
+    for (int k8 = 0; k8 < 8; ++k8)
+        if (k8 * 8 < A) wv[k8] = __ldg(wr + k8);
+    const float bias = b_ain ? b_ain[o] : 0.0f;
+    for (int r = 0; r < rows; ++r) {
+        float acc = bias;
+#pragma unroll
+        for (int k8 = 0; k8 < 8; ++k8) {
+            if (k8 * 8 >= A) break;
+            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&wv[k8]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float2 f = __bfloat1622float2(h2[e]);
-                acc = fmaf(f.x, sx[k + 2 * e], acc);
-                acc = fmaf(f.y, sx[k + 2 * e + 1], acc);
+                acc = fmaf(f.x, sx[r][k8 * 8 + 2 * e], acc);
+                acc = fmaf(f.y, sx[r][k8 * 8 + 2 * e + 1], acc);
             }
         }
-        a[(size_t)row * H + o] = __float2bfloat16(acc);
+        a[(size_t)(row0 + r) * H + o] = __float2bfloat16(acc);
     }
 }
 
@@ -325,8 +336,8 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     vlab200_kv_store st = vb::engine_store(e, e->max_obs);
     const float dt = -1.0f / (float)c.steps;
     for (int step = 0; step < c.steps; ++step) {
-        vb::action_in_kernel<<<dim3(Mc, (H + 1023) / 1024), 256, 0, cs>>>(e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(),
-                                                                          e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), H, A);
+        vb::action_in_kernel<<<dim3((Mc + vb::AIN_ROWS - 1) / vb::AIN_ROWS, (H + 255) / 256), 256, 0, cs>>>(
+            e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), Mc, H, A);
         if (c.model == 0)
             vb::state_token_kernel<<<n_obs, 256, 0, cs>>>(state, e->w_sp.as<__nv_bfloat16>(), e->b_sp.as<float>(),
                                                           e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, c.state_dim, S);
