@@ -439,7 +439,7 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
     const int tn256 = (p.N + 255) / 256, tn128 = (p.N + 127) / 128, pairs = n_sm / 2;
     auto waves = [](int tiles, int units) { return (tiles + units - 1) / units; };
     const float cost256 = (float)waves(tiles_m * tn256, n_sm);
-    const float cost128 = p.N > 128 ? 0.55f * waves(tiles_m * tn128, n_sm) : 1e30f;
+    const float cost128 = p.N > 128 ? 0.60f * waves(tiles_m * tn128, n_sm) : 1e30f;
     const int tn64 = (p.N + 63) / 64;
     const float cost64 = p.N > 64 ? 0.33f * waves(tiles_m * tn64, n_sm) : 1e30f;  // few rows: as many CTAs as possible stream W
     const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
