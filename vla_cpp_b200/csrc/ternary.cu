@@ -121,8 +121,11 @@ __device__ __forceinline__ float ternary_scale_out(int acc, float s, float ws) {
 // grid = N/16 (one 16-row weight block per CTA), 128 threads; warp w takes the 128-k
 // chunks w, w+4, ...  Lane t reads the 16 bytes (4 slots) at offset 16*t of a 512-byte
 // chunk: rows 8*((t%8)/4) + 4*(t%2) + {0..3}, k offset 32*(t/8) + 16*((t%4)/2).
+// Eight warps split the K range of a 16-row weight block: with one CTA per SM at N = 2560 the loads in flight per
+// SM, not the bandwidth, set the time.
+constexpr int GEMV_WARPS = 8, GEMV_THREADS = GEMV_WARPS * 32;
 template <int MT>
-__global__ void __launch_bounds__(128) ternary_gemv_kernel(const int8_t *__restrict__ A,
+__global__ void __launch_bounds__(GEMV_THREADS) ternary_gemv_kernel(const int8_t *__restrict__ A,
                                                            const uint8_t *__restrict__ Wp,
                                                            __nv_bfloat16 *__restrict__ out,
                                                            int32_t *__restrict__ acc_out,
@@ -131,11 +134,11 @@ __global__ void __launch_bounds__(128) ternary_gemv_kernel(const int8_t *__restr
                                                            int K, int m0) {
     extern __shared__ __align__(16) uint8_t gemv_smem[];
     int8_t *As = reinterpret_cast<int8_t *>(gemv_smem);              // [MT][K]
-    int *red = reinterpret_cast<int *>(gemv_smem + (size_t)MT * K);  // [4 warps][MT][16 rows]
+    int *red = reinterpret_cast<int *>(gemv_smem + (size_t)MT * K);  // [GEMV_WARPS][MT][16 rows]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nb = blockIdx.x;
     const int rows_here = min(MT, M - m0);
-    for (int i = tid; i < MT * (K >> 4); i += 128) {
+    for (int i = tid; i < MT * (K >> 4); i += GEMV_THREADS) {
         const int mm = i / (K >> 4), kk = i % (K >> 4);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (mm < rows_here) v = __ldg(reinterpret_cast<const uint4 *>(A + (size_t)(m0 + mm) * K) + kk);
@@ -153,16 +156,16 @@ __global__ void __launch_bounds__(128) ternary_gemv_kernel(const int8_t *__restr
     const uint4 *wbase = reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K) + lane;
     const int koff = 32 * (lane >> 3) + 16 * ((lane & 3) >> 1);
     constexpr int UNROLL = 4;
-    for (int c0 = warp; c0 < nchunks; c0 += 4 * UNROLL) {
+    for (int c0 = warp; c0 < nchunks; c0 += GEMV_WARPS * UNROLL) {
         uint4 wv[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int c = c0 + 4 * u;
+            const int c = c0 + GEMV_WARPS * u;
             wv[u] = (c < nchunks) ? __ldg(wbase + (size_t)c * 32) : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int c = c0 + 4 * u;
+            const int c = c0 + GEMV_WARPS * u;
             if (c >= nchunks) break;
             const uint32_t words[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
             uint32_t d[4][4];
@@ -198,11 +201,12 @@ __global__ void __launch_bounds__(128) ternary_gemv_kernel(const int8_t *__restr
             for (int i = 0; i < 4; ++i) red[(warp * MT + mm) * 16 + r0 + i] = acc[mm][i];
     }
     __syncthreads();
-    for (int i = tid; i < MT * 16; i += 128) {
+    for (int i = tid; i < MT * 16; i += GEMV_THREADS) {
         const int mm = i >> 4, r = i & 15;
         if (mm >= rows_here) continue;
-        const int v = red[(0 * MT + mm) * 16 + r] + red[(1 * MT + mm) * 16 + r] + red[(2 * MT + mm) * 16 + r] +
-                      red[(3 * MT + mm) * 16 + r];
+        int v = 0;
+#pragma unroll
+        for (int w8 = 0; w8 < GEMV_WARPS; ++w8) v += red[(w8 * MT + mm) * 16 + r];
         const int n = nb * 16 + r;
         const int m = m0 + mm;
         if (acc_out) acc_out[(size_t)m * N + n] = v;
@@ -768,10 +772,10 @@ static int check_gemm_args(const void *A, const void *W, const void *out, const 
 template <int MT>
 static int launch_gemv(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, int32_t *acc, const float *s,
                        const float *ws, int ws_num, int M, int N, int K, int m0, cudaStream_t st) {
-    const size_t smem = (size_t)MT * K + 4 * MT * 16 * sizeof(int);
+    const size_t smem = (size_t)MT * K + GEMV_WARPS * MT * 16 * sizeof(int);
     if (smem > 48 * 1024)
         VB_CUDA(cudaFuncSetAttribute(ternary_gemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    ternary_gemv_kernel<MT><<<N / 16, 128, smem, st>>>(A, W, out, acc, s, ws, ws_num, M, N, K, m0);
+    ternary_gemv_kernel<MT><<<N / 16, GEMV_THREADS, smem, st>>>(A, W, out, acc, s, ws, ws_num, M, N, K, m0);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
 }
