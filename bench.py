@@ -56,23 +56,36 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t_up = time.monotonic()  # nvidia-smi takes a moment to start: wait for its first line
+            while not self.rows and time.monotonic() - t_up < 3.0:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
+
+    def mark_begin(self):
+        """Start of the timed region (the sampler itself is started before the warm-up so that nvidia-smi is up)."""
+        self.t0 = time.monotonic()
 
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t1 = time.monotonic()
         self.proc.terminate()
         self.thread.join(timeout=2)
+        t0 = getattr(self, "t0", 0.0)
+        inside = [r for t, r in self.rows if t0 <= t <= t1 + 0.05]
+        window = "timed region"
+        if not inside:  # region shorter than the sampling interval: the warm-up runs the same load
+            inside, window = [r for _, r in self.rows[-3:]], "warm-up (timed region shorter than the sampling interval)"
         sm, mx, reasons = [], None, set()
-        for r in self.rows:
+        for r in inside:
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
@@ -82,7 +95,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 def oracle_chunk(orc, rng, n_chunks):
@@ -168,13 +181,16 @@ def build_pi0_engine(torch, vb, dev, n_obs, seed, policy="pi0"):
     return eng, x0, state
 
 
-def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_graph=False, policy="pi0"):
+def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_graph=False, policy="pi0",
+                on_begin=None):
     """Times `steps` whole denoise loops over n_obs observations: device-resident and through host buffers."""
     eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, seed, policy)
     sync = barrier or torch.cuda.synchronize
     for _ in range(warmup):
         eng.denoise(x0, state)
     sync()
+    if on_begin:
+        on_begin()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     ev[0].record()
     for i in range(steps):
@@ -476,7 +492,7 @@ def main():
         sampler = ClockSampler(local_rank)
         sampler.start()
         r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier, allow_graph=world == 1,
-                        policy=args.workload)
+                        policy=args.workload, on_begin=sampler.mark_begin)
         clocks = sampler.stop()
         stats = torch.tensor([r["total_ms"], r["p50_ms"], r["e2e_ms"]], device=dev, dtype=torch.float64)
         if world > 1:
@@ -545,11 +561,12 @@ def main():
     torch.cuda.synchronize()
 
     # ---- device-resident throughput -----------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         op.run(x)
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark_begin()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     ev[0].record()
     for i in range(args.steps):
