@@ -218,10 +218,11 @@ VLAB200_API int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, con
                                            float *x_out, int32_t pos_base, const int32_t *pad_ranges,
                                            void *stream);
 
-/* Same with state, x0 and x_out in (pinned) host memory: the copies are enqueued on `stream`. */
+/* Same with state, x0, x_out and the optional pad_ranges ([n_obs][2]) in (pinned) host memory: the copies
+ * are enqueued on `stream`. */
 VLAB200_API int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const float *state_host,
                                                 const float *x0_host, float *x_out_host, int32_t pos_base,
-                                                void *stream);
+                                                const int32_t *pad_ranges_host, void *stream);
 
 /* Tiling of the bf16 GEMMs (the fused QKV projection, and inside the engine the O-projection, MLP,
  * embedding MLPs and action head):
@@ -402,6 +403,22 @@ VLAB200_API void bitlinear_int8xint2(int8_t *input0, int8_t *input1, void *outpu
 VLAB200_API void bitlinear_int8xint2_m(int8_t *input0, int8_t *input1, void *output0, float *s, float *ws, int M,
                                        int N, int K, void *stream);
 VLAB200_API void bitvla_act_quant_cuda(const void *in, int8_t *out, float *scales, int M, int K, void *stream);
+
+/* The reference's LM context API by its own names and signatures
+ * (src/kernels/bitvla/bitvla_lm_cuda.h:247-286; callers src/models/bitvla.cpp:760-821,1326-1334): init
+ * allocates the workspace for one sequence of up to max_seq tokens (NULL on failure), set_layer /
+ * set_output_norm bind caller-owned device pointers, forward returns 0 or -1 and writes
+ * d_out = output_norm(layers(d_in)) for seq x hidden bf16 rows.  Failures are reported on stderr as the
+ * reference does.  They forward to vlab200_bitvla_lm_* with max_batch = n_seq = 1. */
+typedef struct bitvla_lm_cuda_ctx bitvla_lm_cuda_ctx;
+typedef vlab200_bitvla_lm_layer bitvla_lm_layer_cuda;
+VLAB200_API bitvla_lm_cuda_ctx *bitvla_lm_cuda_init(int hidden, int n_q, int n_kv, int head_dim, int ffn,
+                                                    int n_layers, float rope_base, float rms_eps, int max_seq);
+VLAB200_API void bitvla_lm_cuda_free(bitvla_lm_cuda_ctx *ctx);
+VLAB200_API void bitvla_lm_cuda_set_layer(bitvla_lm_cuda_ctx *ctx, int L, const bitvla_lm_layer_cuda *layer);
+VLAB200_API void bitvla_lm_cuda_set_output_norm(bitvla_lm_cuda_ctx *ctx, const void *w);
+VLAB200_API int bitvla_lm_cuda_forward(bitvla_lm_cuda_ctx *ctx, const void *d_in, void *d_out, int seq,
+                                       void *stream);
 
 #ifdef __cplusplus
 }

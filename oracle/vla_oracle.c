@@ -229,15 +229,19 @@ ORC_API void orc_ternary_epilogue(const int32_t *acc, const float *s, const floa
 
 /* y[t][o] = sum_i W[o][i] x[t][i] (+ b[o]).  src/layers/linear.h:24-27. */
 ORC_API void orc_linear(const float *x, const float *W, const float *b, int T, int in, int out, float *y) {
-#pragma omp parallel for schedule(static) collapse(2)
-    for (int t = 0; t < T; ++t)
-        for (int o = 0; o < out; ++o) {
+    /* one weight row stays in cache for all T tokens; the dot product is a SIMD reduction (float32,
+     * summation order differs from a left-to-right loop by rounding only) */
+#pragma omp parallel for schedule(static)
+    for (int o = 0; o < out; ++o) {
+        const float *wr = W + (int64_t)o * in;
+        for (int t = 0; t < T; ++t) {
             const float *xr = x + (int64_t)t * in;
-            const float *wr = W + (int64_t)o * in;
             float acc = 0.0f;
+#pragma omp simd reduction(+ : acc)
             for (int i = 0; i < in; ++i) acc += wr[i] * xr[i];
             y[(int64_t)t * out + o] = acc + (b ? b[o] : 0.0f);
         }
+    }
 }
 
 /* y = x * rsqrt(mean(x^2) + eps) * w.  src/cuda/vla_cuda_bf16.cu:549-579,

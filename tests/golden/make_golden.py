@@ -69,7 +69,9 @@ def time_emb():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of the vla.cpp source tree>")
+    ref = sys.argv[1]
     ladder(ref)
     time_emb()
     print("golden fixtures written to", HERE)

@@ -11,9 +11,12 @@ from tests.gpu_util import bits_to_bf16_tensor, rel_l2, require_cuda, to_dev
 pytestmark = pytest.mark.gpu
 
 
-def make_policy(oracle, rng, model, L, H, n_q, n_kv, hd, inter, P, chunk, A, sd, T, self_every=1, wscale=None):
+def make_policy(oracle, rng, model, L, H, n_q, n_kv, hd, inter, P, chunk, A, sd, T, self_every=1, wscale=None,
+                sigma=None):
+    """sigma: every matrix drawn N(0, sigma) (the benchmark configurations say N(0, 0.02)); otherwise each matrix
+    gets 1/sqrt(fan_in) so that activations keep unit scale at any width."""
     qf, kvf = n_q * hd, n_kv * hd
-    r = lambda *s, sc=1.0: oracle.bf16_round((rng.standard_normal(s) * sc).astype(np.float32))
+    r = lambda *s, sc=1.0: oracle.bf16_round((rng.standard_normal(s) * (sigma or sc)).astype(np.float32))
     f = lambda *s, sc=1.0: (rng.standard_normal(s) * sc).astype(np.float32)
     ws = wscale or (1.0 / np.sqrt(H))
     per = {k: [] for k in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "ln_in", "ln_post")}
@@ -58,7 +61,9 @@ def oracle_model(oracle, cfg, per, glob, wqkv, P, pos_base, pad):
     return oracle.DenoiseModel(ocfg, ow)
 
 
-def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, tiling=0, **kw):
+def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, tiling=0, check_obs=None, **kw):
+    """check_obs: the observations compared with the oracle (default: all; the full-depth cases check a few,
+    the oracle needs seconds per observation there)."""
     torch = require_cuda()
     import vla_cpp_b200 as vb
 
@@ -85,7 +90,7 @@ def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, tiling=0, **kw):
     assert np.isfinite(out).all()
     om = oracle_model(oracle, cfg, per, glob, wqkv, P, P if pos_base < 0 else pos_base, pad or (0, 0))
     worst, worst_d = 0.0, 0.0
-    for b in range(n_obs):
+    for b in (range(n_obs) if check_obs is None else check_obs):
         ref = om.denoise([kp[l, b] for l in range(L)], [vp[l, b] for l in range(L)], state[b], x0[b])
         worst = max(worst, rel_l2(out[b], ref))
         worst_d = max(worst_d, rel_l2(out[b] - x0[b], ref - x0[b]))
@@ -93,10 +98,10 @@ def run_case(oracle, seed, n_obs, P, pos_base=-1, pad=None, tiling=0, **kw):
     # host-buffer entry point gives the same result
     x0h, sth = torch.from_numpy(x0).pin_memory(), torch.from_numpy(state).pin_memory()
     outh = torch.empty_like(x0h).pin_memory()
-    eng.denoise_host(x0h, sth, outh, pos_base=pos_base) if pad is None else None
+    padh = None if pad is None else torch.from_numpy(np.tile(np.asarray(pad, np.int32), (n_obs, 1))).pin_memory()
+    eng.denoise_host(x0h, sth, outh, pos_base=pos_base, pad_ranges_host=padh)
     torch.cuda.synchronize()
-    if pad is None:
-        assert np.array_equal(outh.numpy(), out)
+    assert np.array_equal(outh.numpy(), out)
     vb.set_gemm_tiling(0)
     return worst, worst_d
 
@@ -159,3 +164,28 @@ def test_gemm_tilings_are_bit_identical(oracle):
     vb.set_gemm_tiling(0)
     for o in outs[1:]:
         assert np.array_equal(o, outs[0])
+
+
+# ---- the benchmark configurations at their full depth: every layer, all ten Euler steps ----------------------
+PI0_FULL = dict(model=0, L=18, H=1024, n_q=8, n_kv=1, hd=256, inter=4096, chunk=50, A=32, sd=32, T=10)
+SMOLVLA_FULL = dict(model=1, L=16, H=720, n_q=15, n_kv=5, hd=64, inter=2048, chunk=50, A=32, sd=32, T=10,
+                    self_every=2)
+
+
+@pytest.mark.parametrize("n_obs,check,sigma", [(1, [0], 0.02), (6, [0, 5], 0.02), (6, [3], None)])
+def test_pi0_full_depth_18_layers_10_steps(oracle, n_obs, check, sigma):
+    """pi0-shaped expert exactly as benchmarked: 18 layers x 10 steps, prefix 816, 180 layer-steps of bf16
+    activations against the float32 oracle.  One observation takes the few-row path, six the fused path."""
+    w, d = run_case(oracle, 21 + n_obs, n_obs=n_obs, P=816, check_obs=check, sigma=sigma, **PI0_FULL)
+    print(f"pi0 full depth n_obs={n_obs} sigma={sigma}: rel_l2={w:.3e} displacement rel_l2={d:.3e}")
+    assert w < 1e-2 and d < 3e-2, (w, d)
+
+
+@pytest.mark.parametrize("n_obs,check,sigma", [(1, [0], 0.02), (6, [0, 5], 0.02), (6, [2], None)])
+def test_smolvla_full_depth_16_layers_10_steps(oracle, n_obs, check, sigma):
+    """SmolVLA-shaped expert as benchmarked: 16 layers alternating self / cross attention x 10 steps, prefix 177
+    with padded language slots and the rebased suffix positions."""
+    w, d = run_case(oracle, 41 + n_obs, n_obs=n_obs, P=177, pos_base=170, pad=(160, 176), check_obs=check, sigma=sigma,
+                    **SMOLVLA_FULL)
+    print(f"smolvla full depth n_obs={n_obs} sigma={sigma}: rel_l2={w:.3e} displacement rel_l2={d:.3e}")
+    assert w < 1e-2 and d < 3e-2, (w, d)

@@ -223,3 +223,35 @@ def test_drop_in_symbols_compute(oracle):
     rq, rs = oracle.act_quant(x)
     ref = oracle.ternary_epilogue(oracle.gemm_i8_i32(rq, tern), rs, ws)
     assert_bf16_close(bf16_bits(out), ref)
+
+
+@pytest.mark.parametrize("shape", LM_SHAPES)
+def test_whole_matrix_at_4800_rows_against_oracle_and_reference(oracle, shape):
+    """M = 4800 (16 sequences of 300 tokens), every element: all int32 accumulators against the CPU
+    integer GEMM, all bf16 outputs against the oracle's epilogue and, where the reference's CUDA kernels
+    were built, against bitlinear_int8xint2_m itself (<= 1 bf16 ulp: it divides with --use_fast_math)."""
+    torch = require_cuda()
+    from vla_cpp_b200 import api
+
+    n, k, ws_num = shape
+    m = 4800
+    rng = np.random.default_rng(4800 + n + k)
+    tern = rng.integers(-1, 2, (n, k)).astype(np.int8)
+    packed = oracle.pack_ladder_int2(tern)
+    a, _, s, ws = make_case(rng, m, n, k, ws_num)
+    ad, pd, sd, wd = to_dev(a), to_dev(packed), to_dev(s), to_dev(ws)
+    acc = torch.full((m, n), -7, dtype=torch.int32, device="cuda")
+    mine = api.ternary_linear(ad, pd, sd, wd, n, acc_out=acc)
+    assert api.device_status() == 0
+    ref_acc = oracle.gemm_i8_i32(a, tern)
+    assert np.array_equal(acc.cpu().numpy(), ref_acc)
+    assert_bf16_close(bf16_bits(mine), oracle.ternary_epilogue(ref_acc, s, ws))
+    ref = reference_bitnet_lib()
+    if ref is not None:
+        theirs = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        ref.bitlinear_int8xint2_m(C.c_void_p(ad.data_ptr()), C.c_void_p(pd.data_ptr()), C.c_void_p(theirs.data_ptr()),
+                                  C.c_void_p(sd.data_ptr()), C.c_void_p(wd.data_ptr()), m, n, k, C.c_void_p(0))
+        torch.cuda.synchronize()
+        diff = np.abs(bf16_bits(mine).astype(np.int32) - bf16_bits(theirs).astype(np.int32))
+        assert diff.max() <= 1, f"max ulp distance {diff.max()}"
+        assert (diff == 0).mean() > 0.95

@@ -84,6 +84,8 @@ EXPORTS = [
     "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
     "vlab200_node_norm_bf16",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
+    "bitvla_lm_cuda_init", "bitvla_lm_cuda_free", "bitvla_lm_cuda_set_layer", "bitvla_lm_cuda_set_output_norm",
+    "bitvla_lm_cuda_forward",
 ]
 
 
@@ -446,12 +448,14 @@ class PolicyEngine:
                                             pos_base, _ptr(pad_ranges), _stream()), "vlab200_engine_denoise")
         return out
 
-    def denoise_host(self, x0_host, state_host, out_host, pos_base=-1):
-        """Pinned host float32 buffers in and out; copies are enqueued on the current stream."""
+    def denoise_host(self, x0_host, state_host, out_host, pos_base=-1, pad_ranges_host=None):
+        """Pinned host float32 buffers in and out (pad_ranges_host: host int32 [n_obs, 2]); copies are enqueued
+        on the current stream."""
         _check(lib().vlab200_engine_denoise_host(
             C.c_void_p(self.h), x0_host.shape[0],
             C.c_void_p(state_host.data_ptr()) if state_host is not None else None,
-            C.c_void_p(x0_host.data_ptr()), C.c_void_p(out_host.data_ptr()), pos_base, _stream()),
+            C.c_void_p(x0_host.data_ptr()), C.c_void_p(out_host.data_ptr()), pos_base,
+            C.c_void_p(pad_ranges_host.data_ptr()) if pad_ranges_host is not None else None, _stream()),
             "vlab200_engine_denoise_host")
         return out_host
 

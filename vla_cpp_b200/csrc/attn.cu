@@ -53,20 +53,8 @@ struct AttnParams {
     int t1_rot;    // 1: t1_rows <= 32, its rows are placed in TMEM quarter (item ordinal % 4)
     float scale_log2;
     int *status;
-#ifdef VB_TRACE
-    long long *trace;  // developer builds: clock64 stamps of one softmax warp per region
-#endif
 };
 
-#ifdef VB_TRACE
-#define VB_STAMP(slot)                                                                                     \
-    do {                                                                                                   \
-        if (p.trace && qtr == 0 && half == 0 && lane == 0 && k_unit < 16)                                  \
-            p.trace[((size_t)blockIdx.x * 32 + (size_t)(k_unit * 2 + r)) * 8 + (slot)] = clock64();        \
-    } while (0)
-#else
-#define VB_STAMP(slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -337,7 +325,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             }
             for (int t = 0; ok && t < n_tiles; ++t) {
                 const uint32_t k_unit = m * (uint32_t)n_tiles + (uint32_t)t;
-                VB_STAMP(0);
                 // row of this thread inside the R-row block, or -1
                 int row;
                 if (t == 0) row = qtr * 32 + lane;
@@ -355,7 +342,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 ok = mbar_wait(&bar_s[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                VB_STAMP(1);
                 // ---- pass 1: maximum over this thread's columns ----
                 float mxx = -INFINITY;
                 if (warp_active) {
@@ -372,7 +358,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 region_sync(r);
                 mxx = fmaxf(mxx, x_max[(half ^ 1) * 128 + my_row_slot]);
                 const float m2 = (mxx == -INFINITY) ? 0.0f : mxx * p.scale_log2;
-                VB_STAMP(2);
                 // ---- pass 2: p = exp2(s*c - m*c), P (bf16) over this half's consumed S columns ----
                 float sum0 = 0.0f, sum1 = 0.0f;
                 if (warp_active) {
@@ -385,13 +370,11 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                     tmem_st_wait();
                 }
                 x_sum[half * 128 + my_row_slot] = sum0 + sum1;
-                VB_STAMP(3);
                 tc_fence_before();
                 mbar_arrive(&bar_p[2 * r + half]);
                 ok = mbar_wait(&bar_o[r], k_unit & 1u, wc, DEV_TIMEOUT_ACCUM);
                 if (!ok) break;
                 tc_fence_after();
-                VB_STAMP(4);
                 region_sync(r);  // both halves' partial sums are in shared memory
                 const float sum = x_sum[my_row_slot] + x_sum[128 + my_row_slot];
                 uint32_t o[32];
@@ -401,7 +384,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 }
                 tc_fence_before();
                 mbar_arrive(&bar_free[r]);
-                VB_STAMP(5);
                 if (row_ok) {
                     const float inv = 1.0f / sum;
                     __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * 64) +
@@ -440,10 +422,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 
 }  // namespace vb
 
-#ifdef VB_TRACE
-static long long *g_vb_attn_trace = nullptr;
-extern "C" __attribute__((visibility("default"))) void vlab200_set_attn_trace(long long *p) { g_vb_attn_trace = p; }
-#endif
 
 extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, const void *q, void *out,
                                      int32_t S, int32_t n_q, int32_t kv_len, int32_t mask_mode,
@@ -503,19 +481,10 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     p.scale_log2 = 1.4426950408889634f / sqrtf(64.0f);
     p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
-#ifdef VB_TRACE
-    p.trace = g_vb_attn_trace;
-#endif
     const int smem = vb::ATT_SMEM_DATA + 256 + 2 * 512 * 4 + 1024;
-    static bool attr_done = false;
-    static int n_sm = 0;
-    if (!attr_done) {
-        VB_CUDA(cudaFuncSetAttribute(vb::attn_hd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        int dev = 0;
-        VB_CUDA(cudaGetDevice(&dev));
-        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-        attr_done = true;
-    }
+    int rc_attr = vb::ensure_dyn_smem(vb::attn_hd64_kernel, smem);
+    if (rc_attr) return rc_attr;
+    const int n_sm = vb::sm_count();
     const int grid = p.n_items < n_sm ? p.n_items : n_sm;
     vb::attn_hd64_kernel<<<grid, vb::ATT_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(qmap, qmap32, kmap, vmap,
                                                                                             p);

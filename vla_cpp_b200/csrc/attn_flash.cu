@@ -361,16 +361,6 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 // issues at most one tcgen05.mma every ~64 cycles, twice the duration of an N = 64 MMA).  Rings are 4
 // deep.  The even CTA issues; commits are multicast to both CTAs; the odd CTA's MMA warp forwards "my
 // Q tile / K half / V half has landed", its softmax warps arrive on the even CTA's p_full / o_free.
-#ifdef VB_TRACE
-__device__ long long g_fp_trace[2][64][8];
-#define FP_STAMP(who, slot)                                                                             \
-    do {                                                                                                \
-        if (blockIdx.x == 0 && jb < 64 && ((who) == 0 || (warp == 0 && lane == 0)))                      \
-            g_fp_trace[who][jb][slot] = clock64();                                                      \
-    } while (0)
-#else
-#define FP_STAMP(who, slot) do { } while (0)
-#endif
 constexpr int FP_BKV = 128;   // keys per block: 16 Q K^T MMAs (N = 128) serve twice the keys of the one-CTA kernel's N = 64
 constexpr int FP_THREADS = 352;  // warps 0-7 softmax (quarter = warp & 3, column half = warp >> 2), 8 loader, 9 Q K^T issuer, 10 P V issuer
 constexpr int FP_LOADER_WARP = 8, FP_MMA_WARP = 9, FP_PV_WARP = 10;
@@ -531,13 +521,10 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 for (int j = 0; j < nb; ++j, ++jb) {
-                    FP_STAMP(0, 0);
                     ok = ready_s(jb);
                     if (!ok) break;
                     tc_fence_after();
-                    FP_STAMP(0, 1);
                     issue_s(jb);
-                    FP_STAMP(0, 2);
                 }
                 if (!ok) break;
                 tc_commit_pair(q_free, 3);  // the unit's last S block has been issued
@@ -577,7 +564,6 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     if (ok && j == 0) ok = mbar_wait(o_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     tc_fence_after();
-                    FP_STAMP(0, 3);
                     const uint64_t v_desc = v_desc0 + (uint64_t)(st * (L::V_BYTES >> 4));
                     const uint32_t p_tmem = tmem_base + L::O_COLS + sb * FP_BKV;
 #pragma unroll
@@ -586,7 +572,6 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                                             (j | k16) != 0 ? 1u : 0u);
                     tc_commit_pair(&pv_done[sb], 3);
                     tc_commit_pair(&v_free[st], 3);
-                    FP_STAMP(0, 4);
                 }
                 if (!ok) break;
                 tc_commit_pair(o_done, 3);
@@ -640,16 +625,13 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             for (int j = 0; j < nb; ++j, ++jb) {
                 const uint32_t sb = jb % FP_NS, sph = (jb / FP_NS) & 1u;
                 const uint32_t s_addr = tmem_base + L::O_COLS + sb * FP_BKV + lane_sel;
-                FP_STAMP(1, 0);
                 ok = mbar_wait(&s_full[sb], sph, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                FP_STAMP(1, 1);
                 uint32_t sa[32], sc[32];  // this half's 64 of the block's 128 key columns
                 tmem_ld32(s_addr + (uint32_t)(half * 64), sa);
                 tmem_ld32(s_addr + (uint32_t)(half * 64 + 32), sc);
                 tmem_ld_wait();
-                FP_STAMP(1, 2);
                 const int c0 = j * FP_BKV + half * 64;
                 const bool clean = j * FP_BKV + FP_BKV <= clean_end;
                 if (!clean) {
@@ -676,7 +658,6 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 bm = fmaxf(bm, xch[(half ^ 1) * 128 + my_slot]) * p.scale_log2;
                 ok = pair_sync();  // the slot is rewritten in the next block
                 if (!ok) break;
-                FP_STAMP(1, 3);
                 float factor = 1.0f;
                 const bool raise = bm > m_used + 8.0f;
                 if (raise) {
@@ -720,7 +701,6 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tmem_st_wait();
                 tc_fence_before();
                 arrive_even(&p_full[sb]);
-                FP_STAMP(1, 4);
             }
             if (!ok) break;
             // ---- epilogue: O / l -> bf16 -> out (each half stores half of the head dimension) ----
@@ -810,15 +790,7 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
     p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
-    static bool attr_done = false;
-    static int n_sm = 0;
-    if (!attr_done) {
-        VB_CUDA(cudaFuncSetAttribute(attn_flash_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        int dev = 0;
-        VB_CUDA(cudaGetDevice(&dev));
-        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-        attr_done = true;
-    }
+    const int n_sm = sm_count();
     if constexpr (HD >= 128) {
         // CTA pairs once an item has two row tiles and the pairs fill the machine (or when forced for tests)
         const int n_pair_units = st->n_obs * st->n_kv * ((p.n_mt + 1) / 2), pairs = n_sm / 2;
@@ -834,18 +806,14 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
             int rc = make_tensor_map(&vmap128, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, st->v_pages, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return rc;
-            static bool pair_attr_done = false;
-            if (!pair_attr_done) {
-                VB_CUDA(cudaFuncSetAttribute(attn_flash_pair_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             LP::TOTAL));
-                pair_attr_done = true;
-            }
+            if ((rc = ensure_dyn_smem(attn_flash_pair_kernel<HD>, LP::TOTAL))) return rc;
             const int ncl = n_pair_units < pairs ? n_pair_units : pairs;
             attn_flash_pair_kernel<HD><<<2 * ncl, FP_THREADS, LP::TOTAL, stream>>>(qmap, kmap, vmap128, p);
             VB_CUDA(cudaGetLastError());
             return VLAB200_OK;
         }
     }
+    if (int rc = ensure_dyn_smem(attn_flash_kernel<HD>, L::TOTAL)) return rc;
     const int grid = p.n_units < n_sm ? p.n_units : n_sm;
     attn_flash_kernel<HD><<<grid, FA_THREADS, L::TOTAL, stream>>>(qmap, kmap, vmap, p);
     VB_CUDA(cudaGetLastError());
@@ -862,8 +830,3 @@ int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *
 
 }  // namespace vb
 
-#ifdef VB_TRACE
-extern "C" __attribute__((visibility("default"))) int vlab200_flash_pair_trace(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, vb::g_fp_trace, sizeof(long long) * 2 * 64 * 8);
-}
-#endif

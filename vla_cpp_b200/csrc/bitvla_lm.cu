@@ -464,12 +464,9 @@ static int launch_norm_quant(void *in, const void *add, const void *w, float eps
         VB_CUDA(cudaGetLastError());
         return VLAB200_OK;
     }
-    static bool attr_done = false;
     const size_t smem = (size_t)K * 4;
-    if (smem > 48 * 1024 && !attr_done) {
-        VB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
-    }
+    if (smem > 48 * 1024)
+        if (int rc = ensure_dyn_smem(norm_quant_kernel<MODE>, 200 * 1024)) return rc;
     norm_quant_kernel<MODE><<<M, 256, smem, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
@@ -555,6 +552,39 @@ extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void 
     return vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, ctx->output_norm, ctx->eps, M, H, nullptr, nullptr,
                                              d_out, st);
 }
+
+// The reference's own names and signatures for the context API (src/kernels/bitvla/bitvla_lm_cuda.h:247-286),
+// so that src/models/bitvla.cpp (call sites :760-821,1326-1334) links against this library unchanged.
+// One sequence per call (max_batch = n_seq = 1), as the reference runs it; bitvla_lm_layer_cuda has the
+// field order of vlab200_bitvla_lm_layer, so the struct pointer passes through.
+extern "C" {
+
+bitvla_lm_cuda_ctx *bitvla_lm_cuda_init(int hidden, int n_q, int n_kv, int head_dim, int ffn, int n_layers,
+                                        float rope_base, float rms_eps, int max_seq) {
+    vlab200_bitvla_lm *c = vlab200_bitvla_lm_init(hidden, n_q, n_kv, head_dim, ffn, n_layers, rope_base, rms_eps,
+                                                  max_seq, 1);
+    if (!c) std::fprintf(stderr, "vla(bitvla_lm_cuda): %s\n", vlab200_last_error());
+    return reinterpret_cast<bitvla_lm_cuda_ctx *>(c);
+}
+
+void bitvla_lm_cuda_free(bitvla_lm_cuda_ctx *ctx) { vlab200_bitvla_lm_free(reinterpret_cast<vlab200_bitvla_lm *>(ctx)); }
+
+void bitvla_lm_cuda_set_layer(bitvla_lm_cuda_ctx *ctx, int L, const bitvla_lm_layer_cuda *layer) {
+    if (vlab200_bitvla_lm_set_layer(reinterpret_cast<vlab200_bitvla_lm *>(ctx), L, layer) != VLAB200_OK)
+        std::fprintf(stderr, "vla(bitvla_lm_cuda): set_layer %d failed: %s\n", L, vlab200_last_error());
+}
+
+void bitvla_lm_cuda_set_output_norm(bitvla_lm_cuda_ctx *ctx, const void *w) {
+    vlab200_bitvla_lm_set_output_norm(reinterpret_cast<vlab200_bitvla_lm *>(ctx), w);
+}
+
+int bitvla_lm_cuda_forward(bitvla_lm_cuda_ctx *ctx, const void *d_in, void *d_out, int seq, void *stream) {
+    const int rc = vlab200_bitvla_lm_forward(reinterpret_cast<vlab200_bitvla_lm *>(ctx), d_in, d_out, seq, 1, stream);
+    if (rc != VLAB200_OK) std::fprintf(stderr, "vla(bitvla_lm_cuda): forward failed (%d): %s\n", rc, vlab200_last_error());
+    return rc == VLAB200_OK ? 0 : -1;
+}
+
+}  // extern "C"
 
 // The LM stack of a BitVLA checkpoint: metadata "bitvla.lm.*" (src/models/bitvla.cpp:360-364), per layer four
 // float32 norm vectors (uploaded as bf16, bitvla.cpp:768-771) and six ladder-int2 tensors "<base>.weight" (I8,

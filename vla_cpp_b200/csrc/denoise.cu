@@ -6,6 +6,8 @@
 // launches (fused QKV+RoPE+append, attention) on one stream.
 #include <cuda_bf16.h>
 
+#include <cstdint>
+#include <mutex>
 #include <vector>
 
 #include "host_common.h"
@@ -41,9 +43,11 @@ static __device__ __align__(256) unsigned char g_static_q_scratch[kStaticQBytes]
 // per device, with that device current.
 static int static_q_scratch_ptr(void **out) {
     static void *ptrs[64] = {nullptr};
+    static std::mutex mu;
     int dev = 0;
     VB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return VLAB200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(mu);
     if (!ptrs[dev]) {
         void *p = nullptr;
         VB_CUDA(cudaGetSymbolAddress(&p, g_static_q_scratch));
@@ -77,9 +81,12 @@ int32_t vlab200_denoise_attn_loop(const vlab200_kv_store *st, const vlab200_deno
 int32_t vlab200_denoise_attn_loop_static(const vlab200_kv_store *st, const vlab200_denoise_attn_args *a,
                                          void *stream) {
     if (!st || !a) return VLAB200_ERR_ARG;
-    const size_t need = (size_t)st->n_obs * a->n_q * a->S * st->head_dim * 2;
     if (st->n_obs <= 0 || a->n_q <= 0 || a->S <= 0 || st->head_dim <= 0) return VLAB200_ERR_ARG;
-    if (need > vb::kStaticQBytes) {
+    // every factor is bounded before the product is formed, so the size cannot wrap
+    constexpr int32_t kMaxFactor = 1 << 20;
+    const bool absurd = st->n_obs > kMaxFactor || a->n_q > kMaxFactor || a->S > kMaxFactor || st->head_dim > 1024;
+    const size_t need = absurd ? SIZE_MAX : (size_t)st->n_obs * a->n_q * ((size_t)a->S * st->head_dim * 2);
+    if (absurd || (size_t)st->n_obs * a->n_q > ((size_t)1 << 40) || need > vb::kStaticQBytes) {
         vb::set_last_error("vlab200_denoise_attn_loop_static: the query buffer needs %zu bytes, the built-in scratch "
                            "holds %zu; use vlab200_denoise_attn_loop with a caller-provided q_scratch",
                            need, vb::kStaticQBytes);
@@ -104,8 +111,18 @@ int32_t vlab200_denoise_attn_loop_host(const vlab200_kv_store *st, const vlab200
     const size_t x_step_bytes = x_layer_bytes * a->n_layers;
     const size_t out_layer_elems = (size_t)st->n_obs * a->S * a->n_q * st->head_dim;
     // copy stream + events: step s+1's hidden states travel while step s computes
-    static thread_local cudaStream_t copy_stream = nullptr;
-    static thread_local cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr};
+    // one set per (calling thread, device): streams and events belong to the device that was current
+    // when they were created; they live until the thread exits
+    struct CopyLane {
+        cudaStream_t stream = nullptr;
+        cudaEvent_t copied[2] = {nullptr, nullptr}, consumed[2] = {nullptr, nullptr};
+    };
+    static thread_local CopyLane lanes[64];
+    int dev = 0;
+    VB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return VLAB200_ERR_UNSUPPORTED;
+    cudaStream_t &copy_stream = lanes[dev].stream;
+    cudaEvent_t *ev_copied = lanes[dev].copied, *ev_consumed = lanes[dev].consumed;
     if (!copy_stream) {
         VB_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
         for (int i = 0; i < 2; ++i) {

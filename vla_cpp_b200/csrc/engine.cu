@@ -135,7 +135,7 @@ struct vlab200_engine {
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
     vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
     // workspace
-    vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage, vbuf;
+    vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage, pad_stage, vbuf;
     int rope_pos0 = -1;
 };
 
@@ -231,7 +231,7 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
         (rc = e->rope_cross.alloc((size_t)2 * e->S * (hd / 2) * 4)) ||
         (rc = e->tmp_bf.alloc((size_t)2 * B * e->P * kvf * 2)) || (rc = e->x_stage.alloc(Mc * A * 4)) ||
         (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)) ||
-        (rc = e->vbuf.alloc(M * A * 4)))
+        (rc = e->pad_stage.alloc(B * 2 * 4)) || (rc = e->vbuf.alloc(M * A * 4)))
         return rc;
     VB_CUDA(cudaMemset(e->h.p, 0, M * H * 4));
     VB_CUDA(cudaMemset(e->hb.p, 0, M * H * 2));
@@ -258,16 +258,25 @@ extern "C" {
 
 vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vlab200_policy_weights *w,
                                       int32_t max_obs, int32_t prefix_len) {
-    if (!cfg || !w || max_obs <= 0 || prefix_len <= 0) return nullptr;
+    if (!cfg || !w || max_obs <= 0 || prefix_len <= 0) {
+        vb::set_last_error("vlab200_engine_create: null configuration / weights, or max_obs / prefix_len <= 0");
+        return nullptr;
+    }
     const vlab200_policy_config &c = *cfg;
     if (c.n_layers <= 0 || c.H <= 0 || c.n_q <= 0 || c.n_kv <= 0 || c.n_q % c.n_kv || c.inter <= 0 || c.chunk <= 0 ||
         c.action_dim <= 0 || c.action_dim > 64 || c.action_dim % 8 || c.state_dim > 64 || c.steps <= 0 || (c.model != 0 && c.model != 1)) {
         vb::set_last_error("vlab200_engine_create: bad configuration");
         return nullptr;
     }
-    if (c.H % 64 && c.H % 8) return nullptr;
+    if (c.H % 8) {
+        vb::set_last_error("vlab200_engine_create: hidden size %d is not a multiple of 8", c.H);
+        return nullptr;
+    }
     vlab200_engine *e = new (std::nothrow) vlab200_engine();
-    if (!e) return nullptr;
+    if (!e) {
+        vb::set_last_error("vlab200_engine_create: out of host memory");
+        return nullptr;
+    }
     e->c = c;
     e->max_obs = max_obs;
     e->P = prefix_len;
@@ -278,7 +287,9 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
     e->is_self.resize(c.n_layers);
     for (int l = 0; l < c.n_layers; ++l)
         e->is_self[l] = (c.model == 0) || (c.self_every <= 1) || (l % c.self_every == 0);
-    if (vb::engine_build(e, w) != VLAB200_OK) {
+    const int brc = vb::engine_build(e, w);
+    if (brc != VLAB200_OK) {
+        if (brc != VLAB200_ERR_CUDA) vb::set_last_error("vlab200_engine_create: building the engine failed with status %d", brc);
         delete e;
         return nullptr;
     }
@@ -420,7 +431,8 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
 }
 
 int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const float *state_host, const float *x0_host,
-                                    float *x_out_host, int32_t pos_base, void *stream) {
+                                    float *x_out_host, int32_t pos_base, const int32_t *pad_ranges_host,
+                                    void *stream) {
     if (!e || !x0_host || !x_out_host || n_obs <= 0 || n_obs > e->max_obs) return VLAB200_ERR_ARG;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     const size_t xb = (size_t)n_obs * e->c.chunk * e->c.action_dim * 4, sb = (size_t)n_obs * e->c.state_dim * 4;
@@ -428,7 +440,12 @@ int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const floa
     float *s_dev = e->state_stage.as<float>();
     VB_CUDA(cudaMemcpyAsync(x_dev, x0_host, xb, cudaMemcpyHostToDevice, cs));
     if (state_host) VB_CUDA(cudaMemcpyAsync(s_dev, state_host, sb, cudaMemcpyHostToDevice, cs));
-    int rc = vlab200_engine_denoise(e, n_obs, state_host ? s_dev : nullptr, x_dev, x_dev, pos_base, nullptr, cs);
+    int32_t *pad_dev = nullptr;
+    if (pad_ranges_host) {
+        pad_dev = e->pad_stage.as<int32_t>();
+        VB_CUDA(cudaMemcpyAsync(pad_dev, pad_ranges_host, (size_t)n_obs * 2 * 4, cudaMemcpyHostToDevice, cs));
+    }
+    int rc = vlab200_engine_denoise(e, n_obs, state_host ? s_dev : nullptr, x_dev, x_dev, pos_base, pad_dev, cs);
     if (rc) return rc;
     VB_CUDA(cudaMemcpyAsync(x_out_host, x_dev, xb, cudaMemcpyDeviceToHost, cs));
     return VLAB200_OK;

@@ -21,6 +21,8 @@
 // add / mul / unary ggml node each; src/cuda/vla_cuda_bf16.cu:624-678 for the cuBLAS GEMM node).
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "gemm.h"
 #include "host_common.h"
 #include "tc5.cuh"
@@ -389,11 +391,11 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_c
 }
 
 // 0 = choose by cost; 1 / 2 / 3 / 4 force the 128 x 256, 128 x 128, CTA-pair and 128 x 64 tilings (testing knob).
-static int g_gemm_variant = 0;
+static std::atomic<int> g_gemm_variant{0};
 constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile relative to a lone CTA's 128 x 256 tile
 
-void dense_gemm_set_variant(int v) { g_gemm_variant = (v >= 0 && v <= 4) ? v : 0; }
-int dense_gemm_variant() { return g_gemm_variant; }
+void dense_gemm_set_variant(int v) { g_gemm_variant.store((v >= 0 && v <= 4) ? v : 0, std::memory_order_relaxed); }
+int dense_gemm_variant() { return g_gemm_variant.load(std::memory_order_relaxed); }
 
 // Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
@@ -425,12 +427,8 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
-    static int n_sm = 0;
-    if (!n_sm) {
-        int dev = 0;
-        VB_CUDA(cudaGetDevice(&dev));
-        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int n_sm = sm_count();
+    if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
     // Four tilings: one CTA per 128 x 256 tile, per 128 x 128 or 128 x 64 tile (more CTAs streaming the
     // weights when the problem has few rows), a CTA pair per 256 x 256 tile (half the shared-memory traffic
     // per flop).  Costs
@@ -443,7 +441,7 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
     const int tn64 = (p.N + 63) / 64;
     const float cost64 = p.N > 64 ? 0.33f * waves(tiles_m * tn64, n_sm) : 1e30f;  // few rows: as many CTAs as possible stream W
     const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
-    int variant = g_gemm_variant;
+    int variant = dense_gemm_variant();
     if (variant == 0) {
         variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
         const float best = variant == 3 ? cost_pair : (variant == 2 ? cost128 : cost256);
@@ -458,12 +456,7 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        static bool done = false;
-        if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<256, true>::SMEM));
-            done = true;
-        }
+        if (int rc = ensure_dyn_smem(dense_gemm_pair_kernel, GemmCfg<256, true>::SMEM)) return rc;
         const int nt = tiles_mp * tn256;
         dense_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), G_THREADS, GemmCfg<256, true>::SMEM, stream>>>(
             amap, wmap, p, tiles_mp, tn256);
@@ -472,11 +465,7 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        static bool done = false;
-        if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<64, false>::SMEM));
-            done = true;
-        }
+        if (int rc = ensure_dyn_smem(dense_gemm_kernel<64>, GemmCfg<64, false>::SMEM)) return rc;
         const int nt = tiles_m * tn64;
         dense_gemm_kernel<64><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<64, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn64);
     } else if (variant == 2) {
@@ -484,19 +473,11 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        static bool done = false;
-        if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<128, false>::SMEM));
-            done = true;
-        }
+        if (int rc = ensure_dyn_smem(dense_gemm_kernel<128>, GemmCfg<128, false>::SMEM)) return rc;
         const int nt = tiles_m * tn128;
         dense_gemm_kernel<128><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<128, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn128);
     } else {
-        static bool done = false;
-        if (!done) {
-            VB_CUDA(cudaFuncSetAttribute(dense_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256, false>::SMEM));
-            done = true;
-        }
+        if (int rc = ensure_dyn_smem(dense_gemm_kernel<256>, GemmCfg<256, false>::SMEM)) return rc;
         const int nt = tiles_m * tn256;
         dense_gemm_kernel<256><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<256, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn256);
     }

@@ -2,7 +2,9 @@
 
 #include <cstdarg>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace vb {
 
@@ -35,6 +37,34 @@ int *device_status_ptr() {
         ptrs[dev] = static_cast<int *>(p);
     }
     return ptrs[dev];
+}
+
+int sm_count() {
+    static int counts[64] = {0};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!counts[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        counts[dev] = n;
+    }
+    return counts[dev];
+}
+
+int ensure_dyn_smem(const void *func, int bytes) {
+    static std::map<std::pair<int, const void *>, int> opted;  // (device, kernel) -> bytes opted into
+    static std::mutex mu;
+    int dev = 0;
+    VB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    int &have = opted[std::make_pair(dev, func)];
+    if (bytes > have) {
+        VB_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        have = bytes;
+    }
+    return VLAB200_OK;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

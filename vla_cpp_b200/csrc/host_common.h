@@ -13,6 +13,18 @@ namespace vb {
 // or nullptr when no CUDA device can be used.
 int *device_status_ptr();
 
+// Number of SMs of the current device (looked up once per device); 0 when no device can be used.
+int sm_count();
+
+// Opts kernel `func` into `bytes` of dynamic shared memory on the current device.  The attribute is
+// per device, so the call is remembered per (device, function) and repeated only when a larger
+// size is asked for.  Thread-safe.
+int ensure_dyn_smem(const void *func, int bytes);
+template <typename F>
+int ensure_dyn_smem(F *func, int bytes) {
+    return ensure_dyn_smem(reinterpret_cast<const void *>(func), bytes);
+}
+
 // printf-style text for vlab200_last_error() on the calling thread.
 void set_last_error(const char *fmt, ...);
 

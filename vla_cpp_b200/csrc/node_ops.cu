@@ -143,12 +143,8 @@ __global__ void __launch_bounds__(256) norm_kernel(const __nv_bfloat16 *__restri
 }
 
 static int stream_grid(int64_t work_items) {
-    static int n_sm = 0;
-    if (!n_sm) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            n_sm = 148;
-    }
+    int n_sm = sm_count();
+    if (n_sm <= 0) n_sm = 148;
     const int64_t blocks = (work_items + 255) / 256;
     const int64_t cap = (int64_t)n_sm * 8;
     return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));

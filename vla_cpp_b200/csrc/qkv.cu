@@ -744,18 +744,10 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
         if (rc) return rc;
         // shared memory: stages + barriers/stats + store staging + transposed RoPE table
         const int aux = 256 + 1024 + vb::QKVF_STAGING + 2 * (hd / 2) * S * 4;
-        static bool fdone = false;
-        static int n_sm = 0;
-        if (!fdone) {
-            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024));
-            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_tma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024));
-            int dev = 0;
-            VB_CUDA(cudaGetDevice(&dev));
-            VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-            fdone = true;
-        }
+        if ((rc = vb::ensure_dyn_smem(vb::qkv_rope_tma_kernel, 227 * 1024))) return rc;
+        if ((rc = vb::ensure_dyn_smem(vb::qkv_rope_tma_pair_kernel, 227 * 1024))) return rc;
+        const int n_sm = vb::sm_count();
+        if (n_sm <= 0) return vb::cuda_fail(cudaGetLastError(), "sm_count");
         const int tiles_m = (M + vb::QKV_BM - 1) / vb::QKV_BM, tiles_n = (n_total + vb::QKV_BN - 1) / vb::QKV_BN;
         const int tiles_mp = (M + 2 * vb::QKV_BM - 1) / (2 * vb::QKV_BM), pairs = n_sm / 2;
         // CTA pairs (256-row tiles) once they fill the machine at least as well as single CTAs do
@@ -792,18 +784,11 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
     }
     const int smem = vb::QKV_STAGES * vb::QKV_STAGE_BYTES + 256 + ksteps * vb::QKV_BK * 4 + 1024;
     dim3 grid((M + vb::QKV_BM - 1) / vb::QKV_BM, (n_total + vb::QKV_BN - 1) / vb::QKV_BN);
-    static int smem_set[2] = {0, 0};  // largest dynamic shared memory size opted into so far
     if (x_is_f32) {
-        if (smem > smem_set[1]) {
-            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            smem_set[1] = smem;
-        }
+        if ((rc = vb::ensure_dyn_smem(vb::qkv_rope_kernel<true>, smem))) return rc;
         vb::qkv_rope_kernel<true><<<grid, vb::QKV_THREADS, smem, cs>>>(wmap, p);
     } else {
-        if (smem > smem_set[0]) {
-            VB_CUDA(cudaFuncSetAttribute(vb::qkv_rope_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            smem_set[0] = smem;
-        }
+        if ((rc = vb::ensure_dyn_smem(vb::qkv_rope_kernel<false>, smem))) return rc;
         vb::qkv_rope_kernel<false><<<grid, vb::QKV_THREADS, smem, cs>>>(wmap, p);
     }
     VB_CUDA(cudaGetLastError());

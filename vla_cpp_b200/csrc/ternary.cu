@@ -774,7 +774,7 @@ static int launch_gemv(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, in
                        const float *ws, int ws_num, int M, int N, int K, int m0, cudaStream_t st) {
     const size_t smem = (size_t)MT * K + GEMV_WARPS * MT * 16 * sizeof(int);
     if (smem > 48 * 1024)
-        VB_CUDA(cudaFuncSetAttribute(ternary_gemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (int rc = ensure_dyn_smem(ternary_gemv_kernel<MT>, (int)smem)) return rc;
     ternary_gemv_kernel<MT><<<N / 16, GEMV_THREADS, smem, st>>>(A, W, out, acc, s, ws, ws_num, M, N, K, m0);
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
@@ -793,16 +793,9 @@ static int launch_gemm_tc(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
                              CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     using L = GemmSmem<BN, STAGES>;
-    static bool attr_done = false;
-    static int n_sm = 0;
-    if (!attr_done) {
-        VB_CUDA(cudaFuncSetAttribute(ternary_gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     L::TOTAL));
-        int dev = 0;
-        VB_CUDA(cudaGetDevice(&dev));
-        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-        attr_done = true;
-    }
+    if ((rc = ensure_dyn_smem(ternary_gemm_tc_kernel<BN, STAGES>, L::TOTAL))) return rc;
+    const int n_sm = sm_count();
+    if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
     const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + BN - 1) / BN;
     const int nt = tiles_m * tiles_n;
     ternary_gemm_tc_kernel<BN, STAGES><<<nt < n_sm ? nt : n_sm, GEMM_THREADS, L::TOTAL, st>>>(
@@ -822,16 +815,9 @@ static int launch_gemm_pair(const int8_t *A, const uint8_t *W, __nv_bfloat16 *ou
     int rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box,
                              CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    static bool attr_done = false;
-    static int n_sm = 0;
-    if (!attr_done) {
-        VB_CUDA(cudaFuncSetAttribute(ternary_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     PairSmem::TOTAL));
-        int dev = 0;
-        VB_CUDA(cudaGetDevice(&dev));
-        VB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-        attr_done = true;
-    }
+    if ((rc = ensure_dyn_smem(ternary_gemm_pair_kernel, PairSmem::TOTAL))) return rc;
+    const int n_sm = sm_count();
+    if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
     const int tiles_mp = (M + 255) / 256, tiles_n = (N + 255) / 256;
     const int nt = tiles_mp * tiles_n, pairs = n_sm / 2;
     ternary_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), GEMM_THREADS, PairSmem::TOTAL, st>>>(
