@@ -3,17 +3,20 @@
 
 Metric (BASELINE.json): action chunks/s and p50 chunk latency of the denoise loop.
 
-Default workload ("smolvla_attn", BASELINE.json configs[1]): the isolated denoise-attention
-op, bf16 -- 16 layers, prefix KV length 177 written once per observation, a 51-token suffix
-projected by the fused RMSNorm+QKV+RoPE kernel and appended each step, attention over the
-228 keys, 10 steps; GQA 15q/5kv, head_dim 64; batch 256 observations per GPU.  One bench
-"step" runs the whole 10-step x 16-layer loop over the batch, i.e. produces `batch` chunks.
+Default workload ("pi0", BASELINE.json configs[4]): the whole pi0-shaped flow-matching denoise loop --
+18 expert layers, hidden 1024, 8 q / 1 kv heads of 256, MLP 4096, prefix of 816 cached K/V rows per layer,
+a 50 x 32 action chunk plus the state token, 10 Euler steps -- over 1024 independent observations split
+across the ranks (1024 / 512 / 256 / 128 per GPU at 1 / 2 / 4 / 8 GPUs: strong scaling, no collective on the
+data path, every rank holds a weight replica and its own K/V pages).  One bench "step" denoises every
+observation once, i.e. produces 1024 action chunks.
 
   python bench.py --gpus N --steps K --warmup W            # this library
-  python bench.py --impl reference ...                     # the CPU restatement on host cores
+  python bench.py --impl reference ...                     # the CPU restatement of the same loop on host cores
 
-Multi-GPU: observations are independent, so each rank owns `batch` observations with a full
-replica of the weights and its own KV store; no collective on the data path (weak scaling).
+At one GPU the same JSON line also carries: the loop's stage timings with the dominant GEMM's roofline, the
+pi0 attention kernel against both HBM and tensor peaks, batch-1 / batch-64 chunk latency (configs[2]), and
+sub-records for the isolated denoise-attention op (configs[1]), the ternary GEMM sweep and the BitVLA LM stack
+(configs[3]) with the reference's own CUDA kernels timed beside them.  --workload selects one of those alone.
 """
 import argparse
 import json
@@ -31,8 +34,37 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(L=16, T=10, H=720, n_q=15, n_kv=5, hd=64, S=51, P=177, eps=1e-5)
 ATTN_BYTES_PER_OBS_LAYER_STEP = 2 * (177 * 5 * 64 * 2) + 2 * (51 * 5 * 64 * 2) + 2 * (51 * 15 * 64 * 2)  # 487,680
-ATTN_DRAM_BYTES_PER_OBS_NCU = 25.11e6 / 64  # profiles/attn_hd64_smolvla_attn_b64.md
-INT8_PEAK_TOPS = 3249.8  # measured on this pool, profiles/int8_tensor_peak_b200.md
+# DRAM bytes (read + write) of one attn_hd64_kernel launch per observation, from an ncu capture at batch 64
+# (25.11 MB for 64 observations; pages are read once, so the traffic grows in proportion to the batch)
+ATTN_DRAM_BYTES_PER_OBS_NCU = 25.11e6 / 64
+# int8 tensor-core peak measured on this pool (cuBLASLt 8192^3 through torch._int_mm, best of 10): `--int8-peak`
+# repeats the measurement, and the default run measures it again beside the ternary sweep
+INT8_PEAK_TOPS = 3249.8
+
+
+def measure_int8_peak(torch, dev, n=8192):
+    """cuBLASLt int8 x int8 -> int32 GEMM (library call, used only as the roofline's denominator)."""
+    a = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev)
+    b = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev).t().contiguous().t()
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(100):
+        torch._int_mm(a, b)
+    e1.record()
+    torch.cuda.synchronize()
+    return {"n": n, "burst_tops": 2.0 * n ** 3 / best / 1e9, "sustained_tops": 2.0 * n ** 3 * 100 / e0.elapsed_time(e1) / 1e9,
+            "how": "torch._int_mm (cuBLASLt), best of 10 / 100 back to back, CUDA events"}
 
 
 def measured_peaks():
@@ -99,7 +131,8 @@ class ClockSampler:
 
 
 def oracle_chunk(orc, rng, n_chunks):
-    """CPU restatement of the same workload for `n_chunks` observations; returns seconds."""
+    """CPU restatement of the isolated denoise-attention op for `n_chunks` observations; returns seconds.
+    Every input (hidden states included) is generated before the clock starts."""
     c = CFG
     n_rows = (c["n_q"] + 2 * c["n_kv"]) * c["hd"]
     w = orc.bf16_round((rng.standard_normal((c["L"], n_rows, c["H"])) * 0.02).astype(np.float32))
@@ -107,14 +140,62 @@ def oracle_chunk(orc, rng, n_chunks):
     pos = np.arange(c["P"], c["P"] + c["S"]).astype(np.int32)
     kp = rng.standard_normal((c["L"], c["P"], c["n_kv"], c["hd"])).astype(np.float32)
     vp = rng.standard_normal((c["L"], c["P"], c["n_kv"], c["hd"])).astype(np.float32)
+    xs = rng.standard_normal((n_chunks, c["T"], c["L"], c["S"], c["H"]), dtype=np.float32)
+    kfull = np.concatenate([kp, np.zeros((c["L"], c["S"], c["n_kv"], c["hd"]), np.float32)], axis=1)
+    vfull = kfull.copy()
+    vfull[:, :c["P"]] = vp
     t0 = time.perf_counter()
-    for _ in range(n_chunks):
-        for _step in range(c["T"]):
+    for i in range(n_chunks):
+        for step in range(c["T"]):
             for l in range(c["L"]):
-                x = rng.standard_normal((c["S"], c["H"])).astype(np.float32)
-                q, k, v = orc.qkv_rope(x, ln, w[l], pos, c["n_q"], c["n_kv"], c["hd"], c["eps"])
-                orc.attention(q, np.concatenate([kp[l], k]), np.concatenate([vp[l], v]), c["P"], orc.MASK_SMOLVLA)
+                q, k, v = orc.qkv_rope(xs[i, step, l], ln, w[l], pos, c["n_q"], c["n_kv"], c["hd"], c["eps"])
+                kfull[l, c["P"]:], vfull[l, c["P"]:] = k, v  # the KV append of the step
+                orc.attention(q, kfull[l], vfull[l], c["P"], orc.MASK_SMOLVLA)
     return time.perf_counter() - t0
+
+
+class OraclePolicyLoop:
+    """The CPU restatement (oracle.DenoiseModel) of a whole denoise loop with weights N(0, 0.02), one
+    observation per call: the timed CPU baseline of the default workload."""
+
+    def __init__(self, orc, policy, seed):
+        c, P = POLICIES[policy]
+        rng = np.random.default_rng(seed)
+        L, H, I, hd = c["n_layers"], c["H"], c["inter"], c["head_dim"]
+        qf, kvf = c["n_q"] * hd, c["n_kv"] * hd
+        w = lambda *shape: orc.bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+        z = lambda n: np.zeros(n, np.float32)
+        one = lambda n: np.ones(n, np.float32)
+        cross = [c["model"] == 1 and c["self_every"] > 1 and l % c["self_every"] != 0 for l in range(L)]
+        wqkv = []
+        for l in range(L):
+            kv_in = kvf if cross[l] else H
+            wqkv.append(np.concatenate([w(qf, H).ravel(), w(kvf, kv_in).ravel(), w(kvf, kv_in).ravel()]))
+        ow = dict(ln_in=[one(H) for _ in range(L)], Wqkv=wqkv, Wo=[w(H, qf) for _ in range(L)],
+                  ln_post=[one(H) for _ in range(L)], Wgate=[w(I, H) for _ in range(L)], Wup=[w(I, H) for _ in range(L)],
+                  Wdown=[w(H, I) for _ in range(L)], W_sp=w(H, 32) if c["model"] == 0 else None,
+                  b_sp=z(H) if c["model"] == 0 else None, W_ain=w(H, 32), b_ain=z(H), W_at1=w(H, 2 * H), b_at1=z(H),
+                  W_at2=w(H, H), b_at2=z(H), out_norm=one(H), W_aout=w(32, H), b_aout=z(32))
+        ocfg = dict(model=c["model"], n_layers=L, H=H, n_q=c["n_q"], n_kv=c["n_kv"], hd=hd, inter=I, P=P,
+                    chunk=c["chunk"], A=32, state_dim=32, T=c["steps"], pos_base=P, pad_start=0, pad_end=0,
+                    self_every=max(c["self_every"], 1), act_bf16=0, rms_eps=c["rms_eps"], rope_base=c["rope_base"],
+                    min_period=c["min_period"], max_period=c["max_period"])
+        self.model = orc.DenoiseModel(ocfg, ow)
+        self.kp = [rng.standard_normal((P, c["n_kv"], hd), dtype=np.float32) for _ in range(L)]
+        self.vp = [rng.standard_normal((P, c["n_kv"], hd), dtype=np.float32) for _ in range(L)]
+        self.rng = rng
+
+    def run(self, n_obs):
+        """Seconds per observation for n_obs observations (inputs drawn before the clock starts)."""
+        xs = [(self.rng.standard_normal(32).astype(np.float32), self.rng.standard_normal((50, 32)).astype(np.float32))
+              for _ in range(n_obs)]
+        times = []
+        for state, x0 in xs:
+            t0 = time.perf_counter()
+            out = self.model.denoise(self.kp, self.vp, state, x0)
+            times.append(time.perf_counter() - t0)
+            assert np.isfinite(out).all()
+        return times
 
 
 PI0 = dict(model=0, n_layers=18, H=1024, n_q=8, n_kv=1, head_dim=256, inter=4096, chunk=50, action_dim=32,
@@ -301,6 +382,8 @@ def measure_ternary(torch, vb, dev, steps, warmup, only=None):
             del a, wp, sc, out
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
+    reference_cuda = None if only else time_reference_ternary(torch, vb, dev, shapes)
+    int8_live = None if only else measure_int8_peak(torch, dev)
     big = max((r for r in rows if r["M"] == 4800), key=lambda r: r["tops"], default=rows[0])
     gbs = lambda r: r.get("packed_weight_gbs_cuda_graph", r["packed_weight_gbs"])
     gemv = max((r for r in rows if r["M"] == 1), key=gbs, default=rows[0])
@@ -316,7 +399,67 @@ def measure_ternary(torch, vb, dev, steps, warmup, only=None):
             "roofline_gemv": {"kernel": "ternary_gemv_kernel", "bound": "hbm", "achieved": gbs(gemv),
                               "peak": hbm_peak, "unit": "GB/s", "frac": gbs(gemv) / hbm_peak,
                               "peak_kind": f"of {kind}", "shape": gemv},
-            "shapes": rows}
+            "shapes": rows, "int8_peak_live": int8_live, "reference_cuda": reference_cuda}
+
+
+def _median_launch_ms(torch, fn, warm=5, reps=20):
+    """Median of `reps` individually timed launches after `warm` warm-ups: the timing method of the reference's
+    own kernel check (tests/bitvla_gemm_check.cu:146-185); same operands every launch, so L2 stays warm."""
+    ms = []
+    for it in range(warm + reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        if it >= warm:
+            ms.append(e0.elapsed_time(e1))
+    return statistics.median(ms)
+
+
+def reference_lib(name):
+    """A reference-derived checker library built by oracle/Makefile (absent when the reference tree was not
+    there at build time): used here only as the timed GPU baseline, never on the product path."""
+    import ctypes
+
+    path = os.path.join(ROOT, "oracle", "_ref", name)
+    return ctypes.CDLL(path) if os.path.exists(path) else None
+
+
+def time_reference_ternary(torch, vb, dev, shapes):
+    """The reference's own CUDA kernels (bitlinear_int8xint2_m: the "wide" wmma kernel; bitlinear_int8xint2: its
+    M = 1 kernel) on the same shapes and the same box, both sides timed with the reference's method."""
+    import ctypes as C
+
+    ref = reference_lib("libbitnet_ref.so")
+    if ref is None:
+        return None
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    gemv_shapes = {(2560, 2560), (13824, 2560), (2560, 6912)}  # the M = 1 kernel is instantiated for these only
+    rows = []
+    for name, N, K, ws_num in shapes:
+        for M in (1, 300, 4800):
+            if M == 1 and (N, K) not in gemv_shapes:
+                continue
+            a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+            wp = torch.randint(0, 256, (N * K // 4,), dtype=torch.uint8, device=dev, generator=g)
+            sc = torch.rand((M,), device=dev, generator=g) * 100 + 40
+            ws = torch.rand((ws_num,), device=dev, generator=g) * 0.05 + 0.01
+            out_r = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            out_m = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            fn = ref.bitlinear_int8xint2 if M == 1 else ref.bitlinear_int8xint2_m
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            args = [C.c_void_p(t.data_ptr()) for t in (a, wp, out_r, sc, ws)] + [M, N, K, stream]
+            t_ref = _median_launch_ms(torch, lambda: fn(*args))
+            t_own = _median_launch_ms(torch, lambda: vb.ternary_linear(a, wp, sc, ws, N, out=out_m))
+            same = bool((out_r.view(torch.int16).int() - out_m.view(torch.int16).int()).abs().max().item() <= 1)
+            rows.append({"layer": name, "M": M, "N": N, "K": K, "reference_us": t_ref * 1e3, "this_library_us": t_own * 1e3,
+                         "speedup": t_ref / t_own, "reference_tops": 2.0 * M * N * K / t_ref / 1e9,
+                         "outputs_within_1_bf16_ulp": same})
+    return {"kernel": "reference bitlinear_int8xint2_m (wide wmma kernel) / bitlinear_int8xint2 (M = 1), compiled "
+                      "unmodified for sm_100", "method": "median of 20 launches after 5 warm-ups, CUDA events, same "
+                      "operands each launch (L2 warm) -- both sides", "shapes": rows}
 
 
 def measure_bitvla_lm(torch, vb, dev, steps, warmup, n_layers=30):
@@ -371,6 +514,7 @@ def measure_bitvla_lm(torch, vb, dev, steps, warmup, n_layers=30):
                      "launches": 1 + 9 * n_layers + 1})
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
+    reference_cuda = time_reference_lm(torch, dev, layers, norm(hidden), hidden, n_q, n_kv, hd, ffn, seq, rows[0]["ms"])
     big = rows[-1]
     return {"metric": "BitVLA LM stack throughput", "value": big["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
             "steps": steps, "warmup": warmup, "ms_per_step": big["ms"], "higher_is_better": True, "scaling": "weak",
@@ -384,158 +528,264 @@ def measure_bitvla_lm(torch, vb, dev, steps, warmup, n_layers=30):
                          "bound": "tensor", "achieved": big["ternary_tops"], "peak": INT8_PEAK_TOPS, "unit": "TOPS",
                          "frac": big["ternary_tops"] / INT8_PEAK_TOPS,
                          "peak_kind": "of measured (cuBLASLt int8, burst)", "traffic": None},
-            "cases": rows}
+            "cases": rows, "reference_cuda": reference_cuda}
 
 
-def config_dict(batch, n_gpus):
+def time_reference_lm(torch, dev, layers, out_norm, hidden, n_q, n_kv, hd, ffn, seq, own_ms_one_seq):
+    """The reference's bitvla_lm_cuda_forward (cuBLAS attention + its ternary kernels, one sequence per call) on
+    the same weights, timed on the same box."""
+    import ctypes as C
+
+    ref = reference_lib("libbitvla_lm_ref.so")
+    if ref is None:
+        return None
+    fields = ["attn_norm_w", "attn_sub_norm_w", "ffn_norm_w", "ffn_sub_norm_w", "q_packed", "q_ws", "k_packed", "k_ws",
+              "v_packed", "v_ws", "o_packed", "o_ws", "gate_up_packed", "gate_up_ws", "down_packed", "down_ws"]
+
+    class LayerC(C.Structure):
+        _fields_ = [(n, C.c_void_p) for n in fields]
+
+    ref.bitvla_lm_cuda_init.restype = C.c_void_p
+    ref.bitvla_lm_cuda_init.argtypes = [C.c_int] * 6 + [C.c_float, C.c_float, C.c_int]
+    ref.bitvla_lm_cuda_set_layer.argtypes = [C.c_void_p, C.c_int, C.POINTER(LayerC)]
+    ref.bitvla_lm_cuda_set_output_norm.argtypes = [C.c_void_p, C.c_void_p]
+    ref.bitvla_lm_cuda_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    ref.bitvla_lm_cuda_free.argtypes = [C.c_void_p]
+    ctx = ref.bitvla_lm_cuda_init(hidden, n_q, n_kv, hd, ffn, len(layers), 500000.0, 1e-5, seq)
+    if not ctx:
+        return None
+    for i, lw in enumerate(layers):
+        st = LayerC(**{n: lw[n].data_ptr() for n in fields})
+        ref.bitvla_lm_cuda_set_layer(ctx, i, C.byref(st))
+    ref.bitvla_lm_cuda_set_output_norm(ctx, out_norm.data_ptr())
+    x = torch.randn((seq, hidden), device=dev).bfloat16()
+    out = torch.empty_like(x)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    run = lambda: ref.bitvla_lm_cuda_forward(ctx, x.data_ptr(), out.data_ptr(), seq, stream)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 5
+    ref.bitvla_lm_cuda_free(ctx)
+    return {"kernel": "reference bitvla_lm_cuda_forward, compiled unmodified for sm_100 (one sequence per call)",
+            "seq": seq, "ms": ms, "tokens_per_s": seq / ms * 1e3, "this_library_ms_one_sequence": own_ms_one_seq,
+            "speedup_one_sequence": ms / own_ms_one_seq}
+
+
+def attn_config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
             "batch_per_gpu": batch, "global_batch": batch * n_gpus, "parallelism": f"replica x{n_gpus}",
             "l2": "inputs larger than L2 (KV store + hidden states > 126 MB per GPU)"}
 
 
+def policy_config_dict(workload, n_obs, n_global, world):
+    text = {"pi0": "pi0_loop: whole pi0-shaped denoise loop (BASELINE configs[4], shapes of configs[2]): 18 expert layers, "
+                   "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32 + state token, 10 Euler steps; "
+                   "1024 observations split over the GPUs",
+            "smolvla": "smolvla_loop: whole SmolVLA-shaped denoise loop (the action expert of BASELINE configs[0]): 16 "
+                       "layers alternating self / cross attention, hidden 720, 15q/5kv, hd 64, MLP 2048, prefix 177, "
+                       "chunk 50x32, 10 Euler steps"}[workload]
+    return {"workload": text, "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
+            "l2": "inputs larger than L2 (KV pages + expert weights + activations > 126 MB per GPU)"}
+
+
 def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the SAME loop on the host cores (the reference's own CPU
+    path runs through ggml, which is not part of its source tree), one observation per step."""
     if rank != 0:
         return
     from oracle import oracle_ffi as orc
 
-    rng = np.random.default_rng(1)
     # as the reference's default_cpu_threads() (src/arch.h:43-54): min(cores, 16), whatever the launcher exported
     orc.set_num_threads(min(os.cpu_count() or 1, 16))
     threads = orc.num_threads()
-    for _ in range(max(args.warmup, 0)):
-        oracle_chunk(orc, rng, 1)
-    times = [oracle_chunk(orc, rng, 1) for _ in range(args.steps)]
+    if args.workload == "smolvla_attn":
+        rng = np.random.default_rng(1)
+        for _ in range(max(args.warmup, 0)):
+            oracle_chunk(orc, rng, 1)
+        times = [oracle_chunk(orc, rng, 1) for _ in range(args.steps)]
+        config = attn_config_dict(1, 1)
+        sample = "1 observation (chunk) per step: 10 steps x 16 layers of QKV+RoPE+attention"
+    else:
+        workload = args.workload if args.workload in POLICIES else "pi0"
+        loop = OraclePolicyLoop(orc, workload, seed=1)
+        loop.run(max(min(args.warmup, 2), 0))
+        times = loop.run(args.steps)
+        config = policy_config_dict(workload, 1, 1, 1)
+        sample = ("1 observation (chunk) per step through the whole loop (all layers, 10 Euler steps) with float32 "
+                  "weights and activations")
     total = sum(times)
     value = args.steps / total
     line = {
         "impl": "reference", "metric": "action chunks/s (denoise loop)", "value": value, "unit": "chunks/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "p50_chunk_latency_ms": 1e3 * statistics.median(times), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(1, 1),
+        "p50_chunk_latency_ms": 1e3 * statistics.median(times), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": value, "unit": "chunks/s", "cores": threads, "kind": "port",
-                         "sample": "1 observation (chunk) per step: 10 steps x 16 layers of QKV+RoPE+attention; "
-                                   "the reference's own CPU path needs ggml (llama.cpp b10331), absent here"},
+                         "sample": sample + "; the reference's own CPU path needs ggml (llama.cpp b10331), absent here"},
         "e2e": {"value": value, "unit": "chunks/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="smolvla_attn", choices=["smolvla_attn", "pi0", "smolvla", "ternary", "bitvla_lm"],
-                    help="smolvla_attn: isolated denoise-attention op (BASELINE configs[1]); pi0: the whole "
-                         "pi0-shaped denoise loop, 1024 observations split over the GPUs (configs[4])")
-    ap.add_argument("--gemm-tiling", type=int, default=0,
-                    help="bf16 GEMM tiling inside the engine: 0 automatic, 1 128x256, 2 128x128, 3 CTA pairs")
-    ap.add_argument("--ternary-only", default=None,
-                    help="ternary workload: run one case only, e.g. gate_up:4800 (for profiler captures)")
-    ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for --workload pi0 (0: 1024 / N)")
-    ap.add_argument("--no-pi0-extra", action="store_true", help="skip the short pi0-loop measurement in the default run")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    args = ap.parse_args()
+def time_stage(torch, eng, stage, n_obs, n_layers, rounds=2):
+    """Average device time (ms) of one launch of `stage`, walking the layers (each layer has its own weights and
+    K/V pages, so consecutive launches do not find their operands in L2)."""
+    for l in range(n_layers):
+        eng.run_stage(l, stage, n_obs)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(rounds):
+        for l in range(n_layers):
+            eng.run_stage(l, stage, n_obs)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (rounds * n_layers)
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
 
-    import torch
-    import torch.distributed as dist
+def policy_stage_records(torch, eng, c, P, n_obs, peaks):
+    """Per-stage timings of one expert layer at this batch, with the algorithmic FLOPs / bytes of each."""
+    S = c["chunk"] + (1 if c["model"] == 0 else 0)
+    M, H, I, hd = n_obs * S, c["H"], c["inter"], c["head_dim"]
+    qf, kvf = c["n_q"] * hd, c["n_kv"] * hd
+    flops = {"qkv": 2.0 * M * H * (qf + 2 * kvf), "attention": 4.0 * M * c["n_q"] * (P + S) * hd,
+             "o_proj": 2.0 * M * qf * H, "gate_up": 2.0 * M * H * 2 * I, "down": 2.0 * M * I * H}
+    out = {}
+    for stage in ("qkv", "attention", "o_proj", "gate_up", "down"):
+        ms = time_stage(torch, eng, stage, n_obs, c["n_layers"])
+        out[stage] = {"us_per_launch": ms * 1e3, "tflops": flops[stage] / (ms * 1e-3) / 1e12}
+    # attention: prefix K/V + suffix K/V + Q + O per observation per layer-step (algorithmic bytes)
+    att_bytes = n_obs * 2.0 * ((P + S) * kvf * 2 + S * qf * 2)
+    a = out["attention"]
+    a.update({"algorithmic_bytes_per_launch": att_bytes, "hbm_gbs": att_bytes / (a["us_per_launch"] * 1e-6) / 1e9,
+              "hbm_frac": att_bytes / (a["us_per_launch"] * 1e-6) / 1e9 / peaks["hbm_gbs"],
+              "tensor_frac": a["tflops"] / peaks["bf16_tflops_sustained"],
+              "flop_per_byte": flops["attention"] / att_bytes})
+    return out, flops
 
-    import vla_cpp_b200 as vb
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    vb.lib()
-    torch.cuda.set_device(local_rank)
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
+
+
+def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
+    """The whole denoise loop (pi0- or SmolVLA-shaped) over 1024 observations split across the ranks."""
+    from vla_cpp_b200.shard import shard_range
+
+    workload = args.workload
+    c, P = POLICIES[workload]
+    n_obs = args.pi0_obs or shard_range(1024, world, rank)[1]
+    n_global = args.pi0_obs * world if args.pi0_obs else 1024
+    warmup = max(args.warmup, 3)
+    peaks = load_peaks()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    eng, x0, state = build_pi0_engine(torch, vb, dev, n_obs, 99 + rank, workload)
+    for _ in range(warmup):
+        eng.denoise(x0, state)
+    barrier()
+    sampler.mark_begin()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        eng.denoise(x0, state)
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    total_ms = ev[0].elapsed_time(ev[-1])
+    # ---- end to end: state / noise in pinned host memory, actions read back, every step -----------------
+    x0h, sth = x0.cpu().pin_memory(), state.cpu().pin_memory()
+    outh = torch.empty_like(x0h).pin_memory()
+    eng.denoise_host(x0h, sth, outh)
+    barrier()
+    n_e2e = max(2, min(args.steps, 5))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_e2e):
+        eng.denoise_host(x0h, sth, outh)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    if not torch.isfinite(outh).all():
+        raise SystemExit("non-finite action chunk")
+    # ---- the stages of one expert layer, each timed alone on the launching stream -----------------------
+    stages, flops = policy_stage_records(torch, eng, c, P, n_obs, peaks)
+    if vb.device_status() != 0:
+        raise SystemExit("device status word reports a kernel failure")
+    stats = torch.tensor([total_ms, statistics.median(step_ms), e2e_ms, stages["gate_up"]["us_per_launch"],
+                          stages["attention"]["us_per_launch"]], device=dev, dtype=torch.float64)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total_ms, p50_ms, e2e_ms, gu_us, att_us = [float(v) for v in stats.tolist()]
+    if rank != 0:
+        return None
+    S = c["chunk"] + (1 if c["model"] == 0 else 0)
+    loop_tf = policy_flops_per_chunk(c, P) * n_obs * args.steps / (total_ms * 1e-3) / 1e12  # per GPU (rank 0's share)
+    gu_tf = flops["gate_up"] / (gu_us * 1e-6) / 1e12
+    few = n_obs * S <= 256
+    line = {
+        "metric": "action chunks/s (denoise loop)", "value": n_global * args.steps / (total_ms * 1e-3),
+        "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
+        "scaling": "weak" if args.pi0_obs else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": policy_config_dict(workload, n_obs, n_global, world), "clocks": clocks,
+        # per Euler step: 2 embedding kernels + 2 GEMMs, 5 kernels per layer (6 on the few-row path), head + Euler
+        "gpu_launches": (c["steps"] * (4 + c["n_layers"] * (6 if few else 5) + 2) + 3) * args.steps,
+        "roofline": {"kernel": "dense_gemm_pair_kernel (fused RMSNorm + gate/up + activation, the loop's largest "
+                               "share: M x 2*inter x H per layer-step)",
+                     "bound": "tensor", "achieved": gu_tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": gu_tf / peaks["bf16_tflops_sustained"],
+                     "peak_kind": f"of {peaks['kind']} (sustained: the kernel is timed back to back over the layers)",
+                     "traffic": None, "us_per_launch": gu_us, "algorithmic_flops_per_launch": flops["gate_up"]},
+        "loop": {"tflops": loop_tf, "frac_of_sustained_bf16": loop_tf / peaks["bf16_tflops_sustained"],
+                 "flops_per_chunk": policy_flops_per_chunk(c, P)},
+        "stages": stages,
+        "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": x0h.numel() * 4 + sth.numel() * 4,
+                "d2h_bytes_per_step": outh.numel() * 4, "ms_per_step": e2e_ms},
+    }
+    del eng, x0, state
+    torch.cuda.empty_cache()
+    return line
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
-    dev = torch.device("cuda", local_rank)
-    vb.set_gemm_tiling(args.gemm_tiling)
-    if args.workload == "ternary":
-        if rank == 0:
-            print(json.dumps(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3), args.ternary_only)),
-                  flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload == "bitvla_lm":
-        if rank == 0:
-            print(json.dumps(measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3))), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload in ("pi0", "smolvla"):
-        from vla_cpp_b200.shard import shard_range
+def small_batch_latency(torch, vb, dev, workload):
+    """configs[2]: chunk latency at batch 1 and 64 (one GPU)."""
+    c, P = POLICIES[workload]
+    weight_bytes = 2.0 * c["n_layers"] * (c["H"] * (c["n_q"] + 2 * c["n_kv"]) * c["head_dim"] + c["n_q"] * c["head_dim"] * c["H"]
+                                          + 3 * c["H"] * c["inter"])
+    out = {}
+    for b in (1, 64):
+        r = measure_pi0(torch, vb, dev, b, 10 if b == 1 else 5, 3, 7 + b, allow_graph=(b == 1), policy=workload)
+        out[b] = r
+    peaks = load_peaks()
+    best1 = min(v for v in (out[1]["p50_ms"], out[1]["graph_ms"]) if v)
+    return {"p50_chunk_latency_ms_batch1": out[1]["p50_ms"], "p50_chunk_latency_ms_batch1_cuda_graph": out[1]["graph_ms"],
+            "batch1_weight_stream_frac": weight_bytes * c["steps"] / (best1 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "batch1_e2e_ms": out[1]["e2e_ms"],
+            "p50_step_latency_ms_batch64": out[64]["p50_ms"], "chunks_per_s_batch64": 64 / (out[64]["p50_ms"] * 1e-3),
+            "batch64_e2e_ms": out[64]["e2e_ms"]}
 
-        pol_cfg, pol_P = POLICIES[args.workload]
-        n_obs = args.pi0_obs or shard_range(1024, world, rank)[1]
-        n_global = args.pi0_obs * world if args.pi0_obs else 1024
-        sampler = ClockSampler(local_rank)
-        sampler.start()
-        r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99 + rank, barrier, allow_graph=world == 1,
-                        policy=args.workload, on_begin=sampler.mark_begin)
-        clocks = sampler.stop()
-        stats = torch.tensor([r["total_ms"], r["p50_ms"], r["e2e_ms"]], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        total_ms, p50_ms, e2e_ms = [float(v) for v in stats.tolist()]
-        if rank == 0:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
-                os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-            tf_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
-            tf = policy_flops_per_chunk(pol_cfg, pol_P) * n_obs * args.steps / (total_ms * 1e-3) / 1e12  # per GPU (rank 0's share)
-            line = {
-                "metric": "action chunks/s (denoise loop)", "value": n_global * args.steps / (total_ms * 1e-3),
-                "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-                "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
-                "scaling": "weak" if args.pi0_obs else "strong", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic",
-                "config": {"workload": ("pi0: whole pi0-shaped denoise loop (BASELINE configs[2]/[4]): 18 layers, "
-                                        "hidden 1024, 8q/1kv, hd 256, MLP 4096, prefix 816, chunk 50x32, 10 steps")
-                           if args.workload == "pi0" else
-                           ("smolvla: whole SmolVLA-shaped denoise loop (the action expert of BASELINE configs[0]): 16 "
-                            "layers alternating self / cross attention, hidden 720, 15q/5kv, hd 64, MLP 2048, prefix 177, "
-                            "chunk 50x32, 10 steps"),
-                           "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
-                           "l2": "inputs larger than L2 (KV pages + expert weights > 126 MB per GPU)"},
-                # per Euler step: 2 embedding kernels + 2 GEMMs, 18 layers x 5 kernels (6 on the few-row path), head + Euler
-                "clocks": clocks,
-                "gpu_launches": (10 * (4 + pol_cfg["n_layers"] * (6 if n_obs * 51 <= 256 else 5) + 2) + 3) * args.steps,
-                "roofline": {"kernel": "whole loop (dense_gemm_kernel, qkv_rope_tma_kernel, attn_flash_kernel)",
-                             "bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
-                             "frac": tf / tf_peak, "peak_kind": "of measured (sustained)", "traffic": None},
-                "p50_chunk_latency_ms_cuda_graph": r.get("graph_ms"),
-                "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": r["h2d"],
-                        "d2h_bytes_per_step": r["d2h"], "ms_per_step": e2e_ms},
-            }
-            print(json.dumps(line), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
 
+def measure_smolvla_attn(torch, vb, dist, dev, args, rank, world, barrier, with_e2e=True):
+    """BASELINE configs[1]: the isolated denoise-attention op (16 layers x 10 steps of fused QKV+RoPE+append and
+    attention over prefix + suffix K/V) at `args.batch` observations per GPU."""
     c, B = CFG, args.batch
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
-    # ---- synthetic inputs, resident in HBM --------------------------------------------------
     store = vb.KvStore(c["L"], B, c["n_kv"], c["hd"], c["P"], c["S"], device=dev)
     for l in range(c["L"]):  # the prefix KV is written once per observation
         kp = torch.randn((B, c["P"], c["n_kv"], c["hd"]), device=dev, generator=g)
@@ -560,8 +810,7 @@ def main():
     op = vb.DenoiseAttn(store, c["H"], c["n_q"], c["S"], ln_w, wqkv, c["eps"], vb.MASK_CAUSAL)
     torch.cuda.synchronize()
 
-    # ---- device-resident throughput -----------------------------------------------------------
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     sampler.start()
     for _ in range(max(args.warmup, 3)):
         op.run(x)
@@ -579,7 +828,7 @@ def main():
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
 
-    # ---- dominant kernel alone: attention launches on the launching stream ---------------------
+    # the two kernels alone, on the launching stream
     n_att = c["L"] * c["T"]
     for l in range(c["L"]):
         vb.attention(store, l, op.q, c["S"], c["n_q"], c["P"] + c["S"], vb.MASK_CAUSAL, out=op.out[l])
@@ -601,9 +850,8 @@ def main():
     torch.cuda.synchronize()
     qkv_ms = q0.elapsed_time(q1) / n_att
 
-    # ---- end to end through the C ABI with host buffers ----------------------------------------
     e2e = None
-    if not args.no_e2e:
+    if with_e2e:
         x_host = torch.empty(x.shape, dtype=torch.bfloat16, pin_memory=True)
         x_host.copy_(x)
         out_host = torch.empty(op.out.shape, dtype=torch.bfloat16, pin_memory=True)
@@ -617,64 +865,153 @@ def main():
             op.run_host(x_host, out_host)
         e1.record()
         barrier()
-        e2e_ms = e0.elapsed_time(e1) / n_e2e
-        e2e = {"ms": e2e_ms, "h2d": x_host.numel() * 2, "d2h": out_host.numel() * 2}
+        e2e = {"ms": e0.elapsed_time(e1) / n_e2e, "h2d": x_host.numel() * 2, "d2h": out_host.numel() * 2}
         del x_host, out_host
 
-    # ---- max over ranks ------------------------------------------------------------------------
     stats = torch.tensor([total_ms, statistics.median(step_ms), att_ms, qkv_ms, e2e["ms"] if e2e else 0.0],
                          device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     total_ms, p50_ms, att_ms, qkv_ms, e2e_ms = [float(v) for v in stats.tolist()]
+    if rank != 0:
+        return None
+    hbm_peak, peak_kind = measured_peaks()
+    att_gbs = ATTN_BYTES_PER_OBS_LAYER_STEP * B / (att_ms * 1e-3) / 1e9
+    line = {
+        "metric": "action chunks/s (denoise loop)", "value": B * world * args.steps / (total_ms * 1e-3),
+        "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": attn_config_dict(B, world), "clocks": clocks, "gpu_launches": 2 * n_att * args.steps,
+        "roofline": {"kernel": "attn_hd64_kernel", "bound": "hbm", "achieved": att_gbs, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": att_gbs / hbm_peak, "peak_kind": f"of {peak_kind}",
+                     "traffic": ATTN_DRAM_BYTES_PER_OBS_NCU * B, "us_per_launch": att_ms * 1e3,
+                     "algorithmic_bytes_per_launch": ATTN_BYTES_PER_OBS_LAYER_STEP * B},
+        "kernels": {"attn_us": att_ms * 1e3, "qkv_rope_append_us": qkv_ms * 1e3,
+                    "qkv_tflops": 2.0 * B * c["S"] * n_rows * c["H"] / (qkv_ms * 1e-3) / 1e12,
+                    "kv_store_write_us": kvw_ms * 1e3, "kv_store_write_gbs": kvw_bytes / (kvw_ms * 1e-3) / 1e9},
+    }
+    if e2e:
+        line["e2e"] = {"value": B * world / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": e2e["h2d"],
+                       "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e_ms}
+    del store, x, op, wqkv
+    torch.cuda.empty_cache()
+    return line
 
-    if rank == 0:
-        hbm_peak, peak_kind = measured_peaks()
-        att_gbs = ATTN_BYTES_PER_OBS_LAYER_STEP * B / (att_ms * 1e-3) / 1e9
-        line = {
-            "metric": "action chunks/s (denoise loop)", "value": B * world * args.steps / (total_ms * 1e-3),
-            "unit": "chunks/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": total_ms / args.steps, "p50_chunk_latency_ms": p50_ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(B, world), "clocks": clocks,
-            "gpu_launches": 2 * n_att * args.steps,
-            "roofline": {"kernel": "attn_hd64_kernel", "bound": "hbm", "achieved": att_gbs, "peak": hbm_peak,
-                         "unit": "GB/s", "frac": att_gbs / hbm_peak, "peak_kind": f"of {peak_kind}",
-                         # dram__bytes_read + write of one ncu capture at batch 64 (25.11 MB for 64 observations),
-                         # scaled by the observations of a launch: pages are read once, traffic grows in proportion
-                         "traffic": ATTN_DRAM_BYTES_PER_OBS_NCU * B, "us_per_launch": att_ms * 1e3,
-                         "algorithmic_bytes_per_launch": ATTN_BYTES_PER_OBS_LAYER_STEP * B},
-            "kernels": {"attn_us": att_ms * 1e3, "qkv_rope_append_us": qkv_ms * 1e3,
-                        "qkv_tflops": 2.0 * B * c["S"] * n_rows * c["H"] / (qkv_ms * 1e-3) / 1e12,
-                        "kv_store_write_us": kvw_ms * 1e3, "kv_store_write_gbs": kvw_bytes / (kvw_ms * 1e-3) / 1e9},
-        }
-        if e2e:
-            line["e2e"] = {"value": B * world / (e2e_ms * 1e-3), "unit": "chunks/s",
-                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                           "ms_per_step": e2e_ms}
-        if world == 1 and not args.no_pi0_extra:
-            # the whole pi0-shaped loop at batch 64 (BASELINE configs[2]), as an extra figure
-            del store, x, op, wqkv
-            torch.cuda.empty_cache()
-            r = measure_pi0(torch, vb, dev, 64, 3, 2, 5)
-            line["pi0_loop_batch64"] = {
-                "chunks_per_s": 64 * 3 / (r["total_ms"] * 1e-3), "p50_chunk_latency_ms": r["p50_ms"],
-                "tflops": pi0_flops_per_chunk() * 64 * 3 / (r["total_ms"] * 1e-3) / 1e12,
-                "e2e_chunks_per_s": 64 / (r["e2e_ms"] * 1e-3), "h2d_bytes_per_step": r["h2d"],
-                "d2h_bytes_per_step": r["d2h"]}
-        if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle_ffi as orc
 
-            rng = np.random.default_rng(7)
-            orc.set_num_threads(min(os.cpu_count() or 1, 16))
-            t1 = oracle_chunk(orc, rng, 1)
-            n = max(1, min(16, int(args.cpu_seconds / max(t1, 1e-3))))
-            tn = oracle_chunk(orc, rng, n)
-            line["cpu_baseline"] = {"value": n / tn, "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
-                                    "sample": f"{n} observation(s) of the same workload (10 steps x 16 layers each)"}
-        print(json.dumps(line), flush=True)
+def cpu_baseline_record(args, workload):
+    """The CPU restatement of the benchmarked loop on this box's host cores: a bounded sample."""
+    from oracle import oracle_ffi as orc
+
+    orc.set_num_threads(min(os.cpu_count() or 1, 16))
+    if workload == "smolvla_attn":
+        rng = np.random.default_rng(7)
+        t1 = oracle_chunk(orc, rng, 1)
+        n = max(1, min(16, int(args.cpu_seconds / max(t1, 1e-3))))
+        tn = oracle_chunk(orc, rng, n)
+        return {"value": n / tn, "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
+                "sample": f"{n} observation(s) of the same workload (10 steps x 16 layers each)"}
+    loop = OraclePolicyLoop(orc, workload, seed=7)
+    t1 = loop.run(1)[0]
+    n = max(1, min(8, int(args.cpu_seconds / max(t1, 1e-3))))
+    times = loop.run(n)
+    return {"value": n / sum(times), "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{n} observation(s) through the whole loop (all layers x 10 Euler steps, float32), after one "
+                      f"warm-up observation"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
+    ap.add_argument("--workload", default="pi0", choices=["pi0", "smolvla", "smolvla_attn", "ternary", "bitvla_lm"],
+                    help="pi0 (default): the whole pi0-shaped denoise loop, 1024 observations split over the GPUs "
+                         "(BASELINE configs[4]); smolvla: the SmolVLA-shaped loop; smolvla_attn: the isolated "
+                         "denoise-attention op (configs[1]); ternary / bitvla_lm: configs[3]")
+    ap.add_argument("--gemm-tiling", type=int, default=0,
+                    help="bf16 GEMM tiling inside the engine: 0 automatic, 1 128x256, 2 128x128, 3 CTA pairs, 4 128x64")
+    ap.add_argument("--ternary-only", default=None,
+                    help="ternary workload: run one case only, e.g. gate_up:4800 (for profiler captures)")
+    ap.add_argument("--pi0-obs", type=int, default=0, help="observations per GPU for the loop workloads (0: 1024 / N)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default run: skip the small-batch latencies and the configs[1] / configs[3] sub-records")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--int8-peak", action="store_true", help="measure the int8 tensor-core peak (cuBLASLt) and exit")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import vla_cpp_b200 as vb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    vb.lib()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if args.int8_peak:
+        if rank == 0:
+            print(json.dumps(measure_int8_peak(torch, dev)), flush=True)
+        return
     if world > 1:
-        dist.destroy_process_group()
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def finish(line):
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+
+    vb.set_gemm_tiling(args.gemm_tiling)
+    if args.workload == "ternary":
+        finish(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3), args.ternary_only) if rank == 0 else None)
+        return
+    if args.workload == "bitvla_lm":
+        finish(measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3)) if rank == 0 else None)
+        return
+    if args.workload == "smolvla_attn":
+        line = measure_smolvla_attn(torch, vb, dist, dev, args, rank, world, barrier, with_e2e=not args.no_e2e)
+        if line is not None and world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_record(args, "smolvla_attn")
+        finish(line)
+        return
+
+    line = measure_policy(torch, vb, dist, dev, args, rank, world, barrier)
+    if line is not None and world == 1:
+        if not args.no_extras:
+            line.update(small_batch_latency(torch, vb, dev, args.workload))
+            sub = argparse.Namespace(**vars(args))
+            sub.steps, sub.warmup = 5, 3
+            a = measure_smolvla_attn(torch, vb, dist, dev, sub, 0, 1, torch.cuda.synchronize, with_e2e=False)
+            line["smolvla_attn"] = {"config": a["config"], "chunks_per_s": a["value"], "ms_per_step": a["ms_per_step"],
+                                    "roofline": a["roofline"], "kernels": a["kernels"]}
+            t = measure_ternary(torch, vb, dev, 5, 3)
+            line["ternary"] = {k: t[k] for k in ("config", "roofline", "roofline_gemv", "shapes", "int8_peak_live",
+                                                 "reference_cuda") if k in t}
+            lm = measure_bitvla_lm(torch, vb, dev, 5, 3)
+            line["bitvla_lm"] = {k: lm[k] for k in ("config", "roofline", "cases", "reference_cuda") if k in lm}
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_record(args, args.workload)
+    finish(line)
 
 
 if __name__ == "__main__":

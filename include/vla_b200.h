@@ -224,6 +224,14 @@ VLAB200_API int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs
                                                 const float *x0_host, float *x_out_host, int32_t pos_base,
                                                 const int32_t *pad_ranges_host, void *stream);
 
+/* Measurement hook: launches ONE stage of expert layer `layer` `reps` times on the engine's own buffers, as
+ * vlab200_engine_denoise would (0 = fused RMSNorm+QKV+RoPE+append, 1 = attention, 2 = O-projection + residual,
+ * 3 = fused RMSNorm + gate/up + activation, 4 = down projection + residual), so that a caller can bracket one
+ * kernel with CUDA events.  Call vlab200_engine_denoise once before (it fills the RoPE tables and activations);
+ * the residual stream is left modified.  No counterpart in the reference. */
+VLAB200_API int32_t vlab200_engine_run_stage(vlab200_engine *e, int32_t layer, int32_t stage, int32_t n_obs,
+                                             int32_t reps, void *stream);
+
 /* Tiling of the bf16 GEMMs (the fused QKV projection, and inside the engine the O-projection, MLP,
  * embedding MLPs and action head):
  * 0 = chosen per call from the problem size (default), 1 = one CTA per 128 x 256 tile,

@@ -73,7 +73,7 @@ EXPORTS = [
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_denoise_attn_loop_static",
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
-    "vlab200_engine_denoise_host", "vlab200_set_gemm_tiling",
+    "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_set_gemm_tiling",
     "vlab200_act_quant", "vlab200_ternary_linear",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
@@ -458,6 +458,14 @@ class PolicyEngine:
             C.c_void_p(pad_ranges_host.data_ptr()) if pad_ranges_host is not None else None, _stream()),
             "vlab200_engine_denoise_host")
         return out_host
+
+
+    STAGES = {"qkv": 0, "attention": 1, "o_proj": 2, "gate_up": 3, "down": 4}
+
+    def run_stage(self, layer, stage, n_obs, reps=1):
+        """Measurement hook: `reps` launches of one stage of one expert layer (after a denoise call)."""
+        _check(lib().vlab200_engine_run_stage(C.c_void_p(self.h), layer, self.STAGES[stage], n_obs, reps, _stream()),
+               "vlab200_engine_run_stage")
 
 
 NQ_PLAIN, NQ_ADD, NQ_GATE_UP = 0, 1, 2

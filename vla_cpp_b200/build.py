@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvla_b200.so")
-SOURCES = ["host_common.cu", "ternary.cu", "qkv.cu", "attn.cu", "attn_flash.cu", "denoise.cu", "gemm.cu", "engine.cu", "bitvla_lm.cu", "node_ops.cu", "gguf.cu"]
+SOURCES = ["host_common.cu", "ternary.cu", "qkv.cu", "attn.cu", "attn_flash.cu", "denoise.cu", "gemm.cu", "engine.cu", "bitvla_lm.cu", "node_ops.cu", "gguf.cu", "vla_c_api.cu", "predict.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -20,7 +20,7 @@ def _newer(a, b):
 def build(force=False, verbose=False):
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    headers.append(os.path.join(HERE, "..", "include", "vla_b200.h"))
+    headers += [os.path.join(HERE, "..", "include", h) for h in ("vla_b200.h", "vla.h")]
     objs, procs = [], []
     for src in SOURCES:
         s = os.path.join(CSRC, src)

@@ -252,6 +252,74 @@ static vlab200_kv_store engine_store(const vlab200_engine *e, int n_obs_view) {
     return st;
 }
 
+
+// One expert layer = five launches (six on the few-row path).  Stages, in order:
+//   0 fused RMSNorm + Q/K/V projection + RoPE + KV append   1 attention   2 O-projection + residual
+//   3 fused RMSNorm + gate/up + activation                   4 down projection + residual
+constexpr int kLayerStages = 5;
+
+static int layer_stage(vlab200_engine *e, int l, int stage, int n_obs, const float *rs, const float *rx,
+                       const int32_t *pad_ranges, cudaStream_t cs) {
+    const vlab200_policy_config &c = e->c;
+    const int H = c.H, S = e->S, hd = c.head_dim, I = c.inter, half = hd / 2;
+    const int M = n_obs * S;
+    const bool self = e->is_self[l];
+    int rc;
+    // pages are laid out for max_obs observations per layer; the kernels walk st.n_obs
+    // observations from the store base, so hand them a one-layer view of the live ones
+    vlab200_kv_store live = engine_store(e, e->max_obs);
+    live.n_obs = n_obs;
+    const size_t layer_off = (size_t)l * e->max_obs * c.n_kv * e->cap * hd;
+    live.k_pages = e->k_pages.as<__nv_bfloat16>() + layer_off;
+    live.v_pages = e->v_pages.as<__nv_bfloat16>() + layer_off;
+    live.n_layers = 1;
+    switch (stage) {
+    case 0: {
+        const float *rope = self ? rs : rx;
+        const int qkv_n = (c.n_q + (self ? 2 * c.n_kv : 0)) * hd;
+        if (M <= kFewRows && qkv_n <= I) {
+            // Few rows: the fused kernel's 128 x 256 tiles leave most SMs idle (10 CTAs for one
+            // observation).  Project with the narrow-tile GEMM (RMS factor in its epilogue) into the
+            // MLP scratch buffer, which is free here, then rotate / split / append in one small kernel.
+            GemmParams p{};
+            p.M = M; p.N = qkv_n; p.K = H; p.epi = EPI_BIAS_ACT; p.act = ACT_NONE; p.use_rms = 1;
+            p.eps = c.rms_eps; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
+            if ((rc = dense_gemm(e->hb.p, H, e->wqkv[l].p, p, cs))) return rc;
+            return rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S, c.n_q,
+                              self ? c.n_kv : 0, c.n_kv, hd, e->cap, e->P, cs);
+        }
+        return vlab200_qkv_rope_append(&live, 0, e->hb.p, 0, nullptr, e->wqkv[l].p, rope, rope + (size_t)S * half,
+                                       c.rms_eps, S, H, c.n_q, self ? 1 : 0, e->q.p, cs);
+    }
+    case 1: {
+        const int kv_len = self ? e->P + S : e->P;
+        const int mode = self ? (c.model == 0 ? 1 : 2) : 0;
+        return vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs);
+    }
+    case 2: {
+        GemmParams p{};
+        p.M = M; p.N = H; p.K = e->qf; p.epi = EPI_RESIDUAL;
+        p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
+        return dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs);
+    }
+    case 3: {
+        GemmParams p{};
+        p.M = M; p.N = 2 * I; p.K = H; p.epi = EPI_GATED; p.use_rms = 1; p.eps = c.rms_eps;
+        p.act = c.model == 0 ? ACT_GELU_TANH : ACT_SILU;
+        p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = I;
+        return dense_gemm(e->hb.p, H, e->wgu[l].p, p, cs);
+    }
+    case 4: {
+        GemmParams p{};
+        p.M = M; p.N = H; p.K = I; p.epi = EPI_RESIDUAL;
+        p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
+        return dense_gemm(e->g.p, I, e->wdown[l].p, p, cs);
+    }
+    default:
+        return VLAB200_ERR_ARG;
+    }
+}
+
 }  // namespace vb
 
 extern "C" {
@@ -333,7 +401,7 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     if (e->c.model == 0 && !state) return VLAB200_ERR_ARG;
     const vlab200_policy_config &c = e->c;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    const int H = c.H, S = e->S, chunk = c.chunk, A = c.action_dim, hd = c.head_dim, I = c.inter;
+    const int H = c.H, S = e->S, chunk = c.chunk, A = c.action_dim, hd = c.head_dim;
     const int M = n_obs * S, Mc = n_obs * chunk;
     int rc;
     if (pos_base < 0) pos_base = e->P;
@@ -342,9 +410,6 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     if ((rc = vlab200_rope_table(rs, rs + (size_t)S * half, pos_base, S, hd, c.rope_base, cs))) return rc;
     if ((rc = vlab200_rope_table(rx, rx + (size_t)S * half, 0, S, hd, c.rope_base, cs))) return rc;
     VB_CUDA(cudaMemcpyAsync(e->x.p, x0, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
-    // the KV pages are laid out for max_obs observations; the kernels index pages by observation
-    // within a layer, so the view must keep the layer stride of the full store
-    vlab200_kv_store st = vb::engine_store(e, e->max_obs);
     const float dt = -1.0f / (float)c.steps;
     for (int step = 0; step < c.steps; ++step) {
         vb::action_in_kernel<<<dim3((Mc + vb::AIN_ROWS - 1) / vb::AIN_ROWS, (H + 255) / 256), 256, 0, cs>>>(
@@ -366,57 +431,9 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
             p.ld_out = H; p.rows_in = chunk; p.rows_out = S; p.row_off = S - chunk;
             if ((rc = vb::dense_gemm(e->m1.p, H, e->w_at2.p, p, cs))) return rc;
         }
-        for (int l = 0; l < c.n_layers; ++l) {
-            const bool self = e->is_self[l];
-            // pages are laid out for max_obs observations per layer; the kernels walk st.n_obs
-            // observations from the store base, so hand them a one-layer view of the live ones
-            vlab200_kv_store live = st;
-            live.n_obs = n_obs;
-            const size_t layer_off = (size_t)l * e->max_obs * c.n_kv * e->cap * hd;
-            live.k_pages = e->k_pages.as<__nv_bfloat16>() + layer_off;
-            live.v_pages = e->v_pages.as<__nv_bfloat16>() + layer_off;
-            live.n_layers = 1;
-            const float *rope = self ? rs : rx;
-            const int qkv_n = (c.n_q + (self ? 2 * c.n_kv : 0)) * hd;
-            if (M <= vb::kFewRows && qkv_n <= I) {
-                // Few rows: the fused kernel's 128 x 256 tiles leave most SMs idle (10 CTAs for one
-                // observation).  Project with the narrow-tile GEMM (RMS factor in its epilogue) into the
-                // MLP scratch buffer, which is free here, then rotate / split / append in one small kernel.
-                vb::GemmParams p{};
-                p.M = M; p.N = qkv_n; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 1;
-                p.eps = c.rms_eps; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
-                if ((rc = vb::dense_gemm(e->hb.p, H, e->wqkv[l].p, p, cs))) return rc;
-                if ((rc = vb::rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S,
-                                         c.n_q, self ? c.n_kv : 0, c.n_kv, hd, e->cap, e->P, cs)))
-                    return rc;
-            } else if ((rc = vlab200_qkv_rope_append(&live, 0, e->hb.p, 0, nullptr, e->wqkv[l].p, rope,
-                                                     rope + (size_t)S * half, c.rms_eps, S, H, c.n_q, self ? 1 : 0,
-                                                     e->q.p, cs))) {
-                return rc;
-            }
-            const int kv_len = self ? e->P + S : e->P;
-            const int mode = self ? (c.model == 0 ? 1 : 2) : 0;
-            if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs))) return rc;
-            {
-                vb::GemmParams p{};
-                p.M = M; p.N = H; p.K = e->qf; p.epi = vb::EPI_RESIDUAL;
-                p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
-                if ((rc = vb::dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs))) return rc;
-            }
-            {
-                vb::GemmParams p{};
-                p.M = M; p.N = 2 * I; p.K = H; p.epi = vb::EPI_GATED; p.use_rms = 1; p.eps = c.rms_eps;
-                p.act = c.model == 0 ? vb::ACT_GELU_TANH : vb::ACT_SILU;
-                p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = I;
-                if ((rc = vb::dense_gemm(e->hb.p, H, e->wgu[l].p, p, cs))) return rc;
-            }
-            {
-                vb::GemmParams p{};
-                p.M = M; p.N = H; p.K = I; p.epi = vb::EPI_RESIDUAL;
-                p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
-                if ((rc = vb::dense_gemm(e->g.p, I, e->wdown[l].p, p, cs))) return rc;
-            }
-        }
+        for (int l = 0; l < c.n_layers; ++l)
+            for (int stage = 0; stage < vb::kLayerStages; ++stage)
+                if ((rc = vb::layer_stage(e, l, stage, n_obs, rs, rx, pad_ranges, cs))) return rc;
         {   // v = W_aout (rms(h) * w_out) + b_aout over every suffix row, then the Euler update on the action rows
             vb::GemmParams p{};
             p.M = M; p.N = A; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 1; p.eps = c.rms_eps;
@@ -448,6 +465,20 @@ int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const floa
     int rc = vlab200_engine_denoise(e, n_obs, state_host ? s_dev : nullptr, x_dev, x_dev, pos_base, pad_dev, cs);
     if (rc) return rc;
     VB_CUDA(cudaMemcpyAsync(x_out_host, x_dev, xb, cudaMemcpyDeviceToHost, cs));
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engine_run_stage(vlab200_engine *e, int32_t layer, int32_t stage, int32_t n_obs, int32_t reps,
+                                 void *stream) {
+    if (!e || layer < 0 || layer >= e->c.n_layers || stage < 0 || stage >= vb::kLayerStages || n_obs <= 0 ||
+        n_obs > e->max_obs || reps <= 0)
+        return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const float *rs = e->rope_self.as<float>(), *rx = e->rope_cross.as<float>();
+    for (int i = 0; i < reps; ++i) {
+        int rc = vb::layer_stage(e, layer, stage, n_obs, rs, rx, nullptr, cs);
+        if (rc) return rc;
+    }
     return VLAB200_OK;
 }
 
