@@ -43,6 +43,13 @@ VLAB200_API const char *vlab200_last_error(void);
  * failure; 101..104 = a bounded wait inside a kernel ran out).  reset != 0 clears it. */
 VLAB200_API int32_t vlab200_device_status(int32_t *out, int32_t reset);
 
+/* Self-test of the kernels' failure path: one small kernel whose warps wait, with a budget of
+ * `budget_cycles` GPU clock cycles (at most 1e8, i.e. well under a second), on a hardware barrier that
+ * nothing ever signals.  The wait gives up, the kernel returns normally, *gave_up is 1 and the device
+ * status word reads 104 until it is reset; the context stays usable.  Synchronises `stream`.
+ * No counterpart in the reference. */
+VLAB200_API int32_t vlab200_selftest_bounded_wait(int64_t budget_cycles, int32_t *gave_up, void *stream);
+
 /* ------------------------------------------------- prefix-KV store, QKV+RoPE, attention */
 
 /* bf16 K/V pages, written once per observation for the prefix and appended per denoise

@@ -68,10 +68,23 @@ def time_emb():
     np.savez_compressed(os.path.join(HERE, "time_emb.npz"), **out)
 
 
+def vla_h_layout(ref):
+    """sizeof / offsetof of the reference's public C structs (its include/vla.h), as printed by tests/c/vla_h_layout.c."""
+    import tempfile
+
+    src = os.path.join(os.path.dirname(HERE), "c", "vla_h_layout.c")
+    with tempfile.TemporaryDirectory() as d:
+        exe = os.path.join(d, "layout")
+        subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ref, "include"), src, "-o", exe], check=True)
+        txt = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
+    open(os.path.join(HERE, "vla_h_layout.txt"), "w").write(txt)
+
+
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path of the vla.cpp source tree>")
     ref = sys.argv[1]
     ladder(ref)
     time_emb()
+    vla_h_layout(ref)
     print("golden fixtures written to", HERE)

@@ -27,6 +27,12 @@ def declared_symbols():
     return names
 
 
+def declared_model_api_symbols():
+    """The seven functions of include/vla.h (ABI v1)."""
+    text = open(os.path.join(ROOT, "include", "vla.h")).read()
+    return re.findall(r"VLA_API\s+[\w\s\*]+?\b(\w+)\s*\(", text)
+
+
 def test_header_and_binding_list_agree(cuda_lib):
     from vla_cpp_b200 import api
 
@@ -36,6 +42,15 @@ def test_header_and_binding_list_agree(cuda_lib):
 def test_every_declared_symbol_is_exported(cuda_lib):
     for name in declared_symbols():
         assert hasattr(cuda_lib, name), name
+
+
+def test_model_level_abi_is_exported(cuda_lib):
+    names = declared_model_api_symbols()
+    assert sorted(names) == sorted(["vla_abi_version", "vla_model_load", "vla_model_free", "vla_model_config",
+                                    "vla_predict", "vla_free_actions", "vla_last_stats"])
+    for name in names:
+        assert hasattr(cuda_lib, name), name
+    assert cuda_lib.vla_abi_version() == 1
 
 
 def test_abi_version(cuda_lib):

@@ -82,3 +82,23 @@ def test_engine_loop_is_deterministic(oracle, tiling):
         vb.set_gemm_tiling(0)
     for o in outs[1:]:
         assert np.array_equal(o, outs[0])
+
+
+def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable(oracle):
+    """Every mbarrier wait in the library has a cycle budget.  The self-test kernel waits (with a budget of 1e5
+    cycles, ~50 us) on a barrier that nothing signals: the wait must give up, the kernel must return through its
+    common exit, the status word must read 104 (DEV_TIMEOUT_MISC) until reset, and the next ordinary kernel must
+    run and be correct.  Nothing hangs or faults by construction: the wait is bounded."""
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    assert vb.device_status() == 0
+    assert vb.selftest_bounded_wait(100000) is True
+    assert vb.device_status(reset=False) == 104
+    assert vb.device_status(reset=True) == 104
+    assert vb.device_status() == 0
+    x = torch.randn((4, 256), device="cuda").to(torch.bfloat16)
+    q, s = vb.act_quant(x)
+    rq, rs = oracle.act_quant(x.float().cpu().numpy())
+    assert np.array_equal(q.cpu().numpy(), rq) and np.array_equal(s.cpu().numpy(), rs)
+    assert vb.device_status() == 0

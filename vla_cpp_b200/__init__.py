@@ -29,6 +29,7 @@ from .api import (  # noqa: F401
     node_unary,
     qkv_rope_append,
     rope_table,
+    selftest_bounded_wait,
     set_gemm_tiling,
     ternary_linear,
 )

@@ -67,7 +67,7 @@ def lib():
 
 # every symbol include/vla_b200.h declares
 EXPORTS = [
-    "vlab200_abi_version", "vlab200_last_error", "vlab200_device_status",
+    "vlab200_abi_version", "vlab200_last_error", "vlab200_device_status", "vlab200_selftest_bounded_wait",
     "vlab200_kv_store_bytes", "vlab200_kv_store_write", "vlab200_rope_table", "vlab200_fold_norm_weight",
     "vlab200_qkv_rope_append",
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
@@ -113,6 +113,14 @@ def device_status(reset=True):
     out = C.c_int32(0)
     _check(lib().vlab200_device_status(C.byref(out), int(reset)), "vlab200_device_status")
     return out.value
+
+
+def selftest_bounded_wait(budget_cycles=100000):
+    """Runs the kernel whose waits can never be satisfied; True when they gave up within the budget."""
+    out = C.c_int32(0)
+    _check(lib().vlab200_selftest_bounded_wait(C.c_int64(budget_cycles), C.byref(out), _stream()),
+           "vlab200_selftest_bounded_wait")
+    return bool(out.value)
 
 
 def act_quant(x, q=None, scales=None):

@@ -1,4 +1,5 @@
 #include "host_common.h"
+#include "tc5.cuh"
 
 #include <cstdarg>
 #include <cstring>
@@ -113,7 +114,49 @@ int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const vo
 
 }  // namespace vb
 
+namespace vb {
+
+// Self-test of the bounded wait every kernel of this library relies on: two warps wait on an mbarrier that
+// nobody arrives at.  The first to exhaust the budget raises the CTA's abort flag and records
+// DEV_TIMEOUT_MISC; the other leaves through the flag; both reach the common exit.
+__global__ void bounded_wait_selftest_kernel(int *status, long long budget, int *out) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+    }
+    fence_barrier_init();
+    __syncthreads();
+    WaitCtx w{&abort_flag, status, budget};
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(&bar, 0, w, DEV_TIMEOUT_MISC);
+    __syncthreads();  // the common exit of every role
+    if ((threadIdx.x & 31) == 0) out[threadIdx.x >> 5] = ok ? 0 : 1;
+    if (threadIdx.x == 0) out[2] = abort_flag;
+}
+
+}  // namespace vb
+
 extern "C" {
+
+int32_t vlab200_selftest_bounded_wait(int64_t budget_cycles, int32_t *gave_up, void *stream) {
+    if (!gave_up || budget_cycles <= 0 || budget_cycles > 100000000) return VLAB200_ERR_ARG;
+    int *status = vb::device_status_ptr();
+    if (!status) return vb::cuda_fail(cudaGetLastError(), "device_status_ptr");
+    vb::DevBuf out;
+    int rc = out.alloc(3 * sizeof(int));
+    if (rc) return rc;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    VB_CUDA(cudaMemsetAsync(out.p, 0xff, 3 * sizeof(int), cs));
+    vb::bounded_wait_selftest_kernel<<<1, 64, 0, cs>>>(status, (long long)budget_cycles, out.as<int>());
+    VB_CUDA(cudaGetLastError());
+    int h[3] = {-1, -1, -1};
+    VB_CUDA(cudaMemcpyAsync(h, out.p, sizeof h, cudaMemcpyDeviceToHost, cs));
+    VB_CUDA(cudaStreamSynchronize(cs));
+    *gave_up = (h[0] == 1 && h[1] == 1 && h[2] == 1) ? 1 : 0;
+    return VLAB200_OK;
+}
 
 const char *vlab200_last_error(void) { return vb::g_last_error; }
 

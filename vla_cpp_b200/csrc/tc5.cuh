@@ -58,6 +58,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 struct WaitCtx {
     volatile int *abort_flag;
     int *status;
+    long long budget = kWaitCycles;  // clock64 cycles a wait may take before it gives up
 };
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (*w.abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > w.budget) {
                 *w.abort_flag = 1;
                 atomicCAS(w.status, 0, code);
                 return false;
@@ -86,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (*w.abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > w.budget) {
                 *w.abort_flag = 1;
                 atomicCAS(w.status, 0, code);
                 return false;
@@ -234,7 +235,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity
         if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (*w.abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > w.budget) {
                 *w.abort_flag = 1;
                 atomicCAS(w.status, 0, code);
                 return false;
