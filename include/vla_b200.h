@@ -270,6 +270,17 @@ VLAB200_API int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_lad
                                            int32_t *acc_out, const float *s, const float *ws, int32_t ws_num,
                                            int32_t M, int32_t N, int32_t K, int32_t path, void *stream);
 
+/* Load-time ternarisation of a float weight matrix and packing into the ladder layout, on the device:
+ *   absmean = max(mean |W|, 1e-5);  w = clamp(round_half_even(W / absmean), -1, 1);  *scale_out = absmean;
+ *   packed_out = N*K/4 bytes in the layout vlab200_ternary_linear consumes.
+ * W: float32 [N][K] (device, 16-byte aligned), N % 16 == 0, K % 128 == 0; scratch: one double (device).
+ * A fused projection (gate|up, q|k|v) is packed one sub-matrix at a time: the pack is a sequence of
+ * independent 16-row runs of 4K bytes, so sub-matrix i starts at packed_out + rows_before * K / 4 and gets its
+ * own scale.  Replaces recover_ternary_and_scale + pack_ladder_int2 (src/models/bitvla.cpp:430-483; Python
+ * form scripts/convert_bitvla_to_gguf.py:95-152), which run on the host at load time. */
+VLAB200_API int32_t vlab200_ternarize_pack(const float *W, int64_t N, int64_t K, uint8_t *packed_out,
+                                           float *scale_out, double *scratch, void *stream);
+
 /* ---- BitVLA language-model block: the callers either side of the ternary linear ----------
  * One BitNet transformer layer = RMSNorm -> act-quant -> ternary q/k/v -> NeoX RoPE ->
  * bidirectional GQA attention -> sub-norm -> act-quant -> ternary o -> residual -> RMSNorm ->

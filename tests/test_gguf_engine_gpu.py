@@ -136,6 +136,7 @@ def _write_bitvla_lm(path, cfg, layers, out_norm, drop=None):
         w.add_uint32("bitvla.lm." + k, v)
     w.add_float32("bitvla.lm.rope_theta", cfg["rope_base"])
     w.add_float32("bitvla.lm.rms_eps", cfg["rms_eps"])
+    w.add_uint32("bitvla.quant.int2_packed", 1)  # scripts/convert_bitvla_to_gguf.py:263
     names = dict(q="attn_q", k="attn_k", v="attn_v", o="attn_o", gate_up="ffn_gate_up", down="ffn_down")
     for l, lw in enumerate(layers):
         for k in ("attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm"):
@@ -181,3 +182,63 @@ def test_bitvla_lm_from_gguf_matches_direct_context(oracle, tmp_path):
     g = vb.Gguf(tmp_path / "nosidecar.gguf")
     with pytest.raises(vb.VlaB200Error, match="sidecar"):
         vb.BitvlaLM.from_gguf(g)
+
+
+def test_bitvla_lm_from_float_checkpoint_is_ternarised_and_packed_at_load(oracle, tmp_path):
+    """A checkpoint without "bitvla.quant.int2_packed" carries float matrices (ffn_gate and ffn_up separate); the
+    loader ternarises and ladder-packs them on the device, as the reference's load_bit does on the host
+    (src/models/bitvla.cpp:515-543,755-757,808-815).  Result: bit-identical to a context built from the oracle's
+    ternarisation + packing of the same matrices."""
+    require_cuda()
+    import vla_cpp_b200 as vb
+    from tests.gpu_util import bf16_bits
+    from tests.test_bitvla_lm_gpu import SMALL
+
+    cfg = SMALL
+    rng = np.random.default_rng(33)
+    hidden, ffn = cfg["hidden"], cfg["ffn"]
+    hq, hkv = cfg["n_q"] * cfg["head_dim"], cfg["n_kv"] * cfg["head_dim"]
+    F32 = gguf.GGMLQuantizationType.F32
+    w = gguf.GGUFWriter(str(tmp_path / "float.gguf"), "bitvla")
+    for k, v in (("hidden", hidden), ("layers", 2), ("q_heads", cfg["n_q"]), ("kv_heads", cfg["n_kv"]),
+                 ("head_dim", cfg["head_dim"]), ("inter", ffn)):
+        w.add_uint32("bitvla.lm." + k, v)
+    w.add_float32("bitvla.lm.rope_theta", cfg["rope_base"])
+    w.add_float32("bitvla.lm.rms_eps", cfg["rms_eps"])
+    layers = []
+    shapes = dict(attn_q=(hq, hidden), attn_k=(hkv, hidden), attn_v=(hkv, hidden), attn_o=(hidden, hq),
+                  ffn_gate=(ffn, hidden), ffn_up=(ffn, hidden), ffn_down=(hidden, ffn))
+    for l in range(2):
+        lw, mats = {}, {}
+        for k, n in (("attn_norm", hidden), ("attn_sub_norm", hq), ("ffn_norm", hidden), ("ffn_sub_norm", ffn)):
+            lw[k + "_w"] = oracle.bf16_round(rng.uniform(0.8, 1.2, n).astype(np.float32))
+            w.add_tensor(f"lm.blk.{l}.{k}.weight", lw[k + "_w"], raw_dtype=F32)
+        for name, shp in shapes.items():
+            mats[name] = (rng.standard_normal(shp) * rng.uniform(0.01, 0.05)).astype(np.float32)
+            w.add_tensor(f"lm.blk.{l}.{name}.weight", mats[name], raw_dtype=F32)
+        for short, name in (("q", "attn_q"), ("k", "attn_k"), ("v", "attn_v"), ("o", "attn_o"), ("down", "ffn_down")):
+            t, am = oracle.ternarize(mats[name])
+            lw[short + "_packed"], lw[short + "_ws"] = oracle.pack_ladder_int2(t), np.array([am], np.float32)
+        tg, ag = oracle.ternarize(mats["ffn_gate"])
+        tu, au = oracle.ternarize(mats["ffn_up"])
+        lw["gate_up_packed"] = oracle.pack_ladder_int2(np.concatenate([tg, tu]))
+        lw["gate_up_ws"] = np.array([ag, au], np.float32)
+        layers.append(lw)
+    out_norm = oracle.bf16_round(rng.uniform(0.8, 1.2, hidden).astype(np.float32))
+    w.add_tensor("lm.output_norm.weight", out_norm, raw_dtype=F32)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    from tests.test_bitvla_lm_gpu import to_dev_layer
+
+    g = vb.Gguf(tmp_path / "float.gguf")
+    lm_g = vb.BitvlaLM.from_gguf(g, max_seq=64, max_batch=1)
+    g.close()
+    lm_d = vb.BitvlaLM(hidden, cfg["n_q"], cfg["n_kv"], cfg["head_dim"], ffn, [to_dev_layer(oracle, lw) for lw in layers],
+                       bits_to_bf16_tensor(oracle.f32_to_bf16_bits(out_norm)), rope_base=cfg["rope_base"],
+                       rms_eps=cfg["rms_eps"], max_seq=64, max_batch=1)
+    x = bits_to_bf16_tensor(oracle.f32_to_bf16_bits(oracle.bf16_round(rng.standard_normal((29, hidden)).astype(np.float32))))
+    a, b = bf16_bits(lm_g.forward(x)), bf16_bits(lm_d.forward(x))
+    assert vb.device_status() == 0
+    assert np.array_equal(a, b)

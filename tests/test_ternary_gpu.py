@@ -255,3 +255,22 @@ def test_whole_matrix_at_4800_rows_against_oracle_and_reference(oracle, shape):
         diff = np.abs(bf16_bits(mine).astype(np.int32) - bf16_bits(theirs).astype(np.int32))
         assert diff.max() <= 1, f"max ulp distance {diff.max()}"
         assert (diff == 0).mean() > 0.95
+
+
+@pytest.mark.parametrize("n,k,scale", [(640, 2560, 0.02), (2560, 6912, 1.0), (16, 128, 1e-7), (13824, 2560, 0.05)])
+def test_ternarize_pack_on_device_matches_oracle(oracle, n, k, scale):
+    """Float weights -> absmean scale, ternary values and ladder bytes on the GPU, bit for bit what the
+    oracle's restatement of the reference's load-time code produces (and therefore what the reference's
+    Python packer produces: tests/golden/ladder_pack.npz pins the oracle)."""
+    require_cuda()
+    from vla_cpp_b200 import api
+
+    rng = np.random.default_rng(n + k)
+    w = (rng.standard_normal((n, k)) * scale).astype(np.float32)
+    w[0, :16] = [0.5 * scale * 0.7978845, -0.5 * scale * 0.7978845] * 8  # values near the rounding boundary
+    tern, absmean = oracle.ternarize(w)
+    want = oracle.pack_ladder_int2(tern)
+    packed, sc = api.ternarize_pack(to_dev(w))
+    assert api.device_status() == 0
+    assert sc.cpu().numpy()[0] == np.float32(absmean)
+    assert np.array_equal(packed.cpu().numpy(), want)

@@ -31,5 +31,6 @@ from .api import (  # noqa: F401
     rope_table,
     selftest_bounded_wait,
     set_gemm_tiling,
+    ternarize_pack,
     ternary_linear,
 )

@@ -74,7 +74,7 @@ EXPORTS = [
     "vlab200_denoise_attn_loop_static",
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
     "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_set_gemm_tiling",
-    "vlab200_act_quant", "vlab200_ternary_linear",
+    "vlab200_act_quant", "vlab200_ternary_linear", "vlab200_ternarize_pack",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
     "vlab200_gguf_open", "vlab200_gguf_close", "vlab200_gguf_n_tensors", "vlab200_gguf_tensor_name",
@@ -145,6 +145,20 @@ def ternary_linear(a, w_ladder, s, ws, n, out=None, acc_out=None, path=0):
     _check(lib().vlab200_ternary_linear(_ptr(a), _ptr(w_ladder), _ptr(out), _ptr(acc_out), _ptr(s), _ptr(ws),
                                         int(ws.numel()), m, n, k, int(path), _stream()), "vlab200_ternary_linear")
     return out
+
+
+def ternarize_pack(w):
+    """w: cuda float32 [N, K] -> (uint8 [N*K/4] ladder pack, float32 [1] absmean scale), computed on the device."""
+    import torch
+
+    assert w.is_cuda and w.dtype == torch.float32 and w.is_contiguous() and w.dim() == 2
+    n, k = w.shape
+    packed = torch.empty((n * k // 4,), dtype=torch.uint8, device=w.device)
+    scale = torch.empty((1,), dtype=torch.float32, device=w.device)
+    scratch = torch.empty((1,), dtype=torch.float64, device=w.device)
+    _check(lib().vlab200_ternarize_pack(_ptr(w), C.c_int64(n), C.c_int64(k), _ptr(packed), _ptr(scale), _ptr(scratch),
+                                        _stream()), "vlab200_ternarize_pack")
+    return packed, scale
 
 
 MASK_NONE, MASK_PI0, MASK_CAUSAL = 0, 1, 2

@@ -656,6 +656,48 @@ extern "C" vlab200_bitvla_lm *vlab200_bitvla_lm_create_from_gguf(const vlab200_g
         *ws = static_cast<const float *>(upload(tmp.data(), (size_t)n_scales * 4));
         if (ok) *packed = upload(vlab200_gguf_tensor_data(g, wn.c_str()), (size_t)nb);
     };
+    // A checkpoint written without "bitvla.quant.int2_packed" holds float matrices: they are ternarised and
+    // ladder-packed here, on the device, as the reference's load_bit / pack_and_upload_fused do on the host
+    // (src/models/bitvla.cpp:515-543,755-757,808-815).  `parts` are the row blocks of a fused projection.
+    uint32_t packed_flag = 0;
+    const bool packed_file = vlab200_gguf_meta_u32(g, "bitvla.quant.int2_packed", &packed_flag) == VLAB200_OK && packed_flag != 0;
+    vb::DevBuf stage_w, stage_acc;
+    auto bit_float = [&](const std::vector<std::string> &parts, int64_t N_each, int64_t K, const void **packed,
+                         const float **ws) {
+        if (!ok) return;
+        const size_t n_parts = parts.size();
+        c->owned.emplace_back();
+        vb::DevBuf &pk = c->owned.back();
+        c->owned.emplace_back();
+        vb::DevBuf &sc = c->owned.back();
+        if (pk.alloc((size_t)(N_each * K / 4) * n_parts) != VLAB200_OK || sc.alloc(n_parts * 4) != VLAB200_OK ||
+            (!stage_acc.p && stage_acc.alloc(8) != VLAB200_OK)) {
+            ok = false;
+            return;
+        }
+        for (size_t i = 0; ok && i < n_parts; ++i) {
+            const std::string wn = parts[i] + ".weight";
+            tmp.resize((size_t)(N_each * K));
+            if (vlab200_gguf_read_f32(g, wn.c_str(), tmp.data(), N_each * K, 0) != VLAB200_OK) {
+                vb::set_last_error("gguf: %s is missing or is not a %lld x %lld float tensor", wn.c_str(), (long long)N_each,
+                                   (long long)K);
+                ok = false;
+                return;
+            }
+            vb::DevBuf w_dev;
+            if (w_dev.alloc(tmp.size() * 4) != VLAB200_OK ||
+                cudaMemcpy(w_dev.p, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+                vlab200_ternarize_pack(w_dev.as<float>(), N_each, K, pk.as<uint8_t>() + (size_t)i * (size_t)(N_each * K / 4),
+                                       sc.as<float>() + i, stage_acc.as<double>(), nullptr) != VLAB200_OK ||
+                cudaStreamSynchronize(nullptr) != cudaSuccess) {
+                vb::cuda_fail(cudaGetLastError(), "ternarise + pack at load");
+                ok = false;
+                return;
+            }
+        }
+        *packed = pk.p;
+        *ws = sc.as<float>();
+    };
     const int64_t hq = (int64_t)n_q * hd, hkv = (int64_t)n_kv * hd;
     for (uint32_t l = 0; ok && l < n_layers; ++l) {
         const std::string b = "lm.blk." + std::to_string(l) + ".";
@@ -664,12 +706,21 @@ extern "C" vlab200_bitvla_lm *vlab200_bitvla_lm_create_from_gguf(const vlab200_g
         ly.attn_sub_norm_w = norm(b + "attn_sub_norm.weight", hidden);
         ly.ffn_norm_w = norm(b + "ffn_norm.weight", hidden);
         ly.ffn_sub_norm_w = norm(b + "ffn_sub_norm.weight", ffn);
-        bit(b + "attn_q", hq, hidden, 1, &ly.q_packed, &ly.q_ws);
-        bit(b + "attn_k", hkv, hidden, 1, &ly.k_packed, &ly.k_ws);
-        bit(b + "attn_v", hkv, hidden, 1, &ly.v_packed, &ly.v_ws);
-        bit(b + "attn_o", hidden, hq, 1, &ly.o_packed, &ly.o_ws);
-        bit(b + "ffn_gate_up", 2 * (int64_t)ffn, hidden, 2, &ly.gate_up_packed, &ly.gate_up_ws);
-        bit(b + "ffn_down", hidden, ffn, 1, &ly.down_packed, &ly.down_ws);
+        if (packed_file) {
+            bit(b + "attn_q", hq, hidden, 1, &ly.q_packed, &ly.q_ws);
+            bit(b + "attn_k", hkv, hidden, 1, &ly.k_packed, &ly.k_ws);
+            bit(b + "attn_v", hkv, hidden, 1, &ly.v_packed, &ly.v_ws);
+            bit(b + "attn_o", hidden, hq, 1, &ly.o_packed, &ly.o_ws);
+            bit(b + "ffn_gate_up", 2 * (int64_t)ffn, hidden, 2, &ly.gate_up_packed, &ly.gate_up_ws);
+            bit(b + "ffn_down", hidden, ffn, 1, &ly.down_packed, &ly.down_ws);
+        } else {
+            bit_float({b + "attn_q"}, hq, hidden, &ly.q_packed, &ly.q_ws);
+            bit_float({b + "attn_k"}, hkv, hidden, &ly.k_packed, &ly.k_ws);
+            bit_float({b + "attn_v"}, hkv, hidden, &ly.v_packed, &ly.v_ws);
+            bit_float({b + "attn_o"}, hidden, hq, &ly.o_packed, &ly.o_ws);
+            bit_float({b + "ffn_gate", b + "ffn_up"}, ffn, hidden, &ly.gate_up_packed, &ly.gate_up_ws);
+            bit_float({b + "ffn_down"}, hidden, ffn, &ly.down_packed, &ly.down_ws);
+        }
         if (ok && vlab200_bitvla_lm_set_layer(c, (int)l, &ly) != VLAB200_OK) ok = false;
     }
     if (ok) {

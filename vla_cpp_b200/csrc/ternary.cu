@@ -864,6 +864,70 @@ static int reference_ws_num(int N, int K) {
     return 1;
 }
 
+
+// ---- load-time ternarisation of a float weight matrix + ladder packing, on the device ---------------
+// sum_i |W[i]| in double: per-block tree sums, one atomicAdd(double) per block.  The total differs from the
+// reference's sequential host sum (src/models/bitvla.cpp:430-451) by rounding of the double only; the float
+// mean derived from it is the same value unless the double lands within ~1e-13 of a float rounding boundary.
+__global__ void __launch_bounds__(256) absum_kernel(const float *__restrict__ w, size_t n, double *__restrict__ total) {
+    __shared__ double part[8];
+    double acc = 0.0;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        acc += fabs((double)w[i]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < 8; ++i) t += part[i];
+        atomicAdd(total, t);
+    }
+}
+
+// One thread per 4-byte slot of the ladder layout (16 ternaries of one output row, consecutive k): the slot
+// index decomposes as in scripts/convert_bitvla_to_gguf.py:103-152 / src/models/bitvla.cpp:453-483; byte b holds
+// the values t = b + 4j at bits 2j..2j+1 encoded (w + 2) & 3; w = clamp(rne(W / absmean), -1, 1).
+__global__ void __launch_bounds__(256) ternarize_pack_kernel(const float *__restrict__ w, int64_t N, int64_t K,
+                                                             const double *__restrict__ total,
+                                                             uint32_t *__restrict__ packed, float *__restrict__ scale) {
+    const int64_t n_elems = N * K;
+    float mean = (float)(*total / (double)n_elems);
+    if (mean < 1e-5f) mean = 1e-5f;
+    const float inv = __fdiv_rn(1.0f, mean);
+    const int64_t n_slots = n_elems / 16;
+    for (int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; s < n_slots; s += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n_block = s / K;  // 16 rows x K columns = K slots per row block
+        int64_t r = s % K;
+        const int64_t k0 = r / 128;
+        r %= 128;
+        const int64_t major = r / 32;
+        r %= 32;
+        const int64_t y_half = r / 16;
+        r %= 16;
+        const int64_t sub_k = r / 8, y = r % 8;
+        const int64_t n = 16 * n_block + 8 * y_half + y, k_start = 128 * k0 + 32 * major + 16 * sub_k;
+        const float4 *src = reinterpret_cast<const float4 *>(w + n * K + k_start);  // K % 128 == 0: 64-byte aligned
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = __ldg(src + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float q = rintf(__fmul_rn(v[b + 4 * j], inv));
+                q = fminf(fmaxf(q, -1.0f), 1.0f);
+                word |= (uint32_t)(((int)q + 2) & 3) << (8 * b + 2 * j);
+            }
+        packed[s] = word;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale = mean;
+}
+
 }  // namespace vb
 
 extern "C" {
@@ -888,6 +952,23 @@ int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_ladder, void *o
 
 // Drop-in names of the reference (src/kernels/bitvla/bitnet_kernels.cu:31,76,118).  The
 // reference aborts the process on a shape it has no kernel for; these print and return.
+int32_t vlab200_ternarize_pack(const float *W, int64_t N, int64_t K, uint8_t *packed_out, float *scale_out,
+                               double *scratch, void *stream) {
+    if (!W || !packed_out || !scale_out || !scratch || N <= 0 || K <= 0) return VLAB200_ERR_ARG;
+    if (N % 16 || K % 128) return VLAB200_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(packed_out) & 3)) return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const size_t n = (size_t)N * (size_t)K;
+    int n_sm = vb::sm_count();
+    if (n_sm <= 0) n_sm = 148;
+    VB_CUDA(cudaMemsetAsync(scratch, 0, sizeof(double), cs));
+    vb::absum_kernel<<<n_sm * 8, 256, 0, cs>>>(W, n, scratch);
+    vb::ternarize_pack_kernel<<<n_sm * 8, 256, 0, cs>>>(W, N, K, scratch, reinterpret_cast<uint32_t *>(packed_out),
+                                                        scale_out);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
 void bitlinear_int8xint2(int8_t *input0, int8_t *input1, void *output0, float *s, float *ws, int M, int N, int K,
                          void *stream) {
     const int rc = vb::ternary_linear(input0, reinterpret_cast<const uint8_t *>(input1),
