@@ -68,6 +68,64 @@ def time_emb():
     np.savez_compressed(os.path.join(HERE, "time_emb.npz"), **out)
 
 
+class _Recorder:
+    """Stands in for gguf.GGUFWriter: records what the reference's converter functions would write."""
+
+    def __init__(self):
+        self.kv, self.tensors = [], []
+
+    def add_tensor(self, name, data, raw_shape=None, raw_dtype=None):
+        self.tensors.append([name, getattr(raw_dtype, "name", str(raw_dtype)),
+                             [int(x) for x in (raw_shape if raw_shape is not None else data.shape)]])
+
+    def __getattr__(self, attr):  # add_uint32 / add_float32 / add_float64 / add_string / add_bool
+        if not attr.startswith("add_"):
+            raise AttributeError(attr)
+        return lambda key, value: self.kv.append([key, attr[4:]])
+
+
+def gguf_names(ref):
+    """Tensor names, dtypes and metadata keys as the reference's converters write them, recorded by calling the
+    converters' own functions (scripts/gguf_blocks.py write_pi_kv / write_decoder_blocks, scripts/convert_pi0_to_gguf.py
+    and convert_smolvla_to_gguf.py PROJ_SUFFIXES / _add_kv, scripts/convert_bitvla_to_gguf.py _add_bit /
+    _add_bit_fused) on tiny tensors with a recording writer."""
+    import json
+
+    import torch
+
+    sys.path.insert(0, os.path.join(ref, "scripts"))
+    import convert_bitvla_to_gguf as cb
+    import convert_pi0_to_gguf as cp
+    import convert_smolvla_to_gguf as cs
+    import gguf_blocks as gb
+
+    vit = dict(vit_hidden=8, vit_layers=1, vit_heads=1, vit_inter=8, image_size=32, patch_size=16, n_img_tokens=4,
+               vit_ln_eps=1e-6, vit_pixel_shuffle=1)
+    base = dict(hidden=8, intermediate=8, n_q_heads=1, n_kv_heads=1, head_dim=8, n_layers=2, vocab_size=16, expert_h=8,
+                expert_inter=8, chunk_size=2, num_steps=2, n_action_steps=2, max_state_dim=8, max_action_dim=8,
+                real_state_dim=8, real_action_dim=8, tokenizer_max_length=4, min_period=4e-3, max_period=4.0,
+                rope_theta=10000.0, rms_norm_eps=1e-6, norm_eps=1e-8, paligemma_variant="gemma_2b",
+                action_expert_variant="gemma_300m", self_attn_every_n_layers=2, expert_width_multiplier=0.75, vit=vit)
+    tiny = lambda name: torch.zeros((2, 2), dtype=torch.bfloat16)
+    out = {}
+    r = _Recorder()
+    gb.write_pi_kv(r, cp.KV, base)
+    gb.write_decoder_blocks(r, tiny, "root", "aex", 2)
+    out["pi0"] = {"arch": cp.ARCH, "kv": r.kv, "decoder_blocks": r.tensors, "projections": list(cp.PROJ_SUFFIXES),
+                  "output_norm": "aex.output_norm.weight"}
+    r = _Recorder()
+    cs._add_kv(r, base)
+    gb.write_decoder_blocks(r, tiny, "root", "aex", 2)
+    out["smolvla"] = {"arch": cs.ARCH, "kv": r.kv, "decoder_blocks": r.tensors, "projections": list(cs.PROJ_SUFFIXES),
+                      "output_norm": "aex.output_norm.weight"}
+    r = _Recorder()
+    w = torch.randn(16, 128)
+    cb._add_bit(r, "lm.blk.0.attn_q", w)
+    cb._add_bit_fused(r, "lm.blk.0.ffn_gate_up", [w, w])
+    out["bitvla"] = {"packed": r.tensors, "packed_flag_key": "bitvla.quant.int2_packed"}
+    json.dump(out, open(os.path.join(HERE, "gguf_names.json"), "w"), indent=1)
+
+
 def vla_h_layout(ref):
     """sizeof / offsetof of the reference's public C structs (its include/vla.h), as printed by tests/c/vla_h_layout.c."""
     import tempfile
@@ -87,4 +145,5 @@ if __name__ == "__main__":
     ladder(ref)
     time_emb()
     vla_h_layout(ref)
+    gguf_names(ref)
     print("golden fixtures written to", HERE)

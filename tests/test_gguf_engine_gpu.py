@@ -20,10 +20,25 @@ def oracle():
     return oracle_ffi
 
 
+def _golden_names(arch):
+    """Tensor suffixes and metadata keys as the reference's converters write them (tests/golden/gguf_names.json,
+    recorded from scripts/gguf_blocks.py and scripts/convert_*_to_gguf.py by tests/golden/make_golden.py)."""
+    import json
+    import os
+
+    g = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gguf_names.json")))[arch]
+    suffixes = [n.split(".", 3)[3] for n, _, _ in g["decoder_blocks"] if n.startswith("aex.blk.0.")]
+    return suffixes, {k for k, _ in g["kv"]}, g["projections"], g["output_norm"]
+
+
 def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
     F32, BF16 = gguf.GGMLQuantizationType.F32, gguf.GGMLQuantizationType.BF16
     w = gguf.GGUFWriter(str(path), arch)
-    kv = lambda k: arch + "." + k
+    suffixes, golden_keys, golden_proj, golden_out_norm = _golden_names(arch)
+
+    def kv(k):
+        assert arch + "." + k in golden_keys, k  # only keys the reference converter writes
+        return arch + "." + k
     for key, val in (("n_layers", cfg["n_layers"]), ("expert_h", cfg["H"]), ("n_q_heads", cfg["n_q"]),
                      ("n_kv_heads", cfg["n_kv"]), ("head_dim", cfg["head_dim"]), ("expert_inter", cfg["inter"]),
                      ("chunk_size", cfg["chunk"]), ("num_steps", cfg["steps"]), ("max_state_dim", cfg["state_dim"]),
@@ -44,16 +59,18 @@ def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
             w.add_tensor(name, np.ascontiguousarray(a, dtype=np.float32), raw_dtype=F32)
 
     vec = lambda name, a: w.add_tensor(name, np.ascontiguousarray(a, dtype=np.float32), raw_dtype=F32)
-    names = dict(wq="attn_q", wk="attn_k", wv="attn_v", wo="attn_o", wgate="ffn_gate", wup="ffn_up", wdown="ffn_down")
+    ours = {"attn_norm.weight": "ln_raw_in", "attn_q.weight": "wq", "attn_k.weight": "wk", "attn_v.weight": "wv",
+            "attn_o.weight": "wo", "ffn_norm.weight": "ln_raw_post", "ffn_gate.weight": "wgate", "ffn_up.weight": "wup",
+            "ffn_down.weight": "wdown"}
+    assert sorted(ours) == sorted(suffixes)
     for l in range(cfg["n_layers"]):
-        vec(f"aex.blk.{l}.attn_norm.weight", per["ln_raw_in"][l])
-        vec(f"aex.blk.{l}.ffn_norm.weight", per["ln_raw_post"][l])
-        for k, n in names.items():
-            mat(f"aex.blk.{l}.{n}.weight", per[k][l])
-    vec("aex.output_norm.weight", glob["out_norm_raw"])
+        for suffix in suffixes:  # the converter's order
+            (vec if "norm" in suffix else mat)(f"aex.blk.{l}.{suffix}", per[ours[suffix]][l])
+    vec(golden_out_norm, glob["out_norm_raw"])
     heads = (("w_sp", "state_proj"),) if arch == "pi0" else ()
     for k, n in heads + (("w_ain", "action_in_proj"), ("w_at1", "action_time_mlp_in"),
                          ("w_at2", "action_time_mlp_out"), ("w_aout", "action_out_proj")):
+        assert n + ".weight" in golden_proj and n + ".bias" in golden_proj
         mat(n + ".weight", glob[k])
         vec(n + ".bias", glob["b_" + k[2:]])
     w.write_header_to_file()

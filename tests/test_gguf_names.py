@@ -1,0 +1,78 @@
+"""Checkpoint naming pinned to the reference's converters.  tests/golden/gguf_names.json was recorded by calling
+the converters' own functions (scripts/gguf_blocks.py, scripts/convert_{pi0,smolvla,bitvla}_to_gguf.py) with a
+recording writer (tests/golden/make_golden.py); here a file carrying exactly those metadata keys, with the types the
+converters use, must load through vla_model_load, and the loader must resolve its values.  Host only."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+gguf = pytest.importorskip("gguf")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = json.load(open(os.path.join(ROOT, "tests", "golden", "gguf_names.json")))
+
+VALUES = dict(hidden=2048, intermediate=16384, n_q_heads=8, n_kv_heads=1, head_dim=256, n_layers=18, expert_h=1024,
+              expert_inter=4096, chunk_size=50, num_steps=10, max_state_dim=32, max_action_dim=32, real_state_dim=8,
+              real_action_dim=7, tokenizer_max_length=48, self_attn_every_n_layers=2, n_img_tokens=64,
+              min_period=4e-3, max_period=4.0, rope_theta=10000.0, rms_norm_eps=1e-6, norm_eps=1e-8)
+
+
+def write_metadata_only(path, arch):
+    """Every key of the reference converter, written with the converter's type; values where the loader reads them."""
+    g = GOLDEN[arch]
+    w = gguf.GGUFWriter(str(path), g["arch"])
+    for key, kind in g["kv"]:
+        short = key.split(".", 1)[1]
+        if kind == "string":
+            w.add_string(key, "x")
+        elif kind == "bool":
+            w.add_bool(key, True)
+        else:
+            getattr(w, "add_" + kind)(key, VALUES.get(short, 1))
+    w.add_tensor("dummy", np.zeros(4, np.float32))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+@pytest.mark.parametrize("arch", ["pi0", "smolvla"])
+def test_a_file_with_the_converters_metadata_keys_loads(tmp_path, arch):
+    import vla_cpp_b200
+
+    L = vla_cpp_b200.lib()
+    L.vla_model_load.restype = C.c_void_p
+    L.vla_model_load.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p]
+    L.vla_model_free.argtypes = [C.c_void_p]
+    path = tmp_path / (arch + ".gguf")
+    write_metadata_only(path, arch)
+    m = L.vla_model_load(None, str(path).encode(), None)
+    assert m, L.vlab200_last_error()
+    L.vla_model_free(m)
+
+
+def test_expert_tensor_names_are_the_converters():
+    """The names the engine loader asks for are the ones write_decoder_blocks(..., "aex", n) and PROJ_SUFFIXES give."""
+    src = open(os.path.join(ROOT, "vla_cpp_b200", "csrc", "gguf.cu")).read()
+    for arch in ("pi0", "smolvla"):
+        g = GOLDEN[arch]
+        for name, _, _ in g["decoder_blocks"]:
+            suffix = name.split(".", 3)[3]  # aex.blk.N.<suffix>
+            assert name.startswith("aex.blk.") and '"' + suffix + '"' in src, name
+        for name in g["projections"] + [g["output_norm"]]:
+            if arch == "smolvla" and name.startswith("state_proj"):
+                continue  # SmolVLA's state token belongs to the prefix, not to the denoise loop
+            assert '"' + name + '"' in src, name
+
+
+def test_bitvla_pack_naming_is_the_converters():
+    src = open(os.path.join(ROOT, "vla_cpp_b200", "csrc", "bitvla_lm.cu")).read()
+    names = {n: (t, shape) for n, t, shape in GOLDEN["bitvla"]["packed"]}
+    assert names["lm.blk.0.attn_q.weight"] == ("I8", [16 * 128 // 4]) and names["lm.blk.0.attn_q.scale"] == ("F32", [1])
+    assert names["lm.blk.0.ffn_gate_up.weight"] == ("I8", [2 * 16 * 128 // 4])
+    assert names["lm.blk.0.ffn_gate_up.scale"] == ("F32", [2])
+    assert '"' + GOLDEN["bitvla"]["packed_flag_key"] + '"' in src
+    for piece in ('"attn_q"', '"ffn_gate_up"', '".weight"', '".scale"', '"lm.blk."'):
+        assert piece in src, piece
