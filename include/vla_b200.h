@@ -115,7 +115,9 @@ VLAB200_API int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t 
  * `layer`, query head h reading kv head h / (n_q / n_kv).  q: bf16 [n_obs][n_q][S][hd];
  * out: bf16 [n_obs][S][n_q*hd].  mask_mode: 0 = all rows < kv_len visible; 1 = pi0 rule
  * (suffix row 0 sees only suffix column 0, other rows every column; src/models/pi0.cpp:640-651);
- * 2 = causal over the suffix (src/models/smolvla.cpp:1655-1664).  pad_ranges (optional, int32
+ * 2 = causal over the suffix (src/models/smolvla.cpp:1655-1664); 3 = the last column is visible to the last
+ * query token only (SmolVLA prefill: the state token sees the prefix, nothing else sees the state token,
+ * src/models/smolvla.cpp:1637-1645).  pad_ranges (optional, int32
  * [n_obs][2]) masks prefix columns [lo, hi) per observation (padded language slots).
  * head_dim 64 with kv_len <= 256 and (n_q / n_kv) * S <= 256 runs a kernel that holds the whole
  * key range on chip; head_dim 64 / 128 / 256 of any length stream K and V in 64-key blocks with
@@ -230,6 +232,47 @@ VLAB200_API int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, con
 VLAB200_API int32_t vlab200_engine_denoise_host(vlab200_engine *e, int32_t n_obs, const float *state_host,
                                                 const float *x0_host, float *x_out_host, int32_t pos_base,
                                                 const int32_t *pad_ranges_host, void *stream);
+
+/* Reads the prefix rows of `layer` back as float32 [n_obs][prefix_len][n_kv][hd] (the layout
+ * vlab200_engine_set_prefix takes; cross-attention layers return the projected K' / V' they store). */
+VLAB200_API int32_t vlab200_engine_get_prefix(vlab200_engine *e, int32_t layer, int32_t obs0, int32_t n_obs,
+                                              float *K, float *V, void *stream);
+
+/* Rows of the prefix in use for the following set_prefix / prefill / denoise calls: 0 < prefix_len <= the
+ * prefix_len the engine was created with (which sized the pages).  pi0 requests differ in their number of
+ * language tokens, so the prefix length changes from call to call (src/models/pi0.cpp:527-528). */
+VLAB200_API int32_t vlab200_engine_set_prefix_len(vlab200_engine *e, int32_t prefix_len);
+
+/* ---- prefix producer: the VLM layers that fill the K/V pages -----------------------------------------
+ * Runs the backbone's transformer layers over the prefix embeddings of n_obs observations and writes every
+ * layer's rotated K and its V as bf16 rows [0, P) of the engine's pages for observations [obs0, obs0+n_obs)
+ * -- no float32 hand-off, no second copy.  SmolVLA cross-attention layers receive Wk K / Wv V
+ * (expert_cross_kv) in place.  The last layer stops after its K/V (its attention and MLP feed nothing).
+ * Layer = RMSNorm -> q,k,v -> NeoX RoPE -> masked GQA attention -> Wo + residual -> RMSNorm ->
+ * act(gate) * up -> Wdown + residual, act 1 = SiLU (SmolVLA, src/models/smolvla.cpp:778-813), 2 = tanh-GELU
+ * (Gemma, src/models/pi0.cpp:159-233).  Weights as for vlab200_engine_create: matrices bf16 [out][in], norm
+ * vectors float32 (Gemma norms with their +1), host arrays of n_layers device pointers; prepared copies are
+ * kept.  x_emb: float32 [n_obs][P][hidden] (device), already scaled as the model expects
+ * (smolvla.cpp:1362-1369, pi0.cpp:553-555).  pos_host: int32 [P] RoPE positions (HOST; NULL = 0..P-1).
+ * mask_mode 0 = every prefix token sees every other (pi0), 3 = the last token (state) is seen only by itself
+ * (smolvla.cpp:1637-1645); pad_ranges as in vlab200_attention.  P must equal the engine's prefix length in
+ * use.  Replaces the prefill loops of smolvla.cpp:1374-1391 and pi0.cpp:557-566. */
+typedef struct {
+    int32_t n_layers, hidden, n_q, n_kv, head_dim, inter, act;
+    float rms_eps, rope_base;
+} vlab200_prefill_config;
+typedef struct {
+    const void *const *wq, *const *wk, *const *wv, *const *wo, *const *wgate, *const *wup, *const *wdown;
+    const float *const *ln_in, *const *ln_post;
+} vlab200_prefill_weights;
+typedef struct vlab200_prefill vlab200_prefill;
+VLAB200_API vlab200_prefill *vlab200_prefill_create(const vlab200_prefill_config *cfg,
+                                                    const vlab200_prefill_weights *w, int32_t max_obs,
+                                                    int32_t max_prefix);
+VLAB200_API void vlab200_prefill_free(vlab200_prefill *p);
+VLAB200_API int32_t vlab200_prefill_run(vlab200_prefill *p, vlab200_engine *e, int32_t obs0, int32_t n_obs,
+                                        const float *x_emb, int32_t P, const int32_t *pos_host, int32_t mask_mode,
+                                        const int32_t *pad_ranges, void *stream);
 
 /* Measurement hook: launches ONE stage of expert layer `layer` `reps` times on the engine's own buffers, as
  * vlab200_engine_denoise would (0 = fused RMSNorm+QKV+RoPE+append, 1 = attention, 2 = O-projection + residual,

@@ -180,7 +180,7 @@ def time_emb(t, dim, min_p, max_p):
     return out
 
 
-MASK_NONE, MASK_PI0, MASK_SMOLVLA = 0, 1, 2
+MASK_NONE, MASK_PI0, MASK_SMOLVLA, MASK_PREFILL_STATE = 0, 1, 2, 3
 
 
 def attention(q, k, v, p, mode, pad_start=0, pad_end=0):
@@ -203,6 +203,37 @@ def qkv_rope(x, ln_w, wqkv, pos, n_q, n_kv, hd, eps, rope_base=10000.0, act_bf16
     lib().orc_qkv_rope(_p(x), _p(ln_w), _p(wqkv), _p(pos), s, h, n_q, n_kv, hd, C.c_float(eps),
                        C.c_float(rope_base), int(act_bf16), _p(q), _p(k), _p(v))
     return q, k, v
+
+
+def vlm_prefill(x, layers, cfg, pos=None, mask_mode=MASK_NONE, pad=(0, 0)):
+    """The backbone's layers over the prefix embeddings x [P][hidden] (float32); returns per layer the rotated K and
+    the V, each [P][n_kv][hd], that the denoise loop caches.  Layer body: src/models/smolvla.cpp:778-813
+    (build_vlm_layer, SiLU) and src/models/pi0.cpp:159-233 (build_gemma_layer, tanh-GELU); loops
+    smolvla.cpp:1374-1379, pi0.cpp:557-566.  layers: list of dicts ln_in, wqkv [(n_q+2n_kv)hd][H] (q, k, v rows),
+    wo, ln_post, wgate, wup, wdown.  cfg: n_q, n_kv, hd, rms_eps, rope_base, act ("silu" | "gelu")."""
+    h = _c(x, np.float32).copy()
+    P = h.shape[0]
+    pos = np.arange(P, dtype=np.int32) if pos is None else _c(pos, np.int32)
+    ks, vs = [], []
+    for li, lw in enumerate(layers):
+        q, k, v = qkv_rope(h, lw["ln_in"], lw["wqkv"], pos, cfg["n_q"], cfg["n_kv"], cfg["hd"], cfg["rms_eps"],
+                           cfg["rope_base"])
+        ks.append(k)
+        vs.append(v)
+        if li + 1 == len(layers):
+            break
+        att = attention(q, k, v, 0, mask_mode, pad[0], pad[1])
+        h = h + linear(att, lw["wo"])
+        xm = rmsnorm(h, lw["ln_post"], cfg["rms_eps"])
+        gate, up = linear(xm, lw["wgate"]), linear(xm, lw["wup"])
+        if cfg["act"] == "silu":
+            act = gate / (np.float32(1) + np.exp(-gate, dtype=np.float32))
+        else:
+            c0 = np.float32(0.79788456080286535588)
+            act = np.float32(0.5) * gate * (np.float32(1) + np.tanh(c0 * (gate + np.float32(0.044715) * gate * gate * gate),
+                                                                     dtype=np.float32))
+        h = h + linear((act * up).astype(np.float32), lw["wdown"])
+    return ks, vs
 
 
 class DenoiseCfg(C.Structure):

@@ -312,7 +312,14 @@ static inline float gelu_tanh_f(float x) {
  *   suffix column 0, rows >= 1 see all suffix columns.
  * mode 2 (SmolVLA, src/models/smolvla.cpp:1655-1664): prefix visible except
  *   [pad_start, pad_end); suffix causal. */
-static inline int mask_visible(int mode, int P, int row, int col, int pad_start, int pad_end) {
+/* mode 0: everything visible; 1: pi0 suffix rule (src/models/pi0.cpp:640-651); 2: causal suffix
+ * (src/models/smolvla.cpp:1655-1664); 3: SmolVLA prefill rule with P = 0 (smolvla.cpp:1637-1645): the last column
+ * (state token) is visible to the last row only, padded columns to nobody. */
+static inline int mask_visible(int mode, int P, int row, int col, int pad_start, int pad_end, int S, int Tkv) {
+    if (mode == 3) {
+        if (col >= pad_start && col < pad_end) return 0;
+        return col < Tkv - 1 || row == S - 1;
+    }
     if (col < P) return !(col >= pad_start && col < pad_end);
     const int sc = col - P;
     if (mode == 1) return row == 0 ? (sc == 0) : 1;
@@ -336,7 +343,7 @@ ORC_API void orc_attention(const float *q, const float *K, const float *V, int S
             float *sc = (float *)malloc(sizeof(float) * (size_t)Tkv);
             float mx = -INFINITY;
             for (int i = 0; i < Tkv; ++i) {
-                if (!mask_visible(mode, P, j, i, pad_start, pad_end)) {
+                if (!mask_visible(mode, P, j, i, pad_start, pad_end, S, Tkv)) {
                     sc[i] = -INFINITY;
                     continue;
                 }

@@ -8,6 +8,7 @@ call needs the built library and a B200.
 from .api import (  # noqa: F401
     LIB_PATH,
     MASK_CAUSAL,
+    MASK_LAST_PRIVATE,
     MASK_NONE,
     MASK_PI0,
     BitvlaLM,
@@ -15,6 +16,7 @@ from .api import (  # noqa: F401
     Gguf,
     KvStore,
     PolicyEngine,
+    Prefill,
     VlaB200Error,
     act_quant,
     attention,

@@ -38,6 +38,8 @@ def lib():
         L.vlab200_kv_store_bytes.restype = C.c_int64
         L.vlab200_engine_create.restype = C.c_void_p
         L.vlab200_engine_free.restype = None
+        L.vlab200_prefill_create.restype = C.c_void_p
+        L.vlab200_prefill_free.restype = None
         L.vlab200_bitvla_lm_init.restype = C.c_void_p
         L.vlab200_bitvla_lm_init.argtypes = [C.c_int32] * 6 + [C.c_float, C.c_float, C.c_int32, C.c_int32]
         L.vlab200_bitvla_lm_free.restype = None
@@ -73,7 +75,9 @@ EXPORTS = [
     "vlab200_attention", "vlab200_denoise_attn_loop", "vlab200_denoise_attn_loop_host",
     "vlab200_denoise_attn_loop_static",
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
-    "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_set_gemm_tiling",
+    "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_engine_set_prefix_len",
+    "vlab200_engine_get_prefix",
+    "vlab200_prefill_create", "vlab200_prefill_free", "vlab200_prefill_run", "vlab200_set_gemm_tiling",
     "vlab200_act_quant", "vlab200_ternary_linear", "vlab200_ternarize_pack",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
@@ -161,7 +165,7 @@ def ternarize_pack(w):
     return packed, scale
 
 
-MASK_NONE, MASK_PI0, MASK_CAUSAL = 0, 1, 2
+MASK_NONE, MASK_PI0, MASK_CAUSAL, MASK_LAST_PRIVATE = 0, 1, 2, 3
 
 
 class _KvStoreC(C.Structure):
@@ -482,12 +486,83 @@ class PolicyEngine:
         return out_host
 
 
+    def get_prefix(self, layer, n_kv, head_dim, n_obs=1, obs0=0):
+        """-> (K, V) cuda float32 [n_obs, prefix_len, n_kv, head_dim] read back from the pages."""
+        import torch
+
+        k = torch.empty((n_obs, self.prefix_len, n_kv, head_dim), dtype=torch.float32, device="cuda")
+        v = torch.empty_like(k)
+        _check(lib().vlab200_engine_get_prefix(C.c_void_p(self.h), layer, obs0, n_obs, _ptr(k), _ptr(v), _stream()),
+               "vlab200_engine_get_prefix")
+        return k, v
+
+    def set_prefix_len(self, prefix_len):
+        """Prefix rows in use from now on (<= the length the engine was created with)."""
+        _check(lib().vlab200_engine_set_prefix_len(C.c_void_p(self.h), int(prefix_len)), "vlab200_engine_set_prefix_len")
+        self.prefix_len = int(prefix_len)
+
     STAGES = {"qkv": 0, "attention": 1, "o_proj": 2, "gate_up": 3, "down": 4}
 
     def run_stage(self, layer, stage, n_obs, reps=1):
         """Measurement hook: `reps` launches of one stage of one expert layer (after a denoise call)."""
         _check(lib().vlab200_engine_run_stage(C.c_void_p(self.h), layer, self.STAGES[stage], n_obs, reps, _stream()),
                "vlab200_engine_run_stage")
+
+
+class _PrefillConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "hidden", "n_q", "n_kv", "head_dim", "inter", "act")] + [
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)]
+
+
+class _PrefillWeights(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_void_p)) for n in _PER_LAYER]
+
+
+class Prefill:
+    """The backbone's layers over the prefix embeddings, writing K/V straight into a PolicyEngine's pages.
+
+    cfg: dict with the vlab200_prefill_config fields (act: 1 SiLU, 2 tanh-GELU); weights: per-layer lists wq, wk,
+    wv, wo, wgate, wup, wdown (cuda bf16 [out, in]) and ln_in, ln_post (cuda float32)."""
+
+    def __init__(self, cfg, weights, max_obs, max_prefix):
+        import torch
+
+        c = _PrefillConfig(**{k: cfg[k] for k, _ in _PrefillConfig._fields_})
+        w = _PrefillWeights()
+        keep = []
+        for name in _PER_LAYER:
+            ts = [t.contiguous() for t in weights[name]]
+            want = torch.float32 if name.startswith("ln") else torch.bfloat16
+            assert all(t.is_cuda and t.dtype == want for t in ts), name
+            arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+            keep += [ts, arr]
+            setattr(w, name, C.cast(arr, C.POINTER(C.c_void_p)))
+        self.h = lib().vlab200_prefill_create(C.byref(c), C.byref(w), max_obs, max_prefix)
+        torch.cuda.synchronize()
+        del keep
+        if not self.h:
+            raise VlaB200Error(ERR_CUDA, "vlab200_prefill_create: " + lib().vlab200_last_error().decode())
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().vlab200_prefill_free(C.c_void_p(self.h))
+            self.h = None
+
+    def run(self, engine, x_emb, positions=None, mask_mode=MASK_NONE, pad_ranges=None, obs0=0):
+        """x_emb: cuda float32 [n_obs, P, hidden]; positions: host int32 array [P] or None (0..P-1)."""
+        import numpy as np
+        import torch
+
+        assert x_emb.is_cuda and x_emb.dtype == torch.float32 and x_emb.is_contiguous()
+        n_obs, P = x_emb.shape[0], x_emb.shape[1]
+        pos = None
+        if positions is not None:
+            pos = np.ascontiguousarray(positions, dtype=np.int32)
+            assert pos.size == P
+        _check(lib().vlab200_prefill_run(C.c_void_p(self.h), C.c_void_p(engine.h), obs0, n_obs, _ptr(x_emb), P,
+                                         pos.ctypes.data_as(C.c_void_p) if pos is not None else None, mask_mode,
+                                         _ptr(pad_ranges), _stream()), "vlab200_prefill_run")
+        torch.cuda.synchronize()  # pos (host memory) must outlive the copy enqueued on the stream
 
 
 NQ_PLAIN, NQ_ADD, NQ_GATE_UP = 0, 1, 2

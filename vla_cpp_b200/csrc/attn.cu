@@ -336,6 +336,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 int limit = n_suffix_cols;
                 if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
                 else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+                else if (p.mask_mode == 3) limit = tok == p.S - 1 ? n_suffix_cols : n_suffix_cols - 1;
                 int clean_end = p.prefix_len;
                 if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
                 const RowMask rm{p.prefix_len + limit, pad_lo, pad_hi, clean_end};
@@ -429,7 +430,7 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     if (!st || !st->k_pages || !st->v_pages || !q || !out) return VLAB200_ERR_ARG;
     if (layer < 0 || layer >= st->n_layers || S <= 0 || n_q <= 0 || st->n_kv <= 0 || n_q % st->n_kv)
         return VLAB200_ERR_ARG;
-    if (kv_len <= 0 || kv_len > st->cap || st->prefix_len > kv_len || mask_mode < 0 || mask_mode > 2)
+    if (kv_len <= 0 || kv_len > st->cap || st->prefix_len > kv_len || mask_mode < 0 || mask_mode > 3)
         return VLAB200_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (reinterpret_cast<uintptr_t>(st->k_pages) & 15) || (reinterpret_cast<uintptr_t>(st->v_pages) & 15))

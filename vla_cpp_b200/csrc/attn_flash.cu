@@ -227,6 +227,7 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             int limit = n_suffix_cols;
             if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
             else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+            else if (p.mask_mode == 3) limit = tok == p.S - 1 ? n_suffix_cols : n_suffix_cols - 1;
             const int jmax = p.prefix_len + limit;
             int clean_end = p.prefix_len;
             if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);
@@ -616,6 +617,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             int limit = n_suffix_cols;
             if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
             else if (p.mask_mode == 1) limit = tok == 0 ? min(1, n_suffix_cols) : n_suffix_cols;
+            else if (p.mask_mode == 3) limit = tok == p.S - 1 ? n_suffix_cols : n_suffix_cols - 1;
             const int jmax = p.prefix_len + limit;
             int clean_end = p.prefix_len;
             if (pad_hi > pad_lo) clean_end = min(clean_end, pad_lo);

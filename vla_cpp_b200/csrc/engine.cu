@@ -123,13 +123,28 @@ __global__ void euler_kernel(float *__restrict__ x, const float *__restrict__ v,
 }  // namespace vb
 
 namespace vb {
+
+// pages [n_obs][n_kv][cap][hd] rows [0, P) -> float32 [n_obs][P][n_kv][hd]
+__global__ void pages_to_f32_kernel(const __nv_bfloat16 *__restrict__ pages, float *__restrict__ out, int n_kv, int cap,
+                                    int hd, int P, size_t total) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(i % hd);
+        size_t r = i / hd;
+        const int kvh = (int)(r % n_kv);
+        r /= n_kv;
+        const int tok = (int)(r % P);
+        const size_t obs = r / P;
+        out[i] = __bfloat162float(pages[((obs * n_kv + kvh) * cap + tok) * hd + d]);
+    }
+}
+
 constexpr int kFewRows = 256;  // suffix rows (n_obs * S) up to which the QKV projection takes the narrow-tile path
 }
 
 // ------------------------------------------------------------------------ engine --
 struct vlab200_engine {
     vlab200_policy_config c;
-    int max_obs, P, S, cap, qf, kvf;
+    int max_obs, P, P_max, S, cap, qf, kvf;  // P: rows of the prefix in use (<= P_max, the rows the pages were sized for)
     std::vector<int> is_self;
     // prepared weights
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
@@ -348,6 +363,7 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
     e->c = c;
     e->max_obs = max_obs;
     e->P = prefix_len;
+    e->P_max = prefix_len;
     e->S = c.chunk + (c.model == 0 ? 1 : 0);
     e->cap = e->P + e->S;
     e->qf = c.n_q * c.head_dim;
@@ -376,7 +392,7 @@ int32_t vlab200_engine_set_prefix(vlab200_engine *e, int32_t layer, int32_t obs0
     // SmolVLA cross-attention layer: K' = Wk K_flat, V' = Wv V_flat once per observation
     // (src/models/smolvla.cpp:853-860), written head-major into the pages of this layer
     const size_t n = (size_t)n_obs * e->P * e->kvf;
-    __nv_bfloat16 *kb = e->tmp_bf.as<__nv_bfloat16>(), *vbuf = kb + (size_t)e->max_obs * e->P * e->kvf;
+    __nv_bfloat16 *kb = e->tmp_bf.as<__nv_bfloat16>(), *vbuf = kb + (size_t)e->max_obs * e->P_max * e->kvf;
     vb::f32_to_bf16_kernel<<<148 * 4, 256, 0, cs>>>(K, kb, n);
     vb::f32_to_bf16_kernel<<<148 * 4, 256, 0, cs>>>(V, vbuf, n);
     VB_CUDA(cudaGetLastError());
@@ -478,6 +494,214 @@ int32_t vlab200_engine_run_stage(vlab200_engine *e, int32_t layer, int32_t stage
     for (int i = 0; i < reps; ++i) {
         int rc = vb::layer_stage(e, layer, stage, n_obs, rs, rx, nullptr, cs);
         if (rc) return rc;
+    }
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engine_get_prefix(vlab200_engine *e, int32_t layer, int32_t obs0, int32_t n_obs, float *K, float *V,
+                                  void *stream) {
+    if (!e || !K || !V || layer < 0 || layer >= e->c.n_layers || obs0 < 0 || n_obs <= 0 || obs0 + n_obs > e->max_obs)
+        return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const size_t page_off = ((size_t)layer * e->max_obs + obs0) * e->c.n_kv * e->cap * e->c.head_dim;
+    const size_t total = (size_t)n_obs * e->P * e->kvf;
+    vb::pages_to_f32_kernel<<<148 * 4, 256, 0, cs>>>(e->k_pages.as<__nv_bfloat16>() + page_off, K, e->c.n_kv, e->cap,
+                                                     e->c.head_dim, e->P, total);
+    vb::pages_to_f32_kernel<<<148 * 4, 256, 0, cs>>>(e->v_pages.as<__nv_bfloat16>() + page_off, V, e->c.n_kv, e->cap,
+                                                     e->c.head_dim, e->P, total);
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engine_set_prefix_len(vlab200_engine *e, int32_t prefix_len) {
+    if (!e || prefix_len <= 0 || prefix_len > e->P_max) return VLAB200_ERR_ARG;
+    e->P = prefix_len;
+    return VLAB200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ prefix producer --
+// The VLM layers over the prefix tokens of an observation (image, language and, for SmolVLA, state
+// embeddings), written straight into the denoise engine's bf16 K/V pages: layer l's rotated K and its V
+// are what expert layer l reads for the whole denoise loop (src/models/smolvla.cpp:778-813,1374-1391;
+// src/models/pi0.cpp:159-233,557-566).  Same five stages as an expert layer with the prefix as the
+// "suffix" of an empty cache; SmolVLA's cross-attention layers get Wk K / Wv V (expert_cross_kv) in place.
+struct vlab200_prefill {
+    vlab200_prefill_config c;
+    int max_obs, max_prefix, qf, kvf;
+    std::vector<vb::DevBuf> wqkv, wo, wgu, wdown;
+    vb::DevBuf h, hb, qkv, q, att, g, rope, pos;
+};
+
+namespace vb {
+
+__global__ void embed_to_stream_kernel(const float *__restrict__ x, float *__restrict__ h, __nv_bfloat16 *__restrict__ hb,
+                                       size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        h[i] = v;
+        hb[i] = __float2bfloat16(v);
+    }
+}
+
+// cos / sin rows for explicit positions (the SmolVLA state token does not sit at its row index)
+__global__ void rope_table_pos_kernel(float *cos_t, float *sin_t, const int32_t *__restrict__ pos, int S, int hd, float base) {
+    const int half = hd >> 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= S * half) return;
+    const int t = i / half, d = i % half;
+    const float freq = powf(base, -2.0f * (float)d / (float)hd);
+    const float ang = (float)pos[t] * freq;
+    cos_t[i] = cosf(ang);
+    sin_t[i] = sinf(ang);
+}
+
+// pages [n_obs][n_kv][cap][hd] rows [0, P) -> token-major [n_obs * P][n_kv * hd]
+__global__ void pages_to_rows_kernel(const __nv_bfloat16 *__restrict__ pages, __nv_bfloat16 *__restrict__ rows, int n_kv,
+                                     int cap, int hd, int P, size_t total_vec) {
+    const int hv = hd / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const int v8 = (int)(i % hv);
+        size_t r = i / hv;
+        const int kvh = (int)(r % n_kv);
+        r /= n_kv;
+        const int tok = (int)(r % P);
+        const size_t obs = r / P;
+        const uint4 val = *reinterpret_cast<const uint4 *>(pages + ((obs * n_kv + kvh) * cap + tok) * hd + (size_t)v8 * 8);
+        *reinterpret_cast<uint4 *>(rows + ((obs * P + tok) * n_kv + kvh) * hd + (size_t)v8 * 8) = val;
+    }
+}
+
+}  // namespace vb
+
+extern "C" {
+
+vlab200_prefill *vlab200_prefill_create(const vlab200_prefill_config *cfg, const vlab200_prefill_weights *w,
+                                        int32_t max_obs, int32_t max_prefix) {
+    if (!cfg || !w || max_obs <= 0 || max_prefix <= 0) {
+        vb::set_last_error("vlab200_prefill_create: null configuration / weights, or max_obs / max_prefix <= 0");
+        return nullptr;
+    }
+    const vlab200_prefill_config &c = *cfg;
+    if (c.n_layers <= 0 || c.hidden <= 0 || c.hidden % 8 || c.n_q <= 0 || c.n_kv <= 0 || c.n_q % c.n_kv || c.inter <= 0 ||
+        (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) || (c.act != vb::ACT_SILU && c.act != vb::ACT_GELU_TANH)) {
+        vb::set_last_error("vlab200_prefill_create: bad configuration");
+        return nullptr;
+    }
+    auto *p = new (std::nothrow) vlab200_prefill();
+    if (!p) return nullptr;
+    p->c = c;
+    p->max_obs = max_obs;
+    p->max_prefix = max_prefix;
+    p->qf = c.n_q * c.head_dim;
+    p->kvf = c.n_kv * c.head_dim;
+    const int L = c.n_layers, H = c.hidden, I = c.inter, qf = p->qf, kvf = p->kvf;
+    p->wqkv.resize(L); p->wo.resize(L); p->wgu.resize(L); p->wdown.resize(L);
+    int rc = VLAB200_OK;
+    for (int l = 0; l < L && !rc; ++l) {
+        // same prepared forms as the engine: norm weights folded in, q/k/v concatenated, gate/up interleaved
+        if ((rc = p->wqkv[l].alloc((size_t)(qf + 2 * kvf) * H * 2))) break;
+        auto *dst = p->wqkv[l].as<__nv_bfloat16>();
+        if ((rc = vb::fold_rows(w->wq[l], w->ln_in[l], dst, qf, H, 1, 0))) break;
+        if ((rc = vb::fold_rows(w->wk[l], w->ln_in[l], dst + (size_t)qf * H, kvf, H, 1, 0))) break;
+        if ((rc = vb::fold_rows(w->wv[l], w->ln_in[l], dst + (size_t)(qf + kvf) * H, kvf, H, 1, 0))) break;
+        if (l + 1 == L) break;  // the last layer only has to produce K and V
+        if ((rc = vb::copy_dev(p->wo[l], w->wo[l], (size_t)H * qf * 2))) break;
+        if ((rc = p->wgu[l].alloc((size_t)2 * I * H * 2))) break;
+        if ((rc = vb::fold_rows(w->wgate[l], w->ln_post[l], p->wgu[l].p, I, H, 2, 0))) break;
+        if ((rc = vb::fold_rows(w->wup[l], w->ln_post[l], p->wgu[l].p, I, H, 2, 1))) break;
+        if ((rc = vb::copy_dev(p->wdown[l], w->wdown[l], (size_t)H * I * 2))) break;
+    }
+    const size_t M = (size_t)max_obs * max_prefix;
+    if (!rc) rc = p->h.alloc(M * H * 4);
+    if (!rc) rc = p->hb.alloc(M * H * 2);
+    if (!rc) rc = p->qkv.alloc(M * (size_t)(qf + 2 * kvf) * 2);
+    if (!rc) rc = p->q.alloc(M * qf * 2);
+    if (!rc) rc = p->att.alloc(M * qf * 2);
+    if (!rc) rc = p->g.alloc(M * I * 2);
+    if (!rc) rc = p->rope.alloc((size_t)2 * max_prefix * (c.head_dim / 2) * 4);
+    if (!rc) rc = p->pos.alloc((size_t)max_prefix * 4);
+    if (!rc && cudaDeviceSynchronize() != cudaSuccess) rc = vb::cuda_fail(cudaGetLastError(), "vlab200_prefill_create");
+    if (rc) {
+        if (rc != VLAB200_ERR_CUDA) vb::set_last_error("vlab200_prefill_create: failed with status %d", rc);
+        delete p;
+        return nullptr;
+    }
+    return p;
+}
+
+void vlab200_prefill_free(vlab200_prefill *p) { delete p; }
+
+int32_t vlab200_prefill_run(vlab200_prefill *p, vlab200_engine *e, int32_t obs0, int32_t n_obs, const float *x_emb,
+                            int32_t P, const int32_t *pos_host, int32_t mask_mode, const int32_t *pad_ranges,
+                            void *stream) {
+    if (!p || !e || !x_emb || obs0 < 0 || n_obs <= 0 || n_obs > p->max_obs || obs0 + n_obs > e->max_obs || P <= 0 ||
+        P > p->max_prefix || P != e->P)
+        return VLAB200_ERR_ARG;
+    const vlab200_prefill_config &c = p->c;
+    if (c.n_layers != e->c.n_layers || c.n_kv != e->c.n_kv || c.head_dim != e->c.head_dim) {
+        vb::set_last_error("vlab200_prefill_run: the prefill and the engine disagree on layers / kv heads / head_dim");
+        return VLAB200_ERR_ARG;
+    }
+    if (mask_mode != 0 && mask_mode != 3) return VLAB200_ERR_ARG;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const int H = c.hidden, I = c.inter, hd = c.head_dim, qf = p->qf, kvf = p->kvf, half = hd / 2;
+    const int M = n_obs * P, qkv_n = qf + 2 * kvf;
+    int rc;
+    float *cos_t = p->rope.as<float>(), *sin_t = cos_t + (size_t)P * half;
+    if (pos_host) {
+        VB_CUDA(cudaMemcpyAsync(p->pos.p, pos_host, (size_t)P * 4, cudaMemcpyHostToDevice, cs));
+        vb::rope_table_pos_kernel<<<(P * half + 127) / 128, 128, 0, cs>>>(cos_t, sin_t, p->pos.as<int32_t>(), P, hd, c.rope_base);
+        VB_CUDA(cudaGetLastError());
+    } else if ((rc = vlab200_rope_table(cos_t, sin_t, 0, P, hd, c.rope_base, cs))) {
+        return rc;
+    }
+    vb::embed_to_stream_kernel<<<148 * 4, 256, 0, cs>>>(x_emb, p->h.as<float>(), p->hb.as<__nv_bfloat16>(), (size_t)M * H);
+    VB_CUDA(cudaGetLastError());
+    for (int l = 0; l < c.n_layers; ++l) {
+        const size_t page_off = ((size_t)l * e->max_obs + obs0) * c.n_kv * e->cap * hd;
+        __nv_bfloat16 *kp = e->k_pages.as<__nv_bfloat16>() + page_off, *vp = e->v_pages.as<__nv_bfloat16>() + page_off;
+        {   // RMSNorm (factor in the epilogue, weight folded) + q | k | v, then rotation and the page write
+            vb::GemmParams g{};
+            g.M = M; g.N = qkv_n; g.K = H; g.epi = vb::EPI_BIAS_ACT; g.act = vb::ACT_NONE; g.use_rms = 1; g.eps = c.rms_eps;
+            g.out_bf = p->qkv.as<__nv_bfloat16>(); g.ld_out = qkv_n;
+            if ((rc = vb::dense_gemm(p->hb.p, H, p->wqkv[l].p, g, cs))) return rc;
+            if ((rc = vb::rope_split(p->qkv.p, cos_t, sin_t, p->q.p, kp, vp, M, P, c.n_q, c.n_kv, c.n_kv, hd, e->cap, 0, cs)))
+                return rc;
+        }
+        if (l + 1 < c.n_layers) {
+            vlab200_kv_store view{kp, vp, 1, n_obs, c.n_kv, hd, e->cap, 0};
+            if ((rc = vlab200_attention(&view, 0, p->q.p, p->att.p, P, c.n_q, P, mask_mode, pad_ranges, cs))) return rc;
+            vb::GemmParams g{};
+            g.M = M; g.N = H; g.K = qf; g.epi = vb::EPI_RESIDUAL;
+            g.h = p->h.as<float>(); g.out_bf = p->hb.as<__nv_bfloat16>(); g.ld_out = H;
+            if ((rc = vb::dense_gemm(p->att.p, qf, p->wo[l].p, g, cs))) return rc;
+            g = vb::GemmParams{};
+            g.M = M; g.N = 2 * I; g.K = H; g.epi = vb::EPI_GATED; g.use_rms = 1; g.eps = c.rms_eps; g.act = c.act;
+            g.out_bf = p->g.as<__nv_bfloat16>(); g.ld_out = I;
+            if ((rc = vb::dense_gemm(p->hb.p, H, p->wgu[l].p, g, cs))) return rc;
+            g = vb::GemmParams{};
+            g.M = M; g.N = H; g.K = I; g.epi = vb::EPI_RESIDUAL;
+            g.h = p->h.as<float>(); g.out_bf = p->hb.as<__nv_bfloat16>(); g.ld_out = H;
+            if ((rc = vb::dense_gemm(p->g.p, I, p->wdown[l].p, g, cs))) return rc;
+        }
+        if (!e->is_self[l]) {
+            // expert_cross_kv (src/models/smolvla.cpp:853-860): K' = Wk K, V' = Wv V on the flattened kv axis of the
+            // rotated prefix K / V, once per observation; the layer's own attention above has already read the raw pages
+            __nv_bfloat16 *kb = e->tmp_bf.as<__nv_bfloat16>(), *vbuf = kb + (size_t)e->max_obs * e->P_max * kvf;
+            const size_t total_vec = (size_t)n_obs * P * c.n_kv * (hd / 8);
+            vb::pages_to_rows_kernel<<<148 * 4, 256, 0, cs>>>(kp, kb, c.n_kv, e->cap, hd, P, total_vec);
+            vb::pages_to_rows_kernel<<<148 * 4, 256, 0, cs>>>(vp, vbuf, c.n_kv, e->cap, hd, P, total_vec);
+            VB_CUDA(cudaGetLastError());
+            for (int which = 0; which < 2; ++which) {
+                vb::GemmParams g{};
+                g.M = M; g.N = kvf; g.K = kvf; g.epi = vb::EPI_BIAS_ACT; g.act = vb::ACT_NONE;
+                g.out_bf = which ? vp : kp; g.ld_out = hd;
+                g.rows_in = P; g.rows_out = 0; g.row_off = 0; g.scatter_hd = hd; g.scatter_cap = e->cap;
+                if ((rc = vb::dense_gemm(which ? vbuf : kb, kvf, which ? e->wvx[l].p : e->wkx[l].p, g, cs))) return rc;
+            }
+        }
     }
     return VLAB200_OK;
 }
