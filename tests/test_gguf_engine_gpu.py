@@ -31,7 +31,7 @@ def _golden_names(arch):
     return suffixes, {k for k, _ in g["kv"]}, g["projections"], g["output_norm"]
 
 
-def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
+def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0", extra=None, hidden=2048):
     F32, BF16 = gguf.GGMLQuantizationType.F32, gguf.GGMLQuantizationType.BF16
     w = gguf.GGUFWriter(str(path), arch)
     suffixes, golden_keys, golden_proj, golden_out_norm = _golden_names(arch)
@@ -42,7 +42,7 @@ def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
     for key, val in (("n_layers", cfg["n_layers"]), ("expert_h", cfg["H"]), ("n_q_heads", cfg["n_q"]),
                      ("n_kv_heads", cfg["n_kv"]), ("head_dim", cfg["head_dim"]), ("expert_inter", cfg["inter"]),
                      ("chunk_size", cfg["chunk"]), ("num_steps", cfg["steps"]), ("max_state_dim", cfg["state_dim"]),
-                     ("max_action_dim", cfg["action_dim"]), ("hidden", 2048)):
+                     ("max_action_dim", cfg["action_dim"]), ("hidden", hidden)):
         w.add_uint32(kv(key), val)
     w.add_float64(kv("min_period"), cfg["min_period"])
     w.add_float64(kv("max_period"), cfg["max_period"])
@@ -73,6 +73,8 @@ def _write_policy(path, oracle, cfg, per, glob, bf16_matrices, arch="pi0"):
         assert n + ".weight" in golden_proj and n + ".bias" in golden_proj
         mat(n + ".weight", glob[k])
         vec(n + ".bias", glob["b_" + k[2:]])
+    if extra is not None:
+        extra(w, kv, mat, vec)
     w.write_header_to_file()
     w.write_kv_data_to_file()
     w.write_tensors_to_file()

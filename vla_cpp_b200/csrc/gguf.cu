@@ -386,6 +386,15 @@ struct Upload {
     }
 };
 
+// One tensor onto the device for other translation units (same checks and conversions as Upload::get).
+int gguf_upload(const vlab200_gguf *g, const char *name, int64_t d0, int64_t d1, bool as_bf16, bool gemma, DevBuf *out) {
+    Upload up;
+    const void *p = up.get(g, name, d0, d1, as_bf16, gemma);
+    if (!p || !up.ok) return VLAB200_ERR_ARG;
+    *out = std::move(up.bufs.back());
+    return VLAB200_OK;
+}
+
 }  // namespace vb
 
 extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g, int32_t max_obs, int32_t prefix_len) {

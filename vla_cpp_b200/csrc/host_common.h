@@ -49,6 +49,14 @@ struct DevBuf {
     DevBuf(const DevBuf &) = delete;
     DevBuf &operator=(const DevBuf &) = delete;
     DevBuf(DevBuf &&o) noexcept : p(o.p) { o.p = nullptr; }
+    DevBuf &operator=(DevBuf &&o) noexcept {
+        if (this != &o) {
+            if (p) cudaFree(p);
+            p = o.p;
+            o.p = nullptr;
+        }
+        return *this;
+    }
     int alloc(size_t bytes) {
         cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
         return e == cudaSuccess ? VLAB200_OK : cuda_fail(e, "cudaMalloc");
@@ -61,5 +69,9 @@ struct DevBuf {
         return static_cast<T *>(p);
     }
 };
+
+// A checkpoint tensor ([d1][d0], d1 == 1 for vectors; f32 / f16 / bf16 in the file) uploaded as bf16 or float32,
+// optionally with the Gemma-norm "+1" (gguf.cu).  VLAB200_OK or an error with the last-error text set.
+int gguf_upload(const vlab200_gguf *g, const char *name, int64_t d0, int64_t d1, bool as_bf16, bool gemma, DevBuf *out);
 
 }  // namespace vb

@@ -1,17 +1,258 @@
-// Device side of vla_predict.
+// Device side of vla_predict for pi0- and SmolVLA-shaped checkpoints: prefix embeddings -> prefix producer
+// (the backbone's layers, K/V straight into the engine's pages) -> denoise engine -> un-normalised actions.
+//
+// Follows the reference's predict paths: src/models/pi0.cpp:451-681 and src/models/smolvla.cpp:1476-1710.
+//   pi0      prefix = [image embeddings ; E[lang] * sqrt(hidden)], positions 0..P-1, no mask; the state goes
+//            into the suffix (normalised with the dataset statistics); P changes with the number of language tokens
+//   SmolVLA  prefix = [image embeddings * sqrt(hidden) ; E[lang padded to n_lang_max] * sqrt(hidden) ; state_proj(state)],
+//            padded language slots masked, the state token visible to itself only and rotated at position
+//            n_img + n_lang; suffix positions start one past it
+// Image embeddings come from vla_inputs.precomputed_img_emb; the vision tower is not part of this library.
 #include "predict.h"
+
+#include <cuda_bf16.h>
+
+#include <cmath>
+#include <cstring>
+#include <random>
+#include <string>
 
 namespace vb {
 
-struct Predictor {};
+struct Predictor {
+    int arch = 0;  // 0 pi0, 1 SmolVLA
+    vla_config cfg{};
+    vlab200_engine *eng = nullptr;
+    vlab200_prefill *pre = nullptr;
+    DevBuf token_embd, w_state, b_state;  // bf16 [vocab][hidden]; SmolVLA state projection float32 [hidden][sd], [hidden]
+    int64_t vocab = 0;
+    int max_prefix = 0, max_views = 4;
+    std::vector<float> state_mean, state_std, action_mean, action_std;
+    DevBuf x_emb, ids, img_stage, state_dev, pads;
+    std::mt19937 rng{std::random_device{}()};
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    ~Predictor() {
+        vlab200_prefill_free(pre);
+        vlab200_engine_free(eng);
+        for (cudaEvent_t e : ev)
+            if (e) cudaEventDestroy(e);
+    }
+};
 
-Predictor *predictor_create(const vlab200_gguf *, const char *, const vla_config *) {
-    set_last_error("vla_predict: the prefix producer (VLM prefill) is not part of this build");
-    return nullptr;
+// rows [row0, row0 + n) of x_emb = scale * table[ids[i]]
+__global__ void embed_rows_kernel(const __nv_bfloat16 *__restrict__ table, const int32_t *__restrict__ ids, float scale,
+                                  float *__restrict__ out, int n, int hidden) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const __nv_bfloat16 *src = table + (size_t)ids[i] * hidden;
+    for (int k = threadIdx.x; k < hidden; k += blockDim.x) out[(size_t)i * hidden + k] = scale * __bfloat162float(src[k]);
+}
+
+__global__ void scale_copy_kernel(const float *__restrict__ in, float scale, float *__restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = scale * in[i];
+}
+
+// out[o] = b[o] + sum_k W[o][k] x[k]   (float32; the SmolVLA state token, src/models/smolvla.cpp:1365-1366)
+__global__ void state_embed_kernel(const float *__restrict__ W, const float *__restrict__ b, const float *__restrict__ x,
+                                   float *__restrict__ out, int hidden, int sd) {
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= hidden) return;
+    float acc = b ? b[o] : 0.0f;
+    for (int k = 0; k < sd; ++k) acc = fmaf(W[(size_t)o * sd + k], x[k], acc);
+    out[o] = acc;
+}
+
+static void read_stats(const vlab200_gguf *g, const char *name, std::vector<float> &dst) {
+    // missing or mis-sized statistics mean identity, as in load_stats (src/models/pi0.cpp:300-329)
+    std::vector<float> tmp(dst.size());
+    if (!tmp.empty() && vlab200_gguf_read_f32(g, name, tmp.data(), (int64_t)tmp.size(), 0) == VLAB200_OK) dst = tmp;
+}
+
+Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_config *cfg) {
+    auto *p = new (std::nothrow) Predictor();
+    if (!p) return nullptr;
+    p->arch = std::strcmp(arch, "pi0") == 0 ? 0 : 1;
+    p->cfg = *cfg;
+    const vla_config &c = p->cfg;
+    const int64_t n_img_max = c.n_img * p->max_views;
+    p->max_prefix = (int)(n_img_max + c.n_lang + (p->arch == 1 ? 1 : 0));
+    bool ok = true;
+    // ---- the backbone's layers: "vlm.blk.N.*" with the decoder-block suffixes the converters write ----
+    const int L = (int)c.n_layers;
+    const int64_t H = c.hidden, I = c.intermediate, qf = c.q_full_dim, kvf = c.kv_full_dim;
+    std::vector<DevBuf> bufs((size_t)L * 9);
+    std::vector<const void *> wq(L), wk(L), wv(L), wo(L), wg(L), wu(L), wd(L);
+    std::vector<const float *> ln_in(L), ln_post(L);
+    const bool gemma = p->arch == 0;
+    for (int l = 0; l < L && ok; ++l) {
+        const std::string b = "vlm.blk." + std::to_string(l) + ".";
+        DevBuf *d = &bufs[(size_t)l * 9];
+        auto up = [&](int slot, const char *suffix, int64_t d0, int64_t d1, bool bf, bool gm) -> const void * {
+            if (ok && gguf_upload(g, (b + suffix).c_str(), d0, d1, bf, gm, &d[slot]) != VLAB200_OK) ok = false;
+            return d[slot].p;
+        };
+        ln_in[l] = static_cast<const float *>(up(0, "attn_norm.weight", H, 1, false, gemma));
+        wq[l] = up(1, "attn_q.weight", H, qf, true, false);
+        wk[l] = up(2, "attn_k.weight", H, kvf, true, false);
+        wv[l] = up(3, "attn_v.weight", H, kvf, true, false);
+        wo[l] = up(4, "attn_o.weight", qf, H, true, false);
+        ln_post[l] = static_cast<const float *>(up(5, "ffn_norm.weight", H, 1, false, gemma));
+        wg[l] = up(6, "ffn_gate.weight", H, I, true, false);
+        wu[l] = up(7, "ffn_up.weight", H, I, true, false);
+        wd[l] = up(8, "ffn_down.weight", I, H, true, false);
+    }
+    if (ok) {
+        vlab200_prefill_config pc{};
+        pc.n_layers = L; pc.hidden = (int)H; pc.n_q = (int)c.n_q_heads; pc.n_kv = (int)c.n_kv_heads;
+        pc.head_dim = (int)c.head_dim; pc.inter = (int)I; pc.act = gemma ? 2 : 1;
+        pc.rms_eps = c.rms_eps; pc.rope_base = c.rope_freq_base;
+        vlab200_prefill_weights pw{wq.data(), wk.data(), wv.data(), wo.data(), wg.data(), wu.data(), wd.data(),
+                                   ln_in.data(), ln_post.data()};
+        p->pre = vlab200_prefill_create(&pc, &pw, 1, p->max_prefix);
+        ok = p->pre != nullptr;
+    }
+    bufs.clear();  // the prefill keeps prepared copies
+    if (ok) {
+        p->eng = vlab200_engine_create_from_gguf(g, 1, p->max_prefix);
+        ok = p->eng != nullptr;
+    }
+    // ---- token embeddings (bf16 table), SmolVLA state projection, dataset statistics ----
+    if (ok) {
+        int32_t type = 0, nd = 0;
+        int64_t dims[4] = {0, 0, 0, 0};
+        uint64_t nb = 0;
+        if (vlab200_gguf_tensor_info(g, "token_embd.weight", &type, &nd, dims, &nb) != VLAB200_OK || dims[0] != H) {
+            set_last_error("vla_predict: token_embd.weight is missing or is not [vocab][%lld]", (long long)H);
+            ok = false;
+        } else {
+            p->vocab = dims[1];
+            ok = gguf_upload(g, "token_embd.weight", H, p->vocab, true, false, &p->token_embd) == VLAB200_OK;
+        }
+    }
+    if (ok && p->arch == 1)
+        ok = gguf_upload(g, "state_proj.weight", c.max_state_dim, H, false, false, &p->w_state) == VLAB200_OK &&
+             gguf_upload(g, "state_proj.bias", H, 1, false, false, &p->b_state) == VLAB200_OK;
+    p->state_mean.assign((size_t)c.real_state_dim, 0.0f);
+    p->state_std.assign((size_t)c.real_state_dim, 1.0f);
+    p->action_mean.assign((size_t)c.real_action_dim, 0.0f);
+    p->action_std.assign((size_t)c.real_action_dim, 1.0f);
+    read_stats(g, "state_mean", p->state_mean);
+    read_stats(g, "state_std", p->state_std);
+    read_stats(g, "action_mean", p->action_mean);
+    read_stats(g, "action_std", p->action_std);
+    if (ok)
+        ok = p->x_emb.alloc((size_t)p->max_prefix * H * 4) == VLAB200_OK && p->ids.alloc((size_t)c.n_lang * 4) == VLAB200_OK &&
+             p->img_stage.alloc((size_t)n_img_max * H * 4) == VLAB200_OK &&
+             p->state_dev.alloc((size_t)c.max_state_dim * 4) == VLAB200_OK && p->pads.alloc(8) == VLAB200_OK;
+    for (int i = 0; ok && i < 3; ++i) ok = cudaEventCreate(&p->ev[i]) == cudaSuccess;
+    if (!ok) {
+        delete p;
+        return nullptr;
+    }
+    return p;
 }
 
 void predictor_free(Predictor *p) { delete p; }
 
-int predictor_run(Predictor *, const vla_inputs *, std::vector<float> *, vla_stats *) { return VLAB200_ERR_UNSUPPORTED; }
+int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *actions, vla_stats *stats) {
+    const vla_config &c = p->cfg;
+    const int H = (int)c.hidden, sd = (int)c.max_state_dim, ad = (int)c.max_action_dim, chunk = (int)c.n_suffix;
+    if (!in->precomputed_img_emb) {
+        set_last_error("vla_predict: pass vla_inputs.precomputed_img_emb; the vision tower is not part of this library");
+        return VLAB200_ERR_UNSUPPORTED;
+    }
+    if (in->n_img_views < 1 || in->n_img_views > p->max_views) {
+        set_last_error("vla_predict: n_img_views = %d outside [1, %d]", in->n_img_views, p->max_views);
+        return VLAB200_ERR_ARG;
+    }
+    // language tokens index the embedding table: reject ids outside it (src/models/smolvla.cpp:1579-1589)
+    const int n_lang = in->n_lang;
+    if (n_lang < 1 || n_lang > (int)c.n_lang) {
+        set_last_error("vla_predict: lang_tokens length %d out of range [1, %lld]", n_lang, (long long)c.n_lang);
+        return VLAB200_ERR_ARG;
+    }
+    for (int i = 0; i < n_lang; ++i)
+        if (in->lang_tokens[i] < 0 || in->lang_tokens[i] >= p->vocab) {
+            set_last_error("vla_predict: lang_tokens[%d] = %d out of vocab range [0, %lld)", i, in->lang_tokens[i],
+                           (long long)p->vocab);
+            return VLAB200_ERR_ARG;
+        }
+    cudaStream_t cs = nullptr;
+    const int n_img = (int)c.n_img * in->n_img_views;
+    const int n_lang_rows = p->arch == 1 ? (int)c.n_lang : n_lang;  // SmolVLA pads the language block
+    const int P = n_img + n_lang_rows + (p->arch == 1 ? 1 : 0);
+    const float lang_scale = p->arch == 1 ? std::sqrt((float)H) : (float)std::sqrt((double)H);
+    // ---- inputs ----
+    std::vector<float> state((size_t)sd, 0.0f);
+    if (in->state) std::memcpy(state.data(), in->state, (size_t)sd * sizeof(float));
+    for (int64_t i = 0; i < c.real_state_dim && i < sd; ++i)
+        state[(size_t)i] = (state[(size_t)i] - p->state_mean[(size_t)i]) / (p->state_std[(size_t)i] + c.norm_eps);
+    std::vector<float> x0((size_t)chunk * ad);
+    if (in->noise) {
+        std::memcpy(x0.data(), in->noise, x0.size() * sizeof(float));
+    } else {
+        std::normal_distribution<float> nd(0.0f, 1.0f);
+        for (float &v : x0) v = nd(p->rng);
+    }
+    std::vector<int32_t> ids((size_t)n_lang_rows, 0);
+    std::memcpy(ids.data(), in->lang_tokens, (size_t)n_lang * sizeof(int32_t));
+    const bool timed = in->timing_detail == VLA_TIMING_PHASE;
+    VB_CUDA(cudaMemcpyAsync(p->img_stage.p, in->precomputed_img_emb, (size_t)n_img * H * 4, cudaMemcpyHostToDevice, cs));
+    VB_CUDA(cudaMemcpyAsync(p->ids.p, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice, cs));
+    VB_CUDA(cudaMemcpyAsync(p->state_dev.p, state.data(), (size_t)sd * 4, cudaMemcpyHostToDevice, cs));
+    if (timed) VB_CUDA(cudaEventRecord(p->ev[0], cs));
+    // ---- prefix embeddings ----
+    float *x = p->x_emb.as<float>();
+    scale_copy_kernel<<<148, 256, 0, cs>>>(p->img_stage.as<float>(), p->arch == 1 ? lang_scale : 1.0f, x, (size_t)n_img * H);
+    embed_rows_kernel<<<n_lang_rows, 256, 0, cs>>>(p->token_embd.as<__nv_bfloat16>(), p->ids.as<int32_t>(), lang_scale,
+                                                   x + (size_t)n_img * H, n_lang_rows, H);
+    int rc;
+    int32_t pad[2] = {0, 0};
+    std::vector<int32_t> pos;
+    int pos_base = -1;
+    if (p->arch == 1) {
+        state_embed_kernel<<<(H + 127) / 128, 128, 0, cs>>>(p->w_state.as<float>(), p->b_state.as<float>(),
+                                                           p->state_dev.as<float>(), x + (size_t)(P - 1) * H, H, sd);
+        pad[0] = n_img + n_lang;
+        pad[1] = n_img + (int)c.n_lang;
+        pos.resize((size_t)P);
+        for (int i = 0; i < P; ++i) pos[(size_t)i] = i;
+        pos[(size_t)P - 1] = n_img + n_lang;  // the state token's position
+        pos_base = n_img + n_lang + 1;
+        VB_CUDA(cudaMemcpyAsync(p->pads.p, pad, 8, cudaMemcpyHostToDevice, cs));
+    }
+    VB_CUDA(cudaGetLastError());
+    const int32_t *pads_dev = (p->arch == 1 && pad[1] > pad[0]) ? p->pads.as<int32_t>() : nullptr;
+    if ((rc = vlab200_engine_set_prefix_len(p->eng, P))) return rc;
+    if ((rc = vlab200_prefill_run(p->pre, p->eng, 0, 1, x, P, p->arch == 1 ? pos.data() : nullptr, p->arch == 1 ? 3 : 0,
+                                  pads_dev, cs)))
+        return rc;
+    if (timed) VB_CUDA(cudaEventRecord(p->ev[1], cs));
+    // ---- denoise loop, actions back ----
+    actions->assign((size_t)chunk * ad, 0.0f);
+    if ((rc = vlab200_engine_denoise_host(p->eng, 1, p->arch == 0 ? state.data() : nullptr, x0.data(), actions->data(),
+                                          pos_base, (p->arch == 1 && pads_dev) ? pad : nullptr, cs)))
+        return rc;
+    if (timed) VB_CUDA(cudaEventRecord(p->ev[2], cs));
+    VB_CUDA(cudaStreamSynchronize(cs));
+    int status = 0;
+    if (vlab200_device_status(&status, 1) != VLAB200_OK || status != 0) {
+        set_last_error("vla_predict: a kernel reported device status %d", status);
+        return VLAB200_ERR_DEVICE;
+    }
+    // un-normalise the real action columns, zero the padding (src/models/smolvla.cpp:1698-1705, pi0.cpp:673-677)
+    for (int t = 0; t < chunk; ++t)
+        for (int j = 0; j < ad; ++j) {
+            float &v = (*actions)[(size_t)t * ad + j];
+            v = j < c.real_action_dim ? v * (p->action_std[(size_t)j] + c.norm_eps) + p->action_mean[(size_t)j] : 0.0f;
+        }
+    if (timed) {
+        cudaEventElapsedTime(&stats->ms_prefill, p->ev[0], p->ev[1]);
+        cudaEventElapsedTime(&stats->ms_denoise, p->ev[1], p->ev[2]);
+        stats->ms_inference = stats->ms_prefill + stats->ms_denoise;
+    }
+    return VLAB200_OK;
+}
 
 }  // namespace vb
