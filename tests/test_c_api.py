@@ -77,6 +77,13 @@ def test_load_resolves_the_config_from_checkpoint_metadata(tmp_path, arch):
     else:
         assert "n_img=64" in line and "every=2" in line and "rms_eps=1e-05" in line
 
+    # the C++ face (include/vla_model.hpp, the shape of the reference's src/model.h) on the same file
+    cpp = str(tmp_path / "cppapi")
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", INC, os.path.join(ROOT, "tests", "c", "cpp_api.cpp"), "-o", cpp,
+                    "-L", LIBDIR, "-lvla_b200", "-Wl,-rpath," + LIBDIR], check=True, capture_output=True, text=True)
+    r = subprocess.run([cpp, str(path)], capture_output=True, text=True)
+    assert r.returncode == 0 and "cpp api: ok" in r.stdout and "expert_h=1024 n_suffix=50 steps=10" in r.stdout, r.stdout + r.stderr
+
     # a checkpoint that lacks a required key does not load
     bad = tmp_path / "bad.gguf"
     w = gguf.GGUFWriter(str(bad), arch)

@@ -114,6 +114,12 @@ vla_model *vla_model_load(const char *mmproj_path, const char *ckpt_path, const 
             vla_model_free(m);
             return nullptr;
         }
+        // predict sizes its buffers from the max_* dims and loops to the real_* dims (src/model.cpp:131-149)
+        if (m->cfg.real_state_dim > m->cfg.max_state_dim || m->cfg.real_action_dim > m->cfg.max_action_dim) {
+            vb::set_last_error("vla_model_load: real_state_dim / real_action_dim exceed their max_* dims");
+            vla_model_free(m);
+            return nullptr;
+        }
         return m;
     } catch (...) {
         return nullptr;
