@@ -448,6 +448,18 @@ VLAB200_API int32_t vlab200_node_mul_mat_bf16(const void *w_bf16, const void *x_
  * (bin_bcast, vla_cuda_bf16.cu:396-452).  n % nb == 0: b is broadcast over the leading dims. */
 VLAB200_API int32_t vlab200_node_bin_bf16(int32_t op, const void *a_bf16, const void *b, int32_t b_is_f32,
                                           void *out_bf16, int64_t n, int64_t nb, void *stream);
+/* The general form of add / mul with ggml's broadcast rule and strided operands, and the fused run of up to 8
+ * ADD or MUL nodes that ggml hands over as one node:
+ *   dst[i] = ((src0[i] op b_0[j]) op b_1[j]) ... op b_{n-1}[j]
+ * i = (i0, i1, i2, i3) with extents ne[4] (ne[0] fastest), j = i with every dimension whose addend extent ne1[d]
+ * is 1 set to 0.  All addends share one shape (ne1), one stride set (s1) and one type (bf16, or float32 when
+ * addends_f32).  s0 / s1 / d: strides of src0 / the addends / dst in ELEMENTS.  Float accumulation, one rounding,
+ * exactly as the unfused sequence would give (vla_cuda_bf16.cu:99-171 row-broadcast kernels, :330-389 fused
+ * kernel).  VLAB200_ERR_UNSUPPORTED when ne[1] or ne[2]*ne[3] exceeds 65535 (the reference declines those too). */
+VLAB200_API int32_t vlab200_node_bin_nd_bf16(int32_t op, const void *src0_bf16, const void *const *addends,
+                                             int32_t n_addends, int32_t addends_f32, void *dst_bf16,
+                                             const int64_t ne[4], const int64_t s0[4], const int64_t ne1[4],
+                                             const int64_t s1[4], const int64_t d[4], void *stream);
 /* out = scale * x + bias (vla_cuda_bf16.cu:501-527).  16-byte aligned pointers. */
 VLAB200_API int32_t vlab200_node_scale_bf16(const void *x_bf16, void *out_bf16, int64_t n, float scale, float bias,
                                             void *stream);

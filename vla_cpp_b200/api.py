@@ -85,7 +85,7 @@ EXPORTS = [
     "vlab200_gguf_tensor_info", "vlab200_gguf_tensor_data", "vlab200_gguf_read_f32", "vlab200_gguf_meta_u32",
     "vlab200_gguf_meta_f64", "vlab200_gguf_meta_str", "vlab200_engine_create_from_gguf",
     "vlab200_bitvla_lm_create_from_gguf",
-    "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
+    "vlab200_node_mul_mat_bf16", "vlab200_node_bin_bf16", "vlab200_node_bin_nd_bf16", "vlab200_node_scale_bf16", "vlab200_node_unary_bf16",
     "vlab200_node_norm_bf16",
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
     "bitvla_lm_cuda_init", "bitvla_lm_cuda_free", "bitvla_lm_cuda_set_layer", "bitvla_lm_cuda_set_output_norm",

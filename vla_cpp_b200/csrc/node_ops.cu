@@ -142,6 +142,40 @@ __global__ void __launch_bounds__(256) norm_kernel(const __nv_bfloat16 *__restri
     }
 }
 
+// dst[i0,i1,i2,i3] = ((src0[..] op b_0[j]) op b_1[j]) ... op b_{n-1}[j], j the ggml-broadcast index of (i0..i3) in the
+// addends' shape (extent 1 or equal per dimension, every addend with the same shape and strides), float accumulation,
+// one rounding.  Covers the reference's row-broadcast kernels and its fused run of up to 8 ADD / MUL nodes
+// (src/cuda/vla_cuda_bf16.cu:99-171,358-389).  Grid: x over dim 0, y = dim 1, z = dims 2 and 3, so the index
+// arithmetic is paid once per CTA.  Strides are in elements.
+constexpr int kMaxFuse = 8;
+template <typename TB>
+struct AddendPtrs {
+    const TB *p[kMaxFuse];
+};
+struct NdShape {
+    int64_t ne[4], s0[4], ne1[4], s1[4], d[4];
+};
+
+template <bool MUL, typename TB>
+__global__ void __launch_bounds__(256) bin_nd_kernel(const __nv_bfloat16 *__restrict__ src0, const AddendPtrs<TB> b, int n_b,
+                                                     __nv_bfloat16 *__restrict__ dst, const NdShape sh) {
+    const int64_t i1 = blockIdx.y, i2 = blockIdx.z % sh.ne[2], i3 = blockIdx.z / sh.ne[2];
+    const int64_t row1 = (sh.ne1[1] == 1 ? 0 : i1) * sh.s1[1] + (sh.ne1[2] == 1 ? 0 : i2) * sh.s1[2] +
+                         (sh.ne1[3] == 1 ? 0 : i3) * sh.s1[3];
+    const __nv_bfloat16 *r0 = src0 + i1 * sh.s0[1] + i2 * sh.s0[2] + i3 * sh.s0[3];
+    __nv_bfloat16 *rd = dst + i1 * sh.d[1] + i2 * sh.d[2] + i3 * sh.d[3];
+    const bool bc0 = sh.ne1[0] == 1;
+    for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < sh.ne[0]; i0 += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t j = row1 + (bc0 ? 0 : i0) * sh.s1[0];
+        float acc = __bfloat162float(r0[i0 * sh.s0[0]]);
+        for (int k = 0; k < n_b; ++k) {
+            const float y = static_cast<float>(b.p[k][j]);
+            acc = MUL ? acc * y : acc + y;
+        }
+        rd[i0 * sh.d[0]] = __float2bfloat16(acc);
+    }
+}
+
 static int stream_grid(int64_t work_items) {
     int n_sm = sm_count();
     if (n_sm <= 0) n_sm = 148;
@@ -199,6 +233,43 @@ int32_t vlab200_node_bin_bf16(int32_t op, const void *a_bf16, const void *b, int
     } else {
         if (op) vb::bin_kernel<true, __nv_bfloat16><<<grid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n, nb);
         else vb::bin_kernel<false, __nv_bfloat16><<<grid, 256, 0, cs>>>(a, static_cast<const __nv_bfloat16 *>(b), o, n, nb);
+    }
+    VB_CUDA(cudaGetLastError());
+    return VLAB200_OK;
+}
+
+int32_t vlab200_node_bin_nd_bf16(int32_t op, const void *src0_bf16, const void *const *addends, int32_t n_addends,
+                                 int32_t addends_f32, void *dst_bf16, const int64_t ne[4], const int64_t s0[4],
+                                 const int64_t ne1[4], const int64_t s1[4], const int64_t d[4], void *stream) {
+    if (!src0_bf16 || !addends || !dst_bf16 || !ne || !s0 || !ne1 || !s1 || !d || (op != 0 && op != 1)) return VLAB200_ERR_ARG;
+    if (n_addends < 1 || n_addends > vb::kMaxFuse) return VLAB200_ERR_UNSUPPORTED;
+    vb::NdShape sh;
+    for (int i = 0; i < 4; ++i) {
+        if (ne[i] < 0 || ne1[i] < 1 || (ne1[i] != 1 && ne1[i] != ne[i])) return VLAB200_ERR_ARG;  // ggml broadcast: 1 or equal
+        sh.ne[i] = ne[i]; sh.s0[i] = s0[i]; sh.ne1[i] = ne1[i]; sh.s1[i] = s1[i]; sh.d[i] = d[i];
+    }
+    if (ne[0] == 0 || ne[1] == 0 || ne[2] == 0 || ne[3] == 0) return VLAB200_OK;
+    if (ne[1] > 65535 || ne[2] * ne[3] > 65535) return VLAB200_ERR_UNSUPPORTED;  // the caller declines such a node
+    for (int k = 0; k < n_addends; ++k)
+        if (!addends[k]) return VLAB200_ERR_ARG;
+    unsigned bx = 32;
+    while (bx < 256 && (int64_t)bx < ne[0]) bx *= 2;
+    int64_t gx = (ne[0] + bx - 1) / bx;
+    if (gx > 1024) gx = 1024;
+    const dim3 grid((unsigned)gx, (unsigned)ne[1], (unsigned)(ne[2] * ne[3]));
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16 *a = static_cast<const __nv_bfloat16 *>(src0_bf16);
+    __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(dst_bf16);
+    if (addends_f32) {
+        vb::AddendPtrs<float> b{};
+        for (int k = 0; k < n_addends; ++k) b.p[k] = static_cast<const float *>(addends[k]);
+        if (op) vb::bin_nd_kernel<true, float><<<grid, bx, 0, cs>>>(a, b, n_addends, o, sh);
+        else vb::bin_nd_kernel<false, float><<<grid, bx, 0, cs>>>(a, b, n_addends, o, sh);
+    } else {
+        vb::AddendPtrs<__nv_bfloat16> b{};
+        for (int k = 0; k < n_addends; ++k) b.p[k] = static_cast<const __nv_bfloat16 *>(addends[k]);
+        if (op) vb::bin_nd_kernel<true, __nv_bfloat16><<<grid, bx, 0, cs>>>(a, b, n_addends, o, sh);
+        else vb::bin_nd_kernel<false, __nv_bfloat16><<<grid, bx, 0, cs>>>(a, b, n_addends, o, sh);
     }
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;
