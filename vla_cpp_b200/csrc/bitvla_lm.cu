@@ -24,6 +24,8 @@
 #include <cuda_bf16.h>
 
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -495,6 +497,59 @@ extern "C" int32_t vlab200_bitvla_norm_quant(void *x_bf16, const void *add_bf16,
     }
 }
 
+namespace vb {
+
+// Writes device bf16 tensors as float32 files <dir>/<name>.bin (layer-0 stage dump, debugging only).
+struct L0Dump {
+    const char *dir;
+    cudaStream_t st;
+    DevBuf tmp;
+    L0Dump(const char *d, cudaStream_t s, size_t tmp_elems) : dir(d && *d ? d : nullptr), st(s) {
+        if (dir && tmp.alloc(tmp_elems * 2) != VLAB200_OK) dir = nullptr;
+    }
+    bool on() const { return dir != nullptr; }
+    std::vector<float> fetch(const void *dev, size_t n) {
+        std::vector<uint16_t> raw(n);
+        std::vector<float> f(n);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(raw.data(), dev, n * 2, cudaMemcpyDeviceToHost);
+        for (size_t i = 0; i < n; ++i) {
+            const uint32_t b = (uint32_t)raw[i] << 16;
+            std::memcpy(&f[i], &b, 4);
+        }
+        return f;
+    }
+    void put(const char *name, const std::vector<float> &f) {
+        const std::string path = std::string(dir) + "/" + name + ".bin";
+        if (FILE *fp = std::fopen(path.c_str(), "wb")) {
+            std::fwrite(f.data(), sizeof(float), f.size(), fp);
+            std::fclose(fp);
+        }
+    }
+    void write(const char *name, const void *dev, size_t n) { put(name, fetch(dev, n)); }
+    // the fused projection holds q | k | v per token; the reference's file holds the q, k and v matrices one after another
+    void write_qkv(const char *name, const void *dev, int M, int hq, int hkv) {
+        const int row = hq + 2 * hkv;
+        const std::vector<float> f = fetch(dev, (size_t)M * row);
+        std::vector<float> out(f.size());
+        float *q = out.data(), *k = q + (size_t)M * hq, *v = k + (size_t)M * hkv;
+        for (int m = 0; m < M; ++m) {
+            std::memcpy(q + (size_t)m * hq, &f[(size_t)m * row], (size_t)hq * 4);
+            std::memcpy(k + (size_t)m * hkv, &f[(size_t)m * row + hq], (size_t)hkv * 4);
+            std::memcpy(v + (size_t)m * hkv, &f[(size_t)m * row + hq + hkv], (size_t)hkv * 4);
+        }
+        put(name, out);
+    }
+    void write_sum(const char *name, const void *a, const void *b, size_t n) {
+        std::vector<float> x = fetch(a, n);
+        const std::vector<float> y = fetch(b, n);
+        for (size_t i = 0; i < n; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(x[i] + y[i]));
+        put(name, x);
+    }
+};
+
+}  // namespace vb
+
 extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void *d_in, void *d_out, int32_t seq,
                                              int32_t n_seq, void *stream) {
     if (!ctx || !d_in || !d_out) return VLAB200_ERR_ARG;
@@ -519,33 +574,63 @@ extern "C" int32_t vlab200_bitvla_lm_forward(vlab200_bitvla_lm *ctx, const void 
     VB_CUDA(cudaMemcpyAsync(ctx->h.p, d_in, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, st));
     const vlab200_kv_store store = {ctx->k_pages.p, ctx->v_pages.p, 1, n_seq, ctx->n_kv, ctx->hd, ctx->max_seq, 0};
     int rc = VLAB200_OK;
+    // Stage dump of layer 0, switched on like the reference's (VLA_BITVLA_DUMP_L0=<dir>, one sequence): the same ten
+    // float32 files under the same names (src/kernels/bitvla/bitvla_lm_cuda.cu:400-420 and the l0_dump calls up to
+    // :523), so the two stacks can be compared stage by stage.  A debugging path: it synchronises, allocates and
+    // runs the normalisations a second time without their fused quantisation.
+    vb::L0Dump dump(n_seq == 1 ? std::getenv("VLA_BITVLA_DUMP_L0") : nullptr, st, (size_t)M * (size_t)(F > hq ? (F > H ? F : H) : (hq > H ? hq : H)));
     for (int L = 0; L < ctx->n_layers && !rc; ++L) {
         const vb::LmLayer &l = ctx->layers[L];
+        const bool dl = dump.on() && L == 0;
+        if (dl) {
+            vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->h.p, nullptr, l.w.attn_norm_w, ctx->eps, M, H, nullptr, nullptr, dump.tmp.p, st);
+            dump.write("L0_01_attn_norm", dump.tmp.p, (size_t)M * H);
+        }
         if (L == 0) rc = vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->h.p, nullptr, l.w.attn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
         else rc = vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, l.w.attn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
         if (rc) break;
         rc = vlab200_ternary_linear(a8, l.qkv_packed.as<uint8_t>(), ctx->qkv.p, nullptr, s, l.qkv_ws.as<float>(),
                                     ctx->qkv_ws_num, M, hq + 2 * hkv, H, 0, st);
         if (rc) break;
+        if (dl) dump.write_qkv("L0_02_qkv_proj", ctx->qkv.p, M, hq, hkv);
         rc = vb::rope_split(ctx->qkv.p, ctx->cos_t.as<float>(), ctx->sin_t.as<float>(), ctx->q.p, ctx->k_pages.p,
                             ctx->v_pages.p, M, seq, ctx->n_q, ctx->n_kv, ctx->n_kv, ctx->hd, ctx->max_seq, 0, st);
         if (rc) break;
         rc = vlab200_attention(&store, 0, ctx->q.p, ctx->att.p, seq, ctx->n_q, seq, /*mask_mode=*/0, nullptr, st);
         if (rc) break;
+        if (dl) {
+            dump.write("L0_03_attn_merged_pre_subnorm", ctx->att.p, (size_t)M * hq);
+            vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->att.p, nullptr, l.w.attn_sub_norm_w, ctx->eps, M, hq, nullptr, nullptr, dump.tmp.p, st);
+            dump.write("L0_04_attn_sub_norm", dump.tmp.p, (size_t)M * hq);
+        }
         rc = vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->att.p, nullptr, l.w.attn_sub_norm_w, ctx->eps, M, hq, a8, s, nullptr, st);
         if (rc) break;
         rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.o_packed), ctx->proj.p, nullptr, s,
                                     static_cast<const float *>(l.w.o_ws), 1, M, H, hq, 0, st);
         if (rc) break;
+        if (dl) dump.write("L0_05_o_proj_out", ctx->proj.p, (size_t)M * H);
         rc = vb::launch_norm_quant<vb::NQ_ADD>(ctx->h.p, ctx->proj.p, l.w.ffn_norm_w, ctx->eps, M, H, a8, s, nullptr, st);
         if (rc) break;
+        if (dl) {
+            dump.write("L0_06_after_attn_residual", ctx->h.p, (size_t)M * H);
+            vb::launch_norm_quant<vb::NQ_PLAIN>(ctx->h.p, nullptr, l.w.ffn_norm_w, ctx->eps, M, H, nullptr, nullptr, dump.tmp.p, st);
+            dump.write("L0_07_ffn_norm", dump.tmp.p, (size_t)M * H);
+        }
         rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.gate_up_packed), ctx->gate_up.p, nullptr, s,
                                     static_cast<const float *>(l.w.gate_up_ws), 2, M, 2 * F, H, 0, st);
         if (rc) break;
+        if (dl) {
+            vb::launch_norm_quant<vb::NQ_GATE_UP>(ctx->gate_up.p, nullptr, l.w.ffn_sub_norm_w, ctx->eps, M, F, nullptr, nullptr, dump.tmp.p, st);
+            dump.write("L0_08_ffn_sub_norm", dump.tmp.p, (size_t)M * F);
+        }
         rc = vb::launch_norm_quant<vb::NQ_GATE_UP>(ctx->gate_up.p, nullptr, l.w.ffn_sub_norm_w, ctx->eps, M, F, a8, s, nullptr, st);
         if (rc) break;
         rc = vlab200_ternary_linear(a8, static_cast<const uint8_t *>(l.w.down_packed), ctx->proj.p, nullptr, s,
                                     static_cast<const float *>(l.w.down_ws), 1, M, H, F, 0, st);
+        if (dl && !rc) {
+            dump.write("L0_09_down_out", ctx->proj.p, (size_t)M * H);
+            dump.write_sum("L0_10_final", ctx->h.p, ctx->proj.p, (size_t)M * H);  // the residual add is fused into the next stage
+        }
     }
     if (rc) return rc;
     // h += down of the last layer, then the output norm (bitvla_lm_cuda.cu:718)
