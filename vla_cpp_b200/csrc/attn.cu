@@ -192,6 +192,8 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
     const int nchunks = (p.nk16 + 31) / 32;
     // Chunks of the first column half.  Chunks below the prefix end take the unmasked path in every row
     // (pad ranges aside); a masked chunk costs about 1.4 of those, so the first half gets more chunks when
@@ -487,8 +489,6 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     if (rc_attr) return rc_attr;
     const int n_sm = vb::sm_count();
     const int grid = p.n_items < n_sm ? p.n_items : n_sm;
-    vb::attn_hd64_kernel<<<grid, vb::ATT_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(qmap, qmap32, kmap, vmap,
-                                                                                            p);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return vb::launch_pdl(vb::attn_hd64_kernel, dim3(grid), dim3(vb::ATT_THREADS), smem, static_cast<cudaStream_t>(stream), qmap,
+                          qmap32, kmap, vmap, p);
 }

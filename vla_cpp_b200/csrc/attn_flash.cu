@@ -66,7 +66,7 @@ struct FlashSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, HD == 64 ? 2 : 1)
 attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   const __grid_constant__ CUtensorMap v_map, const FlashParams p) {
     using L = FlashSmem<HD>;
@@ -109,6 +109,8 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == 4) {
         // ----------------------------------------------------------------- loader
@@ -453,6 +455,8 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == FP_LOADER_WARP) {
         // ----------------------------------------------------------------- loader (each CTA its own halves)
@@ -810,16 +814,13 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
             if (rc) return rc;
             if ((rc = ensure_dyn_smem(attn_flash_pair_kernel<HD>, LP::TOTAL))) return rc;
             const int ncl = n_pair_units < pairs ? n_pair_units : pairs;
-            attn_flash_pair_kernel<HD><<<2 * ncl, FP_THREADS, LP::TOTAL, stream>>>(qmap, kmap, vmap128, p);
-            VB_CUDA(cudaGetLastError());
-            return VLAB200_OK;
+            return launch_pdl(attn_flash_pair_kernel<HD>, dim3(2 * ncl), dim3(FP_THREADS), LP::TOTAL, stream, qmap, kmap, vmap128, p);
         }
     }
     if (int rc = ensure_dyn_smem(attn_flash_kernel<HD>, L::TOTAL)) return rc;
-    const int grid = p.n_units < n_sm ? p.n_units : n_sm;
-    attn_flash_kernel<HD><<<grid, FA_THREADS, L::TOTAL, stream>>>(qmap, kmap, vmap, p);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    const int slots = (HD == 64 ? 2 : 1) * n_sm;  // head_dim 64: two CTAs share an SM (256 TMEM columns, 50 KB each)
+    const int grid = p.n_units < slots ? p.n_units : slots;
+    return launch_pdl(attn_flash_kernel<HD>, dim3(grid), dim3(FA_THREADS), L::TOTAL, stream, qmap, kmap, vmap, p);
 }
 
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,

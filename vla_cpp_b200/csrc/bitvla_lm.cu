@@ -33,6 +33,7 @@
 
 #include "gemm.h"
 #include "host_common.h"
+#include "tc5.cuh"
 
 namespace vb {
 
@@ -235,6 +236,8 @@ __global__ void __launch_bounds__(128) rope_split_kernel(const __nv_bfloat16 *__
                                                          __nv_bfloat16 *__restrict__ k_pages,
                                                          __nv_bfloat16 *__restrict__ v_pages, int seq, int n_q,
                                                          int n_kv_proj, int n_kv_store, int hd, int cap, int row0) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x;
     const int sq = m / seq, s = m % seq;
     const int half = hd >> 1;
@@ -269,6 +272,8 @@ __global__ void __launch_bounds__(128) rope_split_vec_kernel(const __nv_bfloat16
                                                              __nv_bfloat16 *__restrict__ k_pages,
                                                              __nv_bfloat16 *__restrict__ v_pages, int seq, int n_q,
                                                              int n_kv_proj, int n_kv_store, int hd, int cap, int row0) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x;
     const int sq = m / seq, s = m % seq;
     const int half = hd >> 1, h8 = half >> 3;
@@ -312,19 +317,13 @@ int rope_split(const void *qkv, const float *cos_t, const float *sin_t, void *q_
                int M, int seq, int n_q, int n_kv_proj, int n_kv_store, int hd, int cap, int row0, cudaStream_t st) {
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (hd % 16 == 0 && al16(qkv) && al16(cos_t) && al16(sin_t) && al16(q_out) && al16(k_pages) && al16(v_pages)) {
-        rope_split_vec_kernel<<<M, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
-                                                 static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
-                                                 static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd,
-                                                 cap, row0);
-        VB_CUDA(cudaGetLastError());
-        return VLAB200_OK;
+        return launch_pdl(rope_split_vec_kernel, dim3(M), dim3(128), 0, st, static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
+                          static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
+                          static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd, cap, row0);
     }
-    rope_split_kernel<<<M, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
-                                         static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
-                                         static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd, cap,
-                                         row0);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return launch_pdl(rope_split_kernel, dim3(M), dim3(128), 0, st, static_cast<const __nv_bfloat16 *>(qkv), cos_t, sin_t,
+                      static_cast<__nv_bfloat16 *>(q_out), static_cast<__nv_bfloat16 *>(k_pages),
+                      static_cast<__nv_bfloat16 *>(v_pages), seq, n_q, n_kv_proj, n_kv_store, hd, cap, row0);
 }
 
 static int gcd_int(int a, int b) {

@@ -17,6 +17,7 @@
 
 #include "gemm.h"
 #include "host_common.h"
+#include "tc5.cuh"
 
 namespace vb {
 
@@ -63,6 +64,8 @@ __global__ void __launch_bounds__(256) action_in_kernel(const float *__restrict_
                                                         const float *__restrict__ b_ain, __nv_bfloat16 *__restrict__ a,
                                                         int n_rows, int H, int A) {
     __shared__ float sx[AIN_ROWS][64];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row0 = blockIdx.x * AIN_ROWS;
     const int rows = min(AIN_ROWS, n_rows - row0);
     for (int i = threadIdx.x; i < rows * A; i += blockDim.x) sx[i / A][i % A] = x[(size_t)row0 * A + i];
@@ -98,6 +101,8 @@ __global__ void __launch_bounds__(256) state_token_kernel(const float *__restric
                                                           const float *__restrict__ b_sp, float *__restrict__ h,
                                                           __nv_bfloat16 *__restrict__ hb, int H, int sd, int S) {
     __shared__ float ss[64];
+    pdl_launch_dependents();
+    pdl_wait();
     const int obs = blockIdx.x;
     if (threadIdx.x < sd) ss[threadIdx.x] = state[(size_t)obs * sd + threadIdx.x];
     __syncthreads();
@@ -113,6 +118,8 @@ __global__ void __launch_bounds__(256) state_token_kernel(const float *__restric
 // x[obs][t][a] += dt * v[obs*S + (S - chunk) + t][a]   (v from the head GEMM, row stride A)
 __global__ void euler_kernel(float *__restrict__ x, const float *__restrict__ v, int n, int A, int chunk, int S,
                              float dt) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int a = i % A, row = i / A;
@@ -428,12 +435,14 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     VB_CUDA(cudaMemcpyAsync(e->x.p, x0, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
     const float dt = -1.0f / (float)c.steps;
     for (int step = 0; step < c.steps; ++step) {
-        vb::action_in_kernel<<<dim3((Mc + vb::AIN_ROWS - 1) / vb::AIN_ROWS, (H + 255) / 256), 256, 0, cs>>>(
-            e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), Mc, H, A);
-        if (c.model == 0)
-            vb::state_token_kernel<<<n_obs, 256, 0, cs>>>(state, e->w_sp.as<__nv_bfloat16>(), e->b_sp.as<float>(),
-                                                          e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, c.state_dim, S);
-        VB_CUDA(cudaGetLastError());
+        if ((rc = vb::launch_pdl(vb::action_in_kernel, dim3((Mc + vb::AIN_ROWS - 1) / vb::AIN_ROWS, (H + 255) / 256), dim3(256), 0, cs,
+                                 e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), Mc,
+                                 H, A)))
+            return rc;
+        if (c.model == 0 &&
+            (rc = vb::launch_pdl(vb::state_token_kernel, dim3(n_obs), dim3(256), 0, cs, state, e->w_sp.as<__nv_bfloat16>(),
+                                 e->b_sp.as<float>(), e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, c.state_dim, S)))
+            return rc;
         {
             vb::GemmParams p{};
             p.M = Mc; p.N = H; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_SILU;
@@ -455,8 +464,9 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
             p.M = M; p.N = A; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE; p.use_rms = 1; p.eps = c.rms_eps;
             p.out_f32 = e->vbuf.as<float>(); p.bias = e->b_aout.as<float>(); p.ld_out = A;
             if ((rc = vb::dense_gemm(e->hb.p, H, e->w_aout.p, p, cs))) return rc;
-            vb::euler_kernel<<<(Mc * A + 255) / 256, 256, 0, cs>>>(e->x.as<float>(), e->vbuf.as<float>(), Mc * A, A, chunk, S, dt);
-            VB_CUDA(cudaGetLastError());
+            if ((rc = vb::launch_pdl(vb::euler_kernel, dim3((Mc * A + 255) / 256), dim3(256), 0, cs, e->x.as<float>(),
+                                     e->vbuf.as<float>(), Mc * A, A, chunk, S, dt)))
+                return rc;
         }
     }
     VB_CUDA(cudaMemcpyAsync(x_out, e->x.p, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));

@@ -121,6 +121,8 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
     if (PAIR) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == 0) {
         if (lane == 0) {
@@ -458,8 +460,8 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         if (rc) return rc;
         if (int rc = ensure_dyn_smem(dense_gemm_pair_kernel, GemmCfg<256, true>::SMEM)) return rc;
         const int nt = tiles_mp * tn256;
-        dense_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), G_THREADS, GemmCfg<256, true>::SMEM, stream>>>(
-            amap, wmap, p, tiles_mp, tn256);
+        return launch_pdl(dense_gemm_pair_kernel, dim3(2 * (nt < pairs ? nt : pairs)), dim3(G_THREADS), GemmCfg<256, true>::SMEM,
+                          stream, amap, wmap, p, tiles_mp, tn256);
     } else if (variant == 4) {
         const uint32_t box[2] = {G_BK, 64};
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
@@ -467,7 +469,8 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         if (rc) return rc;
         if (int rc = ensure_dyn_smem(dense_gemm_kernel<64>, GemmCfg<64, false>::SMEM)) return rc;
         const int nt = tiles_m * tn64;
-        dense_gemm_kernel<64><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<64, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn64);
+        return launch_pdl(dense_gemm_kernel<64>, dim3(nt < n_sm ? nt : n_sm), dim3(G_THREADS), GemmCfg<64, false>::SMEM, stream,
+                          amap, wmap, p, tiles_m, tn64);
     } else if (variant == 2) {
         const uint32_t box[2] = {G_BK, 128};
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
@@ -475,11 +478,13 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
         if (rc) return rc;
         if (int rc = ensure_dyn_smem(dense_gemm_kernel<128>, GemmCfg<128, false>::SMEM)) return rc;
         const int nt = tiles_m * tn128;
-        dense_gemm_kernel<128><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<128, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn128);
+        return launch_pdl(dense_gemm_kernel<128>, dim3(nt < n_sm ? nt : n_sm), dim3(G_THREADS), GemmCfg<128, false>::SMEM, stream,
+                          amap, wmap, p, tiles_m, tn128);
     } else {
         if (int rc = ensure_dyn_smem(dense_gemm_kernel<256>, GemmCfg<256, false>::SMEM)) return rc;
         const int nt = tiles_m * tn256;
-        dense_gemm_kernel<256><<<nt < n_sm ? nt : n_sm, G_THREADS, GemmCfg<256, false>::SMEM, stream>>>(amap, wmap, p, tiles_m, tn256);
+        return launch_pdl(dense_gemm_kernel<256>, dim3(nt < n_sm ? nt : n_sm), dim3(G_THREADS), GemmCfg<256, false>::SMEM, stream,
+                          amap, wmap, p, tiles_m, tn256);
     }
     VB_CUDA(cudaGetLastError());
     return VLAB200_OK;

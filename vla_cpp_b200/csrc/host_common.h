@@ -42,6 +42,24 @@ int cuda_fail(cudaError_t e, const char *what);
 int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const uint64_t *dims,
                     const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swz);
 
+// Launches `kernel` so that it may overlap the tail of the preceding kernel in `stream` (programmatic
+// dependent launch).  Only for kernels that call pdl_wait() before their first access to global memory.
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    return e == cudaSuccess ? VLAB200_OK : cuda_fail(e, "cudaLaunchKernelEx");
+}
+
 // Owning device allocation (move-only).
 struct DevBuf {
     void *p = nullptr;

@@ -305,6 +305,8 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
         *abort_flag = 0;
         fence_barrier_init();
     }
+    pdl_launch_dependents();
+    pdl_wait();  // the barrier set-up above overlapped the previous kernel's tail; global memory is read from here on
     // RoPE table, transposed so that lanes (consecutive tokens) read consecutive words
     for (int i = threadIdx.x; i < p.S * half; i += QKVF_THREADS) {
         const int t = i / half, d = i % half;
@@ -768,16 +770,16 @@ int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const
             const int fsmem = nst * stage + aux + 1024;
             if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
             const int nt = tiles_mp * tiles_n;
-            vb::qkv_rope_tma_pair_kernel<<<2 * (nt < pairs ? nt : pairs), vb::QKVF_THREADS, fsmem, cs>>>(
-                xmap, wmap, p, tiles_mp, tiles_n, nst);
+            return vb::launch_pdl(vb::qkv_rope_tma_pair_kernel, dim3(2 * (nt < pairs ? nt : pairs)), dim3(vb::QKVF_THREADS), fsmem, cs,
+                                  xmap, wmap, p, tiles_mp, tiles_n, nst);
         } else {
             int nst = 4;
             while (nst > 2 && nst * vb::QKV_STAGE_BYTES + aux + 1024 > 227 * 1024) --nst;
             const int fsmem = nst * vb::QKV_STAGE_BYTES + aux + 1024;
             if (fsmem > 227 * 1024) return VLAB200_ERR_UNSUPPORTED;
             const int nt = tiles_m * tiles_n;
-            vb::qkv_rope_tma_kernel<<<nt < n_sm ? nt : n_sm, vb::QKVF_THREADS, fsmem, cs>>>(xmap, wmap, p, tiles_m,
-                                                                                          tiles_n, nst);
+            return vb::launch_pdl(vb::qkv_rope_tma_kernel, dim3(nt < n_sm ? nt : n_sm), dim3(vb::QKVF_THREADS), fsmem, cs, xmap, wmap,
+                                  p, tiles_m, tiles_n, nst);
         }
         VB_CUDA(cudaGetLastError());
         return VLAB200_OK;

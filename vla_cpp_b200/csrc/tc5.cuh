@@ -26,6 +26,15 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in
+// the stream is still running; pdl_wait() blocks until that predecessor has completed and its memory is
+// visible, so everything before it (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the
+// predecessor's tail.  pdl_launch_dependents() lets the successor start launching; it never relaxes what
+// the successor's own pdl_wait() waits for.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ----------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
