@@ -81,6 +81,8 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(__nv_bfloat16 *__restri
                                                          __nv_bfloat16 *__restrict__ out_bf) {
     extern __shared__ float row[];
     __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x, tid = threadIdx.x;
     const int K2 = K >> 1;
     const size_t ld = MODE == NQ_GATE_UP ? 2 * (size_t)K : (size_t)K;
@@ -138,6 +140,8 @@ __global__ void __launch_bounds__(256) norm_quant_vec_kernel(__nv_bfloat16 *__re
                                                              int8_t *__restrict__ q_out, float *__restrict__ s_out,
                                                              __nv_bfloat16 *__restrict__ out_bf) {
     __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x, tid = threadIdx.x;
     const int K8 = K >> 3;
     const size_t ld = MODE == NQ_GATE_UP ? 2 * (size_t)K : (size_t)K;
@@ -460,17 +464,13 @@ static int launch_norm_quant(void *in, const void *add, const void *w, float eps
     const __nv_bfloat16 *add_b = static_cast<const __nv_bfloat16 *>(add), *w_b = static_cast<const __nv_bfloat16 *>(w);
     __nv_bfloat16 *out_b = static_cast<__nv_bfloat16 *>(out_bf);
     if (K % 8 == 0 && K <= 8192 && al16(in) && al16(add) && al16(w) && al16(out_bf) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
-        if (K <= 4096) norm_quant_vec_kernel<MODE, 2><<<M, 256, 0, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
-        else norm_quant_vec_kernel<MODE, 4><<<M, 256, 0, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
-        VB_CUDA(cudaGetLastError());
-        return VLAB200_OK;
+        if (K <= 4096) return launch_pdl(norm_quant_vec_kernel<MODE, 2>, dim3(M), dim3(256), 0, st, in_b, add_b, w_b, eps, K, q, s, out_b);
+        return launch_pdl(norm_quant_vec_kernel<MODE, 4>, dim3(M), dim3(256), 0, st, in_b, add_b, w_b, eps, K, q, s, out_b);
     }
     const size_t smem = (size_t)K * 4;
     if (smem > 48 * 1024)
         if (int rc = ensure_dyn_smem(norm_quant_kernel<MODE>, 200 * 1024)) return rc;
-    norm_quant_kernel<MODE><<<M, 256, smem, st>>>(in_b, add_b, w_b, eps, K, q, s, out_b);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return launch_pdl(norm_quant_kernel<MODE>, dim3(M), dim3(256), smem, st, in_b, add_b, w_b, eps, K, q, s, out_b);
 }
 
 }  // namespace vb

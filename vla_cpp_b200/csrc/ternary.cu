@@ -138,6 +138,20 @@ __global__ void __launch_bounds__(GEMV_THREADS) ternary_gemv_kernel(const int8_t
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nb = blockIdx.x;
     const int rows_here = min(MT, M - m0);
+    // The packed weights never depend on the kernel that runs before this one: the first batch of weight loads is
+    // issued before the wait on that kernel (programmatic dependent launch), so it travels during its tail.
+    const int nchunks = K >> 7;
+    const uint4 *wbase = reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K) + lane;
+    constexpr int UNROLL = 4;
+    const uint4 kZeroWeights = make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
+    uint4 wv[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int c = warp + GEMV_WARPS * u;
+        wv[u] = (c < nchunks) ? __ldg(wbase + (size_t)c * 32) : kZeroWeights;
+    }
+    pdl_launch_dependents();
+    pdl_wait();
     for (int i = tid; i < MT * (K >> 4); i += GEMV_THREADS) {
         const int mm = i / (K >> 4), kk = i % (K >> 4);
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -152,16 +166,14 @@ __global__ void __launch_bounds__(GEMV_THREADS) ternary_gemv_kernel(const int8_t
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mm][i] = 0;
 
-    const int nchunks = K >> 7;
-    const uint4 *wbase = reinterpret_cast<const uint4 *>(Wp + (size_t)nb * 4 * K) + lane;
     const int koff = 32 * (lane >> 3) + 16 * ((lane & 3) >> 1);
-    constexpr int UNROLL = 4;
     for (int c0 = warp; c0 < nchunks; c0 += GEMV_WARPS * UNROLL) {
-        uint4 wv[UNROLL];
+        if (c0 != warp) {  // the first batch is already in registers
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int c = c0 + GEMV_WARPS * u;
-            wv[u] = (c < nchunks) ? __ldg(wbase + (size_t)c * 32) : make_uint4(0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu, 0xAAAAAAAAu);
+            for (int u = 0; u < UNROLL; ++u) {
+                const int c = c0 + GEMV_WARPS * u;
+                wv[u] = (c < nchunks) ? __ldg(wbase + (size_t)c * 32) : kZeroWeights;
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -290,6 +302,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();  // the set-up above overlapped the previous kernel's tail
 
     // tiles are ordered m-fastest so that CTAs running at the same time share a weight slab
     if (warp == 0) {
@@ -560,6 +574,10 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: the activations, scales and the output belong to the kernels around this one,
+    // the packed weights do not -- the decode warps fetch their first weight blocks before they wait.
+    pdl_launch_dependents();
+    if (warp < 2 || warp >= 10) pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -642,6 +660,7 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
         };
         uint4 nxt[4];
         fetch(pi, nxt);
+        pdl_wait();
         uint32_t st = (uint32_t)pi, ph = 0;
         bool ok = true;
         for (int g = pi; ok && g < total; g += 4) {
@@ -775,9 +794,7 @@ static int launch_gemv(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, in
     const size_t smem = (size_t)MT * K + GEMV_WARPS * MT * 16 * sizeof(int);
     if (smem > 48 * 1024)
         if (int rc = ensure_dyn_smem(ternary_gemv_kernel<MT>, (int)smem)) return rc;
-    ternary_gemv_kernel<MT><<<N / 16, GEMV_THREADS, smem, st>>>(A, W, out, acc, s, ws, ws_num, M, N, K, m0);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return launch_pdl(ternary_gemv_kernel<MT>, dim3(N / 16), dim3(GEMV_THREADS), smem, st, A, W, out, acc, s, ws, ws_num, M, N, K, m0);
 }
 
 template <int BN, int STAGES>
@@ -798,10 +815,8 @@ static int launch_gemm_tc(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
     if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
     const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + BN - 1) / BN;
     const int nt = tiles_m * tiles_n;
-    ternary_gemm_tc_kernel<BN, STAGES><<<nt < n_sm ? nt : n_sm, GEMM_THREADS, L::TOTAL, st>>>(
-        amap, W, out, acc, s, ws, ws_num, M, N, K, tiles_m, tiles_n, status);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return launch_pdl(ternary_gemm_tc_kernel<BN, STAGES>, dim3(nt < n_sm ? nt : n_sm), dim3(GEMM_THREADS), L::TOTAL, st, amap, W, out,
+                      acc, s, ws, ws_num, M, N, K, tiles_m, tiles_n, status);
 }
 
 static int launch_gemm_pair(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, int32_t *acc, const float *s,
@@ -820,10 +835,8 @@ static int launch_gemm_pair(const int8_t *A, const uint8_t *W, __nv_bfloat16 *ou
     if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
     const int tiles_mp = (M + 255) / 256, tiles_n = (N + 255) / 256;
     const int nt = tiles_mp * tiles_n, pairs = n_sm / 2;
-    ternary_gemm_pair_kernel<<<2 * (nt < pairs ? nt : pairs), GEMM_THREADS, PairSmem::TOTAL, st>>>(
-        amap, W, out, acc, s, ws, ws_num, M, N, K, tiles_mp, tiles_n, status);
-    VB_CUDA(cudaGetLastError());
-    return VLAB200_OK;
+    return launch_pdl(ternary_gemm_pair_kernel, dim3(2 * (nt < pairs ? nt : pairs)), dim3(GEMM_THREADS), PairSmem::TOTAL, st, amap,
+                      W, out, acc, s, ws, ws_num, M, N, K, tiles_mp, tiles_n, status);
 }
 
 static int ternary_linear(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out, int32_t *acc, const float *s,
