@@ -274,6 +274,18 @@ VLAB200_API int32_t vlab200_prefill_run(vlab200_prefill *p, vlab200_engine *e, i
                                         const float *x_emb, int32_t P, const int32_t *pos_host, int32_t mask_mode,
                                         const int32_t *pad_ranges, void *stream);
 
+/* Several GPUs in one process.  vlab200_shard_range: the contiguous block [start, start + count) of `rank` when
+ * n_items independent observations are cut over n_ranks (the first n_items % n_ranks ranks get one more).
+ * vlab200_engines_denoise_host: n_obs observations in (pinned) host memory through n_engines engines, each
+ * created with its own device current (a weight replica and K/V pages per GPU, prefix K/V already set for the
+ * engine's block, observation o of the block in slot o - start); one host thread and one stream per engine,
+ * blocks of at most max_obs observations at a time, no exchange between GPUs; returns when every block is back in
+ * x_out_host.  The reference runs one observation per predict on one device (src/model.h:204-225). */
+VLAB200_API int32_t vlab200_shard_range(int64_t n_items, int32_t n_ranks, int32_t rank, int64_t *start, int64_t *count);
+VLAB200_API int32_t vlab200_engines_denoise_host(vlab200_engine *const *engines, int32_t n_engines, int64_t n_obs,
+                                                 const float *state_host, const float *x0_host, float *x_out_host,
+                                                 int32_t pos_base, const int32_t *pad_ranges_host);
+
 /* Measurement hook: launches ONE stage of expert layer `layer` `reps` times on the engine's own buffers, as
  * vlab200_engine_denoise would (0 = fused RMSNorm+QKV+RoPE+append, 1 = attention, 2 = O-projection + residual,
  * 3 = fused RMSNorm + gate/up + activation, 4 = down projection + residual), so that a caller can bracket one

@@ -189,3 +189,46 @@ def test_smolvla_full_depth_16_layers_10_steps(oracle, n_obs, check, sigma):
                     **SMOLVLA_FULL)
     print(f"smolvla full depth n_obs={n_obs} sigma={sigma}: rel_l2={w:.3e} displacement rel_l2={d:.3e}")
     assert w < 1e-2 and d < 3e-2, (w, d)
+
+
+def test_several_engines_one_host_thread_each(oracle):
+    """vlab200_engines_denoise_host: 11 observations cut over 3 engines (3 replicas; on a one-GPU box they all live
+    on that GPU, each with its own stream and host thread), blocks of at most max_obs = 2 observations at a time.
+    Every observation's chunk is bit-identical to what one engine computes for it alone."""
+    import ctypes as C
+
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    rng = np.random.default_rng(23)
+    kw = dict(model=0, L=2, H=128, n_q=4, n_kv=1, hd=64, inter=256, chunk=10, A=32, sd=32, T=2)
+    n_total, n_eng, P, max_obs = 11, 3, 24, 2
+    cfg, per, glob, _ = make_policy(oracle, rng, P=P, **kw)
+    bf = lambda a: bits_to_bf16_tensor(oracle.f32_to_bf16_bits(a))
+    weights = {k: [bf(a) if k.startswith("w") else to_dev(a) for a in v] for k, v in per.items()}
+    weights.update({k: (bf(a) if k.startswith("w_") else to_dev(a)) for k, v in glob.items() for a in [v]})
+    kp = torch.randn((cfg["n_layers"], 1, P, cfg["n_kv"], cfg["head_dim"]), device="cuda")
+    vp = torch.randn_like(kp)
+    engines = [vb.PolicyEngine(cfg, weights, max_obs=max_obs, prefix_len=P) for _ in range(n_eng)]
+    for e in engines:  # the same prefix in every slot: what an observation computes then depends on its inputs only
+        for l in range(cfg["n_layers"]):
+            e.set_prefix(l, kp[l].expand(max_obs, -1, -1, -1).contiguous(), vp[l].expand(max_obs, -1, -1, -1).contiguous())
+    x0 = torch.randn((n_total, cfg["chunk"], cfg["action_dim"])).pin_memory()
+    state = torch.randn((n_total, cfg["state_dim"])).pin_memory()
+    out = torch.zeros_like(x0).pin_memory()
+    torch.cuda.synchronize()
+    arr = (C.c_void_p * n_eng)(*[e.h for e in engines])
+    rc = vb.lib().vlab200_engines_denoise_host(arr, n_eng, C.c_int64(n_total), C.c_void_p(state.data_ptr()),
+                                               C.c_void_p(x0.data_ptr()), C.c_void_p(out.data_ptr()), -1, None)
+    assert rc == 0, vb.lib().vlab200_last_error()
+    assert vb.device_status() == 0
+    for o in range(n_total):
+        alone = engines[0].denoise(x0[o:o + 1].cuda(), state[o:o + 1].cuda()).cpu()
+        assert torch.equal(alone[0], out[o]), o
+    # sharding arithmetic of the native helper
+    seen = []
+    for r in range(n_eng):
+        s, c = C.c_int64(), C.c_int64()
+        assert vb.lib().vlab200_shard_range(C.c_int64(n_total), n_eng, r, C.byref(s), C.byref(c)) == 0
+        seen += list(range(s.value, s.value + c.value))
+    assert seen == list(range(n_total))

@@ -76,7 +76,7 @@ EXPORTS = [
     "vlab200_denoise_attn_loop_static",
     "vlab200_engine_create", "vlab200_engine_free", "vlab200_engine_set_prefix", "vlab200_engine_denoise",
     "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_engine_set_prefix_len",
-    "vlab200_engine_get_prefix",
+    "vlab200_engine_get_prefix", "vlab200_shard_range", "vlab200_engines_denoise_host",
     "vlab200_prefill_create", "vlab200_prefill_free", "vlab200_prefill_run", "vlab200_set_gemm_tiling",
     "vlab200_act_quant", "vlab200_ternary_linear", "vlab200_ternarize_pack",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",

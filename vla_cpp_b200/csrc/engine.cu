@@ -13,6 +13,8 @@
 
 #include <cmath>
 #include <new>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "gemm.h"
@@ -151,6 +153,7 @@ constexpr int kFewRows = 256;  // suffix rows (n_obs * S) up to which the QKV pr
 // ------------------------------------------------------------------------ engine --
 struct vlab200_engine {
     vlab200_policy_config c;
+    int device = 0;  // the device that was current at creation: all of the engine's memory lives there
     int max_obs, P, P_max, S, cap, qf, kvf;  // P: rows of the prefix in use (<= P_max, the rows the pages were sized for)
     std::vector<int> is_self;
     // prepared weights
@@ -368,6 +371,7 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
         return nullptr;
     }
     e->c = c;
+    if (cudaGetDevice(&e->device) != cudaSuccess) e->device = 0;
     e->max_obs = max_obs;
     e->P = prefix_len;
     e->P_max = prefix_len;
@@ -526,6 +530,68 @@ int32_t vlab200_engine_get_prefix(vlab200_engine *e, int32_t layer, int32_t obs0
 int32_t vlab200_engine_set_prefix_len(vlab200_engine *e, int32_t prefix_len) {
     if (!e || prefix_len <= 0 || prefix_len > e->P_max) return VLAB200_ERR_ARG;
     e->P = prefix_len;
+    return VLAB200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------- several GPUs, one process --
+// Observations are independent (one predict = one observation, src/model.h:204-225): a list of them is cut into
+// contiguous blocks, one per engine (= per GPU, each with its weight replica and its own K/V pages); one host thread
+// and one stream per engine; nothing is exchanged between GPUs on the way.
+extern "C" {
+
+int32_t vlab200_shard_range(int64_t n_items, int32_t n_ranks, int32_t rank, int64_t *start, int64_t *count) {
+    if (!start || !count || n_items < 0 || n_ranks <= 0 || rank < 0 || rank >= n_ranks) return VLAB200_ERR_ARG;
+    const int64_t base = n_items / n_ranks, rem = n_items % n_ranks;
+    *count = base + (rank < rem ? 1 : 0);
+    *start = (int64_t)rank * base + (rank < rem ? rank : rem);
+    return VLAB200_OK;
+}
+
+int32_t vlab200_engines_denoise_host(vlab200_engine *const *engines, int32_t n_engines, int64_t n_obs,
+                                     const float *state_host, const float *x0_host, float *x_out_host, int32_t pos_base,
+                                     const int32_t *pad_ranges_host) {
+    if (!engines || n_engines <= 0 || n_obs < 0 || !x0_host || !x_out_host) return VLAB200_ERR_ARG;
+    for (int i = 0; i < n_engines; ++i)
+        if (!engines[i]) return VLAB200_ERR_ARG;
+    std::vector<int> rcs((size_t)n_engines, VLAB200_OK);
+    std::vector<std::string> errs((size_t)n_engines);
+    std::vector<std::thread> workers;
+    for (int r = 0; r < n_engines; ++r)
+        workers.emplace_back([&, r] {
+            vlab200_engine *e = engines[r];
+            int64_t start = 0, count = 0;
+            vlab200_shard_range(n_obs, n_engines, r, &start, &count);
+            auto fail = [&](int rc) {
+                rcs[(size_t)r] = rc;
+                errs[(size_t)r] = vlab200_last_error();
+            };
+            if (cudaSetDevice(e->device) != cudaSuccess) return fail(vb::cuda_fail(cudaGetLastError(), "cudaSetDevice"));
+            cudaStream_t st = nullptr;
+            if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess)
+                return fail(vb::cuda_fail(cudaGetLastError(), "cudaStreamCreate"));
+            const size_t xrow = (size_t)e->c.chunk * e->c.action_dim, srow = (size_t)e->c.state_dim;
+            int rc = VLAB200_OK;
+            // blocks of at most max_obs observations, one after the other on this engine's stream
+            for (int64_t done = 0; done < count && rc == VLAB200_OK; done += e->max_obs) {
+                const int64_t o = start + done;
+                const int32_t n = (int32_t)(count - done < e->max_obs ? count - done : e->max_obs);
+                rc = vlab200_engine_denoise_host(e, n, state_host ? state_host + (size_t)o * srow : nullptr, x0_host + (size_t)o * xrow,
+                                                 x_out_host + (size_t)o * xrow, pos_base,
+                                                 pad_ranges_host ? pad_ranges_host + (size_t)o * 2 : nullptr, st);
+                // the staging buffers are reused by the next block
+                if (rc == VLAB200_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = vb::cuda_fail(cudaGetLastError(), "cudaStreamSynchronize");
+            }
+            cudaStreamDestroy(st);
+            if (rc != VLAB200_OK) fail(rc);
+        });
+    for (std::thread &t : workers) t.join();
+    for (int r = 0; r < n_engines; ++r)
+        if (rcs[(size_t)r] != VLAB200_OK) {
+            vb::set_last_error("engine %d: %s", r, errs[(size_t)r].c_str());
+            return rcs[(size_t)r];
+        }
     return VLAB200_OK;
 }
 

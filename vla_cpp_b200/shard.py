@@ -10,12 +10,14 @@ import torch.distributed as dist
 
 def shard_range(n_total, world, rank):
     """Contiguous block [start, start + count) of rank `rank`; the first n_total % world ranks get one extra."""
-    if world <= 0 or not (0 <= rank < world) or n_total < 0:
+    import ctypes as C
+
+    from .api import lib
+
+    start, count = C.c_int64(0), C.c_int64(0)
+    if lib().vlab200_shard_range(C.c_int64(n_total), int(world), int(rank), C.byref(start), C.byref(count)) != 0:
         raise ValueError("bad sharding arguments")
-    base, rem = divmod(n_total, world)
-    count = base + (1 if rank < rem else 0)
-    start = rank * base + min(rank, rem)
-    return start, count
+    return start.value, count.value
 
 
 def max_over_ranks(values, device="cpu"):
