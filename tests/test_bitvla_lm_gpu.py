@@ -5,12 +5,14 @@ Bars:
   * fused norm/quant stage: the bf16 normalised row within 1 bf16 ulp of the oracle on <= 0.1 % of the
     elements (rsqrt and summation order), and the int8 row + scale bit-identical to the oracle's
     act-quant of that very row;
-  * whole stack: relative L2 <= 5e-2 on the bf16 output.  The stack re-quantises to int8 four times
-    per layer and squares the gate, so it amplifies ANY rounding difference in attention: moving one
-    bf16 rounding inside the oracle's own attention (probabilities rounded before instead of after
-    the division by the row sum) moves the oracle's output by 1.9e-2 .. 2.4e-2 on these cases, and
-    scaling every rounded tensor by 1 + 2^-12 moves it by 2.5e-2 (tests/test_oracle_bitvla_lm.py).  The CUDA attention keeps scores in float on chip
-    where the reference rounds them to bf16 in HBM, so it sits at that distance, not at 1e-3."""
+  * whole stack: relative L2 <= 5e-2 on the bf16 output against the CPU oracle.  The bar is derived from the
+    comparison with the reference's own CUDA forward (tests/test_bitvla_lm_ref_gpu.py, measured on B200 at the LM's
+    real width): reference vs this library 1.99e-2 (1 layer x 300 tokens) and 3.43e-2 (2 layers x 37 tokens),
+    reference vs the oracle 1.81e-2 / 3.26e-2, this library vs the oracle 1.97e-2 / 3.39e-2 -- three implementations
+    of the same arithmetic sit 2-3.5e-2 from one another on 1-2 layers, because every layer re-quantises to int8 four
+    times and squares the gate, which turns last-bit differences into flipped int8 codes.  5e-2 is that distance with
+    head-room of 1.5x; the per-stage tests below are bit-exact, and the stage-by-stage comparison with the reference's
+    layer-0 dump shows where the distance enters (attention: 4.4e-3, growing to 2e-2 at the layer output)."""
 import numpy as np
 import pytest
 
