@@ -805,8 +805,10 @@ def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
         "loop": {"tflops": loop_tf, "frac_of_sustained_bf16": loop_tf / peaks["bf16_tflops_sustained"],
                  "flops_per_chunk": policy_flops_per_chunk(c, P)},
         "stages": stages,
-        "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": x0h.numel() * 4 + sth.numel() * 4,
-                "d2h_bytes_per_step": outh.numel() * 4, "ms_per_step": e2e_ms},
+        # bytes of the whole job: every rank copies its own shard in and out
+        "e2e": {"value": n_global / (e2e_ms * 1e-3), "unit": "chunks/s",
+                "h2d_bytes_per_step": n_global * (c["chunk"] * 32 + 32) * 4, "d2h_bytes_per_step": n_global * c["chunk"] * 32 * 4,
+                "ms_per_step": e2e_ms},
     }
     del eng, x0, state
     torch.cuda.empty_cache()
