@@ -274,6 +274,44 @@ VLAB200_API int32_t vlab200_prefill_run(vlab200_prefill *p, vlab200_engine *e, i
                                         const float *x_emb, int32_t P, const int32_t *pos_host, int32_t mask_mode,
                                         const int32_t *pad_ranges, void *stream);
 
+/* ---- vision tower: camera views -> image-token embeddings of the prefix ------------------------------
+ * SigLIP encoder + connector of the reference's towers (src/models/smolvla.cpp:394-426 block, :1511-1563
+ * patch embedding / layers / post-LayerNorm / pixel shuffle / connector; src/models/pi0.cpp:130-155,479-517 the
+ * same block with a biased linear projector and a 1/sqrt(out) scale; preprocessing and pixel-shuffle order of
+ * src/modules/preprocess.h:37-75).  Block = LayerNorm -> q,k,v (+bias) -> unmasked attention -> Wo (+bias) +
+ * residual -> LayerNorm -> fc1 (+bias) -> tanh-GELU -> fc2 (+bias) + residual.  All weights are device pointers:
+ * matrices bf16 [out][in] (patch_w = the conv kernel [hidden][3][patch][patch] flattened), vectors float32;
+ * per-layer entries are host arrays of n_layers device pointers; prepared copies are kept.
+ * shuffle: pixel-shuffle factor of the connector (1 = none; the connector then is [out_dim][hidden]); with
+ * shuffle = s it is [out_dim][hidden * s * s] in the channel-innermost order of pixel_shuffle_hf.
+ * connector_b optional.  out_scale: factor on the connector's output (pi0: 1 / sqrt(out_dim); 0 or 1 = none).
+ * head_dim = hidden / n_heads; 64 / 128 / 256 run as they are, any other even value <= 256 is zero-padded to the
+ * next of them in the prepared weights.
+ * vlab200_vision_run: pixels = DEVICE buffer [n_views][image][image][3], uint8 (0..255) or float32 (0..1) in
+ * H, W, C order (vla_image's layout); x -> x / 255 (uint8 only) -> 2 x - 1.  img_emb: float32 device
+ * [n_views * tokens_per_view][out_dim], the tensor vla_inputs.precomputed_img_emb would carry. */
+typedef struct {
+    int32_t image, patch, hidden, n_layers, n_heads, inter, shuffle, out_dim;
+    float ln_eps, out_scale;
+} vlab200_vision_config;
+typedef struct {
+    const void *patch_w;
+    const float *patch_b, *pos; /* [hidden], [n_patches][hidden] */
+    const float *const *ln1_w, *const *ln1_b, *const *ln2_w, *const *ln2_b;
+    const void *const *wq, *const *wk, *const *wv, *const *wo, *const *fc1, *const *fc2;
+    const float *const *bq, *const *bk, *const *bv, *const *bo, *const *b1, *const *b2;
+    const float *post_w, *post_b;
+    const void *connector;
+    const float *connector_b;
+} vlab200_vision_weights;
+typedef struct vlab200_vision vlab200_vision;
+VLAB200_API vlab200_vision *vlab200_vision_create(const vlab200_vision_config *cfg, const vlab200_vision_weights *w,
+                                                  int32_t max_views);
+VLAB200_API void vlab200_vision_free(vlab200_vision *v);
+VLAB200_API int32_t vlab200_vision_tokens_per_view(const vlab200_vision *v);
+VLAB200_API int32_t vlab200_vision_run(vlab200_vision *v, const void *pixels, int32_t pixels_f32, int32_t n_views,
+                                       float *img_emb, void *stream);
+
 /* Several GPUs in one process.  vlab200_shard_range: the contiguous block [start, start + count) of `rank` when
  * n_items independent observations are cut over n_ranks (the first n_items % n_ranks ranks get one more).
  * vlab200_engines_denoise_host: n_obs observations in (pinned) host memory through n_engines engines, each

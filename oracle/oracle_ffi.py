@@ -236,6 +236,75 @@ def vlm_prefill(x, layers, cfg, pos=None, mask_mode=MASK_NONE, pad=(0, 0)):
     return ks, vs
 
 
+# ---- vision tower (numpy float32): SigLIP encoder + connector ----
+
+def preprocess_image_chw(img):
+    """img: [side][side][3] uint8 (0..255) or float32 (0..1), H W C -> float32 [3][side][side] in [-1, 1]
+    (src/modules/preprocess.h:56-75: px = u8 / 255.0f, out = px * 2 - 1)."""
+    img = np.asarray(img)
+    px = img.astype(np.float32) / np.float32(255.0) if img.dtype == np.uint8 else img.astype(np.float32)
+    return np.ascontiguousarray((px * np.float32(2.0) - np.float32(1.0)).transpose(2, 0, 1))
+
+
+def pixel_shuffle_hf(src, grid, s):
+    """src: [grid * grid][embed] -> [(grid / s)^2][embed * s * s], channel innermost
+    (src/modules/preprocess.h:37-52): token (h2, w2) column block hs * s + ws <- patch (h2 s + hs, w2 s + ws)."""
+    src = np.asarray(src, np.float32)
+    embed = src.shape[1]
+    g2 = grid // s
+    x = src.reshape(g2, s, g2, s, embed).transpose(0, 2, 1, 3, 4)  # [h2][w2][hs][ws][e]
+    return np.ascontiguousarray(x.reshape(g2 * g2, s * s * embed))
+
+
+def layer_norm(x, w, b, eps):
+    """ggml_norm followed by weight and bias (src/models/smolvla.cpp:397): mean, variance of the centred values."""
+    x = np.asarray(x, np.float32)
+    mean = x.mean(axis=1, dtype=np.float32, keepdims=True)
+    d = x - mean
+    var = (d * d).mean(axis=1, dtype=np.float32, keepdims=True)
+    return (d * (np.float32(1) / np.sqrt(var + np.float32(eps))) * w + b).astype(np.float32)
+
+
+def gelu_tanh(x):
+    c0 = np.float32(0.79788456080286535588)
+    return np.float32(0.5) * x * (np.float32(1) + np.tanh(c0 * (x + np.float32(0.044715) * x * x * x), dtype=np.float32))
+
+
+def siglip_tower(img, w, cfg):
+    """One camera view -> its image-token embeddings [n_tokens][out_dim].
+
+    Patch embedding (a stride-P convolution = a linear map over flattened patches), position embedding, encoder
+    blocks, post-LayerNorm: src/models/smolvla.cpp:1511-1524 with the block of :394-426; pixel shuffle and the
+    bias-free connector :1533-1563; pi0's variant (src/models/pi0.cpp:479-499) has no shuffle, an optional
+    connector bias and scales the result by 1/sqrt(out_dim).
+    w: patch_w [hidden][3][P][P], patch_b, pos [n_patches][hidden], layers (list of dicts ln1_w, ln1_b, wq, bq, wk,
+    bk, wv, bv, wo, bo, ln2_w, ln2_b, fc1, b1, fc2, b2), post_w, post_b, connector, connector_b (or None).
+    cfg: image, patch, hidden, n_heads, shuffle, ln_eps, out_scale."""
+    P, side, H, heads = cfg["patch"], cfg["image"], cfg["hidden"], cfg["n_heads"]
+    g = side // P
+    hd = H // heads
+    chw = preprocess_image_chw(img)
+    patches = chw.reshape(3, g, P, g, P).transpose(1, 3, 0, 2, 4).reshape(g * g, 3 * P * P)
+    h = linear(patches, np.asarray(w["patch_w"], np.float32).reshape(H, -1), w["patch_b"]) + w["pos"]
+    n = g * g
+    for lw in w["layers"]:
+        n1 = layer_norm(h, lw["ln1_w"], lw["ln1_b"], cfg["ln_eps"])
+        q = linear(n1, lw["wq"], lw["bq"]).reshape(n, heads, hd)
+        k = linear(n1, lw["wk"], lw["bk"]).reshape(n, heads, hd)
+        v = linear(n1, lw["wv"], lw["bv"]).reshape(n, heads, hd)
+        att = attention(q, k, v, 0, MASK_NONE)
+        h = h + linear(att, lw["wo"], lw["bo"])
+        n2 = layer_norm(h, lw["ln2_w"], lw["ln2_b"], cfg["ln_eps"])
+        h = h + linear(gelu_tanh(linear(n2, lw["fc1"], lw["b1"])), lw["fc2"], lw["b2"])
+    post = layer_norm(h, w["post_w"], w["post_b"], cfg["ln_eps"])
+    s = cfg.get("shuffle", 1)
+    if s > 1:
+        post = pixel_shuffle_hf(post, g, s)
+    out = linear(post, w["connector"], w.get("connector_b"))
+    sc = cfg.get("out_scale", 0.0)
+    return out * np.float32(sc) if sc not in (0.0, 1.0) else out
+
+
 class DenoiseCfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "model", "n_layers", "H", "n_q", "n_kv", "hd", "inter", "P", "chunk", "A", "state_dim", "T",

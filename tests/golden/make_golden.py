@@ -123,6 +123,12 @@ def gguf_names(ref):
     cb._add_bit(r, "lm.blk.0.attn_q", w)
     cb._add_bit_fused(r, "lm.blk.0.ffn_gate_up", [w, w])
     out["bitvla"] = {"packed": r.tensors, "packed_flag_key": "bitvla.quant.int2_packed"}
+    # the SigLIP tower as both converters write it (scripts/gguf_blocks.py write_siglip_tower / write_paligemma_vision,
+    # scripts/convert_smolvla_to_gguf.py:213-214), one layer
+    r = _Recorder()
+    gb.write_siglip_tower(r, tiny, "root", 1, f32_norms=True)
+    out["vision"] = {"tower": r.tensors, "connector_smolvla": ["mm.fc.weight"],
+                     "connector_pi0": ["mm.proj.weight", "mm.proj.bias"]}
     json.dump(out, open(os.path.join(HERE, "gguf_names.json"), "w"), indent=1)
 
 

@@ -17,6 +17,7 @@ from .api import (  # noqa: F401
     KvStore,
     PolicyEngine,
     Prefill,
+    VisionTower,
     VlaB200Error,
     act_quant,
     attention,

@@ -40,6 +40,9 @@ def lib():
         L.vlab200_engine_free.restype = None
         L.vlab200_prefill_create.restype = C.c_void_p
         L.vlab200_prefill_free.restype = None
+        L.vlab200_vision_create.restype = C.c_void_p
+        L.vlab200_vision_free.restype = None
+        L.vlab200_vision_tokens_per_view.argtypes = [C.c_void_p]
         L.vlab200_bitvla_lm_init.restype = C.c_void_p
         L.vlab200_bitvla_lm_init.argtypes = [C.c_int32] * 6 + [C.c_float, C.c_float, C.c_int32, C.c_int32]
         L.vlab200_bitvla_lm_free.restype = None
@@ -78,6 +81,7 @@ EXPORTS = [
     "vlab200_engine_denoise_host", "vlab200_engine_run_stage", "vlab200_engine_set_prefix_len",
     "vlab200_engine_get_prefix", "vlab200_shard_range", "vlab200_engines_denoise_host",
     "vlab200_prefill_create", "vlab200_prefill_free", "vlab200_prefill_run", "vlab200_set_gemm_tiling",
+    "vlab200_vision_create", "vlab200_vision_free", "vlab200_vision_tokens_per_view", "vlab200_vision_run",
     "vlab200_act_quant", "vlab200_ternary_linear", "vlab200_ternarize_pack",
     "vlab200_bitvla_lm_init", "vlab200_bitvla_lm_free", "vlab200_bitvla_lm_set_layer",
     "vlab200_bitvla_lm_set_output_norm", "vlab200_bitvla_lm_forward", "vlab200_bitvla_norm_quant",
@@ -563,6 +567,78 @@ class Prefill:
                                          pos.ctypes.data_as(C.c_void_p) if pos is not None else None, mask_mode,
                                          _ptr(pad_ranges), _stream()), "vlab200_prefill_run")
         torch.cuda.synchronize()  # pos (host memory) must outlive the copy enqueued on the stream
+
+
+class _VisionConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("image", "patch", "hidden", "n_layers", "n_heads", "inter", "shuffle",
+                                         "out_dim")] + [("ln_eps", C.c_float), ("out_scale", C.c_float)]
+
+
+_VISION_LAYER_VECS = ("ln1_w", "ln1_b", "ln2_w", "ln2_b")
+_VISION_LAYER_MATS = ("wq", "wk", "wv", "wo", "fc1", "fc2")
+_VISION_LAYER_BIAS = ("bq", "bk", "bv", "bo", "b1", "b2")
+
+
+class _VisionWeights(C.Structure):
+    _fields_ = ([("patch_w", C.c_void_p), ("patch_b", C.c_void_p), ("pos", C.c_void_p)] +
+                [(n, C.POINTER(C.c_void_p)) for n in _VISION_LAYER_VECS + _VISION_LAYER_MATS + _VISION_LAYER_BIAS] +
+                [("post_w", C.c_void_p), ("post_b", C.c_void_p), ("connector", C.c_void_p), ("connector_b", C.c_void_p)])
+
+
+class VisionTower:
+    """SigLIP encoder + connector: camera views -> the image-token embeddings of the prefix.
+
+    cfg: dict with the vlab200_vision_config fields; weights: patch_w (cuda bf16 [hidden, 3 * patch * patch]),
+    patch_b, pos, post_w, post_b (cuda float32), connector (cuda bf16 [out_dim, hidden * shuffle^2]), optional
+    connector_b, and per-layer lists ln1_w, ln1_b, ln2_w, ln2_b, bq, bk, bv, bo, b1, b2 (float32), wq, wk, wv, wo,
+    fc1, fc2 (bf16 [out, in])."""
+
+    def __init__(self, cfg, weights, max_views=4):
+        import torch
+
+        c = _VisionConfig(**{k: cfg[k] for k, _ in _VisionConfig._fields_})
+        w = _VisionWeights()
+        keep = []
+        for name in ("patch_w", "patch_b", "pos", "post_w", "post_b", "connector", "connector_b"):
+            t = weights.get(name)
+            if t is None:
+                continue
+            t = t.contiguous()
+            assert t.is_cuda and t.dtype == (torch.bfloat16 if name in ("patch_w", "connector") else torch.float32), name
+            keep.append(t)
+            setattr(w, name, t.data_ptr())
+        for name in _VISION_LAYER_VECS + _VISION_LAYER_MATS + _VISION_LAYER_BIAS:
+            ts = [t.contiguous() for t in weights[name]]
+            want = torch.bfloat16 if name in _VISION_LAYER_MATS else torch.float32
+            assert len(ts) == cfg["n_layers"] and all(t.is_cuda and t.dtype == want for t in ts), name
+            arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+            keep += [ts, arr]
+            setattr(w, name, C.cast(arr, C.POINTER(C.c_void_p)))
+        self.cfg = dict(cfg)
+        self.h = lib().vlab200_vision_create(C.byref(c), C.byref(w), max_views)
+        torch.cuda.synchronize()
+        del keep
+        if not self.h:
+            raise VlaB200Error(ERR_CUDA, "vlab200_vision_create: " + lib().vlab200_last_error().decode())
+        self.tokens_per_view = lib().vlab200_vision_tokens_per_view(C.c_void_p(self.h))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().vlab200_vision_free(C.c_void_p(self.h))
+            self.h = None
+
+    def run(self, pixels):
+        """pixels: cuda uint8 (0..255) or float32 (0..1) [n_views, image, image, 3] -> float32 [n_views * tokens, out_dim]."""
+        import torch
+
+        assert pixels.is_cuda and pixels.is_contiguous() and pixels.dtype in (torch.uint8, torch.float32)
+        side = self.cfg["image"]
+        assert tuple(pixels.shape[1:]) == (side, side, 3), pixels.shape
+        n_views = pixels.shape[0]
+        out = torch.empty((n_views * self.tokens_per_view, self.cfg["out_dim"]), dtype=torch.float32, device=pixels.device)
+        _check(lib().vlab200_vision_run(C.c_void_p(self.h), _ptr(pixels), 1 if pixels.dtype == torch.float32 else 0, n_views,
+                                        _ptr(out), _stream()), "vlab200_vision_run")
+        return out
 
 
 NQ_PLAIN, NQ_ADD, NQ_GATE_UP = 0, 1, 2

@@ -344,13 +344,22 @@ struct Upload {
     std::vector<uint16_t> tmp16;
     bool ok = true;
 
-    // Reads `name` (f32 / f16 / bf16), checks its shape ([d1][d0], d1 == 1 for vectors), optional Gemma "+1",
+    // Reads `name` (f32 / f16 / bf16), checks its shape ([d1][d0], d1 == 1 for vectors, d1 < 0: d0 elements of any
+    // shape), optional Gemma "+1",
     // converts matrices to bf16 (round to nearest even) and copies to the device.
     const void *get(const vlab200_gguf *g, const std::string &name, int64_t d0, int64_t d1, bool as_bf16, bool gemma) {
         if (!ok) return nullptr;
         const GgufTensor *t = find_tensor(g, name.c_str());
         if (!t) return fail("gguf: missing tensor %s", name);
-        if (t->dims[0] != d0 || t->dims[1] != d1 || t->dims[2] != 1 || t->dims[3] != 1) {
+        if (d1 < 0) {  // any shape with d0 elements in all (a convolution kernel kept as the file lays it out)
+            if (t->dims[0] * t->dims[1] * t->dims[2] * t->dims[3] != d0) {
+                set_last_error("gguf: tensor %s has %lld elements, expected %lld", name.c_str(),
+                               (long long)(t->dims[0] * t->dims[1] * t->dims[2] * t->dims[3]), (long long)d0);
+                ok = false;
+                return nullptr;
+            }
+            d1 = 1;
+        } else if (t->dims[0] != d0 || t->dims[1] != d1 || t->dims[2] != 1 || t->dims[3] != 1) {
             set_last_error("gguf: tensor %s is [%lld][%lld], expected [%lld][%lld]", name.c_str(), (long long)t->dims[1],
                            (long long)t->dims[0], (long long)d1, (long long)d0);
             ok = false;

@@ -88,7 +88,7 @@ struct DevBuf {
     }
 };
 
-// A checkpoint tensor ([d1][d0], d1 == 1 for vectors; f32 / f16 / bf16 in the file) uploaded as bf16 or float32,
+// A checkpoint tensor ([d1][d0], d1 == 1 for vectors, d1 < 0: d0 elements of any shape; f32 / f16 / bf16 in the file) uploaded as bf16 or float32,
 // optionally with the Gemma-norm "+1" (gguf.cu).  VLAB200_OK or an error with the last-error text set.
 int gguf_upload(const vlab200_gguf *g, const char *name, int64_t d0, int64_t d1, bool as_bf16, bool gemma, DevBuf *out);
 

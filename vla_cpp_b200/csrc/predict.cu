@@ -7,7 +7,8 @@
 //   SmolVLA  prefix = [image embeddings * sqrt(hidden) ; E[lang padded to n_lang_max] * sqrt(hidden) ; state_proj(state)],
 //            padded language slots masked, the state token visible to itself only and rotated at position
 //            n_img + n_lang; suffix positions start one past it
-// Image embeddings come from vla_inputs.precomputed_img_emb; the vision tower is not part of this library.
+// Image embeddings come from vla_inputs.precomputed_img_emb or, when the checkpoint carries the SigLIP tower
+// ("vit.*" and "mm.*" tensors), from vla_inputs.images through the vision tower (vision.cu).
 #include "predict.h"
 
 #include <cuda_bf16.h>
@@ -28,10 +29,13 @@ struct Predictor {
     int64_t vocab = 0;
     int max_prefix = 0, max_views = 4;
     std::vector<float> state_mean, state_std, action_mean, action_std;
-    DevBuf x_emb, ids, img_stage, state_dev, pads;
+    DevBuf x_emb, ids, img_stage, state_dev, pads, pixels;
+    vlab200_vision *vis = nullptr;
+    int vit_image = 0;
     std::mt19937 rng{std::random_device{}()};
-    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     ~Predictor() {
+        vlab200_vision_free(vis);
         vlab200_prefill_free(pre);
         vlab200_engine_free(eng);
         for (cudaEvent_t e : ev)
@@ -67,6 +71,98 @@ static void read_stats(const vlab200_gguf *g, const char *name, std::vector<floa
     // missing or mis-sized statistics mean identity, as in load_stats (src/models/pi0.cpp:300-329)
     std::vector<float> tmp(dst.size());
     if (!tmp.empty() && vlab200_gguf_read_f32(g, name, tmp.data(), (int64_t)tmp.size(), 0) == VLAB200_OK) dst = tmp;
+}
+
+// The SigLIP tower and its connector from the checkpoint: geometry keys and defaults of src/models/smolvla.cpp:320-322,
+// 985-1004 and src/models/pi0.cpp:93-95,402-414; tensor names of smolvla.cpp:705-747 (hf_to_gguf) and
+// src/modules/siglip_vit.cpp:23-34, src/modules/encoder.cpp:25-48; connector "mm.fc.weight" (SmolVLA, after the
+// pixel shuffle) or "mm.proj.weight" / "mm.proj.bias" (pi0, scaled by 1/sqrt(hidden), pi0.cpp:494-498).
+static bool load_tower(Predictor *p, const vlab200_gguf *g) {
+    const bool smol = p->arch == 1;
+    const vla_config &c = p->cfg;
+    const std::string pfx = smol ? "smolvla." : "pi0.";
+    int64_t vh = smol ? 768 : 1152, vl = smol ? 12 : 27, heads = smol ? 12 : 16, patch = smol ? 16 : 14,
+            image = smol ? 512 : 224, shuffle = smol ? 4 : 1, inter = smol ? 3072 : 0, n_tok = smol ? 64 : 256;
+    auto vu = [&](const char *k, int64_t &d) {
+        uint32_t u = 0;
+        if (vlab200_gguf_meta_u32(g, (pfx + k).c_str(), &u) == VLAB200_OK) d = u;
+    };
+    vu("vit_hidden", vh); vu("vit_layers", vl); vu("vit_heads", heads); vu("patch_size", patch); vu("image_size", image);
+    vu("n_img_tokens", n_tok);
+    if (smol) { vu("vit_pixel_shuffle", shuffle); vu("vit_inter", inter); }
+    double dv = 0;
+    const float eps = vlab200_gguf_meta_f64(g, (pfx + "vit_ln_eps").c_str(), &dv) == VLAB200_OK ? (float)dv : 1e-6f;
+    if (!smol) {  // the MLP width is the checkpoint's: rows of fc1
+        int32_t type = 0, nd = 0;
+        int64_t dims[4] = {0, 0, 0, 0};
+        uint64_t nb = 0;
+        if (vlab200_gguf_tensor_info(g, "vit.blk.0.fc1.weight", &type, &nd, dims, &nb) != VLAB200_OK) return false;
+        inter = dims[1];
+    }
+    if (vh <= 0 || vl <= 0 || vl > 256 || heads <= 0 || patch <= 0 || image <= 0 || shuffle <= 0 || inter <= 0 || image % patch) {
+        set_last_error("vla_predict: bad vision geometry in the checkpoint");
+        return false;
+    }
+    const int64_t grid = image / patch, np = grid * grid;
+    if (grid % shuffle || (grid / shuffle) * (grid / shuffle) != n_tok || n_tok != c.n_img) {
+        set_last_error("vla_predict: vit geometry mismatch (grid %lld, shuffle %lld, n_img_tokens %lld, n_img %lld)", (long long)grid,
+                       (long long)shuffle, (long long)n_tok, (long long)c.n_img);
+        return false;
+    }
+    const int L = (int)vl;
+    const int64_t c4 = vh * shuffle * shuffle;
+    std::vector<DevBuf> bufs((size_t)L * 16 + 8);
+    bool ok = true;
+    auto up = [&](size_t slot, const std::string &name, int64_t d0, int64_t d1, bool bf) -> const void * {
+        if (ok && gguf_upload(g, name.c_str(), d0, d1, bf, false, &bufs[slot]) != VLAB200_OK) ok = false;
+        return bufs[slot].p;
+    };
+    vlab200_vision_weights w{};
+    const size_t G = (size_t)L * 16;
+    w.patch_w = up(G + 0, "vit.patch_embd.weight", vh * 3 * patch * patch, -1, true);
+    w.patch_b = static_cast<const float *>(up(G + 1, "vit.patch_embd.bias", vh, 1, false));
+    w.pos = static_cast<const float *>(up(G + 2, "vit.pos_embd", vh, np, false));
+    w.post_w = static_cast<const float *>(up(G + 3, "vit.post_ln.weight", vh, 1, false));
+    w.post_b = static_cast<const float *>(up(G + 4, "vit.post_ln.bias", vh, 1, false));
+    if (smol) {
+        w.connector = up(G + 5, "mm.fc.weight", c4, c.hidden, true);
+    } else {
+        w.connector = up(G + 5, "mm.proj.weight", c4, c.hidden, true);
+        int32_t type = 0, nd = 0;
+        int64_t dims[4] = {0, 0, 0, 0};
+        uint64_t nb = 0;
+        if (vlab200_gguf_tensor_info(g, "mm.proj.bias", &type, &nd, dims, &nb) == VLAB200_OK)
+            w.connector_b = static_cast<const float *>(up(G + 6, "mm.proj.bias", c.hidden, 1, false));
+    }
+    std::vector<const void *> mats[6];
+    std::vector<const float *> vecs[10];
+    for (auto &m : mats) m.resize((size_t)L);
+    for (auto &v : vecs) v.resize((size_t)L);
+    static const char *mat_names[6] = {"attn_q", "attn_k", "attn_v", "attn_o", "fc1", "fc2"};
+    static const char *vec_names[10] = {"ln1.weight", "ln1.bias", "ln2.weight", "ln2.bias", "attn_q.bias", "attn_k.bias",
+                                        "attn_v.bias", "attn_o.bias", "fc1.bias", "fc2.bias"};
+    for (int l = 0; l < L && ok; ++l) {
+        const std::string b = "vit.blk." + std::to_string(l) + ".";
+        for (int j = 0; j < 6; ++j) {
+            const int64_t d0 = j == 5 ? inter : vh, d1 = j == 4 ? inter : vh;
+            mats[j][(size_t)l] = up((size_t)l * 16 + j, b + mat_names[j] + ".weight", d0, d1, true);
+        }
+        for (int j = 0; j < 10; ++j)
+            vecs[j][(size_t)l] = static_cast<const float *>(up((size_t)l * 16 + 6 + j, b + vec_names[j], j == 8 ? inter : vh, 1, false));
+    }
+    if (!ok) return false;
+    w.wq = mats[0].data(); w.wk = mats[1].data(); w.wv = mats[2].data(); w.wo = mats[3].data();
+    w.fc1 = mats[4].data(); w.fc2 = mats[5].data();
+    w.ln1_w = vecs[0].data(); w.ln1_b = vecs[1].data(); w.ln2_w = vecs[2].data(); w.ln2_b = vecs[3].data();
+    w.bq = vecs[4].data(); w.bk = vecs[5].data(); w.bv = vecs[6].data(); w.bo = vecs[7].data();
+    w.b1 = vecs[8].data(); w.b2 = vecs[9].data();
+    vlab200_vision_config vc{};
+    vc.image = (int)image; vc.patch = (int)patch; vc.hidden = (int)vh; vc.n_layers = L; vc.n_heads = (int)heads;
+    vc.inter = (int)inter; vc.shuffle = (int)shuffle; vc.out_dim = (int)c.hidden; vc.ln_eps = eps;
+    vc.out_scale = smol ? 0.0f : 1.0f / std::sqrt((float)c.hidden);
+    p->vis = vlab200_vision_create(&vc, &w, p->max_views);
+    p->vit_image = (int)image;
+    return p->vis != nullptr && p->pixels.alloc((size_t)p->max_views * image * image * 3 * 4) == VLAB200_OK;
 }
 
 Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_config *cfg) {
@@ -145,7 +241,13 @@ Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_c
         ok = p->x_emb.alloc((size_t)p->max_prefix * H * 4) == VLAB200_OK && p->ids.alloc((size_t)c.n_lang * 4) == VLAB200_OK &&
              p->img_stage.alloc((size_t)n_img_max * H * 4) == VLAB200_OK &&
              p->state_dev.alloc((size_t)c.max_state_dim * 4) == VLAB200_OK && p->pads.alloc(8) == VLAB200_OK;
-    for (int i = 0; ok && i < 3; ++i) ok = cudaEventCreate(&p->ev[i]) == cudaSuccess;
+    for (int i = 0; ok && i < 4; ++i) ok = cudaEventCreate(&p->ev[i]) == cudaSuccess;
+    if (ok) {  // the tower is optional: a checkpoint without it serves precomputed image embeddings only
+        int32_t type = 0, nd = 0;
+        int64_t dims[4] = {0, 0, 0, 0};
+        uint64_t nb = 0;
+        if (vlab200_gguf_tensor_info(g, "vit.patch_embd.weight", &type, &nd, dims, &nb) == VLAB200_OK) ok = load_tower(p, g);
+    }
     if (!ok) {
         delete p;
         return nullptr;
@@ -158,13 +260,26 @@ void predictor_free(Predictor *p) { delete p; }
 int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *actions, vla_stats *stats) {
     const vla_config &c = p->cfg;
     const int H = (int)c.hidden, sd = (int)c.max_state_dim, ad = (int)c.max_action_dim, chunk = (int)c.n_suffix;
-    if (!in->precomputed_img_emb) {
-        set_last_error("vla_predict: pass vla_inputs.precomputed_img_emb; the vision tower is not part of this library");
+    const bool from_pixels = !in->precomputed_img_emb;
+    const int n_views = from_pixels ? in->n_images : in->n_img_views;
+    if (from_pixels && !p->vis) {
+        set_last_error("vla_predict: the checkpoint has no vision tower (vit.* tensors); pass vla_inputs.precomputed_img_emb");
         return VLAB200_ERR_UNSUPPORTED;
     }
-    if (in->n_img_views < 1 || in->n_img_views > p->max_views) {
-        set_last_error("vla_predict: n_img_views = %d outside [1, %d]", in->n_img_views, p->max_views);
+    if (n_views < 1 || n_views > p->max_views) {
+        set_last_error("vla_predict: %d camera views outside [1, %d]", n_views, p->max_views);
         return VLAB200_ERR_ARG;
+    }
+    if (from_pixels) {
+        if (!in->images) return VLAB200_ERR_ARG;
+        for (int v = 0; v < n_views; ++v) {
+            const vla_image &im = in->images[v];
+            // a view of another size would be read past its end (src/modules/preprocess.h:30-32,58-62)
+            if (!im.data || im.w != p->vit_image || im.h != p->vit_image || (im.format != VLA_PIXEL_U8 && im.format != VLA_PIXEL_F32_RGB_01)) {
+                set_last_error("vla_predict: image view %d is %dx%d, expected %dx%d", v, im.w, im.h, p->vit_image, p->vit_image);
+                return VLAB200_ERR_ARG;
+            }
+        }
     }
     // language tokens index the embedding table: reject ids outside it (src/models/smolvla.cpp:1579-1589)
     const int n_lang = in->n_lang;
@@ -179,7 +294,7 @@ int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *action
             return VLAB200_ERR_ARG;
         }
     cudaStream_t cs = nullptr;
-    const int n_img = (int)c.n_img * in->n_img_views;
+    const int n_img = (int)c.n_img * n_views;
     const int n_lang_rows = p->arch == 1 ? (int)c.n_lang : n_lang;  // SmolVLA pads the language block
     const int P = n_img + n_lang_rows + (p->arch == 1 ? 1 : 0);
     const float lang_scale = p->arch == 1 ? std::sqrt((float)H) : (float)std::sqrt((double)H);
@@ -198,7 +313,32 @@ int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *action
     std::vector<int32_t> ids((size_t)n_lang_rows, 0);
     std::memcpy(ids.data(), in->lang_tokens, (size_t)n_lang * sizeof(int32_t));
     const bool timed = in->timing_detail == VLA_TIMING_PHASE;
-    VB_CUDA(cudaMemcpyAsync(p->img_stage.p, in->precomputed_img_emb, (size_t)n_img * H * 4, cudaMemcpyHostToDevice, cs));
+    int rc;
+    if (from_pixels) {
+        // views of one pixel format go through the tower together, mixed formats one view at a time
+        if (timed) VB_CUDA(cudaEventRecord(p->ev[3], cs));
+        bool same = true;
+        for (int v = 1; v < n_views; ++v) same = same && in->images[v].format == in->images[0].format;
+        const size_t px = (size_t)p->vit_image * p->vit_image * 3;
+        if (same) {
+            const size_t bytes = px * (in->images[0].format == VLA_PIXEL_U8 ? 1 : 4);
+            for (int v = 0; v < n_views; ++v)
+                VB_CUDA(cudaMemcpyAsync(static_cast<char *>(p->pixels.p) + (size_t)v * bytes, in->images[v].data, bytes,
+                                        cudaMemcpyHostToDevice, cs));
+            if ((rc = vlab200_vision_run(p->vis, p->pixels.p, in->images[0].format == VLA_PIXEL_F32_RGB_01, n_views,
+                                         p->img_stage.as<float>(), cs)))
+                return rc;
+        } else {
+            for (int v = 0; v < n_views; ++v) {
+                const bool f32 = in->images[v].format == VLA_PIXEL_F32_RGB_01;
+                char *dst = static_cast<char *>(p->pixels.p) + (size_t)v * px * 4;
+                VB_CUDA(cudaMemcpyAsync(dst, in->images[v].data, px * (f32 ? 4 : 1), cudaMemcpyHostToDevice, cs));
+                if ((rc = vlab200_vision_run(p->vis, dst, f32, 1, p->img_stage.as<float>() + (size_t)v * c.n_img * H, cs))) return rc;
+            }
+        }
+    } else {
+        VB_CUDA(cudaMemcpyAsync(p->img_stage.p, in->precomputed_img_emb, (size_t)n_img * H * 4, cudaMemcpyHostToDevice, cs));
+    }
     VB_CUDA(cudaMemcpyAsync(p->ids.p, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice, cs));
     VB_CUDA(cudaMemcpyAsync(p->state_dev.p, state.data(), (size_t)sd * 4, cudaMemcpyHostToDevice, cs));
     if (timed) VB_CUDA(cudaEventRecord(p->ev[0], cs));
@@ -207,7 +347,6 @@ int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *action
     scale_copy_kernel<<<148, 256, 0, cs>>>(p->img_stage.as<float>(), p->arch == 1 ? lang_scale : 1.0f, x, (size_t)n_img * H);
     embed_rows_kernel<<<n_lang_rows, 256, 0, cs>>>(p->token_embd.as<__nv_bfloat16>(), p->ids.as<int32_t>(), lang_scale,
                                                    x + (size_t)n_img * H, n_lang_rows, H);
-    int rc;
     int32_t pad[2] = {0, 0};
     std::vector<int32_t> pos;
     int pos_base = -1;
@@ -251,6 +390,7 @@ int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *action
         cudaEventElapsedTime(&stats->ms_prefill, p->ev[0], p->ev[1]);
         cudaEventElapsedTime(&stats->ms_denoise, p->ev[1], p->ev[2]);
         stats->ms_inference = stats->ms_prefill + stats->ms_denoise;
+        if (from_pixels) cudaEventElapsedTime(&stats->ms_vision, p->ev[3], p->ev[0]);
     }
     return VLAB200_OK;
 }
