@@ -664,6 +664,15 @@ def run_reference(args, rank, world):
         times = [oracle_chunk(orc, rng, 1) for _ in range(args.steps)]
         config = attn_config_dict(1, 1)
         sample = "1 observation (chunk) per step: 10 steps x 16 layers of QKV+RoPE+attention"
+    elif args.workload.endswith("_predict"):
+        from vla_cpp_b200 import synth_gguf
+
+        arch = args.workload.split("_")[0]
+        d = dict(synth_gguf.SMOLVLA_DIMS if arch == "smolvla" else synth_gguf.PI0_DIMS)
+        n_views = 2 if arch == "smolvla" else 3
+        times = [sum(oracle_predict_seconds(orc, d, arch, n_views)) for _ in range(max(args.steps, 1))]
+        config = {"workload": f"{arch}_predict: one whole request (vision tower per view, backbone prefill, denoise loop), batch 1"}
+        sample = "1 whole request per step with float32 weights and activations"
     else:
         workload = args.workload if args.workload in POLICIES else "pi0"
         loop = OraclePolicyLoop(orc, workload, seed=1)
@@ -952,6 +961,140 @@ def measure_smolvla_attn(torch, vb, dist, dev, args, rank, world, barrier, with_
     return line
 
 
+def predict_inputs(d, arch):
+    """The request of BASELINE configs[0] (SmolVLA: 2 views, 48 token ids) / configs[2] (pi0: 3 views, 48 token ids),
+    seeds 0..3 for the images, the tokens, the state and the noise."""
+    side = d["image_size"]
+    n_views = 2 if arch == "smolvla" else 3
+    images = [np.random.default_rng(v).integers(0, 256, (side, side, 3), dtype=np.uint8) for v in range(n_views)]
+    lang = np.random.default_rng(1).integers(0, d["vocab_size"], d["tokenizer_max_length"]).astype(np.int32)
+    state = np.random.default_rng(2).standard_normal(d["max_state_dim"]).astype(np.float32)
+    noise = np.random.default_rng(3).standard_normal((d["chunk_size"], d["max_action_dim"])).astype(np.float32)
+    return images, lang, state, noise
+
+
+def oracle_predict_seconds(orc, d, arch, n_views):
+    """One whole request through the CPU restatement with random weights of the checkpoint's shapes: the vision tower per
+    view, the backbone's prefill over the prefix, the denoise loop.  Returns (tower s, prefill s, denoise s)."""
+    rng = np.random.default_rng(5)
+    VH, VI, P = d["vit_hidden"], d["vit_inter"], d["patch_size"]
+    g = d["image_size"] // P
+    s = d["vit_pixel_shuffle"]
+    w = lambda *shape: orc.bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+    one, z = (lambda n: np.ones(n, np.float32)), (lambda n: np.zeros(n, np.float32))
+    tw = dict(patch_w=w(VH, 3, P, P), patch_b=z(VH), pos=w(g * g, VH), post_w=one(VH), post_b=z(VH),
+              connector=w(d["hidden"], VH * s * s), connector_b=None,
+              layers=[dict(ln1_w=one(VH), ln1_b=z(VH), ln2_w=one(VH), ln2_b=z(VH), wq=w(VH, VH), bq=z(VH), wk=w(VH, VH),
+                           bk=z(VH), wv=w(VH, VH), bv=z(VH), wo=w(VH, VH), bo=z(VH), fc1=w(VI, VH), b1=z(VI), fc2=w(VH, VI),
+                           b2=z(VH)) for _ in range(d["vit_layers"])])
+    tcfg = dict(image=d["image_size"], patch=P, hidden=VH, n_heads=d["vit_heads"], shuffle=s, ln_eps=d["vit_ln_eps"], out_scale=0.0)
+    img = rng.integers(0, 256, (d["image_size"], d["image_size"], 3), dtype=np.uint8)
+    t0 = time.perf_counter()
+    for _ in range(n_views):
+        emb = orc.siglip_tower(img, tw, tcfg)
+    t_tower = time.perf_counter() - t0
+    H, I, hd = d["hidden"], d["intermediate"], d["head_dim"]
+    qf, kvf = d["n_q_heads"] * hd, d["n_kv_heads"] * hd
+    layers = [dict(ln_in=one(H), wqkv=w(qf + 2 * kvf, H), wo=w(H, qf), ln_post=one(H), wgate=w(I, H), wup=w(I, H), wdown=w(H, I))
+              for _ in range(d["n_layers"])]
+    n_prefix = n_views * emb.shape[0] + d["tokenizer_max_length"] + (1 if arch == "smolvla" else 0)
+    x = rng.standard_normal((n_prefix, H), dtype=np.float32)
+    ocfg = dict(n_q=d["n_q_heads"], n_kv=d["n_kv_heads"], hd=hd, rms_eps=1e-5, rope_base=10000.0,
+                act="silu" if arch == "smolvla" else "gelu")
+    t0 = time.perf_counter()
+    orc.vlm_prefill(x, layers, ocfg)
+    t_prefill = time.perf_counter() - t0
+    t_denoise = OraclePolicyLoop(orc, arch, seed=7).run(1)[0]
+    return t_tower, t_prefill, t_denoise
+
+
+def predict_launches(d, arch):
+    """Kernels of one request, counted from the host code: tower (patchify, stream init, patch GEMM; 8 per layer;
+    post-LayerNorm, connector, pi0's scale), prefix embeddings, prefill (tables, 2 per layer for q|k|v + rotation, 4 more
+    on every layer but the last, 4 for the K/V projection of a cross-attention layer), denoise loop (few-row path)."""
+    L = d["n_layers"]
+    every = d.get("self_attn_every_n_layers", 0) if arch == "smolvla" else 0
+    cross = sum(1 for i in range(L) if every > 1 and i % every != 0)
+    tower = 3 + 8 * d["vit_layers"] + 2 + (0 if arch == "smolvla" else 1)
+    embed = 3 if arch == "smolvla" else 2
+    prefill = 2 + 2 * L + 4 * (L - 1) + 4 * cross
+    denoise = d["num_steps"] * (4 + L * 6 + 2) + 3
+    return tower + embed + prefill + denoise
+
+
+def measure_predict(torch, vb, dev, args, arch):
+    """Whole requests through include/vla.h on a random-init checkpoint of the named shape: camera views (host, uint8)
+    -> vision tower -> backbone prefill -> denoise loop -> actions (host).  One step = one vla_predict call."""
+    import shutil
+    import tempfile
+
+    from vla_cpp_b200 import synth_gguf
+
+    tmp = tempfile.mkdtemp(prefix="vla_b200_bench_")
+    try:
+        path = os.path.join(tmp, arch + "_random.gguf")
+        t0 = time.perf_counter()
+        dims = {} if arch == "smolvla" else {"vocab_size": 32768}  # pi0: a 32k-row embedding table bounds the file size
+        d = synth_gguf.write_checkpoint(path, arch, dims=dims, seed=0, matrix_dtype="f32" if arch == "smolvla" else "bf16")
+        t_write = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        model = vb.VlaModel(path)
+        images, lang, state, noise = predict_inputs(d, arch)
+        first = model.predict(lang, state, images=images, noise=noise)  # creates the device side on first use
+        t_load = time.perf_counter() - t0
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    assert np.isfinite(first).all() and first.shape == (d["chunk_size"], d["max_action_dim"])
+    for _ in range(max(args.warmup, 3)):
+        model.predict(lang, state, images=images, noise=noise)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    sampler.mark_begin()
+    wall, phases = [], []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        out = model.predict(lang, state, images=images, noise=noise)
+        wall.append((time.perf_counter() - t0) * 1e3)
+        st = model.stats
+        phases.append((st.ms_vision, st.ms_prefill, st.ms_denoise))
+    clocks = sampler.stop()
+    assert np.array_equal(out, first)  # same request, same noise: bit-identical actions
+    med = lambda xs: float(statistics.median(xs))
+    ms_v, ms_p, ms_d = (med([ph[i] for ph in phases]) for i in range(3))
+    dev_ms, wall_ms = ms_v + ms_p + ms_d, med(wall)
+    peaks = load_peaks()
+    # weights streamed per request: tower and backbone once, expert once per Euler step (bf16 on the device)
+    VH, VI = d["vit_hidden"], d["vit_inter"]
+    tower_p = d["vit_layers"] * (4 * VH * VH + 2 * VH * VI) + d["hidden"] * VH * d["vit_pixel_shuffle"] ** 2
+    hd = d["head_dim"]
+    qf, kvf, H, I, E, EI = d["n_q_heads"] * hd, d["n_kv_heads"] * hd, d["hidden"], d["intermediate"], d["expert_h"], d["expert_inter"]
+    backbone_p = d["n_layers"] * (H * (2 * qf + 2 * kvf) + 3 * H * I)
+    expert_p = d["n_layers"] * (E * (2 * qf + 2 * kvf) + 3 * E * EI)
+    bytes_alg = 2.0 * (tower_p + backbone_p + d["num_steps"] * expert_p)
+    h2d = sum(a.nbytes for a in images) + lang.nbytes + state.nbytes + noise.nbytes
+    line = {
+        "metric": "action chunks/s and p50 chunk latency (whole request: vision tower + prefill + denoise loop)",
+        "value": 1e3 / dev_ms, "unit": "chunks/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (random-init checkpoint in the reference's GGUF naming, seeded request)",
+        "config": {"workload": f"{arch}_predict: BASELINE configs[{0 if arch == 'smolvla' else 2}] through vla_predict, batch 1, "
+                               f"{len(images)} uint8 views of {d['image_size']}x{d['image_size']}, {lang.size} token ids, "
+                               f"{d['num_steps']} Euler steps", "l2": "weights (> L2) re-read every request"},
+        "phases_ms": {"vision": ms_v, "prefill": ms_p, "denoise": ms_d, "wall_p50": wall_ms, "wall_min": min(wall),
+                      "host_overhead": wall_ms - dev_ms},
+        "e2e": {"value": 1e3 / wall_ms, "unit": "chunks/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(out.nbytes),
+                "ms_per_step": wall_ms},
+        "roofline": {"bound": "hbm", "achieved": bytes_alg / (dev_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": bytes_alg / (dev_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "note": "weights streamed per request (tower + backbone once, expert per step) over the device time of "
+                             "the whole request; a batch-1 request is launch- and latency-bound, not bandwidth-bound",
+                     "peak_source": peaks["kind"]},
+        "gpu_launches": predict_launches(d, arch) * args.steps, "clocks": clocks,
+        "setup_s": {"write_checkpoint": t_write, "load_and_first_predict": t_load},
+    }
+    return line, d
+
+
 def cpu_baseline_record(args, workload):
     """The CPU restatement of the benchmarked loop on this box's host cores: a bounded sample."""
     from oracle import oracle_ffi as orc
@@ -980,7 +1123,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="pi0", choices=["pi0", "smolvla", "smolvla_attn", "ternary", "bitvla_lm"],
+    ap.add_argument("--workload", default="pi0", choices=["pi0", "smolvla", "smolvla_attn", "ternary", "bitvla_lm", "smolvla_predict", "pi0_predict"],
                     help="pi0 (default): the whole pi0-shaped denoise loop, 1024 observations split over the GPUs "
                          "(BASELINE configs[4]); smolvla: the SmolVLA-shaped loop; smolvla_attn: the isolated "
                          "denoise-attention op (configs[1]); ternary / bitvla_lm: configs[3]")
@@ -1040,6 +1183,20 @@ def main():
         return
     if args.workload == "bitvla_lm":
         finish(measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3)) if rank == 0 else None)
+        return
+    if args.workload.endswith("_predict"):
+        line = None
+        if rank == 0:
+            arch = args.workload.split("_")[0]
+            line, d = measure_predict(torch, vb, dev, args, arch)
+            if not args.no_cpu_baseline:
+                from oracle import oracle_ffi as orc
+
+                tt, tp, td = oracle_predict_seconds(orc, d, arch, 2 if arch == "smolvla" else 3)
+                line["cpu_baseline"] = {"value": 1.0 / (tt + tp + td), "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
+                                        "sample": "one whole request of the same shapes (random weights)",
+                                        "seconds": {"vision": tt, "prefill": tp, "denoise": td}}
+        finish(line)
         return
     if args.workload == "smolvla_attn":
         line = measure_smolvla_attn(torch, vb, dist, dev, args, rank, world, barrier, with_e2e=not args.no_e2e)

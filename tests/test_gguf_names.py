@@ -76,3 +76,54 @@ def test_bitvla_pack_naming_is_the_converters():
     assert '"' + GOLDEN["bitvla"]["packed_flag_key"] + '"' in src
     for piece in ('"attn_q"', '"ffn_gate_up"', '".weight"', '".scale"', '"lm.blk."'):
         assert piece in src, piece
+
+
+TINY = dict(hidden=64, intermediate=128, n_q_heads=2, n_kv_heads=1, head_dim=64, n_layers=2, vocab_size=32, expert_h=64,
+            expert_inter=128, chunk_size=4, num_steps=2, vit_hidden=64, vit_layers=1, vit_heads=1, vit_inter=128,
+            image_size=32, patch_size=16, vit_pixel_shuffle=1)
+
+
+@pytest.mark.parametrize("arch", ["pi0", "smolvla"])
+def test_the_random_init_writer_uses_the_converters_names(tmp_path, arch):
+    """vla_cpp_b200.synth_gguf writes only metadata keys and tensor names that the reference's converters write, and
+    the file resolves through vla_model_load / vla_model_config.  Host only."""
+    import vla_cpp_b200
+    from vla_cpp_b200 import synth_gguf
+
+    path = tmp_path / (arch + "_tiny.gguf")
+    dims = dict(TINY)
+    if arch == "pi0":
+        dims.update(image_size=224, patch_size=14)  # pi0 fixes 256 image tokens per view (src/models/pi0.cpp:286)
+    d = synth_gguf.write_checkpoint(path, arch, dims=dims)
+    g = GOLDEN[arch]
+    kv_names = {k for k, _ in g["kv"]}
+    block = {n.split(".", 3)[3] for n, _, _ in g["decoder_blocks"]}
+    vision = {n.replace("vit.blk.0.", "") for n, _, _ in GOLDEN["vision"]["tower"]}
+    conn = set(GOLDEN["vision"]["connector_" + arch])
+    r = gguf.GGUFReader(str(path))
+    for k in r.fields:
+        if k.startswith(arch + "."):
+            assert k in kv_names, k
+    for t in r.tensors:
+        n = t.name
+        if n.startswith(("vlm.blk.", "aex.blk.")):
+            assert n.split(".", 3)[3] in block, n
+        elif n.startswith("vit.blk."):
+            assert n.split(".", 3)[3] in vision, n
+        elif n.startswith("vit."):
+            assert n in vision, n
+        elif n.startswith("mm."):
+            assert n in conn, n
+        elif n in g["projections"]:
+            pass
+        else:
+            assert n in ("token_embd.weight", "vlm.output_norm.weight", g["output_norm"], "state_mean", "state_std",
+                         "action_mean", "action_std"), n
+    L = vla_cpp_b200.lib()
+    L.vla_model_load.restype = C.c_void_p
+    L.vla_model_load.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p]
+    L.vla_model_free.argtypes = [C.c_void_p]
+    m = L.vla_model_load(None, str(path).encode(), None)
+    assert m, L.vlab200_last_error()
+    L.vla_model_free(m)
+    assert d["n_img_tokens"] == (4 if arch == "smolvla" else 256)

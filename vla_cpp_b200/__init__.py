@@ -19,6 +19,7 @@ from .api import (  # noqa: F401
     Prefill,
     VisionTower,
     VlaB200Error,
+    VlaModel,
     act_quant,
     attention,
     bitvla_norm_quant,

@@ -569,6 +569,81 @@ class Prefill:
         torch.cuda.synchronize()  # pos (host memory) must outlive the copy enqueued on the stream
 
 
+class VlaImage(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("w", C.c_int32), ("h", C.c_int32), ("format", C.c_int32)]
+
+
+class VlaInputs(C.Structure):
+    _fields_ = [("images", C.POINTER(VlaImage)), ("n_images", C.c_int32), ("precomputed_img_emb", C.POINTER(C.c_float)),
+                ("n_img_views", C.c_int32), ("lang_tokens", C.POINTER(C.c_int32)), ("n_lang", C.c_int32),
+                ("state", C.POINTER(C.c_float)), ("noise", C.POINTER(C.c_float)), ("attention_mask", C.POINTER(C.c_int32)),
+                ("attention_mask_n", C.c_int32), ("timing_detail", C.c_int32)]
+
+
+class VlaStats(C.Structure):
+    _fields_ = [(n, C.c_float) for n in ("ms_total", "ms_vision", "ms_inference", "ms_prefill", "ms_denoise")]
+
+
+class VlaModel:
+    """include/vla.h from Python: vla_model_load / vla_predict / vla_last_stats on a pi0 or SmolVLA GGUF checkpoint.
+
+    predict(): images = list of numpy arrays [side, side, 3] (uint8 0..255 or float32 0..1) for the checkpoint's own
+    vision tower, or img_emb = float32 [n_views * n_img, hidden] with n_views; lang_tokens int32; state float32
+    [max_state_dim]; noise float32 [n_suffix, max_action_dim] or None (sampled inside).  Returns float32
+    [n_suffix, max_action_dim]; self.stats holds the phase times of the last call."""
+
+    def __init__(self, path):
+        L = lib()
+        L.vla_model_load.restype = C.c_void_p
+        L.vla_model_load.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p]
+        L.vla_model_free.argtypes = [C.c_void_p]
+        L.vla_predict.argtypes = [C.c_void_p, C.POINTER(VlaInputs), C.POINTER(C.POINTER(C.c_float)), C.POINTER(C.c_int64)]
+        L.vla_free_actions.argtypes = [C.POINTER(C.c_float)]
+        L.vla_last_stats.argtypes = [C.c_void_p, C.POINTER(VlaStats)]
+        self.h = L.vla_model_load(None, str(path).encode(), None)
+        if not self.h:
+            raise VlaB200Error(ERR_ARG, "vla_model_load: " + L.vlab200_last_error().decode())
+        self.stats = VlaStats()
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().vla_model_free(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def predict(self, lang_tokens, state, images=None, img_emb=None, n_views=0, noise=None, timing=True):
+        import numpy as np
+
+        f32 = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
+        fp = lambda a: None if a is None else a.ctypes.data_as(C.POINTER(C.c_float))
+        lang = np.ascontiguousarray(lang_tokens, np.int32)
+        state, noise, img_emb = f32(state), f32(noise), f32(img_emb)
+        inp = VlaInputs()
+        keep = []
+        if images is not None:
+            arr = (VlaImage * len(images))()
+            for v, a in enumerate(images):
+                a = np.ascontiguousarray(a)
+                assert a.dtype in (np.uint8, np.float32) and a.ndim == 3 and a.shape[2] == 3
+                keep.append(a)
+                arr[v].data, arr[v].w, arr[v].h, arr[v].format = a.ctypes.data, a.shape[1], a.shape[0], int(a.dtype == np.float32)
+            inp.images, inp.n_images = arr, len(images)
+        else:
+            inp.precomputed_img_emb, inp.n_img_views = fp(img_emb), n_views
+        inp.lang_tokens, inp.n_lang = lang.ctypes.data_as(C.POINTER(C.c_int32)), lang.size
+        inp.state, inp.noise, inp.timing_detail = fp(state), fp(noise), 1 if timing else 0
+        act, n = C.POINTER(C.c_float)(), C.c_int64(0)
+        rc = lib().vla_predict(self.h, C.byref(inp), C.byref(act), C.byref(n))
+        if rc != 0:
+            raise VlaB200Error(rc, "vla_predict: " + lib().vlab200_last_error().decode())
+        out = np.ctypeslib.as_array(act, shape=(n.value,)).copy()
+        lib().vla_free_actions(act)
+        lib().vla_last_stats(self.h, C.byref(self.stats))
+        rows = noise.shape[0] if noise is not None and noise.ndim == 2 else None
+        return out.reshape(rows, -1) if rows else out
+
+
 class _VisionConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("image", "patch", "hidden", "n_layers", "n_heads", "inter", "shuffle",
                                          "out_dim")] + [("ln_eps", C.c_float), ("out_scale", C.c_float)]
