@@ -629,6 +629,75 @@ def time_reference_lm(torch, dev, layers, out_norm, hidden, n_q, n_kv, hd, ffn, 
             "speedup_one_sequence": ms / own_ms_one_seq}
 
 
+def measure_bitvla_vit(torch, vb, dev, n_layers=26):
+    """The BitVLA vision tower (26 ternary ViT layers, hidden 1152, 16 heads of 72, MLP 4304, 256 patches, projector to
+    2560) for one image through bitvla_vit_cuda_forward of this library and, where it was built, of the reference
+    (oracle/_ref/libbitvla_vit_ref.so: its CUDA sources compiled unmodified), same weights, same box."""
+    import ctypes as C
+
+    H, heads, F, S, P, M = 1152, 16, 4304, 256, 588, 2560
+    FP = (F + 127) // 128 * 128
+    fields = ["ln1_w", "ln1_b", "ln2_w", "ln2_b", "q_packed", "q_ws", "q_b", "k_packed", "k_ws", "k_b", "v_packed", "v_ws",
+              "v_b", "o_packed", "o_ws", "o_b", "fc1_packed", "fc1_ws", "fc1_b", "fc2_packed", "fc2_ws", "fc2_b"]
+
+    class LayerC(C.Structure):
+        _fields_ = [(n, C.c_void_p) for n in fields]
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    bf = lambda *shape, sc=1.0: (torch.randn(shape, device=dev, generator=g) * sc).bfloat16()
+    layers = []
+    for _ in range(n_layers):
+        lw = {"ln1_w": 1 + bf(H, sc=0.1), "ln1_b": bf(H, sc=0.05), "ln2_w": 1 + bf(H, sc=0.1), "ln2_b": bf(H, sc=0.05)}
+        for name, n, k in (("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H), ("fc1", F, H), ("fc2", H, FP)):
+            # uniform ternary codes 1..3 (-1, 0, +1) in the ladder layout: any byte pattern is a valid pack
+            codes = torch.randint(1, 4, (n * k // 4, 4), device=dev, generator=g, dtype=torch.int32)
+            lw[name + "_packed"] = (codes[:, 0] | (codes[:, 1] << 2) | (codes[:, 2] << 4) | (codes[:, 3] << 6)).to(torch.uint8)
+            lw[name + "_ws"] = torch.full((1,), (1.5 / k) ** 0.5, device=dev, dtype=torch.float32)
+            lw[name + "_b"] = bf(n, sc=0.05)
+        layers.append(lw)
+    glob = dict(patch_w=bf(H, P, sc=P ** -0.5), patch_b=bf(H, sc=0.05), pos=bf(S, H, sc=0.1), w1=bf(M, H, sc=H ** -0.5),
+                b1=bf(M, sc=0.05), w2=bf(M, M, sc=M ** -0.5), b2=bf(M, sc=0.05))
+    patches = (torch.rand((S, P), device=dev, generator=g) * 2 - 1).bfloat16()
+    out = torch.empty((S, M), device=dev, dtype=torch.bfloat16)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def timed(lib):
+        lib.bitvla_vit_cuda_init.restype = C.c_void_p
+        lib.bitvla_vit_cuda_init.argtypes = [C.c_int] * 6 + [C.c_float, C.c_int]
+        lib.bitvla_vit_cuda_free.argtypes = [C.c_void_p]
+        lib.bitvla_vit_cuda_set_layer.argtypes = [C.c_void_p, C.c_int, C.POINTER(LayerC)]
+        lib.bitvla_vit_cuda_set_embed.argtypes = [C.c_void_p] * 4
+        lib.bitvla_vit_cuda_set_mmproj.argtypes = [C.c_void_p] * 5
+        lib.bitvla_vit_cuda_forward.restype = C.c_int
+        lib.bitvla_vit_cuda_forward.argtypes = [C.c_void_p] * 4
+        ctx = lib.bitvla_vit_cuda_init(n_layers, H, heads, F, S, P, 1e-6, M)
+        if not ctx:
+            return None
+        for i, lw in enumerate(layers):
+            st = LayerC(**{n: lw[n].data_ptr() for n in fields})
+            lib.bitvla_vit_cuda_set_layer(ctx, i, C.byref(st))
+        lib.bitvla_vit_cuda_set_embed(ctx, glob["patch_w"].data_ptr(), glob["patch_b"].data_ptr(), glob["pos"].data_ptr())
+        lib.bitvla_vit_cuda_set_mmproj(ctx, glob["w1"].data_ptr(), glob["b1"].data_ptr(), glob["w2"].data_ptr(), glob["b2"].data_ptr())
+        run = lambda: lib.bitvla_vit_cuda_forward(ctx, patches.data_ptr(), out.data_ptr(), stream)
+        assert run() == 0
+        torch.cuda.synchronize()
+        ms = _median_launch_ms(torch, run, warm=3, reps=10)
+        lib.bitvla_vit_cuda_free(ctx)
+        return ms
+
+    ours = timed(vb.lib())
+    assert vb.device_status() == 0 and bool(torch.isfinite(out.float()).all())
+    rec = {"config": f"BitVLA vision tower: {n_layers} ternary ViT layers, hidden {H}, {heads} heads of {H // heads}, MLP {F}, "
+                     f"{S} patches, projector to {M}; one image per call", "ms": ours, "launches": 3 + 10 * n_layers + 3}
+    ref = reference_lib("libbitvla_vit_ref.so")
+    ref_ms = timed(ref) if ref is not None else None
+    if ref_ms:
+        rec["reference_cuda"] = {"kernel": "reference bitvla_vit_cuda_forward, compiled unmodified for sm_100", "ms": ref_ms,
+                                 "speedup": ref_ms / ours}
+    return rec
+
+
 def attn_config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
@@ -1182,7 +1251,11 @@ def main():
         finish(measure_ternary(torch, vb, dev, args.steps, max(args.warmup, 3), args.ternary_only) if rank == 0 else None)
         return
     if args.workload == "bitvla_lm":
-        finish(measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3)) if rank == 0 else None)
+        line = None
+        if rank == 0:
+            line = measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3))
+            line["vision_tower"] = measure_bitvla_vit(torch, vb, dev)
+        finish(line)
         return
     if args.workload.endswith("_predict"):
         line = None
@@ -1219,6 +1292,7 @@ def main():
                                                  "reference_cuda") if k in t}
             lm = measure_bitvla_lm(torch, vb, dev, 5, 3)
             line["bitvla_lm"] = {k: lm[k] for k in ("config", "roofline", "cases", "one_token", "reference_cuda") if k in lm}
+            line["bitvla_lm"]["vision_tower"] = measure_bitvla_vit(torch, vb, dev)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_record(args, args.workload)
     finish(line)

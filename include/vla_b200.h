@@ -356,7 +356,7 @@ VLAB200_API int32_t vlab200_act_quant(const void *x_bf16, int8_t *q, float *scal
  * acc_out (optional, int32 [M][N]) receives the raw accumulators.
  * path: 0 = automatic (M <= 8: HBM-bound GEMV on the packed weights; larger M: tcgen05
  * int8 MMA, on CTA pairs when N >= 256), 1 = force GEMV, 2 = force the one-CTA-per-tile
- * tensor-core kernel, 3 = force the CTA-pair kernel (2 and 3 need N % 32 == 0).
+ * tensor-core kernel, 3 = force the CTA-pair kernel (with ws_num > 1, 2 and 3 need (N / ws_num) % 32 == 0).
  * Replaces bitlinear_int8xint2 / bitlinear_int8xint2_m
  * (src/kernels/bitvla/bitnet_kernels.cu:31-116, kernels bitnet_kernels.h:108-409). */
 VLAB200_API int32_t vlab200_ternary_linear(const int8_t *A, const uint8_t *W_ladder, void *out_bf16,
@@ -550,6 +550,37 @@ VLAB200_API void bitvla_lm_cuda_set_layer(bitvla_lm_cuda_ctx *ctx, int L, const 
 VLAB200_API void bitvla_lm_cuda_set_output_norm(bitvla_lm_cuda_ctx *ctx, const void *w);
 VLAB200_API int bitvla_lm_cuda_forward(bitvla_lm_cuda_ctx *ctx, const void *d_in, void *d_out, int seq,
                                        void *stream);
+
+/* The reference's vision-tower context API by its own names and signatures
+ * (src/kernels/bitvla/bitvla_vit_cuda.h:44-144; forward src/kernels/bitvla/bitvla_vit_cuda.cu:161-330; callers
+ * src/models/bitvla.cpp): a ternary SigLIP ViT (LayerNorm -> act-quant -> ternary q/k/v + bias -> unmasked attention ->
+ * act-quant -> ternary o + bias -> residual -> LayerNorm -> act-quant -> ternary fc1 + bias -> tanh-GELU -> zero-pad
+ * to a multiple of 128 -> act-quant -> ternary fc2 + bias -> residual, bf16 residual stream) between a bf16 patch
+ * embedding (+ bias + position) and a two-layer projector (erf-GELU).  The layer struct has the reference's field
+ * order; bf16 pointers are __nv_bfloat16*, `stream` a cudaStream_t.  init allocates every buffer (NULL on failure),
+ * set_* bind caller-owned device pointers (q/k/v packs are copied into one fused matrix, the patch-embedding weight
+ * into a copy with 16-byte rows, the projector biases into float32), forward returns 0 or -1 and writes
+ * n_patches x mm_out bf16 rows for one image.  Needs hidden % 128 == 0, ffn % 16 == 0, mm_out % 8 == 0; head_dim
+ * = hidden / n_heads is zero-padded to 64 / 128 / 256 for the attention kernel (softmax scale 1/sqrt(head_dim)). */
+typedef struct {
+    void *ln1_w, *ln1_b, *ln2_w, *ln2_b;   /* bf16 [hidden] */
+    int8_t *q_packed; float *q_ws; void *q_b;       /* ladder pack [hidden][hidden], one scale, bf16 bias */
+    int8_t *k_packed; float *k_ws; void *k_b;
+    int8_t *v_packed; float *v_ws; void *v_b;
+    int8_t *o_packed; float *o_ws; void *o_b;
+    int8_t *fc1_packed; float *fc1_ws; void *fc1_b; /* [ffn][hidden] */
+    int8_t *fc2_packed; float *fc2_ws; void *fc2_b; /* [hidden][ffn padded to a multiple of 128] */
+} bitvla_vit_layer_cuda;
+typedef struct bitvla_vit_cuda_ctx bitvla_vit_cuda_ctx;
+VLAB200_API bitvla_vit_cuda_ctx *bitvla_vit_cuda_init(int n_layers, int hidden, int n_heads, int ffn, int n_patches,
+                                                      int patch_flat, float ln_eps, int mm_out);
+VLAB200_API void bitvla_vit_cuda_free(bitvla_vit_cuda_ctx *ctx);
+VLAB200_API void bitvla_vit_cuda_set_layer(bitvla_vit_cuda_ctx *ctx, int L, const bitvla_vit_layer_cuda *layer);
+VLAB200_API void bitvla_vit_cuda_set_embed(bitvla_vit_cuda_ctx *ctx, const void *patch_w, const void *patch_b,
+                                           const void *pos_emb);
+VLAB200_API void bitvla_vit_cuda_set_mmproj(bitvla_vit_cuda_ctx *ctx, const void *W1, const void *b1, const void *W2,
+                                            const void *b2);
+VLAB200_API int bitvla_vit_cuda_forward(bitvla_vit_cuda_ctx *ctx, const void *d_patches, void *d_out, void *stream);
 
 #ifdef __cplusplus
 }

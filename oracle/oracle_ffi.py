@@ -441,6 +441,69 @@ def bitvla_lm_forward(x, layers, output_norm, cfg):
     return bitvla_rmsnorm_bf16(h, output_norm, cfg["rms_eps"])
 
 
+def bitvla_layernorm_bf16(x, w, b, eps):
+    """layernorm_bias_bf16_kernel (bitvla_lm_cuda.cu:552-607): mean and centred variance of the bf16 row in float,
+    bf16((x - mean) * rsqrt(var + eps) * w + b)."""
+    x = _c(x, np.float32)
+    mean = (x.astype(np.float64).sum(-1) / x.shape[-1]).astype(np.float32)
+    d = x - mean[:, None]
+    var = ((d.astype(np.float64) ** 2).sum(-1) / x.shape[-1]).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt(var + np.float32(eps))).astype(np.float32)
+    return bf16_round((d * inv[:, None]) * _c(w, np.float32)[None, :] + _c(b, np.float32)[None, :])
+
+
+def bitvla_vit_forward(patches, w, cfg):
+    """bitvla_vit_cuda_forward (src/kernels/bitvla/bitvla_vit_cuda.cu:261-330, layer body :161-259) for one image.
+    patches [n_patches, patch_flat]; w: patch_w [hidden, patch_flat], patch_b, pos [n_patches, hidden], mm_w1, mm_b1, mm_w2,
+    mm_b2 and layers = dicts ln1_w, ln1_b, ln2_w, ln2_b, {q,k,v,o,fc1,fc2}_packed / _ws / _b (fc2 packed over the MLP
+    width padded to a multiple of 128); every array bf16-valued float32 but the packs (uint8) and scales.
+    cfg: hidden, n_heads, ffn, ln_eps.  Every value the reference stores as bf16 is rounded here."""
+    import math
+
+    H, heads, ffn, eps = cfg["hidden"], cfg["n_heads"], cfg["ffn"], cfg["ln_eps"]
+    hd, ffn_pad = H // heads, (ffn + 127) // 128 * 128
+    r = bf16_round
+    x = r(_c(patches, np.float32))
+    h = r(linear(x, w["patch_w"]))
+    h = r(r(h + w["patch_b"][None, :]) + w["pos"])
+    seq = h.shape[0]
+    scl = np.float32(1.0 / np.sqrt(np.float32(hd)))
+    for lw in w["layers"]:
+        n1 = bitvla_layernorm_bf16(h, lw["ln1_w"], lw["ln1_b"], eps)
+        a, s = act_quant(n1)
+
+        def proj(name, q=a, sc=s, n=H):
+            acc = ternary_gemm_i32(q, lw[name + "_packed"], n)
+            y = bf16_bits_to_f32(ternary_epilogue(acc, sc, np.atleast_1d(lw[name + "_ws"])))
+            return r(y + lw[name + "_b"][None, :])
+
+        q = proj("q").reshape(seq, heads, hd).transpose(1, 0, 2)
+        k = proj("k").reshape(seq, heads, hd).transpose(1, 0, 2)
+        v = proj("v").reshape(seq, heads, hd).transpose(1, 0, 2)
+        att = np.empty((seq, heads, hd), np.float32)
+        for hh in range(heads):
+            sc = r((q[hh] @ k[hh].T).astype(np.float32))  # scores stored bf16 (:198-209)
+            xs = sc * scl
+            p = np.exp(xs - xs.max(-1, keepdims=True)).astype(np.float32)
+            p = r(p * (np.float32(1.0) / p.sum(-1, keepdims=True, dtype=np.float32)))
+            att[:, hh] = r((p @ v[hh]).astype(np.float32))
+        a2, s2 = act_quant(att.reshape(seq, H))
+        h = r(h + proj("o", a2, s2))
+        n2 = bitvla_layernorm_bf16(h, lw["ln2_w"], lw["ln2_b"], eps)
+        a3, s3 = act_quant(n2)
+        f1 = proj("fc1", a3, s3, ffn)
+        c0 = np.float32(0.7978845608028654)
+        g = r(np.float32(0.5) * f1 * (np.float32(1) + np.tanh(c0 * (f1 + np.float32(0.044715) * f1 * f1 * f1), dtype=np.float32)))
+        gp = np.zeros((seq, ffn_pad), np.float32)
+        gp[:, :ffn] = g
+        a4, s4 = act_quant(gp)
+        h = r(h + proj("fc2", a4, s4))
+    erf = np.vectorize(math.erf, otypes=[np.float64])
+    m1 = r(r(linear(h, w["mm_w1"])) + w["mm_b1"][None, :])
+    m1 = r(np.float32(0.5) * m1 * (np.float32(1) + erf(m1 * np.float32(0.7071067811865475)).astype(np.float32)))
+    return r(r(linear(m1, w["mm_w2"])) + w["mm_b2"][None, :])
+
+
 # ---- node-level bf16 operators (the reference's per-node CUDA hook, src/cuda/vla_cuda_bf16.cu) ----
 # Inputs are float32 arrays holding bf16 values; float32 math; one bf16 rounding of the result.
 

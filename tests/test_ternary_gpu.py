@@ -13,6 +13,10 @@ from tests.gpu_util import bf16_bits, bits_to_bf16_tensor, reference_bitnet_lib,
 pytestmark = pytest.mark.gpu
 
 LM_SHAPES = [(2560, 2560, 1), (640, 2560, 1), (13824, 2560, 2), (2560, 6912, 1)]  # (N, K, ws_num)
+# the vision tower's projections, which the reference's kernels also serve (src/kernels/bitvla/bitnet_kernels.cu:68-70,
+# 85-87): hidden 1152, MLP 4304 (N not a multiple of 32: the last 256-column tile is cut after 208 columns), and the
+# MLP width padded to 4352 on the K side
+VIT_SHAPES = [(1152, 1152, 1), (4304, 1152, 1), (1152, 4352, 1)]
 
 
 def make_case(rng, m, n, k, ws_num, raw_bytes=False):
@@ -99,6 +103,44 @@ def test_gemm_tensor_core_sampled_rows_at_full_size(oracle, m, shape):
     # linearity in A as a whole-matrix property: acc(A) + acc(-A) == 0
     acc_neg, _ = run_gpu(api, (-a).astype(np.int8), packed, s, ws, n, path=0)
     assert not np.any(acc + acc_neg)
+
+
+@pytest.mark.parametrize("m", [1, 7, 256, 300, 768])
+@pytest.mark.parametrize("shape", VIT_SHAPES)
+def test_vision_tower_shapes_whole_matrix(oracle, m, shape):
+    """Every accumulator and every bf16 output of the three vision-tower shapes (256 patches per view; 1 and 7 rows run
+    the GEMV), against the CPU integer GEMM and, where it was built, the reference's own bitlinear_int8xint2_m."""
+    torch = require_cuda()
+    from vla_cpp_b200 import api
+
+    n, k, ws_num = shape
+    rng = np.random.default_rng(7000 + m + n + k)
+    tern = rng.integers(-1, 2, (n, k)).astype(np.int8)
+    packed = oracle.pack_ladder_int2(tern)
+    a, _, s, ws = make_case(rng, m, n, k, ws_num)
+    ref_acc = oracle.gemm_i8_i32(a, tern)
+    ref_out = oracle.ternary_epilogue(ref_acc, s, ws)
+    outs = {}
+    for path in ([0] if m <= 8 else [0, 2, 3]):
+        acc, out = run_gpu(api, a, packed, s, ws, n, path=path)
+        assert np.array_equal(acc, ref_acc), path
+        if m <= 8:
+            assert np.array_equal(out, ref_out)
+        else:
+            assert_bf16_close(out, ref_out)
+        outs[path] = out
+    if m > 8:
+        assert np.array_equal(outs[2], outs[3])
+    ref = reference_bitnet_lib()
+    if ref is not None and m > 1:
+        ad, pd, sd, wd = to_dev(a), to_dev(packed), to_dev(s), to_dev(ws)
+        theirs = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        ref.bitlinear_int8xint2_m(C.c_void_p(ad.data_ptr()), C.c_void_p(pd.data_ptr()), C.c_void_p(theirs.data_ptr()),
+                                  C.c_void_p(sd.data_ptr()), C.c_void_p(wd.data_ptr()), m, n, k, C.c_void_p(0))
+        torch.cuda.synchronize()
+        diff = np.abs(outs[0].astype(np.int32) - bf16_bits(theirs).astype(np.int32))
+        assert diff.max() <= 1, f"max ulp distance {diff.max()}"
+        assert (diff == 0).mean() > 0.95
 
 
 def test_gemv_and_tensor_core_paths_agree(oracle):

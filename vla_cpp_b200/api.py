@@ -94,6 +94,8 @@ EXPORTS = [
     "bitlinear_int8xint2", "bitlinear_int8xint2_m", "bitvla_act_quant_cuda",
     "bitvla_lm_cuda_init", "bitvla_lm_cuda_free", "bitvla_lm_cuda_set_layer", "bitvla_lm_cuda_set_output_norm",
     "bitvla_lm_cuda_forward",
+    "bitvla_vit_cuda_init", "bitvla_vit_cuda_free", "bitvla_vit_cuda_set_layer", "bitvla_vit_cuda_set_embed",
+    "bitvla_vit_cuda_set_mmproj", "bitvla_vit_cuda_forward",
 ]
 
 

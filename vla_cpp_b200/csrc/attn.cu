@@ -33,7 +33,7 @@ namespace vb {
 
 // streaming kernel for wide heads / long key ranges (attn_flash.cu)
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream);
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale = 0.0f);
 
 constexpr int ATT_SOFTMAX_WARPS = 16;
 constexpr int ATT_THREADS = (ATT_SOFTMAX_WARPS + 3) * 32;  // + loader + 2 MMA issuers

@@ -758,7 +758,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
 template <int HD>
 static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                        int mask_mode, const int32_t *pad_ranges, cudaStream_t stream) {
+                        int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale) {
     using L = FlashSmem<HD>;
     int *status = device_status_ptr();
     if (!status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
@@ -793,7 +793,8 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
     p.n_units = st->n_obs * st->n_kv * p.n_mt;
     p.n_blocks = (kv_len + FA_BKV - 1) / FA_BKV;
     p.page0 = layer * st->n_obs * st->n_kv;
-    p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    // softmax_scale > 0 replaces 1 / sqrt(HD): heads narrower than HD that were zero-padded to it
+    p.scale_log2 = 1.4426950408889634f * (softmax_scale > 0.0f ? softmax_scale : 1.0f / sqrtf((float)HD));
     p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
     const int n_sm = sm_count();
@@ -824,12 +825,14 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
 }
 
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream) {
-    if (st->head_dim == 256) return launch_flash<256>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
-    if (st->head_dim == 128) return launch_flash<128>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
-    if (st->head_dim == 64) return launch_flash<64>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream);
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale) {
+    if (st->head_dim == 256)
+        return launch_flash<256>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
+    if (st->head_dim == 128)
+        return launch_flash<128>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
+    if (st->head_dim == 64)
+        return launch_flash<64>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
     return VLAB200_ERR_UNSUPPORTED;
 }
 
 }  // namespace vb
-

@@ -57,6 +57,7 @@ __device__ __forceinline__ float act_apply(float x, int act) {
         const float u = k0 * x * (1.0f + k1 * x * x);
         return __fdividef(x, 1.0f + __expf(-2.0f * u));
     }
+    if (act == ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
     return x;
 }
 

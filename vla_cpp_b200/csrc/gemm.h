@@ -6,7 +6,7 @@
 namespace vb {
 
 enum { EPI_RESIDUAL = 0, EPI_GATED = 1, EPI_BIAS_ACT = 2 };
-enum { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
+enum { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_GELU_ERF = 3 };
 
 struct GemmParams {
     int M, N, K;

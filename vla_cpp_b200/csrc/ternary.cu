@@ -447,17 +447,17 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t 
                 tmem_ld32(lane_addr + (uint32_t)(c + 32), r1);
                 tmem_ld_wait();
                 const int n = n0 + c;
-                if (n >= N) break;  // uniform: N % 32 == 0, the second half may still be past N
+                if (n >= N) break;  // uniform; N % 16 == 0, so the chunk may be cut after any multiple of 16 columns
                 if (acc_out && m < M) {
                     int4 *dst = reinterpret_cast<int4 *>(acc_out + (size_t)m * N + n);
 #pragma unroll
                     for (int e = 0; e < 8; ++e)
-                        dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
-                    if (n + 32 < N) {
+                        if (n + 4 * e < N)
+                            dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
 #pragma unroll
-                        for (int e = 0; e < 8; ++e)
+                    for (int e = 0; e < 8; ++e)
+                        if (n + 32 + 4 * e < N)
                             dst[8 + e] = make_int4((int)r1[4 * e], (int)r1[4 * e + 1], (int)r1[4 * e + 2], (int)r1[4 * e + 3]);
-                    }
                 }
                 // acc / s * ws evaluated as acc * (ws / s): at most one float ulp from the two-step form.
                 // A 32-column chunk never straddles a scale group (the group size is a multiple of 32).
@@ -723,12 +723,12 @@ ternary_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_
                         int4 *dst = reinterpret_cast<int4 *>(acc_out + (size_t)m * N + n);
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
-                            dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
-                        if (n + 32 < N) {
+                            if (n + 4 * e < N)
+                                dst[e] = make_int4((int)r0[4 * e], (int)r0[4 * e + 1], (int)r0[4 * e + 2], (int)r0[4 * e + 3]);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e)
+                        for (int e = 0; e < 8; ++e)
+                            if (n + 32 + 4 * e < N)
                                 dst[8 + e] = make_int4((int)r1[4 * e], (int)r1[4 * e + 1], (int)r1[4 * e + 2], (int)r1[4 * e + 3]);
-                        }
                     }
                     const float cs0 = __fdiv_rn(ws[n / group], sm);
                     const float cs1 = __fdiv_rn(ws[min(n + 32, N - 1) / group], sm);
@@ -860,7 +860,8 @@ static int ternary_linear(const int8_t *A, const uint8_t *W, __nv_bfloat16 *out,
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (acc && (reinterpret_cast<uintptr_t>(acc) & 15)))
         return VLAB200_ERR_ARG;
-    if (N % 32 || (N / ws_num) % 32) return VLAB200_ERR_UNSUPPORTED;
+    // a 32-column epilogue chunk must not straddle two weight-scale groups; with one group N % 16 == 0 is enough
+    if (ws_num > 1 && (N / ws_num) % 32) return VLAB200_ERR_UNSUPPORTED;
     // CTA pairs measured faster than one CTA per tile on every BitVLA shape from M = 300 up
     if (force_path == 3 || (force_path == 0 && N >= 256))
         return launch_gemm_pair(A, W, out, acc, s, ws, ws_num, M, N, K, st);
