@@ -698,6 +698,60 @@ def measure_bitvla_vit(torch, vb, dev, n_layers=26):
     return rec
 
 
+def measure_bitvla_head(vb):
+    """BitVLA's float32 action head (chunk 8, 7 action dims, hidden 2560: fc1 streams 183 MB of float32 weights) and
+    proprioception projector through bitvla_fp32head_* of this library and of the reference (cuBLAS SGEMM), host
+    buffers in, host buffers out, wall clock (the calls copy and synchronise themselves)."""
+    import ctypes as C
+
+    P, H, M, A = 8, 2560, 8, 7
+    D = A * H
+    rng = np.random.default_rng(3)
+    shapes = [(H, P), (H,), (H, H), (H,), (D,), (D,), (H, D), (H,), (H,), (H,), (H, H), (H,), (H,), (H,), (H, H), (H,), (H,), (H,),
+              (A, H), (A,)]
+    ws = [(rng.standard_normal(shp, dtype=np.float32) * (shp[-1] ** -0.5 if len(shp) == 2 else 0.1)) for shp in shapes]
+    state = rng.standard_normal(P, dtype=np.float32)
+    ah_in = rng.standard_normal((M, D), dtype=np.float32)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+
+    def timed(lib):
+        f = C.POINTER(C.c_float)
+        lib.bitvla_fp32head_cuda_init.restype = C.c_void_p
+        lib.bitvla_fp32head_cuda_init.argtypes = [C.c_int] * 4 + [C.c_float] + [f] * 20
+        lib.bitvla_fp32head_proprio_forward.argtypes = [C.c_void_p, f, f, C.c_void_p]
+        lib.bitvla_fp32head_action_forward.argtypes = [C.c_void_p, f, f, C.c_void_p]
+        lib.bitvla_fp32head_cuda_free.argtypes = [C.c_void_p]
+        ctx = lib.bitvla_fp32head_cuda_init(P, H, M, A, 1e-5, *[fp(w) for w in ws])
+        if not ctx:
+            return None
+        pp, act = np.zeros(H, np.float32), np.zeros((M, A), np.float32)
+        res = {}
+        for name, call in (("action_ms", lambda: lib.bitvla_fp32head_action_forward(ctx, fp(ah_in), fp(act), None)),
+                           ("proprio_ms", lambda: lib.bitvla_fp32head_proprio_forward(ctx, fp(state), fp(pp), None))):
+            ts = []
+            for it in range(25):
+                t0 = time.perf_counter()
+                assert call() == 0
+                if it >= 5:
+                    ts.append((time.perf_counter() - t0) * 1e3)
+            res[name] = statistics.median(ts)
+        lib.bitvla_fp32head_cuda_free(ctx)
+        return res
+
+    rec = {"config": f"BitVLA float32 head: chunk {M} x {A} actions, hidden {H} (fc1 {H} x {D}), proprio {P}; host in, host out"}
+    rec.update(timed(vb.lib()))
+    # the action forward streams every weight once: 4 B x (H D + 2 H H + A H) and the two LayerNorm vectors
+    wbytes = 4.0 * (H * D + 2 * H * H + A * H + 2 * D + 8 * H)
+    rec["action_weight_stream_gbs"] = wbytes / (rec["action_ms"] * 1e-3) / 1e9
+    ref = reference_lib("libbitvla_fp32head_ref.so")
+    if ref is not None:
+        r = timed(ref)
+        if r:
+            rec["reference_cuda"] = dict(r, kernel="reference bitvla_fp32head_*, compiled unmodified for sm_100",
+                                         speedup_action=r["action_ms"] / rec["action_ms"])
+    return rec
+
+
 def attn_config_dict(batch, n_gpus):
     return {"workload": "smolvla_attn: isolated denoise-attention op (BASELINE configs[1]), 16 layers x 10 steps, "
                         "P=177, S=51, 15q/5kv, hd 64, bf16",
@@ -1255,6 +1309,7 @@ def main():
         if rank == 0:
             line = measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3))
             line["vision_tower"] = measure_bitvla_vit(torch, vb, dev)
+            line["fp32_head"] = measure_bitvla_head(vb)
         finish(line)
         return
     if args.workload.endswith("_predict"):
@@ -1293,6 +1348,7 @@ def main():
             lm = measure_bitvla_lm(torch, vb, dev, 5, 3)
             line["bitvla_lm"] = {k: lm[k] for k in ("config", "roofline", "cases", "one_token", "reference_cuda") if k in lm}
             line["bitvla_lm"]["vision_tower"] = measure_bitvla_vit(torch, vb, dev)
+            line["bitvla_lm"]["fp32_head"] = measure_bitvla_head(vb)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_record(args, args.workload)
     finish(line)

@@ -582,6 +582,26 @@ VLAB200_API void bitvla_vit_cuda_set_mmproj(bitvla_vit_cuda_ctx *ctx, const void
                                             const void *b2);
 VLAB200_API int bitvla_vit_cuda_forward(bitvla_vit_cuda_ctx *ctx, const void *d_patches, void *d_out, void *stream);
 
+/* The reference's float32 proprioception projector and action head by their own names and signatures
+ * (src/kernels/bitvla/bitvla_fp32head_cuda.h:66-129; bodies src/kernels/bitvla/bitvla_fp32head_cuda.cu:186-358).
+ * init copies the HOST weight arrays (PyTorch order [out][in]) to the device; proprio_forward maps a host state
+ * vector [proprio_dim] to [lm_hidden] (fc1 -> erf-GELU -> fc2); action_forward maps host rows
+ * [chunk][action_dim * lm_hidden] to normalised actions [chunk][action_dim] (LayerNorm -> fc1 -> ReLU -> two
+ * residual blocks h += ReLU(W LayerNorm(h) + b) -> LayerNorm -> fc2); both synchronise `stream` (a cudaStream_t)
+ * before they return 0 (or -1).  All arithmetic is float32. */
+typedef struct bitvla_fp32head_cuda_ctx bitvla_fp32head_cuda_ctx;
+VLAB200_API bitvla_fp32head_cuda_ctx *bitvla_fp32head_cuda_init(
+    int proprio_dim, int lm_hidden, int chunk, int action_dim, float ah_ln_eps, const float *pp_fc1_w,
+    const float *pp_fc1_b, const float *pp_fc2_w, const float *pp_fc2_b, const float *ah_ln1_w, const float *ah_ln1_b,
+    const float *ah_fc1_w, const float *ah_fc1_b, const float *ah_b0_lnw, const float *ah_b0_lnb, const float *ah_b0_w,
+    const float *ah_b0_b, const float *ah_b1_lnw, const float *ah_b1_lnb, const float *ah_b1_w, const float *ah_b1_b,
+    const float *ah_ln2_w, const float *ah_ln2_b, const float *ah_fc2_w, const float *ah_fc2_b);
+VLAB200_API int bitvla_fp32head_proprio_forward(bitvla_fp32head_cuda_ctx *ctx, const float *host_state, float *host_out,
+                                                void *stream);
+VLAB200_API int bitvla_fp32head_action_forward(bitvla_fp32head_cuda_ctx *ctx, const float *host_ah_input,
+                                               float *host_norm_actions, void *stream);
+VLAB200_API void bitvla_fp32head_cuda_free(bitvla_fp32head_cuda_ctx *ctx);
+
 #ifdef __cplusplus
 }
 #endif

@@ -504,6 +504,34 @@ def bitvla_vit_forward(patches, w, cfg):
     return r(r(linear(m1, w["mm_w2"])) + w["mm_b2"][None, :])
 
 
+def bitvla_fp32head(w, cfg, state=None, ah_in=None):
+    """The float32 proprioception projector and action head (src/kernels/bitvla/bitvla_fp32head_cuda.cu:258-358) in
+    float64 numpy: proprio = W2 gelu_erf(W1 state + b1) + b2; action = fc2(LN2(h)), h = relu(fc1(LN1(in))) followed by
+    two blocks h += relu(W LN(h) + b).  w: dict with the names of bitvla_fp32head_cuda_init's arguments."""
+    import math
+
+    f = lambda k: np.asarray(w[k], np.float64)
+    erf = np.vectorize(math.erf, otypes=[np.float64])
+
+    def ln(x, wk, bk):
+        m = x.mean(-1, keepdims=True)
+        d = x - m
+        return d / np.sqrt((d * d).mean(-1, keepdims=True) + cfg["ah_ln_eps"]) * f(wk) + f(bk)
+
+    out = {}
+    if state is not None:
+        h1 = f("pp_fc1_w") @ np.asarray(state, np.float64) + f("pp_fc1_b")
+        h1 = 0.5 * h1 * (1.0 + erf(h1 * 0.70710678118654752440))
+        out["proprio"] = f("pp_fc2_w") @ h1 + f("pp_fc2_b")
+    if ah_in is not None:
+        x = ln(np.asarray(ah_in, np.float64), "ah_ln1_w", "ah_ln1_b")
+        h = np.maximum(x @ f("ah_fc1_w").T + f("ah_fc1_b"), 0)
+        for blk in ("b0", "b1"):
+            h = h + np.maximum(ln(h, f"ah_{blk}_lnw", f"ah_{blk}_lnb") @ f(f"ah_{blk}_w").T + f(f"ah_{blk}_b"), 0)
+        out["action"] = ln(h, "ah_ln2_w", "ah_ln2_b") @ f("ah_fc2_w").T + f("ah_fc2_b")
+    return out
+
+
 # ---- node-level bf16 operators (the reference's per-node CUDA hook, src/cuda/vla_cuda_bf16.cu) ----
 # Inputs are float32 arrays holding bf16 values; float32 math; one bf16 rounding of the result.
 

@@ -96,6 +96,8 @@ EXPORTS = [
     "bitvla_lm_cuda_forward",
     "bitvla_vit_cuda_init", "bitvla_vit_cuda_free", "bitvla_vit_cuda_set_layer", "bitvla_vit_cuda_set_embed",
     "bitvla_vit_cuda_set_mmproj", "bitvla_vit_cuda_forward",
+    "bitvla_fp32head_cuda_init", "bitvla_fp32head_proprio_forward", "bitvla_fp32head_action_forward",
+    "bitvla_fp32head_cuda_free",
 ]
 
 
