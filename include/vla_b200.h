@@ -179,11 +179,14 @@ VLAB200_API int32_t vlab200_denoise_attn_loop_host(const vlab200_kv_store *st, c
  * max_action_dim, max_state_dim, num_steps, self_attn_every_n, rms_eps, rope_freq_base, periods). */
 typedef struct {
     int32_t model;       /* 0 = pi0 (state token in the suffix, tanh-GELU MLP; src/models/pi0.cpp),
-                            1 = SmolVLA (SiLU MLP, alternating self / cross layers; src/models/smolvla.cpp) */
+                            1 = SmolVLA (SiLU MLP, alternating self / cross layers; src/models/smolvla.cpp),
+                            2 = pi0.5 (adaptive RMSNorm conditioned on the time step, gated residuals, no state token,
+                                no mask among the action tokens; src/models/pi05.cpp:208-292,604-631) */
     int32_t n_layers, H, n_q, n_kv, head_dim, inter, chunk, action_dim, state_dim, steps;
     int32_t self_every;  /* SmolVLA: layer l self-attends iff l % self_every == 0; <= 1: every layer */
     float rms_eps, rope_base;
     double min_period, max_period;
+    int32_t cond_dim;    /* pi0.5: width of the time-conditioning vector (pi05.adarms_cond_dim); 0 = H */
 } vlab200_policy_config;
 
 /* Device pointers to the expert's weights, in the reference's tensor shapes (GGUF names of
@@ -201,6 +204,13 @@ typedef struct {
     const void *w_at2;  const float *b_at2;   /* [H][H] */
     const float *out_norm;                    /* [H] (Gemma norms with their +1 applied) */
     const void *w_aout; const float *b_aout;  /* [action_dim][H] */
+    /* pi0.5 only (ln_in, ln_post, out_norm, w_sp, w_at1, w_at2 are not read then); all float32, as the reference keeps
+     * them: per layer the adaptive-norm dense maps [3H][cond_dim] + [3H] (rows scale | shift | gate; GGUF
+     * "aex.blk.N.attn_norm.{weight,bias}" / "ffn_norm"), the final one ("aex.output_norm"), and the time MLP
+     * [cond_dim][H], [cond_dim][cond_dim] ("time_mlp_in" / "time_mlp_out") */
+    const float *const *ada_in_w, *const *ada_in_b, *const *ada_post_w, *const *ada_post_b;
+    const float *ada_final_w, *ada_final_b;
+    const float *w_tin, *b_tin, *w_tout, *b_tout;
 } vlab200_policy_weights;
 
 typedef struct vlab200_engine vlab200_engine;

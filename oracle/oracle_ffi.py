@@ -238,6 +238,45 @@ def vlm_prefill(x, layers, cfg, pos=None, mask_mode=MASK_NONE, pad=(0, 0)):
 
 # ---- vision tower (numpy float32): SigLIP encoder + connector ----
 
+def pi05_denoise(kp, vp, x0, w, cfg):
+    """The pi0.5 Euler loop for one observation (src/models/pi05.cpp:604-631; layer build_expert_layer :226-292;
+    build_adarms :208-224): time enters through adaptive RMSNorm, residuals are gated, the action tokens see the prefix
+    and one another without a mask.  kp, vp: per layer the prefix's rotated K and its V [P][n_kv][hd]; x0 [chunk][A].
+    w: w_ain, b_ain, w_tin, b_tin, w_tout, b_tout, ada_final_w, ada_final_b, w_aout, b_aout and layers = dicts wq, wk, wv,
+    wo, wgate, wup, wdown, ada_in_w, ada_in_b, ada_post_w, ada_post_b.  cfg: H, n_q, n_kv, hd, steps, rms_eps, rope_base,
+    min_period, max_period."""
+    H, n_q, n_kv, hd, T = cfg["H"], cfg["n_q"], cfg["n_kv"], cfg["hd"], cfg["steps"]
+    silu = lambda a: a / (np.float32(1) + np.exp(-a, dtype=np.float32))
+    x = _c(x0, np.float32).copy()
+    S, P = x.shape[0], kp[0].shape[0]
+    pos = np.arange(P, P + S, dtype=np.int32)
+    dt = np.float32(-1.0) / np.float32(T)
+
+    def adarms(h, dense_w, dense_b, cond):
+        mod = linear(cond, dense_w, dense_b)[0]
+        n = rmsnorm(h, None, cfg["rms_eps"])
+        return (n + n * mod[None, :H] + mod[None, H:2 * H]).astype(np.float32), mod[2 * H:]
+
+    for s in range(T):
+        t = np.float32(1.0) + np.float32(s) * dt
+        tau = time_emb(float(t), H, cfg["min_period"], cfg["max_period"])[None, :]
+        cond = silu(linear(silu(linear(tau, w["w_tin"], w["b_tin"])), w["w_tout"], w["b_tout"]))
+        h = linear(x, w["w_ain"], w["b_ain"])
+        for l, lw in enumerate(w["layers"]):
+            xn, gate = adarms(h, lw["ada_in_w"], lw["ada_in_b"], cond)
+            q = rope_neox(linear(xn, lw["wq"]).reshape(S, n_q, hd), pos, cfg["rope_base"])
+            k = rope_neox(linear(xn, lw["wk"]).reshape(S, n_kv, hd), pos, cfg["rope_base"])
+            v = linear(xn, lw["wv"]).reshape(S, n_kv, hd)
+            att = attention(q, np.concatenate([kp[l], k]), np.concatenate([vp[l], v]), P, MASK_NONE)
+            h = h + linear(att, lw["wo"]) * gate[None, :]
+            xn, gate = adarms(h, lw["ada_post_w"], lw["ada_post_b"], cond)
+            inter = gelu_tanh(linear(xn, lw["wgate"])) * linear(xn, lw["wup"])
+            h = h + linear(inter.astype(np.float32), lw["wdown"]) * gate[None, :]
+        xf, _ = adarms(h, w["ada_final_w"], w["ada_final_b"], cond)
+        x = x + dt * linear(xf, w["w_aout"], w["b_aout"])
+    return x
+
+
 def preprocess_image_chw(img):
     """img: [side][side][3] uint8 (0..255) or float32 (0..1), H W C -> float32 [3][side][side] in [-1, 1]
     (src/modules/preprocess.h:56-75: px = u8 / 255.0f, out = px * 2 - 1)."""

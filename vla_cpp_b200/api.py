@@ -394,15 +394,20 @@ class Gguf:
 class _PolicyConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("model", "n_layers", "H", "n_q", "n_kv", "head_dim", "inter", "chunk",
                                           "action_dim", "state_dim", "steps", "self_every")] + [
-        ("rms_eps", C.c_float), ("rope_base", C.c_float), ("min_period", C.c_double), ("max_period", C.c_double)]
+        ("rms_eps", C.c_float), ("rope_base", C.c_float), ("min_period", C.c_double), ("max_period", C.c_double),
+        ("cond_dim", C.c_int32)]
 
 
 _PER_LAYER = ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "ln_in", "ln_post")
 _GLOBAL = ("w_sp", "b_sp", "w_ain", "b_ain", "w_at1", "b_at1", "w_at2", "b_at2", "out_norm", "w_aout", "b_aout")
+# pi0.5 (model 2): adaptive-norm dense maps per layer and the time MLP, all float32
+_ADA_PER_LAYER = ("ada_in_w", "ada_in_b", "ada_post_w", "ada_post_b")
+_ADA_GLOBAL = ("ada_final_w", "ada_final_b", "w_tin", "b_tin", "w_tout", "b_tout")
 
 
 class _PolicyWeights(C.Structure):
-    _fields_ = [(n, C.POINTER(C.c_void_p)) for n in _PER_LAYER] + [(n, C.c_void_p) for n in _GLOBAL]
+    _fields_ = ([(n, C.POINTER(C.c_void_p)) for n in _PER_LAYER] + [(n, C.c_void_p) for n in _GLOBAL] +
+                [(n, C.POINTER(C.c_void_p)) for n in _ADA_PER_LAYER] + [(n, C.c_void_p) for n in _ADA_GLOBAL])
 
 
 class PolicyEngine:
@@ -416,10 +421,25 @@ class PolicyEngine:
         import torch
 
         self.cfg = dict(cfg)
-        c = _PolicyConfig(**{k: cfg[k] for k, _ in _PolicyConfig._fields_})
+        c = _PolicyConfig(**{k: cfg.get(k, 0) if k == "cond_dim" else cfg[k] for k, _ in _PolicyConfig._fields_})
         w = _PolicyWeights()
         keep = []
+        ada = cfg["model"] == 2
+        for name in _ADA_PER_LAYER + _ADA_GLOBAL if ada else ():
+            if name in _ADA_PER_LAYER:
+                ts = [t.contiguous() for t in weights[name]]
+                assert all(t.is_cuda and t.dtype == torch.float32 for t in ts), name
+                arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+                keep += [ts, arr]
+                setattr(w, name, C.cast(arr, C.POINTER(C.c_void_p)))
+            else:
+                t = weights[name].contiguous()
+                assert t.is_cuda and t.dtype == torch.float32, name
+                keep.append(t)
+                setattr(w, name, t.data_ptr())
         for name in _PER_LAYER:
+            if ada and name.startswith("ln"):
+                continue
             ts = [t.contiguous() for t in weights[name]]
             want = torch.float32 if name.startswith("ln") else torch.bfloat16
             assert all(t.is_cuda and t.dtype == want for t in ts), name

@@ -28,7 +28,7 @@ namespace vb {
 constexpr int SK_ROWS = 8;      // activation rows per pass
 constexpr int SK_KT = 1024;     // activation tile (floats per row) in shared memory
 constexpr int SK_COLS = 16;     // weight rows (output columns) per CTA: 8 warps x 2
-enum { SK_ACT_NONE = 0, SK_ACT_RELU = 1, SK_ACT_GELU_ERF = 2 };
+enum { SK_ACT_NONE = 0, SK_ACT_RELU = 1, SK_ACT_GELU_ERF = 2, SK_ACT_SILU = 3 };
 
 // out[m][n] = (residual ? residual[m][n] : 0) + act(bias[n] + sum_k x[m][k] W[n][k]),  m in [m0, m0 + rows)
 __global__ void __launch_bounds__(256) f32_skinny_linear_kernel(const float *__restrict__ W, const float *__restrict__ bias,
@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(256) f32_skinny_linear_kernel(const float *__r
                 v += bias ? bias[n] : 0.0f;
                 if (act == SK_ACT_RELU) v = fmaxf(v, 0.0f);
                 else if (act == SK_ACT_GELU_ERF) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+                else if (act == SK_ACT_SILU) v = v / (1.0f + expf(-v));
                 const size_t o = (size_t)(m0 + m) * N + n;
                 out[o] = residual ? residual[o] + v : v;
             }
@@ -173,8 +174,8 @@ __global__ void __launch_bounds__(256) f32_layernorm_kernel(const float *__restr
     }
 }
 
-static int skinny_linear(const float *W, const float *bias, const float *x, const float *residual, float *out, int M, int N, int K,
-                         int act, cudaStream_t cs) {
+int skinny_linear(const float *W, const float *bias, const float *x, const float *residual, float *out, int M, int N, int K,
+                  int act, cudaStream_t cs) {
     for (int m0 = 0; m0 < M; m0 += SK_ROWS) {
         const int rows = M - m0 < SK_ROWS ? M - m0 : SK_ROWS;
         int rc = launch_pdl(f32_skinny_linear_kernel, dim3((N + SK_COLS - 1) / SK_COLS), dim3(256), 0, cs, W, bias, x, residual, out, m0,

@@ -6,6 +6,12 @@
 //   L expert layers    fused RMSNorm+QKV+RoPE(+KV append) -> attention -> Wo + residual ->
 //                      fused RMSNorm + gate/up + activation -> Wdown + residual
 //   head               v = W_aout (rms(h) * w_out) + b on the action rows;  x += dt * v   (x stays f32)
+// pi0.5 (model 2; src/models/pi05.cpp:208-292,604-631): no state token, the suffix embedding is W_ain x + b alone, and
+// time enters through adaptive RMSNorm: cond_k = silu(W_tout silu(W_tin tau_k + b) + b), per layer
+// (scale | shift | gate) = W_ada cond_k + b, x_norm = rms(x) (1 + scale) + shift, residual += gate * projection.  All
+// of these vectors depend on the step schedule only, so they are computed once, in float32, when the engine is built;
+// a layer is adarms_norm -> q|k|v GEMM -> rotation/split/append -> attention (no mask) -> Wo with the gate in its
+// residual epilogue -> adarms_norm -> gate/up -> Wdown with the gate.
 // W_at1 [a ; tau_k] is split: the tau_k half is a per-step constant vector computed once at
 // engine creation, so the GEMM runs over K = H only.  RMSNorm weights are folded into the
 // projections that consume the normalised activations (load-time step).
@@ -64,7 +70,7 @@ constexpr int AIN_ROWS = 16;
 __global__ void __launch_bounds__(256) action_in_kernel(const float *__restrict__ x,
                                                         const __nv_bfloat16 *__restrict__ w_ain,
                                                         const float *__restrict__ b_ain, __nv_bfloat16 *__restrict__ a,
-                                                        int n_rows, int H, int A) {
+                                                        float *__restrict__ a_f32, int n_rows, int H, int A) {
     __shared__ float sx[AIN_ROWS][64];
     pdl_launch_dependents();
     pdl_wait();
@@ -94,6 +100,27 @@ __global__ void __launch_bounds__(256) action_in_kernel(const float *__restrict_
             }
         }
         a[(size_t)(row0 + r) * H + o] = __float2bfloat16(acc);
+        if (a_f32) a_f32[(size_t)(row0 + r) * H + o] = acc;  // pi0.5: the embedding is the residual stream itself
+    }
+}
+
+// Adaptive RMSNorm (build_adarms, src/models/pi05.cpp:208-224): n = x * rsqrt(mean x^2 + eps);
+// y = bf16(n + n * scale[k] + shift[k]); mod = scale | shift | gate, H floats each.  One warp per row.
+__global__ void __launch_bounds__(256) adarms_norm_kernel(const float *__restrict__ x, const float *__restrict__ mod,
+                                                          __nv_bfloat16 *__restrict__ y, int M, int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const float *xr = x + (size_t)row * H;
+    float ss = 0.0f;
+    for (int k = lane; k < H; k += 32) ss = fmaf(xr[k], xr[k], ss);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int k = lane; k < H; k += 32) {
+        const float n = xr[k] * r;
+        y[(size_t)row * H + k] = __float2bfloat16(n + n * mod[k] + mod[H + k]);
     }
 }
 
@@ -159,6 +186,7 @@ struct vlab200_engine {
     // prepared weights
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
     vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
+    vb::DevBuf mods;  // pi0.5: float32 [n_layers][2][steps][3H] (scale | shift | gate of the two norms), then [steps][3H] final
     // workspace
     vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage, pad_stage, vbuf;
     int rope_pos0 = -1;
@@ -184,25 +212,27 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
     const vlab200_policy_config &c = e->c;
     const int L = c.n_layers, H = c.H, hd = c.head_dim, I = c.inter;
     const int qf = e->qf, kvf = e->kvf;
+    const bool ada = c.model == 2;  // adaptive norms: nothing to fold, the norm is its own kernel
     e->wqkv.resize(L); e->wo.resize(L); e->wgu.resize(L); e->wdown.resize(L); e->wkx.resize(L); e->wvx.resize(L);
     int rc;
     for (int l = 0; l < L; ++l) {
         const bool self = e->is_self[l];
         const int rows = self ? qf + 2 * kvf : qf;
+        const float *ln_in = ada ? nullptr : w->ln_in[l], *ln_post = ada ? nullptr : w->ln_post[l];
         if ((rc = e->wqkv[l].alloc((size_t)rows * H * 2))) return rc;
         auto *dst = e->wqkv[l].as<__nv_bfloat16>();
-        if ((rc = fold_rows(w->wq[l], w->ln_in[l], dst, qf, H, 1, 0))) return rc;
+        if ((rc = fold_rows(w->wq[l], ln_in, dst, qf, H, 1, 0))) return rc;
         if (self) {
-            if ((rc = fold_rows(w->wk[l], w->ln_in[l], dst + (size_t)qf * H, kvf, H, 1, 0))) return rc;
-            if ((rc = fold_rows(w->wv[l], w->ln_in[l], dst + (size_t)(qf + kvf) * H, kvf, H, 1, 0))) return rc;
+            if ((rc = fold_rows(w->wk[l], ln_in, dst + (size_t)qf * H, kvf, H, 1, 0))) return rc;
+            if ((rc = fold_rows(w->wv[l], ln_in, dst + (size_t)(qf + kvf) * H, kvf, H, 1, 0))) return rc;
         } else {
             if ((rc = copy_dev(e->wkx[l], w->wk[l], (size_t)kvf * kvf * 2))) return rc;
             if ((rc = copy_dev(e->wvx[l], w->wv[l], (size_t)kvf * kvf * 2))) return rc;
         }
         if ((rc = copy_dev(e->wo[l], w->wo[l], (size_t)H * qf * 2))) return rc;
         if ((rc = e->wgu[l].alloc((size_t)2 * I * H * 2))) return rc;
-        if ((rc = fold_rows(w->wgate[l], w->ln_post[l], e->wgu[l].p, I, H, 2, 0))) return rc;
-        if ((rc = fold_rows(w->wup[l], w->ln_post[l], e->wgu[l].p, I, H, 2, 1))) return rc;
+        if ((rc = fold_rows(w->wgate[l], ln_post, e->wgu[l].p, I, H, 2, 0))) return rc;
+        if ((rc = fold_rows(w->wup[l], ln_post, e->wgu[l].p, I, H, 2, 1))) return rc;
         if ((rc = copy_dev(e->wdown[l], w->wdown[l], (size_t)H * I * 2))) return rc;
     }
     const int A = c.action_dim, sd = c.state_dim, T = c.steps;
@@ -212,15 +242,17 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
         if ((rc = copy_dev(e->w_sp, w->w_sp, (size_t)H * sd * 2))) return rc;
         if ((rc = copy_dev(e->b_sp, w->b_sp, (size_t)H * 4))) return rc;
     }
-    if ((rc = e->w_at1l.alloc((size_t)H * H * 2))) return rc;
-    VB_CUDA(cudaMemcpy2D(e->w_at1l.p, (size_t)H * 2, w->w_at1, (size_t)2 * H * 2, (size_t)H * 2, H,
-                         cudaMemcpyDeviceToDevice));
+    if (!ada) {
+        if ((rc = e->w_at1l.alloc((size_t)H * H * 2))) return rc;
+        VB_CUDA(cudaMemcpy2D(e->w_at1l.p, (size_t)H * 2, w->w_at1, (size_t)2 * H * 2, (size_t)H * 2, H,
+                             cudaMemcpyDeviceToDevice));
+    }
     // time embeddings tau_k on the host in double, as the reference computes them
     // (src/layers/embed.h:61-73; pi0 forms the timestep in float, SmolVLA in double)
     std::vector<float> tau((size_t)T * H);
     const float dtf = -1.0f / (float)T;
     for (int s = 0; s < T; ++s) {
-        const double t = c.model == 0 ? (double)(1.0f + (float)s * dtf) : 1.0 + (double)s * (double)dtf;
+        const double t = c.model != 1 ? (double)(1.0f + (float)s * dtf) : 1.0 + (double)s * (double)dtf;
         const int half = H / 2;
         for (int i = 0; i < half; ++i) {
             const double frac = half == 1 ? 0.0 : (double)i / (double)(half - 1);
@@ -233,15 +265,38 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
     DevBuf tau_d;
     if ((rc = tau_d.alloc(tau.size() * 4))) return rc;
     VB_CUDA(cudaMemcpy(tau_d.p, tau.data(), tau.size() * 4, cudaMemcpyHostToDevice));
-    if ((rc = e->tvec.alloc((size_t)T * H * 4))) return rc;
-    time_vector_kernel<<<(T * H * 32 + 255) / 256, 256>>>(static_cast<const __nv_bfloat16 *>(w->w_at1), w->b_at1,
-                                                         tau_d.as<float>(), e->tvec.as<float>(), H, T);
-    VB_CUDA(cudaGetLastError());
-    if ((rc = copy_dev(e->w_at2, w->w_at2, (size_t)H * H * 2))) return rc;
-    if ((rc = copy_dev(e->b_at2, w->b_at2, (size_t)H * 4))) return rc;
+    if (!ada) {
+        if ((rc = e->tvec.alloc((size_t)T * H * 4))) return rc;
+        time_vector_kernel<<<(T * H * 32 + 255) / 256, 256>>>(static_cast<const __nv_bfloat16 *>(w->w_at1), w->b_at1,
+                                                             tau_d.as<float>(), e->tvec.as<float>(), H, T);
+        VB_CUDA(cudaGetLastError());
+        if ((rc = copy_dev(e->w_at2, w->w_at2, (size_t)H * H * 2))) return rc;
+        if ((rc = copy_dev(e->b_at2, w->b_at2, (size_t)H * 4))) return rc;
+    } else {
+        // cond_k for every step, then every layer's (scale | shift | gate) for every step: float32 throughout
+        // (the reference keeps these weights float32, src/models/pi05.cpp:467-484)
+        const int Hc = c.cond_dim > 0 ? c.cond_dim : H;
+        DevBuf c1, cond;
+        if ((rc = c1.alloc((size_t)T * Hc * 4)) || (rc = cond.alloc((size_t)T * Hc * 4))) return rc;
+        if ((rc = skinny_linear(w->w_tin, w->b_tin, tau_d.as<float>(), nullptr, c1.as<float>(), T, Hc, H, 3, nullptr))) return rc;
+        if ((rc = skinny_linear(w->w_tout, w->b_tout, c1.as<float>(), nullptr, cond.as<float>(), T, Hc, Hc, 3, nullptr))) return rc;
+        const size_t per = (size_t)T * 3 * H;
+        if ((rc = e->mods.alloc(((size_t)L * 2 + 1) * per * 4))) return rc;
+        float *mods = e->mods.as<float>();
+        for (int l = 0; l < L; ++l) {
+            if ((rc = skinny_linear(w->ada_in_w[l], w->ada_in_b[l], cond.as<float>(), nullptr, mods + ((size_t)l * 2) * per, T, 3 * H, Hc, 0, nullptr)))
+                return rc;
+            if ((rc = skinny_linear(w->ada_post_w[l], w->ada_post_b[l], cond.as<float>(), nullptr, mods + ((size_t)l * 2 + 1) * per, T, 3 * H, Hc, 0,
+                                    nullptr)))
+                return rc;
+        }
+        if ((rc = skinny_linear(w->ada_final_w, w->ada_final_b, cond.as<float>(), nullptr, mods + (size_t)L * 2 * per, T, 3 * H, Hc, 0, nullptr)))
+            return rc;
+        VB_CUDA(cudaDeviceSynchronize());  // c1 / cond are released on return
+    }
     // the output norm weight is folded into the action head like the layer norms into their projections
     if ((rc = e->w_aout.alloc((size_t)A * H * 2))) return rc;
-    if ((rc = fold_rows(w->w_aout, w->out_norm, e->w_aout.p, A, H, 1, 0))) return rc;
+    if ((rc = fold_rows(w->w_aout, ada ? nullptr : w->out_norm, e->w_aout.p, A, H, 1, 0))) return rc;
     if ((rc = copy_dev(e->b_aout, w->b_aout, (size_t)A * 4))) return rc;
     // workspace
     const size_t B = e->max_obs, M = B * e->S, Mc = B * c.chunk;
@@ -345,6 +400,48 @@ static int layer_stage(vlab200_engine *e, int l, int stage, int n_obs, const flo
     }
 }
 
+// One pi0.5 expert layer at Euler step `step` (build_expert_layer, src/models/pi05.cpp:226-292): seven launches.
+static int ada_layer(vlab200_engine *e, int l, int step, int n_obs, const float *rope, cudaStream_t cs) {
+    const vlab200_policy_config &c = e->c;
+    const int H = c.H, S = e->S, hd = c.head_dim, I = c.inter, half = hd / 2, T = c.steps;
+    const int M = n_obs * S, qkv_n = e->qf + 2 * e->kvf;
+    const size_t per = (size_t)T * 3 * H;
+    const float *mod_in = e->mods.as<float>() + ((size_t)l * 2) * per + (size_t)step * 3 * H;
+    const float *mod_post = e->mods.as<float>() + ((size_t)l * 2 + 1) * per + (size_t)step * 3 * H;
+    vlab200_kv_store live = engine_store(e, e->max_obs);
+    live.n_obs = n_obs;
+    const size_t layer_off = (size_t)l * e->max_obs * c.n_kv * e->cap * hd;
+    live.k_pages = e->k_pages.as<__nv_bfloat16>() + layer_off;
+    live.v_pages = e->v_pages.as<__nv_bfloat16>() + layer_off;
+    live.n_layers = 1;
+    int rc;
+    float *h = e->h.as<float>();
+    __nv_bfloat16 *hb = e->hb.as<__nv_bfloat16>();
+    if ((rc = launch_pdl(adarms_norm_kernel, dim3((M + 7) / 8), dim3(256), 0, cs, static_cast<const float *>(h), mod_in, hb, M, H, c.rms_eps)))
+        return rc;
+    GemmParams p{};
+    p.M = M; p.N = qkv_n; p.K = H; p.epi = EPI_BIAS_ACT; p.act = ACT_NONE; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
+    if ((rc = dense_gemm(hb, H, e->wqkv[l].p, p, cs))) return rc;
+    if ((rc = rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S, c.n_q, c.n_kv, c.n_kv, hd,
+                         e->cap, e->P, cs)))
+        return rc;
+    // no mask: every action token sees the prefix and every action token (soft_max_ext without a mask, pi05.cpp:264)
+    if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, e->P + S, 0, nullptr, cs))) return rc;
+    p = GemmParams{};
+    p.M = M; p.N = H; p.K = e->qf; p.epi = EPI_RESIDUAL; p.colscale = mod_in + 2 * H;
+    p.h = h; p.out_bf = hb; p.ld_out = H;
+    if ((rc = dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs))) return rc;
+    if ((rc = launch_pdl(adarms_norm_kernel, dim3((M + 7) / 8), dim3(256), 0, cs, static_cast<const float *>(h), mod_post, hb, M, H, c.rms_eps)))
+        return rc;
+    p = GemmParams{};
+    p.M = M; p.N = 2 * I; p.K = H; p.epi = EPI_GATED; p.act = ACT_GELU_TANH; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = I;
+    if ((rc = dense_gemm(hb, H, e->wgu[l].p, p, cs))) return rc;
+    p = GemmParams{};
+    p.M = M; p.N = H; p.K = I; p.epi = EPI_RESIDUAL; p.colscale = mod_post + 2 * H;
+    p.h = h; p.out_bf = hb; p.ld_out = H;
+    return dense_gemm(e->g.p, I, e->wdown[l].p, p, cs);
+}
+
 }  // namespace vb
 
 extern "C" {
@@ -357,12 +454,17 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
     }
     const vlab200_policy_config &c = *cfg;
     if (c.n_layers <= 0 || c.H <= 0 || c.n_q <= 0 || c.n_kv <= 0 || c.n_q % c.n_kv || c.inter <= 0 || c.chunk <= 0 ||
-        c.action_dim <= 0 || c.action_dim > 64 || c.action_dim % 8 || c.state_dim > 64 || c.steps <= 0 || (c.model != 0 && c.model != 1)) {
+        c.action_dim <= 0 || c.action_dim > 64 || c.action_dim % 8 || c.state_dim > 64 || c.steps <= 0 || c.model < 0 || c.model > 2) {
         vb::set_last_error("vlab200_engine_create: bad configuration");
         return nullptr;
     }
     if (c.H % 8) {
         vb::set_last_error("vlab200_engine_create: hidden size %d is not a multiple of 8", c.H);
+        return nullptr;
+    }
+    if (c.model == 2 && (!w->ada_in_w || !w->ada_in_b || !w->ada_post_w || !w->ada_post_b || !w->ada_final_w || !w->ada_final_b ||
+                         !w->w_tin || !w->b_tin || !w->w_tout || !w->b_tout || (c.n_q + 2 * c.n_kv) * c.head_dim > c.inter)) {
+        vb::set_last_error("vlab200_engine_create: pi0.5 needs the adaptive-norm and time-MLP weights and (n_q + 2 n_kv) head_dim <= inter");
         return nullptr;
     }
     vlab200_engine *e = new (std::nothrow) vlab200_engine();
@@ -375,13 +477,13 @@ vlab200_engine *vlab200_engine_create(const vlab200_policy_config *cfg, const vl
     e->max_obs = max_obs;
     e->P = prefix_len;
     e->P_max = prefix_len;
-    e->S = c.chunk + (c.model == 0 ? 1 : 0);
+    e->S = c.chunk + (c.model == 0 ? 1 : 0);  // pi0 alone carries the state as a suffix token
     e->cap = e->P + e->S;
     e->qf = c.n_q * c.head_dim;
     e->kvf = c.n_kv * c.head_dim;
     e->is_self.resize(c.n_layers);
     for (int l = 0; l < c.n_layers; ++l)
-        e->is_self[l] = (c.model == 0) || (c.self_every <= 1) || (l % c.self_every == 0);
+        e->is_self[l] = (c.model != 1) || (c.self_every <= 1) || (l % c.self_every == 0);
     const int brc = vb::engine_build(e, w);
     if (brc != VLAB200_OK) {
         if (brc != VLAB200_ERR_CUDA) vb::set_last_error("vlab200_engine_create: building the engine failed with status %d", brc);
@@ -440,9 +542,25 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     const float dt = -1.0f / (float)c.steps;
     for (int step = 0; step < c.steps; ++step) {
         if ((rc = vb::launch_pdl(vb::action_in_kernel, dim3((Mc + vb::AIN_ROWS - 1) / vb::AIN_ROWS, (H + 255) / 256), dim3(256), 0, cs,
-                                 e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(), Mc,
-                                 H, A)))
+                                 e->x.as<float>(), e->w_ain.as<__nv_bfloat16>(), e->b_ain.as<float>(), e->a.as<__nv_bfloat16>(),
+                                 c.model == 2 ? e->h.as<float>() : static_cast<float *>(nullptr), Mc, H, A)))
             return rc;
+        if (c.model == 2) {
+            for (int l = 0; l < c.n_layers; ++l)
+                if ((rc = vb::ada_layer(e, l, step, n_obs, rs, cs))) return rc;
+            const float *mod_f = e->mods.as<float>() + (size_t)c.n_layers * 2 * c.steps * 3 * H + (size_t)step * 3 * H;
+            if ((rc = vb::launch_pdl(vb::adarms_norm_kernel, dim3((M + 7) / 8), dim3(256), 0, cs, static_cast<const float *>(e->h.as<float>()),
+                                     mod_f, e->hb.as<__nv_bfloat16>(), M, H, c.rms_eps)))
+                return rc;
+            vb::GemmParams p{};
+            p.M = M; p.N = A; p.K = H; p.epi = vb::EPI_BIAS_ACT; p.act = vb::ACT_NONE;
+            p.out_f32 = e->vbuf.as<float>(); p.bias = e->b_aout.as<float>(); p.ld_out = A;
+            if ((rc = vb::dense_gemm(e->hb.p, H, e->w_aout.p, p, cs))) return rc;
+            if ((rc = vb::launch_pdl(vb::euler_kernel, dim3((Mc * A + 255) / 256), dim3(256), 0, cs, e->x.as<float>(),
+                                     e->vbuf.as<float>(), Mc * A, A, chunk, S, dt)))
+                return rc;
+            continue;
+        }
         if (c.model == 0 &&
             (rc = vb::launch_pdl(vb::state_token_kernel, dim3(n_obs), dim3(256), 0, cs, state, e->w_sp.as<__nv_bfloat16>(),
                                  e->b_sp.as<float>(), e->h.as<float>(), e->hb.as<__nv_bfloat16>(), H, c.state_dim, S)))
@@ -503,6 +621,7 @@ int32_t vlab200_engine_run_stage(vlab200_engine *e, int32_t layer, int32_t stage
     if (!e || layer < 0 || layer >= e->c.n_layers || stage < 0 || stage >= vb::kLayerStages || n_obs <= 0 ||
         n_obs > e->max_obs || reps <= 0)
         return VLAB200_ERR_ARG;
+    if (e->c.model == 2) return VLAB200_ERR_UNSUPPORTED;  // the pi0.5 layer has its own seven stages
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     const float *rs = e->rope_self.as<float>(), *rx = e->rope_cross.as<float>();
     for (int i = 0; i < reps; ++i) {

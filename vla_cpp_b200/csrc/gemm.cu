@@ -10,7 +10,7 @@
 // epilogue warps (two per TMEM lane quarter) drain the accumulator.
 //
 // Epilogues
-//   RESIDUAL  h[m][n] += C (+ bias[n])         (f32 master copy) and hb = bf16(h)   -- Wo, Wdown
+//   RESIDUAL  h[m][n] += C (* colscale[n]) (+ bias[n])   (f32 master copy) and hb = bf16(h)   -- Wo, Wdown
 //   GATED     g[m][i] = act(r C[m][2i]) * (r C[m][2i+1]),  r = rsqrt(mean a^2 + eps) -- Wgate/Wup
 //             (gate and up rows interleaved in W; act = SiLU or tanh-GELU)
 //   BIAS_ACT  y[m'][n] = act(C + bias[n]); bf16 and/or f32 output; rows may be re-mapped
@@ -261,6 +261,11 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                 tmem_ld_wait();
                 if (!row_ok) continue;
                 if (p.epi == EPI_RESIDUAL) {
+                    if (p.colscale) {  // gated residual: the projection's column n is multiplied by colscale[n] first
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (n + e < p.N) v[e] = __float_as_uint(__uint_as_float(v[e]) * __ldg(p.colscale + n + e));
+                    }
                     if (p.bias) {
 #pragma unroll
                         for (int e = 0; e < 32; ++e)

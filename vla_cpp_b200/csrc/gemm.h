@@ -16,6 +16,7 @@ struct GemmParams {
     __nv_bfloat16 *out_bf;  // RESIDUAL: bf16 mirror [M][N]; GATED: [M][N/2]; BIAS_ACT: bf16 output (optional)
     float *out_f32;         // BIAS_ACT: f32 output (optional)
     const float *bias;      // BIAS_ACT, RESIDUAL: [N] (optional)
+    const float *colscale;  // RESIDUAL: [N] factor on the projection before it is added (optional; adaRMS gates)
     int ld_out;             // row stride (elements) of out_bf / out_f32 / h
     int rows_in, rows_out, row_off;  // BIAS_ACT row re-mapping (rows_in == 0: identity)
     int scatter_hd, scatter_cap;     // BIAS_ACT into head-major pages: [m / rows_in][n / hd][cap][hd] (0: off)

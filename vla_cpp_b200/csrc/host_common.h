@@ -92,4 +92,9 @@ struct DevBuf {
 // optionally with the Gemma-norm "+1" (gguf.cu).  VLAB200_OK or an error with the last-error text set.
 int gguf_upload(const vlab200_gguf *g, const char *name, int64_t d0, int64_t d1, bool as_bf16, bool gemma, DevBuf *out);
 
+// Float32 linear for a few rows (bitvla_fp32head.cu): out[m][n] = (residual ? residual[m][n] : 0) +
+// act(bias[n] + sum_k x[m][k] W[n][k]), W float32 [N][K] streamed once; act 0 none, 1 ReLU, 2 erf-GELU, 3 SiLU.
+int skinny_linear(const float *W, const float *bias, const float *x, const float *residual, float *out, int M, int N, int K,
+                  int act, cudaStream_t cs);
+
 }  // namespace vb
