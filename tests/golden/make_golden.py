@@ -96,6 +96,7 @@ def gguf_names(ref):
     sys.path.insert(0, os.path.join(ref, "scripts"))
     import convert_bitvla_to_gguf as cb
     import convert_pi0_to_gguf as cp
+    import convert_pi05_to_gguf as cp5
     import convert_smolvla_to_gguf as cs
     import gguf_blocks as gb
 
@@ -123,6 +124,16 @@ def gguf_names(ref):
     cb._add_bit(r, "lm.blk.0.attn_q", w)
     cb._add_bit_fused(r, "lm.blk.0.ffn_gate_up", [w, w])
     out["bitvla"] = {"packed": r.tensors, "packed_flag_key": "bitvla.quant.int2_packed"}
+    # pi0.5: write_pi_kv(adarms=True) and the adaptive-norm expert blocks (scripts/convert_pi05_to_gguf.py:81-96,250-262)
+    r = _Recorder()
+    gb.write_pi_kv(r, cp5.KV, base, adarms=True)
+
+    class _Sf:
+        get_tensor = staticmethod(tiny)
+
+    cp5._write_adarms_blocks(r, _Sf, 2)
+    out["pi05"] = {"arch": cp5.ARCH, "kv": r.kv, "decoder_blocks": r.tensors, "projections": list(cp5.PROJ_SUFFIXES),
+                   "output_norm": ["aex.output_norm.weight", "aex.output_norm.bias"]}
     # the SigLIP tower as both converters write it (scripts/gguf_blocks.py write_siglip_tower / write_paligemma_vision,
     # scripts/convert_smolvla_to_gguf.py:213-214), one layer
     r = _Recorder()

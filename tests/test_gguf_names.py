@@ -38,7 +38,7 @@ def write_metadata_only(path, arch):
     w.close()
 
 
-@pytest.mark.parametrize("arch", ["pi0", "smolvla"])
+@pytest.mark.parametrize("arch", ["pi0", "smolvla", "pi05"])
 def test_a_file_with_the_converters_metadata_keys_loads(tmp_path, arch):
     import vla_cpp_b200
 

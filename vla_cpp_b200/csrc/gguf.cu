@@ -410,11 +410,12 @@ extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g
     if (!g) return vb::set_last_error("gguf: null handle"), nullptr;
     char arch[32] = "";
     vlab200_gguf_meta_str(g, "general.architecture", arch, sizeof arch);
+    const bool pi05 = std::strcmp(arch, "pi05") == 0;
     const bool pi0 = std::strcmp(arch, "pi0") == 0, smol = std::strcmp(arch, "smolvla") == 0;
-    if (!pi0 && !smol)
-        return vb::set_last_error("gguf: general.architecture is '%s'; pi0 and smolvla checkpoints are mapped to the engine", arch), nullptr;
+    if (!pi0 && !smol && !pi05)
+        return vb::set_last_error("gguf: general.architecture is '%s'; pi0, pi05 and smolvla checkpoints are mapped to the engine", arch), nullptr;
     const std::string pfx = std::string(arch) + ".";
-    // metadata keys of src/models/pi0.cpp:267-293 and src/models/smolvla.cpp:604-632
+    // metadata keys of src/models/pi0.cpp:267-293, src/models/pi05.cpp:292-326 and src/models/smolvla.cpp:604-632
     uint32_t n_layers, H, n_q, n_kv, hd, inter, chunk, steps, sdim, adim, self_every = 1;
     const struct { const char *key; uint32_t *dst; } u32s[] = {
         {"n_layers", &n_layers}, {"expert_h", &H}, {"n_q_heads", &n_q}, {"n_kv_heads", &n_kv},
@@ -426,15 +427,18 @@ extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g
     if (smol && vlab200_gguf_meta_u32(g, "smolvla.self_attn_every_n_layers", &self_every) != VLAB200_OK)
         return vb::set_last_error("gguf: missing u32 metadata smolvla.self_attn_every_n_layers"), nullptr;
     vlab200_policy_config cfg{};
-    cfg.model = pi0 ? 0 : 1;
+    cfg.model = pi0 ? 0 : (pi05 ? 2 : 1);
     cfg.n_layers = (int32_t)n_layers; cfg.H = (int32_t)H; cfg.n_q = (int32_t)n_q; cfg.n_kv = (int32_t)n_kv;
     cfg.head_dim = (int32_t)hd; cfg.inter = (int32_t)inter; cfg.chunk = (int32_t)chunk;
-    cfg.action_dim = (int32_t)adim; cfg.state_dim = (int32_t)sdim; cfg.steps = (int32_t)steps;
+    cfg.action_dim = (int32_t)adim; cfg.state_dim = pi05 ? 0 : (int32_t)sdim; cfg.steps = (int32_t)steps;
     cfg.self_every = (int32_t)self_every;
     double v;
     // SmolVLA fixes both constants in code (smolvla.cpp:622-624); pi0 reads them when present (pi0.cpp:289-293)
-    cfg.rms_eps = smol ? 1e-5f : (vlab200_gguf_meta_f64(g, "pi0.rms_norm_eps", &v) == VLAB200_OK ? (float)v : 1e-6f);
-    cfg.rope_base = (pi0 && vlab200_gguf_meta_f64(g, "pi0.rope_theta", &v) == VLAB200_OK) ? (float)v : 10000.0f;
+    cfg.rms_eps = smol ? 1e-5f : (vlab200_gguf_meta_f64(g, (pfx + "rms_norm_eps").c_str(), &v) == VLAB200_OK ? (float)v : 1e-6f);
+    cfg.rope_base = (!smol && vlab200_gguf_meta_f64(g, (pfx + "rope_theta").c_str(), &v) == VLAB200_OK) ? (float)v : 10000.0f;
+    uint32_t cond_dim = 0;
+    if (pi05 && vlab200_gguf_meta_u32(g, "pi05.adarms_cond_dim", &cond_dim) == VLAB200_OK) cfg.cond_dim = (int32_t)cond_dim;
+    const int64_t Hc = cfg.cond_dim > 0 ? cfg.cond_dim : (int64_t)H;
     if (vlab200_gguf_meta_f64(g, (pfx + "min_period").c_str(), &cfg.min_period) != VLAB200_OK ||
         vlab200_gguf_meta_f64(g, (pfx + "max_period").c_str(), &cfg.max_period) != VLAB200_OK)
         return vb::set_last_error("gguf: missing %smin_period / %smax_period", pfx.c_str(), pfx.c_str()), nullptr;
@@ -446,18 +450,25 @@ extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g
     vb::Upload up;
     const int64_t qd = (int64_t)n_q * hd, kvd = (int64_t)n_kv * hd;
     std::vector<const void *> wq(n_layers), wk(n_layers), wv(n_layers), wo(n_layers), wg(n_layers), wu(n_layers), wd(n_layers);
-    std::vector<const float *> ln_in(n_layers), ln_post(n_layers);
+    std::vector<const float *> ln_in(n_layers), ln_post(n_layers), ada_in_b(n_layers), ada_post_b(n_layers);
     for (uint32_t l = 0; l < n_layers; ++l) {
         const std::string b = "aex.blk." + std::to_string(l) + ".";
         // SmolVLA cross-attention layers project the VLM's K / V rows ([n_kv*hd] wide) instead of the expert's
         const bool cross = smol && self_every > 1 && l % self_every != 0;
         const int64_t kv_in = cross ? kvd : (int64_t)H;
-        ln_in[l] = static_cast<const float *>(up.get(g, b + "attn_norm.weight", H, 1, false, pi0));
+        if (pi05) {  // the norms are dense maps of the time conditioning: [3H][cond] + [3H] (src/models/pi05.cpp:467-474)
+            ln_in[l] = static_cast<const float *>(up.get(g, b + "attn_norm.weight", Hc, 3 * (int64_t)H, false, false));
+            ada_in_b[l] = static_cast<const float *>(up.get(g, b + "attn_norm.bias", 3 * (int64_t)H, 1, false, false));
+            ln_post[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.weight", Hc, 3 * (int64_t)H, false, false));
+            ada_post_b[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.bias", 3 * (int64_t)H, 1, false, false));
+        } else {
+            ln_in[l] = static_cast<const float *>(up.get(g, b + "attn_norm.weight", H, 1, false, pi0));
+            ln_post[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.weight", H, 1, false, pi0));
+        }
         wq[l] = up.get(g, b + "attn_q.weight", H, qd, true, false);
         wk[l] = up.get(g, b + "attn_k.weight", kv_in, kvd, true, false);
         wv[l] = up.get(g, b + "attn_v.weight", kv_in, kvd, true, false);
         wo[l] = up.get(g, b + "attn_o.weight", qd, H, true, false);
-        ln_post[l] = static_cast<const float *>(up.get(g, b + "ffn_norm.weight", H, 1, false, pi0));
         wg[l] = up.get(g, b + "ffn_gate.weight", H, inter, true, false);
         wu[l] = up.get(g, b + "ffn_up.weight", H, inter, true, false);
         wd[l] = up.get(g, b + "ffn_down.weight", inter, H, true, false);
@@ -465,17 +476,27 @@ extern "C" vlab200_engine *vlab200_engine_create_from_gguf(const vlab200_gguf *g
     vlab200_policy_weights w{};
     w.wq = wq.data(); w.wk = wk.data(); w.wv = wv.data(); w.wo = wo.data();
     w.wgate = wg.data(); w.wup = wu.data(); w.wdown = wd.data();
-    w.ln_in = ln_in.data(); w.ln_post = ln_post.data();
-    w.out_norm = static_cast<const float *>(up.get(g, "aex.output_norm.weight", H, 1, false, pi0));
     auto vec = [&](const char *name, int64_t n) { return static_cast<const float *>(up.get(g, name, n, 1, false, false)); };
+    if (pi05) {
+        w.ada_in_w = ln_in.data(); w.ada_in_b = ada_in_b.data(); w.ada_post_w = ln_post.data(); w.ada_post_b = ada_post_b.data();
+        w.ada_final_w = static_cast<const float *>(up.get(g, "aex.output_norm.weight", Hc, 3 * (int64_t)H, false, false));
+        w.ada_final_b = vec("aex.output_norm.bias", 3 * (int64_t)H);
+        w.w_tin = static_cast<const float *>(up.get(g, "time_mlp_in.weight", H, Hc, false, false));   w.b_tin = vec("time_mlp_in.bias", Hc);
+        w.w_tout = static_cast<const float *>(up.get(g, "time_mlp_out.weight", Hc, Hc, false, false)); w.b_tout = vec("time_mlp_out.bias", Hc);
+    } else {
+        w.ln_in = ln_in.data(); w.ln_post = ln_post.data();
+        w.out_norm = static_cast<const float *>(up.get(g, "aex.output_norm.weight", H, 1, false, pi0));
+    }
     if (pi0) {  // SmolVLA's state token belongs to the prefix (smolvla.cpp:1103-1104), not to the denoise loop
         w.w_sp = up.get(g, "state_proj.weight", sdim, H, true, false);
         w.b_sp = vec("state_proj.bias", H);
     }
     w.w_ain = up.get(g, "action_in_proj.weight", adim, H, true, false);       w.b_ain = vec("action_in_proj.bias", H);
-    w.w_at1 = up.get(g, "action_time_mlp_in.weight", 2 * (int64_t)H, H, true, false);
-    w.b_at1 = vec("action_time_mlp_in.bias", H);
-    w.w_at2 = up.get(g, "action_time_mlp_out.weight", H, H, true, false);     w.b_at2 = vec("action_time_mlp_out.bias", H);
+    if (!pi05) {
+        w.w_at1 = up.get(g, "action_time_mlp_in.weight", 2 * (int64_t)H, H, true, false);
+        w.b_at1 = vec("action_time_mlp_in.bias", H);
+        w.w_at2 = up.get(g, "action_time_mlp_out.weight", H, H, true, false);     w.b_at2 = vec("action_time_mlp_out.bias", H);
+    }
     w.w_aout = up.get(g, "action_out_proj.weight", H, adim, true, false);     w.b_aout = vec("action_out_proj.bias", adim);
     if (!up.ok) return nullptr;
     // the engine keeps its own prepared copies; the uploads are released when `up` goes out of scope

@@ -4,6 +4,8 @@
 // Follows the reference's predict paths: src/models/pi0.cpp:451-681 and src/models/smolvla.cpp:1476-1710.
 //   pi0      prefix = [image embeddings ; E[lang] * sqrt(hidden)], positions 0..P-1, no mask; the state goes
 //            into the suffix (normalised with the dataset statistics); P changes with the number of language tokens
+//   pi0.5    (src/models/pi05.cpp:505-705) as pi0 without a state token (the state is part of the prompt); the tower's
+//            embeddings are the raw projector output; actions are un-normalised by mean / std or by quantiles
 //   SmolVLA  prefix = [image embeddings * sqrt(hidden) ; E[lang padded to n_lang_max] * sqrt(hidden) ; state_proj(state)],
 //            padded language slots masked, the state token visible to itself only and rotated at position
 //            n_img + n_lang; suffix positions start one past it
@@ -21,7 +23,9 @@
 namespace vb {
 
 struct Predictor {
-    int arch = 0;  // 0 pi0, 1 SmolVLA
+    int arch = 0;  // 0 pi0, 1 SmolVLA, 2 pi0.5
+    bool quantile_norm = false;
+    std::vector<float> action_q01, action_q99;
     vla_config cfg{};
     vlab200_engine *eng = nullptr;
     vlab200_prefill *pre = nullptr;
@@ -80,7 +84,7 @@ static void read_stats(const vlab200_gguf *g, const char *name, std::vector<floa
 static bool load_tower(Predictor *p, const vlab200_gguf *g) {
     const bool smol = p->arch == 1;
     const vla_config &c = p->cfg;
-    const std::string pfx = smol ? "smolvla." : "pi0.";
+    const std::string pfx = smol ? "smolvla." : (p->arch == 2 ? "pi05." : "pi0.");
     int64_t vh = smol ? 768 : 1152, vl = smol ? 12 : 27, heads = smol ? 12 : 16, patch = smol ? 16 : 14,
             image = smol ? 512 : 224, shuffle = smol ? 4 : 1, inter = smol ? 3072 : 0, n_tok = smol ? 64 : 256;
     auto vu = [&](const char *k, int64_t &d) {
@@ -159,7 +163,8 @@ static bool load_tower(Predictor *p, const vlab200_gguf *g) {
     vlab200_vision_config vc{};
     vc.image = (int)image; vc.patch = (int)patch; vc.hidden = (int)vh; vc.n_layers = L; vc.n_heads = (int)heads;
     vc.inter = (int)inter; vc.shuffle = (int)shuffle; vc.out_dim = (int)c.hidden; vc.ln_eps = eps;
-    vc.out_scale = smol ? 0.0f : 1.0f / std::sqrt((float)c.hidden);
+    // pi0 scales the projector by 1/sqrt(hidden) (pi0.cpp:498); pi0.5 undoes that scale (pi05.cpp:572-577): raw output
+    vc.out_scale = p->arch == 0 ? 1.0f / std::sqrt((float)c.hidden) : 0.0f;
     p->vis = vlab200_vision_create(&vc, &w, p->max_views);
     p->vit_image = (int)image;
     return p->vis != nullptr && p->pixels.alloc((size_t)p->max_views * image * image * 3 * 4) == VLAB200_OK;
@@ -168,7 +173,7 @@ static bool load_tower(Predictor *p, const vlab200_gguf *g) {
 Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_config *cfg) {
     auto *p = new (std::nothrow) Predictor();
     if (!p) return nullptr;
-    p->arch = std::strcmp(arch, "pi0") == 0 ? 0 : 1;
+    p->arch = std::strcmp(arch, "pi0") == 0 ? 0 : (std::strcmp(arch, "pi05") == 0 ? 2 : 1);
     p->cfg = *cfg;
     const vla_config &c = p->cfg;
     const int64_t n_img_max = c.n_img * p->max_views;
@@ -180,7 +185,7 @@ Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_c
     std::vector<DevBuf> bufs((size_t)L * 9);
     std::vector<const void *> wq(L), wk(L), wv(L), wo(L), wg(L), wu(L), wd(L);
     std::vector<const float *> ln_in(L), ln_post(L);
-    const bool gemma = p->arch == 0;
+    const bool gemma = p->arch != 1;
     for (int l = 0; l < L && ok; ++l) {
         const std::string b = "vlm.blk." + std::to_string(l) + ".";
         DevBuf *d = &bufs[(size_t)l * 9];
@@ -237,6 +242,16 @@ Predictor *predictor_create(const vlab200_gguf *g, const char *arch, const vla_c
     read_stats(g, "state_std", p->state_std);
     read_stats(g, "action_mean", p->action_mean);
     read_stats(g, "action_std", p->action_std);
+    if (p->arch == 2) {  // src/models/pi05.cpp:411,361-366
+        char mode[32] = "";
+        p->quantile_norm = vlab200_gguf_meta_str(g, "pi05.norm_mode", mode, sizeof mode) == VLAB200_OK && std::strcmp(mode, "quantiles") == 0;
+        if (p->quantile_norm) {
+            p->action_q01.assign((size_t)c.real_action_dim, -1.0f);
+            p->action_q99.assign((size_t)c.real_action_dim, 1.0f);
+            read_stats(g, "action_q01", p->action_q01);
+            read_stats(g, "action_q99", p->action_q99);
+        }
+    }
     if (ok)
         ok = p->x_emb.alloc((size_t)p->max_prefix * H * 4) == VLAB200_OK && p->ids.alloc((size_t)c.n_lang * 4) == VLAB200_OK &&
              p->img_stage.alloc((size_t)n_img_max * H * 4) == VLAB200_OK &&
@@ -384,7 +399,9 @@ int predictor_run(Predictor *p, const vla_inputs *in, std::vector<float> *action
     for (int t = 0; t < chunk; ++t)
         for (int j = 0; j < ad; ++j) {
             float &v = (*actions)[(size_t)t * ad + j];
-            v = j < c.real_action_dim ? v * (p->action_std[(size_t)j] + c.norm_eps) + p->action_mean[(size_t)j] : 0.0f;
+            if (j >= c.real_action_dim) v = 0.0f;
+            else if (p->quantile_norm) v = (v + 1.0f) * (p->action_q99[(size_t)j] - p->action_q01[(size_t)j]) * 0.5f + p->action_q01[(size_t)j];
+            else v = v * (p->action_std[(size_t)j] + c.norm_eps) + p->action_mean[(size_t)j];
         }
     if (timed) {
         cudaEventElapsedTime(&stats->ms_prefill, p->ev[0], p->ev[1]);

@@ -66,11 +66,12 @@ bool resolve_config(const vlab200_gguf *g, const std::string &arch, vla_config *
     double v = 0;
     c->norm_eps = vlab200_gguf_meta_f64(g, (p + "norm_eps").c_str(), &v) == VLAB200_OK ? (float)v : 1e-8f;
     c->denormalized = 1;
-    if (arch == "pi0") {  // src/models/pi0.cpp:267-300
+    if (arch == "pi0" || arch == "pi05") {  // src/models/pi0.cpp:267-300, src/models/pi05.cpp:300-326
         c->n_img = 256;
         c->self_attn_every_n = 0;
-        c->rms_eps = vlab200_gguf_meta_f64(g, "pi0.rms_norm_eps", &v) == VLAB200_OK ? (float)v : 1e-6f;
-        c->rope_freq_base = vlab200_gguf_meta_f64(g, "pi0.rope_theta", &v) == VLAB200_OK ? (float)v : 10000.0f;
+        c->rms_eps = vlab200_gguf_meta_f64(g, (p + "rms_norm_eps").c_str(), &v) == VLAB200_OK ? (float)v : 1e-6f;
+        c->rope_freq_base = vlab200_gguf_meta_f64(g, (p + "rope_theta").c_str(), &v) == VLAB200_OK ? (float)v : 10000.0f;
+        if (arch == "pi05") c->n_state = 0;  // the state is part of the prompt, not a token of its own
     } else {              // src/models/smolvla.cpp:604-632
         if (!meta_u32(g, "smolvla.self_attn_every_n_layers", &every)) return false;
         int64_t n_img = 64;
@@ -102,8 +103,8 @@ vla_model *vla_model_load(const char *mmproj_path, const char *ckpt_path, const 
         char arch[32] = "";
         vlab200_gguf_meta_str(g, "general.architecture", arch, sizeof arch);
         vla_model *m = new (std::nothrow) vla_model();
-        if (!m || (std::strcmp(arch, "pi0") != 0 && std::strcmp(arch, "smolvla") != 0)) {
-            if (m) vb::set_last_error("vla_model_load: architecture '%s' is not served by this library (pi0, smolvla)", arch);
+        if (!m || (std::strcmp(arch, "pi0") != 0 && std::strcmp(arch, "pi05") != 0 && std::strcmp(arch, "smolvla") != 0)) {
+            if (m) vb::set_last_error("vla_model_load: architecture '%s' is not served by this library (pi0, pi05, smolvla)", arch);
             delete m;
             vlab200_gguf_close(g);
             return nullptr;
