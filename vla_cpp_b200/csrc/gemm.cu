@@ -21,6 +21,8 @@
 // add / mul / unary ggml node each; src/cuda/vla_cuda_bf16.cu:624-678 for the cuBLAS GEMM node).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include <atomic>
 
 #include "gemm.h"
@@ -410,8 +412,73 @@ constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile rel
 void dense_gemm_set_variant(int v) { g_gemm_variant.store((v >= 0 && v <= 4) ? v : 0, std::memory_order_relaxed); }
 int dense_gemm_variant() { return g_gemm_variant.load(std::memory_order_relaxed); }
 
+// Four tilings: one CTA per 128 x 256 tile, per 128 x 128 or 128 x 64 tile (more CTAs streaming the weights when the
+// problem has few rows), a CTA pair per 256 x 256 tile (half the shared-memory traffic per flop).  Cost of the cheapest
+// one in units of one 128 x 256 tile on one SM; the per-tile factors are measured ratios.
+static float tiling_cost(int M, int N, int n_sm, int *variant_out) {
+    const int tiles_m = (M + G_BM - 1) / G_BM, tiles_mp = (M + 2 * G_BM - 1) / (2 * G_BM);
+    const int tn256 = (N + 255) / 256, tn128 = (N + 127) / 128, tn64 = (N + 63) / 64, pairs = n_sm / 2;
+    auto waves = [](int tiles, int units) { return (tiles + units - 1) / units; };
+    const float cost256 = (float)waves(tiles_m * tn256, n_sm);
+    const float cost128 = N > 128 ? 0.60f * waves(tiles_m * tn128, n_sm) : 1e30f;
+    const float cost64 = N > 64 ? 0.33f * waves(tiles_m * tn64, n_sm) : 1e30f;  // few rows: as many CTAs as possible stream W
+    const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
+    int variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
+    float best = variant == 3 ? cost_pair : (variant == 2 ? cost128 : cost256);
+    if (cost64 < best) {
+        variant = 4;
+        best = cost64;
+    }
+    if (variant_out) *variant_out = variant;
+    return best;
+}
+
+static int dense_gemm_one(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream, int forced_variant);
+
 // Launches the GEMM.  A: bf16 [M][K] (row stride lda elements), W: bf16 [N][K].
+//
+// Rows are independent, so a problem whose tiles fill the machine unevenly is cut in two along M: the first rows as
+// CTA-pair tiles in a whole number of waves, the remaining rows with whichever tiling is cheapest for them (for
+// 6528 x 1024: 72 pair tiles on 74 pairs, then 128 tiles of 128 x 128 on 148 SMs, instead of 408 tiles in three waves).
+// Every output element is computed by the same arithmetic in either part, so results do not depend on the cut.
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
+    if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
+    const int n_sm = sm_count();
+    static const bool split_off = std::getenv("VLAB200_NO_GEMM_SPLIT") != nullptr;  // measurement knob
+    if (!split_off && dense_gemm_variant() == 0 && n_sm >= 2 && p.rows_in == 0 && p.scatter_hd == 0 && p.M > 2 * G_BM) {
+        const int pairs = n_sm / 2, tn256 = (p.N + 255) / 256, tiles_mp = (p.M + 2 * G_BM - 1) / (2 * G_BM);
+        int v_all = 0;
+        const float whole = tiling_cost(p.M, p.N, n_sm, &v_all);
+        // a second launch costs about 6 us; a 128 x 256 tile takes about K / 64 x 0.5 us
+        const float launch_pen = 6.0f / (0.5f * (float)((p.K + G_BK - 1) / G_BK));
+        float best = whole;
+        int best_rows = 0;
+        for (int w = 1; w * pairs < tiles_mp * tn256; ++w) {
+            const int a = w * pairs / tn256;  // pair row-tiles that fit into w waves
+            if (a <= 0 || a >= tiles_mp) continue;
+            const float c = kPairTileFactor * (float)w + tiling_cost(p.M - a * 2 * G_BM, p.N, n_sm, nullptr) + launch_pen;
+            if (c < best) {
+                best = c;
+                best_rows = a * 2 * G_BM;
+            }
+        }
+        if (best_rows > 0 && best < 0.97f * whole) {
+            GemmParams pa = p, pb = p;
+            pa.M = best_rows;
+            pb.M = p.M - best_rows;
+            const size_t off = (size_t)best_rows * p.ld_out;
+            if (pb.h) pb.h += off;
+            if (pb.out_bf) pb.out_bf += off;
+            if (pb.out_f32) pb.out_f32 += off;
+            int rc = dense_gemm_one(A, lda, W, pa, stream, 3);
+            if (rc) return rc;
+            return dense_gemm_one(static_cast<const __nv_bfloat16 *>(A) + (size_t)best_rows * lda, lda, W, pb, stream, 0);
+        }
+    }
+    return dense_gemm_one(A, lda, W, p, stream, 0);
+}
+
+static int dense_gemm_one(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream, int forced_variant) {
     if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
     if (p.N % 8 || (p.epi == EPI_GATED && p.N % 16) || p.K % 8 || lda % 8 || p.ld_out % 8) return VLAB200_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VLAB200_ERR_ARG;
@@ -442,24 +509,10 @@ int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t
     }
     const int n_sm = sm_count();
     if (n_sm <= 0) return cuda_fail(cudaGetLastError(), "sm_count");
-    // Four tilings: one CTA per 128 x 256 tile, per 128 x 128 or 128 x 64 tile (more CTAs streaming the
-    // weights when the problem has few rows), a CTA pair per 256 x 256 tile (half the shared-memory traffic
-    // per flop).  Costs
-    // in units of one 128 x 256 tile on one SM; the per-tile factors are measured ratios.
+    int variant = forced_variant > 0 ? forced_variant : dense_gemm_variant();
+    if (variant == 0) tiling_cost(p.M, p.N, n_sm, &variant);
     const int tiles_m = (p.M + G_BM - 1) / G_BM, tiles_mp = (p.M + 2 * G_BM - 1) / (2 * G_BM);
-    const int tn256 = (p.N + 255) / 256, tn128 = (p.N + 127) / 128, pairs = n_sm / 2;
-    auto waves = [](int tiles, int units) { return (tiles + units - 1) / units; };
-    const float cost256 = (float)waves(tiles_m * tn256, n_sm);
-    const float cost128 = p.N > 128 ? 0.60f * waves(tiles_m * tn128, n_sm) : 1e30f;
-    const int tn64 = (p.N + 63) / 64;
-    const float cost64 = p.N > 64 ? 0.33f * waves(tiles_m * tn64, n_sm) : 1e30f;  // few rows: as many CTAs as possible stream W
-    const float cost_pair = pairs > 0 ? kPairTileFactor * waves(tiles_mp * tn256, pairs) : 1e30f;
-    int variant = dense_gemm_variant();
-    if (variant == 0) {
-        variant = (cost_pair <= cost256 && cost_pair <= cost128) ? 3 : (cost128 < cost256 ? 2 : 1);
-        const float best = variant == 3 ? cost_pair : (variant == 2 ? cost128 : cost256);
-        if (cost64 < best) variant = 4;
-    }
+    const int tn256 = (p.N + 255) / 256, tn128 = (p.N + 127) / 128, tn64 = (p.N + 63) / 64, pairs = n_sm / 2;
     if (variant == 2 && p.N <= 128) variant = 1;
     if (variant == 4 && p.N <= 64) variant = 1;
     const uint64_t wdims[2] = {(uint64_t)p.K, (uint64_t)p.N};
