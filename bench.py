@@ -1141,7 +1141,7 @@ def predict_launches(d, arch):
     tower = 3 + 8 * d["vit_layers"] + 2 + (0 if arch == "smolvla" else 1)
     embed = 3 if arch == "smolvla" else 2
     prefill = 2 + 2 * L + 4 * (L - 1) + 4 * cross
-    denoise = d["num_steps"] * (4 + L * 6 + 2) + 3
+    denoise = d["num_steps"] * ((3 if arch == "smolvla" else 4) + L * 6 + 2) + 2  # pi0: + the state-token kernel; 2 RoPE tables
     return tower + embed + prefill + denoise
 
 
