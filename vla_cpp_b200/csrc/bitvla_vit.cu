@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(256) vit_ln_quant_kernel(__nv_bfloat16 *__rest
 
 // qkv [seq][3 H] (q | k | v) + bias -> q [heads][seq][hd_pad], K / V pages [heads][seq][hd_pad], zero past hd.
 // (bitvla_add_bias_bf16 + bitvla_transpose_sNhd_to_NshHd_bf16, bitvla_vit_cuda.cu:185-195)
-__global__ void __launch_bounds__(128) vit_split_heads_kernel(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restrict__ bq,
+// One CTA per token; a thread moves 8 consecutive head-dim elements (16 bytes) at a time when hd % 8 == 0.
+__global__ void __launch_bounds__(256) vit_split_heads_kernel(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restrict__ bq,
                                                               const __nv_bfloat16 *__restrict__ bk, const __nv_bfloat16 *__restrict__ bv,
                                                               __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__restrict__ kp,
                                                               __nv_bfloat16 *__restrict__ vp, int seq, int heads, int hd, int hd_pad) {
@@ -124,6 +125,31 @@ __global__ void __launch_bounds__(128) vit_split_heads_kernel(const __nv_bfloat1
     pdl_wait();
     const int t = blockIdx.x, H = heads * hd;
     const __nv_bfloat16 *src = qkv + (size_t)t * 3 * H;
+    const bool al16 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(bq) | reinterpret_cast<uintptr_t>(bk) |
+                        reinterpret_cast<uintptr_t>(bv)) & 15) == 0;
+    if ((hd & 7) == 0 && al16) {
+        const int cpr = hd_pad >> 3;  // 16-byte chunks per padded head row
+        for (int i = threadIdx.x; i < 3 * heads * cpr; i += blockDim.x) {
+            const int which = i / (heads * cpr), r = i % (heads * cpr), hh = r / cpr, d = (r % cpr) * 8;
+            uint4 out = make_uint4(0u, 0u, 0u, 0u);
+            if (d < hd) {
+                const __nv_bfloat16 *b = which == 0 ? bq : (which == 1 ? bk : bv);
+                const uint4 xv = *reinterpret_cast<const uint4 *>(src + which * H + hh * hd + d);
+                const uint4 bvv = *reinterpret_cast<const uint4 *>(b + hh * hd + d);
+                const __nv_bfloat162 *x2 = reinterpret_cast<const __nv_bfloat162 *>(&xv);
+                const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&bvv);
+                __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&out);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 xf = __bfloat1622float2(x2[e]), bf = __bfloat1622float2(b2[e]);
+                    o2[e] = __floats2bfloat162_rn(xf.x + bf.x, xf.y + bf.y);
+                }
+            }
+            __nv_bfloat16 *dst = which == 0 ? q : (which == 1 ? kp : vp);
+            *reinterpret_cast<uint4 *>(dst + ((size_t)hh * seq + t) * hd_pad + d) = out;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < 3 * heads * hd_pad; i += blockDim.x) {
         const int which = i / (heads * hd_pad), r = i % (heads * hd_pad), hh = r / hd_pad, d = r % hd_pad;
         __nv_bfloat16 val = __float2bfloat16(0.0f);
@@ -168,8 +194,11 @@ __global__ void __launch_bounds__(256) vit_gelu_quant_kernel(const __nv_bfloat16
         float y = 0.f;
         if (k < F) {
             const float v = __bfloat162float(__float2bfloat16(__bfloat162float(x[(size_t)m * F + k]) + __bfloat162float(bias[k])));
+            // tanh.approx: what the reference's tanhf becomes under its --use_fast_math build
             const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            y = __bfloat162float(__float2bfloat16(0.5f * v * (1.0f + tanhf(u))));
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+            y = __bfloat162float(__float2bfloat16(0.5f * v * (1.0f + th)));
         }
         row[k] = y;
         amax = fmaxf(amax, fabsf(y));
@@ -365,7 +394,7 @@ int bitvla_vit_cuda_forward(bitvla_vit_cuda_ctx *ctx, const void *d_patches, voi
             return fail("ln1", rc);
         if ((rc = vlab200_ternary_linear(a8, lr.qkv_packed.as<uint8_t>(), ctx->qkv.p, nullptr, s, lr.qkv_ws.as<float>(), 3, S, 3 * H, H, 0, cs)))
             return fail("qkv projection", rc);
-        if ((rc = vb::launch_pdl(vb::vit_split_heads_kernel, dim3(S), dim3(128), 0, cs, ctx->qkv.as<__nv_bfloat16>(), bf(w.q_b), bf(w.k_b),
+        if ((rc = vb::launch_pdl(vb::vit_split_heads_kernel, dim3(S), dim3(256), 0, cs, ctx->qkv.as<__nv_bfloat16>(), bf(w.q_b), bf(w.k_b),
                                  bf(w.v_b), ctx->q.as<__nv_bfloat16>(), ctx->kp.as<__nv_bfloat16>(), ctx->vp.as<__nv_bfloat16>(), S, heads, hd, hp)))
             return fail("head split", rc);
         vlab200_kv_store view{ctx->kp.p, ctx->vp.p, 1, 1, heads, hp, S, 0};
