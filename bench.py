@@ -206,7 +206,9 @@ PI0_P = 816
 SMOLVLA = dict(model=1, n_layers=16, H=720, n_q=15, n_kv=5, head_dim=64, inter=2048, chunk=50, action_dim=32,
                state_dim=32, steps=10, self_every=2, rms_eps=1e-5, rope_base=10000.0, min_period=4e-3, max_period=4.0)
 SMOLVLA_P = 177
-POLICIES = {"pi0": (PI0, PI0_P), "smolvla": (SMOLVLA, SMOLVLA_P)}
+# pi0.5-shaped expert (src/models/pi05.cpp): pi0's sizes, adaptive RMSNorm, no state token
+PI05 = dict(PI0, model=2, state_dim=0, cond_dim=1024)
+POLICIES = {"pi0": (PI0, PI0_P), "smolvla": (SMOLVLA, SMOLVLA_P), "pi05": (PI05, PI0_P)}
 
 
 def policy_flops_per_chunk(c, P):
@@ -248,6 +250,12 @@ def build_pi0_engine(torch, vb, dev, n_obs, seed, policy="pi0"):
              ln_post=[torch.ones(H, device=dev) for _ in range(L)], w_sp=bw(H, sd), b_sp=fv(H), w_ain=bw(H, A),
              b_ain=fv(H), w_at1=bw(H, 2 * H), b_at1=fv(H), w_at2=bw(H, H), b_at2=fv(H),
              out_norm=torch.ones(H, device=dev), w_aout=bw(A, H), b_aout=fv(A))
+    if c["model"] == 2:
+        fw = lambda *s: torch.randn(s, device=dev, generator=g) * 0.02
+        gate_one = lambda: torch.cat([torch.zeros(2 * H, device=dev), torch.ones(H, device=dev)])  # scale 0, shift 0, gate 1
+        w.update(ada_in_w=[fw(3 * H, H) for _ in range(L)], ada_in_b=[gate_one() for _ in range(L)],
+                 ada_post_w=[fw(3 * H, H) for _ in range(L)], ada_post_b=[gate_one() for _ in range(L)],
+                 ada_final_w=fw(3 * H, H), ada_final_b=gate_one(), w_tin=fw(H, H), b_tin=fv(H), w_tout=fw(H, H), b_tout=fv(H))
     eng = vb.PolicyEngine(c, w, max_obs=n_obs, prefix_len=PI0_P)
     del w
     blk = 64
@@ -257,7 +265,7 @@ def build_pi0_engine(torch, vb, dev, n_obs, seed, policy="pi0"):
             eng.set_prefix(l, torch.randn((n, PI0_P, c["n_kv"], c["head_dim"]), device=dev, generator=g),
                            torch.randn((n, PI0_P, c["n_kv"], c["head_dim"]), device=dev, generator=g), obs0=o)
     x0 = torch.randn((n_obs, 50, 32), device=dev, generator=g)
-    state = torch.randn((n_obs, 32), device=dev, generator=g)
+    state = torch.randn((n_obs, 32), device=dev, generator=g) if c["model"] != 2 else None
     torch.cuda.synchronize()
     return eng, x0, state
 
@@ -279,7 +287,7 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_
         ev[i + 1].record()
     sync()
     step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
-    x0h, sth = x0.cpu().pin_memory(), state.cpu().pin_memory()
+    x0h, sth = x0.cpu().pin_memory(), (state.cpu().pin_memory() if state is not None else None)
     outh = torch.empty_like(x0h).pin_memory()
     eng.denoise_host(x0h, sth, outh)
     sync()
@@ -317,7 +325,8 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_
     if vb.device_status() != 0:
         raise SystemExit("device status word reports a kernel failure")
     return {"total_ms": ev[0].elapsed_time(ev[-1]), "p50_ms": statistics.median(step_ms),
-            "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + sth.numel() * 4, "d2h": outh.numel() * 4,
+            "e2e_ms": e0.elapsed_time(e1) / n_e2e, "h2d": x0h.numel() * 4 + (sth.numel() * 4 if sth is not None else 0),
+            "d2h": outh.numel() * 4,
             "graph_ms": graph_ms}
 
 
@@ -765,7 +774,9 @@ def policy_config_dict(workload, n_obs, n_global, world):
                    "1024 observations split over the GPUs",
             "smolvla": "smolvla_loop: whole SmolVLA-shaped denoise loop (the action expert of BASELINE configs[0]): 16 "
                        "layers alternating self / cross attention, hidden 720, 15q/5kv, hd 64, MLP 2048, prefix 177, "
-                       "chunk 50x32, 10 Euler steps"}[workload]
+                       "chunk 50x32, 10 Euler steps",
+            "pi05": "pi05_loop: whole pi0.5-shaped denoise loop: pi0's expert sizes with adaptive RMSNorm on the time step, "
+                    "gated residuals, no state token, no mask among the 50 action tokens; prefix 816, 10 Euler steps"}[workload]
     return {"workload": text, "batch_per_gpu": n_obs, "global_batch": n_global, "parallelism": f"replica x{world}",
             "l2": "inputs larger than L2 (KV pages + expert weights + activations > 126 MB per GPU)"}
 
@@ -796,6 +807,11 @@ def run_reference(args, rank, world):
         times = [sum(oracle_predict_seconds(orc, d, arch, n_views)) for _ in range(max(args.steps, 1))]
         config = {"workload": f"{arch}_predict: one whole request (vision tower per view, backbone prefill, denoise loop), batch 1"}
         sample = "1 whole request per step with float32 weights and activations"
+    elif args.workload == "pi05":
+        workload = "pi05"
+        times = oracle_pi05_seconds(orc, *POLICIES["pi05"], n=args.steps)
+        config = policy_config_dict(workload, 1, 1, 1)
+        sample = "1 observation (chunk) per step through the whole loop (all layers, 10 Euler steps), float32"
     else:
         workload = args.workload if args.workload in POLICIES else "pi0"
         loop = OraclePolicyLoop(orc, workload, seed=1)
@@ -891,7 +907,7 @@ def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
     step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     total_ms = ev[0].elapsed_time(ev[-1])
     # ---- end to end: state / noise in pinned host memory, actions read back, every step -----------------
-    x0h, sth = x0.cpu().pin_memory(), state.cpu().pin_memory()
+    x0h, sth = x0.cpu().pin_memory(), (state.cpu().pin_memory() if state is not None else None)
     outh = torch.empty_like(x0h).pin_memory()
     eng.denoise_host(x0h, sth, outh)
     barrier()
@@ -1084,6 +1100,36 @@ def measure_smolvla_attn(torch, vb, dist, dev, args, rank, world, barrier, with_
     return line
 
 
+def measure_pi05_loop(torch, vb, dev, args):
+    """The pi0.5-shaped loop on one GPU: device-resident and host-buffer timings of the whole loop (no per-stage hook:
+    its layer has seven stages of its own)."""
+    c, P = POLICIES["pi05"]
+    n_obs = args.pi0_obs if args.pi0_obs > 0 else 1024
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    r = measure_pi0(torch, vb, dev, n_obs, args.steps, max(args.warmup, 3), 99, policy="pi05", on_begin=sampler.mark_begin)
+    clocks = sampler.stop()
+    peaks = load_peaks()
+    per_step_ms = r["total_ms"] / args.steps
+    tf = policy_flops_per_chunk(c, P) * n_obs / (per_step_ms * 1e-3) / 1e12
+    line = {"metric": "action chunks/s (denoise loop)", "value": n_obs / (per_step_ms * 1e-3), "unit": "chunks/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "p50_chunk_latency_ms": r["p50_ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": policy_config_dict("pi05", n_obs, n_obs, 1), "clocks": clocks,
+            # per Euler step: embedding, 7 kernels per layer (+1 where a GEMM is cut along M), norm + head + Euler
+            "gpu_launches": (c["steps"] * (1 + c["n_layers"] * 7 + 3) + 3) * args.steps,
+            "e2e": {"value": n_obs / (r["e2e_ms"] * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": r["h2d"],
+                    "d2h_bytes_per_step": r["d2h"]},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops_sustained"], "traffic": None,
+                         "note": "whole loop (expert GEMMs + attention, algorithmic FLOPs) over its device time", "peak_source": peaks["kind"]}}
+    if n_obs > 1:
+        b1 = measure_pi0(torch, vb, dev, 1, 10, 3, 8, allow_graph=True, policy="pi05")
+        line["p50_chunk_latency_ms_batch1"] = b1["p50_ms"]
+        line["graph_ms_batch1"] = b1["graph_ms"]
+    return line
+
+
 def predict_inputs(d, arch):
     """The request of BASELINE configs[0] (SmolVLA: 2 views, 48 token ids) / configs[2] (pi0: 3 views, 48 token ids),
     seeds 0..3 for the images, the tokens, the state and the noise."""
@@ -1094,6 +1140,32 @@ def predict_inputs(d, arch):
     state = np.random.default_rng(2).standard_normal(d["max_state_dim"]).astype(np.float32)
     noise = np.random.default_rng(3).standard_normal((d["chunk_size"], d["max_action_dim"])).astype(np.float32)
     return images, lang, state, noise
+
+
+def oracle_pi05_seconds(orc, c, P, n=1):
+    """Seconds per observation of the CPU restatement of the pi0.5-shaped loop (random weights of the expert's shapes)."""
+    rng = np.random.default_rng(9)
+    H, I, hd, L = c["H"], c["inter"], c["head_dim"], c["n_layers"]
+    qf, kvf = c["n_q"] * hd, c["n_kv"] * hd
+    w = lambda *shape: orc.bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+    z = lambda k: np.zeros(k, np.float32)
+    gate_one = lambda: np.concatenate([z(2 * H), np.ones(H, np.float32)])
+    layers = [dict(wq=w(qf, H), wk=w(kvf, H), wv=w(kvf, H), wo=w(H, qf), wgate=w(I, H), wup=w(I, H), wdown=w(H, I),
+                   ada_in_w=w(3 * H, H), ada_in_b=gate_one(), ada_post_w=w(3 * H, H), ada_post_b=gate_one()) for _ in range(L)]
+    ww = dict(layers=layers, w_ain=w(H, 32), b_ain=z(H), w_tin=w(H, H), b_tin=z(H), w_tout=w(H, H), b_tout=z(H),
+              ada_final_w=w(3 * H, H), ada_final_b=gate_one(), w_aout=w(32, H), b_aout=z(32))
+    cfg = dict(H=H, n_q=c["n_q"], n_kv=c["n_kv"], hd=hd, steps=c["steps"], rms_eps=c["rms_eps"], rope_base=c["rope_base"],
+               min_period=c["min_period"], max_period=c["max_period"])
+    kp = [rng.standard_normal((P, c["n_kv"], hd), dtype=np.float32) for _ in range(L)]
+    vp = [rng.standard_normal((P, c["n_kv"], hd), dtype=np.float32) for _ in range(L)]
+    times = []
+    for _ in range(n):
+        x0 = rng.standard_normal((c["chunk"], 32), dtype=np.float32)
+        t0 = time.perf_counter()
+        out = orc.pi05_denoise(kp, vp, x0, ww, cfg)
+        times.append(time.perf_counter() - t0)
+        assert np.isfinite(out).all()
+    return times
 
 
 def oracle_predict_seconds(orc, d, arch, n_views):
@@ -1127,7 +1199,10 @@ def oracle_predict_seconds(orc, d, arch, n_views):
     t0 = time.perf_counter()
     orc.vlm_prefill(x, layers, ocfg)
     t_prefill = time.perf_counter() - t0
-    t_denoise = OraclePolicyLoop(orc, arch, seed=7).run(1)[0]
+    if arch == "pi05":
+        t_denoise = oracle_pi05_seconds(orc, POLICIES["pi05"][0], n_prefix)[0]
+    else:
+        t_denoise = OraclePolicyLoop(orc, arch, seed=7).run(1)[0]
     return t_tower, t_prefill, t_denoise
 
 
@@ -1157,7 +1232,7 @@ def measure_predict(torch, vb, dev, args, arch):
     try:
         path = os.path.join(tmp, arch + "_random.gguf")
         t0 = time.perf_counter()
-        dims = {} if arch == "smolvla" else {"vocab_size": 32768}  # pi0: a 32k-row embedding table bounds the file size
+        dims = {} if arch == "smolvla" else {"vocab_size": 32768}  # pi0 / pi0.5: a 32k-row embedding table bounds the file size
         d = synth_gguf.write_checkpoint(path, arch, dims=dims, seed=0, matrix_dtype="f32" if arch == "smolvla" else "bf16")
         t_write = time.perf_counter() - t0
         t0 = time.perf_counter()
@@ -1200,7 +1275,7 @@ def measure_predict(torch, vb, dev, args, arch):
         "value": 1e3 / dev_ms, "unit": "chunks/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (random-init checkpoint in the reference's GGUF naming, seeded request)",
-        "config": {"workload": f"{arch}_predict: BASELINE configs[{0 if arch == 'smolvla' else 2}] through vla_predict, batch 1, "
+        "config": {"workload": f"{arch}_predict: {'BASELINE configs[0]' if arch == 'smolvla' else 'shapes of BASELINE configs[2]'} through vla_predict, batch 1, "
                                f"{len(images)} uint8 views of {d['image_size']}x{d['image_size']}, {lang.size} token ids, "
                                f"{d['num_steps']} Euler steps", "l2": "weights (> L2) re-read every request"},
         "phases_ms": {"vision": ms_v, "prefill": ms_p, "denoise": ms_d, "wall_p50": wall_ms, "wall_min": min(wall),
@@ -1246,7 +1321,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="observations per GPU (smolvla_attn workload)")
-    ap.add_argument("--workload", default="pi0", choices=["pi0", "smolvla", "smolvla_attn", "ternary", "bitvla_lm", "smolvla_predict", "pi0_predict"],
+    ap.add_argument("--workload", default="pi0", choices=["pi0", "smolvla", "pi05", "smolvla_attn", "ternary", "bitvla_lm", "smolvla_predict", "pi0_predict",
+                             "pi05_predict"],
                     help="pi0 (default): the whole pi0-shaped denoise loop, 1024 observations split over the GPUs "
                          "(BASELINE configs[4]); smolvla: the SmolVLA-shaped loop; smolvla_attn: the isolated "
                          "denoise-attention op (configs[1]); ternary / bitvla_lm: configs[3]")
@@ -1310,6 +1386,18 @@ def main():
             line = measure_bitvla_lm(torch, vb, dev, args.steps, max(args.warmup, 3))
             line["vision_tower"] = measure_bitvla_vit(torch, vb, dev)
             line["fp32_head"] = measure_bitvla_head(vb)
+        finish(line)
+        return
+    if args.workload == "pi05":
+        line = None
+        if rank == 0:
+            line = measure_pi05_loop(torch, vb, dev, args)
+            if not args.no_cpu_baseline:
+                from oracle import oracle_ffi as orc
+
+                ts = oracle_pi05_seconds(orc, *POLICIES["pi05"], n=2)
+                line["cpu_baseline"] = {"value": len(ts) / sum(ts), "unit": "chunks/s", "cores": orc.num_threads(), "kind": "port",
+                                        "sample": "2 observations of the same loop"}
         finish(line)
         return
     if args.workload.endswith("_predict"):

@@ -83,7 +83,7 @@ TINY = dict(hidden=64, intermediate=128, n_q_heads=2, n_kv_heads=1, head_dim=64,
             image_size=32, patch_size=16, vit_pixel_shuffle=1)
 
 
-@pytest.mark.parametrize("arch", ["pi0", "smolvla"])
+@pytest.mark.parametrize("arch", ["pi0", "smolvla", "pi05"])
 def test_the_random_init_writer_uses_the_converters_names(tmp_path, arch):
     """vla_cpp_b200.synth_gguf writes only metadata keys and tensor names that the reference's converters write, and
     the file resolves through vla_model_load / vla_model_config.  Host only."""
@@ -92,14 +92,14 @@ def test_the_random_init_writer_uses_the_converters_names(tmp_path, arch):
 
     path = tmp_path / (arch + "_tiny.gguf")
     dims = dict(TINY)
-    if arch == "pi0":
-        dims.update(image_size=224, patch_size=14)  # pi0 fixes 256 image tokens per view (src/models/pi0.cpp:286)
+    if arch != "smolvla":
+        dims.update(image_size=224, patch_size=14)  # pi0 / pi0.5 fix 256 image tokens per view (src/models/pi0.cpp:286)
     d = synth_gguf.write_checkpoint(path, arch, dims=dims)
     g = GOLDEN[arch]
     kv_names = {k for k, _ in g["kv"]}
     block = {n.split(".", 3)[3] for n, _, _ in g["decoder_blocks"]}
     vision = {n.replace("vit.blk.0.", "") for n, _, _ in GOLDEN["vision"]["tower"]}
-    conn = set(GOLDEN["vision"]["connector_" + arch])
+    conn = set(GOLDEN["vision"]["connector_" + ("smolvla" if arch == "smolvla" else "pi0")])
     r = gguf.GGUFReader(str(path))
     for k in r.fields:
         if k.startswith(arch + "."):
@@ -117,8 +117,9 @@ def test_the_random_init_writer_uses_the_converters_names(tmp_path, arch):
         elif n in g["projections"]:
             pass
         else:
-            assert n in ("token_embd.weight", "vlm.output_norm.weight", g["output_norm"], "state_mean", "state_std",
-                         "action_mean", "action_std"), n
+            out_norm = g["output_norm"] if isinstance(g["output_norm"], list) else [g["output_norm"]]
+            assert n in ["token_embd.weight", "vlm.output_norm.weight", "state_mean", "state_std", "action_mean", "action_std",
+                         "action_q01", "action_q99"] + out_norm, n
     L = vla_cpp_b200.lib()
     L.vla_model_load.restype = C.c_void_p
     L.vla_model_load.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p]

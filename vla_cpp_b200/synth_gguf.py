@@ -44,7 +44,7 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
     and held as bf16 on the device)."""
     import gguf
 
-    assert arch in ("smolvla", "pi0") and matrix_dtype in ("f32", "bf16")
+    assert arch in ("smolvla", "pi0", "pi05") and matrix_dtype in ("f32", "bf16")  # pi05: pi0's sizes
     d = dict(SMOLVLA_DIMS if arch == "smolvla" else PI0_DIMS)
     d.update(dims or {})
     rng = np.random.default_rng(seed)
@@ -70,6 +70,10 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
     else:
         w.add_float64(kv("rope_theta"), d["rope_theta"])
         w.add_float32(kv("rms_norm_eps"), d["rms_norm_eps"])
+    if arch == "pi05":  # scripts/gguf_blocks.py write_pi_kv(adarms=True)
+        w.add_bool(kv("use_adarms_expert"), True)
+        w.add_uint32(kv("adarms_cond_dim"), int(d["expert_h"]))
+        w.add_string(kv("norm_mode"), "quantiles")
 
     def bf16(name, shape):
         a = rng.standard_normal(shape, dtype=np.float32) * np.float32(sigma)
@@ -85,13 +89,27 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
         a = np.full(n, value, np.float32) if value is not None else rng.standard_normal(n, dtype=np.float32) * np.float32(sigma)
         w.add_tensor(name, a, raw_dtype=F32)
 
-    norm_one = 0.0 if arch == "pi0" else 1.0  # Gemma norms are stored without their +1
+    norm_one = 1.0 if arch == "smolvla" else 0.0  # Gemma norms are stored without their +1
     H, I, hd = d["hidden"], d["intermediate"], d["head_dim"]
     qf, kvf = d["n_q_heads"] * hd, d["n_kv_heads"] * hd
     E, EI = d["expert_h"], d["expert_inter"]
     bf16("token_embd.weight", (d["vocab_size"], H))
 
-    def decoder_block(prefix, width, inter, k_in):
+    def ada_norm(name, width):
+        # pi0.5: the norm is a dense map of the time conditioning, rows scale | shift | gate; biases give gate 1
+        w.add_tensor(name + ".weight", rng.standard_normal((3 * width, width), dtype=np.float32) * np.float32(sigma), raw_dtype=F32)
+        w.add_tensor(name + ".bias", np.concatenate([np.zeros(2 * width, np.float32), np.ones(width, np.float32)]), raw_dtype=F32)
+
+    def decoder_block(prefix, width, inter, k_in, ada=False):
+        if ada:
+            ada_norm(prefix + "attn_norm", width)
+            for q, rows, cols in (("attn_q", qf, width), ("attn_k", kvf, k_in), ("attn_v", kvf, k_in), ("attn_o", width, qf)):
+                mat(prefix + q + ".weight", rows, cols)
+            ada_norm(prefix + "ffn_norm", width)
+            mat(prefix + "ffn_gate.weight", inter, width)
+            mat(prefix + "ffn_up.weight", inter, width)
+            mat(prefix + "ffn_down.weight", width, inter)
+            return
         vec(prefix + "attn_norm.weight", width, norm_one)
         mat(prefix + "attn_q.weight", qf, width)
         mat(prefix + "attn_k.weight", kvf, k_in)
@@ -106,12 +124,17 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
     for i in range(d["n_layers"]):
         decoder_block(f"vlm.blk.{i}.", H, I, H)
         cross = every > 1 and i % every != 0  # cross-attention layers project the prefix K/V: [kvf, kvf]
-        decoder_block(f"aex.blk.{i}.", E, EI, kvf if cross else E)
+        decoder_block(f"aex.blk.{i}.", E, EI, kvf if cross else E, ada=arch == "pi05")
     vec("vlm.output_norm.weight", H, norm_one)
-    vec("aex.output_norm.weight", E, norm_one)
     sd, ad = d["max_state_dim"], d["max_action_dim"]
-    for name, out, inp in (("state_proj", H if arch == "smolvla" else E, sd), ("action_in_proj", E, ad),
-                           ("action_time_mlp_in", E, 2 * E), ("action_time_mlp_out", E, E), ("action_out_proj", ad, E)):
+    if arch == "pi05":
+        ada_norm("aex.output_norm", E)
+        heads = (("action_in_proj", E, ad), ("time_mlp_in", E, E), ("time_mlp_out", E, E), ("action_out_proj", ad, E))
+    else:
+        vec("aex.output_norm.weight", E, norm_one)
+        heads = (("state_proj", H if arch == "smolvla" else E, sd), ("action_in_proj", E, ad),
+                 ("action_time_mlp_in", E, 2 * E), ("action_time_mlp_out", E, E), ("action_out_proj", ad, E))
+    for name, out, inp in heads:
         # the projection heads stay float32 in the reference
         w.add_tensor(name + ".weight", rng.standard_normal((out, inp), dtype=np.float32) * np.float32(sigma), raw_dtype=F32)
         vec(name + ".bias", out)
@@ -144,6 +167,9 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
     vec("state_std", d["real_state_dim"], 1.0)
     vec("action_mean", d["real_action_dim"], 0.0)
     vec("action_std", d["real_action_dim"], 1.0)
+    if arch == "pi05":
+        vec("action_q01", d["real_action_dim"], -1.0)
+        vec("action_q99", d["real_action_dim"], 1.0)
     w.write_header_to_file()
     w.write_kv_data_to_file()
     w.write_tensors_to_file()
@@ -154,5 +180,5 @@ def write_checkpoint(path, arch, dims=None, seed=0, sigma=0.02, matrix_dtype="f3
 
 if __name__ == "__main__":
     if len(sys.argv) < 3:
-        raise SystemExit("usage: python -m vla_cpp_b200.synth_gguf <smolvla|pi0> <out.gguf> [f32|bf16]")
+        raise SystemExit("usage: python -m vla_cpp_b200.synth_gguf <smolvla|pi0|pi05> <out.gguf> [f32|bf16]")
     print(write_checkpoint(sys.argv[2], sys.argv[1], matrix_dtype=sys.argv[3] if len(sys.argv) > 3 else "f32"))
