@@ -102,7 +102,8 @@ VLAB200_API int32_t vlab200_fold_norm_weight(const void *w_bf16, const float *ln
  * ordered q heads, k heads, v heads.  project_kv == 0 projects q only (SmolVLA cross-attention
  * layers, src/models/smolvla.cpp:870-873; Wqkv then holds the q rows only).  H % 8 == 0.
  * ln_w == NULL means Wqkv was already multiplied by ln_w (vlab200_fold_norm_weight); with bf16 x
- * this selects the fastest kernel (both operands by TMA, persistent CTAs).
+ * this selects the fastest kernel (both operands by TMA, persistent CTAs).  eps < 0: x is taken as already
+ * normalised (no RMS factor; the pi0.5 expert normalises adaptively before the projection, src/models/pi05.cpp:237-241).
  * Replaces the rms_norm/mul, three mul_mat, two rope and two concat nodes of
  * src/models/pi0.cpp:170-201 and src/models/smolvla.cpp:820-833. */
 VLAB200_API int32_t vlab200_qkv_rope_append(const vlab200_kv_store *st, int32_t layer, const void *x,

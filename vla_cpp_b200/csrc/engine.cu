@@ -420,11 +420,16 @@ static int ada_layer(vlab200_engine *e, int l, int step, int n_obs, const float 
     if ((rc = launch_pdl(adarms_norm_kernel, dim3((M + 7) / 8), dim3(256), 0, cs, static_cast<const float *>(h), mod_in, hb, M, H, c.rms_eps)))
         return rc;
     GemmParams p{};
-    p.M = M; p.N = qkv_n; p.K = H; p.epi = EPI_BIAS_ACT; p.act = ACT_NONE; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
-    if ((rc = dense_gemm(hb, H, e->wqkv[l].p, p, cs))) return rc;
-    if ((rc = rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S, c.n_q, c.n_kv, c.n_kv, hd,
-                         e->cap, e->P, cs)))
+    if (M <= kFewRows) {  // few rows: narrow-tile GEMM, then rotation / split / append (as in layer_stage)
+        p.M = M; p.N = qkv_n; p.K = H; p.epi = EPI_BIAS_ACT; p.act = ACT_NONE; p.out_bf = e->g.as<__nv_bfloat16>(); p.ld_out = qkv_n;
+        if ((rc = dense_gemm(hb, H, e->wqkv[l].p, p, cs))) return rc;
+        if ((rc = rope_split(e->g.p, rope, rope + (size_t)S * half, e->q.p, live.k_pages, live.v_pages, M, S, c.n_q, c.n_kv, c.n_kv,
+                             hd, e->cap, e->P, cs)))
+            return rc;
+    } else if ((rc = vlab200_qkv_rope_append(&live, 0, hb, 0, nullptr, e->wqkv[l].p, rope, rope + (size_t)S * half, -1.0f, S, H, c.n_q,
+                                             1, e->q.p, cs))) {  // the fused kernel without its RMS factor
         return rc;
+    }
     // no mask: every action token sees the prefix and every action token (soft_max_ext without a mask, pi05.cpp:264)
     if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, e->P + S, 0, nullptr, cs))) return rc;
     p = GemmParams{};

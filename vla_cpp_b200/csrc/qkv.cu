@@ -180,7 +180,7 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap w_map, const QkvParams p) {
         // (tcgen05.ld is warp-collective: every lane runs the loads, only stores are predicated)
         if (mbar_wait(accum_bar, 0, wc, DEV_TIMEOUT_ACCUM)) {
             tc_fence_after();
-            const float rms = rsqrtf(sumsq / (float)p.H + p.eps);
+            const float rms = p.eps < 0.0f ? 1.0f : rsqrtf(sumsq / (float)p.H + p.eps);  // eps < 0: x is already normalised
             const int obs = m / p.S, tok = m % p.S;
             const int hd = p.hd, half = hd >> 1;
             const int n_total = (p.n_q + 2 * p.n_kv_proj) * hd;
@@ -469,7 +469,7 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
             if (ok) ok = mbar_wait(&stats_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
             if (!ok) break;
             tc_fence_after();
-            const float rms = rsqrtf(stats[buf * 128 + row] / (float)p.H + p.eps);
+            const float rms = p.eps < 0.0f ? 1.0f : rsqrtf(stats[buf * 128 + row] / (float)p.H + p.eps);
             const float *cs = rope_s + tok, *sn = rope_s + (size_t)half * p.S + tok;
             const uint32_t lane_addr = tmem_base + buf * QKV_BN + ((uint32_t)(qtr * 32) << 16);
             // heads of the tile alternate between the two groups; a single wide head is split by columns
