@@ -59,11 +59,13 @@ __device__ __forceinline__ float act_apply(float x, int act) {
         const float u = k0 * x * (1.0f + k1 * x * x);
         return __fdividef(x, 1.0f + __expf(-2.0f * u));
     }
-    if (act == ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
     return x;
 }
 
-template <int G_BN, bool PAIR>
+// SPLIT: the K loop of every output tile is cut into p.ksplit slices that run as separate work items; a slice stores its
+// float accumulator to p.partial[slice][m][n] and splitk_reduce_kernel adds the slices in a fixed order (few rows and a
+// narrow N would otherwise leave most SMs without work while a handful stream all of K).
+template <int G_BN, bool PAIR, bool SPLIT = false>
 __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const CUtensorMap &w_map, const GemmParams &p,
                                                 int tiles_m, int tiles_n) {
     using Cfg = GemmCfg<G_BN, PAIR>;
@@ -87,7 +89,8 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ksteps = (p.K + G_BK - 1) / G_BK;
-    const int n_tiles = tiles_m * tiles_n;
+    const int ks_n = SPLIT ? p.ksplit : 1;
+    const int n_tiles = tiles_m * tiles_n * ks_n;
     const int t_begin = (int)((long long)n_tiles * unit / n_units), t_end = (int)((long long)n_tiles * (unit + 1) / n_units);
     const WaitCtx wc{abort_flag, p.status};
     const uint32_t empty_count = p.use_rms ? 5u : 1u;
@@ -134,9 +137,11 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
             uint32_t st = 0, ph = 0;
             bool ok = true;
             for (int tile = t_begin; ok && tile < t_end; ++tile) {
-                const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM;
-                const int n0 = (tile % tiles_n) * G_BN + (int)rank * Cfg::B_ROWS * (PAIR ? 1 : 0);
-                for (int kt = 0; kt < ksteps; ++kt) {
+                const int sp = SPLIT ? tile / ks_n : tile, ks = SPLIT ? tile % ks_n : 0;
+                const int kbeg = SPLIT ? ks * ksteps / ks_n : 0, kend = SPLIT ? (ks + 1) * ksteps / ks_n : ksteps;
+                const int m0 = (sp / tiles_n) * TILE_M + (int)rank * G_BM;
+                const int n0 = (sp % tiles_n) * G_BN + (int)rank * Cfg::B_ROWS * (PAIR ? 1 : 0);
+                for (int kt = kbeg; kt < kend; ++kt) {
                     ok = mbar_wait(&empty[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_expect_tx(&full[st], G_STAGE_BYTES);
@@ -161,15 +166,18 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * G_BN;
-                for (int kt = 0; kt < ksteps; ++kt) {
+                const int ks = SPLIT ? tile % ks_n : 0;
+                const int kbeg = SPLIT ? ks * ksteps / ks_n : 0, kend = SPLIT ? (ks + 1) * ksteps / ks_n : ksteps;
+                for (int kt = kbeg; kt < kend; ++kt) {
                     ok = mbar_wait(&full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t off = (uint64_t)(st * (G_STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < G_BK / 16; ++k) {
-                        if (PAIR) mma_f16_pair(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
-                        else mma_f16(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+                        const uint32_t acc = (kt != kbeg || k != 0) ? 1u : 0u;  // the first MMA of a tile overwrites the accumulator
+                        if (PAIR) mma_f16_pair(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, acc);
+                        else mma_f16(d_tmem, a_desc0 + off + 2 * k, b_desc0 + off + 2 * k, idesc, acc);
                     }
                     if (PAIR) tc_commit_pair(&empty[st], 3);
                     else tc_commit(&empty[st]);
@@ -244,7 +252,8 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
         bool ok = true;
         for (int tile = t_begin; ok && tile < t_end; ++tile, ++j) {
             const uint32_t buf = j & 1u;
-            const int m0 = (tile / tiles_n) * TILE_M + (int)rank * G_BM, n0 = (tile % tiles_n) * G_BN;
+            const int sp = SPLIT ? tile / ks_n : tile;
+            const int m0 = (sp / tiles_n) * TILE_M + (int)rank * G_BM, n0 = (sp % tiles_n) * G_BN;
             const int m = m0 + row;
             const bool row_ok = m < p.M;
             ok = mbar_wait(&accum_full[buf], (j >> 1) & 1u, wc, DEV_TIMEOUT_ACCUM);
@@ -262,6 +271,15 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                 tmem_ld32(lane_addr + (uint32_t)c, v);
                 tmem_ld_wait();
                 if (!row_ok) continue;
+                if constexpr (SPLIT) {  // this slice's float sums, row-major [slice][M][N]
+                    float4 *dst = reinterpret_cast<float4 *>(p.partial + ((size_t)(tile % ks_n) * p.M + m) * p.N + n);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (n + 4 * e < p.N)
+                            dst[e] = make_float4(__uint_as_float(v[4 * e]), __uint_as_float(v[4 * e + 1]), __uint_as_float(v[4 * e + 2]),
+                                                 __uint_as_float(v[4 * e + 3]));
+                    continue;
+                }
                 if (p.epi == EPI_RESIDUAL) {
                     if (p.colscale) {  // gated residual: the projection's column n is multiplied by colscale[n] first
 #pragma unroll
@@ -342,6 +360,12 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                     for (int e = 0; e < 32; ++e)
                         f[e] = act_apply(__uint_as_float(v[e]) * rms + ((p.bias && n + e < p.N) ? __ldg(p.bias + n + e) : 0.0f),
                                          p.act);
+                    // erf-GELU behind its own uniform branch: inside act_apply the compiler evaluated it for every element of
+                    // every epilogue (gate/up of the denoise loop lost 15 % to it)
+                    if (p.act == ACT_GELU_ERF) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) f[e] = 0.5f * f[e] * (1.0f + erff(f[e] * 0.70710678118654752440f));
+                    }
                     if (p.out_f32) {
                         float4 *fp = reinterpret_cast<float4 *>(p.out_f32 + mo * p.ld_out + n);
 #pragma unroll
@@ -405,6 +429,44 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_c
     dense_gemm_body<256, true>(a_map, w_map, p, tiles_m, tiles_n);
 }
 
+__global__ void __launch_bounds__(G_THREADS, 1)
+dense_gemm_splitk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                         const GemmParams p, int tiles_m, int tiles_n) {
+    dense_gemm_body<64, false, true>(a_map, w_map, p, tiles_m, tiles_n);
+}
+
+// h[m][n] += (sum over the K slices, in slice order) (* colscale[n]) (+ bias[n]); hb = bf16(h).  Four columns per thread.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, int ksplit, int M, int N,
+                                                            const float *__restrict__ colscale, const float *__restrict__ bias,
+                                                            float *__restrict__ h, __nv_bfloat16 *__restrict__ hb, int ld) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total4 = (size_t)M * N / 4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / (N / 4)), n = (int)(i % (N / 4)) * 4;
+        float4 a = *reinterpret_cast<const float4 *>(partial + (size_t)m * N + n);
+        for (int s = 1; s < ksplit; ++s) {
+            const float4 b = *reinterpret_cast<const float4 *>(partial + ((size_t)s * M + m) * N + n);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (colscale) {
+            const float4 c = *reinterpret_cast<const float4 *>(colscale + n);
+            a.x *= c.x; a.y *= c.y; a.z *= c.z; a.w *= c.w;
+        }
+        if (bias) {
+            const float4 c = *reinterpret_cast<const float4 *>(bias + n);
+            a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+        }
+        float4 *hp = reinterpret_cast<float4 *>(h + (size_t)m * ld + n);
+        float4 r = *hp;
+        r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
+        *hp = r;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+        *reinterpret_cast<uint2 *>(hb + (size_t)m * ld + n) =
+            make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+    }
+}
+
 // 0 = choose by cost; 1 / 2 / 3 / 4 force the 128 x 256, 128 x 128, CTA-pair and 128 x 64 tilings (testing knob).
 static std::atomic<int> g_gemm_variant{0};
 constexpr float kPairTileFactor = 0.95f;  // time of a pair's 256 x 256 tile relative to a lone CTA's 128 x 256 tile
@@ -444,6 +506,25 @@ static int dense_gemm_one(const void *A, int lda, const void *W, GemmParams p, c
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
     if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
     const int n_sm = sm_count();
+    // Few rows, narrow N, long K (Wo / Wdown of one observation: 16 tiles of 128 x 64 for N = 1024, each streaming all of
+    // K through one SM): cut K so that the slices fill the machine, then add the slices in a fixed order.
+    if (p.partial && p.epi == EPI_RESIDUAL && dense_gemm_variant() == 0 && p.M <= G_BM && p.rows_in == 0 && p.scatter_hd == 0 &&
+        !p.use_rms && p.N % 4 == 0 && n_sm > 0) {
+        const int tiles = (p.N + 63) / 64, ksteps = (p.K + G_BK - 1) / G_BK;
+        int ksplit = n_sm / tiles;
+        if (ksplit > ksteps / 4) ksplit = ksteps / 4;  // at least four 64-wide k-steps per slice
+        if (ksplit > p.partial_slices) ksplit = p.partial_slices;
+        if (ksplit >= 2) {
+            GemmParams ps = p;
+            ps.ksplit = ksplit;
+            int rc = dense_gemm_one(A, lda, W, ps, stream, 5);
+            if (rc) return rc;
+            const size_t total4 = (size_t)p.M * p.N / 4;
+            const int blocks = (int)((total4 + 255) / 256 < (size_t)n_sm * 4 ? (total4 + 255) / 256 : (size_t)n_sm * 4);
+            return launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, static_cast<const float *>(p.partial), ksplit,
+                              p.M, p.N, p.colscale, p.bias, p.h, p.out_bf, p.ld_out);
+        }
+    }
     static const bool split_off = std::getenv("VLAB200_NO_GEMM_SPLIT") != nullptr;  // measurement knob
     if (!split_off && dense_gemm_variant() == 0 && n_sm >= 2 && p.rows_in == 0 && p.scatter_hd == 0 && p.M > 2 * G_BM) {
         const int pairs = n_sm / 2, tn256 = (p.N + 255) / 256, tiles_mp = (p.M + 2 * G_BM - 1) / (2 * G_BM);
@@ -517,6 +598,16 @@ static int dense_gemm_one(const void *A, int lda, const void *W, GemmParams p, c
     if (variant == 4 && p.N <= 64) variant = 1;
     const uint64_t wdims[2] = {(uint64_t)p.K, (uint64_t)p.N};
     const uint64_t wstrides[1] = {(uint64_t)p.K * 2};
+    if (variant == 5) {  // split-K slices on 128 x 64 tiles
+        const uint32_t box[2] = {G_BK, 64};
+        int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        if (int rc = ensure_dyn_smem(dense_gemm_splitk_kernel, GemmCfg<64, false>::SMEM)) return rc;
+        const int nt = tiles_m * tn64 * p.ksplit;
+        return launch_pdl(dense_gemm_splitk_kernel, dim3(nt < n_sm ? nt : n_sm), dim3(G_THREADS), GemmCfg<64, false>::SMEM, stream,
+                          amap, wmap, p, tiles_m, tn64);
+    }
     if (variant == 3) {
         const uint32_t box[2] = {G_BK, 128};  // each CTA of a pair stages half of the 256 weight rows
         int rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, wdims, wstrides, box,
