@@ -33,7 +33,8 @@ namespace vb {
 
 // streaming kernel for wide heads / long key ranges (attn_flash.cu)
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale = 0.0f);
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale = 0.0f,
+                    float *ws = nullptr, size_t ws_bytes = 0);
 
 constexpr int ATT_SOFTMAX_WARPS = 16;
 constexpr int ATT_THREADS = (ATT_SOFTMAX_WARPS + 3) * 32;  // + loader + 2 MMA issuers
@@ -429,6 +430,13 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, const void *q, void *out,
                                      int32_t S, int32_t n_q, int32_t kv_len, int32_t mask_mode,
                                      const int32_t *pad_ranges, void *stream) {
+    return vb::attention_ws(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, static_cast<cudaStream_t>(stream), nullptr, 0);
+}
+
+// vlab200_attention with an optional float workspace: with it, calls that have few work units (one observation) run
+// the streaming kernel over key slices on separate SMs and merge the slices (attn_flash.cu).
+int vb::attention_ws(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len, int mask_mode,
+                     const int32_t *pad_ranges, cudaStream_t stream, float *ws, size_t ws_bytes) {
     if (!st || !st->k_pages || !st->v_pages || !q || !out) return VLAB200_ERR_ARG;
     if (layer < 0 || layer >= st->n_layers || S <= 0 || n_q <= 0 || st->n_kv <= 0 || n_q % st->n_kv)
         return VLAB200_ERR_ARG;
@@ -440,9 +448,11 @@ extern "C" int32_t vlab200_attention(const vlab200_kv_store *st, int32_t layer, 
     const int g = n_q / st->n_kv;
     const int R = g * S;
     if (st->head_dim != 64 && st->head_dim != 128 && st->head_dim != 256) return VLAB200_ERR_UNSUPPORTED;
-    if (st->head_dim != 64 || kv_len > vb::ATT_MAX_KEYS || R > 256)
-        return vb::attention_flash(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges,
-                                   static_cast<cudaStream_t>(stream));
+    // the whole-range kernel gives one CTA per (observation, kv head): with a workspace and few of those, the key-split
+    // streaming kernel spreads them over more SMs
+    const bool few = ws && st->n_obs * st->n_kv * 4 <= vb::sm_count() && kv_len > 3 * 64;
+    if (st->head_dim != 64 || kv_len > vb::ATT_MAX_KEYS || R > 256 || few)
+        return vb::attention_flash(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, 0.0f, ws, ws_bytes);
     int *status = vb::device_status_ptr();
     if (!status) return vb::cuda_fail(cudaGetLastError(), "device_status_ptr");
 

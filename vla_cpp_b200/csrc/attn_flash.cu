@@ -33,6 +33,11 @@ struct FlashParams {
     float scale_log2;
     int out_al32;  // out is 32-byte aligned: 256-bit stores
     int *status;
+    // key-split mode (few work units): a unit's key blocks are cut into n_split slices that run as separate work items;
+    // a slice leaves its un-normalised O rows, running maximum and row sum in the workspace for attn_split_combine_kernel
+    int n_split;
+    float *ws_o;   // [n_units * n_split][128][HD]
+    float *ws_ml;  // [n_units * n_split][128][2]: maximum (log2 units), row sum
 };
 
 __device__ __forceinline__ float fa_ex2(float x) {
@@ -65,7 +70,7 @@ struct FlashSmem {
     static constexpr int TMEM_COLS = (HD + 128 <= 256) ? 256 : 512;
 };
 
-template <int HD>
+template <int HD, bool SPLIT = false>
 __global__ void __launch_bounds__(FA_THREADS, HD == 64 ? 2 : 1)
 attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   const __grid_constant__ CUtensorMap v_map, const FlashParams p) {
@@ -83,6 +88,8 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const WaitCtx wc{abort_flag, p.status};
     const int nb = p.n_blocks;
+    const int ns = SPLIT ? p.n_split : 1;  // key slices per unit
+    const int n_work = p.n_units * ns;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -120,7 +127,9 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             tma_prefetch_desc(&v_map);
             uint32_t ui = 0, jb = 0;  // units and key blocks processed so far by this CTA
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+            for (int wu = blockIdx.x; ok && wu < n_work; wu += gridDim.x, ++ui) {
+                const int unit = SPLIT ? wu / ns : wu, sp = SPLIT ? wu % ns : 0;
+                const int j0 = SPLIT ? sp * nb / ns : 0, j1 = SPLIT ? (sp + 1) * nb / ns : nb;
                 const int item = unit / p.n_mt, mt = unit % p.n_mt;
                 const int obs = item / p.n_kv, kvh = item % p.n_kv;
                 const int page = p.page0 + item;
@@ -129,7 +138,7 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (!ok) break;
                 mbar_expect_tx(q_full, L::Q_BYTES);
                 for (int cb = 0; cb < L::CB; ++cb) tma_load_2d(smem + cb * 16384, &q_map, q_full, cb * 64, qrow0);
-                for (int j = 0; j < nb; ++j, ++jb) {
+                for (int j = j0; j < j1; ++j, ++jb) {
                     const int st = jb & 1;
                     const uint32_t ph = (jb >> 1) & 1u;
                     ok = mbar_wait(&k_free[st], ph ^ 1u, wc, DEV_TIMEOUT_EMPTY);
@@ -168,7 +177,9 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 tc_commit(&s_full[st]);
                 tc_commit(&k_free[st]);
             };
-            for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+            for (int wu = blockIdx.x; ok && wu < n_work; wu += gridDim.x, ++ui) {
+                const int sp = SPLIT ? wu % ns : 0;
+                const int j0 = SPLIT ? sp * nb / ns : 0, j1 = SPLIT ? (sp + 1) * nb / ns : nb;
                 ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 // first S block of the unit: its TMEM buffer was last read by the P V of block jb-2
@@ -177,21 +188,21 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
                 issue_s(jb);
-                if (nb == 1) tc_commit(q_free);
-                for (int j = 0; j < nb; ++j, ++jb) {
+                if (j1 - j0 == 1) tc_commit(q_free);
+                for (int j = j0; j < j1; ++j, ++jb) {
                     const uint32_t st = jb & 1u, ph = (jb >> 1) & 1u;
-                    if (j + 1 < nb) {
+                    if (j + 1 < j1) {
                         const uint32_t jn = jb + 1;
                         ok = mbar_wait(&k_full[jn & 1u], (jn >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
                         if (ok && jn >= 2) ok = mbar_wait(&pv_done[jn & 1u], ((jn - 2) >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
                         if (!ok) break;
                         tc_fence_after();
                         issue_s(jn);
-                        if (j + 2 == nb) tc_commit(q_free);  // the unit's last S block has been issued
+                        if (j + 2 == j1) tc_commit(q_free);  // the unit's last S block has been issued
                     }
                     ok = mbar_wait(&p_full[st], ph, wc, DEV_TIMEOUT_FULL);
                     if (ok) ok = mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_FULL);
-                    if (ok && j == 0) ok = mbar_wait(o_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
+                    if (ok && j == j0) ok = mbar_wait(o_free, (ui & 1u) ^ 1u, wc, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t v_addr = v_base + st * L::KV_BYTES;
@@ -200,7 +211,7 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     for (int k16 = 0; k16 < FA_BKV / 16; ++k16)
                         mma_f16_tmem_a(tmem_base, p_tmem + (uint32_t)(k16 * 8),
                                        smem_desc_sw128(v_addr + k16 * 2048, 8192, 1024), idesc_o,
-                                       (j | k16) != 0 ? 1u : 0u);
+                                       (j != j0 || k16 != 0) ? 1u : 0u);
                     tc_commit(&pv_done[st]);
                     tc_commit(&v_free[st]);
                 }
@@ -215,7 +226,9 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         const int n_suffix_cols = p.kv_len - p.prefix_len;
         uint32_t ui = 0, jb = 0;
         bool ok = true;
-        for (int unit = blockIdx.x; ok && unit < p.n_units; unit += gridDim.x, ++ui) {
+        for (int wu = blockIdx.x; ok && wu < n_work; wu += gridDim.x, ++ui) {
+            const int unit = SPLIT ? wu / ns : wu, sp = SPLIT ? wu % ns : 0;
+            const int j0 = SPLIT ? sp * nb / ns : 0, j1 = SPLIT ? (sp + 1) * nb / ns : nb;
             const int item = unit / p.n_mt, mt = unit % p.n_mt;
             const int obs = item / p.n_kv, kvh = item % p.n_kv;
             const int row = mt * 128 + qtr * 32 + lane;
@@ -236,7 +249,7 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const int pad_w = pad_hi - pad_lo;
             float m_used = -INFINITY;  // running maximum in log2 units (lazy)
             float l_sum = 0.0f;
-            for (int j = 0; j < nb; ++j, ++jb) {
+            for (int j = j0; j < j1; ++j, ++jb) {
                 const uint32_t st = jb & 1u, ph = (jb >> 1) & 1u;
                 const uint32_t s_addr = tmem_base + L::O_COLS + st * 64 + lane_sel;
                 ok = mbar_wait(&s_full[st], ph, wc, DEV_TIMEOUT_FULL);
@@ -275,7 +288,7 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     m_used = bm;
                     l_sum *= factor;
                 }
-                if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                if (j > j0 && __any_sync(0xffffffffu, raise)) {
                     // O holds contributions scaled with the old maximum: rescale it in TMEM once the
                     // previous block's P V has landed
                     const uint32_t jp = jb - 1;
@@ -317,6 +330,26 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             ok = mbar_wait(o_done, ui & 1u, wc, DEV_TIMEOUT_ACCUM);
             if (!ok) break;
             tc_fence_after();
+            if constexpr (SPLIT) {
+                // this slice's un-normalised rows and their (maximum, sum): attn_split_combine_kernel merges the slices
+                const size_t wrow = (size_t)wu * 128 + qtr * 32 + lane;
+                float4 *wo = reinterpret_cast<float4 *>(p.ws_o + wrow * HD);
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            wo[(c >> 2) + e] = make_float4(__uint_as_float(ov[4 * e]), __uint_as_float(ov[4 * e + 1]),
+                                                           __uint_as_float(ov[4 * e + 2]), __uint_as_float(ov[4 * e + 3]));
+                    }
+                }
+                if (row_ok) *reinterpret_cast<float2 *>(p.ws_ml + wrow * 2) = make_float2(m_used, l_sum);
+                tc_fence_before();
+                mbar_arrive(o_free);
+                continue;
+            }
             const float inv = 1.0f / l_sum;
             __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
             for (int c = 0; c < HD; c += 32) {
@@ -756,9 +789,44 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     }
 }
 
+// Merges the key slices of every (unit, row): M = max_s m_s; O = sum_s O_s 2^(m_s - M); l = sum_s l_s 2^(m_s - M);
+// out = bf16(O / l), slices in order.  One warp per row, HD / 32 columns per lane.
+template <int HD>
+__global__ void __launch_bounds__(256) attn_split_combine_kernel(const FlashParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp_g = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (warp_g >= p.n_units * 128) return;
+    const int unit = warp_g >> 7, r = warp_g & 127;
+    const int item = unit / p.n_mt, mt = unit % p.n_mt;
+    const int obs = item / p.n_kv, kvh = item % p.n_kv;
+    const int row = mt * 128 + r;
+    if (row >= p.R) return;
+    const int head_l = row / p.S, tok = row % p.S;
+    float M = -INFINITY;
+    for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, p.ws_ml[(((size_t)unit * p.n_split + s) * 128 + r) * 2]);
+    float acc[HD / 32];
+#pragma unroll
+    for (int i = 0; i < HD / 32; ++i) acc[i] = 0.0f;
+    float l = 0.0f;
+    for (int s = 0; s < p.n_split; ++s) {
+        const size_t wrow = ((size_t)unit * p.n_split + s) * 128 + r;
+        const float2 ml = *reinterpret_cast<const float2 *>(p.ws_ml + wrow * 2);
+        const float w = ml.x == -INFINITY ? 0.0f : fa_ex2(ml.x - M);
+        l = fmaf(ml.y, w, l);
+#pragma unroll
+        for (int i = 0; i < HD / 32; ++i) acc[i] = fmaf(p.ws_o[wrow * HD + i * 32 + lane], w, acc[i]);
+    }
+    const float inv = 1.0f / l;
+    __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
+#pragma unroll
+    for (int i = 0; i < HD / 32; ++i) dst[i * 32 + lane] = __float2bfloat16(acc[i] * inv);
+}
+
 template <int HD>
 static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                        int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale) {
+                        int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale, float *ws,
+                        size_t ws_bytes) {
     using L = FlashSmem<HD>;
     int *status = device_status_ptr();
     if (!status) return cuda_fail(cudaGetLastError(), "device_status_ptr");
@@ -818,6 +886,24 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
             return launch_pdl(attn_flash_pair_kernel<HD>, dim3(2 * ncl), dim3(FP_THREADS), LP::TOTAL, stream, qmap, kmap, vmap128, p);
         }
     }
+    p.n_split = 1;
+    if (ws && p.n_units * 2 <= n_sm && p.n_blocks >= 4) {
+        // few units (one observation): cut every unit's keys into slices of at least two 64-key blocks so that the slices fill
+        // the machine, then merge them (flash-decoding)
+        int n_split = n_sm / p.n_units;
+        if (n_split > p.n_blocks / 2) n_split = p.n_blocks / 2;  // two to four blocks per slice measured alike, one slower
+        const size_t need = (size_t)p.n_units * n_split * 128 * (HD + 2) * sizeof(float);
+        if (n_split >= 2 && need <= ws_bytes) {
+            p.n_split = n_split;
+            p.ws_o = ws;
+            p.ws_ml = ws + (size_t)p.n_units * n_split * 128 * HD;
+            if (int rc = ensure_dyn_smem(attn_flash_kernel<HD, true>, L::TOTAL)) return rc;
+            if (int rc = launch_pdl(attn_flash_kernel<HD, true>, dim3(p.n_units * n_split), dim3(FA_THREADS), L::TOTAL, stream, qmap, kmap,
+                                    vmap, p))
+                return rc;
+            return launch_pdl(attn_split_combine_kernel<HD>, dim3((p.n_units * 128 + 7) / 8), dim3(256), 0, stream, p);
+        }
+    }
     if (int rc = ensure_dyn_smem(attn_flash_kernel<HD>, L::TOTAL)) return rc;
     const int slots = (HD == 64 ? 2 : 1) * n_sm;  // head_dim 64: two CTAs share an SM (256 TMEM columns, 50 KB each)
     const int grid = p.n_units < slots ? p.n_units : slots;
@@ -825,13 +911,14 @@ static int launch_flash(const vlab200_kv_store *st, int layer, const void *q, vo
 }
 
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale) {
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale, float *ws,
+                    size_t ws_bytes) {
     if (st->head_dim == 256)
-        return launch_flash<256>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
+        return launch_flash<256>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale, ws, ws_bytes);
     if (st->head_dim == 128)
-        return launch_flash<128>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
+        return launch_flash<128>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale, ws, ws_bytes);
     if (st->head_dim == 64)
-        return launch_flash<64>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale);
+        return launch_flash<64>(st, layer, q, out, S, n_q, kv_len, mask_mode, pad_ranges, stream, softmax_scale, ws, ws_bytes);
     return VLAB200_ERR_UNSUPPORTED;
 }
 

@@ -33,7 +33,7 @@
 namespace vb {
 
 int attention_flash(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len,
-                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale);
+                    int mask_mode, const int32_t *pad_ranges, cudaStream_t stream, float softmax_scale, float *ws, size_t ws_bytes);
 
 __device__ __forceinline__ float vit_block_sum(float v, float *red) {
 #pragma unroll
@@ -398,7 +398,7 @@ int bitvla_vit_cuda_forward(bitvla_vit_cuda_ctx *ctx, const void *d_patches, voi
                                  bf(w.v_b), ctx->q.as<__nv_bfloat16>(), ctx->kp.as<__nv_bfloat16>(), ctx->vp.as<__nv_bfloat16>(), S, heads, hd, hp)))
             return fail("head split", rc);
         vlab200_kv_store view{ctx->kp.p, ctx->vp.p, 1, 1, heads, hp, S, 0};
-        if ((rc = vb::attention_flash(&view, 0, ctx->q.p, ctx->att.p, S, heads, S, 0, nullptr, cs, scale))) return fail("attention", rc);
+        if ((rc = vb::attention_flash(&view, 0, ctx->q.p, ctx->att.p, S, heads, S, 0, nullptr, cs, scale, nullptr, 0))) return fail("attention", rc);
         if ((rc = vb::launch_pdl(vb::vit_merge_quant_kernel, dim3(S), dim3(256), (size_t)H * 4, cs, ctx->att.as<__nv_bfloat16>(), heads, hd,
                                  hp, a8, s)))
             return fail("merge", rc);

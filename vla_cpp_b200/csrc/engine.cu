@@ -176,6 +176,8 @@ __global__ void pages_to_f32_kernel(const __nv_bfloat16 *__restrict__ pages, flo
 
 constexpr int kFewRows = 256;  // suffix rows (n_obs * S) up to which the QKV projection takes the narrow-tile path
 constexpr int kSplitSlices = 8;  // most K slices of a residual GEMM with <= 128 rows
+// key-split attention: at most one (unit, slice) per SM, 128 rows of head_dim + 2 floats each
+static size_t kAttnWsBytes(int hd) { return (size_t)160 * 128 * (hd + 2) * sizeof(float); }
 }
 
 // ------------------------------------------------------------------------ engine --
@@ -187,6 +189,7 @@ struct vlab200_engine {
     // prepared weights
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
     vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
+    vb::DevBuf attn_ws;  // float32 workspace of the key-split attention path (calls with one or two observations)
     vb::DevBuf splitk;  // float32 [kSplitSlices][128][H]: K slices of Wo / Wdown when a call has at most 128 suffix rows
     vb::DevBuf mods;  // pi0.5: float32 [n_layers][2][steps][3H] (scale | shift | gate of the two norms), then [steps][3H] final
     // workspace
@@ -314,7 +317,7 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
         (rc = e->tmp_bf.alloc((size_t)2 * B * e->P * kvf * 2)) || (rc = e->x_stage.alloc(Mc * A * 4)) ||
         (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)) ||
         (rc = e->pad_stage.alloc(B * 2 * 4)) || (rc = e->vbuf.alloc(M * A * 4)) ||
-        (rc = e->splitk.alloc((size_t)kSplitSlices * 128 * H * 4)))
+        (rc = e->splitk.alloc((size_t)kSplitSlices * 128 * H * 4)) || (rc = e->attn_ws.alloc(kAttnWsBytes(hd))))
         return rc;
     VB_CUDA(cudaMemset(e->h.p, 0, M * H * 4));
     VB_CUDA(cudaMemset(e->hb.p, 0, M * H * 2));
@@ -377,7 +380,8 @@ static int layer_stage(vlab200_engine *e, int l, int stage, int n_obs, const flo
     case 1: {
         const int kv_len = self ? e->P + S : e->P;
         const int mode = self ? (c.model == 0 ? 1 : 2) : 0;
-        return vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs);
+        return attention_ws(&live, 0, e->q.p, e->att.p, S, c.n_q, kv_len, mode, pad_ranges, cs, e->attn_ws.as<float>(),
+                            kAttnWsBytes(hd));
     }
     case 2: {
         GemmParams p{};
@@ -436,7 +440,8 @@ static int ada_layer(vlab200_engine *e, int l, int step, int n_obs, const float 
         return rc;
     }
     // no mask: every action token sees the prefix and every action token (soft_max_ext without a mask, pi05.cpp:264)
-    if ((rc = vlab200_attention(&live, 0, e->q.p, e->att.p, S, c.n_q, e->P + S, 0, nullptr, cs))) return rc;
+    if ((rc = attention_ws(&live, 0, e->q.p, e->att.p, S, c.n_q, e->P + S, 0, nullptr, cs, e->attn_ws.as<float>(), kAttnWsBytes(hd))))
+        return rc;
     p = GemmParams{};
     p.M = M; p.N = H; p.K = e->qf; p.epi = EPI_RESIDUAL; p.colscale = mod_in + 2 * H;
     p.h = h; p.out_bf = hb; p.ld_out = H; p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices;

@@ -92,6 +92,10 @@ struct DevBuf {
 // optionally with the Gemma-norm "+1" (gguf.cu).  VLAB200_OK or an error with the last-error text set.
 int gguf_upload(const vlab200_gguf *g, const char *name, int64_t d0, int64_t d1, bool as_bf16, bool gemma, DevBuf *out);
 
+// vlab200_attention with an optional float workspace for the key-split path of calls with few work units (attn.cu).
+int attention_ws(const vlab200_kv_store *st, int layer, const void *q, void *out, int S, int n_q, int kv_len, int mask_mode,
+                 const int32_t *pad_ranges, cudaStream_t stream, float *ws, size_t ws_bytes);
+
 // Float32 linear for a few rows (bitvla_fp32head.cu): out[m][n] = (residual ? residual[m][n] : 0) +
 // act(bias[n] + sum_k x[m][k] W[n][k]), W float32 [N][K] streamed once; act 0 none, 1 ReLU, 2 erf-GELU, 3 SiLU.
 int skinny_linear(const float *W, const float *bias, const float *x, const float *residual, float *out, int M, int N, int K,
