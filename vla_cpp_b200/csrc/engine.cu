@@ -175,7 +175,7 @@ __global__ void pages_to_f32_kernel(const __nv_bfloat16 *__restrict__ pages, flo
 }
 
 constexpr int kFewRows = 256;  // suffix rows (n_obs * S) up to which the QKV projection takes the narrow-tile path
-constexpr int kSplitSlices = 8;  // most K slices of a residual GEMM with <= 128 rows
+constexpr int kSplitSlices = 8;  // most K slices of a residual GEMM with few rows
 // key-split attention: at most one (unit, slice) per SM, 128 rows of head_dim + 2 floats each
 static size_t kAttnWsBytes(int hd) { return (size_t)160 * 128 * (hd + 2) * sizeof(float); }
 }
@@ -190,7 +190,7 @@ struct vlab200_engine {
     std::vector<vb::DevBuf> wqkv, wo, wgu, wdown, wkx, wvx;
     vb::DevBuf w_ain, b_ain, w_sp, b_sp, w_at1l, tvec, w_at2, b_at2, out_norm, w_aout, b_aout;
     vb::DevBuf attn_ws;  // float32 workspace of the key-split attention path (calls with one or two observations)
-    vb::DevBuf splitk;  // float32 [kSplitSlices][128][H]: K slices of Wo / Wdown when a call has at most 128 suffix rows
+    vb::DevBuf splitk;  // float32 [kSplitSlices][kFewRows][H]: K slices of Wo / Wdown when a call has few suffix rows
     vb::DevBuf mods;  // pi0.5: float32 [n_layers][2][steps][3H] (scale | shift | gate of the two norms), then [steps][3H] final
     // workspace
     vb::DevBuf k_pages, v_pages, h, hb, q, att, g, a, m1, x, rope_self, rope_cross, tmp_bf, x_stage, state_stage, pad_stage, vbuf;
@@ -317,7 +317,7 @@ static int engine_build(vlab200_engine *e, const vlab200_policy_weights *w) {
         (rc = e->tmp_bf.alloc((size_t)2 * B * e->P * kvf * 2)) || (rc = e->x_stage.alloc(Mc * A * 4)) ||
         (rc = e->state_stage.alloc(B * (size_t)(c.state_dim > 0 ? c.state_dim : 1) * 4)) ||
         (rc = e->pad_stage.alloc(B * 2 * 4)) || (rc = e->vbuf.alloc(M * A * 4)) ||
-        (rc = e->splitk.alloc((size_t)kSplitSlices * 128 * H * 4)) || (rc = e->attn_ws.alloc(kAttnWsBytes(hd))))
+        (rc = e->splitk.alloc((size_t)kSplitSlices * kFewRows * H * 4)) || (rc = e->attn_ws.alloc(kAttnWsBytes(hd))))
         return rc;
     VB_CUDA(cudaMemset(e->h.p, 0, M * H * 4));
     VB_CUDA(cudaMemset(e->hb.p, 0, M * H * 2));
@@ -387,7 +387,7 @@ static int layer_stage(vlab200_engine *e, int l, int stage, int n_obs, const flo
         GemmParams p{};
         p.M = M; p.N = H; p.K = e->qf; p.epi = EPI_RESIDUAL;
         p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
-        p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices;
+        p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices; p.partial_rows = kFewRows;
         return dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs);
     }
     case 3: {
@@ -401,7 +401,7 @@ static int layer_stage(vlab200_engine *e, int l, int stage, int n_obs, const flo
         GemmParams p{};
         p.M = M; p.N = H; p.K = I; p.epi = EPI_RESIDUAL;
         p.h = e->h.as<float>(); p.out_bf = e->hb.as<__nv_bfloat16>(); p.ld_out = H;
-        p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices;
+        p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices; p.partial_rows = kFewRows;
         return dense_gemm(e->g.p, I, e->wdown[l].p, p, cs);
     }
     default:
@@ -444,7 +444,7 @@ static int ada_layer(vlab200_engine *e, int l, int step, int n_obs, const float 
         return rc;
     p = GemmParams{};
     p.M = M; p.N = H; p.K = e->qf; p.epi = EPI_RESIDUAL; p.colscale = mod_in + 2 * H;
-    p.h = h; p.out_bf = hb; p.ld_out = H; p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices;
+    p.h = h; p.out_bf = hb; p.ld_out = H; p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices; p.partial_rows = kFewRows;
     if ((rc = dense_gemm(e->att.p, e->qf, e->wo[l].p, p, cs))) return rc;
     if ((rc = launch_pdl(adarms_norm_kernel, dim3((M + 7) / 8), dim3(256), 0, cs, static_cast<const float *>(h), mod_post, hb, M, H, c.rms_eps)))
         return rc;
@@ -453,7 +453,7 @@ static int ada_layer(vlab200_engine *e, int l, int step, int n_obs, const float 
     if ((rc = dense_gemm(hb, H, e->wgu[l].p, p, cs))) return rc;
     p = GemmParams{};
     p.M = M; p.N = H; p.K = I; p.epi = EPI_RESIDUAL; p.colscale = mod_post + 2 * H;
-    p.h = h; p.out_bf = hb; p.ld_out = H; p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices;
+    p.h = h; p.out_bf = hb; p.ld_out = H; p.partial = e->splitk.as<float>(); p.partial_slices = kSplitSlices; p.partial_rows = kFewRows;
     return dense_gemm(e->g.p, I, e->wdown[l].p, p, cs);
 }
 

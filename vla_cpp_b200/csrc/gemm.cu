@@ -506,11 +506,11 @@ static int dense_gemm_one(const void *A, int lda, const void *W, GemmParams p, c
 int dense_gemm(const void *A, int lda, const void *W, GemmParams p, cudaStream_t stream) {
     if (!A || !W || p.M <= 0 || p.N <= 0 || p.K <= 0) return VLAB200_ERR_ARG;
     const int n_sm = sm_count();
-    // Few rows, narrow N, long K (Wo / Wdown of one observation: 16 tiles of 128 x 64 for N = 1024, each streaming all of
-    // K through one SM): cut K so that the slices fill the machine, then add the slices in a fixed order.
-    if (p.partial && p.epi == EPI_RESIDUAL && dense_gemm_variant() == 0 && p.M <= G_BM && p.rows_in == 0 && p.scatter_hd == 0 &&
-        !p.use_rms && p.N % 4 == 0 && n_sm > 0) {
-        const int tiles = (p.N + 63) / 64, ksteps = (p.K + G_BK - 1) / G_BK;
+    // Few rows, narrow N, long K (Wo / Wdown of one to five observations: 16 or 32 tiles of 128 x 64 for N = 1024, each
+    // streaming all of K through one SM): cut K so that the slices fill the machine, then add the slices in a fixed order.
+    if (p.partial && p.epi == EPI_RESIDUAL && dense_gemm_variant() == 0 && p.M <= p.partial_rows && p.rows_in == 0 &&
+        p.scatter_hd == 0 && !p.use_rms && p.N % 4 == 0 && n_sm > 0) {
+        const int tiles = ((p.M + G_BM - 1) / G_BM) * ((p.N + 63) / 64), ksteps = (p.K + G_BK - 1) / G_BK;
         int ksplit = n_sm / tiles;
         if (ksplit > ksteps / 4) ksplit = ksteps / 4;  // at least four 64-wide k-steps per slice
         if (ksplit > p.partial_slices) ksplit = p.partial_slices;

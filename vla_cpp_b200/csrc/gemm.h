@@ -21,10 +21,10 @@ struct GemmParams {
     int rows_in, rows_out, row_off;  // BIAS_ACT row re-mapping (rows_in == 0: identity)
     int scatter_hd, scatter_cap;     // BIAS_ACT into head-major pages: [m / rows_in][n / hd][cap][hd] (0: off)
     int al32;  // set by dense_gemm: h / out_bf rows start on 32-byte boundaries (256-bit epilogue accesses)
-    // split-K workspace (optional): float32 [partial_slices][M][N]; with it a RESIDUAL problem of <= 128 rows may run as
+    // split-K workspace (optional): float32 [partial_slices][M][N], M <= partial_rows; with it a RESIDUAL problem may run as
     // K slices on separate SMs followed by a fixed-order reduction (ksplit is chosen by dense_gemm)
     float *partial;
-    int partial_slices, ksplit;
+    int partial_slices, partial_rows, ksplit;
     int *status;
 };
 
