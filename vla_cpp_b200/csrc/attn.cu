@@ -193,6 +193,11 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {  // kernel parameters: independent of the previous kernel
+        tma_prefetch_desc(&q_map);
+        tma_prefetch_desc(&k_map);
+        tma_prefetch_desc(&v_map);
+    }
     pdl_launch_dependents();
     pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
     const int nchunks = (p.nk16 + 31) / 32;
@@ -222,9 +227,6 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     if (warp == ATT_SOFTMAX_WARPS) {
         // ------------------------------------------------------------- loader
         if (lane == 0) {
-            tma_prefetch_desc(&q_map);
-            tma_prefetch_desc(&k_map);
-            tma_prefetch_desc(&v_map);
             int n = 0;
             for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
                 const int st = n & 1;

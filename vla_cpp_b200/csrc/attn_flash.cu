@@ -116,15 +116,17 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {  // kernel parameters: independent of the previous kernel
+        tma_prefetch_desc(&q_map);
+        tma_prefetch_desc(&k_map);
+        tma_prefetch_desc(&v_map);
+    }
     pdl_launch_dependents();
     pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == 4) {
         // ----------------------------------------------------------------- loader
         if (lane == 0) {
-            tma_prefetch_desc(&q_map);
-            tma_prefetch_desc(&k_map);
-            tma_prefetch_desc(&v_map);
             uint32_t ui = 0, jb = 0;  // units and key blocks processed so far by this CTA
             bool ok = true;
             for (int wu = blockIdx.x; ok && wu < n_work; wu += gridDim.x, ++ui) {
@@ -488,15 +490,17 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {  // kernel parameters: independent of the previous kernel
+        tma_prefetch_desc(&q_map);
+        tma_prefetch_desc(&k_map);
+        tma_prefetch_desc(&v_map);
+    }
     pdl_launch_dependents();
     pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == FP_LOADER_WARP) {
         // ----------------------------------------------------------------- loader (each CTA its own halves)
         if (lane == 0) {
-            tma_prefetch_desc(&q_map);
-            tma_prefetch_desc(&k_map);
-            tma_prefetch_desc(&v_map);
             uint32_t ui = 0, jb = 0;
             bool ok = true;
             for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {

@@ -127,13 +127,15 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
     if (PAIR) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {  // the descriptors are kernel parameters: fetching them does not depend on the previous kernel
+        tma_prefetch_desc(&a_map);
+        tma_prefetch_desc(&w_map);
+    }
     pdl_launch_dependents();
     pdl_wait();  // everything above overlapped the previous kernel's tail; global memory is touched below
 
     if (warp == 0) {
         if (lane == 0) {
-            tma_prefetch_desc(&a_map);
-            tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
             for (int tile = t_begin; ok && tile < t_end; ++tile) {

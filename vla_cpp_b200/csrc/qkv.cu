@@ -305,6 +305,10 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
         *abort_flag = 0;
         fence_barrier_init();
     }
+    if (threadIdx.x == 0) {  // kernel parameters: independent of the previous kernel
+        tma_prefetch_desc(&x_map);
+        tma_prefetch_desc(&w_map);
+    }
     pdl_launch_dependents();
     pdl_wait();  // the barrier set-up above overlapped the previous kernel's tail; global memory is read from here on
     // RoPE table, transposed so that lanes (consecutive tokens) read consecutive words
@@ -334,8 +338,6 @@ __device__ __forceinline__ void qkv_rope_tma_body(const CUtensorMap &x_map, cons
 
     if (warp == 0) {
         if (lane == 0) {
-            tma_prefetch_desc(&x_map);
-            tma_prefetch_desc(&w_map);
             uint32_t st = 0, ph = 0;
             bool ok = true;
             for (int tile = t_begin; ok && tile < t_end; ++tile) {
