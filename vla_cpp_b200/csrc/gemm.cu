@@ -52,14 +52,36 @@ struct GemmCfg {
 // tanh-GELU(x) = 0.5 x (1 + tanh(u)) = x / (1 + e^-2u) with u = k0 x (1 + k1 x^2) (constants of
 // src/cuda/vla_cuda_bf16.cu:470-474).  One ex2 and one reciprocal each (relative error ~1e-6) keep the
 // epilogue off the critical path; tanhf and an IEEE division cost several times the issue slots.
-__device__ __forceinline__ float act_apply(float x, int act) {
-    if (act == ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
-    if (act == ACT_GELU_TANH) {
+template <int ACT>
+__device__ __forceinline__ float act_t(float x) {
+    if (ACT == ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
+    if (ACT == ACT_GELU_TANH) {
         const float k0 = 0.79788456080286535587989211986876f, k1 = 0.044715f;
         const float u = k0 * x * (1.0f + k1 * x * x);
         return __fdividef(x, 1.0f + __expf(-2.0f * u));
     }
+    if (ACT == ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
     return x;
+}
+
+// The activation is uniform over a launch: the epilogues branch on it ONCE per 32-column chunk and run a loop compiled
+// for that activation.  (With the activation as a run-time argument of the element function the compiler evaluated
+// every variant for every element and selected: the epilogue of a plain projection paid for SiLU, tanh-GELU and erf.)
+template <int ACT>
+__device__ __forceinline__ void gated_chunk(const uint32_t (&v)[32], float rms, uint32_t (&w)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float g0 = act_t<ACT>(__uint_as_float(v[4 * e]) * rms) * (__uint_as_float(v[4 * e + 1]) * rms);
+        const float g1 = act_t<ACT>(__uint_as_float(v[4 * e + 2]) * rms) * (__uint_as_float(v[4 * e + 3]) * rms);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
+        w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+    }
+}
+
+template <int ACT>
+__device__ __forceinline__ void act_chunk(float (&f)[32]) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) f[e] = act_t<ACT>(f[e]);
 }
 
 // SPLIT: the K loop of every output tile is cut into p.ksplit slices that run as separate work items; a slice stores its
@@ -341,13 +363,8 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                     }
                 } else if (p.epi == EPI_GATED) {
                     uint32_t w[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float g0 = act_apply(__uint_as_float(v[4 * e]) * rms, p.act) * (__uint_as_float(v[4 * e + 1]) * rms);
-                        const float g1 = act_apply(__uint_as_float(v[4 * e + 2]) * rms, p.act) * (__uint_as_float(v[4 * e + 3]) * rms);
-                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
-                        w[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                    }
+                    if (p.act == ACT_SILU) gated_chunk<ACT_SILU>(v, rms, w);
+                    else gated_chunk<ACT_GELU_TANH>(v, rms, w);
                     __nv_bfloat16 *brow = p.out_bf + mo * p.ld_out + (n >> 1);
                     if (p.al32 && n + 16 < p.N) {
                         st_global_v8(brow, w);
@@ -360,14 +377,10 @@ __device__ __forceinline__ void dense_gemm_body(const CUtensorMap &a_map, const 
                     float f[32];
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        f[e] = act_apply(__uint_as_float(v[e]) * rms + ((p.bias && n + e < p.N) ? __ldg(p.bias + n + e) : 0.0f),
-                                         p.act);
-                    // erf-GELU behind its own uniform branch: inside act_apply the compiler evaluated it for every element of
-                    // every epilogue (gate/up of the denoise loop lost 15 % to it)
-                    if (p.act == ACT_GELU_ERF) {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) f[e] = 0.5f * f[e] * (1.0f + erff(f[e] * 0.70710678118654752440f));
-                    }
+                        f[e] = __uint_as_float(v[e]) * rms + ((p.bias && n + e < p.N) ? __ldg(p.bias + n + e) : 0.0f);
+                    if (p.act == ACT_SILU) act_chunk<ACT_SILU>(f);
+                    else if (p.act == ACT_GELU_TANH) act_chunk<ACT_GELU_TANH>(f);
+                    else if (p.act == ACT_GELU_ERF) act_chunk<ACT_GELU_ERF>(f);
                     if (p.out_f32) {
                         float4 *fp = reinterpret_cast<float4 *>(p.out_f32 + mo * p.ld_out + n);
 #pragma unroll
