@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvla_b200.so")
-SOURCES = ["host_common.cu", "ternary.cu", "qkv.cu", "attn.cu", "attn_flash.cu", "denoise.cu", "gemm.cu", "engine.cu", "bitvla_lm.cu", "node_ops.cu", "gguf.cu", "vla_c_api.cu", "predict.cu", "vision.cu", "bitvla_vit.cu", "bitvla_fp32head.cu"]
+SOURCES = ["host_common.cu", "ternary.cu", "qkv.cu", "attn.cu", "attn_flash.cu", "denoise.cu", "gemm.cu", "engine.cu", "bitvla_lm.cu", "node_ops.cu", "gguf.cu", "vla_c_api.cu", "predict.cu", "chunk_loop.cu", "vision.cu", "bitvla_vit.cu", "bitvla_fp32head.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
