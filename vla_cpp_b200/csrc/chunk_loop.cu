@@ -793,6 +793,9 @@ __device__ __noinline__ void pages_prologue(const LoopParams &lp) {
 }
 
 // ---------------------------------------------------------------------------------------------- kernel
+// One instantiation per head_dim: the kernel's code has to stay small (each phase runs its code once every few microseconds
+// and what does not fit the SM's instruction cache is fetched from L2 every time).
+template <int HD>
 __global__ void __launch_bounds__(CL_THREADS, 1) chunk_loop_kernel(const __grid_constant__ LoopParams lp) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     if (threadIdx.x == 0) *reinterpret_cast<int *>(smem_raw + 72) = lp.n_wtab;
@@ -834,19 +837,14 @@ __global__ void __launch_bounds__(CL_THREADS, 1) chunk_loop_kernel(const __grid_
             switch (p.type) {
             case PH_GEMM:
                 if (p.ng == 2) gemm_phase<2>(p, lp, step, pr, cons, a_cnt);
-                else if (p.ng == 4) gemm_phase<4>(p, lp, step, pr, cons, a_cnt);
-                else gemm_phase<8>(p, lp, step, pr, cons, a_cnt);
+                else gemm_phase<4>(p, lp, step, pr, cons, a_cnt);
                 break;
             case PH_EMBED: embed_phase(p, lp); break;
             case PH_ATT:
-                if (p.hd == 64) att_phase<64>(p, lp, a_cnt);
-                else if (p.hd == 128) att_phase<128>(p, lp, a_cnt);
-                else att_phase<256>(p, lp, a_cnt);
+                att_phase<HD>(p, lp, a_cnt);
                 break;
             default:
-                if (p.hd == 64) combine_phase<64>(p);
-                else if (p.hd == 128) combine_phase<128>(p);
-                else combine_phase<256>(p);
+                combine_phase<HD>(p);
                 break;
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
@@ -878,6 +876,7 @@ __global__ void pad_image_kernel(const __nv_bfloat16 *__restrict__ src, uint8_t 
 
 // ------------------------------------------------------------------------------------------------ host
 struct ChunkLoop {
+    const void *kernel = nullptr;
     DevBuf phases, wtab, counter, ws_o, ws_ml, trace;
     DevBuf hbp, ap, m1p, attp, gp, qp, kpp, vpp;  // padded activations and pages
     DevBuf ssq;                                    // [H / 16][64] partial sums of squares of the residual mirror
@@ -912,7 +911,7 @@ int pick_kchunk(int kslice, int ng) {
 int pick_ng(int n_blocks16, int blocks_per_head, int n_cta) {  // n_blocks16: 16-column blocks; blocks_per_head: 0 = not paired
     int best = 2;
     double best_cost = 0;
-    for (int ng = 2; ng <= 4; ng *= 2) {  // 8 groups (kept in the kernel) need more weight bytes per unit than the ring holds
+    for (int ng = 2; ng <= 4; ng *= 2) {  // wider units need more weight bytes than the ring holds
         const int b = ng / 2;
         if (n_blocks16 % b || (blocks_per_head && blocks_per_head % b)) continue;
         const int units = n_blocks16 / b;
@@ -940,8 +939,11 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
     if ((size_t)S * (H * 2 + 16) + (size_t)4 * S * CL_SC_ROW > (size_t)CL_ARENA) return VLAB200_ERR_UNSUPPORTED;
     if ((size_t)(d.chunk * d.A + 64) * 4 > (size_t)CL_ARENA || d.A > 64) return VLAB200_ERR_UNSUPPORTED;
     int occ = 0;
-    if (ensure_dyn_smem(chunk_loop_kernel, CL_SMEM)) return VLAB200_ERR_CUDA;
-    VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, chunk_loop_kernel, CL_THREADS, CL_SMEM));
+    const void *kernel = hd == 64    ? reinterpret_cast<const void *>(chunk_loop_kernel<64>)
+                         : hd == 128 ? reinterpret_cast<const void *>(chunk_loop_kernel<128>)
+                                     : reinterpret_cast<const void *>(chunk_loop_kernel<256>);
+    if (ensure_dyn_smem(kernel, CL_SMEM)) return VLAB200_ERR_CUDA;
+    VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, CL_THREADS, CL_SMEM));
     int coop = 0, dev = 0;
     VB_CUDA(cudaGetDevice(&dev));
     VB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
@@ -1098,6 +1100,7 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
     cl->n_phases = (int)ph.size();
     cl->steps = d.steps;
     cl->n_cta = n_cta;
+    cl->kernel = kernel;
     LoopParams &lp = cl->lp;
     lp.phases = cl->phases.as<LoopPhase>();
     lp.n_phases = cl->n_phases;
@@ -1132,8 +1135,7 @@ int chunk_loop_run(ChunkLoop *cl, const float *state, const int32_t *pad, cudaSt
         lp.trace = cl->trace.as<unsigned long long>();
     }
     void *args[] = {&lp};
-    VB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(chunk_loop_kernel), dim3(cl->n_cta), dim3(CL_THREADS), args, CL_SMEM,
-                                        stream));
+    VB_CUDA(cudaLaunchCooperativeKernel(cl->kernel, dim3(cl->n_cta), dim3(CL_THREADS), args, CL_SMEM, stream));
     if (lp.trace) {
         const size_t n = (size_t)cl->n_phases * cl->steps;
         std::vector<unsigned long long> t(n);
