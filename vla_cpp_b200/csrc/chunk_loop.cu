@@ -54,7 +54,8 @@ enum { PH_GEMM = 0, PH_ATT = 2, PH_COMBINE = 3, PH_EMBED = 4 };
 enum { OUT_RESID = 0, OUT_GATED = 1, OUT_QKV = 2, OUT_BIAS_ACT = 3, OUT_EULER = 4 };
 enum { RMS_NONE = 0, RMS_PARTS = 1, RMS_LOCAL = 2 };  // use_rms: row sums of squares from the producer's per-sub-unit partials, or from the A tile
 
-constexpr int CL_THREADS = 256;
+constexpr int CL_THREADS = 256;   // the eight computing warps
+constexpr int CL_BLOCK = 288;     // + one warp whose lane 0 feeds the weight ring
 constexpr int CL_STAGES = 3;
 constexpr int CL_MAX_KSLICE = 1024;                               // columns of one K slice
 constexpr int CL_STAGE_BYTES = 64 * (256 * 2 + 16);                // 8 NG padded weight rows of 2048 / NG columns: NG = 8 is the largest
@@ -71,7 +72,6 @@ constexpr int CL_SC_LD = 20;                                      // floats per 
 constexpr int CL_SC_ROW = CL_SC_LD * 4;                           // bytes; the scratch tile holds the four K quarters of M x 16 sums
 constexpr int CL_EMBED_ROWS = 10;
 constexpr int CL_DEV_TIMEOUT = 105;
-constexpr int CL_PRODUCER_TID = 224;  // lane 0 of the last warp
 
 // A bf16 matrix [rows][cols] as a padded image: K slices of `kslice` columns, each a block of `rows` rows of
 // kslice * 2 + 16 bytes.  Element (row, col) sits at this byte offset.
@@ -170,8 +170,11 @@ struct WEntry {  // what the weight cursor needs to know about one GEMM phase
 static_assert(sizeof(LoopPhase) <= CL_DESC_BYTES && sizeof(LoopPhase) % 16 == 0, "descriptor slot");
 static_assert(sizeof(WEntry) == 32, "cursor table entry");
 
+// barrier of the computing warps (the feeder warp is not part of it)
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 struct Smem {
-    uint64_t *full, *a_full;
+    uint64_t *full, *a_full, *empty, *done;
     const WEntry *wtab;
     int n_wtab;
     volatile int *abort_flag;
@@ -186,6 +189,8 @@ __device__ __forceinline__ Smem get_smem() {
     Smem sm;
     sm.full = reinterpret_cast<uint64_t *>(smem_raw);
     sm.a_full = sm.full + CL_STAGES;
+    sm.empty = sm.a_full + 1;
+    sm.done = sm.empty + CL_STAGES;
     sm.abort_flag = reinterpret_cast<volatile int *>(smem_raw + 64);
     sm.n_wtab = *reinterpret_cast<const int *>(smem_raw + 72);
     sm.rms = reinterpret_cast<float *>(smem_raw + 128);
@@ -197,28 +202,10 @@ __device__ __forceinline__ Smem get_smem() {
     return sm;
 }
 
-// The weight cursor of the producer thread: the next sub-unit whose 16 rows go into the ring.
-struct Producer {
-    int step, gi, id, id_end;  // gi: index into the cursor table
-    unsigned issued;
-};
-
-// Sub-units of a phase dealt to this CTA: ids [b, e).  Sliced phases run the K slices of a sub-unit back to back
-// (id = u * kslices + slice), so the range is cut between sub-units.
-__device__ __forceinline__ void sub_range(int kslices, int n_sub, int &b, int &e) {
-    b = (int)((unsigned)n_sub * blockIdx.x / gridDim.x) * kslices;
-    e = (int)((unsigned)n_sub * (blockIdx.x + 1) / gridDim.x) * kslices;
-}
-
-__device__ __forceinline__ void producer_seek(Producer &pr, int steps, const Smem &sm) {
-    while (pr.step < steps && pr.id >= pr.id_end) {
-        if (++pr.gi == sm.n_wtab) {
-            pr.gi = 0;
-            if (++pr.step == steps) return;
-        }
-        const WEntry &w = sm.wtab[pr.gi];
-        sub_range(w.n_chunks, w.n_units, pr.id, pr.id_end);
-    }
+// Sub-units of a phase dealt to this CTA: ids [b, e) with id = unit * chunks + chunk: the range is cut between units.
+__device__ __forceinline__ void sub_range(int n_chunks, int n_units, int &b, int &e) {
+    b = (int)((unsigned)n_units * blockIdx.x / gridDim.x) * n_chunks;
+    e = (int)((unsigned)n_units * (blockIdx.x + 1) / gridDim.x) * n_chunks;
 }
 
 // weight rows of the 16-column block `sub16`: two groups of 8 rows
@@ -233,33 +220,47 @@ __device__ __forceinline__ void sub_rows(int half, int sub16, int &r0, int &r1) 
     }
 }
 
-__device__ __forceinline__ void producer_issue(Producer &pr, int steps, const Smem &sm) {
-    if (pr.step >= steps) return;
-    const WEntry w = sm.wtab[pr.gi];
-    const int u = pr.id / w.n_chunks, c = pr.id - u * w.n_chunks;
-    const unsigned stage = pr.issued % CL_STAGES;
-    uint64_t *bar = &sm.full[stage];
-    uint8_t *dst = sm.ring + (size_t)stage * CL_STAGE_BYTES;
-    const uint8_t *src = w.Wp + (size_t)c * w.N * w.stride;
-    mbar_expect_tx(bar, (uint32_t)w.ng * 8u * w.stride);
-    if (w.half > 0) {
-        for (int blk = 0; blk < w.ng / 2; ++blk) {
-            int r0, r1;
-            sub_rows(w.half, u * (w.ng / 2) + blk, r0, r1);
-            bulk_g2s(dst + (size_t)(2 * blk) * 8u * w.stride, src + (size_t)r0 * w.stride, 8u * w.stride, bar);
-            bulk_g2s(dst + (size_t)(2 * blk + 1) * 8u * w.stride, src + (size_t)r1 * w.stride, 8u * w.stride, bar);
+// The feeder: one thread walks the GEMM phases of every step in order and copies each (unit, chunk) of this CTA into the
+// next ring stage as soon as the eight computing warps have released it.  It runs ahead of the computation by the depth
+// of the ring, across phase boundaries and grid barriers.
+__device__ __noinline__ void feeder_loop(const LoopParams &lp) {
+    const Smem sm = get_smem();
+    const WaitCtx wc{sm.abort_flag, lp.status};
+    unsigned issued = 0;
+    bool ok = true;
+    for (int step = 0; ok && step < lp.steps; ++step)
+        for (int gi = 0; ok && gi < sm.n_wtab; ++gi) {
+            const WEntry w = sm.wtab[gi];
+            int id0, id1;
+            sub_range(w.n_chunks, w.n_units, id0, id1);
+            for (int id = id0; id < id1; ++id, ++issued) {
+                const int u = id / w.n_chunks, c = id - u * w.n_chunks;
+                const unsigned stage = issued % CL_STAGES;
+                if (issued >= CL_STAGES && !mbar_wait_backoff(&sm.empty[stage], ((issued / CL_STAGES) - 1u) & 1u, wc, CL_DEV_TIMEOUT, 20)) {
+                    ok = false;
+                    break;
+                }
+                uint64_t *bar = &sm.full[stage];
+                uint8_t *dst = sm.ring + (size_t)stage * CL_STAGE_BYTES;
+                const uint8_t *src = w.Wp + (size_t)c * w.N * w.stride;
+                mbar_expect_tx(bar, 16u * w.stride);
+                if (w.half > 0) {
+                    int r0, r1;
+                    sub_rows(w.half, u, r0, r1);
+                    bulk_g2s(dst, src + (size_t)r0 * w.stride, 8u * w.stride, bar);
+                    bulk_g2s(dst + 8u * w.stride, src + (size_t)r1 * w.stride, 8u * w.stride, bar);
+                } else {
+                    bulk_g2s(dst, src + (size_t)u * 16u * w.stride, 16u * w.stride, bar);
+                }
+            }
         }
-    } else {
-        bulk_g2s(dst, src + (size_t)u * w.ng * 8u * w.stride, (uint32_t)w.ng * 8u * w.stride, bar);
-    }
-    ++pr.issued;
-    ++pr.id;
-    producer_seek(pr, steps, sm);
+    *reinterpret_cast<volatile unsigned *>(reinterpret_cast<uint8_t *>(sm.full) + 76) = issued;
+    mbar_arrive(sm.done);
 }
 
 // Grid-wide barrier: every CTA arrives once; `target` counts arrivals since the launch.
 __device__ __forceinline__ bool grid_barrier(const LoopParams &lp, unsigned target, const Smem &sm, const WaitCtx &wc) {
-    __syncthreads();
+    cons_sync();
     if (threadIdx.x == 0 && !*sm.abort_flag) {
         __threadfence();
         atomicAdd(lp.counter, 1u);
@@ -279,7 +280,7 @@ __device__ __forceinline__ bool grid_barrier(const LoopParams &lp, unsigned targ
             }
         }
     }
-    __syncthreads();
+    cons_sync();
     return *sm.abort_flag == 0;
 }
 
@@ -374,7 +375,7 @@ __device__ __forceinline__ void gemm_epilogue(const LoopPhase &pg, const Smem &s
 // A unit = NG groups of 8 output columns; its weights arrive as K chunks of 2048 / NG columns (one ring stage each), A as
 // K slices of at most 1024 columns; the accumulators live in registers across all chunks and slices of the unit.
 template <int NG>
-__device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &lp, int step, Producer &pr, unsigned &cons, unsigned &a_cnt) {
+__device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &lp, int step, unsigned &cons, unsigned &a_cnt) {
     const Smem sm = get_smem();
     const WaitCtx wc{sm.abort_flag, lp.status};
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -411,7 +412,7 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
     for (int id = id0; id < id1; ++id) {
         const int u = id / n_chunks, c = id - u * n_chunks, slice = c / cps, cs = c - slice * cps;
         if (slice != cur_slice) {
-            __syncthreads();  // the arena is free: earlier readers are done
+            cons_sync();  // the arena is free: earlier readers are done
             if (tid == 0) {
                 mbar_expect_tx(sm.a_full, (uint32_t)M * astride);
                 bulk_g2s(As, Ap + (size_t)slice * M * astride, (uint32_t)M * astride, sm.a_full);
@@ -482,14 +483,15 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
                 }
             }
         }
-        __syncthreads();  // every warp has read the ring stage (and the previous block's epilogue has read the scratch tile)
-        if (tid == CL_PRODUCER_TID) producer_issue(pr, lp.steps, sm);
+        __syncwarp();  // every lane's fragments of this stage have been consumed by its products
+        if (lane == 0) mbar_arrive(&sm.empty[stage]);
         ++cons;
         if (c + 1 < n_chunks) continue;  // more of this unit's K follows: keep accumulating
+        cons_sync();  // the previous unit's epilogue has read the scratch tile
         // ---- epilogue: NG / 2 blocks of 16 columns through the scratch tile
 #pragma unroll
         for (int blk = 0; blk < NG / 2; ++blk) {
-            if (blk > 0) __syncthreads();  // the previous block's sums have been read
+            if (blk > 0) cons_sync();  // the previous block's sums have been read
             float *dst = sc + (size_t)kq * M * CL_SC_LD;
 #pragma unroll
             for (int mtl = 0; mtl < 2; ++mtl)
@@ -501,7 +503,7 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
                     *reinterpret_cast<float2 *>(rp) = make_float2(acc[mtl][2 * blk][2 * hr], acc[mtl][2 * blk][2 * hr + 1]);
                     *reinterpret_cast<float2 *>(rp + 8) = make_float2(acc[mtl][2 * blk + 1][2 * hr], acc[mtl][2 * blk + 1][2 * hr + 1]);
                 }
-            __syncthreads();
+            cons_sync();
             gemm_epilogue(pg, sm, sc, u * (NG / 2) + blk, step, M, N, half, out_mode, use_rms, act, erow, ec4);
         }
     }
@@ -512,11 +514,11 @@ __device__ __noinline__ void embed_phase(const LoopPhase &p, const LoopParams &l
     const Smem sm = get_smem();
     float *xs = reinterpret_cast<float *>(sm.arena);
     const int A = p.A_dim, H = p.H, chunk = p.chunk, sd = p.sd;
-    __syncthreads();
+    cons_sync();
     for (int i = threadIdx.x; i < chunk * A; i += CL_THREADS) xs[i] = __ldcg(p.x + i);
     float *ss = xs + chunk * A;
     for (int i = threadIdx.x; i < sd; i += CL_THREADS) ss[i] = lp.state[i];
-    __syncthreads();
+    cons_sync();
     const int nrb = (chunk + CL_EMBED_ROWS - 1) / CL_EMBED_ROWS;
     const int gt = blockIdx.x * CL_THREADS + threadIdx.x, gn = gridDim.x * CL_THREADS;
     for (int item = gt; item < nrb * H; item += gn) {
@@ -579,7 +581,7 @@ __device__ __noinline__ void att_phase(const LoopPhase &pg, const LoopParams &lp
         const int kvh = u / (n_rt * ns), rem = u - kvh * (n_rt * ns), rt = rem / ns, s = rem - rt * ns;
         const int key0 = s * ks, nkeys = min(ks, kv_len - key0), ks16 = (nkeys + 15) & ~15;
         const int row0 = rt * 32, nrows = min(32, R - row0);
-        __syncthreads();  // the arena is free
+        cons_sync();  // the arena is free
         if (tid == 0) {
             mbar_expect_tx(sm.a_full, (uint32_t)(nrows + 2 * nkeys) * SQ);
             bulk_g2s(Qs, pg.qp + ((size_t)kvh * gq * S + row0) * SQ, (uint32_t)nrows * SQ, sm.a_full);
@@ -592,7 +594,7 @@ __device__ __noinline__ void att_phase(const LoopPhase &pg, const LoopParams &lp
         }
         mbar_wait(sm.a_full, a_cnt & 1u, wc, CL_DEV_TIMEOUT);
         ++a_cnt;
-        __syncthreads();
+        cons_sync();
         // ---- S = Q K^T for this warp's 16 rows and its share of the 8-key groups
         const int ng = ks16 >> 3, g0 = kp * ng / 4, g1 = (kp + 1) * ng / 4, n_g = g1 - g0;  // n_g <= 3
         float sacc[3][4];
@@ -649,7 +651,7 @@ __device__ __noinline__ void att_phase(const LoopPhase &pg, const LoopParams &lp
             mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 2));
             if ((lane & 3) == 0) sm.red_max[rl[hr] * 4 + kp] = mx[hr];
         }
-        __syncthreads();
+        cons_sync();
         float sum[2] = {0.0f, 0.0f};
 #pragma unroll
         for (int hr = 0; hr < 2; ++hr) {
@@ -676,7 +678,7 @@ __device__ __noinline__ void att_phase(const LoopPhase &pg, const LoopParams &lp
             sum[hr] += __shfl_xor_sync(0xffffffffu, sum[hr], 2);
             if ((lane & 3) == 0) sm.red_sum[rl[hr] * 4 + kp] = sum[hr];
         }
-        __syncthreads();
+        cons_sync();
         // ---- O = P V: this warp's HD / 8 output columns, all 32 rows
         float oacc[2][NGV][4];
 #pragma unroll
@@ -796,30 +798,33 @@ __device__ __noinline__ void pages_prologue(const LoopParams &lp) {
 // One instantiation per head_dim: the kernel's code has to stay small (each phase runs its code once every few microseconds
 // and what does not fit the SM's instruction cache is fetched from L2 every time).
 template <int HD>
-__global__ void __launch_bounds__(CL_THREADS, 1) chunk_loop_kernel(const __grid_constant__ LoopParams lp) {
+__global__ void __launch_bounds__(CL_BLOCK, 1) chunk_loop_kernel(const __grid_constant__ LoopParams lp) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     if (threadIdx.x == 0) *reinterpret_cast<int *>(smem_raw + 72) = lp.n_wtab;
     __syncthreads();
     const Smem sm = get_smem();
     WEntry *wtab = reinterpret_cast<WEntry *>(smem_raw + CL_WTAB_OFF);
     if (threadIdx.x == 0) {
-        for (int i = 0; i < CL_STAGES; ++i) mbar_init(&sm.full[i], 1);
+        for (int i = 0; i < CL_STAGES; ++i) {
+            mbar_init(&sm.full[i], 1);
+            mbar_init(&sm.empty[i], CL_THREADS / 32);
+        }
         mbar_init(sm.a_full, 1);
+        mbar_init(sm.done, 1);
         *sm.abort_flag = 0;
         fence_barrier_init();
     }
-    for (int i = threadIdx.x; i < lp.n_wtab * 8; i += CL_THREADS)
+    for (int i = threadIdx.x; i < lp.n_wtab * 8; i += CL_BLOCK)
         reinterpret_cast<uint32_t *>(wtab)[i] = reinterpret_cast<const uint32_t *>(lp.wtab)[i];
     // descriptor of phase 0 into slot 0; from then on every phase fetches its successor's while it works
-    for (int i = threadIdx.x; i < (int)(sizeof(LoopPhase) / 4); i += CL_THREADS)
+    for (int i = threadIdx.x; i < (int)(sizeof(LoopPhase) / 4); i += CL_BLOCK)
         reinterpret_cast<uint32_t *>(smem_raw + CL_DESC_OFF)[i] = reinterpret_cast<const uint32_t *>(lp.phases)[i];
     __syncthreads();
-    WaitCtx wc{sm.abort_flag, lp.status};
-    Producer pr{0, -1, 0, 0, 0u};
-    if (threadIdx.x == CL_PRODUCER_TID) {
-        producer_seek(pr, lp.steps, sm);
-        for (int i = 0; i < CL_STAGES; ++i) producer_issue(pr, lp.steps, sm);
+    if (threadIdx.x >= CL_THREADS) {  // the feeder warp: lane 0 works, the warp takes no part in any later barrier
+        if (threadIdx.x == CL_THREADS) feeder_loop(lp);
+        return;
     }
+    const WaitCtx wc{sm.abort_flag, lp.status};
     unsigned cons = 0, a_cnt = 0, barriers = 0, seq = 0;
     pages_prologue(lp);
     ++barriers;
@@ -836,8 +841,7 @@ __global__ void __launch_bounds__(CL_THREADS, 1) chunk_loop_kernel(const __grid_
             }
             switch (p.type) {
             case PH_GEMM:
-                if (p.ng == 2) gemm_phase<2>(p, lp, step, pr, cons, a_cnt);
-                else gemm_phase<4>(p, lp, step, pr, cons, a_cnt);
+                gemm_phase<2>(p, lp, step, cons, a_cnt);
                 break;
             case PH_EMBED: embed_phase(p, lp); break;
             case PH_ATT:
@@ -857,10 +861,13 @@ __global__ void __launch_bounds__(CL_THREADS, 1) chunk_loop_kernel(const __grid_
             }
         }
     }
-    // weight rows still on their way must land before the CTA gives its shared memory back
-    if (threadIdx.x == CL_PRODUCER_TID)
-        for (unsigned i = cons; i < pr.issued; ++i) mbar_wait(&sm.full[i % CL_STAGES], (i / CL_STAGES) & 1u, wc, CL_DEV_TIMEOUT);
-    __syncthreads();
+    // Weight chunks still on their way must land before the CTA gives its shared memory back (only after a failure are
+    // there any: the feeder stops with the computation).
+    if (threadIdx.x == 0 && mbar_wait(sm.done, 0u, wc, CL_DEV_TIMEOUT)) {
+        const unsigned issued = *reinterpret_cast<volatile unsigned *>(smem_raw + 76);
+        for (unsigned i = cons; i < issued; ++i) mbar_wait(&sm.full[i % CL_STAGES], (i / CL_STAGES) & 1u, wc, CL_DEV_TIMEOUT);
+    }
+    cons_sync();
 }
 
 // dense [rows][K] bf16 -> padded image with K slices of `kslice` columns (the pad bytes stay zero)
@@ -907,23 +914,6 @@ int pick_kchunk(int kslice, int ng) {
     return 0;
 }
 
-// groups per unit of a full-K phase: fewest rounds over the CTAs, weighted by what a unit of that width costs
-int pick_ng(int n_blocks16, int blocks_per_head, int n_cta) {  // n_blocks16: 16-column blocks; blocks_per_head: 0 = not paired
-    int best = 2;
-    double best_cost = 0;
-    for (int ng = 2; ng <= 4; ng *= 2) {  // wider units need more weight bytes than the ring holds
-        const int b = ng / 2;
-        if (n_blocks16 % b || (blocks_per_head && blocks_per_head % b)) continue;
-        const int units = n_blocks16 / b;
-        const double cost = (double)((units + n_cta - 1) / n_cta) * (0.5 + 0.9 * b);
-        if (ng == 2 || cost < best_cost) {
-            best = ng;
-            best_cost = cost;
-        }
-    }
-    return best;
-}
-
 size_t image_bytes(int rows, int K, int kslices) { return (size_t)kslices * rows * ((size_t)(K / kslices) * 2 + 16); }
 
 }  // namespace
@@ -943,7 +933,7 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
                          : hd == 128 ? reinterpret_cast<const void *>(chunk_loop_kernel<128>)
                                      : reinterpret_cast<const void *>(chunk_loop_kernel<256>);
     if (ensure_dyn_smem(kernel, CL_SMEM)) return VLAB200_ERR_CUDA;
-    VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, CL_THREADS, CL_SMEM));
+    VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, CL_BLOCK, CL_SMEM));
     int coop = 0, dev = 0;
     VB_CUDA(cudaGetDevice(&dev));
     VB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
@@ -991,10 +981,10 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
 
     std::vector<LoopPhase> ph;
     bool bad = false;
-    auto gemm = [&](const uint8_t *Ap, int M, const void *w_dense, int N, int K, int kslices, int out_mode, int blocks_per_head) {
+    auto gemm = [&](const uint8_t *Ap, int M, const void *w_dense, int N, int K, int kslices, int out_mode) {
         LoopPhase p{};
         p.type = PH_GEMM; p.out_mode = out_mode; p.Ap = Ap; p.M = M; p.N = N; p.K = K; p.kslices = kslices;
-        p.ng = kslices > 1 ? 2 : pick_ng(N / 16, blocks_per_head, n_cta);
+        p.ng = 2;  // units of 4 groups (half as many, twice the weight bytes each) measured 2-5 % slower, and their code costs instruction cache
         p.kchunk = pick_kchunk(K / kslices, p.ng);
         p.n_sub = N / (8 * p.ng);
         p.eps = d.rms_eps; p.S = S; p.chunk = d.chunk;
@@ -1010,10 +1000,10 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         p.sd = d.model == 0 ? d.sd : 0; p.w2 = static_cast<const __nv_bfloat16 *>(d.w_sp); p.b2 = d.b_sp; p.h = d.h;
         p.hbp = cl->hbp.as<uint8_t>();
         ph.push_back(p);
-        LoopPhase m1 = gemm(cl->ap.as<uint8_t>(), d.chunk, d.w_at1l, H, H, 1, OUT_BIAS_ACT, 0);
+        LoopPhase m1 = gemm(cl->ap.as<uint8_t>(), d.chunk, d.w_at1l, H, H, 1, OUT_BIAS_ACT);
         m1.act = ACT_SILU; m1.bias = d.tvec; m1.bias_step_stride = H; m1.outp = cl->m1p.as<uint8_t>(); m1.out_rows = d.chunk; m1.out_kslice = H;
         ph.push_back(m1);
-        LoopPhase m2 = gemm(cl->m1p.as<uint8_t>(), d.chunk, d.w_at2, H, H, 1, OUT_BIAS_ACT, 0);
+        LoopPhase m2 = gemm(cl->m1p.as<uint8_t>(), d.chunk, d.w_at2, H, H, 1, OUT_BIAS_ACT);
         m2.act = ACT_NONE; m2.bias = d.b_at2; m2.outp = cl->hbp.as<uint8_t>(); m2.out_rows = S; m2.out_kslice = H; m2.out_f32 = d.h;
         m2.row_off = S - d.chunk;
         ph.push_back(m2);
@@ -1022,7 +1012,7 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         const bool self = d.is_self[l];
         uint8_t *kp = cl->kpp.as<uint8_t>() + (size_t)l * page_layer, *vp = cl->vpp.as<uint8_t>() + (size_t)l * page_layer;
         const int n_heads = d.n_q + (self ? 2 * d.n_kv : 0);
-        LoopPhase qkv = gemm(cl->hbp.as<uint8_t>(), S, d.wqkv[l], n_heads * hd, H, 1, OUT_QKV, half / 8);
+        LoopPhase qkv = gemm(cl->hbp.as<uint8_t>(), S, d.wqkv[l], n_heads * hd, H, 1, OUT_QKV);
         qkv.use_rms = l == 0 ? RMS_LOCAL : RMS_PARTS; qkv.ssq_in = cl->ssq.as<float>(); qkv.ssq_n = H / 16; qkv.half = half; qkv.qp = cl->qp.as<uint8_t>();
         qkv.kpp = kp; qkv.vpp = vp; qkv.rope = self ? d.rope_self : d.rope_cross; qkv.n_q = d.n_q; qkv.n_kvp = self ? d.n_kv : 0;
         qkv.cap = d.cap; qkv.P = d.P;
@@ -1055,19 +1045,19 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         LoopPhase cb = at;
         cb.type = PH_COMBINE; cb.outp = cl->attp.as<uint8_t>(); cb.out_rows = S; cb.out_kslice = qf / ks_o;
         ph.push_back(cb);
-        LoopPhase o = gemm(cl->attp.as<uint8_t>(), S, d.wo[l], H, qf, ks_o, OUT_RESID, 0);
+        LoopPhase o = gemm(cl->attp.as<uint8_t>(), S, d.wo[l], H, qf, ks_o, OUT_RESID);
         o.h = d.h; o.hbp = cl->hbp.as<uint8_t>(); o.ssq_out = cl->ssq.as<float>();
         ph.push_back(o);
-        LoopPhase gu = gemm(cl->hbp.as<uint8_t>(), S, d.wgu[l], 2 * d.I, H, 1, OUT_GATED, 0);
+        LoopPhase gu = gemm(cl->hbp.as<uint8_t>(), S, d.wgu[l], 2 * d.I, H, 1, OUT_GATED);
         gu.use_rms = RMS_PARTS; gu.ssq_in = cl->ssq.as<float>(); gu.ssq_n = H / 16;
         gu.act = d.act; gu.outp = cl->gp.as<uint8_t>(); gu.out_rows = S; gu.out_kslice = d.I / ks_d;
         ph.push_back(gu);
-        LoopPhase dn = gemm(cl->gp.as<uint8_t>(), S, d.wdown[l], H, d.I, ks_d, OUT_RESID, 0);
+        LoopPhase dn = gemm(cl->gp.as<uint8_t>(), S, d.wdown[l], H, d.I, ks_d, OUT_RESID);
         dn.h = d.h; dn.hbp = cl->hbp.as<uint8_t>(); dn.ssq_out = cl->ssq.as<float>();
         ph.push_back(dn);
     }
     {
-        LoopPhase hdp = gemm(cl->hbp.as<uint8_t>(), S, d.w_aout, d.A, H, 1, OUT_EULER, 0);
+        LoopPhase hdp = gemm(cl->hbp.as<uint8_t>(), S, d.w_aout, d.A, H, 1, OUT_EULER);
         hdp.use_rms = RMS_PARTS; hdp.ssq_in = cl->ssq.as<float>(); hdp.ssq_n = H / 16; hdp.bias = d.b_aout; hdp.x = d.x; hdp.dt = -1.0f / (float)d.steps;
         ph.push_back(hdp);
     }
@@ -1135,7 +1125,7 @@ int chunk_loop_run(ChunkLoop *cl, const float *state, const int32_t *pad, cudaSt
         lp.trace = cl->trace.as<unsigned long long>();
     }
     void *args[] = {&lp};
-    VB_CUDA(cudaLaunchCooperativeKernel(cl->kernel, dim3(cl->n_cta), dim3(CL_THREADS), args, CL_SMEM, stream));
+    VB_CUDA(cudaLaunchCooperativeKernel(cl->kernel, dim3(cl->n_cta), dim3(CL_BLOCK), args, CL_SMEM, stream));
     if (lp.trace) {
         const size_t n = (size_t)cl->n_phases * cl->steps;
         std::vector<unsigned long long> t(n);

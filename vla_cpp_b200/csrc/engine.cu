@@ -583,11 +583,10 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     if ((rc = vlab200_rope_table(rs, rs + (size_t)S * half, pos_base, S, hd, c.rope_base, cs))) return rc;
     if ((rc = vlab200_rope_table(rx, rx + (size_t)S * half, 0, S, hd, c.rope_base, cs))) return rc;
     VB_CUDA(cudaMemcpyAsync(e->x.p, x0, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
-    // One observation: the whole loop as one persistent kernel.  On by default where it measured faster than the
-    // launch-per-operator path (SmolVLA-shaped experts: 6.9 vs 7.6 ms per chunk; pi0-shaped: 11.8 vs 11.4 ms);
-    // VLAB200_CHUNK_LOOP=1 / =0 forces it on / off.
+    // One observation: the whole loop as one persistent kernel (10.4 vs 11.4 ms per chunk for a pi0-shaped expert, 5.9 vs
+    // 7.6 ms SmolVLA-shaped); VLAB200_CHUNK_LOOP=0 keeps the launch-per-operator path.
     const char *loop_env = std::getenv("VLAB200_CHUNK_LOOP");
-    const bool want_loop = loop_env ? loop_env[0] == '1' : c.model == 1;
+    const bool want_loop = !loop_env || loop_env[0] != '0';
     if (n_obs == 1 && c.model != 2 && want_loop) {
         if (e->loop_P != e->P) {
             vb::chunk_loop_free(e->loop);
