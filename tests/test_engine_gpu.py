@@ -3,6 +3,8 @@
 Bar: rel-L2 <= 1e-2 on the final action chunk (bf16 activations on the GPU, float32 oracle on
 the same bf16-representable weights); the displacement x_T - x_0 is checked as well so that the
 noise x_0 cannot hide an error in the predicted velocities."""
+import os
+
 import numpy as np
 import pytest
 
@@ -218,13 +220,30 @@ def test_several_engines_one_host_thread_each(oracle):
     out = torch.zeros_like(x0).pin_memory()
     torch.cuda.synchronize()
     arr = (C.c_void_p * n_eng)(*[e.h for e in engines])
-    rc = vb.lib().vlab200_engines_denoise_host(arr, n_eng, C.c_int64(n_total), C.c_void_p(state.data_ptr()),
-                                               C.c_void_p(x0.data_ptr()), C.c_void_p(out.data_ptr()), -1, None)
-    assert rc == 0, vb.lib().vlab200_last_error()
-    assert vb.device_status() == 0
-    for o in range(n_total):
-        alone = engines[0].denoise(x0[o:o + 1].cuda(), state[o:o + 1].cuda()).cpu()
-        assert torch.equal(alone[0], out[o]), o
+
+    def run_all():
+        rc = vb.lib().vlab200_engines_denoise_host(arr, n_eng, C.c_int64(n_total), C.c_void_p(state.data_ptr()),
+                                                   C.c_void_p(x0.data_ptr()), C.c_void_p(out.data_ptr()), -1, None)
+        assert rc == 0, vb.lib().vlab200_last_error()
+        assert vb.device_status() == 0
+
+    # Blocks of one observation take the persistent loop kernel, blocks of two the launch-per-operator path: the two
+    # agree to rounding, not to the bit.  With the loop kernel off every block takes the same kernels.
+    old_env = os.environ.get("VLAB200_CHUNK_LOOP")
+    os.environ["VLAB200_CHUNK_LOOP"] = "0"
+    try:
+        run_all()
+        for o in range(n_total):
+            alone = engines[0].denoise(x0[o:o + 1].cuda(), state[o:o + 1].cuda()).cpu()
+            assert torch.equal(alone[0], out[o]), o
+    finally:
+        if old_env is None:
+            del os.environ["VLAB200_CHUNK_LOOP"]
+        else:
+            os.environ["VLAB200_CHUNK_LOOP"] = old_env
+    exact = out.clone()
+    run_all()  # default: three host threads launch the cooperative loop kernel and the operator path side by side
+    assert ((out - exact).norm() / exact.norm()).item() <= 1e-2
     # sharding arithmetic of the native helper
     seen = []
     for r in range(n_eng):

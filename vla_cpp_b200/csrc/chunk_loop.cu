@@ -58,7 +58,7 @@ constexpr int CL_THREADS = 256;   // the eight computing warps
 constexpr int CL_BLOCK = 288;     // + one warp whose lane 0 feeds the weight ring
 constexpr int CL_STAGES = 3;
 constexpr int CL_MAX_KSLICE = 1024;                               // columns of one K slice
-constexpr int CL_STAGE_BYTES = 64 * (256 * 2 + 16);                // 8 NG padded weight rows of 2048 / NG columns: NG = 8 is the largest
+constexpr int CL_STAGE_BYTES = 16 * (CL_MAX_KSLICE * 2 + 16);     // 16 padded weight rows of at most 1024 columns
 constexpr int CL_DESC_BYTES = 320;                                // one phase descriptor slot (two of them: this phase, the next)
 constexpr int CL_DESC_OFF = 1536;
 constexpr int CL_WTAB_OFF = 2304;                                 // weight cursor table: one 32-byte entry per GEMM phase of a step
@@ -187,12 +187,12 @@ struct Smem {
 __device__ __forceinline__ Smem get_smem() {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem sm;
-    sm.full = reinterpret_cast<uint64_t *>(smem_raw);
-    sm.a_full = sm.full + CL_STAGES;
-    sm.empty = sm.a_full + 1;
+    sm.full = reinterpret_cast<uint64_t *>(smem_raw);          // [CL_STAGES]
+    sm.a_full = sm.full + CL_STAGES;                          // [2]
+    sm.empty = sm.a_full + 2;                                 // [CL_STAGES]
     sm.done = sm.empty + CL_STAGES;
-    sm.abort_flag = reinterpret_cast<volatile int *>(smem_raw + 64);
-    sm.n_wtab = *reinterpret_cast<const int *>(smem_raw + 72);
+    sm.abort_flag = reinterpret_cast<volatile int *>(smem_raw + 120);
+    sm.n_wtab = *reinterpret_cast<const int *>(smem_raw + 124);
     sm.rms = reinterpret_cast<float *>(smem_raw + 128);
     sm.red_max = reinterpret_cast<float *>(smem_raw + 512);
     sm.red_sum = reinterpret_cast<float *>(smem_raw + 1024);
@@ -254,7 +254,7 @@ __device__ __noinline__ void feeder_loop(const LoopParams &lp) {
                 }
             }
         }
-    *reinterpret_cast<volatile unsigned *>(reinterpret_cast<uint8_t *>(sm.full) + 76) = issued;
+    *reinterpret_cast<volatile unsigned *>(reinterpret_cast<uint8_t *>(sm.full) + 384) = issued;
     mbar_arrive(sm.done);
 }
 
@@ -375,7 +375,7 @@ __device__ __forceinline__ void gemm_epilogue(const LoopPhase &pg, const Smem &s
 // A unit = NG groups of 8 output columns; its weights arrive as K chunks of 2048 / NG columns (one ring stage each), A as
 // K slices of at most 1024 columns; the accumulators live in registers across all chunks and slices of the unit.
 template <int NG>
-__device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &lp, int step, unsigned &cons, unsigned &a_cnt) {
+__device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &lp, int step, unsigned &cons, unsigned &a_cnt_ref) {
     const Smem sm = get_smem();
     const WaitCtx wc{sm.abort_flag, lp.status};
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -390,9 +390,10 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
     const float eps = pg.eps;
     const int kslice = K / kslices, cps = kslice / kchunk;  // chunks per A slice
     const uint32_t astride = (uint32_t)kslice * 2u + 16u, wstride = (uint32_t)kchunk * 2u + 16u;
-    uint8_t *As = sm.arena;
-    float *sc = reinterpret_cast<float *>(sm.arena + (size_t)M * astride);  // [4 K quarters][M][CL_SC_LD]
-    const uint32_t as_addr = smem_u32(As);
+    const uint32_t slot_bytes = kslices > 1 ? (uint32_t)M * astride : 0u;  // two A buffers when A comes in slices
+    float *sc = reinterpret_cast<float *>(sm.arena + (size_t)(kslices > 1 ? 2 : 1) * M * astride);  // [4 K quarters][M][CL_SC_LD]
+    const uint32_t as_addr = smem_u32(sm.arena);
+    unsigned a_cnt = a_cnt_ref, a_iss = a_cnt_ref;  // A tiles consumed / issued since the launch: barrier and buffer alternate with them
     const int nk = kchunk >> 4, ks0 = kq * nk / 4, ks1 = (kq + 1) * nk / 4;
     // ldmatrix lane addressing
     const int mi = lane >> 3, lr = lane & 7;
@@ -407,16 +408,24 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
     const bool mt_ok[2] = {(2 * mh) * 16 < M, (2 * mh + 1) * 16 < M};
     const int g = lane >> 2, q2 = (lane & 3) * 2;
     const int erow = tid >> 2, ec4 = (tid & 3) * 4;
-    int cur_slice = -1;
     float acc[2][NG][4];
+    uint32_t a_slot = 0;  // byte offset of the A buffer in use
     for (int id = id0; id < id1; ++id) {
         const int u = id / n_chunks, c = id - u * n_chunks, slice = c / cps, cs = c - slice * cps;
-        if (slice != cur_slice) {
-            cons_sync();  // the arena is free: earlier readers are done
+        if (cs == 0 && (kslices > 1 || id == id0)) {  // an unsliced A serves every unit of the phase
+            cons_sync();  // every warp is done with the slice before: the buffer that is filled next is free
             if (tid == 0) {
-                mbar_expect_tx(sm.a_full, (uint32_t)M * astride);
-                bulk_g2s(As, Ap + (size_t)slice * M * astride, (uint32_t)M * astride, sm.a_full);
+                if (slice == 0) {
+                    mbar_expect_tx(&sm.a_full[a_iss & 1u], (uint32_t)M * astride);
+                    bulk_g2s(sm.arena + (a_iss & 1u) * slot_bytes, Ap, (uint32_t)M * astride, &sm.a_full[a_iss & 1u]);
+                }
+                if (slice + 1 < kslices) {  // the next slice loads while this one is multiplied
+                    const unsigned nx = a_iss + (slice == 0 ? 1u : 0u);
+                    mbar_expect_tx(&sm.a_full[nx & 1u], (uint32_t)M * astride);
+                    bulk_g2s(sm.arena + (nx & 1u) * slot_bytes, Ap + (size_t)(slice + 1) * M * astride, (uint32_t)M * astride, &sm.a_full[nx & 1u]);
+                }
             }
+            a_iss += (slice == 0 ? 1u : 0u) + (slice + 1 < kslices ? 1u : 0u);
             if (use_rms == RMS_PARTS && id == id0) {  // rms factors from the producer's partial sums, fixed order
                 const int r = tid >> 2, q = tid & 3, n = (int)pg.ssq_n;
                 float part[16];
@@ -429,8 +438,10 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
                 ss += __shfl_xor_sync(0xffffffffu, ss, 2);
                 if (q == 0 && r < M) sm.rms[r] = rsqrtf(ss / (float)K + eps);
             }
-            mbar_wait(sm.a_full, a_cnt & 1u, wc, CL_DEV_TIMEOUT);
+            mbar_wait(&sm.a_full[a_cnt & 1u], (a_cnt >> 1) & 1u, wc, CL_DEV_TIMEOUT);
+            a_slot = (a_cnt & 1u) * slot_bytes;
             ++a_cnt;
+            const uint8_t *As = sm.arena + a_slot;
             if (use_rms == RMS_LOCAL) {  // four threads per row, interleaved 16-byte chunks
                 const int r = tid >> 2, q = tid & 3;
                 float s0 = 0.0f, s1 = 0.0f;
@@ -452,7 +463,6 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
                 ss += __shfl_xor_sync(0xffffffffu, ss, 2);
                 if (q == 0 && r < M) sm.rms[r] = rsqrtf(ss / (float)K + eps);
             }
-            cur_slice = slice;
         }
         const unsigned stage = cons % CL_STAGES;
         mbar_wait(&sm.full[stage], (cons / CL_STAGES) & 1u, wc, CL_DEV_TIMEOUT);
@@ -465,7 +475,7 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
         }
-        const uint32_t a_k = (uint32_t)cs * (uint32_t)kchunk * 2u;
+        const uint32_t a_k = a_slot + (uint32_t)cs * (uint32_t)kchunk * 2u;
 #pragma unroll 2
         for (int ks = ks0; ks < ks1; ++ks) {
             uint32_t a[2][4];
@@ -507,6 +517,7 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
             gemm_epilogue(pg, sm, sc, u * (NG / 2) + blk, step, M, N, half, out_mode, use_rms, act, erow, ec4);
         }
     }
+    a_cnt_ref = a_cnt;
 }
 
 // ----------------------------------------------------------------------------------------------- EMBED
@@ -583,16 +594,17 @@ __device__ __noinline__ void att_phase(const LoopPhase &pg, const LoopParams &lp
         const int row0 = rt * 32, nrows = min(32, R - row0);
         cons_sync();  // the arena is free
         if (tid == 0) {
-            mbar_expect_tx(sm.a_full, (uint32_t)(nrows + 2 * nkeys) * SQ);
-            bulk_g2s(Qs, pg.qp + ((size_t)kvh * gq * S + row0) * SQ, (uint32_t)nrows * SQ, sm.a_full);
-            bulk_g2s(Ks, pg.kpp + ((size_t)kvh * cap + key0) * SQ, (uint32_t)nkeys * SQ, sm.a_full);
-            bulk_g2s(Vs, pg.vpp + ((size_t)kvh * cap + key0) * SQ, (uint32_t)nkeys * SQ, sm.a_full);
+            uint64_t *bar = &sm.a_full[a_cnt & 1u];
+            mbar_expect_tx(bar, (uint32_t)(nrows + 2 * nkeys) * SQ);
+            bulk_g2s(Qs, pg.qp + ((size_t)kvh * gq * S + row0) * SQ, (uint32_t)nrows * SQ, bar);
+            bulk_g2s(Ks, pg.kpp + ((size_t)kvh * cap + key0) * SQ, (uint32_t)nkeys * SQ, bar);
+            bulk_g2s(Vs, pg.vpp + ((size_t)kvh * cap + key0) * SQ, (uint32_t)nkeys * SQ, bar);
         }
         for (int i = tid; i < (ks16 - nkeys) * (HD / 8); i += CL_THREADS) {
             const int r = nkeys + i / (HD / 8), c = i % (HD / 8);
             *reinterpret_cast<uint4 *>(Vs + (size_t)r * SQ + c * 16) = make_uint4(0, 0, 0, 0);
         }
-        mbar_wait(sm.a_full, a_cnt & 1u, wc, CL_DEV_TIMEOUT);
+        mbar_wait(&sm.a_full[a_cnt & 1u], (a_cnt >> 1) & 1u, wc, CL_DEV_TIMEOUT);
         ++a_cnt;
         cons_sync();
         // ---- S = Q K^T for this warp's 16 rows and its share of the 8-key groups
@@ -800,7 +812,7 @@ __device__ __noinline__ void pages_prologue(const LoopParams &lp) {
 template <int HD>
 __global__ void __launch_bounds__(CL_BLOCK, 1) chunk_loop_kernel(const __grid_constant__ LoopParams lp) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    if (threadIdx.x == 0) *reinterpret_cast<int *>(smem_raw + 72) = lp.n_wtab;
+    if (threadIdx.x == 0) *reinterpret_cast<int *>(smem_raw + 124) = lp.n_wtab;
     __syncthreads();
     const Smem sm = get_smem();
     WEntry *wtab = reinterpret_cast<WEntry *>(smem_raw + CL_WTAB_OFF);
@@ -809,7 +821,8 @@ __global__ void __launch_bounds__(CL_BLOCK, 1) chunk_loop_kernel(const __grid_co
             mbar_init(&sm.full[i], 1);
             mbar_init(&sm.empty[i], CL_THREADS / 32);
         }
-        mbar_init(sm.a_full, 1);
+        mbar_init(&sm.a_full[0], 1);
+        mbar_init(&sm.a_full[1], 1);
         mbar_init(sm.done, 1);
         *sm.abort_flag = 0;
         fence_barrier_init();
@@ -864,7 +877,7 @@ __global__ void __launch_bounds__(CL_BLOCK, 1) chunk_loop_kernel(const __grid_co
     // Weight chunks still on their way must land before the CTA gives its shared memory back (only after a failure are
     // there any: the feeder stops with the computation).
     if (threadIdx.x == 0 && mbar_wait(sm.done, 0u, wc, CL_DEV_TIMEOUT)) {
-        const unsigned issued = *reinterpret_cast<volatile unsigned *>(smem_raw + 76);
+        const unsigned issued = *reinterpret_cast<volatile unsigned *>(smem_raw + 384);
         for (unsigned i = cons; i < issued; ++i) mbar_wait(&sm.full[i % CL_STAGES], (i / CL_STAGES) & 1u, wc, CL_DEV_TIMEOUT);
     }
     cons_sync();
@@ -894,14 +907,16 @@ struct ChunkLoop {
 
 namespace {
 
-// K slices of a projection: the fewest whose slice of A (all M rows) fits the arena beside the scratch tile.  The slices of
-// a sub-unit run back to back on one CTA and accumulate in registers.
+// K slices of a projection's A operand: one when all of K (<= 1024 columns) fits the arena beside the scratch tile, else the
+// fewest of at most 512 columns such that TWO of them fit (they alternate: the next slice loads while this one is
+// multiplied).  The slices of a unit run back to back on one CTA and accumulate in registers.
 int choose_kslices(int K, int M) {
-    for (int ks = 1; ks <= 64; ++ks) {
+    if (K <= CL_MAX_KSLICE && K % 16 == 0 && (size_t)M * (K * 2 + 16) + (size_t)4 * M * CL_SC_ROW <= (size_t)CL_ARENA) return 1;
+    for (int ks = 2; ks <= 64; ++ks) {
         if (K % ks) continue;
         const int kslice = K / ks;
-        if (kslice % 16 || kslice > CL_MAX_KSLICE) continue;
-        if ((size_t)M * (kslice * 2 + 16) + (size_t)4 * M * CL_SC_ROW > (size_t)CL_ARENA) continue;
+        if (kslice % 16 || kslice > 512) continue;
+        if ((size_t)2 * M * (kslice * 2 + 16) + (size_t)4 * M * CL_SC_ROW > (size_t)CL_ARENA) continue;
         return ks;
     }
     return 0;
@@ -909,7 +924,7 @@ int choose_kslices(int K, int M) {
 
 // columns per weight chunk of a unit of `ng` groups: the largest divisor of the A slice that is a multiple of 16 and fits a ring stage
 int pick_kchunk(int kslice, int ng) {
-    for (int kc = std::min(kslice, 2048 / ng); kc >= 16; --kc)
+    for (int kc = std::min(kslice, CL_MAX_KSLICE); kc >= 16; --kc)
         if (kslice % kc == 0 && kc % 16 == 0 && (size_t)ng * 8 * (kc * 2 + 16) <= (size_t)CL_STAGE_BYTES) return kc;
     return 0;
 }
