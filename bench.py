@@ -943,7 +943,9 @@ def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
         "scaling": "weak" if args.pi0_obs else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": policy_config_dict(workload, n_obs, n_global, world), "clocks": clocks,
         # per Euler step: 2 embedding kernels + 2 GEMMs, 5 kernels per layer (6 on the few-row path), head + Euler
-        "gpu_launches": (c["steps"] * (4 + c["n_layers"] * (6 if few else 5) + 2) + 3) * args.steps,
+        # (one observation: two rotation tables + the persistent loop kernel)
+        "gpu_launches": (3 if n_obs == 1 and os.environ.get("VLAB200_CHUNK_LOOP") != "0"
+                         else c["steps"] * (4 + c["n_layers"] * (6 if few else 5) + 2) + 3) * args.steps,
         "roofline": {"kernel": "dense_gemm_pair_kernel (fused RMSNorm + gate/up + activation, the loop's largest "
                                "share: M x 2*inter x H per layer-step)",
                      "bound": "tensor", "achieved": gu_tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
@@ -970,12 +972,23 @@ def small_batch_latency(torch, vb, dev, workload):
                                           + 3 * c["H"] * c["inter"])
     out = {}
     for b in (1, 64):
-        r = measure_pi0(torch, vb, dev, b, 10 if b == 1 else 5, 3, 7 + b, allow_graph=(b == 1), policy=workload)
-        out[b] = r
+        out[b] = measure_pi0(torch, vb, dev, b, 10 if b == 1 else 5, 3, 7 + b, policy=workload)
+    # one observation again on the launch-per-operator path (the persistent loop kernel off), also replayed as a CUDA graph
+    old_env = os.environ.get("VLAB200_CHUNK_LOOP")
+    os.environ["VLAB200_CHUNK_LOOP"] = "0"
+    try:
+        ops = measure_pi0(torch, vb, dev, 1, 10, 3, 8, allow_graph=True, policy=workload)
+    finally:
+        if old_env is None:
+            del os.environ["VLAB200_CHUNK_LOOP"]
+        else:
+            os.environ["VLAB200_CHUNK_LOOP"] = old_env
     peaks = load_peaks()
-    best1 = min(v for v in (out[1]["p50_ms"], out[1]["graph_ms"]) if v)
-    return {"p50_chunk_latency_ms_batch1": out[1]["p50_ms"], "p50_chunk_latency_ms_batch1_cuda_graph": out[1]["graph_ms"],
-            "batch1_weight_stream_frac": weight_bytes * c["steps"] / (best1 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+    return {"p50_chunk_latency_ms_batch1": out[1]["p50_ms"],
+            "batch1_path": "persistent loop kernel (one cooperative launch per chunk)" if old_env != "0" else "launch per operator",
+            "p50_chunk_latency_ms_batch1_operator_path": ops["p50_ms"],
+            "p50_chunk_latency_ms_batch1_operator_path_cuda_graph": ops["graph_ms"],
+            "batch1_weight_stream_frac": weight_bytes * c["steps"] / (out[1]["p50_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "batch1_e2e_ms": out[1]["e2e_ms"],
             "p50_step_latency_ms_batch64": out[64]["p50_ms"], "chunks_per_s_batch64": 64 / (out[64]["p50_ms"] * 1e-3),
             "batch64_e2e_ms": out[64]["e2e_ms"]}
@@ -1209,7 +1222,8 @@ def oracle_predict_seconds(orc, d, arch, n_views):
 def predict_launches(d, arch):
     """Kernels of one request, counted from the host code: tower (patchify, stream init, patch GEMM; 8 per layer;
     post-LayerNorm, connector, pi0's scale), prefix embeddings, prefill (tables, 2 per layer for q|k|v + rotation, 4 more
-    on every layer but the last, 4 for the K/V projection of a cross-attention layer), denoise loop (few-row path)."""
+    on every layer but the last, 4 for the K/V projection of a cross-attention layer), denoise loop (one persistent kernel;
+    pi0.5 and VLAB200_CHUNK_LOOP=0: the few-row path, a launch per operator)."""
     L = d["n_layers"]
     every = d.get("self_attn_every_n_layers", 0) if arch == "smolvla" else 0
     cross = sum(1 for i in range(L) if every > 1 and i % every != 0)
@@ -1217,6 +1231,8 @@ def predict_launches(d, arch):
     embed = 3 if arch == "smolvla" else 2
     prefill = 2 + 2 * L + 4 * (L - 1) + 4 * cross
     denoise = d["num_steps"] * ((3 if arch == "smolvla" else 4) + L * 6 + 2) + 2  # pi0: + the state-token kernel; 2 RoPE tables
+    if arch != "pi05" and os.environ.get("VLAB200_CHUNK_LOOP") != "0":
+        denoise = 3  # one observation: two rotation tables + the persistent loop kernel
     return tower + embed + prefill + denoise
 
 
