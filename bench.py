@@ -960,16 +960,37 @@ def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
                 "h2d_bytes_per_step": n_global * (c["chunk"] * 32 + 32) * 4, "d2h_bytes_per_step": n_global * c["chunk"] * 32 * 4,
                 "ms_per_step": e2e_ms},
     }
+    if n_obs == 1 and c["model"] != 2 and os.environ.get("VLAB200_CHUNK_LOOP") != "0":
+        # one observation runs as ONE persistent kernel: its roofline is the stream of the expert's weights, once per Euler step
+        wbytes = expert_weight_bytes(c) * c["steps"]
+        ms = total_ms / args.steps
+        gbs = wbytes / (ms * 1e-3) / 1e9
+        line["stages_note"] = "stage records are the launch-per-operator kernels (vlab200_engine_run_stage), not what this run timed"
+        line["roofline"] = {"kernel": "chunk_loop_kernel (whole Euler loop of one observation, one cooperative launch per chunk)",
+                            "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                            "peak_kind": f"of {peaks['kind']}",
+                            # ncu: 2,010 MB read + 15.7 MB written per launch for the SmolVLA-shaped expert (profiles/chunk_loop_smolvla_b1.md)
+                            "traffic": 2026.1e6 if workload == "smolvla" else None,
+                            "us_per_launch": ms * 1e3, "algorithmic_bytes_per_launch": wbytes}
     del eng, x0, state
     torch.cuda.empty_cache()
     return line
 
 
+def expert_weight_bytes(c):
+    """bf16 bytes of the expert's layer weights, streamed once per Euler step (cross-attention layers project q only)."""
+    qf, kvf = c["n_q"] * c["head_dim"], c["n_kv"] * c["head_dim"]
+    total = 0
+    for l in range(c["n_layers"]):
+        cross = c["model"] == 1 and c.get("self_every", 1) > 1 and l % c["self_every"] != 0
+        total += c["H"] * (qf + (0 if cross else 2 * kvf)) + qf * c["H"] + 3 * c["H"] * c["inter"]
+    return 2.0 * total
+
+
 def small_batch_latency(torch, vb, dev, workload):
     """configs[2]: chunk latency at batch 1 and 64 (one GPU)."""
     c, P = POLICIES[workload]
-    weight_bytes = 2.0 * c["n_layers"] * (c["H"] * (c["n_q"] + 2 * c["n_kv"]) * c["head_dim"] + c["n_q"] * c["head_dim"] * c["H"]
-                                          + 3 * c["H"] * c["inter"])
+    weight_bytes = expert_weight_bytes(c)
     out = {}
     for b in (1, 64):
         out[b] = measure_pi0(torch, vb, dev, b, 10 if b == 1 else 5, 3, 7 + b, policy=workload)
