@@ -299,7 +299,7 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_
     e1.record()
     sync()
     graph_ms = None
-    if n_obs <= 8 and allow_graph:
+    if n_obs <= 8 and allow_graph and not (n_obs == 1 and os.environ.get("VLAB200_CHUNK_LOOP") != "0"):
         # small batches are launch- and latency-bound (943 launches per chunk): the same loop replayed as one CUDA graph
         try:
             side = torch.cuda.Stream()
@@ -960,7 +960,7 @@ def measure_policy(torch, vb, dist, dev, args, rank, world, barrier):
                 "h2d_bytes_per_step": n_global * (c["chunk"] * 32 + 32) * 4, "d2h_bytes_per_step": n_global * c["chunk"] * 32 * 4,
                 "ms_per_step": e2e_ms},
     }
-    if n_obs == 1 and c["model"] != 2 and os.environ.get("VLAB200_CHUNK_LOOP") != "0":
+    if n_obs == 1 and os.environ.get("VLAB200_CHUNK_LOOP") != "0":
         # one observation runs as ONE persistent kernel: its roofline is the stream of the expert's weights, once per Euler step
         wbytes = expert_weight_bytes(c) * c["steps"]
         ms = total_ms / args.steps
@@ -1151,16 +1151,15 @@ def measure_pi05_loop(torch, vb, dev, args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": policy_config_dict("pi05", n_obs, n_obs, 1), "clocks": clocks,
             # per Euler step: embedding, 7 kernels per layer (+1 where a GEMM is cut along M), norm + head + Euler
-            "gpu_launches": (c["steps"] * (1 + c["n_layers"] * 7 + 3) + 3) * args.steps,
+            "gpu_launches": (3 if n_obs == 1 and os.environ.get("VLAB200_CHUNK_LOOP") != "0"
+                             else c["steps"] * (1 + c["n_layers"] * 7 + 3) + 3) * args.steps,
             "e2e": {"value": n_obs / (r["e2e_ms"] * 1e-3), "unit": "chunks/s", "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": r["d2h"]},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": tf / peaks["bf16_tflops_sustained"], "traffic": None,
                          "note": "whole loop (expert GEMMs + attention, algorithmic FLOPs) over its device time", "peak_source": peaks["kind"]}}
     if n_obs > 1:
-        b1 = measure_pi0(torch, vb, dev, 1, 10, 3, 8, allow_graph=True, policy="pi05")
-        line["p50_chunk_latency_ms_batch1"] = b1["p50_ms"]
-        line["graph_ms_batch1"] = b1["graph_ms"]
+        line.update({k: v for k, v in small_batch_latency(torch, vb, dev, "pi05").items() if "batch1" in k})
     return line
 
 
@@ -1244,7 +1243,7 @@ def predict_launches(d, arch):
     """Kernels of one request, counted from the host code: tower (patchify, stream init, patch GEMM; 8 per layer;
     post-LayerNorm, connector, pi0's scale), prefix embeddings, prefill (tables, 2 per layer for q|k|v + rotation, 4 more
     on every layer but the last, 4 for the K/V projection of a cross-attention layer), denoise loop (one persistent kernel;
-    pi0.5 and VLAB200_CHUNK_LOOP=0: the few-row path, a launch per operator)."""
+    VLAB200_CHUNK_LOOP=0: the few-row path, a launch per operator)."""
     L = d["n_layers"]
     every = d.get("self_attn_every_n_layers", 0) if arch == "smolvla" else 0
     cross = sum(1 for i in range(L) if every > 1 and i % every != 0)
@@ -1252,7 +1251,7 @@ def predict_launches(d, arch):
     embed = 3 if arch == "smolvla" else 2
     prefill = 2 + 2 * L + 4 * (L - 1) + 4 * cross
     denoise = d["num_steps"] * ((3 if arch == "smolvla" else 4) + L * 6 + 2) + 2  # pi0: + the state-token kernel; 2 RoPE tables
-    if arch != "pi05" and os.environ.get("VLAB200_CHUNK_LOOP") != "0":
+    if os.environ.get("VLAB200_CHUNK_LOOP") != "0":
         denoise = 3  # one observation: two rotation tables + the persistent loop kernel
     return tower + embed + prefill + denoise
 

@@ -234,7 +234,7 @@ VLAB200_API int32_t vlab200_engine_set_prefix(vlab200_engine *e, int32_t layer, 
  * state float32 [n_obs][state_dim] (pi0; normalised), pos_base = RoPE position of suffix token 0
  * on self-attention layers (< 0: prefix_len), pad_ranges optional [n_obs][2] masked prefix columns.
  * Replaces the unrolled suffix sub-graph of src/models/pi0.cpp:568-588 / smolvla.cpp:1393-1418.
- * A call with ONE observation (models 0 and 1) runs the whole loop as one persistent cooperative kernel (the reference's
+ * A call with ONE observation runs the whole loop as one persistent cooperative kernel (the reference's
  * answer to per-operator cost is one cached graph per predict, src/scratch_ctx.h:34-141); its first use builds a padded copy
  * of the expert's weights on the engine's device.  Environment VLAB200_CHUNK_LOOP=0 keeps a launch per operator.  The two
  * paths round activations to bf16 at different points: results agree to ~3e-3 rel-L2, each is reproducible bit for bit. */

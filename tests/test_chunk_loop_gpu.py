@@ -28,7 +28,7 @@ def _with_loop(flag, fn):
             os.environ["VLAB200_CHUNK_LOOP"] = old
 
 
-@pytest.mark.parametrize("policy", ["pi0", "smolvla"])
+@pytest.mark.parametrize("policy", ["pi0", "smolvla", "pi05"])
 def test_loop_kernel_matches_operator_path(policy):
     torch = require_cuda()
     import vla_cpp_b200 as vb

@@ -59,7 +59,7 @@ constexpr int CL_BLOCK = 288;     // + one warp whose lane 0 feeds the weight ri
 constexpr int CL_STAGES = 3;
 constexpr int CL_MAX_KSLICE = 1024;                               // columns of one K slice
 constexpr int CL_STAGE_BYTES = 16 * (CL_MAX_KSLICE * 2 + 16);     // 16 padded weight rows of at most 1024 columns
-constexpr int CL_DESC_BYTES = 320;                                // one phase descriptor slot (two of them: this phase, the next)
+constexpr int CL_DESC_BYTES = 352;                                // one phase descriptor slot (two of them: this phase, the next)
 constexpr int CL_DESC_OFF = 1536;
 constexpr int CL_WTAB_OFF = 2304;                                 // weight cursor table: one 32-byte entry per GEMM phase of a step
 constexpr int CL_WTAB_MAX = 104;
@@ -92,6 +92,10 @@ struct alignas(16) LoopPhase {
     float *ssq_out;                     // [n_sub][64]: sum of squares of the bf16 values this phase writes, per sub-unit and row (optional)
     const float *ssq_in;                // RMS_PARTS: the producer's partials, ssq_n of them per row
     long long ssq_n;
+    // pi0.5 (adaptive RMSNorm, gated residuals): per-step vectors, element stride mod_stride between steps
+    const float *colscale;              // OUT_RESID: gate on the projection before it is added
+    const float *scale_next;            // OUT_RESID / EMBED: the mirror is written as bf16(h * (1 + scale_next[col])) for the norm that reads it
+    long long mod_stride;
     uint8_t *outp;                      // padded image the phase writes (out_rows rows, slices of out_kslice columns)
     uint8_t *hbp, *qp, *kpp, *vpp;      // padded: residual mirror [S][H], q [n_q S][hd], this layer's K / V pages [n_kv cap][hd]
     const float *bias, *rope;
@@ -307,15 +311,30 @@ __device__ __forceinline__ void gemm_epilogue(const LoopPhase &pg, const Smem &s
         if (out_mode == OUT_RESID) {  // residual stream += projection; bf16 mirror; sums of squares of the mirror
             float4 *hp = reinterpret_cast<float4 *>(pg.h + (size_t)erow * N + wrow);
             float4 hv = __ldcg(hp);
+            if (pg.colscale) {
+                const float4 gt = *reinterpret_cast<const float4 *>(pg.colscale + (size_t)step * pg.mod_stride + wrow);
+                v.x *= gt.x; v.y *= gt.y; v.z *= gt.z; v.w *= gt.w;
+            }
             hv.x += v.x; hv.y += v.y; hv.z += v.z; hv.w += v.w;
             __stcg(hp, hv);
-            const uint2 pk = make_uint2(pack_bf16(hv.x, hv.y), pack_bf16(hv.z, hv.w));
-            __stcg(reinterpret_cast<uint2 *>(pg.hbp + pad_off(M, N, erow, wrow)), pk);
-            const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&pk.x));
-            const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&pk.y));
-            ssq = fmaf(f0.x, f0.x, fmaf(f0.y, f0.y, fmaf(f1.x, f1.x, f1.y * f1.y)));
+            if (pg.scale_next) {  // the adaptive norm's (1 + scale) goes into the mirror, its sums of squares come from h itself
+                const float4 sn = *reinterpret_cast<const float4 *>(pg.scale_next + (size_t)step * pg.mod_stride + wrow);
+                __stcg(reinterpret_cast<uint2 *>(pg.hbp + pad_off(M, N, erow, wrow)),
+                       make_uint2(pack_bf16(hv.x + hv.x * sn.x, hv.y + hv.y * sn.y), pack_bf16(hv.z + hv.z * sn.z, hv.w + hv.w * sn.w)));
+                ssq = fmaf(hv.x, hv.x, fmaf(hv.y, hv.y, fmaf(hv.z, hv.z, hv.w * hv.w)));
+            } else {
+                const uint2 pk = make_uint2(pack_bf16(hv.x, hv.y), pack_bf16(hv.z, hv.w));
+                __stcg(reinterpret_cast<uint2 *>(pg.hbp + pad_off(M, N, erow, wrow)), pk);
+                const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&pk.x));
+                const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&pk.y));
+                ssq = fmaf(f0.x, f0.x, fmaf(f0.y, f0.y, fmaf(f1.x, f1.x, f1.y * f1.y)));
+            }
         } else if (out_mode == OUT_GATED) {
             // interleaved weight rows: even = gate, odd = up
+            if (pg.bias) {
+                const float4 b = *reinterpret_cast<const float4 *>(pg.bias + (size_t)step * pg.bias_step_stride + wrow);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
             const float o0 = act_rt(v.x, act) * v.y, o1 = act_rt(v.z, act) * v.w;
             __stcg(reinterpret_cast<unsigned *>(pg.outp + pad_off(pg.out_rows, pg.out_kslice, erow, wrow >> 1)), pack_bf16(o0, o1));
         } else if (out_mode == OUT_QKV) {
@@ -326,6 +345,12 @@ __device__ __forceinline__ void gemm_epilogue(const LoopPhase &pg, const Smem &s
                 w.x += t.x; w.y += t.y; w.z += t.z; w.w += t.w;
             }
             w.x *= rms; w.y *= rms; w.z *= rms; w.w *= rms;
+            if (pg.bias) {
+                const float *bp = pg.bias + (size_t)step * pg.bias_step_stride;
+                const float4 b0 = *reinterpret_cast<const float4 *>(bp + r0 + ec4), b1 = *reinterpret_cast<const float4 *>(bp + r1 + ec4);
+                v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+                w.x += b1.x; w.y += b1.y; w.z += b1.z; w.w += b1.w;
+            }
             const int hd = 2 * half, head = r0 / hd, k = r0 - head * hd + ec4;
             const int n_q = pg.n_q, n_kvp = pg.n_kvp, S = pg.S;
             const uint32_t sq = (uint32_t)hd * 2u + 16u;
@@ -521,7 +546,7 @@ __device__ __noinline__ void gemm_phase(const LoopPhase &pg, const LoopParams &l
 }
 
 // ----------------------------------------------------------------------------------------------- EMBED
-__device__ __noinline__ void embed_phase(const LoopPhase &p, const LoopParams &lp) {
+__device__ __noinline__ void embed_phase(const LoopPhase &p, const LoopParams &lp, int step) {
     const Smem sm = get_smem();
     float *xs = reinterpret_cast<float *>(sm.arena);
     const int A = p.A_dim, H = p.H, chunk = p.chunk, sd = p.sd;
@@ -554,7 +579,19 @@ __device__ __noinline__ void embed_phase(const LoopPhase &p, const LoopParams &l
                     acc = fmaf(f.y, xs[r * A + k8 * 8 + 2 * e + 1], acc);
                 }
             }
-            *reinterpret_cast<__nv_bfloat16 *>(p.outp + pad_off(chunk, H, r, o)) = __float2bfloat16(acc);
+            if (!p.scale_next) {
+                *reinterpret_cast<__nv_bfloat16 *>(p.outp + pad_off(chunk, H, r, o)) = __float2bfloat16(acc);
+            } else {
+                // pi0.5: the embedding IS the residual stream (rows = action tokens); mirror with the first norm's (1 + scale),
+                // sums of squares per 32 columns (a warp holds 32 consecutive columns of one row block)
+                __stcg(p.h + (size_t)r * H + o, acc);
+                const float sn = p.scale_next[(size_t)step * p.mod_stride + o];
+                *reinterpret_cast<__nv_bfloat16 *>(p.hbp + pad_off(p.S, H, r, o)) = __float2bfloat16(acc + acc * sn);
+                float sq = acc * acc;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+                if ((threadIdx.x & 31) == 0) __stcg(p.ssq_out + (size_t)(o >> 5) * 64 + r, sq);
+            }
         }
     }
     if (sd > 0)  // pi0: the state token is row 0 of the residual stream
@@ -856,7 +893,7 @@ __global__ void __launch_bounds__(CL_BLOCK, 1) chunk_loop_kernel(const __grid_co
             case PH_GEMM:
                 gemm_phase<2>(p, lp, step, cons, a_cnt);
                 break;
-            case PH_EMBED: embed_phase(p, lp); break;
+            case PH_EMBED: embed_phase(p, lp, step); break;
             case PH_ATT:
                 att_phase<HD>(p, lp, a_cnt);
                 break;
@@ -892,6 +929,23 @@ __global__ void pad_image_kernel(const __nv_bfloat16 *__restrict__ src, uint8_t 
     }
 }
 
+// pi0.5: the adaptive norm's shift passes through the projection as a per-column constant,
+// out[s][n] = (add ? add[n] : 0) + sum_k W[n][k] shift_s[k]   (shift_s = shift + s * stride; one warp per (s, n))
+__global__ void shift_bias_kernel(const __nv_bfloat16 *__restrict__ W, const float *__restrict__ shift, size_t stride, const float *__restrict__ add,
+                                  float *__restrict__ out, int steps, int N, int K) {
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (size_t)steps * N) return;
+    const int s = (int)(warp / N), n = (int)(warp % N);
+    const __nv_bfloat16 *wr = W + (size_t)n * K;
+    const float *sh = shift + (size_t)s * stride;
+    float acc = 0.0f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(wr[k]), sh[k], acc);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) out[warp] = acc + (add ? add[n] : 0.0f);
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------ host
@@ -900,6 +954,7 @@ struct ChunkLoop {
     DevBuf phases, wtab, counter, ws_o, ws_ml, trace;
     DevBuf hbp, ap, m1p, attp, gp, qp, kpp, vpp;  // padded activations and pages
     DevBuf ssq;                                    // [H / 16][64] partial sums of squares of the residual mirror
+    std::vector<DevBuf> cvec;                      // pi0.5: the shift terms of every norm, [steps][N] each
     std::vector<DevBuf> wp;                        // padded weights
     int n_phases = 0, steps = 0, n_cta = 0;
     LoopParams lp{};
@@ -938,7 +993,7 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
     const int n_sm = sm_count();
     if (n_sm <= 0) return VLAB200_ERR_CUDA;
     const int hd = d.hd, half = hd / 2, qf = d.n_q * hd, H = d.H, S = d.S;
-    if (d.model != 0 && d.model != 1) return VLAB200_ERR_UNSUPPORTED;
+    if (d.model < 0 || d.model > 2 || (d.model == 2 && (!d.mods || H % 32))) return VLAB200_ERR_UNSUPPORTED;
     if (hd != 64 && hd != 128 && hd != 256) return VLAB200_ERR_UNSUPPORTED;
     if (S > 64 || H % 16 || H > CL_MAX_KSLICE || d.A % 16 || (2 * d.I) % 16 || qf % 16 || d.I % 16) return VLAB200_ERR_UNSUPPORTED;
     if ((size_t)S * (H * 2 + 16) + (size_t)4 * S * CL_SC_ROW > (size_t)CL_ARENA) return VLAB200_ERR_UNSUPPORTED;
@@ -1007,6 +1062,25 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         return p;
     };
     size_t ws_units = 0;
+    const bool ada = d.model == 2;
+    const size_t mod_step = (size_t)3 * H, mod_block = (size_t)d.steps * mod_step;  // one norm's vectors for every step
+    auto mod_in = [&](int l) { return d.mods + (size_t)(2 * l) * mod_block; };
+    auto mod_post = [&](int l) { return d.mods + (size_t)(2 * l + 1) * mod_block; };
+    const float *mod_final = ada ? d.mods + (size_t)(2 * d.L) * mod_block : nullptr;
+    // W shift (+ bias) of a norm whose output feeds `w_dense` [N][H]
+    auto shift_bias = [&](const void *w_dense, int N, const float *mod, const float *add, const float **out_vec) -> int {
+        cl->cvec.emplace_back();
+        DevBuf &b = cl->cvec.back();
+        int r = b.alloc((size_t)d.steps * N * 4);
+        if (r) return r;
+        const size_t warps = (size_t)d.steps * N;
+        shift_bias_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256>>>(static_cast<const __nv_bfloat16 *>(w_dense), mod + H, mod_step, add,
+                                                                          b.as<float>(), d.steps, N, H);
+        VB_CUDA(cudaGetLastError());
+        *out_vec = b.as<float>();
+        return VLAB200_OK;
+    };
+    cl->cvec.reserve((size_t)d.L * 2 + 2);
     // ---- suffix embedding
     {
         LoopPhase p{};
@@ -1014,28 +1088,38 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         p.outp = cl->ap.as<uint8_t>(); p.chunk = d.chunk; p.A_dim = d.A; p.H = H; p.S = S;
         p.sd = d.model == 0 ? d.sd : 0; p.w2 = static_cast<const __nv_bfloat16 *>(d.w_sp); p.b2 = d.b_sp; p.h = d.h;
         p.hbp = cl->hbp.as<uint8_t>();
+        if (ada) {  // the embedding is the residual stream; its mirror carries the first norm's (1 + scale)
+            p.scale_next = mod_in(0); p.mod_stride = (long long)mod_step; p.ssq_out = cl->ssq.as<float>();
+        }
         ph.push_back(p);
-        LoopPhase m1 = gemm(cl->ap.as<uint8_t>(), d.chunk, d.w_at1l, H, H, 1, OUT_BIAS_ACT);
-        m1.act = ACT_SILU; m1.bias = d.tvec; m1.bias_step_stride = H; m1.outp = cl->m1p.as<uint8_t>(); m1.out_rows = d.chunk; m1.out_kslice = H;
-        ph.push_back(m1);
-        LoopPhase m2 = gemm(cl->m1p.as<uint8_t>(), d.chunk, d.w_at2, H, H, 1, OUT_BIAS_ACT);
-        m2.act = ACT_NONE; m2.bias = d.b_at2; m2.outp = cl->hbp.as<uint8_t>(); m2.out_rows = S; m2.out_kslice = H; m2.out_f32 = d.h;
-        m2.row_off = S - d.chunk;
-        ph.push_back(m2);
+        if (!ada) {
+            LoopPhase m1 = gemm(cl->ap.as<uint8_t>(), d.chunk, d.w_at1l, H, H, 1, OUT_BIAS_ACT);
+            m1.act = ACT_SILU; m1.bias = d.tvec; m1.bias_step_stride = H; m1.outp = cl->m1p.as<uint8_t>(); m1.out_rows = d.chunk; m1.out_kslice = H;
+            ph.push_back(m1);
+            LoopPhase m2 = gemm(cl->m1p.as<uint8_t>(), d.chunk, d.w_at2, H, H, 1, OUT_BIAS_ACT);
+            m2.act = ACT_NONE; m2.bias = d.b_at2; m2.outp = cl->hbp.as<uint8_t>(); m2.out_rows = S; m2.out_kslice = H; m2.out_f32 = d.h;
+            m2.row_off = S - d.chunk;
+            ph.push_back(m2);
+        }
     }
     for (int l = 0; l < d.L; ++l) {
         const bool self = d.is_self[l];
         uint8_t *kp = cl->kpp.as<uint8_t>() + (size_t)l * page_layer, *vp = cl->vpp.as<uint8_t>() + (size_t)l * page_layer;
         const int n_heads = d.n_q + (self ? 2 * d.n_kv : 0);
         LoopPhase qkv = gemm(cl->hbp.as<uint8_t>(), S, d.wqkv[l], n_heads * hd, H, 1, OUT_QKV);
-        qkv.use_rms = l == 0 ? RMS_LOCAL : RMS_PARTS; qkv.ssq_in = cl->ssq.as<float>(); qkv.ssq_n = H / 16; qkv.half = half; qkv.qp = cl->qp.as<uint8_t>();
+        qkv.use_rms = (l == 0 && !ada) ? RMS_LOCAL : RMS_PARTS; qkv.ssq_in = cl->ssq.as<float>(); qkv.ssq_n = (l == 0 && ada) ? H / 32 : H / 16;
+        qkv.half = half; qkv.qp = cl->qp.as<uint8_t>();
+        if (ada) {
+            if ((rc = shift_bias(d.wqkv[l], n_heads * hd, mod_in(l), nullptr, &qkv.bias))) return fail(rc);
+            qkv.bias_step_stride = n_heads * hd;
+        }
         qkv.kpp = kp; qkv.vpp = vp; qkv.rope = self ? d.rope_self : d.rope_cross; qkv.n_q = d.n_q; qkv.n_kvp = self ? d.n_kv : 0;
         qkv.cap = d.cap; qkv.P = d.P;
         ph.push_back(qkv);
         LoopPhase at{};
         at.type = PH_ATT; at.hd = hd; at.qp = cl->qp.as<uint8_t>(); at.kpp = kp; at.vpp = vp; at.n_kv = d.n_kv; at.g = g;
         at.S = S; at.R = R; at.n_rt = n_rt; at.kv_len = self ? d.P + S : d.P; at.P = d.P; at.cap = d.cap; at.n_q = d.n_q;
-        at.mask_mode = self ? (d.model == 0 ? 1 : 2) : 0;
+        at.mask_mode = (self && !ada) ? (d.model == 0 ? 1 : 2) : 0;  // pi0.5: every action token sees the prefix and every action token
         at.scale_log2 = 1.4426950408889634f / std::sqrt((float)hd);
         {   // keys per slice: the fewest rounds over the CTAs, then the cheapest unit
             int best = 0;
@@ -1062,18 +1146,32 @@ int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out) {
         ph.push_back(cb);
         LoopPhase o = gemm(cl->attp.as<uint8_t>(), S, d.wo[l], H, qf, ks_o, OUT_RESID);
         o.h = d.h; o.hbp = cl->hbp.as<uint8_t>(); o.ssq_out = cl->ssq.as<float>();
+        if (ada) {
+            o.colscale = mod_in(l) + 2 * H; o.scale_next = mod_post(l); o.mod_stride = (long long)mod_step;
+        }
         ph.push_back(o);
         LoopPhase gu = gemm(cl->hbp.as<uint8_t>(), S, d.wgu[l], 2 * d.I, H, 1, OUT_GATED);
         gu.use_rms = RMS_PARTS; gu.ssq_in = cl->ssq.as<float>(); gu.ssq_n = H / 16;
         gu.act = d.act; gu.outp = cl->gp.as<uint8_t>(); gu.out_rows = S; gu.out_kslice = d.I / ks_d;
+        if (ada) {
+            if ((rc = shift_bias(d.wgu[l], 2 * d.I, mod_post(l), nullptr, &gu.bias))) return fail(rc);
+            gu.bias_step_stride = 2 * d.I;
+        }
         ph.push_back(gu);
         LoopPhase dn = gemm(cl->gp.as<uint8_t>(), S, d.wdown[l], H, d.I, ks_d, OUT_RESID);
         dn.h = d.h; dn.hbp = cl->hbp.as<uint8_t>(); dn.ssq_out = cl->ssq.as<float>();
+        if (ada) {
+            dn.colscale = mod_post(l) + 2 * H; dn.scale_next = l + 1 < d.L ? mod_in(l + 1) : mod_final; dn.mod_stride = (long long)mod_step;
+        }
         ph.push_back(dn);
     }
     {
         LoopPhase hdp = gemm(cl->hbp.as<uint8_t>(), S, d.w_aout, d.A, H, 1, OUT_EULER);
         hdp.use_rms = RMS_PARTS; hdp.ssq_in = cl->ssq.as<float>(); hdp.ssq_n = H / 16; hdp.bias = d.b_aout; hdp.x = d.x; hdp.dt = -1.0f / (float)d.steps;
+        if (ada) {
+            if ((rc = shift_bias(d.w_aout, d.A, mod_final, d.b_aout, &hdp.bias))) return fail(rc);
+            hdp.bias_step_stride = d.A;
+        }
         ph.push_back(hdp);
     }
     if (bad) return fail(VLAB200_ERR_UNSUPPORTED);

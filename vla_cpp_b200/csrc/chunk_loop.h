@@ -11,7 +11,7 @@ namespace vb {
 // float32 residual stream and x).  Arrays indexed by layer are host arrays of device pointers.  The loop keeps its own
 // bf16 activations, q and K/V pages in the padded layout its tiles are copied from, and a padded copy of every weight.
 struct ChunkLoopDesc {
-    int model;  // 0 pi0 (state token, row 0 private), 1 SmolVLA (causal suffix, cross layers)
+    int model;  // 0 pi0 (state token, row 0 private), 1 SmolVLA (causal suffix, cross layers), 2 pi0.5 (adaptive norms, no mask)
     int L, H, I, n_q, n_kv, hd, S, chunk, A, sd, steps, cap, P, act;
     float rms_eps;
     const int *is_self;
@@ -22,6 +22,8 @@ struct ChunkLoopDesc {
     size_t layer_stride;        // elements between two layers' pages
     float *h, *x;               // f32 [S][H], [chunk][A]
     const float *rope_self, *rope_cross;  // [2][S][hd/2] (cos | sin)
+    // pi0.5: float32 [L][2][steps][3H] (scale | shift | gate of the layer's two norms for every step), then [steps][3H] final
+    const float *mods;
 };
 
 struct ChunkLoop;

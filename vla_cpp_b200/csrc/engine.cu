@@ -469,7 +469,7 @@ static int engine_chunk_loop(vlab200_engine *e) {
     ChunkLoopDesc d{};
     d.model = c.model; d.L = c.n_layers; d.H = c.H; d.I = c.inter; d.n_q = c.n_q; d.n_kv = c.n_kv; d.hd = c.head_dim; d.S = e->S;
     d.chunk = c.chunk; d.A = c.action_dim; d.sd = c.state_dim; d.steps = c.steps; d.cap = e->cap; d.P = e->P;
-    d.act = c.model == 0 ? ACT_GELU_TANH : ACT_SILU; d.rms_eps = c.rms_eps;
+    d.act = c.model == 1 ? ACT_SILU : ACT_GELU_TANH; d.rms_eps = c.rms_eps;
     d.is_self = e->is_self.data();
     std::vector<const void *> wqkv(c.n_layers), wo(c.n_layers), wgu(c.n_layers), wdown(c.n_layers);
     for (int l = 0; l < c.n_layers; ++l) {
@@ -483,6 +483,7 @@ static int engine_chunk_loop(vlab200_engine *e) {
     d.layer_stride = (size_t)e->max_obs * c.n_kv * e->cap * c.head_dim;
     d.h = e->h.as<float>(); d.x = e->x.as<float>();
     d.rope_self = e->rope_self.as<float>(); d.rope_cross = e->rope_cross.as<float>();
+    d.mods = c.model == 2 ? e->mods.as<float>() : nullptr;
     return chunk_loop_create(d, &e->loop);
 }
 
@@ -587,7 +588,7 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
     // 7.6 ms SmolVLA-shaped); VLAB200_CHUNK_LOOP=0 keeps the launch-per-operator path.
     const char *loop_env = std::getenv("VLAB200_CHUNK_LOOP");
     const bool want_loop = !loop_env || loop_env[0] != '0';
-    if (n_obs == 1 && c.model != 2 && want_loop) {
+    if (n_obs == 1 && want_loop) {
         if (e->loop_P != e->P) {
             vb::chunk_loop_free(e->loop);
             e->loop = nullptr;
