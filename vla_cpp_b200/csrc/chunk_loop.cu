@@ -1238,7 +1238,12 @@ int chunk_loop_run(ChunkLoop *cl, const float *state, const int32_t *pad, cudaSt
         lp.trace = cl->trace.as<unsigned long long>();
     }
     void *args[] = {&lp};
-    VB_CUDA(cudaLaunchCooperativeKernel(cl->kernel, dim3(cl->n_cta), dim3(CL_BLOCK), args, CL_SMEM, stream));
+    const cudaError_t le = cudaLaunchCooperativeKernel(cl->kernel, dim3(cl->n_cta), dim3(CL_BLOCK), args, CL_SMEM, stream);
+    if (le == cudaErrorCooperativeLaunchTooLarge) {  // fewer SMs than the device reports are ours (a partitioned GPU): not an error of the call
+        cudaGetLastError();
+        return VLAB200_ERR_UNSUPPORTED;
+    }
+    if (le != cudaSuccess) return cuda_fail(le, "cudaLaunchCooperativeKernel");
     if (lp.trace) {
         const size_t n = (size_t)cl->n_phases * cl->steps;
         std::vector<unsigned long long> t(n);

@@ -33,7 +33,8 @@ struct ChunkLoop;
 int chunk_loop_create(const ChunkLoopDesc &d, ChunkLoop **out);
 void chunk_loop_free(ChunkLoop *cl);
 // One chunk: x (in place, [chunk][A] float32) through `steps` Euler steps.  state: [sd] float32 (pi0), pad: two int32
-// (key range hidden from every row) or nullptr.  Both are device pointers read by the kernel.
+// (key range hidden from every row) or nullptr.  Both are device pointers read by the kernel.  VLAB200_ERR_UNSUPPORTED (nothing
+// launched, x untouched) when the grid cannot be co-resident because part of the device is not available to this process.
 int chunk_loop_run(ChunkLoop *cl, const float *state, const int32_t *pad, cudaStream_t stream);
 int chunk_loop_phases(const ChunkLoop *cl);  // phases (= grid-wide barriers) per Euler step
 

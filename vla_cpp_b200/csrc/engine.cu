@@ -596,9 +596,14 @@ int32_t vlab200_engine_denoise(vlab200_engine *e, int32_t n_obs, const float *st
             if ((rc = vb::engine_chunk_loop(e)) && rc != VLAB200_ERR_UNSUPPORTED) return rc;
         }
         if (e->loop) {
-            if ((rc = vb::chunk_loop_run(e->loop, state, pad_ranges, cs))) return rc;
-            VB_CUDA(cudaMemcpyAsync(x_out, e->x.p, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
-            return VLAB200_OK;
+            rc = vb::chunk_loop_run(e->loop, state, pad_ranges, cs);
+            if (rc == VLAB200_OK) {
+                VB_CUDA(cudaMemcpyAsync(x_out, e->x.p, (size_t)Mc * A * 4, cudaMemcpyDeviceToDevice, cs));
+                return VLAB200_OK;
+            }
+            if (rc != VLAB200_ERR_UNSUPPORTED) return rc;
+            vb::chunk_loop_free(e->loop);  // the grid does not fit this process's share of the device: a launch per operator from now on
+            e->loop = nullptr;
         }
     }
     const float dt = -1.0f / (float)c.steps;
