@@ -265,6 +265,34 @@ def test_attention_streaming_kernel_large_score_spread(oracle, tiling):
     assert rel_l2(from_bf16(oracle, out)[0], ref) < TOL
 
 
+@pytest.mark.parametrize("mask_mode", [2, 0])
+def test_attention_hd64_score_spread_within_a_column_half(oracle, mask_mode):
+    """head_dim 64, 228 keys: key norms grow along the sequence (and jump in the middle of each half of the key range), so
+    later 32-key chunks beat the first chunk of their half by far more than 2^8: the single-pass kernel has to raise its
+    reference and rescale the P chunks it has already written."""
+    torch = require_cuda()
+    import vla_cpp_b200 as vb
+
+    hd, n_q, n_kv, S, P, n_obs = 64, 15, 5, 51, 177, 3
+    rng = np.random.default_rng(310 + mask_mode)
+    st = vb.KvStore(1, n_obs, n_kv, hd, P, S)
+    q = oracle.bf16_round(rng.standard_normal((n_obs, n_q, S, hd)).astype(np.float32))
+    ramp = np.linspace(0.3, 2.5, st.cap).astype(np.float32)
+    ramp[70:] *= 2.0   # inside the first half of the key range (keys 0..127)
+    ramp[200:] *= 1.6  # inside the second half
+    k = oracle.bf16_round((rng.standard_normal((n_obs, n_kv, st.cap, hd)) * ramp[None, None, :, None]).astype(np.float32))
+    v = oracle.bf16_round(rng.standard_normal((n_obs, n_kv, st.cap, hd)).astype(np.float32))
+    st.k[0].copy_(bf16_tensor(oracle, k))
+    st.v[0].copy_(bf16_tensor(oracle, v))
+    out = vb.attention(st, 0, bf16_tensor(oracle, q), S, n_q, P + S, mask_mode)
+    assert vb.device_status() == 0
+    got = from_bf16(oracle, out)
+    assert np.isfinite(got).all()
+    for b in range(n_obs):
+        ref = oracle.attention(q[b].transpose(1, 0, 2), k[b].transpose(1, 0, 2), v[b].transpose(1, 0, 2), P, mask_mode)
+        assert rel_l2(got[b], ref) < TOL
+
+
 def test_isolated_denoise_attention_two_layers_chain(oracle):
     """QKV+RoPE+append feeding attention, two layers, as the isolated-op config runs them."""
     require_cuda()

@@ -11,10 +11,12 @@
 //                 S = Q K^T (kind::f16, f32 accumulator, all keys at once), then O = P V with
 //                 A = P read from TMEM and V as an MN-major operand
 //   2 x 8 softmax warps (per region two warps per TMEM lane quarter, one per half of the key
-//                 columns): one thread per (row, column half); two passes over its columns
-//                 straight out of TMEM, exp2 with the scale folded in, masks applied as selects;
-//                 the halves exchange row maximum and row sum through shared memory; P (bf16)
-//                 overwrites consumed S columns; epilogue O / rowsum -> bf16
+//                 columns): one thread per (row, column half), straight out of TMEM, exp2 with the
+//                 scale folded in, masks applied as selects; P (bf16) overwrites consumed S columns.
+//                 More than 128 keys: ONE pass per half with a lazily raised reference, an O
+//                 accumulator per half, the halves merged in the epilogue.  Fewer keys: two passes
+//                 (maximum, then exp2), the halves exchange row maximum and row sum through shared
+//                 memory.  Epilogue O / rowsum -> bf16
 //
 // TMEM region (256 columns): S [0, nk16) in nchunks chunks of 32 columns, the first n_a of them
 // owned by column half A.  P (bf16, 16 columns per chunk) overwrites columns its own half has
@@ -25,6 +27,8 @@
 // with the score matrix in HBM), src/models/smolvla.cpp:835-842,874-881 (ggml_flash_attn_ext);
 // masks src/models/pi0.cpp:640-651, smolvla.cpp:1655-1664.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 #include "host_common.h"
 #include "tc5.cuh"
@@ -151,6 +155,12 @@ __device__ __forceinline__ void att_exp_chunk(const uint32_t (&sv)[32], int c, c
     tmem_st16(p_addr, pk);
 }
 
+// SP (single pass, key ranges of more than 128 keys): the two column halves of a row are independent softmax problems.
+// Each walks its chunks ONCE with a lazily raised reference (the first chunk's maximum; raised, with the P chunks already
+// written rescaled in TMEM, only when a later chunk exceeds it by more than 2^8), P V of each half accumulates into an O of
+// its own (columns 64.. and 192.., both inside consumed S columns: n_a is 4), and the epilogue merges the two like two key
+// slices.  This removes the maximum pass over S (a second round of TMEM loads) and the exchange in the middle of a unit.
+template <bool SP>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap q_map32,
                  const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -219,6 +229,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             }
         }
     }
+    if (SP) n_a = 4;
     const int pb_col = n_a * 32;  // P of the second half starts where its S columns start
     // O (64 columns) goes behind the P of the first half when that half's consumed S columns have room for it,
     // else behind the P of the second half.
@@ -287,7 +298,7 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                     // P V over the keys of the column half whose consumed S columns hold O (O may only be
                     // written once that half has finished reading S), then over the other half's keys
                     const int n_k16 = p.nk16 / 16;
-                    const int first = (n_a >= 4) ? 0 : 1;
+                    const int first = (SP || n_a >= 4) ? 0 : 1;
                     uint32_t acc = 0u;
                     for (int part = 0; ok && part < 2; ++part) {
                         const int h = part ^ first;
@@ -296,9 +307,11 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                         ok = mbar_wait(&bar_p[2 * r + h], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
                         if (!ok) break;
                         tc_fence_after();
+                        if (SP) acc = 0u;  // an accumulator per half
+                        const uint32_t o_dst = SP ? (h ? 192u : 64u) : (uint32_t)o_col;
                         for (int k16 = k_lo; k16 < k_hi; ++k16) {
                             const uint32_t p_col = h ? (uint32_t)(pb_col + (k16 - k16_a) * 8) : (uint32_t)(k16 * 8);
-                            mma_f16_tmem_a(treg + (uint32_t)o_col, treg + p_col, smem_desc_sw128(v_addr + k16 * 2048, 16, 1024),
+                            mma_f16_tmem_a(treg + o_dst, treg + p_col, smem_desc_sw128(v_addr + k16 * 2048, 16, 1024),
                                            idesc_o, acc);
                             acc = 1u;
                         }
@@ -348,6 +361,49 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 ok = mbar_wait(&bar_s[r], k_unit & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
+                float sum_half;
+                if (SP) {
+                    // ---- one pass: reference = the first chunk's maximum, raised lazily ----
+                    float sum0 = 0.0f, sum1 = 0.0f;
+                    float m_ref = -INFINITY;  // log2 units
+                    if (warp_active) {
+                        for (int c = c_begin; c < c_end; ++c) {
+                            uint32_t sa[32];
+                            tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);
+                            tmem_ld_wait();
+                            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                            att_max_chunk(sa, c, rm, mx);
+                            const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+                            const bool raise = cm > m_ref + 8.0f;
+                            if (c > c_begin && __any_sync(0xffffffffu, raise)) {
+                                // rare: the P chunks written so far are relative to the old reference
+                                const float f = raise ? (m_ref == -INFINITY ? 0.0f : ex2_approx(m_ref - cm)) : 1.0f;
+                                tmem_st_wait();
+                                for (int cc = c_begin; cc < c; ++cc) {
+                                    uint32_t pk[16];
+                                    tmem_ld16(p_base + (uint32_t)((cc - c_begin) * 16), pk);
+                                    tmem_ld_wait();
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j) {
+                                        const float a = __uint_as_float(pk[j] << 16) * f, b = __uint_as_float(pk[j] & 0xffff0000u) * f;
+                                        pk[j] = __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);
+                                    }
+                                    tmem_st16(p_base + (uint32_t)((cc - c_begin) * 16), pk);
+                                }
+                                sum0 *= f;
+                                sum1 *= f;
+                                tmem_ld32(lane_addr + (uint32_t)(c * 32), sa);  // (not kept in registers across the rescaling)
+                                tmem_ld_wait();
+                            }
+                            if (raise) m_ref = cm;
+                            att_exp_chunk(sa, c, rm, p.scale_log2, m_ref == -INFINITY ? 0.0f : m_ref, sum0, sum1,
+                                          p_base + (uint32_t)((c - c_begin) * 16));
+                        }
+                        tmem_st_wait();
+                    }
+                    x_max[half * 128 + my_row_slot] = m_ref;
+                    sum_half = sum0 + sum1;
+                } else {
                 // ---- pass 1: maximum over this thread's columns ----
                 float mxx = -INFINITY;
                 if (warp_active) {
@@ -375,16 +431,35 @@ attn_hd64_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                     }
                     tmem_st_wait();
                 }
-                x_sum[half * 128 + my_row_slot] = sum0 + sum1;
+                sum_half = sum0 + sum1;
+                }
+                x_sum[half * 128 + my_row_slot] = sum_half;
                 tc_fence_before();
                 mbar_arrive(&bar_p[2 * r + half]);
                 ok = mbar_wait(&bar_o[r], k_unit & 1u, wc, DEV_TIMEOUT_ACCUM);
                 if (!ok) break;
                 tc_fence_after();
                 region_sync(r);  // both halves' partial sums are in shared memory
-                const float sum = x_sum[my_row_slot] + x_sum[128 + my_row_slot];
+                float sum = x_sum[my_row_slot] + x_sum[128 + my_row_slot];
                 uint32_t o[32];
-                if (warp_active) {
+                if (SP) {
+                    // merge the two halves: O = (wA O_A + wB O_B) / (wA l_A + wB l_B)
+                    const float mA = x_max[my_row_slot], mB = x_max[128 + my_row_slot], mm = fmaxf(mA, mB);
+                    const float wA = mA == -INFINITY ? 0.0f : ex2_approx(mA - mm), wB = mB == -INFINITY ? 0.0f : ex2_approx(mB - mm);
+                    sum = wA * x_sum[my_row_slot] + wB * x_sum[128 + my_row_slot];
+                    if (warp_active) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            uint32_t oa[16], ob[16];
+                            tmem_ld16(lane_addr + (uint32_t)(64 + half * 32 + 16 * j), oa);
+                            tmem_ld16(lane_addr + (uint32_t)(192 + half * 32 + 16 * j), ob);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                o[16 * j + e] = __float_as_uint(fmaf(wA, __uint_as_float(oa[e]), wB * __uint_as_float(ob[e])));
+                        }
+                    }
+                } else if (warp_active) {
                     tmem_ld32(lane_addr + (uint32_t)(o_col + half * 32), o);
                     tmem_ld_wait();
                 }
@@ -497,10 +572,14 @@ int vb::attention_ws(const vlab200_kv_store *st, int layer, const void *q, void 
     p.out_al32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 ? 1 : 0;
     p.status = status;
     const int smem = vb::ATT_SMEM_DATA + 256 + 2 * 512 * 4 + 1024;
-    int rc_attr = vb::ensure_dyn_smem(vb::attn_hd64_kernel, smem);
+    // more than 128 keys (5 to 8 chunks of 32): the single-pass variant; VLAB200_ATTN_TWO_PASS=1 keeps the two-pass one
+    static const bool two_pass_env = std::getenv("VLAB200_ATTN_TWO_PASS") != nullptr;
+    const bool single_pass = (p.nk16 + 31) / 32 >= 5 && !two_pass_env;
+    auto kernel = single_pass ? vb::attn_hd64_kernel<true> : vb::attn_hd64_kernel<false>;
+    int rc_attr = vb::ensure_dyn_smem(kernel, smem);
     if (rc_attr) return rc_attr;
     const int n_sm = vb::sm_count();
     const int grid = p.n_items < n_sm ? p.n_items : n_sm;
-    return vb::launch_pdl(vb::attn_hd64_kernel, dim3(grid), dim3(vb::ATT_THREADS), smem, static_cast<cudaStream_t>(stream), qmap,
-                          qmap32, kmap, vmap, p);
+    return vb::launch_pdl(kernel, dim3(grid), dim3(vb::ATT_THREADS), smem, static_cast<cudaStream_t>(stream), qmap, qmap32, kmap, vmap,
+                          p);
 }
