@@ -300,7 +300,7 @@ def measure_pi0(torch, vb, dev, n_obs, steps, warmup, seed, barrier=None, allow_
     sync()
     graph_ms = None
     if n_obs <= 8 and allow_graph and not (n_obs == 1 and os.environ.get("VLAB200_CHUNK_LOOP") != "0"):
-        # small batches are launch- and latency-bound (943 launches per chunk): the same loop replayed as one CUDA graph
+        # small batches on the launch-per-operator path are latency-bound (~1,600 launches per chunk): the same loop replayed as one CUDA graph
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
