@@ -80,3 +80,16 @@ def test_loop_kernel_full_depth_against_oracle(oracle, policy):
                                                **SMOLVLA_FULL))
     print(f"loop kernel {policy} full depth: rel_l2={w:.3e} displacement rel_l2={d:.3e}")
     assert w < 1e-2 and d < 3e-2, (w, d)
+
+
+def test_loop_kernel_other_shapes_against_oracle(oracle):
+    """head_dim 128 (its own kernel instantiation), and a small SmolVLA-shaped expert with cross-attention layers, a hidden key
+    range and rebased suffix positions; one observation each, so both take the loop kernel."""
+    from tests.test_engine_gpu import run_case
+
+    w, d = _with_loop("1", lambda: run_case(oracle, 73, n_obs=1, P=40, model=0, L=2, H=128, n_q=2, n_kv=1, hd=128, inter=256,
+                                           chunk=10, A=32, sd=32, T=2))
+    assert w < 1e-2 and d < 3e-2, (w, d)
+    w, d = _with_loop("1", lambda: run_case(oracle, 74, n_obs=1, P=30, pos_base=27, pad=(20, 29), model=1, L=4, H=192, n_q=6, n_kv=2,
+                                           hd=64, inter=384, chunk=10, A=32, sd=32, T=2, self_every=2))
+    assert w < 1e-2 and d < 3e-2, (w, d)
