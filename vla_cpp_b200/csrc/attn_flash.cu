@@ -414,8 +414,8 @@ struct FlashPairSmem {
     static constexpr int V_BYTES = CBH * FP_BKV * 128;       // [CBH][128 keys][128 B]: this CTA's half of the head dimension
     static constexpr int K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * K_BYTES;
     static constexpr int BAR_OFF = V_OFF + STAGES * V_BYTES;
-    static constexpr int XCH_OFF = BAR_OFF + 512;      // float [2 halves][128 rows] block maxima, then row sums
-    static constexpr int TOTAL = XCH_OFF + 2048 + 1024;
+    static constexpr int XCH_OFF = BAR_OFF + 512;      // float [2 halves][128 rows] block maxima, then row sums, then the maxima of odd blocks
+    static constexpr int TOTAL = XCH_OFF + 3072 + 1024;
     static constexpr int O_COLS = HD;
     static constexpr int TMEM_COLS = 512;              // O [0, HD), then NS S buffers of 128 columns
     static_assert(HD + NS * FP_BKV <= 512 && NS >= 2, "TMEM");
@@ -449,6 +449,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint64_t *pair_bar = bars + 32;  // [4] the two softmax warps of a lane quarter meet here (64 arrivals)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 36);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile uint32_t *pv_issued = reinterpret_cast<volatile uint32_t *>(tmem_slot + 2);  // P V blocks issued so far (even CTA)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -477,6 +478,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&pv_done[i], 1);
         }
         *abort_flag = 0;
+        *pv_issued = 0;
         fence_barrier_init();
     }
     __syncthreads();
@@ -554,9 +556,25 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // used the same TMEM buffer (jbx - FP_NS) has finished.  This thread issues only the Q K^T MMAs
             // (16 per block, the longer stream); the P V MMAs come from a thread of their own (warp
             // FP_PV_WARP): one thread issuing both spent ~2500 cycles per block, twice the tensor time.
+            // It does not wait for that P V block to COMPLETE: the tensor pipe takes the MMAs of a CTA pair in the order
+            // they were issued, so it is enough that the P V thread has issued them (a counter in shared memory that
+            // it bumps after its last MMA of a block).  Waiting for the commit instead kept the pipe idle for the
+            // ~500 cycles between the block's last MMA and the moment this thread saw the barrier flip.
             auto ready_s = [&](uint32_t jbx) -> bool {
                 bool r = mbar_wait(&k_full[jbx % FP_STAGES], (jbx / FP_STAGES) & 1u, wc, DEV_TIMEOUT_FULL);
-                if (r && jbx >= FP_NS) r = mbar_wait(&pv_done[jbx % FP_NS], ((jbx / FP_NS) - 1u) & 1u, wc, DEV_TIMEOUT_FULL);
+                if (r && jbx >= FP_NS && *pv_issued < jbx - FP_NS + 1u) {
+                    const long long t0 = clock64();
+                    for (uint32_t it = 1; *pv_issued < jbx - FP_NS + 1u; ++it) {
+                        if ((it & 63u) == 0) {
+                            if (*abort_flag) return false;
+                            if (clock64() - t0 > wc.budget) {
+                                *abort_flag = 1;
+                                atomicCAS(p.status, 0, (int)DEV_TIMEOUT_FULL);
+                                return false;
+                            }
+                        }
+                    }
+                }
                 return r;
             };
             for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
@@ -612,6 +630,7 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     for (int k16 = 0; k16 < FP_BKV / 16; ++k16)
                         mma_f16_tmem_a_pair(tmem_base, p_tmem + (uint32_t)(k16 * 8), v_desc + (uint64_t)(k16 * 128), idesc_o,
                                             (j | k16) != 0 ? 1u : 0u);
+                    *pv_issued = jb + 1u;
                     tc_commit_pair(&pv_done[sb], 3);
                     tc_commit_pair(&v_free[st], 3);
                 }
@@ -695,12 +714,11 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                                  fmaxf(fmaxf(__uint_as_float(sc[4 * e]), __uint_as_float(sc[4 * e + 1])),
                                        fmaxf(__uint_as_float(sc[4 * e + 2]), __uint_as_float(sc[4 * e + 3]))));
                 float bm = fmaxf(fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])), fmaxf(fmaxf(t[4], t[5]), fmaxf(t[6], t[7])));
-                xch[half * 128 + my_slot] = bm;
+                float *xm = xch + (jb & 1u) * 512;  // two sets of slots, used in turn: one meeting per block is enough
+                xm[half * 128 + my_slot] = bm;
                 ok = pair_sync();
                 if (!ok) break;
-                bm = fmaxf(bm, xch[(half ^ 1) * 128 + my_slot]) * p.scale_log2;
-                ok = pair_sync();  // the slot is rewritten in the next block
-                if (!ok) break;
+                bm = fmaxf(bm, xm[(half ^ 1) * 128 + my_slot]) * p.scale_log2;
                 float factor = 1.0f;
                 const bool raise = bm > m_used + 8.0f;
                 if (raise) {
