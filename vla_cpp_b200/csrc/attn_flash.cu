@@ -661,18 +661,65 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 else mbar_arrive_cluster(bar, 0);
             }
         };
+        // The O drain of a unit runs AFTER the first S block of the next unit: that block only needs its S buffer, and the
+        // ~2000 cycles between a unit's last P and "O complete" (its last P V) are spent on it instead of on waiting.
+        auto drain = [&](uint32_t u, float l_mine, __nv_bfloat16 *dst, bool row_ok) -> bool {
+            xch[256 + half * 128 + my_slot] = l_mine;
+            if (!mbar_wait(o_done, u & 1u, wc, DEV_TIMEOUT_ACCUM)) return false;
+            tc_fence_after();
+            if (!pair_sync()) return false;
+            const float inv = 1.0f / (l_mine + xch[256 + (half ^ 1) * 128 + my_slot]);
+            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int q8 = 0; q8 < 2; ++q8) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[16 * q8 + 2 * e]) * inv,
+                                                                           __uint_as_float(ov[16 * q8 + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        if (p.out_al32) {  // one full 32-byte sector per store instruction and thread
+                            st_global_v8(dst + c + 16 * q8, w);
+                        } else {
+                            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c + 16 * q8);
+                            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    }
+                }
+            }
+            // (the row-sum slots are next written after at least two more meetings of the pair)
+            tc_fence_before();
+            arrive_even(o_free);
+            return true;
+        };
         uint32_t ui = 0, jb = 0;
         bool ok = true;
+        float prev_l = 0.0f;  // the unit whose O is still to be drained
+        __nv_bfloat16 *prev_dst = nullptr;
+        bool prev_row_ok = false;
+        int pad_lo = 0, pad_hi = 0;  // of the unit about to start (read one unit ahead: a global-memory round trip)
+        if (p.pad && cid < n_units) {
+            const int obs0 = (cid / n_mt2) / p.n_kv;
+            pad_lo = p.pad[2 * obs0];
+            pad_hi = p.pad[2 * obs0 + 1];
+        }
         for (int unit = cid; ok && unit < n_units; unit += ncl, ++ui) {
             const int item = unit / n_mt2, mt = (unit % n_mt2) * 2 + (int)rank;
             const int obs = item / p.n_kv, kvh = item % p.n_kv;
             const int row = mt * 128 + qtr * 32 + lane;
             const bool row_ok = row < p.R;
             const int head_l = row_ok ? row / p.S : 0, tok = row_ok ? row % p.S : 0;
-            int pad_lo = 0, pad_hi = 0;
-            if (p.pad) {
-                pad_lo = p.pad[2 * obs];
-                pad_hi = p.pad[2 * obs + 1];
+            int pad_lo_n = 0, pad_hi_n = 0;
+            if (p.pad && unit + ncl < n_units) {
+                const int obs_n = ((unit + ncl) / n_mt2) / p.n_kv;
+                pad_lo_n = p.pad[2 * obs_n];
+                pad_hi_n = p.pad[2 * obs_n + 1];
             }
             int limit = n_suffix_cols;
             if (p.mask_mode == 2) limit = min(tok + 1, n_suffix_cols);
@@ -762,45 +809,23 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tmem_st_wait();
                 tc_fence_before();
                 arrive_even(&p_full[sb]);
-            }
-            if (!ok) break;
-            // ---- epilogue: O / l -> bf16 -> out (each half stores half of the head dimension) ----
-            xch[256 + half * 128 + my_slot] = l_sum;
-            ok = mbar_wait(o_done, ui & 1u, wc, DEV_TIMEOUT_ACCUM);
-            if (!ok) break;
-            tc_fence_after();
-            ok = pair_sync();
-            if (!ok) break;
-            const float inv = 1.0f / (l_sum + xch[256 + (half ^ 1) * 128 + my_slot]);
-            __nv_bfloat16 *dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
-            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-                uint32_t ov[32];
-                tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
-                tmem_ld_wait();
-                if (row_ok) {
-#pragma unroll
-                    for (int q8 = 0; q8 < 2; ++q8) {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[16 * q8 + 2 * e]) * inv,
-                                                                           __uint_as_float(ov[16 * q8 + 2 * e + 1]) * inv);
-                            w[e] = *reinterpret_cast<const uint32_t *>(&h);
-                        }
-                        if (p.out_al32) {  // one full 32-byte sector per store instruction and thread
-                            st_global_v8(dst + c + 16 * q8, w);
-                        } else {
-                            uint4 *d4 = reinterpret_cast<uint4 *>(dst + c + 16 * q8);
-                            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        }
+                if (j == 0 && ui > 0) {
+                    ok = drain(ui - 1, prev_l, prev_dst, prev_row_ok);
+                    if (!ok) {
+                        ++jb;
+                        break;
                     }
                 }
             }
-            // (the row-sum slots are next written after at least two more meetings of the pair)
-            tc_fence_before();
-            arrive_even(o_free);
+            if (!ok) break;
+            // ---- O / l -> bf16 -> out (each half stores half of the head dimension): after the next unit's first block ----
+            prev_l = l_sum;
+            prev_dst = p.out + ((size_t)obs * p.S + tok) * ((size_t)p.n_q * HD) + (size_t)(kvh * p.g + head_l) * HD;
+            prev_row_ok = row_ok;
+            pad_lo = pad_lo_n;
+            pad_hi = pad_hi_n;
         }
+        if (ok && ui > 0) ok = drain(ui - 1, prev_l, prev_dst, prev_row_ok);
     }
     tc_fence_before();
     __syncthreads();
