@@ -265,12 +265,20 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const bool clean = c0 + FA_BKV <= clean_end;
                 if (!clean) {
                     const int rel_jmax = jmax - c0, rel_pad = pad_lo - c0;
+                    if (pad_w <= 0) {  // the usual case (no hidden range in this unit): one comparison per column
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
-                        const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
-                        sa[e] = v0 ? sa[e] : 0xff800000u;
-                        sb[e] = v1 ? sb[e] : 0xff800000u;
+                        for (int e = 0; e < 32; ++e) {
+                            sa[e] = e < rel_jmax ? sa[e] : 0xff800000u;
+                            sb[e] = e + 32 < rel_jmax ? sb[e] : 0xff800000u;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
+                            const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
+                            sa[e] = v0 ? sa[e] : 0xff800000u;
+                            sb[e] = v1 ? sb[e] : 0xff800000u;
+                        }
                     }
                 }
                 float t[8];
@@ -745,12 +753,20 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const bool clean = j * FP_BKV + FP_BKV <= clean_end;
                 if (!clean) {
                     const int rel_jmax = jmax - c0, rel_pad = pad_lo - c0;
+                    if (pad_w <= 0) {  // the usual case (no hidden range in this unit): one comparison per column
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
-                        const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
-                        sa[e] = v0 ? sa[e] : 0xff800000u;
-                        sc[e] = v1 ? sc[e] : 0xff800000u;
+                        for (int e = 0; e < 32; ++e) {
+                            sa[e] = e < rel_jmax ? sa[e] : 0xff800000u;
+                            sc[e] = e + 32 < rel_jmax ? sc[e] : 0xff800000u;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const bool v0 = e < rel_jmax && !((unsigned)(e - rel_pad) < (unsigned)pad_w);
+                            const bool v1 = e + 32 < rel_jmax && !((unsigned)(e + 32 - rel_pad) < (unsigned)pad_w);
+                            sa[e] = v0 ? sa[e] : 0xff800000u;
+                            sc[e] = v1 ? sc[e] : 0xff800000u;
+                        }
                     }
                 }
                 float t[8];
