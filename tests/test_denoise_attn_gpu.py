@@ -240,6 +240,21 @@ def test_attention_streaming_kernel_other_shapes(oracle, tiling):
     assert attn_case(oracle, 1, 8, 1, 5, 3, 2, seed=215, hd=256, tiling=tiling) < TOL
 
 
+def test_attention_pair_kernel_several_units_per_cta_pair(oracle):
+    """More work units than CTA pairs: a pair drains a unit's O after the first key block of its next unit, reads that
+    unit's hidden key range one unit ahead and keeps its block counters running across units.  Every observation is
+    compared with the oracle; hidden ranges differ between neighbours."""
+    require_cuda()
+    n_obs = 100  # x 2 tile pairs = 200 units on 74 CTA pairs
+    pads = [((7 * b) % 90, (7 * b) % 90 + (b % 3) * 20) for b in range(n_obs)]
+    # two key blocks (130 + 51 keys), pi0 mask, hidden ranges
+    assert attn_case(oracle, n_obs, 8, 1, 51, 130, 1, seed=230, hd=256, pads=pads, tiling=3) < TOL
+    # one key block per unit (60 + 51 keys <= 128): the drain follows directly
+    assert attn_case(oracle, n_obs, 8, 1, 51, 60, 2, seed=231, hd=256, tiling=3) < TOL
+    # head_dim 128 (three S buffers), five key blocks, bidirectional
+    assert attn_case(oracle, 90, 8, 2, 50, 500, 0, seed=232, hd=128, tiling=3) < TOL
+
+
 @pytest.mark.parametrize("tiling", [1, 3])
 def test_attention_streaming_kernel_large_score_spread(oracle, tiling):
     """Keys whose scores grow along the sequence force the lazy running-maximum update (and the
