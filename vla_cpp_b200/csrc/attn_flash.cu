@@ -184,9 +184,9 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const int j0 = SPLIT ? sp * nb / ns : 0, j1 = SPLIT ? (sp + 1) * nb / ns : nb;
                 ok = mbar_wait(q_full, ui & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
-                // first S block of the unit: its TMEM buffer was last read by the P V of block jb-2
+                // first S block of the unit: its TMEM buffer was last read by the P V of block jb-2, which this thread
+                // issued earlier -- the tensor pipe runs a thread's MMAs in issue order, so there is nothing to wait for
                 ok = mbar_wait(&k_full[jb & 1u], (jb >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
-                if (ok && jb >= 2) ok = mbar_wait(&pv_done[jb & 1u], ((jb - 2) >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
                 issue_s(jb);
@@ -196,7 +196,6 @@ attn_flash_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (j + 1 < j1) {
                         const uint32_t jn = jb + 1;
                         ok = mbar_wait(&k_full[jn & 1u], (jn >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
-                        if (ok && jn >= 2) ok = mbar_wait(&pv_done[jn & 1u], ((jn - 2) >> 1) & 1u, wc, DEV_TIMEOUT_FULL);
                         if (!ok) break;
                         tc_fence_after();
                         issue_s(jn);
