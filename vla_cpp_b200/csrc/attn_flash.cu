@@ -680,6 +680,10 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 uint32_t ov[32];
                 tmem_ld32(tmem_base + lane_sel + (uint32_t)c, ov);
                 tmem_ld_wait();
+                if (c + 32 >= (half + 1) * (HD / 2)) {  // O is out of TMEM: the next unit's P V may start while the last stores go out
+                    tc_fence_before();
+                    arrive_even(o_free);
+                }
                 if (row_ok) {
 #pragma unroll
                     for (int q8 = 0; q8 < 2; ++q8) {
@@ -701,8 +705,6 @@ attn_flash_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             }
             // (the row-sum slots are next written after at least two more meetings of the pair)
-            tc_fence_before();
-            arrive_even(o_free);
             return true;
         };
         uint32_t ui = 0, jb = 0;
